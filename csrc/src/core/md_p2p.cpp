@@ -1,0 +1,204 @@
+#include "core/md_p2p.h"
+
+#include <arpa/inet.h>
+#include <cerrno>
+#include <cstring>
+#include <fcntl.h>
+#include <netdb.h>
+#include <netinet/in.h>
+#include <netinet/tcp.h>
+#include <poll.h>
+#include <sys/socket.h>
+#include <unistd.h>
+
+#include <algorithm>
+#include <chrono>
+
+#include "utils/log.h"
+
+namespace nixl_p2p {
+namespace {
+constexpr char kLoad[] = "NIXLCOMM:LOAD";
+constexpr char kSend[] = "NIXLCOMM:SEND";
+constexpr char kInvl[] = "NIXLCOMM:INVL";
+
+int64_t nowMs() {
+    return std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now().time_since_epoch()).count();
+}
+
+bool writeAll(int fd, const char *p, size_t n) {
+    while (n) {
+        const ssize_t w = ::send(fd, p, n, MSG_NOSIGNAL);
+        if (w < 0) {
+            if (errno == EINTR) continue;
+            if (errno == EAGAIN || errno == EWOULDBLOCK) {
+                pollfd pf{fd, POLLOUT, 0};
+                if (::poll(&pf, 1, kBodyTimeoutMs) <= 0) return false;
+                continue;
+            }
+            return false;
+        }
+        p += w;
+        n -= static_cast<size_t>(w);
+    }
+    return true;
+}
+
+bool readAll(int fd, char *p, size_t n, int timeout_ms) {
+    const int64_t deadline = nowMs() + timeout_ms;
+    while (n) {
+        const int64_t left = deadline - nowMs();
+        if (left <= 0) return false;
+        pollfd pf{fd, POLLIN, 0};
+        const int pr = ::poll(&pf, 1, static_cast<int>(left));
+        if (pr < 0 && errno == EINTR) continue;
+        if (pr <= 0) return false;
+        const ssize_t r = ::recv(fd, p, n, 0);
+        if (r == 0) return false;
+        if (r < 0) {
+            if (errno == EINTR || errno == EAGAIN || errno == EWOULDBLOCK) continue;
+            return false;
+        }
+        p += r;
+        n -= static_cast<size_t>(r);
+    }
+    return true;
+}
+} // namespace
+
+bool sendFrame(int fd, const std::string &body) {
+    const uint64_t n = body.size();
+    return writeAll(fd, reinterpret_cast<const char *>(&n), sizeof(n)) && writeAll(fd, body.data(), body.size());
+}
+
+bool recvFrame(int fd, std::string &body, int timeout_ms) {
+    uint64_t n = 0;
+    if (!readAll(fd, reinterpret_cast<char *>(&n), sizeof(n), timeout_ms)) return false;
+    if (n > kMaxFrame) {
+        NIXL_ERROR << "p2p metadata: frame of " << n << " bytes exceeds the limit";
+        return false;
+    }
+    body.resize(n);
+    return n == 0 || readAll(fd, body.data(), n, kBodyTimeoutMs);
+}
+
+int dial(const std::string &ip, int port, int timeout_ms) {
+    addrinfo hints{}, *res = nullptr;
+    hints.ai_family = AF_UNSPEC;
+    hints.ai_socktype = SOCK_STREAM;
+    if (getaddrinfo(ip.c_str(), std::to_string(port).c_str(), &hints, &res) != 0 || !res) return -1;
+    int fd = -1;
+    for (addrinfo *a = res; a; a = a->ai_next) {
+        fd = ::socket(a->ai_family, a->ai_socktype | SOCK_NONBLOCK, a->ai_protocol);
+        if (fd < 0) continue;
+        int rc = ::connect(fd, a->ai_addr, a->ai_addrlen);
+        if (rc != 0 && errno == EINPROGRESS) {
+            pollfd pf{fd, POLLOUT, 0};
+            if (::poll(&pf, 1, timeout_ms) == 1) {
+                int err = 0;
+                socklen_t len = sizeof(err);
+                getsockopt(fd, SOL_SOCKET, SO_ERROR, &err, &len);
+                rc = err ? -1 : 0;
+            } else rc = -1;
+        }
+        if (rc == 0) break;
+        ::close(fd);
+        fd = -1;
+    }
+    freeaddrinfo(res);
+    if (fd >= 0) {
+        int one = 1;
+        setsockopt(fd, IPPROTO_TCP, TCP_NODELAY, &one, sizeof(one));
+    }
+    return fd;
+}
+} // namespace nixl_p2p
+
+using namespace nixl_p2p;
+
+nixlP2PListener::nixlP2PListener(nixlMetadataContext &ctx, uint16_t port, uint64_t poll_delay_us)
+    : ctx_(ctx), delayUs_(poll_delay_us ? poll_delay_us : 100000) {
+    listenFd_ = ::socket(AF_INET, SOCK_STREAM | SOCK_NONBLOCK, 0);
+    if (listenFd_ < 0) return;
+    int one = 1;
+    setsockopt(listenFd_, SOL_SOCKET, SO_REUSEADDR, &one, sizeof(one));
+    sockaddr_in addr{};
+    addr.sin_family = AF_INET;
+    addr.sin_addr.s_addr = htonl(INADDR_ANY);
+    addr.sin_port = htons(port);
+    if (::bind(listenFd_, reinterpret_cast<sockaddr *>(&addr), sizeof(addr)) != 0 || ::listen(listenFd_, 64) != 0) {
+        NIXL_ERROR << "p2p metadata listener: cannot bind port " << port << ": " << std::strerror(errno);
+        ::close(listenFd_);
+        listenFd_ = -1;
+        return;
+    }
+    socklen_t len = sizeof(addr);
+    getsockname(listenFd_, reinterpret_cast<sockaddr *>(&addr), &len);
+    port_ = ntohs(addr.sin_port);
+}
+
+nixlP2PListener::~nixlP2PListener() {
+    stop();
+    if (listenFd_ >= 0) ::close(listenFd_);
+    for (int fd : clients_) ::close(fd);
+}
+
+void nixlP2PListener::start() {
+    if (listenFd_ < 0 || th_.joinable()) return;
+    stop_ = false;
+    th_ = std::thread([this] { loop(); });
+}
+
+void nixlP2PListener::stop() {
+    stop_ = true;
+    if (th_.joinable()) th_.join();
+}
+
+void nixlP2PListener::loop() {
+    const int wait_ms = static_cast<int>(std::max<uint64_t>(1, std::min<uint64_t>(delayUs_ / 1000, 200)));
+    while (!stop_) {
+        std::vector<pollfd> fds;
+        fds.push_back({listenFd_, POLLIN, 0});
+        for (int fd : clients_) fds.push_back({fd, POLLIN, 0});
+        const int pr = ::poll(fds.data(), fds.size(), wait_ms);
+        if (pr <= 0) continue;
+        if (fds[0].revents & POLLIN) {
+            const int c = ::accept4(listenFd_, nullptr, nullptr, SOCK_NONBLOCK);
+            if (c >= 0) {
+                int one = 1;
+                setsockopt(c, IPPROTO_TCP, TCP_NODELAY, &one, sizeof(one));
+                clients_.push_back(c);
+            }
+        }
+        for (size_t i = 1; i < fds.size(); ++i)
+            if (fds[i].revents & (POLLIN | POLLHUP | POLLERR)) serve(fds[i].fd);
+    }
+}
+
+// Handle one frame from a client; drops the connection on EOF or protocol error.
+void nixlP2PListener::serve(int fd) {
+    auto drop = [&] {
+        ::close(fd);
+        clients_.erase(std::remove(clients_.begin(), clients_.end(), fd), clients_.end());
+    };
+    std::string body;
+    if (!recvFrame(fd, body, 50)) return drop();
+    auto is = [&](const char *cmd) { return body.compare(0, std::strlen(cmd), cmd) == 0; };
+    if (is(kLoad)) {
+        std::string who;
+        const nixl_status_t st = ctx_.mdLoadRemote(body.substr(std::strlen(kLoad)), who);
+        if (st != NIXL_SUCCESS) NIXL_ERROR << "p2p metadata: received metadata was rejected: " << nixlEnumStrings::statusStr(st);
+    } else if (is(kSend)) {
+        nixl_blob_t mine;
+        if (ctx_.mdGetLocal(mine) == NIXL_SUCCESS) {
+            if (!sendFrame(fd, std::string(kLoad) + mine)) return drop();
+        } else {
+            sendFrame(fd, std::string(kInvl) + ctx_.mdAgentName()); // nothing to offer
+        }
+    } else if (is(kInvl)) {
+        ctx_.mdInvalidateRemote(body.substr(std::strlen(kInvl)));
+    } else {
+        NIXL_ERROR << "p2p metadata: unknown command";
+        return drop();
+    }
+}

@@ -1,0 +1,1177 @@
+#include "plugins/nvlink/nvlink_backend.h"
+
+#include <cerrno>
+#include <csignal>
+#include <cstring>
+#include <random>
+#include <sys/socket.h>
+#include <sys/uio.h>
+#include <sys/un.h>
+#include <unistd.h>
+
+#include <algorithm>
+
+#include "backend/backend_plugin.h"
+#include "device/nixl_device_layout.h"
+#include "serdes/serdes.h"
+#include "utils/log.h"
+
+namespace nixl_nvlink {
+namespace {
+
+// ---------------------------------------------------------------- process-wide state
+
+uint64_t random64() {
+    static std::mutex mu;
+    static std::mt19937_64 gen{std::random_device{}() ^ (static_cast<uint64_t>(::getpid()) << 32)};
+    std::lock_guard<std::mutex> g(mu);
+    return gen();
+}
+
+uint64_t processTag() {
+    static const uint64_t tag = random64() | 1;
+    return tag;
+}
+
+std::string hostName() {
+    char buf[256] = {0};
+    if (::gethostname(buf, sizeof(buf) - 1) != 0) return "localhost";
+    return buf;
+}
+
+// Engines alive in this process, by agent name: same-process peers talk directly.
+std::mutex g_regMu;
+std::unordered_map<std::string, Engine *> g_registry;
+
+// CUDA IPC mappings are per process, not per engine: two agents (or two registrations that
+// share one allocation) must not open the same handle twice.
+struct IpcMapping {
+    void *base = nullptr;
+    int refs = 0;
+    int device = -1;
+};
+std::mutex g_ipcMu;
+std::unordered_map<std::string, IpcMapping> g_ipc;
+
+std::mutex g_peerAccessMu;
+std::vector<std::pair<int, int>> g_peerAccess;
+
+// RAII: run a block with a given current device, then restore the caller's.
+class DeviceScope {
+public:
+    explicit DeviceScope(int dev) {
+        if (cudaGetDevice(&prev_) != cudaSuccess) prev_ = -1;
+        if (dev >= 0 && dev != prev_) {
+            cudaSetDevice(dev);
+            changed_ = true;
+        }
+    }
+    ~DeviceScope() {
+        if (changed_ && prev_ >= 0) cudaSetDevice(prev_);
+    }
+
+private:
+    int prev_ = -1;
+    bool changed_ = false;
+};
+
+bool cudaOk(cudaError_t e, const char *what) {
+    if (e == cudaSuccess) return true;
+    NIXL_ERROR << "NVLINK backend: " << what << " failed: " << cudaGetErrorString(e);
+    cudaGetLastError(); // clear the sticky-less error so later calls are not blamed
+    return false;
+}
+
+// cuMemGetAddressRange through the runtime's driver entry point (no link against libcuda).
+bool allocationRange(uintptr_t ptr, uintptr_t &base, size_t &size) {
+    using fn_t = int (*)(unsigned long long *, size_t *, unsigned long long);
+    static fn_t fn = [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<fn_t>(p);
+    }();
+    if (!fn) return false;
+    unsigned long long b = 0;
+    size_t s = 0;
+    if (fn(&b, &s, ptr) != 0) return false;
+    base = b;
+    size = s;
+    return true;
+}
+
+// ---------------------------------------------------------------- wire structs
+
+constexpr uint8_t kPubVersion = 1;
+
+#pragma pack(push, 1)
+struct PubReg {
+    uint8_t version;
+    uint8_t mem; // nixl_mem_t
+    uint8_t hasIpc;
+    uint8_t pad;
+    int32_t device;
+    uint64_t addr;
+    uint64_t len;
+    uint64_t ipcOffset;
+    uint64_t engineTag;
+    unsigned char ipc[sizeof(cudaIpcMemHandle_t)];
+};
+#pragma pack(pop)
+
+std::string encodePeer(const PeerId &p) {
+    nixlSerDes sd;
+    sd.addStr("agent", p.agent);
+    sd.addStr("host", p.host);
+    sd.addBuf("pid", &p.pid, sizeof(p.pid));
+    sd.addBuf("ptag", &p.procTag, sizeof(p.procTag));
+    sd.addBuf("etag", &p.engineTag, sizeof(p.engineTag));
+    sd.addStr("sock", p.sockName);
+    return sd.exportStr();
+}
+
+bool decodePeer(const std::string &blob, PeerId &p) {
+    nixlSerDes sd;
+    if (sd.importStr(blob) != NIXL_SUCCESS) return false;
+    p.agent = sd.getStr("agent");
+    p.host = sd.getStr("host");
+    if (sd.getBuf("pid", &p.pid, sizeof(p.pid)) != NIXL_SUCCESS) return false;
+    if (sd.getBuf("ptag", &p.procTag, sizeof(p.procTag)) != NIXL_SUCCESS) return false;
+    if (sd.getBuf("etag", &p.engineTag, sizeof(p.engineTag)) != NIXL_SUCCESS) return false;
+    p.sockName = sd.getStr("sock");
+    return !p.agent.empty() && !p.sockName.empty();
+}
+
+sockaddr_un abstractAddr(const std::string &name, socklen_t &len) {
+    sockaddr_un a{};
+    a.sun_family = AF_UNIX;
+    const size_t n = std::min(name.size(), sizeof(a.sun_path) - 2);
+    std::memcpy(a.sun_path + 1, name.data(), n); // leading NUL = abstract namespace
+    len = static_cast<socklen_t>(offsetof(sockaddr_un, sun_path) + 1 + n);
+    return a;
+}
+
+uint32_t log2Ceil(uint64_t v) {
+    uint32_t s = 0;
+    while ((uint64_t(1) << s) < v) ++s;
+    return s;
+}
+
+bool paramBool(const nixl_b_params_t &p, const char *key, bool dflt) {
+    auto it = p.find(key);
+    if (it == p.end()) return dflt;
+    const std::string &v = it->second;
+    return v == "1" || v == "true" || v == "yes" || v == "on" || v == "y";
+}
+
+long paramLong(const nixl_b_params_t &p, const char *key, long dflt) {
+    auto it = p.find(key);
+    if (it == p.end() || it->second.empty()) return dflt;
+    char *end = nullptr;
+    const long v = std::strtol(it->second.c_str(), &end, 0);
+    return end && *end == 0 ? v : dflt;
+}
+
+} // namespace
+
+// ================================================================ DeviceArena
+
+DeviceArena::~DeviceArena() {
+    DeviceScope ds(device_);
+    for (auto &s : slabs_) cudaFree(s.base);
+}
+
+void *DeviceArena::alloc(size_t bytes) {
+    bytes = (bytes + 255) & ~size_t(255);
+    std::lock_guard<std::mutex> g(mu_);
+    for (int pass = 0; pass < 2; ++pass) {
+        for (auto &s : slabs_) {
+            for (auto it = s.freeByOff.begin(); it != s.freeByOff.end(); ++it) {
+                if (it->second < bytes) continue;
+                const size_t off = it->first, sz = it->second;
+                s.freeByOff.erase(it);
+                if (sz > bytes) s.freeByOff[off + bytes] = sz - bytes;
+                s.used[off] = bytes;
+                return s.base + off;
+            }
+        }
+        if (pass == 1) break;
+        const size_t slab = std::max<size_t>(bytes, size_t(8) << 20);
+        DeviceScope ds(device_);
+        void *p = nullptr;
+        if (!cudaOk(cudaMalloc(&p, slab), "cudaMalloc(arena)")) return nullptr;
+        cudaMemset(p, 0, slab);
+        Slab s{static_cast<char *>(p), slab, {}, {}};
+        s.freeByOff[0] = slab;
+        slabs_.push_back(std::move(s));
+    }
+    return nullptr;
+}
+
+void DeviceArena::free(void *p) {
+    if (!p) return;
+    std::lock_guard<std::mutex> g(mu_);
+    for (auto &s : slabs_) {
+        char *c = static_cast<char *>(p);
+        if (c < s.base || c >= s.base + s.size) continue;
+        size_t off = static_cast<size_t>(c - s.base);
+        auto u = s.used.find(off);
+        if (u == s.used.end()) return;
+        size_t sz = u->second;
+        s.used.erase(u);
+        // coalesce with neighbours
+        auto next = s.freeByOff.find(off + sz);
+        if (next != s.freeByOff.end()) {
+            sz += next->second;
+            s.freeByOff.erase(next);
+        }
+        auto prev = s.freeByOff.lower_bound(off);
+        if (prev != s.freeByOff.begin()) {
+            --prev;
+            if (prev->first + prev->second == off) {
+                off = prev->first;
+                sz += prev->second;
+                s.freeByOff.erase(prev);
+            }
+        }
+        s.freeByOff[off] = sz;
+        return;
+    }
+}
+
+// ================================================================ Engine: lifecycle
+
+Engine::Engine(const nixlBackendInitParams *init) : nixlBackendEngine(init) {
+    const nixl_b_params_t &params = getCustomParams();
+    self_.agent = localAgent;
+    self_.host = hostName();
+    self_.pid = ::getpid();
+    self_.procTag = processTag();
+    self_.engineTag = random64() | 1;
+
+    int n = 0;
+    const bool want_cuda = paramBool(params, "use_cuda", true);
+    if (want_cuda && cudaGetDeviceCount(&n) == cudaSuccess && n > 0) {
+        cuda_ = true;
+        deviceCount_ = n;
+    } else {
+        cudaGetLastError();
+    }
+    pinDram_ = paramBool(params, "pin_dram", true);
+    auto cp = params.find("copy_path");
+    if (cp != params.end() && (cp->second == "bulk" || cp->second == "tma")) copyPath_ = CopyPath::BULK;
+    gridOverride_ = static_cast<int>(paramLong(params, "grid_ctas", 0));
+    livenessPing_ = paramBool(params, "liveness_ping", false);
+    const long dev = paramLong(params, "device_id", -1);
+    if (dev >= 0) primaryDevice_ = static_cast<int>(dev);
+
+    // Notification endpoint.
+    notifFd_ = ::socket(AF_UNIX, SOCK_DGRAM | SOCK_NONBLOCK | SOCK_CLOEXEC, 0);
+    if (notifFd_ < 0) {
+        NIXL_ERROR << "NVLINK backend: cannot create the notification socket: " << std::strerror(errno);
+        initErr = true;
+        return;
+    }
+    char name[96];
+    std::snprintf(name, sizeof(name), "nixl_b200.%lld.%016llx", static_cast<long long>(self_.pid),
+                  static_cast<unsigned long long>(self_.engineTag));
+    self_.sockName = name;
+    socklen_t alen = 0;
+    sockaddr_un addr = abstractAddr(self_.sockName, alen);
+    if (::bind(notifFd_, reinterpret_cast<sockaddr *>(&addr), alen) != 0) {
+        NIXL_ERROR << "NVLINK backend: cannot bind the notification socket: " << std::strerror(errno);
+        initErr = true;
+        return;
+    }
+    int big = 8 << 20;
+    setsockopt(notifFd_, SOL_SOCKET, SO_RCVBUF, &big, sizeof(big));
+    setsockopt(notifFd_, SOL_SOCKET, SO_SNDBUF, &big, sizeof(big));
+
+    {
+        std::lock_guard<std::mutex> g(g_regMu);
+        g_registry[self_.agent] = this;
+    }
+    progThread_ = init->enableProgTh;
+    progDelayUs_ = init->pthrDelay;
+    if (progThread_) progTh_ = std::thread([this] { progressLoop(); });
+}
+
+Engine::~Engine() {
+    progStop_ = true;
+    progCv_.notify_all();
+    if (progTh_.joinable()) progTh_.join();
+    {
+        std::lock_guard<std::mutex> g(g_regMu);
+        auto it = g_registry.find(self_.agent);
+        if (it != g_registry.end() && it->second == this) g_registry.erase(it);
+    }
+    if (notifFd_ >= 0) ::close(notifFd_);
+    for (auto &c : ctxs_) {
+        if (!c) continue;
+        DeviceScope ds(c->device);
+        if (c->stream) {
+            cudaStreamSynchronize(c->stream);
+            cudaStreamDestroy(c->stream);
+        }
+        if (c->prepStream) cudaStreamDestroy(c->prepStream);
+        c->arena.reset();
+        if (c->flags) cudaFreeHost(c->flags);
+    }
+}
+
+constexpr int kFlagSlots = 4096;
+
+DeviceCtx *Engine::ctx(int device) const {
+    if (!cuda_ || device < 0 || device >= deviceCount_) return nullptr;
+    std::lock_guard<std::mutex> g(ctxMu_);
+    if (ctxs_.size() < static_cast<size_t>(deviceCount_)) ctxs_.resize(deviceCount_);
+    if (ctxs_[device]) return ctxs_[device].get();
+    DeviceScope ds(device);
+    auto c = std::make_unique<DeviceCtx>();
+    c->device = device;
+    if (!cudaOk(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking), "cudaStreamCreate")) return nullptr;
+    if (!cudaOk(cudaStreamCreateWithFlags(&c->prepStream, cudaStreamNonBlocking), "cudaStreamCreate")) return nullptr;
+    void *flags = nullptr;
+    if (!cudaOk(cudaHostAlloc(&flags, kFlagSlots * sizeof(uint64_t), cudaHostAllocMapped | cudaHostAllocPortable), "cudaHostAlloc"))
+        return nullptr;
+    std::memset(flags, 0, kFlagSlots * sizeof(uint64_t));
+    c->flags = static_cast<uint64_t *>(flags);
+    for (int i = kFlagSlots - 1; i >= 0; --i) c->freeFlags.push_back(i);
+    c->arena = std::make_unique<DeviceArena>(device);
+    c->gridCtas = gridOverride_ > 0 ? gridOverride_ : defaultGridCtas(device);
+    ctxs_[device] = std::move(c);
+    return ctxs_[device].get();
+}
+
+bool Engine::ensurePeerAccess(int from, int to) const {
+    if (from == to) return true;
+    std::lock_guard<std::mutex> g(g_peerAccessMu);
+    if (std::find(g_peerAccess.begin(), g_peerAccess.end(), std::make_pair(from, to)) != g_peerAccess.end()) return true;
+    int can = 0;
+    if (cudaDeviceCanAccessPeer(&can, from, to) != cudaSuccess || !can) {
+        cudaGetLastError();
+        return false;
+    }
+    DeviceScope ds(from);
+    const cudaError_t e = cudaDeviceEnablePeerAccess(to, 0);
+    if (e != cudaSuccess && e != cudaErrorPeerAccessAlreadyEnabled) {
+        cudaOk(e, "cudaDeviceEnablePeerAccess");
+        return false;
+    }
+    cudaGetLastError();
+    g_peerAccess.emplace_back(from, to);
+    return true;
+}
+
+// ================================================================ registration
+
+nixl_status_t Engine::registerMem(const nixlBlobDesc &mem, const nixl_mem_t &nixl_mem, nixlBackendMD *&out) {
+    if (mem.len == 0) return NIXL_ERR_INVALID_PARAM;
+    auto md = std::make_unique<LocalMD>();
+    md->mem = nixl_mem;
+    md->addr = mem.addr;
+    md->len = mem.len;
+    if (nixl_mem == VRAM_SEG) {
+        if (!cuda_) return NIXL_ERR_NOT_SUPPORTED;
+        if (mem.devId >= static_cast<uint64_t>(deviceCount_)) return NIXL_ERR_INVALID_PARAM;
+        md->device = static_cast<int>(mem.devId);
+        md->devVisible = mem.addr;
+        cudaPointerAttributes attr{};
+        if (cudaPointerGetAttributes(&attr, reinterpret_cast<void *>(mem.addr)) != cudaSuccess ||
+            (attr.type != cudaMemoryTypeDevice && attr.type != cudaMemoryTypeManaged)) {
+            cudaGetLastError();
+            NIXL_ERROR << "NVLINK backend: address " << reinterpret_cast<void *>(mem.addr) << " is not device memory";
+            return NIXL_ERR_INVALID_PARAM;
+        }
+        if (attr.device != md->device) {
+            NIXL_ERROR << "NVLINK backend: descriptor says device " << md->device << " but the memory lives on " << attr.device;
+            return NIXL_ERR_INVALID_PARAM;
+        }
+        int expected = -1;
+        primaryDevice_.compare_exchange_strong(expected, md->device);
+        // Export for other processes.  Memory that CUDA IPC cannot export (VMM, pools) stays
+        // reachable from this process only.
+        DeviceScope ds(md->device);
+        uintptr_t base = 0;
+        size_t size = 0;
+        if (allocationRange(mem.addr, base, size) && mem.addr + mem.len <= base + size &&
+            cudaIpcGetMemHandle(&md->ipc, reinterpret_cast<void *>(base)) == cudaSuccess) {
+            md->hasIpc = true;
+            md->ipcOffset = mem.addr - base;
+        } else {
+            cudaGetLastError();
+            NIXL_DEBUG << "NVLINK backend: no IPC handle for " << reinterpret_cast<void *>(mem.addr) << "; same-process use only";
+        }
+    } else if (nixl_mem == DRAM_SEG) {
+        if (cuda_ && pinDram_) {
+            const int dev = primaryDevice_.load() >= 0 ? primaryDevice_.load() : 0;
+            DeviceScope ds(dev);
+            cudaError_t e = cudaHostRegister(reinterpret_cast<void *>(mem.addr), mem.len, cudaHostRegisterPortable | cudaHostRegisterMapped);
+            if (e == cudaSuccess) md->pinnedByUs = true;
+            if (e == cudaSuccess || e == cudaErrorHostMemoryAlreadyRegistered) {
+                cudaGetLastError();
+                void *dp = nullptr;
+                if (cudaHostGetDevicePointer(&dp, reinterpret_cast<void *>(mem.addr), 0) == cudaSuccess)
+                    md->devVisible = reinterpret_cast<uintptr_t>(dp);
+                else cudaGetLastError();
+            } else {
+                cudaGetLastError();
+                NIXL_DEBUG << "NVLINK backend: DRAM region not pinned (" << cudaGetErrorString(e) << "); staged copies will be used";
+            }
+        }
+    } else {
+        return NIXL_ERR_NOT_SUPPORTED;
+    }
+    out = md.release();
+    return NIXL_SUCCESS;
+}
+
+nixl_status_t Engine::deregisterMem(nixlBackendMD *meta) {
+    auto *md = dynamic_cast<LocalMD *>(meta);
+    if (!md) return NIXL_ERR_INVALID_PARAM;
+    if (md->pinnedByUs) {
+        if (cudaHostUnregister(reinterpret_cast<void *>(md->addr)) != cudaSuccess) cudaGetLastError();
+    }
+    delete md;
+    return NIXL_SUCCESS;
+}
+
+nixl_status_t Engine::getPublicData(const nixlBackendMD *meta, std::string &str) const {
+    auto *md = dynamic_cast<const LocalMD *>(meta);
+    if (!md) return NIXL_ERR_INVALID_PARAM;
+    PubReg pub{};
+    pub.version = kPubVersion;
+    pub.mem = static_cast<uint8_t>(md->mem);
+    pub.hasIpc = md->hasIpc ? 1 : 0;
+    pub.device = md->device;
+    pub.addr = md->addr;
+    pub.len = md->len;
+    pub.ipcOffset = md->ipcOffset;
+    pub.engineTag = self_.engineTag;
+    std::memcpy(pub.ipc, &md->ipc, sizeof(md->ipc));
+    str.assign(reinterpret_cast<const char *>(&pub), sizeof(pub));
+    return NIXL_SUCCESS;
+}
+
+nixl_status_t Engine::getConnInfo(std::string &str) const {
+    str = encodePeer(self_);
+    return NIXL_SUCCESS;
+}
+
+nixl_status_t Engine::loadRemoteConnInfo(const std::string &remote_agent, const std::string &remote_conn_info) {
+    PeerId p;
+    if (!decodePeer(remote_conn_info, p) || p.agent != remote_agent) return NIXL_ERR_MISMATCH;
+    if (p.host != self_.host) {
+        NIXL_ERROR << "NVLINK backend: agent " << remote_agent << " runs on host " << p.host
+                   << "; this backend reaches peers of one NVLink box only";
+        return NIXL_ERR_NOT_SUPPORTED;
+    }
+    std::lock_guard<std::mutex> g(peersMu_);
+    peers_[remote_agent] = p;
+    return NIXL_SUCCESS;
+}
+
+nixl_status_t Engine::connect(const std::string &remote_agent) {
+    if (remote_agent == self_.agent) {
+        std::lock_guard<std::mutex> g(peersMu_);
+        peers_[remote_agent] = self_;
+        return NIXL_SUCCESS;
+    }
+    PeerId p;
+    {
+        std::lock_guard<std::mutex> g(peersMu_);
+        auto it = peers_.find(remote_agent);
+        if (it == peers_.end()) return NIXL_ERR_NOT_FOUND;
+        p = it->second;
+    }
+    return peerAlive(p) ? NIXL_SUCCESS : NIXL_ERR_REMOTE_DISCONNECT;
+}
+
+nixl_status_t Engine::disconnect(const std::string &remote_agent) {
+    std::lock_guard<std::mutex> g(peersMu_);
+    return peers_.erase(remote_agent) ? NIXL_SUCCESS : NIXL_ERR_NOT_FOUND;
+}
+
+nixl_status_t Engine::loadRemoteMD(const nixlBlobDesc &input, const nixl_mem_t &nixl_mem, const std::string &remote_agent,
+                                   nixlBackendMD *&output) {
+    if (input.metaInfo.size() != sizeof(PubReg)) return NIXL_ERR_MISMATCH;
+    PubReg pub;
+    std::memcpy(&pub, input.metaInfo.data(), sizeof(pub));
+    if (pub.version != kPubVersion || pub.mem != static_cast<uint8_t>(nixl_mem)) return NIXL_ERR_MISMATCH;
+    PeerId peer;
+    {
+        std::lock_guard<std::mutex> g(peersMu_);
+        auto it = peers_.find(remote_agent);
+        if (it == peers_.end()) return NIXL_ERR_NOT_FOUND;
+        peer = it->second;
+    }
+    auto md = std::make_unique<RemoteMD>();
+    md->agent = remote_agent;
+    md->mem = nixl_mem;
+    md->addr = pub.addr;
+    md->len = pub.len;
+    md->ownerDevice = pub.device;
+    md->ownerPid = peer.pid;
+    md->sameProcess = peer.pid == self_.pid && peer.procTag == self_.procTag;
+    if (md->sameProcess) {
+        if (nixl_mem == VRAM_SEG) md->devVisible = pub.addr;
+        else if (cuda_) {
+            void *dp = nullptr; // pinned by its owner? then kernels can touch it
+            if (cudaHostGetDevicePointer(&dp, reinterpret_cast<void *>(pub.addr), 0) == cudaSuccess)
+                md->devVisible = reinterpret_cast<uintptr_t>(dp);
+            else cudaGetLastError();
+        }
+    } else if (nixl_mem == VRAM_SEG && cuda_ && pub.hasIpc) {
+        const std::string key(reinterpret_cast<const char *>(pub.ipc), sizeof(pub.ipc));
+        std::lock_guard<std::mutex> g(g_ipcMu);
+        IpcMapping &m = g_ipc[key];
+        if (!m.base) {
+            int dev = primaryDevice_.load();
+            if (dev < 0 && cudaGetDevice(&dev) != cudaSuccess) dev = 0;
+            DeviceScope ds(dev);
+            cudaIpcMemHandle_t h;
+            std::memcpy(&h, pub.ipc, sizeof(h));
+            void *base = nullptr;
+            if (!cudaOk(cudaIpcOpenMemHandle(&base, h, cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle")) {
+                g_ipc.erase(key);
+                return NIXL_ERR_BACKEND;
+            }
+            m.base = base;
+            m.device = dev;
+        }
+        ++m.refs;
+        md->ipcKey = key;
+        md->mapDevice = m.device;
+        md->devVisible = reinterpret_cast<uintptr_t>(m.base) + pub.ipcOffset;
+    }
+    output = md.release();
+    return NIXL_SUCCESS;
+}
+
+nixl_status_t Engine::loadLocalMD(nixlBackendMD *input, nixlBackendMD *&output) {
+    auto *l = dynamic_cast<LocalMD *>(input);
+    if (!l) return NIXL_ERR_INVALID_PARAM;
+    auto md = std::make_unique<RemoteMD>();
+    md->agent = self_.agent;
+    md->mem = l->mem;
+    md->addr = l->addr;
+    md->len = l->len;
+    md->ownerDevice = l->device;
+    md->ownerPid = self_.pid;
+    md->sameProcess = true;
+    md->devVisible = l->devVisible;
+    md->loopback = true;
+    output = md.release();
+    return NIXL_SUCCESS;
+}
+
+nixl_status_t Engine::unloadMD(nixlBackendMD *input) {
+    auto *md = dynamic_cast<RemoteMD *>(input);
+    if (!md) return NIXL_ERR_INVALID_PARAM;
+    if (!md->ipcKey.empty()) {
+        std::lock_guard<std::mutex> g(g_ipcMu);
+        auto it = g_ipc.find(md->ipcKey);
+        if (it != g_ipc.end() && --it->second.refs == 0) {
+            DeviceScope ds(it->second.device);
+            if (cudaIpcCloseMemHandle(it->second.base) != cudaSuccess) cudaGetLastError();
+            g_ipc.erase(it);
+        }
+    }
+    delete md;
+    return NIXL_SUCCESS;
+}
+
+// ================================================================ transfers
+
+void Engine::freeBatch(KernelBatch &b) const {
+    DeviceCtx *c = ctx(b.device);
+    if (!c) return;
+    if (b.table) c->arena->free(b.table);
+    if (b.counter) c->arena->free(b.counter);
+    if (b.uploaded) {
+        DeviceScope ds(b.device);
+        cudaEventDestroy(b.uploaded);
+    }
+    if (b.flagSlot >= 0) {
+        std::lock_guard<std::mutex> g(c->mu);
+        c->freeFlags.push_back(b.flagSlot);
+    }
+    b.table = nullptr;
+    b.counter = nullptr;
+    b.uploaded = nullptr;
+    b.flagSlot = -1;
+}
+
+nixl_status_t Engine::prepXfer(const nixl_xfer_op_t &operation, const nixl_meta_dlist_t &local, const nixl_meta_dlist_t &remote,
+                               const std::string &remote_agent, nixlBackendReqH *&handle, const nixl_opt_b_args_t *) const {
+    if (local.descCount() != remote.descCount() || local.isEmpty()) return NIXL_ERR_INVALID_PARAM;
+    auto req = std::make_unique<ReqH>();
+    req->op = operation;
+    req->remoteAgent = remote_agent;
+    std::map<int, std::vector<XferDesc>> perDevice;
+
+    for (int i = 0; i < local.descCount(); ++i) {
+        auto *l = dynamic_cast<LocalMD *>(local[i].metadataP);
+        auto *r = dynamic_cast<RemoteMD *>(remote[i].metadataP);
+        if (!l || !r || local[i].len != remote[i].len) return NIXL_ERR_INVALID_PARAM;
+        const size_t len = local[i].len;
+        if (len == 0) continue;
+        req->totalBytes += len;
+        const uintptr_t laddr = local[i].addr, raddr = remote[i].addr;
+        // Kernel-visible addresses of both ends, when they exist.
+        const uintptr_t lvis = l->devVisible ? l->devVisible + (laddr - l->addr) : 0;
+        const uintptr_t rvis = r->devVisible ? r->devVisible + (raddr - r->addr) : 0;
+        const bool any_vram = l->mem == VRAM_SEG || r->mem == VRAM_SEG;
+
+        if (!any_vram) { // DRAM <-> DRAM: the CPU moves it
+            if (r->sameProcess) {
+                if (operation == NIXL_WRITE) req->hostCopies.push_back({reinterpret_cast<void *>(raddr), reinterpret_cast<void *>(laddr), len});
+                else req->hostCopies.push_back({reinterpret_cast<void *>(laddr), reinterpret_cast<void *>(raddr), len});
+            } else {
+                req->cmaCopies.push_back({laddr, raddr, len});
+                req->cmaPid = r->ownerPid;
+            }
+            continue;
+        }
+        if (!cuda_) return NIXL_ERR_NOT_SUPPORTED;
+        if (lvis && rvis) { // the copy kernel can see both ends
+            int dev;
+            if (l->mem == VRAM_SEG) dev = l->device;
+            else dev = r->sameProcess ? r->ownerDevice : r->mapDevice;
+            if (dev < 0) return NIXL_ERR_BACKEND;
+            if (r->mem == VRAM_SEG && r->sameProcess && !ensurePeerAccess(dev, r->ownerDevice)) {
+                NIXL_ERROR << "NVLINK backend: GPU " << dev << " cannot access GPU " << r->ownerDevice;
+                return NIXL_ERR_BACKEND;
+            }
+            XferDesc d;
+            d.src = operation == NIXL_WRITE ? lvis : rvis;
+            d.dst = operation == NIXL_WRITE ? rvis : lvis;
+            d.len = len;
+            perDevice[dev].push_back(d);
+            continue;
+        }
+        // One end is pageable host memory: let the runtime stage it.
+        if (l->mem == DRAM_SEG && rvis) {
+            const int dev = r->sameProcess ? r->ownerDevice : r->mapDevice;
+            if (operation == NIXL_WRITE) req->asyncCopies.push_back({reinterpret_cast<void *>(rvis), reinterpret_cast<void *>(laddr), len, dev});
+            else req->asyncCopies.push_back({reinterpret_cast<void *>(laddr), reinterpret_cast<void *>(rvis), len, dev});
+            continue;
+        }
+        if (l->mem == VRAM_SEG && r->mem == DRAM_SEG && r->sameProcess) {
+            if (operation == NIXL_WRITE) req->asyncCopies.push_back({reinterpret_cast<void *>(raddr), reinterpret_cast<void *>(lvis), len, l->device});
+            else req->asyncCopies.push_back({reinterpret_cast<void *>(lvis), reinterpret_cast<void *>(raddr), len, l->device});
+            continue;
+        }
+        NIXL_ERROR << "NVLINK backend: no path between local " << nixlEnumStrings::memTypeStr(l->mem) << " and remote "
+                   << nixlEnumStrings::memTypeStr(r->mem) << " of agent " << remote_agent
+                   << (r->sameProcess ? "" : " (other process; its VRAM must be cudaMalloc memory, its DRAM is reachable from DRAM only)");
+        return NIXL_ERR_NOT_SUPPORTED;
+    }
+
+    for (auto &kv : perDevice) {
+        DeviceCtx *c = ctx(kv.first);
+        if (!c) return NIXL_ERR_BACKEND;
+        KernelBatch b;
+        b.device = kv.first;
+        b.descs = std::move(kv.second);
+        uint64_t total = 0, longest = 0;
+        for (auto &d : b.descs) {
+            total += d.len;
+            longest = std::max<uint64_t>(longest, d.len);
+        }
+        // Chunk size: aim at ~2 chunks per CTA of a full grid, between 16 KiB and 256 KiB.
+        uint32_t shift = log2Ceil(std::max<uint64_t>(1, total / (2 * static_cast<uint64_t>(c->gridCtas))));
+        shift = std::min<uint32_t>(18, std::max<uint32_t>(14, shift));
+        const size_t n = b.descs.size();
+        std::vector<uint32_t> starts(n + 1);
+        uint64_t chunks = 0;
+        for (size_t i = 0; i < n; ++i) {
+            starts[i] = static_cast<uint32_t>(chunks);
+            chunks += (b.descs[i].len + (uint64_t(1) << shift) - 1) >> shift;
+            while (chunks > 0x7fffffffull) { // cannot happen below 2^31 * 16 KiB, but stay safe
+                return NIXL_ERR_INVALID_PARAM;
+            }
+        }
+        starts[n] = static_cast<uint32_t>(chunks);
+        b.launch.nDescs = static_cast<uint32_t>(n);
+        b.launch.totalChunks = static_cast<uint32_t>(chunks);
+        b.launch.chunkShift = shift;
+        {
+            std::lock_guard<std::mutex> g(c->mu);
+            if (c->freeFlags.empty()) return NIXL_ERR_BACKEND;
+            b.flagSlot = c->freeFlags.back();
+            c->freeFlags.pop_back();
+        }
+        c->flags[b.flagSlot] = 0;
+        b.launch.hostFlag = c->flags + b.flagSlot; // UVA: the pinned allocation's host address is device-visible
+        b.counter = static_cast<unsigned int *>(c->arena->alloc(256));
+        if (!b.counter) {
+            freeBatch(b);
+            return NIXL_ERR_BACKEND;
+        }
+        b.launch.doneCounter = b.counter;
+        if (n <= static_cast<size_t>(kInlineDescs)) {
+            b.launch.table = nullptr;
+            b.launch.chunkStart = nullptr;
+            for (size_t i = 0; i < n; ++i) b.launch.inl[i] = b.descs[i];
+            for (size_t i = 0; i <= n; ++i) b.launch.inlStart[i] = starts[i];
+        } else {
+            const size_t tbytes = n * sizeof(XferDesc), sbytes = (n + 1) * sizeof(uint32_t);
+            const size_t toff = 0, soff = (tbytes + 15) & ~size_t(15);
+            b.table = c->arena->alloc(soff + sbytes);
+            if (!b.table) {
+                freeBatch(b);
+                return NIXL_ERR_BACKEND;
+            }
+            DeviceScope ds(b.device);
+            char *base = static_cast<char *>(b.table);
+            // Pageable source: the runtime copies it out before returning, so the vectors may die.
+            bool ok = cudaOk(cudaMemcpyAsync(base + toff, b.descs.data(), tbytes, cudaMemcpyHostToDevice, c->prepStream), "table upload");
+            ok = ok && cudaOk(cudaMemcpyAsync(base + soff, starts.data(), sbytes, cudaMemcpyHostToDevice, c->prepStream), "table upload");
+            ok = ok && cudaOk(cudaEventCreateWithFlags(&b.uploaded, cudaEventDisableTiming), "cudaEventCreate");
+            ok = ok && cudaOk(cudaEventRecord(b.uploaded, c->prepStream), "cudaEventRecord");
+            if (!ok) {
+                freeBatch(b);
+                return NIXL_ERR_BACKEND;
+            }
+            b.launch.table = reinterpret_cast<const XferDesc *>(base + toff);
+            b.launch.chunkStart = reinterpret_cast<const uint32_t *>(base + soff);
+        }
+        req->kernels.push_back(std::move(b));
+    }
+    for (auto &a : req->asyncCopies) {
+        bool have = false;
+        for (auto &e : req->asyncEvents) have |= e.first == a.device;
+        if (have) continue;
+        if (!ctx(a.device)) return NIXL_ERR_BACKEND;
+        DeviceScope ds(a.device);
+        cudaEvent_t ev = nullptr;
+        if (!cudaOk(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming), "cudaEventCreate")) return NIXL_ERR_BACKEND;
+        req->asyncEvents.emplace_back(a.device, ev);
+    }
+    handle = req.release();
+    return NIXL_SUCCESS;
+}
+
+bool Engine::peerAlive(const PeerId &peer) const {
+    if (peer.engineTag == self_.engineTag) return true;
+    if (peer.pid == self_.pid && peer.procTag == self_.procTag) {
+        std::lock_guard<std::mutex> g(g_regMu);
+        auto it = g_registry.find(peer.agent);
+        return it != g_registry.end() && it->second->engineTag() == peer.engineTag;
+    }
+    if (::kill(static_cast<pid_t>(peer.pid), 0) != 0 && errno == ESRCH) return false;
+    if (livenessPing_) {
+        socklen_t alen = 0;
+        sockaddr_un addr = abstractAddr(peer.sockName, alen);
+        if (::sendto(notifFd_, "", 0, MSG_DONTWAIT | MSG_NOSIGNAL, reinterpret_cast<sockaddr *>(&addr), alen) != 0 &&
+            (errno == ECONNREFUSED || errno == ENOENT))
+            return false;
+    }
+    return true;
+}
+
+nixl_status_t Engine::postXfer(const nixl_xfer_op_t &operation, const nixl_meta_dlist_t &, const nixl_meta_dlist_t &,
+                               const std::string &remote_agent, nixlBackendReqH *&handle, const nixl_opt_b_args_t *opt_args) const {
+    auto *req = dynamic_cast<ReqH *>(handle);
+    if (!req || req->op != operation) return NIXL_ERR_INVALID_PARAM;
+    PeerId peer;
+    {
+        std::lock_guard<std::mutex> g(peersMu_);
+        auto it = peers_.find(remote_agent);
+        if (it == peers_.end()) return NIXL_ERR_NOT_FOUND;
+        peer = it->second;
+    }
+    if (!peerAlive(peer)) return NIXL_ERR_REMOTE_DISCONNECT;
+
+    std::unique_lock<std::mutex> lk(req->mu);
+    req->notifPending = opt_args && opt_args->hasNotif;
+    req->notifMsg = req->notifPending ? opt_args->notifMsg : std::string();
+
+    // Optional stream-ordered posting: customParam "stream=<address of a cudaStream_t value>".
+    cudaStream_t user_stream = nullptr;
+    bool has_user_stream = false;
+    if (opt_args && opt_args->customParam.rfind("stream=", 0) == 0) {
+        user_stream = reinterpret_cast<cudaStream_t>(std::strtoull(opt_args->customParam.c_str() + 7, nullptr, 0));
+        has_user_stream = true;
+    }
+
+    for (auto &h : req->hostCopies) std::memcpy(h.dst, h.src, h.len);
+
+    if (!req->cmaCopies.empty()) {
+        constexpr size_t kBatch = 512;
+        iovec liov[kBatch], riov[kBatch];
+        size_t i = 0;
+        while (i < req->cmaCopies.size()) {
+            size_t n = 0, want = 0;
+            for (; n < kBatch && i + n < req->cmaCopies.size(); ++n) {
+                const CmaCopy &cc = req->cmaCopies[i + n];
+                liov[n] = {reinterpret_cast<void *>(cc.local), cc.len};
+                riov[n] = {reinterpret_cast<void *>(cc.remote), cc.len};
+                want += cc.len;
+            }
+            const ssize_t got = operation == NIXL_WRITE
+                ? ::process_vm_writev(static_cast<pid_t>(req->cmaPid), liov, n, riov, n, 0)
+                : ::process_vm_readv(static_cast<pid_t>(req->cmaPid), liov, n, riov, n, 0);
+            if (got < 0 || static_cast<size_t>(got) != want) {
+                if (errno == ESRCH) return NIXL_ERR_REMOTE_DISCONNECT;
+                NIXL_ERROR << "NVLINK backend: cross-process DRAM copy failed: " << std::strerror(errno);
+                return NIXL_ERR_BACKEND;
+            }
+            i += n;
+        }
+    }
+
+    for (auto &b : req->kernels) {
+        DeviceCtx *c = ctx(b.device);
+        if (!c) return NIXL_ERR_BACKEND;
+        DeviceScope ds(b.device);
+        cudaStream_t s = has_user_stream ? user_stream : c->stream;
+        if (b.uploaded && !cudaOk(cudaStreamWaitEvent(s, b.uploaded, 0), "cudaStreamWaitEvent")) return NIXL_ERR_BACKEND;
+        b.seq = (b.seq + 1) & 0x7fffffffffffffffull;
+        if (b.seq == 0) b.seq = 1;
+        b.launch.seq = b.seq;
+        if (!cudaOk(launchBatchCopy(b.launch, c->gridCtas, copyPath_, s), "copy kernel launch")) return NIXL_ERR_BACKEND;
+        b.inFlight = true;
+    }
+
+    if (!req->asyncCopies.empty()) {
+        for (auto &a : req->asyncCopies) {
+            DeviceCtx *c = ctx(a.device);
+            DeviceScope ds(a.device);
+            cudaStream_t s = has_user_stream ? user_stream : c->stream;
+            if (!cudaOk(cudaMemcpyAsync(a.dst, a.src, a.len, cudaMemcpyDefault, s), "cudaMemcpyAsync")) return NIXL_ERR_BACKEND;
+        }
+        for (auto &e : req->asyncEvents) {
+            DeviceCtx *c = ctx(e.first);
+            DeviceScope ds(e.first);
+            if (!cudaOk(cudaEventRecord(e.second, has_user_stream ? user_stream : c->stream), "cudaEventRecord")) return NIXL_ERR_BACKEND;
+        }
+        req->asyncInFlight = true;
+    }
+
+    nixl_status_t st = pollData(req);
+    if (st == NIXL_SUCCESS) st = finishIfDone(req);
+    req->last = st;
+    const bool watch = st == NIXL_IN_PROG && progThread_ && req->notifPending;
+    lk.unlock();
+    if (watch) {
+        std::lock_guard<std::mutex> g(progMu_);
+        progWatch_.push_back(req);
+        progCv_.notify_one();
+    }
+    return st;
+}
+
+// Data state only: SUCCESS when every launched piece has completed.
+nixl_status_t Engine::pollData(ReqH *req) const {
+    for (auto &b : req->kernels) {
+        if (!b.inFlight) continue;
+        DeviceCtx *c = ctx(b.device);
+        const uint64_t v = *reinterpret_cast<volatile uint64_t *>(c->flags + b.flagSlot);
+        if (v >> 63) {
+            c->flags[b.flagSlot] = 0;
+            b.inFlight = false;
+            NIXL_ERROR << "NVLINK backend: copy kernel reported a lost bulk copy";
+            return NIXL_ERR_BACKEND;
+        }
+        if (v != b.seq) return NIXL_IN_PROG;
+        b.inFlight = false;
+    }
+    if (req->asyncInFlight) {
+        for (auto &e : req->asyncEvents) {
+            const cudaError_t q = cudaEventQuery(e.second);
+            if (q == cudaErrorNotReady) {
+                cudaGetLastError();
+                return NIXL_IN_PROG;
+            }
+            if (q != cudaSuccess) {
+                cudaOk(q, "cudaEventQuery");
+                return NIXL_ERR_BACKEND;
+            }
+        }
+        req->asyncInFlight = false;
+    }
+    std::atomic_thread_fence(std::memory_order_acquire);
+    return NIXL_SUCCESS;
+}
+
+nixl_status_t Engine::finishIfDone(ReqH *req) const {
+    if (!req->notifPending) return NIXL_SUCCESS;
+    PeerId peer;
+    {
+        std::lock_guard<std::mutex> g(peersMu_);
+        auto it = peers_.find(req->remoteAgent);
+        if (it == peers_.end()) return NIXL_ERR_NOT_FOUND;
+        peer = it->second;
+    }
+    req->notifPending = false;
+    return sendNotif(peer, req->notifMsg);
+}
+
+nixl_status_t Engine::checkXfer(nixlBackendReqH *handle) const {
+    auto *req = dynamic_cast<ReqH *>(handle);
+    if (!req) return NIXL_ERR_INVALID_PARAM;
+    std::lock_guard<std::mutex> g(req->mu);
+    if (req->last != NIXL_IN_PROG) return req->last;
+    nixl_status_t st = pollData(req);
+    if (st == NIXL_SUCCESS) st = finishIfDone(req);
+    req->last = st;
+    return st;
+}
+
+nixl_status_t Engine::releaseReqH(nixlBackendReqH *handle) const {
+    auto *req = dynamic_cast<ReqH *>(handle);
+    if (!req) return NIXL_ERR_INVALID_PARAM;
+    {
+        std::lock_guard<std::mutex> g(progMu_);
+        progWatch_.erase(std::remove(progWatch_.begin(), progWatch_.end(), req), progWatch_.end());
+    }
+    {
+        std::lock_guard<std::mutex> g(req->mu);
+        // A running kernel still reads the table: wait for it (transfers are short-lived).
+        for (auto &b : req->kernels) {
+            if (b.inFlight) {
+                DeviceCtx *c = ctx(b.device);
+                DeviceScope ds(b.device);
+                cudaStreamSynchronize(c->stream);
+                b.inFlight = false;
+            }
+            freeBatch(b);
+        }
+        for (auto &e : req->asyncEvents) {
+            DeviceScope ds(e.first);
+            if (req->asyncInFlight) cudaEventSynchronize(e.second);
+            cudaEventDestroy(e.second);
+        }
+    }
+    delete req;
+    return NIXL_SUCCESS;
+}
+
+void Engine::progressLoop() {
+    std::unique_lock<std::mutex> lk(progMu_);
+    while (!progStop_) {
+        if (progWatch_.empty()) {
+            progCv_.wait_for(lk, std::chrono::milliseconds(50));
+            continue;
+        }
+        for (size_t i = 0; i < progWatch_.size();) {
+            ReqH *req = progWatch_[i];
+            nixl_status_t st;
+            {
+                std::lock_guard<std::mutex> g(req->mu);
+                st = req->last;
+                if (st == NIXL_IN_PROG) {
+                    st = pollData(req);
+                    if (st == NIXL_SUCCESS) st = finishIfDone(req);
+                    req->last = st;
+                }
+            }
+            if (st != NIXL_IN_PROG) progWatch_.erase(progWatch_.begin() + i);
+            else ++i;
+        }
+        lk.unlock();
+        if (progDelayUs_) std::this_thread::sleep_for(std::chrono::microseconds(progDelayUs_));
+        else std::this_thread::yield();
+        lk.lock();
+    }
+}
+
+nixl_status_t Engine::estimateXferCost(const nixl_xfer_op_t &, const nixl_meta_dlist_t &local, const nixl_meta_dlist_t &remote,
+                                       const std::string &, nixlBackendReqH *const &handle, std::chrono::microseconds &duration,
+                                       std::chrono::microseconds &err_margin, nixl_cost_t &method, const nixl_opt_args_t *) const {
+    // Analytical model: fixed launch/poll latency plus bytes over the slowest link involved.
+    double bytes = 0;
+    for (const auto &d : local) bytes += static_cast<double>(d.len);
+    double gbps = 20.0; // host memcpy
+    if (local.getType() == VRAM_SEG && remote.getType() == VRAM_SEG) {
+        gbps = 700.0; // NVLink 5, one direction
+        if (auto *req = dynamic_cast<ReqH *>(handle))
+            if (!req->kernels.empty() && local.descCount() > 0) {
+                auto *r = dynamic_cast<RemoteMD *>(remote[0].metadataP);
+                if (r && r->sameProcess && r->ownerDevice == req->kernels[0].device) gbps = 2800.0; // same-GPU HBM copy
+            }
+    } else if (local.getType() == VRAM_SEG || remote.getType() == VRAM_SEG) {
+        gbps = 50.0; // PCIe Gen5 x16
+    }
+    const double us = 6.0 + bytes / (gbps * 1e3);
+    duration = std::chrono::microseconds(static_cast<int64_t>(us + 0.5));
+    err_margin = std::chrono::microseconds(static_cast<int64_t>(us * 0.25 + 1.0));
+    method = nixl_cost_t::ANALYTICAL_BACKEND;
+    return NIXL_SUCCESS;
+}
+
+// ================================================================ notifications
+
+void Engine::pushNotif(const std::string &from, const std::string &msg) {
+    std::lock_guard<std::mutex> g(notifMu_);
+    inbox_.emplace_back(from, msg);
+}
+
+nixl_status_t Engine::sendNotif(const PeerId &peer, const std::string &msg) const {
+    if (peer.pid == self_.pid && peer.procTag == self_.procTag) {
+        std::lock_guard<std::mutex> g(g_regMu);
+        auto it = g_registry.find(peer.agent);
+        if (it == g_registry.end() || it->second->engineTag() != peer.engineTag) return NIXL_ERR_REMOTE_DISCONNECT;
+        it->second->pushNotif(self_.agent, msg);
+        return NIXL_SUCCESS;
+    }
+    // Payload layout follows the reference's UCX notification (ucx_backend.cpp:1376): name + msg.
+    nixlSerDes sd;
+    sd.addStr("name", self_.agent);
+    sd.addStr("msg", msg);
+    const std::string wire = sd.exportStr();
+    socklen_t alen = 0;
+    sockaddr_un addr = abstractAddr(peer.sockName, alen);
+    for (int attempt = 0; attempt < 2000; ++attempt) {
+        if (::sendto(notifFd_, wire.data(), wire.size(), MSG_DONTWAIT | MSG_NOSIGNAL, reinterpret_cast<sockaddr *>(&addr), alen) >= 0)
+            return NIXL_SUCCESS;
+        if (errno == EAGAIN || errno == EWOULDBLOCK || errno == ENOBUFS) { // receiver's queue is full: give it a moment
+            std::this_thread::sleep_for(std::chrono::microseconds(100));
+            continue;
+        }
+        if (errno == ECONNREFUSED || errno == ENOENT) return NIXL_ERR_REMOTE_DISCONNECT;
+        if (errno == EMSGSIZE) return NIXL_ERR_INVALID_PARAM;
+        NIXL_ERROR << "NVLINK backend: notification send failed: " << std::strerror(errno);
+        return NIXL_ERR_BACKEND;
+    }
+    return NIXL_ERR_BACKEND;
+}
+
+nixl_status_t Engine::genNotif(const std::string &remote_agent, const std::string &msg) const {
+    PeerId peer;
+    {
+        std::lock_guard<std::mutex> g(peersMu_);
+        auto it = peers_.find(remote_agent);
+        if (it == peers_.end()) return NIXL_ERR_NOT_FOUND;
+        peer = it->second;
+    }
+    return sendNotif(peer, msg);
+}
+
+nixl_status_t Engine::getNotifs(notif_list_t &notif_list) {
+    {
+        std::lock_guard<std::mutex> g(notifMu_);
+        for (auto &n : inbox_) notif_list.push_back(std::move(n));
+        inbox_.clear();
+    }
+    std::vector<char> buf(256 * 1024);
+    for (;;) {
+        const ssize_t n = ::recv(notifFd_, buf.data(), buf.size(), MSG_DONTWAIT | MSG_TRUNC);
+        if (n < 0) break;
+        if (n == 0) continue; // liveness ping
+        if (static_cast<size_t>(n) > buf.size()) { // truncated: grow for the next one, this one is lost
+            NIXL_ERROR << "NVLINK backend: dropped an oversized notification (" << n << " bytes)";
+            buf.resize(static_cast<size_t>(n));
+            continue;
+        }
+        nixlSerDes sd;
+        if (sd.importStr(std::string(buf.data(), static_cast<size_t>(n))) != NIXL_SUCCESS) continue;
+        std::string from = sd.getStr("name");
+        std::string msg = sd.getStr("msg");
+        if (!from.empty()) notif_list.emplace_back(std::move(from), std::move(msg));
+    }
+    return NIXL_SUCCESS;
+}
+
+// ================================================================ memory views
+
+namespace {
+std::mutex g_viewMu;
+std::unordered_map<void *, MemViewHost> g_views;
+
+nixl_status_t buildView(const Engine *owner, const std::vector<nixlMemViewEntry> &entries, uint32_t kind, nixlMemViewH &mvh) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) {
+        cudaGetLastError();
+        return NIXL_ERR_BACKEND;
+    }
+    const size_t bytes = sizeof(nixlMemViewHeader) + entries.size() * sizeof(nixlMemViewEntry);
+    std::vector<char> host(bytes);
+    auto *hdr = reinterpret_cast<nixlMemViewHeader *>(host.data());
+    hdr->magic = NIXL_MEMVIEW_MAGIC;
+    hdr->count = static_cast<uint32_t>(entries.size());
+    hdr->kind = kind;
+    std::memcpy(host.data() + sizeof(nixlMemViewHeader), entries.data(), entries.size() * sizeof(nixlMemViewEntry));
+    void *d = nullptr;
+    if (!cudaOk(cudaMalloc(&d, bytes), "cudaMalloc(view)")) return NIXL_ERR_BACKEND;
+    if (!cudaOk(cudaMemcpy(d, host.data(), bytes, cudaMemcpyHostToDevice), "view upload")) {
+        cudaFree(d);
+        return NIXL_ERR_BACKEND;
+    }
+    std::lock_guard<std::mutex> g(g_viewMu);
+    g_views[d] = MemViewHost{NIXL_MEMVIEW_MAGIC, owner, d, dev};
+    mvh = d;
+    return NIXL_SUCCESS;
+}
+} // namespace
+
+nixl_status_t Engine::prepMemView(const nixl_remote_meta_dlist_t &dlist, nixlMemViewH &mvh, const nixl_opt_b_args_t *) const {
+    if (!cuda_) return NIXL_ERR_NOT_SUPPORTED;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    std::vector<nixlMemViewEntry> entries;
+    for (const auto &d : dlist) {
+        nixlMemViewEntry e{0, 0};
+        if (d.remoteAgent != nixl_null_agent) {
+            auto *r = dynamic_cast<RemoteMD *>(d.metadataP);
+            if (!r || !r->devVisible) return NIXL_ERR_NOT_SUPPORTED;
+            if (r->mem == VRAM_SEG && r->sameProcess && !ensurePeerAccess(dev, r->ownerDevice)) return NIXL_ERR_BACKEND;
+            e.ptr = r->devVisible + (d.addr - r->addr);
+            e.len = d.len;
+        }
+        entries.push_back(e);
+    }
+    return buildView(this, entries, NIXL_MEMVIEW_REMOTE, mvh);
+}
+
+nixl_status_t Engine::prepMemView(const nixl_meta_dlist_t &dlist, nixlMemViewH &mvh, const nixl_opt_b_args_t *) const {
+    if (!cuda_) return NIXL_ERR_NOT_SUPPORTED;
+    std::vector<nixlMemViewEntry> entries;
+    for (const auto &d : dlist) {
+        auto *l = dynamic_cast<LocalMD *>(d.metadataP);
+        if (!l || !l->devVisible) return NIXL_ERR_NOT_SUPPORTED;
+        entries.push_back({l->devVisible + (d.addr - l->addr), d.len});
+    }
+    return buildView(this, entries, NIXL_MEMVIEW_LOCAL, mvh);
+}
+
+void Engine::releaseMemView(nixlMemViewH mvh) const {
+    MemViewHost v{};
+    {
+        std::lock_guard<std::mutex> g(g_viewMu);
+        auto it = g_views.find(mvh);
+        if (it == g_views.end() || it->second.owner != this) return;
+        v = it->second;
+        g_views.erase(it);
+    }
+    DeviceScope ds(v.device);
+    cudaFree(v.devBlock);
+}
+
+} // namespace nixl_nvlink
+
+// ================================================================ plugin entry points
+
+namespace {
+nixl_b_params_t nvlinkDefaults() {
+    return {
+        {"use_cuda", "true"},      // false: host-only operation (DRAM transfers)
+        {"pin_dram", "true"},      // cudaHostRegister DRAM registrations so kernels can reach them
+        {"copy_path", "vector"},   // "vector" (SIMT 16-byte) or "bulk" (TMA 1-D through shared memory)
+        {"grid_ctas", "0"},        // 0: two CTAs per SM
+        {"device_id", "-1"},       // GPU that maps other processes' memory; -1: first registered / current
+        {"liveness_ping", "false"} // probe the peer's socket at every post
+    };
+}
+} // namespace
+
+extern "C" NIXL_PLUGIN_EXPORT nixlBackendPlugin *nixl_plugin_init() {
+    return nixlBackendPluginCreator<nixl_nvlink::Engine>::create(NIXL_PLUGIN_API_VERSION, "NVLINK", "1.0.0", nvlinkDefaults(),
+                                                                 {DRAM_SEG, VRAM_SEG});
+}
+
+extern "C" NIXL_PLUGIN_EXPORT void nixl_plugin_fini() {}

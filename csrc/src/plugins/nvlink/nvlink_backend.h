@@ -1,0 +1,244 @@
+// NVLINK backend: intra-box transfers between registered DRAM and VRAM regions.
+//
+// This is the B200-native replacement for the reference's default UCX backend
+// (src/plugins/ucx/ucx_backend.{h,cpp}); it fills the same south-bound interface:
+//   * registration exports what a peer needs to reach the memory (CUDA IPC handle of the
+//     enclosing allocation + offset for VRAM; pid + address for DRAM) in the public
+//     metadata blob, the slot where UCX ships rkeys;
+//   * loading remote metadata maps the peer's memory into this process (same process:
+//     the pointer itself plus peer access; other process: cudaIpcOpenMemHandle);
+//   * a transfer is ONE kernel launch per local GPU for the whole descriptor batch
+//     (xfer_kernels.cu), which stores straight into the peer's HBM over NVLink (WRITE) or
+//     loads from it (READ) and publishes completion to a host-mapped word;
+//   * DRAM<->DRAM moves by memcpy (same process) or process_vm_readv/writev (other
+//     process); pinned DRAM is visible to the copy kernel, so DRAM<->VRAM is the same kernel;
+//   * notifications travel as datagrams on an abstract unix socket (other process) or a
+//     direct queue push (same process), after the data is complete;
+//   * a dead peer is detected on the host (registry / pid / socket) and reported as
+//     NIXL_ERR_REMOTE_DISCONNECT; nothing on the GPU waits for a peer.
+// Device-side memory views for GPU-initiated transfers are prepared here too
+// (include/device/nixl_device.cuh).
+#ifndef NIXL_B200_NVLINK_BACKEND_H
+#define NIXL_B200_NVLINK_BACKEND_H
+
+#include <atomic>
+#include <condition_variable>
+#include <deque>
+#include <map>
+#include <memory>
+#include <mutex>
+#include <thread>
+#include <unordered_map>
+#include <vector>
+
+#include <cuda_runtime.h>
+
+#include "backend/backend_engine.h"
+#include "plugins/nvlink/xfer_kernels.h"
+
+namespace nixl_nvlink {
+
+// Identity of an engine as published in its connection info.
+struct PeerId {
+    std::string agent;
+    std::string host;
+    int64_t pid = 0;
+    uint64_t procTag = 0;   // random per process: tells "same pid number" from "same process"
+    uint64_t engineTag = 0; // random per engine instance
+    std::string sockName;   // abstract unix datagram socket receiving notifications
+};
+
+class Engine;
+
+// Local registration.
+class LocalMD : public nixlBackendMD {
+public:
+    LocalMD() : nixlBackendMD(true) {}
+    nixl_mem_t mem = DRAM_SEG;
+    uintptr_t addr = 0;
+    size_t len = 0;
+    int device = -1;           // VRAM: CUDA ordinal
+    uintptr_t devVisible = 0;  // address usable by kernels (VRAM: addr; pinned DRAM: mapped address; else 0)
+    bool pinnedByUs = false;   // we called cudaHostRegister
+    bool hasIpc = false;
+    cudaIpcMemHandle_t ipc{};
+    uint64_t ipcOffset = 0;    // addr - base of the enclosing allocation
+};
+
+// A peer's registration as seen from here.
+class RemoteMD : public nixlBackendMD {
+public:
+    RemoteMD() : nixlBackendMD(false) {}
+    std::string agent;
+    nixl_mem_t mem = DRAM_SEG;
+    uintptr_t addr = 0;        // address in the owner's address space
+    size_t len = 0;
+    int ownerDevice = -1;      // owner's CUDA ordinal (VRAM)
+    bool sameProcess = false;
+    uintptr_t devVisible = 0;  // kernel-usable address in THIS process covering [addr, addr+len); 0 if none
+    int mapDevice = -1;        // local device the IPC mapping was opened on (other-process VRAM)
+    int64_t ownerPid = 0;
+    std::string ipcKey;        // key into the process-wide IPC mapping cache (empty: none)
+    bool loopback = false;     // produced by loadLocalMD
+};
+
+// Simple first-fit sub-allocator over device slabs (tables and counters of requests).
+class DeviceArena {
+public:
+    explicit DeviceArena(int device) : device_(device) {}
+    ~DeviceArena();
+    void *alloc(size_t bytes); // 256-byte aligned; nullptr on failure
+    void free(void *p);
+
+private:
+    struct Slab { char *base; size_t size; std::map<size_t, size_t> freeByOff; std::map<size_t, size_t> used; };
+    int device_;
+    std::mutex mu_;
+    std::vector<Slab> slabs_;
+};
+
+// Per-device resources of one engine.
+struct DeviceCtx {
+    int device = -1;
+    cudaStream_t stream = nullptr;     // transfers
+    cudaStream_t prepStream = nullptr; // table uploads
+    std::unique_ptr<DeviceArena> arena;
+    uint64_t *flags = nullptr;         // pinned, mapped completion words
+    std::vector<int> freeFlags;
+    int gridCtas = 0;
+    std::mutex mu;
+};
+
+struct KernelBatch {
+    int device = -1;
+    std::vector<XferDesc> descs;
+    XferLaunch launch{};
+    void *table = nullptr; // arena block holding table + chunk starts (nullptr when inline)
+    unsigned int *counter = nullptr;
+    int flagSlot = -1;
+    cudaEvent_t uploaded = nullptr;
+    uint64_t seq = 0;
+    bool inFlight = false;
+};
+
+struct HostCopy { void *dst; const void *src; size_t len; };
+struct CmaCopy { uintptr_t local; uintptr_t remote; size_t len; };
+struct AsyncCopy { void *dst; const void *src; size_t len; int device; };
+
+class ReqH : public nixlBackendReqH {
+public:
+    nixl_xfer_op_t op = NIXL_WRITE;
+    std::string remoteAgent;
+    std::vector<KernelBatch> kernels;
+    std::vector<HostCopy> hostCopies;
+    std::vector<CmaCopy> cmaCopies;
+    int64_t cmaPid = 0;
+    std::vector<AsyncCopy> asyncCopies;
+    std::vector<std::pair<int, cudaEvent_t>> asyncEvents; // device, event
+    bool asyncInFlight = false;
+    size_t totalBytes = 0;
+    // notification to deliver once the data is complete
+    bool notifPending = false;
+    std::string notifMsg;
+    std::mutex mu; // progress thread vs. user thread
+    nixl_status_t last = NIXL_ERR_NOT_POSTED;
+};
+
+// Device-side view handle header (mirrors include/device/nixl_device.cuh).
+struct MemViewHost {
+    uint64_t magic;
+    const Engine *owner;
+    void *devBlock;
+    int device;
+};
+
+class Engine : public nixlBackendEngine {
+public:
+    explicit Engine(const nixlBackendInitParams *init);
+    ~Engine() override;
+
+    bool supportsRemote() const override { return true; }
+    bool supportsLocal() const override { return true; }
+    bool supportsNotif() const override { return true; }
+    nixl_mem_list_t getSupportedMems() const override { return {DRAM_SEG, VRAM_SEG}; }
+
+    nixl_status_t registerMem(const nixlBlobDesc &mem, const nixl_mem_t &nixl_mem, nixlBackendMD *&out) override;
+    nixl_status_t deregisterMem(nixlBackendMD *meta) override;
+    nixl_status_t connect(const std::string &remote_agent) override;
+    nixl_status_t disconnect(const std::string &remote_agent) override;
+    nixl_status_t unloadMD(nixlBackendMD *input) override;
+
+    nixl_status_t prepXfer(const nixl_xfer_op_t &operation, const nixl_meta_dlist_t &local, const nixl_meta_dlist_t &remote,
+                           const std::string &remote_agent, nixlBackendReqH *&handle,
+                           const nixl_opt_b_args_t *opt_args = nullptr) const override;
+    nixl_status_t postXfer(const nixl_xfer_op_t &operation, const nixl_meta_dlist_t &local, const nixl_meta_dlist_t &remote,
+                           const std::string &remote_agent, nixlBackendReqH *&handle,
+                           const nixl_opt_b_args_t *opt_args = nullptr) const override;
+    nixl_status_t checkXfer(nixlBackendReqH *handle) const override;
+    nixl_status_t releaseReqH(nixlBackendReqH *handle) const override;
+
+    nixl_status_t prepMemView(const nixl_remote_meta_dlist_t &, nixlMemViewH &, const nixl_opt_b_args_t * = nullptr) const override;
+    nixl_status_t prepMemView(const nixl_meta_dlist_t &, nixlMemViewH &, const nixl_opt_b_args_t * = nullptr) const override;
+    void releaseMemView(nixlMemViewH) const override;
+
+    nixl_status_t getPublicData(const nixlBackendMD *meta, std::string &str) const override;
+    nixl_status_t getConnInfo(std::string &str) const override;
+    nixl_status_t loadRemoteConnInfo(const std::string &remote_agent, const std::string &remote_conn_info) override;
+    nixl_status_t loadRemoteMD(const nixlBlobDesc &input, const nixl_mem_t &nixl_mem, const std::string &remote_agent,
+                               nixlBackendMD *&output) override;
+    nixl_status_t loadLocalMD(nixlBackendMD *input, nixlBackendMD *&output) override;
+
+    nixl_status_t getNotifs(notif_list_t &notif_list) override;
+    nixl_status_t genNotif(const std::string &remote_agent, const std::string &msg) const override;
+
+    nixl_status_t estimateXferCost(const nixl_xfer_op_t &, const nixl_meta_dlist_t &, const nixl_meta_dlist_t &,
+                                   const std::string &, nixlBackendReqH *const &, std::chrono::microseconds &,
+                                   std::chrono::microseconds &, nixl_cost_t &, const nixl_opt_args_t * = nullptr) const override;
+
+    // Used by peers in the same process.
+    void pushNotif(const std::string &from, const std::string &msg);
+    uint64_t engineTag() const { return self_.engineTag; }
+
+private:
+    DeviceCtx *ctx(int device) const;
+    bool peerAlive(const PeerId &peer) const;
+    nixl_status_t sendNotif(const PeerId &peer, const std::string &msg) const;
+    nixl_status_t finishIfDone(ReqH *req) const; // data complete -> deliver notification
+    nixl_status_t pollData(ReqH *req) const;
+    bool ensurePeerAccess(int from, int to) const;
+    void progressLoop();
+    void freeBatch(KernelBatch &b) const;
+
+    PeerId self_;
+    bool cuda_ = false;
+    int deviceCount_ = 0;
+    bool pinDram_ = true;
+    CopyPath copyPath_ = CopyPath::VECTOR;
+    int gridOverride_ = 0;
+    size_t memcpyAsyncThreshold_ = 0;
+    bool livenessPing_ = false;
+
+    mutable std::mutex peersMu_;
+    std::unordered_map<std::string, PeerId> peers_;
+
+    mutable std::mutex ctxMu_;
+    mutable std::vector<std::unique_ptr<DeviceCtx>> ctxs_;
+    mutable std::atomic<int> primaryDevice_{-1};
+
+    int notifFd_ = -1;
+    mutable std::mutex notifMu_;
+    notif_list_t inbox_; // same-process deliveries
+
+    // progress thread
+    bool progThread_ = false;
+    uint64_t progDelayUs_ = 0;
+    mutable std::mutex progMu_;
+    mutable std::condition_variable progCv_;
+    mutable std::vector<ReqH *> progWatch_;
+    std::atomic<bool> progStop_{false};
+    std::thread progTh_;
+};
+
+} // namespace nixl_nvlink
+
+#endif

@@ -1,0 +1,305 @@
+// Batched descriptor copy kernels for sm_100a.
+//
+// Replaces the per-descriptor put/get loop of the reference's UCX backend
+// (src/plugins/ucx/ucx_backend.cpp:1184-1265): a WRITE pushes with local loads and
+// stores into the peer's mapped memory, a READ pulls with loads over NVLink; both are
+// the same kernel because source and destination are just device-visible addresses
+// (local HBM, a peer GPU's HBM through NVLink, or pinned host memory through PCIe).
+// Completion and the hand-off to the host are fused into the kernel's tail.
+#include "plugins/nvlink/xfer_kernels.h"
+
+#include <cuda.h>
+
+namespace nixl_nvlink {
+namespace {
+
+constexpr int kThreads = 512;
+constexpr int kUnroll = 4;
+
+__device__ __forceinline__ uint4 ld_stream(const uint4 *p) {
+    uint4 v;
+    asm volatile("ld.global.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ void st_stream(uint4 *p, const uint4 &v) {
+    asm volatile("st.global.L1::no_allocate.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+                 : "memory");
+}
+
+__device__ __forceinline__ void st_release_sys(uint64_t *p, uint64_t v) {
+    asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+
+// Copies n bytes with the whole CTA.  Fast path: source and destination share their
+// offset within 16 bytes, so after a short head both are 16-byte aligned.
+__device__ __forceinline__ void copyRange(const char *__restrict__ s, char *__restrict__ d, size_t n) {
+    const unsigned tid = threadIdx.x;
+    if ((((uintptr_t)s ^ (uintptr_t)d) & 15) == 0) {
+        size_t head = (16 - ((uintptr_t)s & 15)) & 15;
+        if (head > n) head = n;
+        if (tid < head) d[tid] = s[tid];
+        s += head;
+        d += head;
+        n -= head;
+        const size_t nvec = n >> 4;
+        const uint4 *sv = reinterpret_cast<const uint4 *>(s);
+        uint4 *dv = reinterpret_cast<uint4 *>(d);
+        size_t i = tid;
+        // kUnroll independent loads in flight per thread before the first store.
+        for (; i + (kUnroll - 1) * kThreads < nvec; i += kUnroll * kThreads) {
+            uint4 v[kUnroll];
+#pragma unroll
+            for (int k = 0; k < kUnroll; ++k) v[k] = ld_stream(sv + i + k * kThreads);
+#pragma unroll
+            for (int k = 0; k < kUnroll; ++k) st_stream(dv + i + k * kThreads, v[k]);
+        }
+        for (; i < nvec; i += kThreads) st_stream(dv + i, ld_stream(sv + i));
+        const size_t done = nvec << 4;
+        const size_t tail = n - done;
+        if (tid < tail) d[done + tid] = s[done + tid];
+    } else if ((((uintptr_t)s ^ (uintptr_t)d) & 3) == 0) {
+        size_t head = (4 - ((uintptr_t)s & 3)) & 3;
+        if (head > n) head = n;
+        if (tid < head) d[tid] = s[tid];
+        s += head;
+        d += head;
+        n -= head;
+        const size_t nw = n >> 2;
+        const uint32_t *sw = reinterpret_cast<const uint32_t *>(s);
+        uint32_t *dw = reinterpret_cast<uint32_t *>(d);
+        for (size_t i = tid; i < nw; i += kThreads) dw[i] = sw[i];
+        const size_t done = nw << 2;
+        if (tid < n - done) d[done + tid] = s[done + tid];
+    } else {
+        for (size_t i = tid; i < n; i += kThreads) d[i] = s[i];
+    }
+}
+
+// Which descriptor owns chunk c?  Upper-bound search in the prefix array.
+template<class StartFn> __device__ __forceinline__ uint32_t ownerOf(uint32_t c, uint32_t n, StartFn start) {
+    uint32_t lo = 0, hi = n; // invariant: start(lo) <= c < start(hi)
+    while (hi - lo > 1) {
+        const uint32_t mid = (lo + hi) >> 1;
+        if (start(mid) <= c) lo = mid; else hi = mid;
+    }
+    return lo;
+}
+
+// Tail shared by all variants: publish completion once every CTA has finished.
+__device__ __forceinline__ void finishBatch(const XferLaunch &p) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence_system(); // this CTA's stores (ordered by the barrier) before the count
+        const unsigned prev = atomicAdd(p.doneCounter, 1u);
+        if (prev == gridDim.x - 1) {
+            *p.doneCounter = 0; // ready for the next post of this request
+            __threadfence_system();
+            st_release_sys(p.hostFlag, p.seq);
+        }
+    }
+}
+
+__global__ void __launch_bounds__(kThreads) batchCopyVector(const __grid_constant__ XferLaunch p) {
+    const bool inl = p.table == nullptr;
+    const size_t chunk = size_t(1) << p.chunkShift;
+    for (uint32_t c = blockIdx.x; c < p.totalChunks; c += gridDim.x) {
+        uint32_t i, first;
+        XferDesc d;
+        if (inl) {
+            i = ownerOf(c, p.nDescs, [&](uint32_t k) { return p.inlStart[k]; });
+            first = p.inlStart[i];
+            d = p.inl[i];
+        } else {
+            i = ownerOf(c, p.nDescs, [&](uint32_t k) { return __ldg(p.chunkStart + k); });
+            first = __ldg(p.chunkStart + i);
+            d.src = __ldg(&p.table[i].src);
+            d.dst = __ldg(&p.table[i].dst);
+            d.len = __ldg(&p.table[i].len);
+        }
+        const size_t off = size_t(c - first) << p.chunkShift;
+        const size_t n = d.len - off < chunk ? d.len - off : chunk;
+        copyRange(reinterpret_cast<const char *>(d.src) + off, reinterpret_cast<char *>(d.dst) + off, n);
+    }
+    finishBatch(p);
+}
+
+// ------------------------------------------------------------------ bulk (TMA 1-D) variant
+//
+// One elected thread per CTA drives a ring of shared-memory stages:
+//   cp.async.bulk global -> shared (completion on an mbarrier), then
+//   cp.async.bulk shared -> global (completion tracked by bulk groups).
+// No multicast anywhere: the source may be another GPU's memory.  Every wait is bounded;
+// on expiry the kernel records the failure in the completion word's top bit and leaves.
+
+constexpr int kStages = 4;
+constexpr uint32_t kStageBytes = 32 * 1024;
+constexpr uint64_t kWaitBudgetNs = 2000000000ull; // a bulk load that has not landed after 2 s is treated as lost
+
+__device__ __forceinline__ uint64_t globalTimerNs() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+__device__ __forceinline__ uint32_t smemAddr(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbarInit(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smemAddr(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbarExpectTx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smemAddr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbarTryWait(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok)
+                 : "r"(smemAddr(bar)), "r"(parity)
+                 : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ void bulkLoad(void *smem_dst, const void *gsrc, uint32_t bytes, uint64_t *bar) {
+    asm volatile("cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smemAddr(smem_dst)),
+                 "l"(gsrc), "r"(bytes), "r"(smemAddr(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void bulkStore(void *gdst, const void *smem_src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smemAddr(smem_src)), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void bulkCommit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template<int N> __device__ __forceinline__ void bulkWaitRead() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+template<int N> __device__ __forceinline__ void bulkWait() { asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory"); }
+
+__global__ void __launch_bounds__(128) batchCopyBulk(const __grid_constant__ XferLaunch p) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    __shared__ uint64_t full[kStages];
+    __shared__ int failed;
+    const bool inl = p.table == nullptr;
+    const size_t chunk = size_t(1) << p.chunkShift;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) mbarInit(&full[s], 1);
+        failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    uint32_t issued = 0; // pieces handed to the ring by thread 0
+    for (uint32_t c = blockIdx.x; c < p.totalChunks; c += gridDim.x) {
+        uint32_t i, first;
+        XferDesc d;
+        if (inl) {
+            i = ownerOf(c, p.nDescs, [&](uint32_t k) { return p.inlStart[k]; });
+            first = p.inlStart[i];
+            d = p.inl[i];
+        } else {
+            i = ownerOf(c, p.nDescs, [&](uint32_t k) { return __ldg(p.chunkStart + k); });
+            first = __ldg(p.chunkStart + i);
+            d.src = __ldg(&p.table[i].src);
+            d.dst = __ldg(&p.table[i].dst);
+            d.len = __ldg(&p.table[i].len);
+        }
+        const size_t off = size_t(c - first) << p.chunkShift;
+        const size_t n = d.len - off < chunk ? d.len - off : chunk;
+        const char *s = reinterpret_cast<const char *>(d.src) + off;
+        char *dst = reinterpret_cast<char *>(d.dst) + off;
+        // Bulk copies need 16-byte aligned addresses and sizes; anything else goes the SIMT way.
+        const bool bulk_ok = ((((uintptr_t)s | (uintptr_t)dst) & 15) == 0) && n >= 16;
+        if (!bulk_ok) {
+            for (size_t k = threadIdx.x; k < n; k += blockDim.x) dst[k] = s[k];
+            continue;
+        }
+        const size_t body = n & ~size_t(15);
+        if (threadIdx.x == 0 && !failed) {
+            // Software pipeline: keep up to kStages loads in flight; a stage is reused once
+            // the bulk store that read it has finished reading shared memory.
+            const uint32_t pieces = static_cast<uint32_t>((body + kStageBytes - 1) / kStageBytes);
+            uint32_t loaded = 0, stored = 0;
+            while (stored < pieces) {
+                while (loaded < pieces && loaded - stored < kStages) {
+                    const uint32_t g = issued + loaded;
+                    const uint32_t slot = g % kStages;
+                    if (g >= kStages) bulkWaitRead<kStages - 1>(); // the store that used this slot kStages pieces ago
+                    const size_t o = size_t(loaded) * kStageBytes;
+                    const uint32_t bytes = static_cast<uint32_t>(body - o < kStageBytes ? body - o : kStageBytes);
+                    mbarExpectTx(&full[slot], bytes);
+                    bulkLoad(smem + size_t(slot) * kStageBytes, s + o, bytes, &full[slot]);
+                    ++loaded;
+                }
+                const uint32_t g = issued + stored;
+                const uint32_t slot = g % kStages;
+                const uint32_t parity = (g / kStages) & 1;
+                uint32_t spins = 0;
+                uint64_t t0 = 0;
+                while (!mbarTryWait(&full[slot], parity)) {
+                    if ((++spins & 255u) == 0) { // look at the clock only now and then
+                        const uint64_t now = globalTimerNs();
+                        if (t0 == 0) t0 = now;
+                        else if (now - t0 > kWaitBudgetNs) {
+                            failed = 1;
+                            break;
+                        }
+                    }
+                }
+                if (failed) break;
+                const size_t o = size_t(stored) * kStageBytes;
+                const uint32_t bytes = static_cast<uint32_t>(body - o < kStageBytes ? body - o : kStageBytes);
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                bulkStore(dst + o, smem + size_t(slot) * kStageBytes, bytes);
+                bulkCommit();
+                ++stored;
+            }
+            issued += pieces;
+        }
+        // Sub-16-byte tail of the chunk.
+        if (threadIdx.x >= 32 && threadIdx.x - 32 < n - body) dst[body + threadIdx.x - 32] = s[body + threadIdx.x - 32];
+    }
+    if (threadIdx.x == 0) bulkWait<0>(); // all stores globally performed before the completion count
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence_system();
+        const unsigned prev = atomicAdd(p.doneCounter, 1u);
+        if (failed) atomicOr(reinterpret_cast<unsigned long long *>(p.hostFlag), 1ull << 63);
+        if (prev == gridDim.x - 1) {
+            *p.doneCounter = 0;
+            __threadfence_system();
+            // Bit 63 set by any CTA marks the batch as failed; keep it.
+            const unsigned long long cur = atomicAdd(reinterpret_cast<unsigned long long *>(p.hostFlag), 0ull);
+            st_release_sys(p.hostFlag, p.seq | (cur & (1ull << 63)));
+        }
+    }
+}
+
+} // namespace
+
+int defaultGridCtas(int device) {
+    int sms = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0) sms = 148;
+    return sms * 2;
+}
+
+cudaError_t launchBatchCopy(const XferLaunch &params, int grid_ctas, CopyPath path, cudaStream_t stream) {
+    if (params.totalChunks == 0) return cudaErrorInvalidValue;
+    int grid = grid_ctas > 0 ? grid_ctas : 296;
+    if (static_cast<uint32_t>(grid) > params.totalChunks) grid = static_cast<int>(params.totalChunks);
+    if (path == CopyPath::BULK) {
+        static bool attr_set[64] = {};
+        int dev = 0;
+        cudaGetDevice(&dev);
+        const size_t smem = size_t(kStages) * kStageBytes;
+        if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+            cudaError_t e = cudaFuncSetAttribute(batchCopyBulk, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+            if (e != cudaSuccess) return e;
+            attr_set[dev] = true;
+        }
+        batchCopyBulk<<<grid, 128, smem, stream>>>(params);
+    } else {
+        batchCopyVector<<<grid, kThreads, 0, stream>>>(params);
+    }
+    return cudaGetLastError();
+}
+
+} // namespace nixl_nvlink

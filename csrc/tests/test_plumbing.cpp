@@ -1,0 +1,228 @@
+// CPU plumbing: two agents in one process move 64 x 1 MiB DRAM descriptors (WRITE then
+// READ) with a completion notification, metadata round-trips through loadRemoteMD, and the
+// same buffers go to a file and back through the POSIX backend.
+// Mirrors the scenarios of the reference's test/gtest/test_transfer.cpp and
+// test/unit/plugins/posix/nixl_posix_test.cpp.
+#include <chrono>
+#include <cstring>
+#include <fcntl.h>
+#include <random>
+#include <thread>
+#include <unistd.h>
+
+#include "harness.h"
+#include "nixl.h"
+
+namespace {
+constexpr size_t kDescs = 64, kLen = 1 << 20;
+
+std::vector<uint8_t> seeded(size_t n, uint64_t seed) {
+    std::mt19937_64 g(seed);
+    std::vector<uint8_t> v(n);
+    for (size_t i = 0; i < n; i += 8) {
+        const uint64_t r = g();
+        std::memcpy(&v[i], &r, std::min<size_t>(8, n - i));
+    }
+    return v;
+}
+
+nixl_status_t waitDone(nixlAgent &a, nixlXferReqH *req) {
+    nixl_status_t st;
+    const auto deadline = std::chrono::steady_clock::now() + std::chrono::seconds(30);
+    while ((st = a.getXferStatus(req)) == NIXL_IN_PROG) {
+        if (std::chrono::steady_clock::now() > deadline) return NIXL_ERR_UNKNOWN;
+        std::this_thread::yield();
+    }
+    return st;
+}
+
+nixl_xfer_dlist_t slices(nixl_mem_t mem, const void *base, uint64_t dev) {
+    nixl_xfer_dlist_t l(mem);
+    for (size_t i = 0; i < kDescs; ++i) l.addDesc(nixlBasicDesc(reinterpret_cast<uintptr_t>(base) + i * kLen, kLen, dev));
+    return l;
+}
+} // namespace
+
+TEST_CASE(dram_write_read_notif) {
+    nixlAgentConfig cfg(false);
+    nixlAgent A("alpha", cfg), B("beta", cfg);
+    nixlBackendH *ba = nullptr, *bb = nullptr;
+    nixl_b_params_t params;
+    nixl_mem_list_t mems;
+    CHECK_EQ(A.getPluginParams("NVLINK", mems, params), NIXL_SUCCESS);
+    CHECK(mems.size() == 2);
+    CHECK_EQ(A.createBackend("NVLINK", params, ba), NIXL_SUCCESS);
+    CHECK_EQ(B.createBackend("UCX", params, bb), NIXL_SUCCESS); // alias of the NVLink backend
+
+    std::vector<uint8_t> src = seeded(kDescs * kLen, 0), dst(kDescs * kLen, 0);
+    nixl_reg_dlist_t ra(DRAM_SEG), rb(DRAM_SEG);
+    ra.addDesc(nixlBlobDesc(reinterpret_cast<uintptr_t>(src.data()), src.size(), 0, ""));
+    rb.addDesc(nixlBlobDesc(reinterpret_cast<uintptr_t>(dst.data()), dst.size(), 0, ""));
+    CHECK_EQ(A.registerMem(ra), NIXL_SUCCESS);
+    CHECK_EQ(B.registerMem(rb), NIXL_SUCCESS);
+
+    nixl_blob_t mdA, mdB;
+    CHECK_EQ(A.getLocalMD(mdA), NIXL_SUCCESS);
+    CHECK_EQ(B.getLocalMD(mdB), NIXL_SUCCESS);
+    std::string name;
+    CHECK_EQ(A.loadRemoteMD(mdB, name), NIXL_SUCCESS);
+    CHECK(name == "beta");
+    CHECK_EQ(B.loadRemoteMD(mdA, name), NIXL_SUCCESS);
+    CHECK(name == "alpha");
+    CHECK_EQ(A.loadRemoteMD(mdA, name), NIXL_ERR_INVALID_PARAM); // own metadata
+    CHECK_EQ(A.checkRemoteMD("beta", slices(DRAM_SEG, dst.data(), 0)), NIXL_SUCCESS);
+    CHECK_EQ(A.checkRemoteMD("gamma", nixl_xfer_dlist_t(DRAM_SEG)), NIXL_ERR_NOT_FOUND);
+
+    // WRITE alpha -> beta with a notification.
+    nixl_opt_args_t opt;
+    opt.notif = "write-done";
+    nixlXferReqH *req = nullptr;
+    CHECK_EQ(A.createXferReq(NIXL_WRITE, slices(DRAM_SEG, src.data(), 0), slices(DRAM_SEG, dst.data(), 0), "beta", req, &opt),
+             NIXL_SUCCESS);
+    nixl_status_t st = A.postXferReq(req);
+    CHECK(st == NIXL_SUCCESS || st == NIXL_IN_PROG);
+    CHECK_EQ(waitDone(A, req), NIXL_SUCCESS);
+    CHECK(src == dst);
+    nixl_notifs_t notifs;
+    for (int i = 0; i < 1000 && notifs.empty(); ++i) CHECK_EQ(B.getNotifs(notifs), NIXL_SUCCESS);
+    CHECK(notifs.count("alpha") == 1 && notifs["alpha"].size() == 1 && notifs["alpha"][0] == "write-done");
+    CHECK_EQ(A.releaseXferReq(req), NIXL_SUCCESS);
+
+    // READ: alpha pulls beta's (modified) buffer back.
+    for (auto &b : dst) b ^= 0x5a;
+    CHECK_EQ(A.createXferReq(NIXL_READ, slices(DRAM_SEG, src.data(), 0), slices(DRAM_SEG, dst.data(), 0), "beta", req),
+             NIXL_SUCCESS);
+    st = A.postXferReq(req);
+    CHECK(st >= 0);
+    CHECK_EQ(waitDone(A, req), NIXL_SUCCESS);
+    CHECK(src == dst);
+    // Requests are re-postable once complete.
+    st = A.postXferReq(req);
+    CHECK(st >= 0);
+    CHECK_EQ(waitDone(A, req), NIXL_SUCCESS);
+    CHECK_EQ(A.releaseXferReq(req), NIXL_SUCCESS);
+
+    // Stand-alone notification.
+    CHECK_EQ(B.genNotif("alpha", "hello"), NIXL_SUCCESS);
+    notifs.clear();
+    for (int i = 0; i < 1000 && notifs.empty(); ++i) A.getNotifs(notifs);
+    CHECK(notifs["beta"].size() == 1 && notifs["beta"][0] == "hello");
+
+    // After invalidation the remote is unknown.
+    CHECK_EQ(A.invalidateRemoteMD("beta"), NIXL_SUCCESS);
+    CHECK_EQ(A.createXferReq(NIXL_WRITE, slices(DRAM_SEG, src.data(), 0), slices(DRAM_SEG, dst.data(), 0), "beta", req),
+             NIXL_ERR_NOT_FOUND);
+    CHECK_EQ(A.deregisterMem(ra), NIXL_SUCCESS);
+    CHECK_EQ(B.deregisterMem(rb), NIXL_SUCCESS);
+}
+
+TEST_CASE(prepared_lists_and_merge) {
+    nixlAgentConfig cfg(false);
+    nixlAgent A("p1", cfg), B("p2", cfg);
+    nixlBackendH *ba = nullptr, *bb = nullptr;
+    CHECK_EQ(A.createBackend("NVLINK", {}, ba), NIXL_SUCCESS);
+    CHECK_EQ(B.createBackend("NVLINK", {}, bb), NIXL_SUCCESS);
+    std::vector<uint8_t> src = seeded(kDescs * 4096, 3), dst(kDescs * 4096, 0);
+    nixl_reg_dlist_t ra(DRAM_SEG), rb(DRAM_SEG);
+    ra.addDesc(nixlBlobDesc(reinterpret_cast<uintptr_t>(src.data()), src.size(), 0, ""));
+    rb.addDesc(nixlBlobDesc(reinterpret_cast<uintptr_t>(dst.data()), dst.size(), 0, ""));
+    CHECK_EQ(A.registerMem(ra), NIXL_SUCCESS);
+    CHECK_EQ(B.registerMem(rb), NIXL_SUCCESS);
+    nixl_blob_t md;
+    std::string name;
+    CHECK_EQ(B.getLocalMD(md), NIXL_SUCCESS);
+    CHECK_EQ(A.loadRemoteMD(md, name), NIXL_SUCCESS);
+
+    nixl_xfer_dlist_t l(DRAM_SEG), r(DRAM_SEG);
+    for (size_t i = 0; i < kDescs; ++i) {
+        l.addDesc(nixlBasicDesc(reinterpret_cast<uintptr_t>(src.data()) + i * 4096, 4096, 0));
+        r.addDesc(nixlBasicDesc(reinterpret_cast<uintptr_t>(dst.data()) + i * 4096, 4096, 0));
+    }
+    nixlDlistH *lh = nullptr, *rh = nullptr;
+    CHECK_EQ(A.prepXferDlist(NIXL_INIT_AGENT, l, lh), NIXL_SUCCESS);
+    CHECK_EQ(A.prepXferDlist("p2", r, rh), NIXL_SUCCESS);
+    // Reverse order on the remote side: block i lands in slot 63-i.
+    std::vector<int> li, ri;
+    for (int i = 0; i < (int)kDescs; ++i) {
+        li.push_back(i);
+        ri.push_back((int)kDescs - 1 - i);
+    }
+    nixlXferReqH *req = nullptr;
+    CHECK_EQ(A.makeXferReq(NIXL_WRITE, lh, li, rh, ri, req), NIXL_SUCCESS);
+    CHECK(A.postXferReq(req) >= 0);
+    CHECK_EQ(waitDone(A, req), NIXL_SUCCESS);
+    for (size_t i = 0; i < kDescs; ++i)
+        CHECK(std::memcmp(src.data() + i * 4096, dst.data() + (kDescs - 1 - i) * 4096, 4096) == 0);
+    CHECK_EQ(A.releaseXferReq(req), NIXL_SUCCESS);
+    // In-order indices merge into one descriptor; mismatched counts are rejected.
+    CHECK_EQ(A.makeXferReq(NIXL_WRITE, lh, li, rh, li, req), NIXL_SUCCESS);
+    CHECK(A.postXferReq(req) >= 0);
+    CHECK_EQ(waitDone(A, req), NIXL_SUCCESS);
+    CHECK(src == dst);
+    CHECK_EQ(A.releaseXferReq(req), NIXL_SUCCESS);
+    std::vector<int> short_idx = {0, 1};
+    CHECK_EQ(A.makeXferReq(NIXL_WRITE, lh, li, rh, short_idx, req), NIXL_ERR_INVALID_PARAM);
+    CHECK_EQ(A.makeXferReq(NIXL_WRITE, rh, li, lh, li, req), NIXL_ERR_INVALID_PARAM); // sides swapped
+    CHECK_EQ(A.releasedDlistH(lh), NIXL_SUCCESS);
+    CHECK_EQ(A.releasedDlistH(rh), NIXL_SUCCESS);
+}
+
+TEST_CASE(posix_file_roundtrip) {
+    nixlAgentConfig cfg(false);
+    nixlAgent A("filer", cfg);
+    nixlBackendH *posix = nullptr;
+    CHECK_EQ(A.createBackend("POSIX", {}, posix), NIXL_SUCCESS);
+    std::vector<uint8_t> src = seeded(kDescs * kLen, 0), back(kDescs * kLen, 0);
+    char path[] = "/tmp/nixl_b200_plumbing_XXXXXX";
+    const int fd = ::mkstemp(path);
+    CHECK(fd >= 0);
+
+    nixl_reg_dlist_t rm(DRAM_SEG), rf(FILE_SEG);
+    rm.addDesc(nixlBlobDesc(reinterpret_cast<uintptr_t>(src.data()), src.size(), 0, ""));
+    rm.addDesc(nixlBlobDesc(reinterpret_cast<uintptr_t>(back.data()), back.size(), 0, ""));
+    rf.addDesc(nixlBlobDesc(0, 0, fd, "")); // whole file, fd mode
+    CHECK_EQ(A.registerMem(rm), NIXL_SUCCESS);
+    CHECK_EQ(A.registerMem(rf), NIXL_SUCCESS);
+
+    nixl_xfer_dlist_t file(FILE_SEG);
+    for (size_t i = 0; i < kDescs; ++i) file.addDesc(nixlBasicDesc(i * kLen, kLen, fd));
+    nixlXferReqH *req = nullptr;
+    CHECK_EQ(A.createXferReq(NIXL_WRITE, slices(DRAM_SEG, src.data(), 0), file, "filer", req), NIXL_SUCCESS);
+    CHECK(A.postXferReq(req) >= 0);
+    CHECK_EQ(waitDone(A, req), NIXL_SUCCESS);
+    CHECK_EQ(A.releaseXferReq(req), NIXL_SUCCESS);
+    CHECK_EQ(A.createXferReq(NIXL_READ, slices(DRAM_SEG, back.data(), 0), file, "filer", req), NIXL_SUCCESS);
+    CHECK(A.postXferReq(req) >= 0);
+    CHECK_EQ(waitDone(A, req), NIXL_SUCCESS);
+    CHECK_EQ(A.releaseXferReq(req), NIXL_SUCCESS);
+    CHECK(src == back);
+
+    // queryMem: the file exists and has the expected size; a bogus name does not.
+    nixl_reg_dlist_t q(FILE_SEG);
+    q.addDesc(nixlBlobDesc(0, 0, 0, path));
+    q.addDesc(nixlBlobDesc(0, 0, 0, "/nonexistent/nixl_b200"));
+    std::vector<nixl_query_resp_t> resp;
+    nixl_opt_args_t opt;
+    opt.backends.push_back(posix);
+    CHECK_EQ(A.queryMem(q, resp, &opt), NIXL_SUCCESS);
+    CHECK(resp.size() == 2 && resp[0].has_value() && !resp[1].has_value());
+    CHECK(resp[0]->at("size") == std::to_string(kDescs * kLen));
+
+    // Path mode: the backend opens the file itself; devId is just a unique key.
+    CHECK_EQ(A.deregisterMem(rf), NIXL_SUCCESS);
+    nixl_reg_dlist_t rp(FILE_SEG);
+    rp.addDesc(nixlBlobDesc(0, 0, 777, std::string("ro:") + path));
+    CHECK_EQ(A.registerMem(rp), NIXL_SUCCESS);
+    std::fill(back.begin(), back.end(), 0);
+    nixl_xfer_dlist_t pfile(FILE_SEG);
+    for (size_t i = 0; i < kDescs; ++i) pfile.addDesc(nixlBasicDesc(i * kLen, kLen, 777));
+    CHECK_EQ(A.createXferReq(NIXL_READ, slices(DRAM_SEG, back.data(), 0), pfile, "filer", req), NIXL_SUCCESS);
+    CHECK(A.postXferReq(req) >= 0);
+    CHECK_EQ(waitDone(A, req), NIXL_SUCCESS);
+    CHECK_EQ(A.releaseXferReq(req), NIXL_SUCCESS);
+    CHECK(src == back);
+    ::close(fd);
+    ::unlink(path);
+}
+
+TEST_MAIN()
