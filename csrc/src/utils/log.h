@@ -26,10 +26,14 @@ private:
     int line_;
     std::ostringstream ss_;
 };
+struct Voidify {
+    void operator&(const Line &) {}
+};
 } // namespace nixl_log
 
+// `cond ? (void)0 : Voidify() & stream` keeps the macro a single expression (no dangling else).
 #define NIXL_LOG_AT(lvl) \
-    if (nixl_log::lvl < nixl_log::threshold()) {} else nixl_log::Line(nixl_log::lvl, __FILE__, __LINE__)
+    (nixl_log::lvl < nixl_log::threshold()) ? (void)0 : nixl_log::Voidify() & nixl_log::Line(nixl_log::lvl, __FILE__, __LINE__)
 #define NIXL_TRACE NIXL_LOG_AT(TRACE)
 #define NIXL_DEBUG NIXL_LOG_AT(DEBUG)
 #define NIXL_INFO NIXL_LOG_AT(INFO)

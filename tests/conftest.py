@@ -1,0 +1,11 @@
+"""pytest configuration: registers the `gpu` marker and makes the repository importable."""
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: test needs at least one CUDA GPU (run with -m gpu on a B200 box)")

@@ -1,0 +1,135 @@
+"""Python API on CPU: two agents in one process, torch CPU tensors, notifications,
+descriptor helpers, metadata helpers.  Mirrors the reference's test/python/test_nixl_api.py
+and examples/python/basic_two_peers.py scenarios."""
+import pickle
+
+import numpy as np
+import pytest
+import torch
+
+import nixl_b200
+from nixl_b200 import _bindings as nb
+from nixl_b200 import nixl_agent, nixl_agent_config
+
+
+def _wait(agent, handle, limit=200000):
+    for _ in range(limit):
+        state = agent.check_xfer_state(handle)
+        if state != "PROC":
+            return state
+    return "TIMEOUT"
+
+
+@pytest.fixture
+def pair():
+    a = nixl_agent("py_a", nixl_agent_config(enable_prog_thread=False))
+    b = nixl_agent("py_b", nixl_agent_config(enable_prog_thread=True))
+    yield a, b
+    del a, b
+
+
+def test_plugins_visible(pair):
+    a, _ = pair
+    assert "NVLINK" in a.get_plugin_list() and "POSIX" in a.get_plugin_list()
+    assert set(a.get_plugin_mem_types("NVLINK")) == {"DRAM_SEG", "VRAM_SEG"}
+    assert "copy_path" in a.get_plugin_params("NVLINK")
+    assert "UCX" in a.backends  # default backend name resolves to the NVLink backend
+    assert a.get_backend_mem_types("UCX") == ["DRAM_SEG", "VRAM_SEG"]
+
+
+def test_descriptor_helpers(pair):
+    a, _ = pair
+    t = torch.arange(1024, dtype=torch.float32)
+    xl = a.get_xfer_descs(t)
+    assert len(xl) == 1 and xl[0] == (t.data_ptr(), 4096, 0)
+    arr = np.array([[4096, 128, 0], [8192, 256, 1]], dtype=np.uint64)
+    xa = a.get_xfer_descs(arr, "DRAM")
+    assert xa[1] == (8192, 256, 1) and xa.totalBytes() == 384
+    assert (xa.to_array() == arr).all()
+    rl = a.get_reg_descs([(4096, 128, 0, "meta")], "FILE")
+    assert rl[0][3] == b"meta" and rl.getType() == nb.FILE_SEG
+    again = pickle.loads(pickle.dumps(xa))
+    assert again == xa
+    again_r = a.deserialize_descs(a.get_serialized_descs(rl))
+    assert again_r == rl
+    with pytest.raises(ValueError):
+        a.get_xfer_descs(t.t().reshape(32, 32).t())  # non-contiguous
+
+
+def test_write_read_with_notifications(pair):
+    a, b = pair
+    src = torch.randint(0, 255, (64, 1 << 16), dtype=torch.uint8)
+    dst = torch.zeros_like(src)
+    reg_a = a.register_memory(src)
+    reg_b = b.register_memory(dst)
+    name = a.add_remote_agent(b.get_agent_metadata())
+    assert name == "py_b"
+    assert b.add_remote_agent(a.get_agent_metadata()) == "py_a"
+    assert a.check_remote_metadata("py_b", a.get_xfer_descs(dst))
+
+    h = a.initialize_xfer("WRITE", [src[i] for i in range(64)], [dst[i] for i in range(64)], "py_b", b"wr-1")
+    assert a.transfer(h) in ("DONE", "PROC")
+    assert _wait(a, h) == "DONE"
+    assert torch.equal(src, dst)
+    for _ in range(10000):
+        if b.check_remote_xfer_done("py_a", b"wr-"):
+            break
+    else:
+        pytest.fail("notification never arrived")
+    assert a.query_xfer_backend(h) == "UCX"
+    dur, margin, method = a.estimate_xfer_cost(h)
+    assert dur > 0 and margin > 0 and method == nb.NIXL_COST_ANALYTICAL_BACKEND
+    a.release_xfer_handle(h)
+
+    dst.add_(1)
+    h = a.initialize_xfer("READ", src, dst, "py_b")
+    assert a.transfer(h) in ("DONE", "PROC")
+    assert _wait(a, h) == "DONE"
+    assert torch.equal(src, dst)
+    a.release_xfer_handle(h)
+
+    b.send_notif("py_a", b"ping")
+    got = {}
+    for _ in range(10000):
+        got = a.get_new_notifs()
+        if got:
+            break
+    assert got == {"py_b": [b"ping"]}
+
+    a.remove_remote_agent("py_b")
+    with pytest.raises(nb.nixlNotFoundError):
+        a.initialize_xfer("WRITE", src, dst, "py_b")
+    a.deregister_memory(reg_a)
+    b.deregister_memory(reg_b)
+
+
+def test_prepped_transfers(pair):
+    a, b = pair
+    src = torch.randint(0, 255, (32, 4096), dtype=torch.uint8)
+    dst = torch.zeros_like(src)
+    a.register_memory(src)
+    b.register_memory(dst)
+    a.add_remote_agent(b.get_agent_metadata())
+    lside = a.prep_xfer_dlist("NIXL_INIT_AGENT", [src[i] for i in range(32)])
+    rside = a.prep_xfer_dlist("py_b", [dst[i] for i in range(32)])
+    perm = np.random.default_rng(0).permutation(32).astype(np.int32)
+    h = a.make_prepped_xfer("WRITE", lside, list(range(32)), rside, perm, b"prepped")
+    assert a.transfer(h) in ("DONE", "PROC")
+    assert _wait(a, h) == "DONE"
+    for i in range(32):
+        assert torch.equal(src[i], dst[perm[i]])
+    a.release_xfer_handle(h)
+    with pytest.raises(nb.nixlInvalidParamError):
+        a.make_prepped_xfer("WRITE", lside, [0, 1], rside, [0])
+    a.release_dlist_handle(lside)
+    a.release_dlist_handle(rside)
+
+
+def test_error_types():
+    a = nixl_agent("py_err", nixl_agent_config(backends=[]))
+    with pytest.raises(nb.nixlNotFoundError):
+        a.create_backend("NO_SUCH_BACKEND")
+    with pytest.raises(nb.nixlInvalidParamError):
+        a.get_agent_metadata()  # no backend that supports remote access
+    assert issubclass(nb.nixlNotFoundError, nb.nixlError)
+    assert nixl_b200.__version__
