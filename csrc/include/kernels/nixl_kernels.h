@@ -55,6 +55,98 @@ typedef struct NixlKvXferParams {
 
 int nixl_kv_xfer_launch(const NixlKvXferParams *params, void *stream);
 
+
+/* ---------------------------------------------------------------- MoE expert-parallel all-to-all
+ *
+ * Every rank owns one symmetric buffer (same layout on all ranks) registered with its agent;
+ * `peers` is a remote memory view whose entry r is rank r's buffer (entry `rank` is the local
+ * one; a hole marks an absent rank).  All offsets below are byte offsets into that buffer and
+ * already select the parity (double-buffer half) of this call.
+ *
+ * Dispatch ("count first, then place"):
+ *   1. histogram of topk_idx -> tokens per expert;
+ *   2. the E counts go to every rank (all-gather), with an epoch flag;
+ *   3. once all counts are in, every sender knows where its rows belong at every receiver:
+ *      rows of one expert are contiguous and ordered by source rank, so the receiver needs
+ *      no second pass to pack them;
+ *   4. each token is read once, quantised once (1x128 e4m3 + fp32 scale) and stored to the
+ *      up-to-K receivers' packed buffers over NVLink, with its source in `info`;
+ *   5. per (expert, source) flags tell the receiver - or a consumer kernel such as the grouped
+ *      GEMM below - when an expert's rows from one source have landed.
+ * Combine sends expert outputs back to (source rank, token, k) and the source reduces
+ * sum_k w[t,k] * y[t,k] in fp32.
+ * Every wait on a peer is bounded by timeout_ns; on expiry the peer is marked in `mask`, a bit
+ * is set in `status` and the kernel carries on without it.  Nothing traps.
+ *
+ * Parity with the reference's examples/device/ep (low-latency dispatch/combine kernels
+ * nixl_ep_ll.cu:72,:619 and the layout kernel layout.cu:32); the placement algorithm, the
+ * single-pass receive and the throughput ("compact") layout are this library's own.
+ */
+typedef struct NixlEpLayout {
+    int64_t off_counts;      /* int32  [R][E]   counts[r][e]: tokens rank r sends to expert e */
+    int64_t off_counts_flag; /* uint64 [R]      epoch once row r of counts is complete */
+    int64_t off_disp_flag;   /* uint64 [El][R]  epoch once rows of (local expert, source) landed */
+    int64_t off_recv_x;      /* [cap][row_bytes] dispatched tokens (e4m3 or bf16) */
+    int64_t off_recv_scales; /* float  [cap][H/128] (fp8 only) */
+    int64_t off_recv_info;   /* uint32 [cap][2] {source rank, token*K + k} */
+    int64_t off_comb_x;      /* bf16   [M][K][H] combine landing zone */
+    int64_t off_comb_flag;   /* uint64 [R]      epoch once rank r finished its combine sends */
+} NixlEpLayout;
+
+typedef struct NixlEpScratch { /* device memory private to the rank; zero before first use */
+    int32_t *cnt;      /* [E] */
+    int32_t *fill;     /* [E] */
+    int32_t *sent;     /* [E] */
+    uint32_t *barrier; /* [4] */
+    int32_t *status;   /* [1] bit0: a peer timed out, bit1: grid barrier timed out, bit2: capacity exceeded */
+    int32_t *mask;     /* [R] non-zero: rank excluded */
+} NixlEpScratch;
+
+typedef struct NixlEpDispatchParams {
+    const void *x;            /* bf16 [T][H] */
+    const int64_t *topk_idx;  /* [T][K], -1 = unused slot */
+    int32_t T, K, H, E, R, rank;
+    int32_t use_fp8;          /* 1: e4m3 + scales, 0: bf16 */
+    int32_t round_scale;      /* 1: scales rounded up to a power of two */
+    int32_t rows_per_expert;  /* >0: expert le starts at row le*rows_per_expert; 0: compact (prefix) layout */
+    int32_t cap;              /* rows available at every receiver */
+    int32_t phases;           /* bit0 send, bit1 receive (wait for arrivals) */
+    int32_t grid;             /* CTAs (cooperative launch); 0 = one per SM */
+    const void *peers;        /* remote memory view */
+    NixlEpLayout lay;
+    uint64_t epoch;
+    uint64_t timeout_ns;
+    int32_t *recv_count;      /* out [El] rows per local expert */
+    int64_t *layout_range;    /* out [El][R] (first row within expert << 32) | rows */
+    int32_t *expert_offsets;  /* out [El+1] first row of each local expert (both layouts) */
+    NixlEpScratch scr;
+} NixlEpDispatchParams;
+
+typedef struct NixlEpCombineParams {
+    const void *x;              /* bf16 [cap][H] expert outputs, rows as delivered by dispatch */
+    const uint32_t *recv_info;  /* [cap][2] from the dispatch being answered (local pointer) */
+    const int32_t *recv_count;  /* [El] */
+    const int32_t *expert_offsets; /* [El+1] */
+    const int64_t *topk_idx;    /* [T][K] */
+    const float *topk_weights;  /* [T][K] */
+    void *out;                  /* bf16 [T][H] */
+    int32_t T, K, H, E, R, rank;
+    int32_t phases;
+    int32_t grid;
+    const void *peers;
+    NixlEpLayout lay;
+    uint64_t epoch;
+    uint64_t timeout_ns;
+    NixlEpScratch scr;
+} NixlEpCombineParams;
+
+int nixl_ep_dispatch_launch(const NixlEpDispatchParams *params, void *stream);
+int nixl_ep_combine_launch(const NixlEpCombineParams *params, void *stream);
+/* Barrier across ranks through the symmetric buffers (bounded): flag slot `slot` of
+ * off_counts_flag-style array at `off_flags`. */
+int nixl_ep_barrier_launch(const void *peers, int64_t off_flags, int32_t R, int32_t rank, uint64_t epoch, uint64_t timeout_ns,
+                           int32_t *status, int32_t *mask, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,490 @@
+// MoE expert-parallel dispatch / combine for one NVLink domain (contract and algorithm:
+// include/kernels/nixl_kernels.h).
+//
+// Both kernels are persistent, cooperatively launched grids (every CTA resident, so the
+// in-kernel grid barrier cannot deadlock) of 256 threads.  Peer memory is reached through the
+// remote memory view prepared by the agent: plain stores over NVLink, release-ordered flags,
+// and bounded waits that mask a silent peer instead of hanging the GPU.
+#include <cooperative_groups.h>
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+
+#include "device/nixl_device_layout.h"
+#include "kernels/nixl_kernels.h"
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kMaxRanks = 64;
+constexpr int kMaxTopk = 16;
+constexpr int kGroup = 128; // channels per quantisation group
+
+enum : int { ST_PEER_TIMEOUT = 1, ST_BARRIER_TIMEOUT = 2, ST_CAPACITY = 4 };
+
+// ------------------------------------------------------------------ small device helpers
+
+__device__ __forceinline__ uint64_t nowNs() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ uint64_t ldAcquireSys(const uint64_t *p) {
+    uint64_t v;
+    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void stReleaseSys(uint64_t *p, uint64_t v) {
+    asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned ldAcquireGpu(const unsigned *p) {
+    unsigned v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ int ldVolatile(const int *p) { return *reinterpret_cast<const volatile int *>(p); }
+__device__ __forceinline__ uint4 ldNc(const void *p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ void stPeer16(void *p, const uint4 &v) {
+    asm volatile("st.global.L1::no_allocate.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+__device__ __forceinline__ char *peerBase(const void *view, int r) {
+    const nixlMemViewEntry *e = reinterpret_cast<const nixlMemViewEntry *>(static_cast<const char *>(view) + sizeof(nixlMemViewHeader));
+    return reinterpret_cast<char *>(e[r].ptr);
+}
+
+// Waits until *flag >= epoch.  False on timeout.
+__device__ __forceinline__ bool waitFlag(const uint64_t *flag, uint64_t epoch, uint64_t timeout_ns) {
+    uint64_t t0 = 0;
+    unsigned spins = 0;
+    while (ldAcquireSys(flag) < epoch) {
+        if ((++spins & 31u) == 0) {
+            const uint64_t now = nowNs();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > timeout_ns) return false;
+        }
+    }
+    return true;
+}
+
+// Grid-wide barrier on two words {arrivals, generation}.  Bounded: on timeout sets the status
+// bit and returns (the caller's results are then unreliable, which the host sees in `status`).
+__device__ __forceinline__ void gridBarrier(unsigned *bar, int *status, uint64_t timeout_ns) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned gen = ldAcquireGpu(bar + 1);
+        __threadfence();
+        if (atomicAdd(bar, 1u) == gridDim.x - 1) {
+            bar[0] = 0;
+            __threadfence();
+            atomicAdd(bar + 1, 1u);
+        } else {
+            uint64_t t0 = 0;
+            unsigned spins = 0;
+            while (ldAcquireGpu(bar + 1) == gen) {
+                if ((++spins & 63u) == 0) {
+                    const uint64_t now = nowNs();
+                    if (t0 == 0) t0 = now;
+                    else if (now - t0 > timeout_ns) {
+                        atomicOr(status, ST_BARRIER_TIMEOUT);
+                        break;
+                    }
+                }
+            }
+        }
+    }
+    __syncthreads();
+}
+
+// ------------------------------------------------------------------ dispatch
+
+// Quantises one 128-channel group held by 16 lanes (8 bf16 each): returns 8 e4m3 bytes and,
+// in lane%16 == 0, the group's scale.
+__device__ __forceinline__ uint2 quantGroup(const uint4 &raw, bool round_scale, float &scale_out) {
+    const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&raw);
+    float f[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 v = __bfloat1622float2(h[i]);
+        f[2 * i] = v.x;
+        f[2 * i + 1] = v.y;
+    }
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(f[i]));
+#pragma unroll
+    for (int o = 8; o >= 1; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    amax = fmaxf(amax, 1e-4f); // margin of the reference's cast (csrc/kernels/utils.cuh:430-456): never divide by ~0
+    float scale = amax / 448.f, inv;
+    if (round_scale) {
+        const int ex = static_cast<int>(ceilf(log2f(scale)));
+        scale = exp2f(static_cast<float>(ex));
+        inv = exp2f(static_cast<float>(-ex));
+    } else {
+        inv = 448.f / amax;
+    }
+    scale_out = scale;
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+        w[i] = static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(make_float2(f[2 * i] * inv, f[2 * i + 1] * inv), __NV_SATFINITE, __NV_E4M3));
+    return make_uint2(w[0] | (w[1] << 16), w[2] | (w[3] << 16));
+}
+
+__global__ void __launch_bounds__(kThreads) epDispatchKernel(const __grid_constant__ NixlEpDispatchParams p) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    const int El = p.E / p.R;
+    const int groups = p.H / kGroup;
+    const int row_bytes = p.use_fp8 ? p.H : p.H * 2;
+    // shared: before[E] | ebase[E] | slots[kMaxTopk] | row bytes | scales
+    int *before = reinterpret_cast<int *>(smem);
+    int *ebase = before + p.E;
+    int *slots = ebase + p.E;
+    unsigned char *rowbuf = reinterpret_cast<unsigned char *>(slots + kMaxTopk);
+    float *scalebuf = reinterpret_cast<float *>(rowbuf + row_bytes);
+
+    char *self = peerBase(p.peers, p.rank);
+    const int tid = threadIdx.x;
+
+    if (p.phases & 1) {
+        // 1. histogram of destinations
+        const long long n = static_cast<long long>(p.T) * p.K;
+        for (long long i = static_cast<long long>(blockIdx.x) * kThreads + tid; i < n; i += static_cast<long long>(gridDim.x) * kThreads) {
+            const long long e = p.topk_idx[i];
+            if (e >= 0 && e < p.E && ldVolatile(p.scr.mask + static_cast<int>(e) / El) == 0) atomicAdd(p.scr.cnt + e, 1);
+        }
+        gridBarrier(p.scr.barrier, p.scr.status, p.timeout_ns);
+
+        // 2. all-gather of counts: CTA b serves destination ranks b, b+grid, ...
+        for (int d = blockIdx.x; d < p.R; d += gridDim.x) {
+            if (ldVolatile(p.scr.mask + d) != 0) continue;
+            char *peer = peerBase(p.peers, d);
+            if (peer == nullptr) continue;
+            int *dst = reinterpret_cast<int *>(peer + p.lay.off_counts) + static_cast<long long>(p.rank) * p.E;
+            for (int e = tid; e < p.E; e += kThreads) dst[e] = ldVolatile(p.scr.cnt + e);
+            // Experts of that rank that get nothing from us are complete right away.
+            uint64_t *dflag = reinterpret_cast<uint64_t *>(peer + p.lay.off_disp_flag);
+            __syncthreads();
+            if (tid == 0) {
+                __threadfence_system();
+                stReleaseSys(reinterpret_cast<uint64_t *>(peer + p.lay.off_counts_flag) + p.rank, p.epoch);
+            }
+            for (int le = tid; le < El; le += kThreads)
+                if (ldVolatile(p.scr.cnt + d * El + le) == 0) stReleaseSys(dflag + static_cast<long long>(le) * p.R + p.rank, p.epoch);
+        }
+    }
+
+    // 3. wait for everybody's counts (every CTA looks for itself: 8 flags, no grid barrier needed)
+    const uint64_t *cflag = reinterpret_cast<const uint64_t *>(self + p.lay.off_counts_flag);
+    if (tid < p.R) {
+        if (ldVolatile(p.scr.mask + tid) == 0 && peerBase(p.peers, tid) != nullptr) {
+            if (!waitFlag(cflag + tid, p.epoch, p.timeout_ns)) {
+                atomicExch(p.scr.mask + tid, 1);
+                atomicOr(p.scr.status, ST_PEER_TIMEOUT);
+            }
+        } else if (peerBase(p.peers, tid) == nullptr) {
+            atomicExch(p.scr.mask + tid, 1);
+        }
+    }
+    __syncthreads();
+
+    // 4. placement tables.  counts[r][e] is the local copy of the all-gather.
+    const int *counts = reinterpret_cast<const int *>(self + p.lay.off_counts);
+    for (int e = tid; e < p.E; e += kThreads) {
+        int b = 0, total = 0;
+        for (int r = 0; r < p.R; ++r) {
+            if (ldVolatile(p.scr.mask + r) != 0) continue;
+            const int c = ldVolatile(counts + static_cast<long long>(r) * p.E + e);
+            if (r < p.rank) b += c;
+            total += c;
+        }
+        before[e] = b;
+        ebase[e] = total; // totals first, turned into per-rank prefixes below
+    }
+    __syncthreads();
+    if (p.rows_per_expert > 0) {
+        for (int e = tid; e < p.E; e += kThreads) {
+            const int total = ebase[e];
+            if (total > p.rows_per_expert) atomicOr(p.scr.status, ST_CAPACITY);
+        }
+        __syncthreads();
+        for (int e = tid; e < p.E; e += kThreads) ebase[e] = (e % El) * p.rows_per_expert;
+    } else if (tid < p.R) {
+        // exclusive prefix over the local experts of destination rank `tid`
+        int run = 0;
+        for (int le = 0; le < El; ++le) {
+            const int total = ebase[tid * El + le];
+            ebase[tid * El + le] = run;
+            run += total;
+        }
+        if (run > p.cap) atomicOr(p.scr.status, ST_CAPACITY);
+    }
+    __syncthreads();
+
+    // Receiver-side bookkeeping is known as soon as the counts are: CTA 0 publishes it.
+    if (blockIdx.x == 0 && (p.phases & 2)) {
+        for (int le = tid; le < El; le += kThreads) {
+            const int e = p.rank * El + le;
+            int total = 0;
+            for (int r = 0; r < p.R; ++r) {
+                int c = 0;
+                if (ldVolatile(p.scr.mask + r) == 0) c = ldVolatile(counts + static_cast<long long>(r) * p.E + e);
+                p.layout_range[static_cast<long long>(le) * p.R + r] = (static_cast<long long>(total) << 32) | static_cast<unsigned>(c);
+                total += c;
+            }
+            p.recv_count[le] = total;
+            p.expert_offsets[le] = ebase[e];
+            if (le == El - 1) p.expert_offsets[El] = ebase[e] + (p.rows_per_expert > 0 ? p.rows_per_expert : total);
+        }
+    }
+
+    if (p.phases & 1) {
+        // 5. data: one token per CTA iteration
+        const __nv_bfloat16 *x = static_cast<const __nv_bfloat16 *>(p.x);
+        const int vecs = p.H / 8; // 16-byte bf16 vectors per row
+        for (int t = blockIdx.x; t < p.T; t += gridDim.x) {
+            const uint4 *src = reinterpret_cast<const uint4 *>(x + static_cast<long long>(t) * p.H);
+            if (p.use_fp8) {
+                // 16 lanes own one 128-channel group
+                for (int v = tid; v < vecs; v += kThreads) {
+                    float scale;
+                    const uint2 q = quantGroup(ldNc(src + v), p.round_scale != 0, scale);
+                    reinterpret_cast<uint2 *>(rowbuf)[v] = q;
+                    if ((v & 15) == 0) scalebuf[v >> 4] = scale;
+                }
+            } else {
+                for (int v = tid; v < vecs; v += kThreads) reinterpret_cast<uint4 *>(rowbuf)[v] = ldNc(src + v);
+            }
+            // reserve one slot per destination
+            if (tid < p.K) {
+                const long long e = p.topk_idx[static_cast<long long>(t) * p.K + tid];
+                int slot = -1;
+                if (e >= 0 && e < p.E && ldVolatile(p.scr.mask + static_cast<int>(e) / El) == 0) slot = atomicAdd(p.scr.fill + e, 1);
+                slots[tid] = slot;
+            }
+            __syncthreads();
+            for (int k = 0; k < p.K; ++k) {
+                const int slot = slots[k];
+                if (slot < 0) continue;
+                const int e = static_cast<int>(p.topk_idx[static_cast<long long>(t) * p.K + k]);
+                const int d = e / El;
+                const long long row = static_cast<long long>(ebase[e]) + before[e] + slot;
+                if (row >= p.cap) continue; // flagged as ST_CAPACITY above
+                char *peer = peerBase(p.peers, d);
+                uint4 *dx = reinterpret_cast<uint4 *>(peer + p.lay.off_recv_x + row * row_bytes);
+                for (int v = tid; v < row_bytes / 16; v += kThreads) stPeer16(dx + v, reinterpret_cast<const uint4 *>(rowbuf)[v]);
+                if (p.use_fp8) {
+                    float *ds = reinterpret_cast<float *>(peer + p.lay.off_recv_scales) + row * groups;
+                    for (int g = tid; g < groups; g += kThreads) ds[g] = scalebuf[g];
+                }
+                if (tid == 0) {
+                    uint2 info = make_uint2(static_cast<unsigned>(p.rank), static_cast<unsigned>(t * p.K + k));
+                    *reinterpret_cast<uint2 *>(peer + p.lay.off_recv_info + row * 8) = info;
+                }
+            }
+            __syncthreads(); // all stores of this token issued (and rowbuf free for the next one)
+            if (tid < p.K && slots[tid] >= 0) {
+                // Count the row as sent; whoever completes an expert's rows raises its flag.
+                const int e = static_cast<int>(p.topk_idx[static_cast<long long>(t) * p.K + tid]);
+                __threadfence_system();
+                const int done = atomicAdd(p.scr.sent + e, 1) + 1;
+                if (done == ldVolatile(p.scr.cnt + e)) {
+                    __threadfence_system(); // acquire side of the count: other CTAs' rows of this expert are out
+                    char *peer = peerBase(p.peers, e / El);
+                    stReleaseSys(reinterpret_cast<uint64_t *>(peer + p.lay.off_disp_flag) + static_cast<long long>(e % El) * p.R + p.rank, p.epoch);
+                }
+            }
+            __syncthreads();
+        }
+    }
+
+    if (p.phases & 2) {
+        // 6. arrivals: El x R flags, spread over the grid's threads
+        const uint64_t *dflag = reinterpret_cast<const uint64_t *>(self + p.lay.off_disp_flag);
+        const int nflags = El * p.R;
+        for (int i = blockIdx.x * kThreads + tid; i < nflags; i += gridDim.x * kThreads) {
+            const int r = i % p.R;
+            if (ldVolatile(p.scr.mask + r) != 0) continue;
+            if (!waitFlag(dflag + i, p.epoch, p.timeout_ns)) {
+                atomicExch(p.scr.mask + r, 1);
+                atomicOr(p.scr.status, ST_PEER_TIMEOUT);
+            }
+        }
+    }
+
+    // 7. leave the scratch counters at zero for the next call
+    if (p.phases & 1) {
+        gridBarrier(p.scr.barrier, p.scr.status, p.timeout_ns);
+        if (blockIdx.x == 0)
+            for (int e = tid; e < p.E; e += kThreads) {
+                p.scr.cnt[e] = 0;
+                p.scr.fill[e] = 0;
+                p.scr.sent[e] = 0;
+            }
+    }
+}
+
+// ------------------------------------------------------------------ combine
+
+__global__ void __launch_bounds__(kThreads) epCombineKernel(const __grid_constant__ NixlEpCombineParams p) {
+    __shared__ int offs[kMaxRanks * 8 + 1]; // expert_offsets copy (El + 1 <= 513)
+    __shared__ int cnts[kMaxRanks * 8];
+    const int El = p.E / p.R;
+    const int tid = threadIdx.x;
+    char *self = peerBase(p.peers, p.rank);
+    const int vecs = p.H / 8;
+
+    if (p.phases & 1) {
+        for (int i = tid; i <= El; i += kThreads) offs[i] = p.expert_offsets[i];
+        for (int i = tid; i < El; i += kThreads) cnts[i] = p.recv_count[i];
+        __syncthreads();
+        // Rows are enumerated expert by expert; a CTA takes every gridDim-th valid row.
+        const __nv_bfloat16 *x = static_cast<const __nv_bfloat16 *>(p.x);
+        int le = 0, seen = 0; // rows of experts < le
+        for (long long j = blockIdx.x;; j += gridDim.x) {
+            while (le < El && j >= seen + cnts[le]) seen += cnts[le++];
+            if (le >= El) break;
+            const long long row = static_cast<long long>(offs[le]) + (j - seen);
+            const uint2 info = *reinterpret_cast<const uint2 *>(p.recv_info + row * 2);
+            const int r = static_cast<int>(info.x);
+            if (r < 0 || r >= p.R || ldVolatile(p.scr.mask + r) != 0) continue;
+            char *peer = peerBase(p.peers, r);
+            if (peer == nullptr) continue;
+            const uint4 *src = reinterpret_cast<const uint4 *>(x + row * p.H);
+            uint4 *dst = reinterpret_cast<uint4 *>(peer + p.lay.off_comb_x + static_cast<long long>(info.y) * p.H * 2);
+            for (int v = tid; v < vecs; v += kThreads) stPeer16(dst + v, ldNc(src + v));
+        }
+        __syncthreads();
+        if (tid == 0) __threadfence_system();
+        gridBarrier(p.scr.barrier, p.scr.status, p.timeout_ns);
+        // Everybody's rows are out: tell each source rank.
+        for (int d = blockIdx.x; d < p.R; d += gridDim.x) {
+            if (ldVolatile(p.scr.mask + d) != 0) continue;
+            char *peer = peerBase(p.peers, d);
+            if (peer != nullptr && tid == 0) {
+                __threadfence_system();
+                stReleaseSys(reinterpret_cast<uint64_t *>(peer + p.lay.off_comb_flag) + p.rank, p.epoch);
+            }
+        }
+    }
+
+    if (p.phases & 2) {
+        const uint64_t *flag = reinterpret_cast<const uint64_t *>(self + p.lay.off_comb_flag);
+        if (tid < p.R && ldVolatile(p.scr.mask + tid) == 0 && peerBase(p.peers, tid) != nullptr) {
+            if (!waitFlag(flag + tid, p.epoch, p.timeout_ns)) {
+                atomicExch(p.scr.mask + tid, 1);
+                atomicOr(p.scr.status, ST_PEER_TIMEOUT);
+            }
+        }
+        __syncthreads();
+        // out[t] = sum_k w[t,k] * y[t,k] in fp32
+        const __nv_bfloat16 *landing = reinterpret_cast<const __nv_bfloat16 *>(self + p.lay.off_comb_x);
+        __nv_bfloat16 *out = static_cast<__nv_bfloat16 *>(p.out);
+        for (int t = blockIdx.x; t < p.T; t += gridDim.x) {
+            float w[kMaxTopk];
+#pragma unroll
+            for (int k = 0; k < kMaxTopk; ++k) {
+                w[k] = 0.f;
+                if (k < p.K) {
+                    const long long e = p.topk_idx[static_cast<long long>(t) * p.K + k];
+                    if (e >= 0 && e < p.E && ldVolatile(p.scr.mask + static_cast<int>(e) / El) == 0)
+                        w[k] = p.topk_weights[static_cast<long long>(t) * p.K + k];
+                    else w[k] = __int_as_float(0x7fc00000); // NaN marks "skip" (a real weight may be 0)
+                }
+            }
+            for (int v = tid; v < vecs; v += kThreads) {
+                float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int k = 0; k < kMaxTopk; ++k) {
+                    if (k >= p.K || w[k] != w[k]) continue;
+                    const uint4 raw = *reinterpret_cast<const uint4 *>(landing + (static_cast<long long>(t) * p.K + k) * p.H + v * 8);
+                    const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&raw);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float2 f = __bfloat1622float2(h[i]);
+                        acc[2 * i] = fmaf(w[k], f.x, acc[2 * i]);
+                        acc[2 * i + 1] = fmaf(w[k], f.y, acc[2 * i + 1]);
+                    }
+                }
+                uint4 o;
+                __nv_bfloat162 *oh = reinterpret_cast<__nv_bfloat162 *>(&o);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) oh[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+                *reinterpret_cast<uint4 *>(out + static_cast<long long>(t) * p.H + v * 8) = o;
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------ barrier across ranks
+
+__global__ void epBarrierKernel(const void *peers, int64_t off_flags, int R, int rank, uint64_t epoch, uint64_t timeout_ns, int *status,
+                                int *mask) {
+    const int r = threadIdx.x;
+    if (r >= R) return;
+    char *peer = peerBase(peers, r);
+    if (peer == nullptr || ldVolatile(mask + r) != 0) return;
+    __threadfence_system();
+    stReleaseSys(reinterpret_cast<uint64_t *>(peer + off_flags) + rank, epoch);
+    const uint64_t *mine = reinterpret_cast<const uint64_t *>(peerBase(peers, rank) + off_flags);
+    if (!waitFlag(mine + r, epoch, timeout_ns)) {
+        atomicExch(mask + r, 1);
+        atomicOr(status, ST_PEER_TIMEOUT);
+    }
+}
+
+int coopGrid(const void *kernel, int requested, size_t smem) {
+    int dev = 0, sms = 0, per_sm = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, smem);
+    const int limit = sms * (per_sm > 0 ? per_sm : 1);
+    int grid = requested > 0 ? requested : sms;
+    return grid > limit ? limit : grid;
+}
+
+} // namespace
+
+extern "C" int nixl_ep_dispatch_launch(const NixlEpDispatchParams *params, void *stream) {
+    if (!params || !params->peers || !params->topk_idx || (!params->x && (params->phases & 1))) return cudaErrorInvalidValue;
+    const NixlEpDispatchParams &p = *params;
+    if (p.R <= 0 || p.R > kMaxRanks || p.E <= 0 || p.E % p.R || p.K <= 0 || p.K > kMaxTopk || p.H <= 0 || p.H % kGroup ||
+        p.E / p.R > kMaxRanks * 8 || p.rank < 0 || p.rank >= p.R || p.T < 0)
+        return cudaErrorInvalidValue;
+    if (p.use_fp8 && (p.H % 256)) return cudaErrorInvalidValue; // whole warps per quantisation pass
+    if (p.rows_per_expert > 0 && static_cast<long long>(p.rows_per_expert) < static_cast<long long>(p.R) * p.T) return cudaErrorInvalidValue;
+    const size_t smem = size_t(2) * p.E * sizeof(int) + kMaxTopk * sizeof(int) + size_t(p.use_fp8 ? p.H : p.H * 2) + (p.H / kGroup) * sizeof(float) + 16;
+    static bool attr_done = false;
+    if (smem > 48 * 1024 && !attr_done) {
+        cudaError_t e = cudaFuncSetAttribute(epDispatchKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+        if (e != cudaSuccess) return e;
+        attr_done = true;
+    }
+    const int grid = coopGrid(reinterpret_cast<const void *>(epDispatchKernel), p.grid, smem);
+    void *args[] = {const_cast<NixlEpDispatchParams *>(params)};
+    return cudaLaunchCooperativeKernel(reinterpret_cast<const void *>(epDispatchKernel), dim3(grid), dim3(kThreads), args, smem,
+                                       static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int nixl_ep_combine_launch(const NixlEpCombineParams *params, void *stream) {
+    if (!params || !params->peers || !params->topk_idx) return cudaErrorInvalidValue;
+    const NixlEpCombineParams &p = *params;
+    if (p.R <= 0 || p.R > kMaxRanks || p.E <= 0 || p.E % p.R || p.K <= 0 || p.K > kMaxTopk || p.H <= 0 || p.H % 8 ||
+        p.E / p.R > kMaxRanks * 8 || p.rank < 0 || p.rank >= p.R)
+        return cudaErrorInvalidValue;
+    const int grid = coopGrid(reinterpret_cast<const void *>(epCombineKernel), p.grid, 0);
+    void *args[] = {const_cast<NixlEpCombineParams *>(params)};
+    return cudaLaunchCooperativeKernel(reinterpret_cast<const void *>(epCombineKernel), dim3(grid), dim3(kThreads), args, 0,
+                                       static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int nixl_ep_barrier_launch(const void *peers, int64_t off_flags, int32_t R, int32_t rank, uint64_t epoch, uint64_t timeout_ns,
+                                      int32_t *status, int32_t *mask, void *stream) {
+    if (!peers || R <= 0 || R > kMaxRanks || !status || !mask) return cudaErrorInvalidValue;
+    epBarrierKernel<<<1, kMaxRanks, 0, static_cast<cudaStream_t>(stream)>>>(peers, off_flags, R, rank, epoch, timeout_ns, status, mask);
+    return cudaGetLastError();
+}
