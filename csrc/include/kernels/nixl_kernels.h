@@ -147,6 +147,37 @@ int nixl_ep_combine_launch(const NixlEpCombineParams *params, void *stream);
 int nixl_ep_barrier_launch(const void *peers, int64_t off_flags, int32_t R, int32_t rank, uint64_t epoch, uint64_t timeout_ns,
                            int32_t *status, int32_t *mask, void *stream);
 
+/* ---------------------------------------------------------------- grouped expert GEMM (tcgen05 / TMEM)
+ *
+ * D[rows of group g, :] = dequant(A rows) x dequant(W[g])^T, bf16 output.  A and W are e4m3;
+ * scale_a has one fp32 per row per 128 channels, scale_w one per 128 x 128 block of W[g].
+ * Rows of group g are row_start[g] .. row_start[g] + row_count[g] (device arrays, so the launch
+ * can follow an EP dispatch without a host round trip).  With disp_flag set, the kernel waits
+ * per (group, source rank) for the arrival flags of that dispatch before it reads rows written
+ * by that source (see ep_kernels.cu); `counts` is the dispatch's local [ranks][experts_total]
+ * count matrix and expert_base the first global expert of this rank.
+ * status bits: 1 = an internal wait exceeded its budget, 2 = an arrival flag never came.
+ */
+typedef struct NixlGroupedGemmParams {
+    const void *a;            /* e4m3 [a_rows][K] */
+    const float *scale_a;     /* [a_rows][K/128] */
+    const void *w;            /* e4m3 [groups][N][K] */
+    const float *scale_w;     /* [groups][N/128][K/128] */
+    void *d;                  /* bf16 [a_rows][N] */
+    const int32_t *row_start; /* device [groups] */
+    const int32_t *row_count; /* device [groups] */
+    int32_t groups, N, K, a_rows;
+    int32_t grid;             /* 0: one CTA per SM */
+    int32_t ranks, experts_total, expert_base;
+    int32_t *status;          /* device word, OR-ed */
+    const uint64_t *disp_flag; /* [groups][ranks] or NULL */
+    const int32_t *counts;     /* [ranks][experts_total] or NULL */
+    uint64_t epoch;
+    uint64_t timeout_ns;
+} NixlGroupedGemmParams;
+
+int nixl_grouped_gemm_fp8_launch(const NixlGroupedGemmParams *params, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

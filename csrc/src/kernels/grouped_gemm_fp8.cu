@@ -1,0 +1,408 @@
+// Grouped expert GEMM on 5th-generation tensor cores, optionally fed by EP dispatch arrivals.
+//
+//   D[rows of expert g, :] = dequant(A[rows, K]) x dequant(W[g, N, K])^T        (bf16 out)
+//   A: e4m3, one fp32 scale per row per 128 channels (what EP dispatch delivers)
+//   W: e4m3, one fp32 scale per 128 x 128 block
+//
+// sm_100a only.  One persistent CTA per SM, 256 threads, warp-specialised:
+//   warp 0  TMA producer   cp.async.bulk.tensor (2-D, 128-byte swizzle) of a 128x128 A tile and a
+//                          128x128 W tile per 128-channel step into a 5-stage shared-memory ring
+//   warp 1  MMA issuer     4 x tcgen05.mma.kind::f8f6f4 (M128 N128 K32) per step into one of two
+//                          TMEM accumulators (128 lanes x 128 fp32 columns each)
+//   warp 2  TMEM allocator
+//   warps 4-7 promotion + epilogue: tcgen05.ld the step's partial sums, multiply by
+//                          scaleA[row, step] * scaleW[g, n-block, step], accumulate in registers
+//                          (the per-128-channel scales cannot be folded into the MMA), finally
+//                          store bf16.  The MMA of step i+1 overlaps the promotion of step i.
+// TMA loads read this GPU's own memory only and use no cluster multicast.  When `disp_flag` is
+// given, the producer waits (bounded) for the per-(expert, source rank) arrival flags raised by
+// ep_kernels.cu before it loads rows that those sources wrote: dispatch and GEMM overlap tile by
+// tile instead of being separated by a receive phase.
+//
+// The reference has no GEMM (it moves tokens only); this kernel is the "dispatch fused into a
+// tcgen05/TMEM grouped expert GEMM" variant of the EP path.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <mutex>
+
+#include "kernels/nixl_kernels.h"
+
+namespace {
+
+constexpr int BM = 128, BN = 128, BK = 128; // tile; BK is also the scale granularity
+constexpr int UMMA_K = 32;                  // fp8: 32 bytes of K per instruction
+constexpr int kStages = 5;
+constexpr int kThreads = 256;
+constexpr int kTileBytes = BM * BK;         // 16 KiB (fp8)
+constexpr int kStageBytes = 2 * kTileBytes; // A + W
+constexpr int kTmemCols = 256;              // two accumulators of 128 columns
+constexpr int kMaxGroups = 512;
+constexpr uint64_t kWaitNs = 4000000000ull; // any single wait longer than 4 s aborts the kernel
+
+enum : int { GEMM_ERR_TIMEOUT = 1, GEMM_ERR_ARRIVAL = 2 };
+
+struct Shared {
+    uint64_t full[kStages];
+    uint64_t empty[kStages];
+    uint64_t tmemFull[2];
+    uint64_t tmemEmpty[2];
+    uint32_t tmemBase;
+    int abort;
+    int tilePrefix[kMaxGroups + 1]; // tiles before group g
+    int rowStart[kMaxGroups];
+    int rowCount[kMaxGroups];
+};
+
+// ------------------------------------------------------------------ PTX wrappers
+
+__device__ __forceinline__ uint32_t smemU32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ uint64_t nowNs() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ void mbarInit(uint64_t *b, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smemU32(b)), "r"(count));
+}
+__device__ __forceinline__ void mbarExpectTx(uint64_t *b, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smemU32(b)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbarArrive(uint64_t *b) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smemU32(b)) : "memory");
+}
+__device__ __forceinline__ bool mbarTry(uint64_t *b, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok)
+                 : "r"(smemU32(b)), "r"(parity)
+                 : "memory");
+    return ok != 0;
+}
+// Bounded wait; false when the budget ran out or another role aborted.
+__device__ __forceinline__ bool mbarWait(uint64_t *b, uint32_t parity, volatile int *abort_flag) {
+    uint64_t t0 = 0;
+    unsigned spins = 0;
+    while (!mbarTry(b, parity)) {
+        if ((++spins & 127u) == 0) {
+            if (*abort_flag) return false;
+            const uint64_t now = nowNs();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > kWaitNs) {
+                *abort_flag = 1;
+                return false;
+            }
+        }
+    }
+    return true;
+}
+__device__ __forceinline__ void tmaLoad2d(void *smem_dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+                     smemU32(smem_dst)),
+                 "l"(map), "r"(smemU32(bar)), "r"(x), "r"(y)
+                 : "memory");
+}
+__device__ __forceinline__ void tcFenceBefore() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcFenceAfter() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcCommit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smemU32(bar)) : "memory");
+}
+__device__ __forceinline__ void tcMma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+                 " tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}" ::"r"(tmem_d),
+                 "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u)
+                 : "memory");
+}
+// 32 lanes x 32 consecutive fp32 columns -> 32 registers per thread (thread = lane = row).
+__device__ __forceinline__ void tmemLoad32(uint32_t addr, float (&v)[32]) {
+    uint32_t *r = reinterpret_cast<uint32_t *>(v);
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+                   "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+                   "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+                   "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(addr));
+}
+__device__ __forceinline__ void tmemLoadWait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor for a K-major tile of 128-byte rows written by TMA with the
+// 128-byte swizzle: 8-row groups are 1024 bytes apart (stride byte offset), the leading offset
+// is unused for this layout, descriptor version 1 (sm_100), layout type 2 = SWIZZLE_128B.
+__device__ __forceinline__ uint64_t smemDesc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);       // start address, bits [0,14)
+    d |= static_cast<uint64_t>(1) << 16;                           // leading byte offset (ignored), bits [16,30)
+    d |= static_cast<uint64_t>(1024 >> 4) << 32;                   // stride byte offset, bits [32,46)
+    d |= static_cast<uint64_t>(1) << 46;                           // version, bits [46,48)
+    d |= static_cast<uint64_t>(2) << 61;                           // layout type, bits [61,64)
+    return d;
+}
+
+// Instruction descriptor: D fp32, A and B e4m3, both K-major, M = 128, N = 128.
+__device__ __forceinline__ constexpr uint32_t instrDesc() {
+    return (1u << 4) | (0u << 7) | (0u << 10) | (0u << 15) | (0u << 16) | (static_cast<uint32_t>(BN >> 3) << 17) |
+        (static_cast<uint32_t>(BM >> 4) << 24);
+}
+
+__device__ __forceinline__ uint64_t ldAcquireSys(const uint64_t *p) {
+    uint64_t v;
+    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+
+struct Tile {
+    int g, mt, nt;
+};
+
+__device__ __forceinline__ bool tileAt(const Shared &sh, int groups, int n_tiles, int t, Tile &out) {
+    if (t >= sh.tilePrefix[groups]) return false;
+    int lo = 0, hi = groups; // tilePrefix[lo] <= t < tilePrefix[hi]
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (sh.tilePrefix[mid] <= t) lo = mid; else hi = mid;
+    }
+    const int local = t - sh.tilePrefix[lo];
+    out.g = lo;
+    out.mt = local / n_tiles;
+    out.nt = local - out.mt * n_tiles;
+    return true;
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+groupedGemmKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapW, const NixlGroupedGemmParams p) {
+    extern __shared__ __align__(1024) unsigned char dyn[];
+    unsigned char *tiles = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(dyn) + 1023) & ~uintptr_t(1023));
+    Shared &sh = *reinterpret_cast<Shared *>(tiles + kStages * kStageBytes);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n_tiles = p.N / BN, k_steps = p.K / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbarInit(&sh.full[s], 1);
+            mbarInit(&sh.empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbarInit(&sh.tmemFull[b], 1);
+            mbarInit(&sh.tmemEmpty[b], 4); // one arrival per promotion warp
+        }
+        sh.abort = 0;
+        // Tile table: group g owns ceil(count/BM) x n_tiles tiles.
+        int run = 0;
+        for (int g = 0; g < p.groups; ++g) {
+            const int c = p.row_count[g];
+            sh.tilePrefix[g] = run;
+            sh.rowStart[g] = p.row_start[g];
+            sh.rowCount[g] = c;
+            run += ((c + BM - 1) / BM) * n_tiles;
+        }
+        sh.tilePrefix[p.groups] = run;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 2) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smemU32(&sh.tmemBase)), "r"(kTmemCols));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+    }
+    tcFenceBefore();
+    __syncthreads();
+    tcFenceAfter();
+    const uint32_t tmem = sh.tmemBase;
+    volatile int *abort_flag = &sh.abort;
+
+    if (warp == 0 && lane == 0) {
+        // ---------------------------------------------------------------- TMA producer
+        uint32_t it = 0; // k-steps issued so far (ring position)
+        Tile t;
+        for (int ti = blockIdx.x; tileAt(sh, p.groups, n_tiles, ti, t); ti += gridDim.x) {
+            const int row0 = sh.rowStart[t.g] + t.mt * BM;
+            if (p.disp_flag) {
+                // Rows of an expert are ordered by source rank: wait for the sources whose rows
+                // intersect this tile.
+                const int lo = t.mt * BM, hi = min(lo + BM, sh.rowCount[t.g]);
+                int first = 0;
+                for (int r = 0; r < p.ranks; ++r) {
+                    const int c = p.counts[static_cast<long long>(r) * p.experts_total + p.expert_base + t.g];
+                    if (c > 0 && first < hi && first + c > lo) {
+                        const uint64_t *flag = p.disp_flag + static_cast<long long>(t.g) * p.ranks + r;
+                        uint64_t t0 = 0;
+                        unsigned spins = 0;
+                        while (ldAcquireSys(flag) < p.epoch) {
+                            if ((++spins & 63u) == 0) {
+                                const uint64_t now = nowNs();
+                                if (t0 == 0) t0 = now;
+                                else if (now - t0 > p.timeout_ns) {
+                                    atomicOr(p.status, GEMM_ERR_ARRIVAL); // compute on what is there; the host sees the bit
+                                    break;
+                                }
+                            }
+                        }
+                    }
+                    first += c;
+                }
+                asm volatile("fence.proxy.async;" ::: "memory"); // peers' generic-proxy stores before our async-proxy reads
+            }
+            for (int ks = 0; ks < k_steps; ++ks, ++it) {
+                const int s = it % kStages;
+                if (!mbarWait(&sh.empty[s], ((it / kStages) & 1) ^ 1, abort_flag)) goto producer_done;
+                mbarExpectTx(&sh.full[s], kStageBytes);
+                tmaLoad2d(tiles + s * kStageBytes, &mapA, ks * BK, row0, &sh.full[s]);
+                tmaLoad2d(tiles + s * kStageBytes + kTileBytes, &mapW, ks * BK, t.g * p.N + t.nt * BN, &sh.full[s]);
+            }
+        }
+    producer_done:;
+    } else if (warp == 1 && lane == 0) {
+        // ---------------------------------------------------------------- MMA issuer
+        uint32_t it = 0;
+        Tile t;
+        for (int ti = blockIdx.x; tileAt(sh, p.groups, n_tiles, ti, t); ti += gridDim.x) {
+            for (int ks = 0; ks < k_steps; ++ks, ++it) {
+                const int s = it % kStages, buf = it & 1;
+                if (!mbarWait(&sh.tmemEmpty[buf], ((it >> 1) & 1) ^ 1, abort_flag)) goto mma_done;
+                if (!mbarWait(&sh.full[s], (it / kStages) & 1, abort_flag)) goto mma_done;
+                tcFenceAfter();
+                const uint32_t a_addr = smemU32(tiles + s * kStageBytes);
+                const uint32_t w_addr = a_addr + kTileBytes;
+                const uint64_t da = smemDesc(a_addr), dw = smemDesc(w_addr);
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k) {
+                    // Advancing 32 bytes along K inside the swizzle atom = +2 in the 16-byte address field.
+                    tcMma(tmem + buf * BN, da + static_cast<uint64_t>(k * (UMMA_K >> 4)), dw + static_cast<uint64_t>(k * (UMMA_K >> 4)),
+                          instrDesc(), k > 0 ? 1u : 0u);
+                }
+                tcCommit(&sh.empty[s]);      // the stage may be refilled once these MMAs have read it
+                tcCommit(&sh.tmemFull[buf]); // and the accumulator is ready for promotion
+            }
+        }
+    mma_done:;
+    } else if (warp >= 4) {
+        // ---------------------------------------------------------------- promotion + epilogue
+        const int q = warp - 4;            // TMEM lane quarter this warp may touch
+        const int row_in_tile = q * 32 + lane;
+        uint32_t it = 0;
+        Tile t;
+        const float *scale_a = p.scale_a;
+        for (int ti = blockIdx.x; tileAt(sh, p.groups, n_tiles, ti, t); ti += gridDim.x) {
+            const int local_row = t.mt * BM + row_in_tile;
+            const bool valid = local_row < sh.rowCount[t.g];
+            const long long grow = static_cast<long long>(sh.rowStart[t.g]) + local_row;
+            const float *sa_row = scale_a + grow * k_steps;
+            const float *sw = p.scale_w + (static_cast<long long>(t.g) * n_tiles + t.nt) * k_steps;
+            float acc[BN];
+#pragma unroll
+            for (int i = 0; i < BN; ++i) acc[i] = 0.f;
+            bool ok = true;
+            for (int ks = 0; ks < k_steps; ++ks, ++it) {
+                const int buf = it & 1;
+                const float s = (valid ? __ldg(sa_row + ks) : 0.f) * __ldg(sw + ks);
+                if (!mbarWait(&sh.tmemFull[buf], (it >> 1) & 1, abort_flag)) {
+                    ok = false;
+                    break;
+                }
+                tcFenceAfter();
+                const uint32_t base = tmem + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
+#pragma unroll
+                for (int c = 0; c < BN / 32; ++c) {
+                    float v[32];
+                    tmemLoad32(base + c * 32, v);
+                    tmemLoadWait();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) acc[c * 32 + i] = fmaf(v[i], s, acc[c * 32 + i]);
+                }
+                tcFenceBefore();
+                __syncwarp();
+                if (lane == 0) mbarArrive(&sh.tmemEmpty[buf]);
+            }
+            if (!ok) break;
+            if (valid) {
+                __nv_bfloat16 *out = static_cast<__nv_bfloat16 *>(p.d) + grow * p.N + t.nt * BN;
+#pragma unroll
+                for (int i = 0; i < BN; i += 8) {
+                    uint4 o;
+                    __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&o);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(acc[i + 2 * j], acc[i + 2 * j + 1]);
+                    *reinterpret_cast<uint4 *>(out + i) = o;
+                }
+            }
+        }
+    }
+
+    tcFenceBefore();
+    __syncthreads();
+    if (threadIdx.x == 0 && sh.abort) atomicOr(p.status, GEMM_ERR_TIMEOUT);
+    if (warp == 2) {
+        tcFenceAfter();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols));
+    }
+}
+
+// ------------------------------------------------------------------ host side
+
+using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                              const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                              CUtensorMapFloatOOBfill);
+
+EncodeFn encoder() {
+    static EncodeFn fn = [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<EncodeFn>(p);
+    }();
+    return fn;
+}
+
+// 2-D map over a row-major [rows, k] byte matrix, 128 x 128 boxes, 128-byte swizzle.
+bool makeMap(CUtensorMap *map, const void *base, uint64_t rows, uint64_t k) {
+    EncodeFn fn = encoder();
+    if (!fn) return false;
+    const cuuint64_t dims[2] = {k, rows};
+    const cuuint64_t strides[1] = {k};
+    const cuuint32_t box[2] = {BK, BM};
+    const cuuint32_t elem[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+} // namespace
+
+extern "C" int nixl_grouped_gemm_fp8_launch(const NixlGroupedGemmParams *params, void *stream) {
+    if (!params || !params->a || !params->w || !params->d || !params->scale_a || !params->scale_w || !params->row_start ||
+        !params->row_count || !params->status)
+        return cudaErrorInvalidValue;
+    const NixlGroupedGemmParams &p = *params;
+    if (p.groups <= 0 || p.groups > kMaxGroups || p.N <= 0 || p.N % BN || p.K <= 0 || p.K % BK || p.a_rows <= 0)
+        return cudaErrorInvalidValue;
+    if ((reinterpret_cast<uintptr_t>(p.a) | reinterpret_cast<uintptr_t>(p.w) | reinterpret_cast<uintptr_t>(p.d)) & 15) return cudaErrorInvalidValue;
+    if (p.disp_flag && (!p.counts || p.ranks <= 0)) return cudaErrorInvalidValue;
+    CUtensorMap mapA, mapW;
+    if (!makeMap(&mapA, p.a, static_cast<uint64_t>(p.a_rows), static_cast<uint64_t>(p.K)) ||
+        !makeMap(&mapW, p.w, static_cast<uint64_t>(p.groups) * p.N, static_cast<uint64_t>(p.K))) {
+        std::fprintf(stderr, "nixl_grouped_gemm_fp8_launch: cuTensorMapEncodeTiled failed\n");
+        return cudaErrorInvalidValue;
+    }
+    const size_t smem = size_t(kStages) * kStageBytes + sizeof(Shared) + 1024;
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [&] { attr_err = cudaFuncSetAttribute(groupedGemmKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)); });
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    // The attribute is per device: set it again when this device differs from the first caller's.
+    static int attr_dev = -1;
+    if (attr_dev != dev) {
+        attr_err = cudaFuncSetAttribute(groupedGemmKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        attr_dev = dev;
+    }
+    if (attr_err != cudaSuccess) return attr_err;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    int grid = p.grid > 0 ? p.grid : sms;
+    // Upper bound of tiles (row counts live on the device): never launch more CTAs than that.
+    const long long max_tiles = (static_cast<long long>(p.a_rows + BM - 1) / BM + p.groups) * (p.N / BN);
+    if (grid > max_tiles) grid = static_cast<int>(max_tiles);
+    groupedGemmKernel<<<grid, kThreads, smem, static_cast<cudaStream_t>(stream)>>>(mapA, mapW, p);
+    return cudaGetLastError();
+}

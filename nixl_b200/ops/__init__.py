@@ -1,4 +1,5 @@
 """Fused GPU operations of the library (hand-written sm_100a kernels behind a C ABI)."""
+from .grouped_gemm import grouped_gemm_fp8, quantize_weights, reference_grouped_gemm  # noqa: F401
 from .kv_transfer import KVLayout, KVTransfer, reference_kv_transfer  # noqa: F401
 
 
