@@ -110,7 +110,7 @@ typedef struct NixlEpDispatchParams {
     int32_t round_scale;      /* 1: scales rounded up to a power of two */
     int32_t rows_per_expert;  /* >0: expert le starts at row le*rows_per_expert; 0: compact (prefix) layout */
     int32_t cap;              /* rows available at every receiver */
-    int32_t phases;           /* bit0 send, bit1 receive (wait for arrivals) */
+    int32_t phases;           /* bit0 send, bit1 receive (wait for arrivals), bit2 publish recv_count/offsets without waiting */
     int32_t grid;             /* CTAs (cooperative launch); 0 = one per SM */
     const void *peers;        /* remote memory view */
     NixlEpLayout lay;

@@ -226,7 +226,7 @@ __global__ void __launch_bounds__(kThreads) epDispatchKernel(const __grid_consta
     __syncthreads();
 
     // Receiver-side bookkeeping is known as soon as the counts are: CTA 0 publishes it.
-    if (blockIdx.x == 0 && (p.phases & 2)) {
+    if (blockIdx.x == 0 && (p.phases & 6)) {
         for (int le = tid; le < El; le += kThreads) {
             const int e = p.rank * El + le;
             int total = 0;

@@ -213,6 +213,8 @@ class Buffer:
 
         ``metadata`` is the list of every rank's ``local_metadata()``; when omitted it is gathered
         over the ``torch.distributed`` group given at construction."""
+        if metadata is None and self.num_ranks == 1:
+            metadata = [self.local_metadata()]
         if metadata is None:
             import torch.distributed as dist
 
