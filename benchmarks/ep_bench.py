@@ -40,6 +40,7 @@ def timed(fn, iters, warmup, flush, world, dev, pre=None):
             dist.barrier()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda._sleep(400_000)  # keeps the GPU busy while the host queues fn(): the events then see device time only
         e0.record()
         fn()
         e1.record()

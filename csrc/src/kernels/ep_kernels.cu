@@ -100,6 +100,21 @@ __device__ __forceinline__ void gridBarrier(unsigned *bar, int *status, uint64_t
     __syncthreads();
 }
 
+// Barrier among the `nthreads` threads of one token group (named barrier `id`, 1..15).
+__device__ __forceinline__ void groupBarrier(int id, int nthreads) {
+    if (nthreads == 32) __syncwarp();
+    else asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+// Threads cooperating on one token / row: as many as keeps the whole grid busy, a power of two
+// between one warp and one CTA.
+__device__ __forceinline__ int threadsPerItem(long long items) {
+    const long long avail = static_cast<long long>(gridDim.x) * kThreads;
+    int t = kThreads;
+    while (t > 32 && static_cast<long long>(t) * items > avail) t >>= 1;
+    return t;
+}
+
 // ------------------------------------------------------------------ dispatch
 
 // Quantises one 128-channel group held by 16 lanes (8 bf16 each): returns 8 e4m3 bytes and,
@@ -140,12 +155,11 @@ __global__ void __launch_bounds__(kThreads) epDispatchKernel(const __grid_consta
     const int El = p.E / p.R;
     const int groups = p.H / kGroup;
     const int row_bytes = p.use_fp8 ? p.H : p.H * 2;
-    // shared: before[E] | ebase[E] | slots[kMaxTopk] | row bytes | scales
+    // shared: before[E] | ebase[E] | per token group: slots[kMaxTopk] | row bytes | scales
     int *before = reinterpret_cast<int *>(smem);
     int *ebase = before + p.E;
-    int *slots = ebase + p.E;
-    unsigned char *rowbuf = reinterpret_cast<unsigned char *>(slots + kMaxTopk);
-    float *scalebuf = reinterpret_cast<float *>(rowbuf + row_bytes);
+    unsigned char *group_area = reinterpret_cast<unsigned char *>(ebase + p.E);
+    const int group_bytes = (kMaxTopk * 4 + row_bytes + groups * 4 + 15) & ~15;
 
     char *self = peerBase(p.peers, p.rank);
     const int tid = threadIdx.x;
@@ -243,30 +257,47 @@ __global__ void __launch_bounds__(kThreads) epDispatchKernel(const __grid_consta
     }
 
     if (p.phases & 1) {
-        // 5. data: one token per CTA iteration
+        // 5. data: a group of `nt` threads (one warp ... the whole CTA) owns a token: read once,
+        //    quantise once into the group's shared buffer, store to up to K receivers.
         const __nv_bfloat16 *x = static_cast<const __nv_bfloat16 *>(p.x);
         const int vecs = p.H / 8; // 16-byte bf16 vectors per row
-        for (int t = blockIdx.x; t < p.T; t += gridDim.x) {
+        const int nt = threadsPerItem(p.T);
+        const int groups_per_cta = kThreads / nt;
+        const int grp = tid / nt, gtid = tid - grp * nt;
+        int *slots = reinterpret_cast<int *>(group_area + static_cast<size_t>(grp) * group_bytes);
+        unsigned char *rowbuf = reinterpret_cast<unsigned char *>(slots + kMaxTopk);
+        float *scalebuf = reinterpret_cast<float *>(rowbuf + row_bytes);
+        const int bar_id = 1 + grp;
+        for (int t = blockIdx.x * groups_per_cta + grp; t < p.T; t += gridDim.x * groups_per_cta) {
             const uint4 *src = reinterpret_cast<const uint4 *>(x + static_cast<long long>(t) * p.H);
-            if (p.use_fp8) {
-                // 16 lanes own one 128-channel group
-                for (int v = tid; v < vecs; v += kThreads) {
-                    float scale;
-                    const uint2 q = quantGroup(ldNc(src + v), p.round_scale != 0, scale);
-                    reinterpret_cast<uint2 *>(rowbuf)[v] = q;
-                    if ((v & 15) == 0) scalebuf[v >> 4] = scale;
+            // Four loads in flight per thread.  `vecs` is a multiple of 32, so the guards are warp-uniform.
+            for (int v0 = gtid; v0 < vecs; v0 += 4 * nt) {
+                uint4 raw[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    if (v0 + j * nt < vecs) raw[j] = ldNc(src + v0 + j * nt);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int v = v0 + j * nt;
+                    if (v >= vecs) continue;
+                    if (p.use_fp8) {
+                        float scale;
+                        const uint2 q = quantGroup(raw[j], p.round_scale != 0, scale); // 16 lanes own one 128-channel group
+                        reinterpret_cast<uint2 *>(rowbuf)[v] = q;
+                        if ((v & 15) == 0) scalebuf[v >> 4] = scale;
+                    } else {
+                        reinterpret_cast<uint4 *>(rowbuf)[v] = raw[j];
+                    }
                 }
-            } else {
-                for (int v = tid; v < vecs; v += kThreads) reinterpret_cast<uint4 *>(rowbuf)[v] = ldNc(src + v);
             }
             // reserve one slot per destination
-            if (tid < p.K) {
-                const long long e = p.topk_idx[static_cast<long long>(t) * p.K + tid];
+            if (gtid < p.K) {
+                const long long e = p.topk_idx[static_cast<long long>(t) * p.K + gtid];
                 int slot = -1;
                 if (e >= 0 && e < p.E && ldVolatile(p.scr.mask + static_cast<int>(e) / El) == 0) slot = atomicAdd(p.scr.fill + e, 1);
-                slots[tid] = slot;
+                slots[gtid] = slot;
             }
-            __syncthreads();
+            groupBarrier(bar_id, nt);
             for (int k = 0; k < p.K; ++k) {
                 const int slot = slots[k];
                 if (slot < 0) continue;
@@ -276,29 +307,29 @@ __global__ void __launch_bounds__(kThreads) epDispatchKernel(const __grid_consta
                 if (row >= p.cap) continue; // flagged as ST_CAPACITY above
                 char *peer = peerBase(p.peers, d);
                 uint4 *dx = reinterpret_cast<uint4 *>(peer + p.lay.off_recv_x + row * row_bytes);
-                for (int v = tid; v < row_bytes / 16; v += kThreads) stPeer16(dx + v, reinterpret_cast<const uint4 *>(rowbuf)[v]);
+                for (int v = gtid; v < row_bytes / 16; v += nt) stPeer16(dx + v, reinterpret_cast<const uint4 *>(rowbuf)[v]);
                 if (p.use_fp8) {
-                    float *ds = reinterpret_cast<float *>(peer + p.lay.off_recv_scales) + row * groups;
-                    for (int g = tid; g < groups; g += kThreads) ds[g] = scalebuf[g];
+                    float4 *ds = reinterpret_cast<float4 *>(reinterpret_cast<float *>(peer + p.lay.off_recv_scales) + row * groups);
+                    for (int g = gtid; g < groups / 4; g += nt) ds[g] = reinterpret_cast<const float4 *>(scalebuf)[g];
                 }
-                if (tid == 0) {
+                if (gtid == 0) {
                     uint2 info = make_uint2(static_cast<unsigned>(p.rank), static_cast<unsigned>(t * p.K + k));
                     *reinterpret_cast<uint2 *>(peer + p.lay.off_recv_info + row * 8) = info;
                 }
             }
-            __syncthreads(); // all stores of this token issued (and rowbuf free for the next one)
-            if (tid < p.K && slots[tid] >= 0) {
+            groupBarrier(bar_id, nt); // all stores of this token issued (and the buffer is free for the next one)
+            if (gtid < p.K && slots[gtid] >= 0) {
                 // Count the row as sent; whoever completes an expert's rows raises its flag.
-                const int e = static_cast<int>(p.topk_idx[static_cast<long long>(t) * p.K + tid]);
+                const int e = static_cast<int>(p.topk_idx[static_cast<long long>(t) * p.K + gtid]);
                 __threadfence_system();
                 const int done = atomicAdd(p.scr.sent + e, 1) + 1;
                 if (done == ldVolatile(p.scr.cnt + e)) {
-                    __threadfence_system(); // acquire side of the count: other CTAs' rows of this expert are out
+                    __threadfence_system(); // acquire side of the count: other groups' rows of this expert are out
                     char *peer = peerBase(p.peers, e / El);
                     stReleaseSys(reinterpret_cast<uint64_t *>(peer + p.lay.off_disp_flag) + static_cast<long long>(e % El) * p.R + p.rank, p.epoch);
                 }
             }
-            __syncthreads();
+            groupBarrier(bar_id, nt);
         }
     }
 
@@ -342,10 +373,12 @@ __global__ void __launch_bounds__(kThreads) epCombineKernel(const __grid_constan
         for (int i = tid; i <= El; i += kThreads) offs[i] = p.expert_offsets[i];
         for (int i = tid; i < El; i += kThreads) cnts[i] = p.recv_count[i];
         __syncthreads();
-        // Rows are enumerated expert by expert; a CTA takes every gridDim-th valid row.
+        // Rows are enumerated expert by expert; every warp of the grid takes every n-th valid row.
         const __nv_bfloat16 *x = static_cast<const __nv_bfloat16 *>(p.x);
+        const int lane = tid & 31;
+        const long long warps = static_cast<long long>(gridDim.x) * (kThreads / 32);
         int le = 0, seen = 0; // rows of experts < le
-        for (long long j = blockIdx.x;; j += gridDim.x) {
+        for (long long j = static_cast<long long>(blockIdx.x) * (kThreads / 32) + (tid >> 5);; j += warps) {
             while (le < El && j >= seen + cnts[le]) seen += cnts[le++];
             if (le >= El) break;
             const long long row = static_cast<long long>(offs[le]) + (j - seen);
@@ -356,7 +389,15 @@ __global__ void __launch_bounds__(kThreads) epCombineKernel(const __grid_constan
             if (peer == nullptr) continue;
             const uint4 *src = reinterpret_cast<const uint4 *>(x + row * p.H);
             uint4 *dst = reinterpret_cast<uint4 *>(peer + p.lay.off_comb_x + static_cast<long long>(info.y) * p.H * 2);
-            for (int v = tid; v < vecs; v += kThreads) stPeer16(dst + v, ldNc(src + v));
+            for (int v0 = lane; v0 < vecs; v0 += 8 * 32) { // eight loads in flight per lane
+                uint4 val[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    if (v0 + i * 32 < vecs) val[i] = ldNc(src + v0 + i * 32);
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    if (v0 + i * 32 < vecs) stPeer16(dst + v0 + i * 32, val[i]);
+            }
         }
         __syncthreads();
         if (tid == 0) __threadfence_system();
@@ -384,7 +425,10 @@ __global__ void __launch_bounds__(kThreads) epCombineKernel(const __grid_constan
         // out[t] = sum_k w[t,k] * y[t,k] in fp32
         const __nv_bfloat16 *landing = reinterpret_cast<const __nv_bfloat16 *>(self + p.lay.off_comb_x);
         __nv_bfloat16 *out = static_cast<__nv_bfloat16 *>(p.out);
-        for (int t = blockIdx.x; t < p.T; t += gridDim.x) {
+        const int nt = threadsPerItem(p.T);
+        const int groups_per_cta = kThreads / nt;
+        const int grp = tid / nt, gtid = tid - grp * nt;
+        for (int t = blockIdx.x * groups_per_cta + grp; t < p.T; t += gridDim.x * groups_per_cta) {
             float w[kMaxTopk];
 #pragma unroll
             for (int k = 0; k < kMaxTopk; ++k) {
@@ -396,13 +440,17 @@ __global__ void __launch_bounds__(kThreads) epCombineKernel(const __grid_constan
                     else w[k] = __int_as_float(0x7fc00000); // NaN marks "skip" (a real weight may be 0)
                 }
             }
-            for (int v = tid; v < vecs; v += kThreads) {
+            for (int v = gtid; v < vecs; v += nt) {
                 float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                uint4 raw[kMaxTopk];
+#pragma unroll
+                for (int k = 0; k < kMaxTopk; ++k)
+                    if (k < p.K && w[k] == w[k])
+                        raw[k] = *reinterpret_cast<const uint4 *>(landing + (static_cast<long long>(t) * p.K + k) * p.H + v * 8);
 #pragma unroll
                 for (int k = 0; k < kMaxTopk; ++k) {
                     if (k >= p.K || w[k] != w[k]) continue;
-                    const uint4 raw = *reinterpret_cast<const uint4 *>(landing + (static_cast<long long>(t) * p.K + k) * p.H + v * 8);
-                    const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&raw);
+                    const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&raw[k]);
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
                         const float2 f = __bfloat1622float2(h[i]);
@@ -455,14 +503,20 @@ extern "C" int nixl_ep_dispatch_launch(const NixlEpDispatchParams *params, void 
     if (p.R <= 0 || p.R > kMaxRanks || p.E <= 0 || p.E % p.R || p.K <= 0 || p.K > kMaxTopk || p.H <= 0 || p.H % kGroup ||
         p.E / p.R > kMaxRanks * 8 || p.rank < 0 || p.rank >= p.R || p.T < 0)
         return cudaErrorInvalidValue;
-    if (p.use_fp8 && (p.H % 256)) return cudaErrorInvalidValue; // whole warps per quantisation pass
+    if (p.H % 512) return cudaErrorInvalidValue; // whole warps per pass; scales move as float4
     if (p.rows_per_expert > 0 && static_cast<long long>(p.rows_per_expert) < static_cast<long long>(p.R) * p.T) return cudaErrorInvalidValue;
-    const size_t smem = size_t(2) * p.E * sizeof(int) + kMaxTopk * sizeof(int) + size_t(p.use_fp8 ? p.H : p.H * 2) + (p.H / kGroup) * sizeof(float) + 16;
-    static bool attr_done = false;
-    if (smem > 48 * 1024 && !attr_done) {
-        cudaError_t e = cudaFuncSetAttribute(epDispatchKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
-        if (e != cudaSuccess) return e;
-        attr_done = true;
+    const size_t group_bytes = (kMaxTopk * sizeof(int) + size_t(p.use_fp8 ? p.H : p.H * 2) + (p.H / kGroup) * sizeof(float) + 15) & ~size_t(15);
+    const size_t smem = size_t(2) * p.E * sizeof(int) + (kThreads / 32) * group_bytes + 16;
+    {
+        // The shared-memory limit is a per-device function attribute.
+        static bool attr_done[64] = {};
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+            cudaError_t e = cudaFuncSetAttribute(epDispatchKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+            if (e != cudaSuccess) return e;
+            attr_done[dev] = true;
+        }
     }
     const int grid = coopGrid(reinterpret_cast<const void *>(epDispatchKernel), p.grid, smem);
     void *args[] = {const_cast<NixlEpDispatchParams *>(params)};

@@ -127,7 +127,18 @@ __device__ __forceinline__ void tmemLoad32(uint32_t addr, float (&v)[32]) {
                    "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
                  : "r"(addr));
 }
-__device__ __forceinline__ void tmemLoadWait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// Waits for outstanding TMEM loads.  The registers are listed as read-write operands so that no
+// use of them can be scheduled above the wait (the load instruction returns before its data).
+__device__ __forceinline__ void tmemLoadWait(float (&v)[32]) {
+    uint32_t *r = reinterpret_cast<uint32_t *>(v);
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]), "+r"(r[9]),
+                   "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]),
+                   "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]),
+                   "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+                 :
+                 : "memory");
+}
 
 // Shared-memory matrix descriptor for a K-major tile of 128-byte rows written by TMA with the
 // 128-byte swizzle: 8-row groups are 1024 bytes apart (stride byte offset), the leading offset
@@ -303,17 +314,28 @@ groupedGemmKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
                 }
                 tcFenceAfter();
                 const uint32_t base = tmem + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
+                // Two register buffers: the load of chunk c+1 is in flight while chunk c is scaled and added.
+                float v0[32], v1[32];
+                tmemLoad32(base, v0);
+                tmemLoadWait(v0);
+                tmemLoad32(base + 32, v1);
 #pragma unroll
-                for (int c = 0; c < BN / 32; ++c) {
-                    float v[32];
-                    tmemLoad32(base + c * 32, v);
-                    tmemLoadWait();
+                for (int i = 0; i < 32; ++i) acc[i] = fmaf(v0[i], s, acc[i]);
+                tmemLoadWait(v1);
+                tmemLoad32(base + 64, v0);
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) acc[c * 32 + i] = fmaf(v[i], s, acc[c * 32 + i]);
-                }
+                for (int i = 0; i < 32; ++i) acc[32 + i] = fmaf(v1[i], s, acc[32 + i]);
+                tmemLoadWait(v0);
+                tmemLoad32(base + 96, v1);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) acc[64 + i] = fmaf(v0[i], s, acc[64 + i]);
+                tmemLoadWait(v1);
+                // All of this accumulator has been read: hand it back before the last FMAs.
                 tcFenceBefore();
                 __syncwarp();
                 if (lane == 0) mbarArrive(&sh.tmemEmpty[buf]);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) acc[96 + i] = fmaf(v1[i], s, acc[96 + i]);
             }
             if (!ok) break;
             if (valid) {
@@ -386,18 +408,17 @@ extern "C" int nixl_grouped_gemm_fp8_launch(const NixlGroupedGemmParams *params,
         return cudaErrorInvalidValue;
     }
     const size_t smem = size_t(kStages) * kStageBytes + sizeof(Shared) + 1024;
-    static std::once_flag once;
-    static cudaError_t attr_err = cudaSuccess;
-    std::call_once(once, [&] { attr_err = cudaFuncSetAttribute(groupedGemmKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)); });
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
-    // The attribute is per device: set it again when this device differs from the first caller's.
-    static int attr_dev = -1;
-    if (attr_dev != dev) {
-        attr_err = cudaFuncSetAttribute(groupedGemmKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-        attr_dev = dev;
+    {
+        // The shared-memory limit is a per-device function attribute.
+        static bool attr_done[64] = {};
+        if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+            cudaError_t e = cudaFuncSetAttribute(groupedGemmKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+            if (e != cudaSuccess) return e;
+            attr_done[dev] = true;
+        }
     }
-    if (attr_err != cudaSuccess) return attr_err;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     int grid = p.grid > 0 ? p.grid : sms;
     // Upper bound of tiles (row counts live on the device): never launch more CTAs than that.
