@@ -178,6 +178,39 @@ typedef struct NixlGroupedGemmParams {
 
 int nixl_grouped_gemm_fp8_launch(const NixlGroupedGemmParams *params, void *stream);
 
+/* ---------------------------------------------------------------- device API exercisers
+ *
+ * nixl_devapi_put_test: one calling group (level 0 thread, 1 warp, 2 block) performs `iters`
+ * puts (or gets) of `size` bytes between entry 0 of two views, each followed by an atomic add
+ * on entry 0 of `sig_view`; status_out[4] receives {last status, status of an out-of-range put,
+ * get-pointer of entry 0 non-null, get-pointer of a bad index null}.
+ *
+ * nixl_devapi_put_signal_launch: the persistent kernel of the device-initiated benchmark.  One
+ * producer CTA per peer puts a tile and signals the peer's counter every iteration from inside
+ * its compute loop; one consumer CTA waits on this rank's counters and acknowledges, which is
+ * the producers' flow control (at most `window` tiles in flight per peer).
+ * Memory: local_signals entry 0 = this rank's word array: [0, ranks) arrival counters indexed by
+ * source rank, then at ack_offset [0, ranks) acknowledgement counters; remote_signals entry r =
+ * the same array of rank r; remote_tiles entry r = rank r's landing area of
+ * ranks * window * tile_bytes.
+ */
+typedef struct NixlDevPutParams {
+    void *local_tiles;          /* local view, entry 0: peers * tile_bytes source tiles */
+    void *remote_tiles;         /* remote view, one entry per rank */
+    void *local_signals;        /* local view, entry 0 */
+    void *remote_signals;       /* remote view, one entry per rank */
+    const int32_t *peer_ids;    /* device [peers] ranks this rank talks to */
+    int32_t peers, rank, iters, window, compute_passes;
+    uint64_t tile_bytes;
+    uint64_t ack_offset;        /* bytes */
+    uint64_t timeout_ns;
+    int32_t *status;            /* bit0: a wait timed out */
+} NixlDevPutParams;
+
+int nixl_devapi_put_test(int level, const void *src_view, const void *dst_view, const void *sig_view, uint64_t size, int iters,
+                         int use_get, int *status_out, void *stream);
+int nixl_devapi_put_signal_launch(const NixlDevPutParams *params, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,121 @@
+// Kernels that exercise the GPU device API (include/device/nixl_device.cuh) from outside the
+// library's own transfer paths: a correctness kernel used by the tests (put / get / atomic add
+// / get-pointer at THREAD, WARP and BLOCK level) and the persistent put-with-signal kernel of
+// the device-initiated benchmark.
+//
+// Parity: the reference's test/gtest/device_api/single_write_test.cu (putKernel :34,
+// getPtrKernel :84) and benchmark/nixlbench/src/kernels/nixlbench_device_launch.cu:79
+// (nixlbenchPutKernel: puts per region, then a completion counter add).
+#include <cuda_runtime.h>
+
+#include "device/nixl_device.cuh"
+#include "kernels/nixl_kernels.h"
+
+namespace {
+
+template<nixl_gpu_level_t level>
+__global__ void putTestKernel(nixlMemViewH src, nixlMemViewH dst, nixlMemViewH sig, size_t size, int iters, int use_get, int *status_out) {
+    // One calling group per launch (a thread, a warp or a block); every iteration moves `size`
+    // bytes from entry 0 of the local view to entry 0 of the remote view at offset iter * size
+    // and then bumps the remote counter.
+    nixl_status_t st = NIXL_SUCCESS;
+    for (int i = 0; i < iters && st == NIXL_SUCCESS; ++i) {
+        nixlMemViewElem s{src, 0, static_cast<size_t>(i) * size};
+        nixlMemViewElem d{dst, 0, static_cast<size_t>(i) * size};
+        nixlGpuXferStatusH h;
+        if (use_get) st = nixlGet<level>(s, d, size, 0, 0, &h); // local <- remote
+        else st = nixlPut<level>(s, d, size, 0, (i & 1) ? nixl_gpu_flags::defer : 0, &h);
+        if (st == NIXL_SUCCESS) st = nixlGpuGetXferStatus<level>(h);
+        if (st == NIXL_SUCCESS) st = nixlAtomicAdd<level>(1, nixlMemViewElem{sig, 0, 0}, 0, 0, nullptr);
+    }
+    // Out-of-range requests must be refused, not executed.
+    nixlMemViewElem bad{dst, 99, 0};
+    const nixl_status_t refused = nixlPut<level>(nixlMemViewElem{src, 0, 0}, bad, 16);
+    if (threadIdx.x == 0 && blockIdx.x == 0) {
+        status_out[0] = static_cast<int>(st);
+        status_out[1] = static_cast<int>(refused);
+        status_out[2] = nixlGetPtr(dst, 0) != nullptr;
+        status_out[3] = nixlGetPtr(dst, 99) == nullptr;
+    }
+}
+
+// Persistent producer/consumer kernel of the device-initiated benchmark.
+//   CTA b < peers: producer for peer b: per iteration a stand-in compute pass over its tile,
+//                  then nixlPut<BLOCK> of the tile into the peer's slot for this rank and an
+//                  atomic add on the peer's counter for this rank;
+//   CTA peers:     consumer: waits (bounded) until every peer's counter reaches the iteration.
+// Flow control: a producer may run at most `window` iterations ahead of what its peer consumed
+// (the peer publishes its consumed count back through a second counter).
+__global__ void __launch_bounds__(512) putSignalKernel(NixlDevPutParams p) {
+    __shared__ int failed;
+    if (threadIdx.x == 0) failed = 0;
+    __syncthreads();
+    const int b = blockIdx.x;
+    if (b < p.peers) {
+        const int peer = p.peer_ids[b];
+        float4 *tile = reinterpret_cast<float4 *>(static_cast<char *>(nixlGetPtr(p.local_tiles, 0)) + static_cast<size_t>(b) * p.tile_bytes);
+        const size_t n4 = p.tile_bytes / sizeof(float4);
+        for (int it = 1; it <= p.iters; ++it) {
+            // stand-in for the compute that produces the tile
+            for (int r = 0; r < p.compute_passes; ++r)
+                for (size_t i = threadIdx.x; i < n4; i += blockDim.x) {
+                    float4 v = tile[i];
+                    v.x = fmaf(v.x, 1.0001f, 0.5f);
+                    v.y = fmaf(v.y, 0.9999f, -0.5f);
+                    tile[i] = v;
+                }
+            __syncthreads();
+            // do not overrun the consumer: it acknowledges in ack[peer slot for me]
+            if (it > p.window) {
+                if (threadIdx.x == 0) {
+                    const uint64_t *ack = reinterpret_cast<const uint64_t *>(static_cast<char *>(nixlGetPtr(p.local_signals, 0)) + p.ack_offset) + peer;
+                    if (nixlSignalWait(ack, static_cast<uint64_t>(it - p.window), p.timeout_ns) != NIXL_SUCCESS) failed = 1;
+                }
+                __syncthreads();
+                if (failed) break;
+            }
+            const size_t slot = static_cast<size_t>((it - 1) % p.window);
+            nixlMemViewElem src{p.local_tiles, 0, static_cast<size_t>(b) * p.tile_bytes};
+            nixlMemViewElem dst{p.remote_tiles, static_cast<size_t>(peer), (static_cast<size_t>(p.rank) * p.window + slot) * p.tile_bytes};
+            nixlPut<nixl_gpu_level_t::BLOCK>(src, dst, p.tile_bytes);
+            nixlAtomicAdd<nixl_gpu_level_t::BLOCK>(1, nixlMemViewElem{p.remote_signals, static_cast<size_t>(peer), static_cast<size_t>(p.rank) * 8});
+        }
+    } else if (b == p.peers) {
+        // consumer: thread j watches peer j's arrivals and acknowledges them
+        if (static_cast<int>(threadIdx.x) < p.peers) {
+            const int peer = p.peer_ids[threadIdx.x];
+            const uint64_t *arrived = reinterpret_cast<const uint64_t *>(nixlGetPtr(p.local_signals, 0)) + peer;
+            for (int it = 1; it <= p.iters; ++it) {
+                if (nixlSignalWait(arrived, static_cast<uint64_t>(it), p.timeout_ns) != NIXL_SUCCESS) {
+                    failed = 1;
+                    break;
+                }
+                nixlAtomicAdd<nixl_gpu_level_t::THREAD>(
+                    1, nixlMemViewElem{p.remote_signals, static_cast<size_t>(peer), p.ack_offset + static_cast<size_t>(p.rank) * 8});
+            }
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && failed) atomicOr(p.status, 1);
+}
+
+} // namespace
+
+extern "C" int nixl_devapi_put_test(int level, const void *src_view, const void *dst_view, const void *sig_view, uint64_t size, int iters,
+                                    int use_get, int *status_out, void *stream) {
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    nixlMemViewH a = const_cast<void *>(src_view), b = const_cast<void *>(dst_view), c = const_cast<void *>(sig_view);
+    switch (level) {
+    case 0: putTestKernel<nixl_gpu_level_t::THREAD><<<1, 1, 0, s>>>(a, b, c, size, iters, use_get, status_out); break;
+    case 1: putTestKernel<nixl_gpu_level_t::WARP><<<1, 32, 0, s>>>(a, b, c, size, iters, use_get, status_out); break;
+    case 2: putTestKernel<nixl_gpu_level_t::BLOCK><<<1, 256, 0, s>>>(a, b, c, size, iters, use_get, status_out); break;
+    default: return cudaErrorInvalidValue;
+    }
+    return cudaGetLastError();
+}
+
+extern "C" int nixl_devapi_put_signal_launch(const NixlDevPutParams *params, void *stream) {
+    if (!params || params->peers <= 0 || params->peers > 64 || params->window <= 0 || (params->tile_bytes & 15)) return cudaErrorInvalidValue;
+    putSignalKernel<<<params->peers + 1, 512, 0, static_cast<cudaStream_t>(stream)>>>(*params);
+    return cudaGetLastError();
+}
