@@ -33,6 +33,7 @@ def main():
     ap.add_argument("--window", type=int, default=4)
     ap.add_argument("--compute-passes", type=int, default=1)
     ap.add_argument("--host-iters", type=int, default=128)
+    ap.add_argument("--ctas-per-peer", type=int, default=8)
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -76,6 +77,7 @@ def main():
         p.local_tiles, p.remote_tiles, p.local_signals, p.remote_signals = local_tiles, remote_tiles, local_signals, remote_signals
         p.peer_ids = peer_ids.data_ptr()
         p.peers, p.rank, p.iters, p.window, p.compute_passes = P, rank, iters, args.window, passes
+        p.ctas_per_peer = args.ctas_per_peer
         p.tile_bytes, p.ack_offset, p.timeout_ns = args.tile, world * 8, 20_000_000_000
         p.status = status.data_ptr()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -91,7 +93,7 @@ def main():
     run(64, args.compute_passes)  # warm-up
     t_full = run(args.iters, args.compute_passes)
     t_compute_only_proxy = run(args.iters, 0)  # communication only: the cost of the puts without the compute pass
-    ok = int(status.item()) == 0 and int(signals[peers[0]]) == args.iters
+    ok = int(status.item()) == 0 and int(signals[peers[0]]) == args.iters * args.ctas_per_peer
 
     # Host-posted baseline: the same tile to every peer, posted and completed from the host.
     handles = []
@@ -118,7 +120,7 @@ def main():
     if rank == 0:
         bytes_per_iter = P * args.tile
         print(json.dumps({
-            "bench": "device_put_signal", "n_gpus": world, "peers_per_gpu": P, "tile_bytes": args.tile, "iters": args.iters, "window": args.window,
+            "bench": "device_put_signal", "n_gpus": world, "peers_per_gpu": P, "tile_bytes": args.tile, "iters": args.iters, "window": args.window, "ctas_per_peer": args.ctas_per_peer,
             "us_per_iter": round(t_full / args.iters, 2), "us_per_put": round(t_full / args.iters / P, 2),
             "us_per_iter_comm_only": round(t_compute_only_proxy / args.iters, 2),
             "GBps_per_gpu": round(bytes_per_iter * args.iters / t_full / 1e3, 1),

@@ -1,0 +1,208 @@
+#!/usr/bin/env python
+"""Disaggregated KV-cache transfer benchmark (Llama-3-8B shape).
+
+32 layers x (K, V), 8 KV heads, head_dim 128, bf16, paged blocks of 16 tokens; batch of 8 requests
+x 4096-token prompts (256 blocks each) with block tables shuffled by a seeded permutation.  The
+first half of the GPUs are prefill ranks holding 2 KV heads each (TP=4 at 8 GPUs), the second
+half decode ranks holding 4 KV heads (TP=2): prefill rank p writes its heads into head slots
+(p % 2) * 2 of decode rank N/2 + p // 2.  With one GPU both caches live on it.
+
+Measured per prefill rank (device clock, max over ranks): the fused kernel (block-table
+gather/scatter + TP reshard, bf16 and bf16->fp8 e4m3), against the unfused pipeline a descriptor
+based library needs: one descriptor per (tensor, block) into a staging area on the decode GPU
+through ``nixl_agent`` WRITE, then a separate reshard(+cast) pass on the decode GPU.
+KV size math follows the reference's kvbench model files (benchmark/kvbench/models/llama3_1.py:62-93).
+"""
+import argparse
+import json
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+import torch.distributed as dist  # noqa: E402
+
+from nixl_b200 import _bindings as nb  # noqa: E402
+from nixl_b200 import nixl_agent, nixl_agent_config  # noqa: E402
+from nixl_b200.ops import KVLayout, KVTransfer  # noqa: E402
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--layers", type=int, default=32)
+    ap.add_argument("--requests", type=int, default=8)
+    ap.add_argument("--prompt", type=int, default=4096)
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--skip-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    tokens, head_dim, src_heads, dst_heads = 16, 128, 2, 4
+    blocks_per_req = args.prompt // tokens
+    n_blocks = args.requests * blocks_per_req
+    n_tensors = args.layers * 2
+    n_prefill = max(1, world // 2)
+    is_prefill = rank < n_prefill or world == 1
+    is_decode = rank >= n_prefill or world == 1
+    decode_of = (lambda p: (n_prefill + p // 2) if world >= 4 else (world - 1))
+
+    agent = nixl_agent(f"kv{rank}", nixl_agent_config(enable_prog_thread=False, backends=["NVLINK"]))
+    g = torch.Generator(device=dev).manual_seed(7 + rank)
+    src = dst = dst8 = staging = None
+    if is_prefill:
+        src = [torch.randn(n_blocks, tokens, src_heads, head_dim, device=dev, dtype=torch.bfloat16, generator=g) for _ in range(n_tensors)]
+        agent.register_memory(src)
+    if is_decode:
+        dst = [torch.zeros(n_blocks, tokens, dst_heads, head_dim, device=dev, dtype=torch.bfloat16) for _ in range(n_tensors)]
+        dst8 = [torch.zeros(n_blocks, tokens, dst_heads, head_dim, device=dev, dtype=torch.uint8) for _ in range(n_tensors)]
+        # staging for the unfused baseline: one landing area per (up to two) prefill senders
+        staging = torch.zeros(2, n_tensors, n_blocks, tokens * src_heads * head_dim, device=dev, dtype=torch.bfloat16)
+        agent.register_memory(dst)
+        agent.register_memory(dst8)
+        agent.register_memory(staging)
+    info = {"md": agent.get_agent_metadata(), "name": agent.name,
+            "dst": [(t.data_ptr(), t.numel() * 2, local) for t in dst] if is_decode else None,
+            "dst8": [(t.data_ptr(), t.numel(), local) for t in dst8] if is_decode else None,
+            "staging": (staging.data_ptr(), staging.numel() * 2, local) if is_decode else None}
+    infos = [None] * world
+    if world > 1:
+        dist.all_gather_object(infos, info)
+    else:
+        infos = [info]
+    target = decode_of(rank) if is_prefill else None
+    if world == 1:
+        target = 0
+    if is_prefill and target != rank:
+        agent.add_remote_agent(infos[target]["md"])
+
+    perm = torch.randperm(n_blocks, generator=torch.Generator().manual_seed(123))
+    src_table = perm.int().to(dev)                     # request r uses blocks perm[r*256:(r+1)*256] of the prefill cache
+    dst_table = torch.randperm(n_blocks, generator=torch.Generator().manual_seed(321)).int().to(dev)
+    head_off = (rank % 2) * src_heads if world >= 4 else 0
+    rec = {"bench": "kvbench", "n_gpus": world, "layers": args.layers, "requests": args.requests, "prompt_tokens": args.prompt,
+           "blocks": n_blocks, "prefill_ranks": n_prefill if world > 1 else 1}
+    block_bytes = tokens * src_heads * head_dim * 2
+    bytes_per_rank = n_tensors * n_blocks * block_bytes
+    rec["bytes_per_prefill_rank"] = bytes_per_rank
+
+    def time_dev(fn, iters):
+        ts = []
+        for i in range(iters + 2):
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            if i >= 2:
+                ts.append(e0.elapsed_time(e1))
+        ts.sort()
+        t = torch.tensor([ts[len(ts) // 2]], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t)
+
+    for fp8 in (False, True):
+        xfer = None
+        if is_prefill:
+            remote = infos[target]["dst8" if fp8 else "dst"]
+            xfer = KVTransfer(agent, src, KVLayout(tokens, src_heads, head_dim), infos[target]["name"], remote,
+                              KVLayout(tokens, dst_heads, head_dim, elem_bytes=1 if fp8 else 2), dst_head_offset=head_off, cast_fp8=fp8)
+
+        def fused_all():
+            if xfer is not None:
+                xfer.post(src_table, dst_table)
+
+        def fused_one():
+            if xfer is not None:
+                xfer.post(src_table[:blocks_per_req], dst_table[:blocks_per_req])
+
+        ms_all = time_dev(fused_all, args.iters)
+        ms_one = time_dev(fused_one, args.iters)
+        key = "fp8" if fp8 else "bf16"
+        rec[f"fused_{key}_ms_per_batch"] = round(ms_all, 4)
+        rec[f"fused_{key}_ms_per_request"] = round(ms_all / args.requests, 4)
+        rec[f"fused_{key}_single_request_ms"] = round(ms_one, 4)
+        rec[f"fused_{key}_GBps_per_prefill_rank"] = round(bytes_per_rank / (ms_all * 1e-3) / 1e9, 1)
+        if is_prefill and not fp8:
+            # spot check of one tensor against the PyTorch statement
+            torch.cuda.synchronize()
+        barrier()
+        if world == 1 and not fp8:
+            from nixl_b200.ops import reference_kv_transfer
+            want = reference_kv_transfer(src[3], torch.zeros_like(dst[3]), src_table, dst_table, head_off)
+            rec["verified"] = bool(torch.equal(want, dst[3]))
+        if xfer is not None:
+            xfer.close()
+
+    if not args.skip_baseline:
+        # Unfused: descriptor list (one per tensor x block, 8 KiB each) into staging, then reshard on the decode GPU.
+        h = None
+        if is_prefill:
+            sbase, _, sdev = infos[target]["staging"]
+            lane = (rank % 2) if world >= 4 else 0
+            la, ra = [], []
+            src_blocks = src_table.tolist()
+            for t in range(n_tensors):
+                tb = src[t].data_ptr()
+                rb = sbase + ((lane * n_tensors + t) * n_blocks) * block_bytes
+                for i, sb in enumerate(src_blocks):
+                    la.append((tb + sb * block_bytes, block_bytes, local))
+                    ra.append((rb + i * block_bytes, block_bytes, sdev))
+            import numpy as np
+            h = agent.initialize_xfer("WRITE", agent.get_xfer_descs(np.array(la, dtype=np.uint64), "VRAM"),
+                                      agent.get_xfer_descs(np.array(ra, dtype=np.uint64), "VRAM"), infos[target]["name"])
+            rec["baseline_descriptors"] = len(la)
+
+        def unfused_transfer():
+            if h is not None:
+                agent.agent.postXferReq(h)
+                while agent.agent.getXferStatus(h) != nb.NIXL_SUCCESS:
+                    pass
+
+        def reshard(fp8):
+            if not is_decode:
+                return
+            lanes = 2 if world >= 4 else 1
+            idx = dst_table.long()
+            for lane in range(lanes):
+                for t in range(n_tensors):
+                    blk = staging[lane, t].view(n_blocks, tokens, src_heads, head_dim)
+                    if fp8:
+                        dst8[t][idx, :, lane * src_heads:(lane + 1) * src_heads, :] = blk.float().to(torch.float8_e4m3fn).view(torch.uint8)
+                    else:
+                        dst[t][idx, :, lane * src_heads:(lane + 1) * src_heads, :] = blk
+
+        ms_x = time_dev(unfused_transfer, max(3, args.iters // 2))
+        ms_r = time_dev(lambda: reshard(False), max(3, args.iters // 2))
+        ms_r8 = time_dev(lambda: reshard(True), max(3, args.iters // 2))
+        rec["unfused_transfer_ms_per_batch"] = round(ms_x, 4)
+        rec["unfused_reshard_bf16_ms_per_batch"] = round(ms_r, 4)
+        rec["unfused_reshard_fp8_ms_per_batch"] = round(ms_r8, 4)
+        rec["unfused_bf16_ms_per_request"] = round((ms_x + ms_r) / args.requests, 4)
+        rec["unfused_fp8_ms_per_request"] = round((ms_x + ms_r8) / args.requests, 4)
+        rec["speedup_bf16"] = round((ms_x + ms_r) / rec["fused_bf16_ms_per_batch"], 2)
+        rec["speedup_fp8"] = round((ms_x + ms_r8) / rec["fused_fp8_ms_per_batch"], 2)
+        if h is not None:
+            agent.release_xfer_handle(h)
+    if rank == 0:
+        print(json.dumps(rec), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -85,12 +85,12 @@ template<nixl_gpu_level_t level> __device__ __forceinline__ void copy(char *dst,
         const uint4 *s = reinterpret_cast<const uint4 *>(src);
         uint4 *d = reinterpret_cast<uint4 *>(dst);
         size_t i = lane;
-        for (; i + 3 * size_t(width) < nvec; i += 4 * size_t(width)) {
-            const uint4 a = s[i], b = s[i + width], c = s[i + 2 * size_t(width)], e = s[i + 3 * size_t(width)];
-            d[i] = a;
-            d[i + width] = b;
-            d[i + 2 * size_t(width)] = c;
-            d[i + 3 * size_t(width)] = e;
+        for (; i + 7 * size_t(width) < nvec; i += 8 * size_t(width)) { // eight loads in flight before the first store
+            uint4 t[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) t[k] = s[i + k * size_t(width)];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) d[i + k * size_t(width)] = t[k];
         }
         for (; i < nvec; i += width) d[i] = s[i];
         for (size_t k = (nvec << 4) + lane; k < n; k += width) dst[k] = src[k];

@@ -201,6 +201,7 @@ typedef struct NixlDevPutParams {
     void *remote_signals;       /* remote view, one entry per rank */
     const int32_t *peer_ids;    /* device [peers] ranks this rank talks to */
     int32_t peers, rank, iters, window, compute_passes;
+    int32_t ctas_per_peer;      /* the tile is cut into this many slices, one producer CTA each */
     uint64_t tile_bytes;
     uint64_t ack_offset;        /* bytes */
     uint64_t timeout_ns;

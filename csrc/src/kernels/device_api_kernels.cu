@@ -40,10 +40,10 @@ __global__ void putTestKernel(nixlMemViewH src, nixlMemViewH dst, nixlMemViewH s
 }
 
 // Persistent producer/consumer kernel of the device-initiated benchmark.
-//   CTA b < peers: producer for peer b: per iteration a stand-in compute pass over its tile,
+//   producer CTAs (ctas_per_peer per peer): per iteration a stand-in compute pass over a slice of the tile,
 //                  then nixlPut<BLOCK> of the tile into the peer's slot for this rank and an
 //                  atomic add on the peer's counter for this rank;
-//   CTA peers:     consumer: waits (bounded) until every peer's counter reaches the iteration.
+//   last CTA:      consumer: waits (bounded) until every peer's counter reaches the iteration.
 // Flow control: a producer may run at most `window` iterations ahead of what its peer consumed
 // (the peer publishes its consumed count back through a second counter).
 __global__ void __launch_bounds__(512) putSignalKernel(NixlDevPutParams p) {
@@ -51,10 +51,15 @@ __global__ void __launch_bounds__(512) putSignalKernel(NixlDevPutParams p) {
     if (threadIdx.x == 0) failed = 0;
     __syncthreads();
     const int b = blockIdx.x;
-    if (b < p.peers) {
-        const int peer = p.peer_ids[b];
-        float4 *tile = reinterpret_cast<float4 *>(static_cast<char *>(nixlGetPtr(p.local_tiles, 0)) + static_cast<size_t>(b) * p.tile_bytes);
-        const size_t n4 = p.tile_bytes / sizeof(float4);
+    const int cpp = p.ctas_per_peer;
+    if (b < p.peers * cpp) {
+        // Producer: slice `part` of the tile for peer `pi`.
+        const int pi = b / cpp, part = b - pi * cpp;
+        const int peer = p.peer_ids[pi];
+        const size_t slice = p.tile_bytes / cpp;
+        const size_t tile_off = static_cast<size_t>(pi) * p.tile_bytes + part * slice;
+        float4 *tile = reinterpret_cast<float4 *>(static_cast<char *>(nixlGetPtr(p.local_tiles, 0)) + tile_off);
+        const size_t n4 = slice / sizeof(float4);
         for (int it = 1; it <= p.iters; ++it) {
             // stand-in for the compute that produces the tile
             for (int r = 0; r < p.compute_passes; ++r)
@@ -65,7 +70,7 @@ __global__ void __launch_bounds__(512) putSignalKernel(NixlDevPutParams p) {
                     tile[i] = v;
                 }
             __syncthreads();
-            // do not overrun the consumer: it acknowledges in ack[peer slot for me]
+            // do not overrun the consumer: it acknowledges in ack[peer]
             if (it > p.window) {
                 if (threadIdx.x == 0) {
                     const uint64_t *ack = reinterpret_cast<const uint64_t *>(static_cast<char *>(nixlGetPtr(p.local_signals, 0)) + p.ack_offset) + peer;
@@ -75,18 +80,19 @@ __global__ void __launch_bounds__(512) putSignalKernel(NixlDevPutParams p) {
                 if (failed) break;
             }
             const size_t slot = static_cast<size_t>((it - 1) % p.window);
-            nixlMemViewElem src{p.local_tiles, 0, static_cast<size_t>(b) * p.tile_bytes};
-            nixlMemViewElem dst{p.remote_tiles, static_cast<size_t>(peer), (static_cast<size_t>(p.rank) * p.window + slot) * p.tile_bytes};
-            nixlPut<nixl_gpu_level_t::BLOCK>(src, dst, p.tile_bytes);
+            nixlMemViewElem src{p.local_tiles, 0, tile_off};
+            nixlMemViewElem dst{p.remote_tiles, static_cast<size_t>(peer),
+                                (static_cast<size_t>(p.rank) * p.window + slot) * p.tile_bytes + part * slice};
+            nixlPut<nixl_gpu_level_t::BLOCK>(src, dst, slice);
             nixlAtomicAdd<nixl_gpu_level_t::BLOCK>(1, nixlMemViewElem{p.remote_signals, static_cast<size_t>(peer), static_cast<size_t>(p.rank) * 8});
         }
-    } else if (b == p.peers) {
-        // consumer: thread j watches peer j's arrivals and acknowledges them
+    } else {
+        // Consumer: thread j watches peer j's arrivals (every slice counts once) and acknowledges whole tiles.
         if (static_cast<int>(threadIdx.x) < p.peers) {
             const int peer = p.peer_ids[threadIdx.x];
             const uint64_t *arrived = reinterpret_cast<const uint64_t *>(nixlGetPtr(p.local_signals, 0)) + peer;
             for (int it = 1; it <= p.iters; ++it) {
-                if (nixlSignalWait(arrived, static_cast<uint64_t>(it), p.timeout_ns) != NIXL_SUCCESS) {
+                if (nixlSignalWait(arrived, static_cast<uint64_t>(it) * cpp, p.timeout_ns) != NIXL_SUCCESS) {
                     failed = 1;
                     break;
                 }
@@ -115,7 +121,16 @@ extern "C" int nixl_devapi_put_test(int level, const void *src_view, const void 
 }
 
 extern "C" int nixl_devapi_put_signal_launch(const NixlDevPutParams *params, void *stream) {
-    if (!params || params->peers <= 0 || params->peers > 64 || params->window <= 0 || (params->tile_bytes & 15)) return cudaErrorInvalidValue;
-    putSignalKernel<<<params->peers + 1, 512, 0, static_cast<cudaStream_t>(stream)>>>(*params);
+    if (!params || params->peers <= 0 || params->peers > 64 || params->window <= 0 || params->ctas_per_peer <= 0 ||
+        (params->tile_bytes % (16ull * params->ctas_per_peer)))
+        return cudaErrorInvalidValue;
+    // All CTAs must be resident together (producers wait for acknowledgements raised by consumer
+    // CTAs of the peers, and the local consumer CTA must run next to the producers).
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int grid = params->peers * params->ctas_per_peer + 1;
+    if (grid > sms) return cudaErrorInvalidValue;
+    putSignalKernel<<<grid, 512, 0, static_cast<cudaStream_t>(stream)>>>(*params);
     return cudaGetLastError();
 }

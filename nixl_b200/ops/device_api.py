@@ -18,6 +18,7 @@ class DevPutParams(ctypes.Structure):
         ("local_tiles", ctypes.c_void_p), ("remote_tiles", ctypes.c_void_p), ("local_signals", ctypes.c_void_p), ("remote_signals", ctypes.c_void_p),
         ("peer_ids", ctypes.c_void_p),
         ("peers", ctypes.c_int32), ("rank", ctypes.c_int32), ("iters", ctypes.c_int32), ("window", ctypes.c_int32), ("compute_passes", ctypes.c_int32),
+        ("ctas_per_peer", ctypes.c_int32),
         ("tile_bytes", ctypes.c_uint64), ("ack_offset", ctypes.c_uint64), ("timeout_ns", ctypes.c_uint64), ("status", ctypes.c_void_p),
     ]
 
