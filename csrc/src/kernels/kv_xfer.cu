@@ -95,14 +95,15 @@ template<bool kCast> __global__ void __launch_bounds__(kThreads) kvXferKernel(co
         }
     }
 
-    // Completion: the last CTA to finish signals the receiver (and the host, if asked).
+    // Completion: the last CTA to finish signals the receiver (and the host, if asked).  One
+    // acquire-release add at GPU scope chains the CTAs; the release operations at system scope
+    // that follow publish every CTA's stores before the signal becomes visible.
     __syncthreads();
     if (threadIdx.x == 0) {
-        __threadfence_system();
-        const unsigned prev = atomicAdd(p.done_counter, 1u);
+        unsigned prev;
+        asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(prev) : "l"(p.done_counter) : "memory");
         if (prev == gridDim.x - 1) {
             *p.done_counter = 0;
-            __threadfence_system();
             if (p.done_signal) asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(p.done_signal), "l"(p.done_value) : "memory");
             if (p.host_flag) asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p.host_flag), "l"(p.host_seq) : "memory");
         }

@@ -33,11 +33,48 @@ __device__ __forceinline__ void st_release_sys(uint64_t *p, uint64_t v) {
     asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
 
-// Copies n bytes with the whole CTA.  Fast path: source and destination share their
-// offset within 16 bytes, so after a short head both are 16-byte aligned.
+struct Vec32 {
+    float v[8];
+};
+__device__ __forceinline__ Vec32 ld_stream32(const void *p) {
+    Vec32 r;
+    asm volatile("ld.global.L1::no_allocate.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=f"(r.v[0]), "=f"(r.v[1]), "=f"(r.v[2]), "=f"(r.v[3]), "=f"(r.v[4]), "=f"(r.v[5]), "=f"(r.v[6]), "=f"(r.v[7])
+                 : "l"(p));
+    return r;
+}
+__device__ __forceinline__ void st_stream32(void *p, const Vec32 &r) {
+    asm volatile("st.global.L1::no_allocate.v8.f32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "f"(r.v[0]), "f"(r.v[1]), "f"(r.v[2]),
+                 "f"(r.v[3]), "f"(r.v[4]), "f"(r.v[5]), "f"(r.v[6]), "f"(r.v[7])
+                 : "memory");
+}
+
+// Copies n bytes with the whole CTA.  Fastest path: source and destination share their offset
+// within 32 bytes, so after a short head both take 256-bit accesses (sm_100: one warp
+// instruction moves 1 KiB).  Otherwise 16-byte, 4-byte or byte accesses by relative alignment.
 __device__ __forceinline__ void copyRange(const char *__restrict__ s, char *__restrict__ d, size_t n) {
     const unsigned tid = threadIdx.x;
-    if ((((uintptr_t)s ^ (uintptr_t)d) & 15) == 0) {
+    if ((((uintptr_t)s ^ (uintptr_t)d) & 31) == 0) {
+        size_t head = (32 - ((uintptr_t)s & 31)) & 31;
+        if (head > n) head = n;
+        if (tid < head) d[tid] = s[tid];
+        s += head;
+        d += head;
+        n -= head;
+        const size_t nvec = n >> 5;
+        size_t i = tid;
+        for (; i + (kUnroll - 1) * kThreads < nvec; i += kUnroll * kThreads) {
+            Vec32 v[kUnroll];
+#pragma unroll
+            for (int k = 0; k < kUnroll; ++k) v[k] = ld_stream32(s + ((i + k * kThreads) << 5));
+#pragma unroll
+            for (int k = 0; k < kUnroll; ++k) st_stream32(d + ((i + k * kThreads) << 5), v[k]);
+        }
+        for (; i < nvec; i += kThreads) st_stream32(d + (i << 5), ld_stream32(s + (i << 5)));
+        const size_t done = nvec << 5;
+        const size_t tail = n - done;
+        if (tid < tail) d[done + tid] = s[done + tid];
+    } else if ((((uintptr_t)s ^ (uintptr_t)d) & 15) == 0) {
         size_t head = (16 - ((uintptr_t)s & 15)) & 15;
         if (head > n) head = n;
         if (tid < head) d[tid] = s[tid];
@@ -89,16 +126,22 @@ template<class StartFn> __device__ __forceinline__ uint32_t ownerOf(uint32_t c, 
 }
 
 // Tail shared by all variants: publish completion once every CTA has finished.
+// One acquire-release add at GPU scope chains the CTAs (each CTA's stores are ordered before
+// its add by the barrier; the add that sees all others therefore follows every store), and one
+// release store at system scope makes all of it visible before the completion word changes.
+// System-scope fences are expensive when stores to a peer GPU and to host memory are in
+// flight, so the tail uses exactly one.
 __device__ __forceinline__ void finishBatch(const XferLaunch &p) {
     __syncthreads();
     if (threadIdx.x == 0) {
-        __threadfence_system(); // this CTA's stores (ordered by the barrier) before the count
-        const unsigned prev = atomicAdd(p.doneCounter, 1u);
-        if (prev == gridDim.x - 1) {
-            *p.doneCounter = 0; // ready for the next post of this request
-            __threadfence_system();
-            st_release_sys(p.hostFlag, p.seq);
+        bool last = true;
+        if (gridDim.x > 1) {
+            unsigned prev;
+            asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(prev) : "l"(p.doneCounter) : "memory");
+            last = prev == gridDim.x - 1;
+            if (last) *p.doneCounter = 0; // ready for the next post of this request (stream order protects it)
         }
+        if (last) st_release_sys(p.hostFlag, p.seq);
     }
 }
 
@@ -257,18 +300,22 @@ __global__ void __launch_bounds__(128) batchCopyBulk(const __grid_constant__ Xfe
         // Sub-16-byte tail of the chunk.
         if (threadIdx.x >= 32 && threadIdx.x - 32 < n - body) dst[body + threadIdx.x - 32] = s[body + threadIdx.x - 32];
     }
-    if (threadIdx.x == 0) bulkWait<0>(); // all stores globally performed before the completion count
+    if (threadIdx.x == 0) bulkWait<0>(); // this CTA's bulk stores are complete
     __syncthreads();
     if (threadIdx.x == 0) {
-        __threadfence_system();
-        const unsigned prev = atomicAdd(p.doneCounter, 1u);
+        asm volatile("fence.proxy.async;" ::: "memory"); // async-proxy stores before the generic-proxy flag
         if (failed) atomicOr(reinterpret_cast<unsigned long long *>(p.hostFlag), 1ull << 63);
-        if (prev == gridDim.x - 1) {
-            *p.doneCounter = 0;
-            __threadfence_system();
+        bool last = true;
+        if (gridDim.x > 1) {
+            unsigned prev;
+            asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(prev) : "l"(p.doneCounter) : "memory");
+            last = prev == gridDim.x - 1;
+            if (last) *p.doneCounter = 0;
+        }
+        if (last) {
             // Bit 63 set by any CTA marks the batch as failed; keep it.
-            const unsigned long long cur = atomicAdd(reinterpret_cast<unsigned long long *>(p.hostFlag), 0ull);
-            st_release_sys(p.hostFlag, p.seq | (cur & (1ull << 63)));
+            const unsigned long long cur = failed ? (1ull << 63) : (atomicAdd(reinterpret_cast<unsigned long long *>(p.hostFlag), 0ull) & (1ull << 63));
+            st_release_sys(p.hostFlag, p.seq | cur);
         }
     }
 }
