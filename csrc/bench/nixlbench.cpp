@@ -9,7 +9,7 @@
 //
 //   nixlbench [--backend NVLINK] [--op WRITE|READ] [--mem VRAM|DRAM] [--src-dev 0] [--dst-dev 1]
 //             [--min 4096] [--max 1073741824] [--batch 1] [--iters 1000] [--warmup 100]
-//             [--depth 1] [--copy-path vector|bulk] [--check]
+//             [--depth 1] [--copy-path vector|bulk] [--param key=value]... [--check]
 #include <algorithm>
 #include <chrono>
 #include <cstdio>
@@ -31,6 +31,7 @@ struct Args {
     int src_dev = 0, dst_dev = -1, batch = 1, iters = 1000, warmup = 100, depth = 1;
     size_t min = 4096, max = size_t(1) << 30, total = size_t(8) << 30;
     bool check = false;
+    nixl_b_params_t extra; // --param key=value, passed to the backend
 };
 
 double pct(std::vector<double> &v, double q) {
@@ -59,6 +60,11 @@ int main(int argc, char **argv) {
         else if (k == "--max") a.max = std::strtoull(val(), nullptr, 0);
         else if (k == "--total") a.total = std::strtoull(val(), nullptr, 0);
         else if (k == "--check") a.check = true;
+        else if (k == "--param") {
+            const std::string kv = val();
+            const size_t eq = kv.find('=');
+            if (eq != std::string::npos) a.extra[kv.substr(0, eq)] = kv.substr(eq + 1);
+        }
         else {
             std::fprintf(stderr, "unknown option %s\n", k.c_str());
             return 2;
@@ -92,6 +98,7 @@ int main(int argc, char **argv) {
     nixlAgent ini("initiator", cfg), tgt("target", cfg);
     nixlBackendH *bi = nullptr, *bt = nullptr;
     nixl_b_params_t params = {{"copy_path", a.copy_path}};
+    for (auto &kv : a.extra) params[kv.first] = kv.second;
     if (ini.createBackend(a.backend, params, bi) != NIXL_SUCCESS || tgt.createBackend(a.backend, params, bt) != NIXL_SUCCESS) {
         std::fprintf(stderr, "cannot create backend %s\n", a.backend.c_str());
         return 4;
