@@ -305,37 +305,52 @@ groupedGemmKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
 #pragma unroll
             for (int i = 0; i < BN; ++i) acc[i] = 0.f;
             bool ok = true;
-            for (int ks = 0; ks < k_steps; ++ks, ++it) {
-                const int buf = it & 1;
-                const float s = (valid ? __ldg(sa_row + ks) : 0.f) * __ldg(sw + ks);
-                if (!mbarWait(&sh.tmemFull[buf], (it >> 1) & 1, abort_flag)) {
-                    ok = false;
-                    break;
+            // The combined scale of a step is needed by every FMA of that step, so its two loads
+            // must not sit on the critical path: a register ring keeps them kPrefetch steps ahead.
+            constexpr int kPrefetch = 4;
+            float sring[kPrefetch];
+#pragma unroll
+            for (int j = 0; j < kPrefetch; ++j)
+                sring[j] = j < k_steps ? (valid ? __ldg(sa_row + j) : 0.f) * __ldg(sw + j) : 0.f;
+            for (int ks0 = 0; ks0 < k_steps && ok; ks0 += kPrefetch) {
+#pragma unroll
+                for (int j = 0; j < kPrefetch; ++j) {
+                    const int ks = ks0 + j;
+                    if (ks >= k_steps) break;
+                    const int buf = it & 1;
+                    const float s = sring[j];
+                    const int nxt = ks + kPrefetch;
+                    if (nxt < k_steps) sring[j] = (valid ? __ldg(sa_row + nxt) : 0.f) * __ldg(sw + nxt);
+                    if (!mbarWait(&sh.tmemFull[buf], (it >> 1) & 1, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    tcFenceAfter();
+                    const uint32_t base = tmem + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
+                    // Two register buffers: the load of chunk c+1 is in flight while chunk c is scaled and added.
+                    float v0[32], v1[32];
+                    tmemLoad32(base, v0);
+                    tmemLoadWait(v0);
+                    tmemLoad32(base + 32, v1);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) acc[i] = fmaf(v0[i], s, acc[i]);
+                    tmemLoadWait(v1);
+                    tmemLoad32(base + 64, v0);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) acc[32 + i] = fmaf(v1[i], s, acc[32 + i]);
+                    tmemLoadWait(v0);
+                    tmemLoad32(base + 96, v1);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) acc[64 + i] = fmaf(v0[i], s, acc[64 + i]);
+                    tmemLoadWait(v1);
+                    // All of this accumulator has been read: hand it back before the last FMAs.
+                    tcFenceBefore();
+                    __syncwarp();
+                    if (lane == 0) mbarArrive(&sh.tmemEmpty[buf]);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) acc[96 + i] = fmaf(v1[i], s, acc[96 + i]);
+                    ++it;
                 }
-                tcFenceAfter();
-                const uint32_t base = tmem + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
-                // Two register buffers: the load of chunk c+1 is in flight while chunk c is scaled and added.
-                float v0[32], v1[32];
-                tmemLoad32(base, v0);
-                tmemLoadWait(v0);
-                tmemLoad32(base + 32, v1);
-#pragma unroll
-                for (int i = 0; i < 32; ++i) acc[i] = fmaf(v0[i], s, acc[i]);
-                tmemLoadWait(v1);
-                tmemLoad32(base + 64, v0);
-#pragma unroll
-                for (int i = 0; i < 32; ++i) acc[32 + i] = fmaf(v1[i], s, acc[32 + i]);
-                tmemLoadWait(v0);
-                tmemLoad32(base + 96, v1);
-#pragma unroll
-                for (int i = 0; i < 32; ++i) acc[64 + i] = fmaf(v0[i], s, acc[64 + i]);
-                tmemLoadWait(v1);
-                // All of this accumulator has been read: hand it back before the last FMAs.
-                tcFenceBefore();
-                __syncwarp();
-                if (lane == 0) mbarArrive(&sh.tmemEmpty[buf]);
-#pragma unroll
-                for (int i = 0; i < 32; ++i) acc[96 + i] = fmaf(v1[i], s, acc[96 + i]);
             }
             if (!ok) break;
             if (valid) {
