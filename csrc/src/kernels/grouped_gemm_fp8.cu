@@ -4,16 +4,18 @@
 //   A: e4m3, one fp32 scale per row per 128 channels (what EP dispatch delivers)
 //   W: e4m3, one fp32 scale per 128 x 128 block
 //
-// sm_100a only.  One persistent CTA per SM, 256 threads, warp-specialised:
+// sm_100a only.  One persistent CTA per SM, 384 threads, warp-specialised:
 //   warp 0  TMA producer   cp.async.bulk.tensor (2-D, 128-byte swizzle) of a 128x128 A tile and a
 //                          128x128 W tile per 128-channel step into a 5-stage shared-memory ring
-//   warp 1  MMA issuer     4 x tcgen05.mma.kind::f8f6f4 (M128 N128 K32) per step into one of two
-//                          TMEM accumulators (128 lanes x 128 fp32 columns each)
+//   warp 1  MMA issuer     4 x tcgen05.mma.kind::f8f6f4 (M128 N128 K32) per step into one of four
+//                          TMEM accumulators (128 lanes x 128 fp32 columns each: all 512 columns)
 //   warp 2  TMEM allocator
-//   warps 4-7 promotion + epilogue: tcgen05.ld the step's partial sums, multiply by
+//   warps 4-11 promotion + epilogue (two warps per TMEM lane quarter, 64 columns each):
+//                          tcgen05.ld the step's partial sums, multiply by
 //                          scaleA[row, step] * scaleW[g, n-block, step], accumulate in registers
 //                          (the per-128-channel scales cannot be folded into the MMA), finally
-//                          store bf16.  The MMA of step i+1 overlaps the promotion of step i.
+//                          store bf16.  Four accumulators keep the MMA pipe fed across the
+//                          commit -> wait -> load -> release round trip of each step.
 // TMA loads read this GPU's own memory only and use no cluster multicast.  When `disp_flag` is
 // given, the producer waits (bounded) for the per-(expert, source rank) arrival flags raised by
 // ep_kernels.cu before it loads rows that those sources wrote: dispatch and GEMM overlap tile by
@@ -35,10 +37,11 @@ namespace {
 constexpr int BM = 128, BN = 128, BK = 128; // tile; BK is also the scale granularity
 constexpr int UMMA_K = 32;                  // fp8: 32 bytes of K per instruction
 constexpr int kStages = 5;
-constexpr int kThreads = 256;
+constexpr int kThreads = 384;              // 4 role warps + 8 promotion warps
 constexpr int kTileBytes = BM * BK;         // 16 KiB (fp8)
 constexpr int kStageBytes = 2 * kTileBytes; // A + W
-constexpr int kTmemCols = 256;              // two accumulators of 128 columns
+constexpr int kAccBufs = 4;                 // TMEM accumulators in flight (4 x 128 columns = all of TMEM)
+constexpr int kTmemCols = kAccBufs * BN;
 constexpr int kMaxGroups = 512;
 constexpr uint64_t kWaitNs = 4000000000ull; // any single wait longer than 4 s aborts the kernel
 
@@ -47,8 +50,8 @@ enum : int { GEMM_ERR_TIMEOUT = 1, GEMM_ERR_ARRIVAL = 2 };
 struct Shared {
     uint64_t full[kStages];
     uint64_t empty[kStages];
-    uint64_t tmemFull[2];
-    uint64_t tmemEmpty[2];
+    uint64_t tmemFull[kAccBufs];
+    uint64_t tmemEmpty[kAccBufs];
     uint32_t tmemBase;
     int abort;
     int tilePrefix[kMaxGroups + 1]; // tiles before group g
@@ -196,9 +199,9 @@ groupedGemmKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
             mbarInit(&sh.full[s], 1);
             mbarInit(&sh.empty[s], 1);
         }
-        for (int b = 0; b < 2; ++b) {
+        for (int b = 0; b < kAccBufs; ++b) {
             mbarInit(&sh.tmemFull[b], 1);
-            mbarInit(&sh.tmemEmpty[b], 4); // one arrival per promotion warp
+            mbarInit(&sh.tmemEmpty[b], 8); // one arrival per promotion warp
         }
         sh.abort = 0;
         // Tile table: group g owns ceil(count/BM) x n_tiles tiles.
@@ -270,8 +273,8 @@ groupedGemmKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
         Tile t;
         for (int ti = blockIdx.x; tileAt(sh, p.groups, n_tiles, ti, t); ti += gridDim.x) {
             for (int ks = 0; ks < k_steps; ++ks, ++it) {
-                const int s = it % kStages, buf = it & 1;
-                if (!mbarWait(&sh.tmemEmpty[buf], ((it >> 1) & 1) ^ 1, abort_flag)) goto mma_done;
+                const int s = it % kStages, buf = it % kAccBufs;
+                if (!mbarWait(&sh.tmemEmpty[buf], ((it / kAccBufs) & 1) ^ 1, abort_flag)) goto mma_done;
                 if (!mbarWait(&sh.full[s], (it / kStages) & 1, abort_flag)) goto mma_done;
                 tcFenceAfter();
                 const uint32_t a_addr = smemU32(tiles + s * kStageBytes);
@@ -290,7 +293,9 @@ groupedGemmKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
     mma_done:;
     } else if (warp >= 4) {
         // ---------------------------------------------------------------- promotion + epilogue
-        const int q = warp - 4;            // TMEM lane quarter this warp may touch
+        const int q = warp & 3;            // TMEM lane quarter this warp may touch (fixed by warp id % 4)
+        const int half = (warp - 4) >> 2;  // which 64 of the tile's 128 columns this warp promotes
+        constexpr int HN = BN / 2;
         const int row_in_tile = q * 32 + lane;
         uint32_t it = 0;
         Tile t;
@@ -301,9 +306,9 @@ groupedGemmKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
             const long long grow = static_cast<long long>(sh.rowStart[t.g]) + local_row;
             const float *sa_row = scale_a + grow * k_steps;
             const float *sw = p.scale_w + (static_cast<long long>(t.g) * n_tiles + t.nt) * k_steps;
-            float acc[BN];
+            float acc[HN];
 #pragma unroll
-            for (int i = 0; i < BN; ++i) acc[i] = 0.f;
+            for (int i = 0; i < HN; ++i) acc[i] = 0.f;
             bool ok = true;
             // The combined scale of a step is needed by every FMA of that step, so its two loads
             // must not sit on the critical path: a register ring keeps them kPrefetch steps ahead.
@@ -317,46 +322,38 @@ groupedGemmKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
                 for (int j = 0; j < kPrefetch; ++j) {
                     const int ks = ks0 + j;
                     if (ks >= k_steps) break;
-                    const int buf = it & 1;
+                    const int buf = it % kAccBufs;
                     const float s = sring[j];
                     const int nxt = ks + kPrefetch;
                     if (nxt < k_steps) sring[j] = (valid ? __ldg(sa_row + nxt) : 0.f) * __ldg(sw + nxt);
-                    if (!mbarWait(&sh.tmemFull[buf], (it >> 1) & 1, abort_flag)) {
+                    if (!mbarWait(&sh.tmemFull[buf], (it / kAccBufs) & 1, abort_flag)) {
                         ok = false;
                         break;
                     }
                     tcFenceAfter();
-                    const uint32_t base = tmem + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
-                    // Two register buffers: the load of chunk c+1 is in flight while chunk c is scaled and added.
+                    const uint32_t base = tmem + (static_cast<uint32_t>(q * 32) << 16) + buf * BN + half * HN;
+                    // Two register buffers: the second load is in flight while the first is scaled and added.
                     float v0[32], v1[32];
                     tmemLoad32(base, v0);
-                    tmemLoadWait(v0);
                     tmemLoad32(base + 32, v1);
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) acc[i] = fmaf(v0[i], s, acc[i]);
-                    tmemLoadWait(v1);
-                    tmemLoad32(base + 64, v0);
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) acc[32 + i] = fmaf(v1[i], s, acc[32 + i]);
                     tmemLoadWait(v0);
-                    tmemLoad32(base + 96, v1);
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) acc[64 + i] = fmaf(v0[i], s, acc[64 + i]);
                     tmemLoadWait(v1);
-                    // All of this accumulator has been read: hand it back before the last FMAs.
+                    // This warp's part of the accumulator has been read: hand it back before the FMAs.
                     tcFenceBefore();
                     __syncwarp();
                     if (lane == 0) mbarArrive(&sh.tmemEmpty[buf]);
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) acc[96 + i] = fmaf(v1[i], s, acc[96 + i]);
+                    for (int i = 0; i < 32; ++i) acc[i] = fmaf(v0[i], s, acc[i]);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) acc[32 + i] = fmaf(v1[i], s, acc[32 + i]);
                     ++it;
                 }
             }
             if (!ok) break;
             if (valid) {
-                __nv_bfloat16 *out = static_cast<__nv_bfloat16 *>(p.d) + grow * p.N + t.nt * BN;
+                __nv_bfloat16 *out = static_cast<__nv_bfloat16 *>(p.d) + grow * p.N + t.nt * BN + half * HN;
 #pragma unroll
-                for (int i = 0; i < BN; i += 8) {
+                for (int i = 0; i < HN; i += 8) {
                     uint4 o;
                     __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&o);
 #pragma unroll
