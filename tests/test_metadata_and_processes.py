@@ -1,0 +1,127 @@
+"""Metadata exchange through a torch TCPStore and a two-process transfer on 127.0.0.1.
+
+Mirrors the reference's test/gtest/md_manager.cpp (TCPStore fixture) and test/nixl/nixl_test.cpp
+(target / initiator processes).  The two-process case moves DRAM between processes (the
+NVLink backend's cross-process DRAM path) and checks the completion notification; it needs
+permission to read another process's memory, which a default container grants to children of
+the same user - the test skips otherwise."""
+import datetime
+import multiprocessing as mp
+import os
+import socket
+import time
+
+import pytest
+import torch
+import torch.distributed as dist
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def test_tcpstore_metadata_roundtrip(monkeypatch):
+    port = _free_port()
+    store = dist.TCPStore("127.0.0.1", port, is_master=True, wait_for_workers=False, timeout=datetime.timedelta(seconds=20))
+    monkeypatch.setenv("NIXL_TCPSTORE_ENDPOINT", f"127.0.0.1:{port}")
+    monkeypatch.setenv("NIXL_TCPSTORE_TIMEOUT_MS", "5000")
+    from nixl_b200 import nixl_agent, nixl_agent_config
+
+    a = nixl_agent("store_a", nixl_agent_config(enable_prog_thread=False, backends=["NVLINK"]))
+    b = nixl_agent("store_b", nixl_agent_config(enable_prog_thread=False, backends=["NVLINK"]))
+    ta, tb = torch.arange(4096, dtype=torch.uint8), torch.zeros(4096, dtype=torch.uint8)
+    a.register_memory(ta)
+    b.register_memory(tb)
+    a.send_local_metadata()  # publishes under nixl/agents/metadata/store_a/NULL_AGENT
+    b.send_local_metadata()
+    b.fetch_remote_metadata("store_a")
+    a.fetch_remote_metadata("store_b")
+    deadline = time.time() + 10
+    while time.time() < deadline and not (a.check_remote_metadata("store_b") and b.check_remote_metadata("store_a")):
+        time.sleep(0.01)
+    assert a.check_remote_metadata("store_b", a.get_xfer_descs(tb))
+    # the key is visible to a plain torch client under the documented name
+    assert store.check(["nixl/agents/metadata/store_a/NULL_AGENT"])
+    h = a.initialize_xfer("WRITE", ta, tb, "store_b")
+    assert a.transfer(h) in ("DONE", "PROC")
+    while a.check_xfer_state(h) == "PROC":
+        pass
+    assert torch.equal(ta, tb)
+    a.release_xfer_handle(h)
+    a.invalidate_local_metadata()
+    deadline = time.time() + 5
+    while time.time() < deadline and store.check(["nixl/agents/metadata/store_a/NULL_AGENT"]):
+        time.sleep(0.01)
+    assert not store.check(["nixl/agents/metadata/store_a/NULL_AGENT"])
+    del a, b
+
+
+def _target(port_t, port_i, ready, result):
+    from nixl_b200 import nixl_agent, nixl_agent_config
+
+    agent = nixl_agent("target", nixl_agent_config(enable_prog_thread=False, enable_listen_thread=True, listen_port=port_t, backends=["NVLINK"]))
+    buf = torch.zeros(1 << 20, dtype=torch.uint8)
+    agent.register_memory(buf)
+    result["addr"] = buf.data_ptr()
+    ready.set()
+    deadline = time.time() + 30
+    while time.time() < deadline:
+        if agent.check_remote_xfer_done("initiator", b"written"):
+            result["sum"] = int(buf.to(torch.int64).sum())
+            result["ok"] = True
+            # answer so the initiator can also test the reverse direction of notifications
+            agent.send_notif("initiator", b"thanks")
+            time.sleep(0.2)
+            return
+        time.sleep(0.001)
+    result["ok"] = False
+
+
+def test_two_processes_over_localhost():
+    ctx = mp.get_context("spawn")
+    mgr = ctx.Manager()
+    result = mgr.dict()
+    ready = ctx.Event()
+    port_t, port_i = _free_port(), _free_port()
+    proc = ctx.Process(target=_target, args=(port_t, port_i, ready, result))
+    proc.start()
+    try:
+        assert ready.wait(60)
+        from nixl_b200 import _bindings as nb
+        from nixl_b200 import nixl_agent, nixl_agent_config
+
+        agent = nixl_agent("initiator", nixl_agent_config(enable_prog_thread=False, enable_listen_thread=True, listen_port=port_i, backends=["NVLINK"]))
+        src = torch.randint(0, 255, (1 << 20,), dtype=torch.uint8)
+        agent.register_memory(src)
+        agent.fetch_remote_metadata("target", "127.0.0.1", port_t)
+        agent.send_local_metadata("127.0.0.1", port_t)
+        deadline = time.time() + 20
+        while time.time() < deadline and not agent.check_remote_metadata("target"):
+            time.sleep(0.005)
+        assert agent.check_remote_metadata("target")
+        remote = agent.get_xfer_descs([(result["addr"], 1 << 20, 0)], "DRAM")
+        h = agent.initialize_xfer("WRITE", src, remote, "target", b"written")
+        try:
+            state = agent.agent.postXferReq(h)
+        except nb.nixlBackendError:
+            pytest.skip("cross-process memory access (process_vm_writev) is not permitted here")
+        while state != nb.NIXL_SUCCESS:
+            state = agent.agent.getXferStatus(h)
+        proc.join(40)
+        assert result.get("ok") is True
+        assert result["sum"] == int(src.to(torch.int64).sum())
+        got = {}
+        deadline = time.time() + 5
+        while time.time() < deadline and not got:
+            got = agent.get_new_notifs()
+        assert got == {"target": [b"thanks"]}
+        # the target process is gone now: the next post must report it, not hang
+        time.sleep(0.1)
+        with pytest.raises(nb.nixlRemoteDisconnectError):
+            agent.agent.postXferReq(h)
+    finally:
+        if proc.is_alive():
+            proc.terminate()
+        proc.join(5)
