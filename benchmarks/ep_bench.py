@@ -186,12 +186,8 @@ def main():
                 grouped_gemm_fp8(state["rx"], state["sc"], wq, sw, state["h"].expert_offsets[:El].contiguous(), state["h"].recv_count, out=d, status=st)
 
             def fused():
-                # send only; the GEMM waits for arrivals tile by tile
-                if compact:
-                    rx, sc, hh, _, keep = buf._dispatch(x, idx, True, False, 0, 5, False)
-                else:
-                    rx, sc, hh, _, keep = buf._dispatch(x, idx, True, False, world * T, 5, False)
-                grouped_gemm_fp8(rx, sc, wq, sw, hh.expert_offsets[:El].contiguous(), hh.recv_count, out=d, status=st, fused_with=(buf, hh))
+                # dispatch on a side stream with a small grid; the GEMM consumes arrivals tile by tile
+                _, hh, _, _ = buf.dispatch_gemm(x, idx, wq, sw, low_latency=not compact, out=d)
                 state["h"] = hh
 
             def unfused():
@@ -205,7 +201,7 @@ def main():
             rec.update({
                 "gemm_us": round(t_gemm, 1), "gemm_TFLOPs": round(flops / t_gemm / 1e6, 1),
                 "dispatch_then_gemm_us": round(t_unf, 1), "fused_dispatch_gemm_us": round(t_fus, 1),
-                "gemm_status": int(st.item()), "gemm_weight_GB": round(El * args.inter * H / 1e9, 3),
+                "gemm_status": int(st.item()) | int(buf._gemm_status.item()), "gemm_weight_GB": round(El * args.inter * H / 1e9, 3),
             })
             del wq, sw, d
 

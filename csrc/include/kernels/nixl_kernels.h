@@ -157,6 +157,8 @@ int nixl_ep_barrier_launch(const void *peers, int64_t off_flags, int32_t R, int3
  * by that source (see ep_kernels.cu); `counts` is the dispatch's local [ranks][experts_total]
  * count matrix and expert_base the first global expert of this rank.
  * status bits: 1 = an internal wait exceeded its budget, 2 = an arrival flag never came.
+ * To overlap the GEMM with the dispatch that feeds it, launch the dispatch first on another stream
+ * with a small grid and give this kernel at most (SM count - that grid) CTAs.
  */
 typedef struct NixlGroupedGemmParams {
     const void *a;            /* e4m3 [a_rows][K] */
@@ -174,6 +176,12 @@ typedef struct NixlGroupedGemmParams {
     const int32_t *counts;     /* [ranks][experts_total] or NULL */
     uint64_t epoch;
     uint64_t timeout_ns;
+    /* Overlapped mode: with counts_flag set the kernel does not read row_start / row_count (the
+     * dispatch may still be running on another stream); it waits for the count all-gather
+     * itself and derives them: rows_per_expert > 0 selects the expert-major layout
+     * (row_start[g] = g * rows_per_expert), 0 the compact prefix layout. */
+    const uint64_t *counts_flag; /* [ranks] or NULL */
+    int32_t rows_per_expert;
 } NixlGroupedGemmParams;
 
 int nixl_grouped_gemm_fp8_launch(const NixlGroupedGemmParams *params, void *stream);

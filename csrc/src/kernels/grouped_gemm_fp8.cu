@@ -206,12 +206,40 @@ groupedGemmKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
         sh.abort = 0;
         // Tile table: group g owns ceil(count/BM) x n_tiles tiles.
         int run = 0;
-        for (int g = 0; g < p.groups; ++g) {
-            const int c = p.row_count[g];
-            sh.tilePrefix[g] = run;
-            sh.rowStart[g] = p.row_start[g];
-            sh.rowCount[g] = c;
-            run += ((c + BM - 1) / BM) * n_tiles;
+        if (p.counts_flag) {
+            // Overlapped with the dispatch: wait for everybody's counts, then derive the rows.
+            for (int r = 0; r < p.ranks; ++r) {
+                uint64_t t0 = 0;
+                unsigned spins = 0;
+                while (ldAcquireSys(p.counts_flag + r) < p.epoch) {
+                    if ((++spins & 63u) == 0) {
+                        const uint64_t now = nowNs();
+                        if (t0 == 0) t0 = now;
+                        else if (now - t0 > p.timeout_ns) {
+                            atomicOr(p.status, GEMM_ERR_ARRIVAL);
+                            break;
+                        }
+                    }
+                }
+            }
+            int next = 0;
+            for (int g = 0; g < p.groups; ++g) {
+                int c = 0;
+                for (int r = 0; r < p.ranks; ++r) c += p.counts[static_cast<long long>(r) * p.experts_total + p.expert_base + g];
+                sh.tilePrefix[g] = run;
+                sh.rowStart[g] = p.rows_per_expert > 0 ? g * p.rows_per_expert : next;
+                sh.rowCount[g] = c;
+                next += c;
+                run += ((c + BM - 1) / BM) * n_tiles;
+            }
+        } else {
+            for (int g = 0; g < p.groups; ++g) {
+                const int c = p.row_count[g];
+                sh.tilePrefix[g] = run;
+                sh.rowStart[g] = p.row_start[g];
+                sh.rowCount[g] = c;
+                run += ((c + BM - 1) / BM) * n_tiles;
+            }
         }
         sh.tilePrefix[p.groups] = run;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -405,14 +433,14 @@ bool makeMap(CUtensorMap *map, const void *base, uint64_t rows, uint64_t k) {
 } // namespace
 
 extern "C" int nixl_grouped_gemm_fp8_launch(const NixlGroupedGemmParams *params, void *stream) {
-    if (!params || !params->a || !params->w || !params->d || !params->scale_a || !params->scale_w || !params->row_start ||
-        !params->row_count || !params->status)
+    if (!params || !params->a || !params->w || !params->d || !params->scale_a || !params->scale_w || !params->status)
         return cudaErrorInvalidValue;
+    if (!params->counts_flag && (!params->row_start || !params->row_count)) return cudaErrorInvalidValue;
     const NixlGroupedGemmParams &p = *params;
     if (p.groups <= 0 || p.groups > kMaxGroups || p.N <= 0 || p.N % BN || p.K <= 0 || p.K % BK || p.a_rows <= 0)
         return cudaErrorInvalidValue;
     if ((reinterpret_cast<uintptr_t>(p.a) | reinterpret_cast<uintptr_t>(p.w) | reinterpret_cast<uintptr_t>(p.d)) & 15) return cudaErrorInvalidValue;
-    if (p.disp_flag && (!p.counts || p.ranks <= 0)) return cudaErrorInvalidValue;
+    if ((p.disp_flag || p.counts_flag) && (!p.counts || p.ranks <= 0)) return cudaErrorInvalidValue;
     CUtensorMap mapA, mapW;
     if (!makeMap(&mapA, p.a, static_cast<uint64_t>(p.a_rows), static_cast<uint64_t>(p.K)) ||
         !makeMap(&mapW, p.w, static_cast<uint64_t>(p.groups) * p.N, static_cast<uint64_t>(p.K))) {

@@ -24,6 +24,7 @@ class _Params(ctypes.Structure):
         ("grid", ctypes.c_int32), ("ranks", ctypes.c_int32), ("experts_total", ctypes.c_int32), ("expert_base", ctypes.c_int32),
         ("status", ctypes.c_void_p), ("disp_flag", ctypes.c_void_p), ("counts", ctypes.c_void_p),
         ("epoch", ctypes.c_uint64), ("timeout_ns", ctypes.c_uint64),
+        ("counts_flag", ctypes.c_void_p), ("rows_per_expert", ctypes.c_int32),
     ]
 
 
@@ -48,12 +49,17 @@ def grouped_gemm_fp8(
     status: Optional[torch.Tensor] = None,
     fused_with=None,
     grid: int = 0,
+    overlapped: bool = False,
+    rows_per_expert: int = 0,
 ) -> torch.Tensor:
     """``out[rows of g] = dequant(a[rows]) @ dequant(w[g]).T`` in bf16.
 
     ``a``: e4m3 ``[rows, K]``; ``scale_a``: fp32 ``[rows, K/128]``; ``w``: e4m3 ``[G, N, K]``;
     ``scale_w``: fp32 ``[G, N/128, K/128]``; ``row_start`` / ``row_count``: int32 ``[G]`` on the device.
-    ``fused_with``: ``(buffer, handle)`` of the EP dispatch that is filling ``a`` (optional)."""
+    ``fused_with``: ``(buffer, handle)`` of the EP dispatch that is filling ``a`` (optional).
+    ``overlapped``: that dispatch was launched on another stream and may still be running; the
+    kernel then waits for the count exchange itself (``rows_per_expert`` names the layout) and
+    ``grid`` should leave the dispatch's CTAs free (see ``Buffer.dispatch_gemm``)."""
     rows, K = a.shape
     G, N, K2 = w.shape
     if K != K2 or K % 128 or N % 128:
@@ -62,6 +68,8 @@ def grouped_gemm_fp8(
         raise TypeError("a and w must be float8_e4m3fn")
     if scale_a.shape != (rows, K // 128) or scale_w.shape != (G, N // 128, K // 128):
         raise ValueError("scale shapes do not match")
+    if row_start.numel() == G + 1:
+        row_start = row_start[:G]
     for t in (a, scale_a, w, scale_w, row_start, row_count):
         if not t.is_contiguous():
             raise ValueError("inputs must be contiguous")
@@ -86,6 +94,10 @@ def grouped_gemm_fp8(
         p.counts = base + lay.off_counts
         p.ranks, p.experts_total, p.expert_base = buf.num_ranks, buf.num_experts, buf.rank * buf.local_experts
         p.epoch, p.timeout_ns = handle.epoch, buf.timeout_ns
+        if overlapped:
+            # The dispatch runs on another stream right now: the kernel derives the row ranges itself.
+            p.counts_flag = base + lay.off_counts_flag
+            p.rows_per_expert = rows_per_expert
     fn = _lib.lib().nixl_grouped_gemm_fp8_launch
     fn.argtypes = [ctypes.POINTER(_Params), ctypes.c_void_p]
     fn.restype = ctypes.c_int

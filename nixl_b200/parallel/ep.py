@@ -176,6 +176,10 @@ class Buffer:
         self._barrier_epoch = 0
         self._connected: dict[int, str] = {}
         self._disp_cache: dict = {}
+        self._side = None
+        self._sms = 0
+        with torch.cuda.device(self.device):
+            self._gemm_status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._comb_params = _CombineParams()
         lib = _lib.lib()
         self._dispatch_fn = lib.nixl_ep_dispatch_launch
@@ -308,7 +312,36 @@ class Buffer:
         start = self._lay[name] + parity * self._half
         return self.buffer[start : start + nbytes]
 
-    def _dispatch(self, x, topk_idx, use_fp8, round_scale, rows_per_expert, phases_now, hook_later):
+    def dispatch_gemm(self, x: torch.Tensor, topk_idx: torch.Tensor, w: torch.Tensor, scale_w: torch.Tensor,
+                      low_latency: bool = True, out: Optional[torch.Tensor] = None, dispatch_ctas: int = 32):
+        """Dispatch fused with the grouped expert GEMM (fp8, ``w [local_experts, N, hidden]``).
+
+        The dispatch kernel is launched on a side stream with ``dispatch_ctas`` CTAs; the GEMM
+        follows immediately on the current stream with the remaining SMs and consumes rows as
+        their (expert, source) arrival flags come in, so token movement and expert math overlap
+        instead of running back to back.  Returns ``(d [rows, N] bf16, handle, recv_x, scales)``;
+        ``handle.recv_count`` / ``expert_offsets`` are valid once the current stream has caught up."""
+        from ..ops.grouped_gemm import grouped_gemm_fp8
+
+        if self._side is None:
+            self._side = torch.cuda.Stream(device=self.device)
+            self._sms = torch.cuda.get_device_properties(self.device).multi_processor_count
+        cur = torch.cuda.current_stream(self.device)
+        self._side.wait_stream(cur)
+        rpe = self.num_ranks * self.max_tokens if low_latency else 0
+        with torch.cuda.stream(self._side):
+            recv_x, scales, handle, _, keep = self._dispatch(x, topk_idx, True, False, rpe, 5, False, grid=dispatch_ctas)
+        self._keep = keep
+        rows = self.ll_rows if low_latency else self.compact_rows
+        if out is None:
+            out = torch.empty(rows, w.shape[1], dtype=torch.bfloat16, device=self.device)
+        d = grouped_gemm_fp8(recv_x[:rows], scales[:rows], w, scale_w, handle.expert_offsets, handle.recv_count, out=out,
+                             status=self._gemm_status, fused_with=(self, handle), grid=max(1, self._sms - dispatch_ctas),
+                             overlapped=True, rows_per_expert=rpe)
+        cur.wait_stream(self._side)
+        return d, handle, recv_x, scales
+
+    def _dispatch(self, x, topk_idx, use_fp8, round_scale, rows_per_expert, phases_now, hook_later, grid=0):
         if not self._peers_view:
             if self.num_ranks == 1:
                 self.connect_ranks(metadata=[self.local_metadata()])
@@ -357,6 +390,7 @@ class Buffer:
         p.round_scale = int(round_scale)
         p.peers = self._peers_view
         p.epoch = epoch
+        p.grid = grid
         stream_ptr = ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
         fn, ref = self._dispatch_fn, ctypes.byref(p)
 
