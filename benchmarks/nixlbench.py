@@ -85,7 +85,8 @@ def main():
             if world == 1:
                 return [0]
             return [1 - rank] if rank < 2 else []
-        return [r for r in range(world) if r != rank] or [rank]
+        # staggered: rank r starts with r+1, so no receiver is hit by everybody at once
+        return [(rank + 1 + i) % world for i in range(world - 1)] or [rank]
 
     def wait(h):
         while agent.agent.getXferStatus(h) != nb.NIXL_SUCCESS:
