@@ -166,3 +166,26 @@ def test_telemetry_and_cost():
     t = a.get_xfer_telemetry(h)
     assert t.totalBytes == 1 << 24 and t.descCount == 1 and t.xferDuration >= 0
     a.release_xfer_handle(h)
+
+
+@pytest.mark.gpu
+def test_gds_vram_file_roundtrip(tmp_path):
+    """GPU memory -> file -> other GPU buffer through the staged GDS engine (several 8 MiB chunks and a ragged tail)."""
+    a = nixl_agent("gds_gpu", nixl_agent_config(backends=[]))
+    a.create_backend("GDS", {"thread_count": "2"})
+    n = (20 << 20) + 4096 + 24
+    src = torch.randint(0, 255, (n,), dtype=torch.uint8, device="cuda:0")
+    dst = torch.zeros_like(src)
+    a.register_memory(src)
+    a.register_memory(dst)
+    path = str(tmp_path / "kv.bin")
+    a.register_memory([(0, n, 0, "rw,create:" + path)], "FILE")
+    file_descs = a.get_xfer_descs([(0, n, 0)], "FILE")
+    for op, t in (("WRITE", src), ("READ", dst)):
+        h = a.initialize_xfer(op, a.get_xfer_descs(t), file_descs, a.name)
+        st = a.transfer(h)
+        while st == "PROC":
+            st = a.check_xfer_state(h)
+        assert st == "DONE"
+        a.release_xfer_handle(h)
+    assert torch.equal(src, dst)
