@@ -131,9 +131,9 @@ def main():
         logits = torch.randn(T, E, device=dev, generator=gen)
         w, idx = torch.topk(torch.softmax(logits, dim=-1), K, dim=-1)
         idx, w = idx.to(torch.int64).contiguous(), w.float().contiguous()
-        buf = Buffer(rank, world, E, H, T, K, device=dev, timeout_ms=20000)
-        buf.connect_ranks()
         compact = mode != "ll"
+        buf = Buffer(rank, world, E, H, T, K, device=dev, timeout_ms=20000, low_latency_mode=not compact)
+        buf.connect_ranks()
 
         state = {}
 
@@ -150,17 +150,33 @@ def main():
         y = torch.randn(rows_total, H, device=dev, dtype=torch.bfloat16) if rows_total * H * 2 < (8 << 30) else torch.zeros(
             rows_total, H, device=dev, dtype=torch.bfloat16)
 
+        variant = {"v": "default"}
+
         def do_combine():
+            # push: expert ranks store rows into the home rank's landing zone, which then reduces;
+            # pull: home ranks load rows from the expert ranks' exposed output buffer and reduce;
+            # pull_copy: same, but the outputs first have to be copied into that buffer.
+            v = variant["v"]
+            if v == "default":
+                v = "pull" if compact else "push"
+            buf.combine_pull = v != "push"
+            src = buf.get_next_combine_buffer(state["h"]).view(-1, H) if v == "pull" else y
             if compact:
-                state["o"] = buf.combine(y, idx, w, state["h"])
+                state["o"] = buf.combine(src, idx, w, state["h"])
             else:
-                state["o"] = buf.low_latency_combine(y.view(El, -1, H), idx, w, state["h"])[0]
+                state["o"] = buf.low_latency_combine(src.view(El, -1, H), idx, w, state["h"])[0]
 
         def both():
             do_dispatch()
             do_combine()
 
         t_disp = timed(do_dispatch, args.iters, args.warmup, flush, world, dev)
+        per_variant = {}
+        for v in ("push", "pull_copy", "pull"):
+            variant["v"] = v
+            per_variant[f"combine_us_{v}"] = round(timed(do_combine, args.iters, args.warmup, flush, world, dev, pre=do_dispatch), 1)
+            per_variant[f"dispatch_plus_combine_us_{v}"] = round(timed(both, args.iters, args.warmup, flush, world, dev), 1)
+        variant["v"] = "default"
         t_comb = timed(do_combine, args.iters, args.warmup, flush, world, dev, pre=do_dispatch)
         t_both = timed(both, args.iters, args.warmup, flush, world, dev)
         status = buf.status
@@ -171,8 +187,9 @@ def main():
             "bench": "ep", "mode": mode, "n_gpus": world, "tokens_per_gpu": T, "hidden": H, "experts": E, "topk": K,
             "dispatch_us": round(t_disp, 1), "combine_us": round(t_comb, 1), "dispatch_plus_combine_us": round(t_both, 1),
             "recv_rows": recv_rows, "dispatch_GBps_in": round(disp_bytes / t_disp / 1e3, 1), "combine_GBps_out": round(comb_bytes / t_comb / 1e3, 1),
-            "status": status,
+            "status": status, "combine_default": "pull" if compact else "push",
         }
+        rec.update(per_variant)
 
         if not args.skip_gemm:
             wt = torch.randn(El, args.inter, H, device=dev, generator=gen) * 0.02

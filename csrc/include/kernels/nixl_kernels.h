@@ -90,7 +90,8 @@ typedef struct NixlEpLayout {
     int64_t off_recv_scales; /* float  [cap][H/128] (fp8 only) */
     int64_t off_recv_info;   /* uint32 [cap][2] {source rank, token*K + k} */
     int64_t off_comb_x;      /* bf16   [M][K][H] combine landing zone */
-    int64_t off_comb_flag;   /* uint64 [R]      epoch once rank r finished its combine sends */
+    int64_t off_comb_flag;   /* uint64 [R]      epoch once rank r finished its combine sends (push) / its outputs are ready (pull) */
+    int64_t off_comb_in;     /* bf16   [cap][H] expert outputs exposed to peers (pull-mode combine), rows as in recv_x */
 } NixlEpLayout;
 
 typedef struct NixlEpScratch { /* device memory private to the rank; zero before first use */
@@ -120,6 +121,7 @@ typedef struct NixlEpDispatchParams {
     int64_t *layout_range;    /* out [El][R] (first row within expert << 32) | rows */
     int32_t *expert_offsets;  /* out [El+1] first row of each local expert (both layouts) */
     NixlEpScratch scr;
+    int32_t *send_row;        /* out [T][K] (optional) row each (token, k) landed on at its receiver, -1 if not sent */
 } NixlEpDispatchParams;
 
 typedef struct NixlEpCombineParams {
@@ -138,6 +140,11 @@ typedef struct NixlEpCombineParams {
     uint64_t epoch;
     uint64_t timeout_ns;
     NixlEpScratch scr;
+    /* Pull mode: x already lies at lay.off_comb_in of this rank's symmetric buffer; ranks announce
+     * "outputs ready" and every home rank loads its tokens' rows straight from the expert ranks
+     * and reduces them, so no row is written twice.  send_row comes from the dispatch. */
+    int32_t pull;
+    const int32_t *send_row;    /* [T][K] */
 } NixlEpCombineParams;
 
 int nixl_ep_dispatch_launch(const NixlEpDispatchParams *params, void *stream);

@@ -296,6 +296,14 @@ __global__ void __launch_bounds__(kThreads) epDispatchKernel(const __grid_consta
                 int slot = -1;
                 if (e >= 0 && e < p.E && ldVolatile(p.scr.mask + static_cast<int>(e) / El) == 0) slot = atomicAdd(p.scr.fill + e, 1);
                 slots[gtid] = slot;
+                if (p.send_row != nullptr) {
+                    long long row = -1;
+                    if (slot >= 0) {
+                        row = static_cast<long long>(ebase[e]) + before[e] + slot;
+                        if (row >= p.cap) row = -1;
+                    }
+                    p.send_row[static_cast<long long>(t) * p.K + gtid] = static_cast<int>(row);
+                }
             }
             groupBarrier(bar_id, nt);
             for (int k = 0; k < p.K; ++k) {
@@ -361,6 +369,80 @@ __global__ void __launch_bounds__(kThreads) epDispatchKernel(const __grid_consta
 
 // ------------------------------------------------------------------ combine
 
+// Pull-mode combine: announce that this rank's expert outputs are complete, wait for the same
+// word from every peer, then each token's home rank loads the K rows from where dispatch put
+// them and reduces in fp32.  Every row crosses NVLink once and is never staged.
+__device__ __forceinline__ void epCombinePull(const NixlEpCombineParams &p) {
+    const int El = p.E / p.R;
+    const int tid = threadIdx.x;
+    char *self = peerBase(p.peers, p.rank);
+    const int vecs = p.H / 8;
+    if ((p.phases & 1) && blockIdx.x == 0 && tid < p.R) {
+        char *peer = peerBase(p.peers, tid);
+        if (peer != nullptr && ldVolatile(p.scr.mask + tid) == 0) {
+            __threadfence_system();
+            stReleaseSys(reinterpret_cast<uint64_t *>(peer + p.lay.off_comb_flag) + p.rank, p.epoch);
+        }
+    }
+    if (!(p.phases & 2)) return;
+    const uint64_t *flag = reinterpret_cast<const uint64_t *>(self + p.lay.off_comb_flag);
+    if (tid < p.R && ldVolatile(p.scr.mask + tid) == 0 && peerBase(p.peers, tid) != nullptr) {
+        if (!waitFlag(flag + tid, p.epoch, p.timeout_ns)) {
+            atomicExch(p.scr.mask + tid, 1);
+            atomicOr(p.scr.status, ST_PEER_TIMEOUT);
+        }
+    }
+    __syncthreads();
+    __nv_bfloat16 *out = static_cast<__nv_bfloat16 *>(p.out);
+    const int nt = threadsPerItem(p.T);
+    const int groups_per_cta = kThreads / nt;
+    const int grp = tid / nt, gtid = tid - grp * nt;
+    for (int t = blockIdx.x * groups_per_cta + grp; t < p.T; t += gridDim.x * groups_per_cta) {
+        float w[kMaxTopk];
+        const uint4 *src[kMaxTopk];
+#pragma unroll
+        for (int k = 0; k < kMaxTopk; ++k) {
+            w[k] = __int_as_float(0x7fc00000); // NaN marks "skip" (a real weight may be 0)
+            src[k] = nullptr;
+            if (k < p.K) {
+                const long long e = p.topk_idx[static_cast<long long>(t) * p.K + k];
+                const int row = p.send_row[static_cast<long long>(t) * p.K + k];
+                if (e >= 0 && e < p.E && row >= 0) {
+                    const int r = static_cast<int>(e) / El;
+                    char *peer = peerBase(p.peers, r);
+                    if (peer != nullptr && ldVolatile(p.scr.mask + r) == 0) {
+                        w[k] = p.topk_weights[static_cast<long long>(t) * p.K + k];
+                        src[k] = reinterpret_cast<const uint4 *>(peer + p.lay.off_comb_in + static_cast<long long>(row) * p.H * 2);
+                    }
+                }
+            }
+        }
+        for (int v = gtid; v < vecs; v += nt) {
+            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            uint4 raw[kMaxTopk];
+#pragma unroll
+            for (int k = 0; k < kMaxTopk; ++k)
+                if (k < p.K && w[k] == w[k]) raw[k] = ldNc(src[k] + v);
+#pragma unroll
+            for (int k = 0; k < kMaxTopk; ++k) {
+                if (k >= p.K || w[k] != w[k]) continue;
+                const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&raw[k]);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float2 f = __bfloat1622float2(h[i]);
+                    acc[2 * i] = fmaf(w[k], f.x, acc[2 * i]);
+                    acc[2 * i + 1] = fmaf(w[k], f.y, acc[2 * i + 1]);
+                }
+            }
+            uint4 o;
+            __nv_bfloat162 *oh = reinterpret_cast<__nv_bfloat162 *>(&o);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) oh[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+            *reinterpret_cast<uint4 *>(out + static_cast<long long>(t) * p.H + v * 8) = o;
+        }
+    }
+}
+
 __global__ void __launch_bounds__(kThreads) epCombineKernel(const __grid_constant__ NixlEpCombineParams p) {
     __shared__ int offs[kMaxRanks * 8 + 1]; // expert_offsets copy (El + 1 <= 513)
     __shared__ int cnts[kMaxRanks * 8];
@@ -368,6 +450,11 @@ __global__ void __launch_bounds__(kThreads) epCombineKernel(const __grid_constan
     const int tid = threadIdx.x;
     char *self = peerBase(p.peers, p.rank);
     const int vecs = p.H / 8;
+
+    if (p.pull) {
+        epCombinePull(p);
+        return;
+    }
 
     if (p.phases & 1) {
         for (int i = tid; i <= El; i += kThreads) offs[i] = p.expert_offsets[i];
@@ -527,6 +614,7 @@ extern "C" int nixl_ep_dispatch_launch(const NixlEpDispatchParams *params, void 
 extern "C" int nixl_ep_combine_launch(const NixlEpCombineParams *params, void *stream) {
     if (!params || !params->peers || !params->topk_idx) return cudaErrorInvalidValue;
     const NixlEpCombineParams &p = *params;
+    if (p.pull && !p.send_row) return cudaErrorInvalidValue;
     if (p.R <= 0 || p.R > kMaxRanks || p.E <= 0 || p.E % p.R || p.K <= 0 || p.K > kMaxTopk || p.H <= 0 || p.H % 8 ||
         p.E / p.R > kMaxRanks * 8 || p.rank < 0 || p.rank >= p.R)
         return cudaErrorInvalidValue;

@@ -40,7 +40,7 @@ def _up(x: int, a: int = _ALIGN) -> int:
 
 class _Layout(ctypes.Structure):
     _fields_ = [(n, ctypes.c_int64) for n in (
-        "off_counts", "off_counts_flag", "off_disp_flag", "off_recv_x", "off_recv_scales", "off_recv_info", "off_comb_x", "off_comb_flag")]
+        "off_counts", "off_counts_flag", "off_disp_flag", "off_recv_x", "off_recv_scales", "off_recv_info", "off_comb_x", "off_comb_flag", "off_comb_in")]
 
 
 class _Scratch(ctypes.Structure):
@@ -55,6 +55,7 @@ class _DispatchParams(ctypes.Structure):
         ("phases", ctypes.c_int32), ("grid", ctypes.c_int32),
         ("peers", ctypes.c_void_p), ("lay", _Layout), ("epoch", ctypes.c_uint64), ("timeout_ns", ctypes.c_uint64),
         ("recv_count", ctypes.c_void_p), ("layout_range", ctypes.c_void_p), ("expert_offsets", ctypes.c_void_p), ("scr", _Scratch),
+        ("send_row", ctypes.c_void_p),
     ]
 
 
@@ -65,6 +66,7 @@ class _CombineParams(ctypes.Structure):
         ("T", ctypes.c_int32), ("K", ctypes.c_int32), ("H", ctypes.c_int32), ("E", ctypes.c_int32), ("R", ctypes.c_int32), ("rank", ctypes.c_int32),
         ("phases", ctypes.c_int32), ("grid", ctypes.c_int32),
         ("peers", ctypes.c_void_p), ("lay", _Layout), ("epoch", ctypes.c_uint64), ("timeout_ns", ctypes.c_uint64), ("scr", _Scratch),
+        ("pull", ctypes.c_int32), ("send_row", ctypes.c_void_p),
     ]
 
 
@@ -81,6 +83,8 @@ class EPHandle:
     num_max_tokens: int
     hidden: int
     topk: int
+    send_row: Optional[torch.Tensor] = None  # int32 [tokens, topk]: row each copy landed on at its receiver
+    rows_per_expert: int = 0
 
 
 class EventOverlap:
@@ -109,6 +113,12 @@ class Buffer:
         timeout_ms: bound of every in-kernel wait on a peer.
         compact_rows: capacity of the throughput-mode layout; default worst case
             ``num_ranks * tokens * min(topk, local_experts)``.
+        low_latency_mode: also size the buffer for the low-latency layout
+            (``local_experts * num_ranks * tokens`` rows); pass False for a throughput-only buffer.
+        combine_pull: combine by letting each token's home rank load its expert outputs straight
+            from the expert ranks (every row crosses NVLink once) instead of having the expert
+            ranks store them into a landing zone first.  ``None`` picks pull for the throughput
+            layout and push for the low-latency one.  All ranks must use the same setting.
     """
 
     def __init__(
@@ -126,6 +136,7 @@ class Buffer:
         compact_rows: Optional[int] = None,
         low_latency_mode: bool = True,
         explicitly_destroy: bool = False,
+        combine_pull: Optional[bool] = None,
     ):
         from .. import nixl_agent, nixl_agent_config
 
@@ -144,7 +155,9 @@ class Buffer:
         R, E, El, H, M, K = num_ranks, num_experts, self.local_experts, hidden, self.max_tokens, num_topk
         self.ll_rows = El * R * M
         self.compact_rows = compact_rows if compact_rows is not None else R * M * min(K, El)
-        cap = max(self.ll_rows, self.compact_rows)
+        self.low_latency_mode = low_latency_mode
+        self.combine_pull = combine_pull
+        cap = max(self.ll_rows, self.compact_rows) if low_latency_mode else self.compact_rows
         self.cap = cap
         # one parity half
         off, lay = 0, {}
@@ -157,6 +170,7 @@ class Buffer:
             ("off_recv_scales", cap * (H // 128) * 4),
             ("off_recv_x", cap * H * 2),
             ("off_comb_x", M * K * H * 2),
+            ("off_comb_in", cap * H * 2),
         ):
             lay[name] = off
             off = _up(off + size)
@@ -200,7 +214,7 @@ class Buffer:
         """Bytes of symmetric buffer a rank allocates for these shapes (both parity halves)."""
         El = num_experts // num_ranks
         rows = El * num_ranks * num_max_dispatch_tokens_per_rank
-        half = rows * (hidden * 2 + (hidden // 128) * 4 + 8) + num_max_dispatch_tokens_per_rank * num_topk * hidden * 2
+        half = rows * (hidden * 4 + (hidden // 128) * 4 + 8) + num_max_dispatch_tokens_per_rank * num_topk * hidden * 2
         return 2 * half + (1 << 20)
 
     # ------------------------------------------------------------------ connection management
@@ -349,6 +363,8 @@ class Buffer:
                 raise RuntimeError("connect_ranks() must run before dispatch")
         T, H = x.shape
         K = topk_idx.shape[1]
+        if rows_per_expert and not self.low_latency_mode:
+            raise ValueError("buffer was created with low_latency_mode=False")
         if H != self.hidden or K != self.topk or T > self.max_tokens:
             raise ValueError("dispatch shapes exceed what the buffer was sized for")
         if x.dtype != torch.bfloat16 or topk_idx.dtype != torch.int64 or not x.is_contiguous() or not topk_idx.is_contiguous():
@@ -365,6 +381,7 @@ class Buffer:
                 recv_count = torch.empty(El, dtype=torch.int32, device=self.device)
                 layout_range = torch.empty(El, R, dtype=torch.int64, device=self.device)
                 expert_offsets = torch.empty(El + 1, dtype=torch.int32, device=self.device)
+                send_row = torch.empty(self.max_tokens, K, dtype=torch.int32, device=self.device)
             p = _DispatchParams()
             p.K, p.H, p.E, p.R, p.rank = K, H, self.num_experts, R, self.rank
             p.use_fp8 = int(use_fp8)
@@ -375,6 +392,7 @@ class Buffer:
             p.timeout_ns = self.timeout_ns
             p.recv_count, p.layout_range, p.expert_offsets = recv_count.data_ptr(), layout_range.data_ptr(), expert_offsets.data_ptr()
             p.scr = self._scratch()
+            p.send_row = send_row.data_ptr()
             rows = p.cap
             row_bytes = H if use_fp8 else 2 * H
             raw = self._region(parity, "off_recv_x", rows * row_bytes)
@@ -383,9 +401,10 @@ class Buffer:
             if use_fp8:
                 scales = self._region(parity, "off_recv_scales", rows * (H // 128) * 4).view(torch.float32).view(rows, H // 128)
             src_info = self._region(parity, "off_recv_info", rows * 8).view(torch.int32).view(rows, 2)
-            slot = (p, recv_count, layout_range, expert_offsets, recv_x, scales, src_info)
+            slot = (p, recv_count, layout_range, expert_offsets, recv_x, scales, src_info, send_row)
             self._disp_cache[key] = slot
-        p, recv_count, layout_range, expert_offsets, recv_x, scales, src_info = slot
+        p, recv_count, layout_range, expert_offsets, recv_x, scales, src_info, send_row = slot
+
         p.x, p.topk_idx, p.T = x.data_ptr(), topk_idx.data_ptr(), T
         p.round_scale = int(round_scale)
         p.peers = self._peers_view
@@ -401,7 +420,7 @@ class Buffer:
 
         launch(phases_now)
         hook = (lambda: launch(2)) if hook_later else None
-        handle = EPHandle(parity, epoch, recv_count, expert_offsets, layout_range, src_info, self.max_tokens, H, K)
+        handle = EPHandle(parity, epoch, recv_count, expert_offsets, layout_range, src_info, self.max_tokens, H, K, send_row[:T], rows_per_expert)
         keep = (x, topk_idx, p)  # the hook may launch later: keep inputs alive
         return recv_x, scales, handle, hook, keep
 
@@ -453,11 +472,15 @@ class Buffer:
         out: Optional[torch.Tensor] = None,
     ):
         """Send expert outputs ``x [local_experts, ranks * max_tokens, hidden]`` (bf16) back and
-        reduce ``sum_k w[t,k] * y[t,k]``.  Returns ``(combined_x [tokens, hidden], event, hook)``."""
+        reduce ``sum_k w[t,k] * y[t,k]``.  Returns ``(combined_x [tokens, hidden], event, hook)``.
+
+        ``zero_copy=True`` (on every rank) says ``x`` was written into ``get_next_combine_buffer(handle)``:
+        the home ranks then load the rows directly from there."""
         if use_logfmt:
             raise NotImplementedError("LogFMT compression is not implemented")
         flat = x.reshape(-1, self.hidden)
-        out, hook = self._combine(flat, topk_idx, topk_weights, handle, 1 if return_recv_hook else 3, return_recv_hook, out)
+        out, hook = self._combine(flat, topk_idx, topk_weights, handle, 1 if return_recv_hook else 3, return_recv_hook, out,
+                                  pull=True if zero_copy else None)
         return out, EventOverlap(self._record() if async_finish else None), hook
 
     # ------------------------------------------------------------------ throughput mode
@@ -476,7 +499,7 @@ class Buffer:
         out, _ = self._combine(x, topk_idx, topk_weights, handle, 3, False, out)
         return out
 
-    def _combine(self, x, topk_idx, topk_weights, handle, phases_now, hook_later, out):
+    def _combine(self, x, topk_idx, topk_weights, handle, phases_now, hook_later, out, pull=None):
         if x.dtype != torch.bfloat16 or not x.is_contiguous():
             raise TypeError("combine input must be contiguous bf16")
         if topk_weights.dtype != torch.float32 or not topk_weights.is_contiguous():
@@ -485,7 +508,18 @@ class Buffer:
         with torch.cuda.device(self.device):
             if out is None:
                 out = torch.empty(T, self.hidden, dtype=torch.bfloat16, device=self.device)
+        if pull is None:
+            pull = self.combine_pull if self.combine_pull is not None else handle.rows_per_expert == 0
+        if pull:
+            rows = self.ll_rows if handle.rows_per_expert else self.compact_rows
+            if x.shape[0] > rows:
+                raise ValueError("combine input has more rows than the buffer holds")
+            staged = self._region(handle.parity, "off_comb_in", rows * self.hidden * 2).view(torch.bfloat16).view(rows, self.hidden)
+            if x.data_ptr() != staged.data_ptr():
+                staged[: x.shape[0]].copy_(x)  # callers that write into get_next_combine_buffer() skip this copy
         p = self._comb_params
+        p.pull = int(pull)
+        p.send_row = handle.send_row.data_ptr() if pull else None
         p.x = x.data_ptr()
         p.recv_info = handle.src_info.data_ptr()
         p.recv_count, p.expert_offsets = handle.recv_count.data_ptr(), handle.expert_offsets.data_ptr()
@@ -507,6 +541,16 @@ class Buffer:
         launch(phases_now)
         self._keep_c = (x, topk_idx, topk_weights, out, p)
         return out, ((lambda: launch(2)) if hook_later else None)
+
+    def get_next_combine_buffer(self, handle: EPHandle) -> torch.Tensor:
+        """The symmetric region pull-mode combine reads from, shaped like the dispatch result
+        (``[local_experts, ranks * max_tokens, hidden]`` for the low-latency layout, ``[rows, hidden]``
+        for the compact one).  An expert GEMM that writes its output here makes combine copy-free."""
+        rows = self.ll_rows if handle.rows_per_expert else self.compact_rows
+        flat = self._region(handle.parity, "off_comb_in", rows * self.hidden * 2).view(torch.bfloat16).view(rows, self.hidden)
+        if handle.rows_per_expert:
+            return flat.view(self.local_experts, handle.rows_per_expert, self.hidden)
+        return flat
 
     # ------------------------------------------------------------------ misc
 

@@ -12,7 +12,7 @@ from nixl_b200.parallel import Buffer, dequant_fp8, per_token_cast_to_fp8
 pytestmark = pytest.mark.gpu
 
 
-def _make_ranks(n, experts, hidden, tokens, topk, timeout_ms=20000, tag="ep"):
+def _make_ranks(n, experts, hidden, tokens, topk, timeout_ms=20000, tag="ep", **kw):
     from nixl_b200 import nixl_agent, nixl_agent_config
 
     bufs = []
@@ -20,7 +20,7 @@ def _make_ranks(n, experts, hidden, tokens, topk, timeout_ms=20000, tag="ep"):
         dev = torch.device("cuda", r % torch.cuda.device_count())
         agent = nixl_agent(f"{tag}_rank{r}", nixl_agent_config(enable_prog_thread=False, backends=["NVLINK"]))
         with torch.cuda.device(dev):
-            bufs.append(Buffer(r, n, experts, hidden, tokens, topk, device=dev, agent=agent, timeout_ms=timeout_ms))
+            bufs.append(Buffer(r, n, experts, hidden, tokens, topk, device=dev, agent=agent, timeout_ms=timeout_ms, **kw))
     md = [b.local_metadata() for b in bufs]
     for b in bufs:
         b.connect_ranks(metadata=md)
@@ -81,7 +81,7 @@ def _check_dispatch(bufs, xs, idxs, results, use_fp8, compact):
                 assert all(int(info[start + first + j, 0]) == r for j in range(rows))
 
 
-def _run(bufs, tokens, hidden, experts, topk, use_fp8, compact):
+def _run(bufs, tokens, hidden, experts, topk, use_fp8, compact, zero_copy=False):
     xs, idxs, ws = _inputs(bufs, tokens, hidden, experts, topk)
     results = []
     for b, x, idx in zip(bufs, xs, idxs):  # launch every rank before waiting on any
@@ -103,7 +103,11 @@ def _run(bufs, tokens, hidden, experts, topk, use_fp8, compact):
     for d, b in enumerate(bufs):
         recv_x, scales, handle = results[d]
         with torch.cuda.device(b.device):
-            y = torch.zeros(recv_x.shape[0], hidden, dtype=torch.bfloat16, device=b.device)
+            if zero_copy:  # the "expert" writes straight into the region peers will read
+                y = b.get_next_combine_buffer(handle).view(-1, hidden)
+                y.zero_()
+            else:
+                y = torch.zeros(recv_x.shape[0], hidden, dtype=torch.bfloat16, device=b.device)
             offs, cnts = handle.expert_offsets.cpu(), handle.recv_count.cpu()
             for le in range(b.local_experts):
                 s, c = int(offs[le]), int(cnts[le])
@@ -115,7 +119,7 @@ def _run(bufs, tokens, hidden, experts, topk, use_fp8, compact):
                 outs.append(b.combine(y, idxs[d], ws[d], handle))
             else:
                 El, rows = b.local_experts, b.num_ranks * b.max_tokens
-                outs.append(b.low_latency_combine(y.view(El, rows, hidden), idxs[d], ws[d], handle)[0])
+                outs.append(b.low_latency_combine(y.view(El, rows, hidden), idxs[d], ws[d], handle, zero_copy=zero_copy)[0])
     for b in bufs:
         torch.cuda.synchronize(b.device)
         assert b.status == 0
@@ -155,6 +159,33 @@ def test_multi_rank(use_fp8, compact):
         torch.cuda.synchronize(b.device)
         assert b.status == 0
         b.destroy()
+
+
+@pytest.mark.parametrize("compact,pull,zero_copy", [(True, False, False), (True, True, True), (False, True, False), (False, None, True)])
+def test_combine_push_pull_and_zero_copy(compact, pull, zero_copy):
+    """Both combine algorithms on both layouts, with and without the caller writing into the exposed buffer."""
+    n = min(torch.cuda.device_count(), 8)
+    bufs = _make_ranks(n, 8 * n, 1024, 40, 4, tag=f"epc_{int(compact)}{pull}{int(zero_copy)}", combine_pull=pull)
+    for _ in range(3):
+        _run(bufs, 40, 1024, 8 * n, 4, True, compact, zero_copy=zero_copy)
+    for b in bufs:
+        torch.cuda.synchronize(b.device)
+        assert b.status == 0
+        b.destroy()
+
+
+def test_throughput_only_buffer_is_smaller_and_rejects_low_latency_calls():
+    dev = torch.device("cuda", 0)
+    small = Buffer(0, 1, 8, 1024, 64, 2, device=dev, low_latency_mode=False)
+    big = Buffer(0, 1, 8, 1024, 64, 2, device=dev, agent=small.agent)
+    assert small.buffer.numel() < big.buffer.numel()
+    x = torch.randn(64, 1024, device=dev, dtype=torch.bfloat16)
+    idx = torch.randint(0, 8, (64, 2), device=dev)
+    with pytest.raises(ValueError):
+        small.low_latency_dispatch(x, idx)
+    rx, sc, h = small.dispatch(x, idx)
+    torch.cuda.synchronize()
+    assert int(h.recv_count.sum()) == 128 and small.status == 0
 
 
 def test_silent_rank_is_masked_not_waited_for():
