@@ -157,8 +157,8 @@ def main():
             # pull: home ranks load rows from the expert ranks' exposed output buffer and reduce;
             # pull_copy: same, but the outputs first have to be copied into that buffer.
             v = variant["v"]
-            if v == "default":
-                v = "pull" if compact else "push"
+            if v == "default":  # what a pipeline does: the expert GEMM writes into the exposed buffer
+                v = "pull"
             buf.combine_pull = v != "push"
             src = buf.get_next_combine_buffer(state["h"]).view(-1, H) if v == "pull" else y
             if compact:
@@ -187,7 +187,7 @@ def main():
             "bench": "ep", "mode": mode, "n_gpus": world, "tokens_per_gpu": T, "hidden": H, "experts": E, "topk": K,
             "dispatch_us": round(t_disp, 1), "combine_us": round(t_comb, 1), "dispatch_plus_combine_us": round(t_both, 1),
             "recv_rows": recv_rows, "dispatch_GBps_in": round(disp_bytes / t_disp / 1e3, 1), "combine_GBps_out": round(comb_bytes / t_comb / 1e3, 1),
-            "status": status, "combine_default": "pull" if compact else "push",
+            "status": status, "combine_default": "pull",
         }
         rec.update(per_variant)
 

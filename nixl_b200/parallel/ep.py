@@ -117,8 +117,9 @@ class Buffer:
             (``local_experts * num_ranks * tokens`` rows); pass False for a throughput-only buffer.
         combine_pull: combine by letting each token's home rank load its expert outputs straight
             from the expert ranks (every row crosses NVLink once) instead of having the expert
-            ranks store them into a landing zone first.  ``None`` picks pull for the throughput
-            layout and push for the low-latency one.  All ranks must use the same setting.
+            ranks store them into a landing zone first.  ``None`` picks pull when the combine input
+            was written into ``get_next_combine_buffer()`` and push otherwise.  All ranks must make
+            the same choice in a given call.
     """
 
     def __init__(
@@ -508,13 +509,15 @@ class Buffer:
         with torch.cuda.device(self.device):
             if out is None:
                 out = torch.empty(T, self.hidden, dtype=torch.bfloat16, device=self.device)
+        rows = self.ll_rows if handle.rows_per_expert else self.compact_rows
+        staged = self._region(handle.parity, "off_comb_in", rows * self.hidden * 2).view(torch.bfloat16).view(rows, self.hidden)
         if pull is None:
-            pull = self.combine_pull if self.combine_pull is not None else handle.rows_per_expert == 0
+            # Unless told otherwise: pull when the caller wrote its outputs into the exposed buffer
+            # (nothing to copy), push when they live elsewhere (staging them first costs more than it saves).
+            pull = self.combine_pull if self.combine_pull is not None else x.data_ptr() == staged.data_ptr()
         if pull:
-            rows = self.ll_rows if handle.rows_per_expert else self.compact_rows
             if x.shape[0] > rows:
                 raise ValueError("combine input has more rows than the buffer holds")
-            staged = self._region(handle.parity, "off_comb_in", rows * self.hidden * 2).view(torch.bfloat16).view(rows, self.hidden)
             if x.data_ptr() != staged.data_ptr():
                 staged[: x.shape[0]].copy_(x)  # callers that write into get_next_combine_buffer() skip this copy
         p = self._comb_params
