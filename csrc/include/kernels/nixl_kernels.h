@@ -189,6 +189,7 @@ typedef struct NixlGroupedGemmParams {
      * (row_start[g] = g * rows_per_expert), 0 the compact prefix layout. */
     const uint64_t *counts_flag; /* [ranks] or NULL */
     int32_t rows_per_expert;
+    int32_t tile_mode;           /* 0: choose; 1: 128 x 128 tiles, one CTA each; 2: 256 x 256 tiles, one CTA pair each (N % 256 == 0) */
 } NixlGroupedGemmParams;
 
 int nixl_grouped_gemm_fp8_launch(const NixlGroupedGemmParams *params, void *stream);

@@ -31,8 +31,12 @@
 #include <mutex>
 
 #include "kernels/nixl_kernels.h"
+#include "kernels/grouped_gemm_internal.h"
+#include "kernels/tcgen05_ptx.cuh"
 
 namespace {
+
+using namespace nixl_tc;
 
 constexpr int BM = 128, BN = 128, BK = 128; // tile; BK is also the scale granularity
 constexpr int UMMA_K = 32;                  // fp8: 32 bytes of K per instruction
@@ -42,10 +46,10 @@ constexpr int kTileBytes = BM * BK;         // 16 KiB (fp8)
 constexpr int kStageBytes = 2 * kTileBytes; // A + W
 constexpr int kAccBufs = 4;                 // TMEM accumulators in flight (4 x 128 columns = all of TMEM)
 constexpr int kTmemCols = kAccBufs * BN;
-constexpr int kMaxGroups = 512;
-constexpr uint64_t kWaitNs = 4000000000ull; // any single wait longer than 4 s aborts the kernel
 
-enum : int { GEMM_ERR_TIMEOUT = 1, GEMM_ERR_ARRIVAL = 2 };
+using nixl_gemm::GEMM_ERR_ARRIVAL;
+using nixl_gemm::GEMM_ERR_TIMEOUT;
+using nixl_gemm::kMaxGroups;
 
 struct Shared {
     uint64_t full[kStages];
@@ -59,113 +63,10 @@ struct Shared {
     int rowCount[kMaxGroups];
 };
 
-// ------------------------------------------------------------------ PTX wrappers
-
-__device__ __forceinline__ uint32_t smemU32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
-__device__ __forceinline__ uint64_t nowNs() {
-    uint64_t t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
-__device__ __forceinline__ void mbarInit(uint64_t *b, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smemU32(b)), "r"(count));
-}
-__device__ __forceinline__ void mbarExpectTx(uint64_t *b, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smemU32(b)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbarArrive(uint64_t *b) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smemU32(b)) : "memory");
-}
-__device__ __forceinline__ bool mbarTry(uint64_t *b, uint32_t parity) {
-    uint32_t ok;
-    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
-                 : "=r"(ok)
-                 : "r"(smemU32(b)), "r"(parity)
-                 : "memory");
-    return ok != 0;
-}
-// Bounded wait; false when the budget ran out or another role aborted.
-__device__ __forceinline__ bool mbarWait(uint64_t *b, uint32_t parity, volatile int *abort_flag) {
-    uint64_t t0 = 0;
-    unsigned spins = 0;
-    while (!mbarTry(b, parity)) {
-        if ((++spins & 127u) == 0) {
-            if (*abort_flag) return false;
-            const uint64_t now = nowNs();
-            if (t0 == 0) t0 = now;
-            else if (now - t0 > kWaitNs) {
-                *abort_flag = 1;
-                return false;
-            }
-        }
-    }
-    return true;
-}
-__device__ __forceinline__ void tmaLoad2d(void *smem_dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
-                     smemU32(smem_dst)),
-                 "l"(map), "r"(smemU32(bar)), "r"(x), "r"(y)
-                 : "memory");
-}
-__device__ __forceinline__ void tcFenceBefore() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tcFenceAfter() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tcCommit(uint64_t *bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smemU32(bar)) : "memory");
-}
-__device__ __forceinline__ void tcMma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-                 " tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}" ::"r"(tmem_d),
-                 "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u)
-                 : "memory");
-}
-// 32 lanes x 32 consecutive fp32 columns -> 32 registers per thread (thread = lane = row).
-__device__ __forceinline__ void tmemLoad32(uint32_t addr, float (&v)[32]) {
-    uint32_t *r = reinterpret_cast<uint32_t *>(v);
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
-                   "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
-                   "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
-                   "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-                 : "r"(addr));
-}
-// Waits for outstanding TMEM loads.  The registers are listed as read-write operands so that no
-// use of them can be scheduled above the wait (the load instruction returns before its data).
-__device__ __forceinline__ void tmemLoadWait(float (&v)[32]) {
-    uint32_t *r = reinterpret_cast<uint32_t *>(v);
-    asm volatile("tcgen05.wait::ld.sync.aligned;"
-                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]), "+r"(r[9]),
-                   "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]),
-                   "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]),
-                   "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
-                 :
-                 : "memory");
-}
-
-// Shared-memory matrix descriptor for a K-major tile of 128-byte rows written by TMA with the
-// 128-byte swizzle: 8-row groups are 1024 bytes apart (stride byte offset), the leading offset
-// is unused for this layout, descriptor version 1 (sm_100), layout type 2 = SWIZZLE_128B.
-__device__ __forceinline__ uint64_t smemDesc(uint32_t smem_addr) {
-    uint64_t d = 0;
-    d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);       // start address, bits [0,14)
-    d |= static_cast<uint64_t>(1) << 16;                           // leading byte offset (ignored), bits [16,30)
-    d |= static_cast<uint64_t>(1024 >> 4) << 32;                   // stride byte offset, bits [32,46)
-    d |= static_cast<uint64_t>(1) << 46;                           // version, bits [46,48)
-    d |= static_cast<uint64_t>(2) << 61;                           // layout type, bits [61,64)
-    return d;
-}
-
 // Instruction descriptor: D fp32, A and B e4m3, both K-major, M = 128, N = 128.
 __device__ __forceinline__ constexpr uint32_t instrDesc() {
     return (1u << 4) | (0u << 7) | (0u << 10) | (0u << 15) | (0u << 16) | (static_cast<uint32_t>(BN >> 3) << 17) |
         (static_cast<uint32_t>(BM >> 4) << 24);
-}
-
-__device__ __forceinline__ uint64_t ldAcquireSys(const uint64_t *p) {
-    uint64_t v;
-    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
-    return v;
 }
 
 struct Tile {
@@ -338,22 +239,28 @@ groupedGemmKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
 #pragma unroll
             for (int i = 0; i < HN; ++i) acc[i] = 0.f;
             bool ok = true;
-            // The combined scale of a step is needed by every FMA of that step, so its two loads
-            // must not sit on the critical path: a register ring keeps them kPrefetch steps ahead.
+            // The scales of a step are needed by every FMA of that step, so their loads must not sit on
+            // the critical path: a register ring keeps them kPrefetch steps ahead.  They are kept as
+            // loaded; multiplying them right away would make the warp wait for the loads it just issued.
             constexpr int kPrefetch = 4;
-            float sring[kPrefetch];
+            float ring_a[kPrefetch], ring_w[kPrefetch];
 #pragma unroll
-            for (int j = 0; j < kPrefetch; ++j)
-                sring[j] = j < k_steps ? (valid ? __ldg(sa_row + j) : 0.f) * __ldg(sw + j) : 0.f;
+            for (int j = 0; j < kPrefetch; ++j) {
+                ring_a[j] = (j < k_steps && valid) ? __ldg(sa_row + j) : 0.f;
+                ring_w[j] = j < k_steps ? __ldg(sw + j) : 0.f;
+            }
             for (int ks0 = 0; ks0 < k_steps && ok; ks0 += kPrefetch) {
 #pragma unroll
                 for (int j = 0; j < kPrefetch; ++j) {
                     const int ks = ks0 + j;
                     if (ks >= k_steps) break;
                     const int buf = it % kAccBufs;
-                    const float s = sring[j];
+                    const float s = ring_a[j] * ring_w[j];
                     const int nxt = ks + kPrefetch;
-                    if (nxt < k_steps) sring[j] = (valid ? __ldg(sa_row + nxt) : 0.f) * __ldg(sw + nxt);
+                    if (nxt < k_steps) {
+                        ring_a[j] = valid ? __ldg(sa_row + nxt) : 0.f;
+                        ring_w[j] = __ldg(sw + nxt);
+                    }
                     if (!mbarWait(&sh.tmemFull[buf], (it / kAccBufs) & 1, abort_flag)) {
                         ok = false;
                         break;
@@ -418,19 +325,18 @@ EncodeFn encoder() {
     return fn;
 }
 
-// 2-D map over a row-major [rows, k] byte matrix, 128 x 128 boxes, 128-byte swizzle.
-bool makeMap(CUtensorMap *map, const void *base, uint64_t rows, uint64_t k) {
+} // namespace
+
+bool nixl_gemm::makeTileMap(CUtensorMap *map, const void *base, uint64_t rows, uint64_t k, uint32_t box_rows) {
     EncodeFn fn = encoder();
     if (!fn) return false;
     const cuuint64_t dims[2] = {k, rows};
     const cuuint64_t strides[1] = {k};
-    const cuuint32_t box[2] = {BK, BM};
+    const cuuint32_t box[2] = {BK, box_rows};
     const cuuint32_t elem[2] = {1, 1};
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
-
-} // namespace
 
 extern "C" int nixl_grouped_gemm_fp8_launch(const NixlGroupedGemmParams *params, void *stream) {
     if (!params || !params->a || !params->w || !params->d || !params->scale_a || !params->scale_w || !params->status)
@@ -442,10 +348,21 @@ extern "C" int nixl_grouped_gemm_fp8_launch(const NixlGroupedGemmParams *params,
     if ((reinterpret_cast<uintptr_t>(p.a) | reinterpret_cast<uintptr_t>(p.w) | reinterpret_cast<uintptr_t>(p.d)) & 15) return cudaErrorInvalidValue;
     if ((p.disp_flag || p.counts_flag) && (!p.counts || p.ranks <= 0)) return cudaErrorInvalidValue;
     CUtensorMap mapA, mapW;
-    if (!makeMap(&mapA, p.a, static_cast<uint64_t>(p.a_rows), static_cast<uint64_t>(p.K)) ||
-        !makeMap(&mapW, p.w, static_cast<uint64_t>(p.groups) * p.N, static_cast<uint64_t>(p.K))) {
+    if (!nixl_gemm::makeTileMap(&mapA, p.a, static_cast<uint64_t>(p.a_rows), static_cast<uint64_t>(p.K)) ||
+        !nixl_gemm::makeTileMap(&mapW, p.w, static_cast<uint64_t>(p.groups) * p.N, static_cast<uint64_t>(p.K))) {
         std::fprintf(stderr, "nixl_grouped_gemm_fp8_launch: cuTensorMapEncodeTiled failed\n");
         return cudaErrorInvalidValue;
+    }
+    // Tile shape: CTA pairs with 256 x 256 tiles when rows per expert are plentiful (compact layout
+    // of a throughput dispatch), single CTAs with 128 x 128 tiles for the expert-major low-latency
+    // layout, where most tiles hold a handful of rows.
+    int mode = p.tile_mode & 0xff;
+    if (mode == 0) mode = (p.rows_per_expert == 0 && !p.counts_flag && p.N % 256 == 0 && p.a_rows >= 256LL * p.groups) ? 2 : 1;
+    if (mode == 2) {
+        if (p.N % 256) return cudaErrorInvalidValue;
+        CUtensorMap mapW64; // the pair kernel loads W in 64-row boxes
+        if (!nixl_gemm::makeTileMap(&mapW64, p.w, static_cast<uint64_t>(p.groups) * p.N, static_cast<uint64_t>(p.K), 64)) return cudaErrorInvalidValue;
+        return nixl_gemm::launchPairKernel(mapA, mapW64, p, static_cast<cudaStream_t>(stream));
     }
     const size_t smem = size_t(kStages) * kStageBytes + sizeof(Shared) + 1024;
     int dev = 0, sms = 148;

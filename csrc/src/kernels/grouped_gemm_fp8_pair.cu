@@ -1,0 +1,426 @@
+// Grouped fp8 expert GEMM, 256 x 256 output tiles computed by CTA pairs (tcgen05 cta_group::2).
+//
+// Same math and operand formats as grouped_gemm_fp8.cu.  Two CTAs of a cluster share one tile:
+// each loads its own 128 rows of A and 128 of the tile's 256 W rows per 128-channel step (32 KiB
+// per CTA and step: half the L2 -> shared-memory traffic per MAC of 128 x 128 tiles), the even CTA
+// issues M256 N128 K32 MMAs that read both CTAs' shared memory and write both CTAs' TMEM, and each
+// CTA promotes and stores its own 128 rows.
+//
+// A 128-channel step is issued as two half-steps of four MMAs, one per 128-column half of the
+// tile, each into its own 128-column TMEM slot (four slots in flight), so a slot is handed to the
+// promotion warps, read and handed back while the following half-steps execute.  To make the two
+// N = 128 instructions cover contiguous columns, CTA c keeps W rows [64c, 64c+64) of the left
+// half and of the right half of the tile (two 64-row TMA boxes).
+//
+// The tensor pipe only stays busy while the issuing thread keeps feeding it: an MMA's issue
+// returns about when its predecessor starts, so any latency between two groups of MMAs idles the
+// pipe.  The issuer therefore polls the barriers of the next half-step (non-blocking test) before
+// it issues the current one, and the promotion warps do the same for their next slot.
+//
+//   warp 0      TMA producer (both CTAs; completion bytes are counted on the even CTA's barrier)
+//   warp 1      MMA issuer (even CTA only); commits are multicast to both CTAs' barriers
+//   warp 2      TMEM allocator (512 columns, cta_group::2)
+//   warps 4-11  promotion + epilogue: lane quarter q = warp % 4, 64-column part (warp - 4) / 4 of
+//               every slot; 128 fp32 accumulators per thread, so these warps raise their register
+//               budget (setmaxnreg) with what the role warps give back
+//
+// TMA loads read this GPU's memory only and carry no cluster multicast.  Every wait is bounded.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "kernels/grouped_gemm_internal.h"
+#include "kernels/tcgen05_ptx.cuh"
+
+namespace {
+
+using namespace nixl_tc;
+using nixl_gemm::GEMM_ERR_ARRIVAL;
+using nixl_gemm::GEMM_ERR_TIMEOUT;
+using nixl_gemm::kMaxGroups;
+
+constexpr int BM = 128;        // rows per CTA (256 per pair)
+constexpr int BN = 256;        // tile columns
+constexpr int BNS = 128;       // columns per half-step / TMEM slot
+constexpr int WBOX = 64;       // W rows per TMA box (per CTA and column half)
+constexpr int BK = 128;
+constexpr int UMMA_K = 32;
+constexpr int kStages = 6;
+constexpr int kThreads = 384;
+constexpr int kATileBytes = BM * BK;           // 16 KiB
+constexpr int kWBoxBytes = WBOX * BK;          // 8 KiB
+constexpr int kStageBytes = kATileBytes + 2 * kWBoxBytes; // 32 KiB per CTA
+constexpr int kSlots = 4;
+constexpr int kTmemCols = kSlots * BNS;        // 512
+constexpr int kPromoWarps = 8;
+
+struct Shared {
+    uint64_t full[kStages];       // used on the even CTA: both CTAs' bytes of a stage have landed
+    uint64_t empty[kStages];      // per CTA: the MMAs that read the stage are done
+    uint64_t tmemFull[kSlots];    // per CTA: slot ready for promotion
+    uint64_t tmemEmpty[kSlots];   // used on the even CTA: all 16 promotion warps of the pair have read the slot
+    uint32_t tmemBase;
+    int abort;
+    int tilePrefix[kMaxGroups + 1];
+    int rowStart[kMaxGroups];
+    int rowCount[kMaxGroups];
+};
+
+__device__ __forceinline__ uint32_t clusterCtaRank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t mapToCta(uint32_t smem_addr, uint32_t cta) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(cta));
+    return r;
+}
+__device__ __forceinline__ void clusterSync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Relaxed on purpose: a release at cluster scope made the arriving thread wait several hundred
+// cycles, once per slot.  What the arrive has to order are this warp's TMEM reads, and those are
+// complete (tcgen05.wait::ld returned, the values are in registers) before it is issued.
+__device__ __forceinline__ void mbarArriveCluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// Tile load whose completion bytes are counted on a barrier given by its cluster address
+// (the even CTA's), as the paired MMA needs both halves before it may start.
+__device__ __forceinline__ void tmaLoad2dPair(void *smem_dst, const CUtensorMap *map, int x, int y, uint32_t bar_cluster_addr) {
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+                     smemU32(smem_dst)),
+                 "l"(map), "r"(bar_cluster_addr), "r"(x), "r"(y)
+                 : "memory");
+}
+__device__ __forceinline__ void tcCommitPair(uint64_t *bar) {
+    // Arrives on the barrier at this offset in both CTAs of the pair.
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(smemU32(bar)),
+                 "h"(static_cast<uint16_t>(3))
+                 : "memory");
+}
+__device__ __forceinline__ void tcMmaPair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+                 " tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n}" ::"r"(tmem_d),
+                 "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u)
+                 : "memory");
+}
+// D fp32, A and B e4m3, both K-major, M = 256 (both CTAs), N = 128.
+__device__ __forceinline__ constexpr uint32_t instrDescPair() {
+    return (1u << 4) | (static_cast<uint32_t>(BNS >> 3) << 17) | (static_cast<uint32_t>((2 * BM) >> 4) << 24);
+}
+
+struct Tile {
+    int g, mt, nt;
+};
+
+__device__ __forceinline__ bool tileAt(const Shared &sh, int groups, int n_tiles, int t, Tile &out) {
+    if (t >= sh.tilePrefix[groups]) return false;
+    int lo = 0, hi = groups;
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (sh.tilePrefix[mid] <= t) lo = mid; else hi = mid;
+    }
+    const int local = t - sh.tilePrefix[lo];
+    out.g = lo;
+    out.mt = local / n_tiles;
+    out.nt = local - out.mt * n_tiles;
+    return true;
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+groupedGemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapW, const NixlGroupedGemmParams p) {
+    extern __shared__ __align__(1024) unsigned char dyn[];
+    unsigned char *tiles = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(dyn) + 1023) & ~uintptr_t(1023));
+    Shared &sh = *reinterpret_cast<Shared *>(tiles + kStages * kStageBytes);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n_tiles = p.N / BN, k_steps = p.K / BK;
+    const uint32_t cta = clusterCtaRank(); // 0: issues the MMAs, 1: its partner
+    const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbarInit(&sh.full[s], 1);
+            mbarInit(&sh.empty[s], 1);
+        }
+        for (int b = 0; b < kSlots; ++b) {
+            mbarInit(&sh.tmemFull[b], 1);
+            mbarInit(&sh.tmemEmpty[b], 2 * kPromoWarps);
+        }
+        sh.abort = 0;
+        int run = 0;
+        if (p.counts_flag) {
+            for (int r = 0; r < p.ranks; ++r) {
+                uint64_t t0 = 0;
+                unsigned spins = 0;
+                while (ldAcquireSys(p.counts_flag + r) < p.epoch) {
+                    if ((++spins & 63u) == 0) {
+                        const uint64_t now = nowNs();
+                        if (t0 == 0) t0 = now;
+                        else if (now - t0 > p.timeout_ns) {
+                            atomicOr(p.status, GEMM_ERR_ARRIVAL);
+                            break;
+                        }
+                    }
+                }
+            }
+            int next = 0;
+            for (int g = 0; g < p.groups; ++g) {
+                int c = 0;
+                for (int r = 0; r < p.ranks; ++r) c += p.counts[static_cast<long long>(r) * p.experts_total + p.expert_base + g];
+                sh.tilePrefix[g] = run;
+                sh.rowStart[g] = p.rows_per_expert > 0 ? g * p.rows_per_expert : next;
+                sh.rowCount[g] = c;
+                next += c;
+                run += ((c + 2 * BM - 1) / (2 * BM)) * n_tiles;
+            }
+        } else {
+            for (int g = 0; g < p.groups; ++g) {
+                const int c = p.row_count[g];
+                sh.tilePrefix[g] = run;
+                sh.rowStart[g] = p.row_start[g];
+                sh.rowCount[g] = c;
+                run += ((c + 2 * BM - 1) / (2 * BM)) * n_tiles;
+            }
+        }
+        sh.tilePrefix[p.groups] = run;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 2) {
+        // Both CTAs of the pair issue the paired allocation from the same warp and shared offset.
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smemU32(&sh.tmemBase)), "r"(kTmemCols));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;");
+    }
+    tcFenceBefore();
+    __syncthreads();
+    clusterSync(); // the partner's barriers exist before anything arrives on them
+    tcFenceAfter();
+    const uint32_t tmem = sh.tmemBase;
+    volatile int *abort_flag = &sh.abort;
+    // k-steps this pair executes in total (every tile has k_steps of them)
+    int my_tiles = 0;
+    {
+        const int total = sh.tilePrefix[p.groups];
+        if (pair < total) my_tiles = (total - pair + pairs - 1) / pairs;
+    }
+
+    if (warp < 4) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+        if (warp == 0 && lane == 0) {
+            // ------------------------------------------------------------ TMA producer (both CTAs)
+            const uint32_t full0 = mapToCta(smemU32(&sh.full[0]), 0);
+            uint32_t it = 0;
+            Tile t;
+            for (int ti = pair; tileAt(sh, p.groups, n_tiles, ti, t); ti += pairs) {
+                const int row0 = sh.rowStart[t.g] + t.mt * (2 * BM) + static_cast<int>(cta) * BM;
+                if (p.disp_flag) {
+                    const int lo = t.mt * (2 * BM) + static_cast<int>(cta) * BM, hi = min(lo + BM, sh.rowCount[t.g]);
+                    int first = 0;
+                    for (int r = 0; r < p.ranks; ++r) {
+                        const int c = p.counts[static_cast<long long>(r) * p.experts_total + p.expert_base + t.g];
+                        if (c > 0 && first < hi && first + c > lo) {
+                            const uint64_t *flag = p.disp_flag + static_cast<long long>(t.g) * p.ranks + r;
+                            uint64_t t0 = 0;
+                            unsigned spins = 0;
+                            while (ldAcquireSys(flag) < p.epoch) {
+                                if ((++spins & 63u) == 0) {
+                                    const uint64_t now = nowNs();
+                                    if (t0 == 0) t0 = now;
+                                    else if (now - t0 > p.timeout_ns) {
+                                        atomicOr(p.status, GEMM_ERR_ARRIVAL);
+                                        break;
+                                    }
+                                }
+                            }
+                        }
+                        first += c;
+                    }
+                    asm volatile("fence.proxy.async;" ::: "memory");
+                }
+                const int wrow = t.g * p.N + t.nt * BN + static_cast<int>(cta) * WBOX;
+                for (int ks = 0; ks < k_steps; ++ks, ++it) {
+                    const int s = it % kStages;
+                    if (!mbarWait(&sh.empty[s], ((it / kStages) & 1) ^ 1, abort_flag)) goto role_done;
+                    if (cta == 0) mbarExpectTx(&sh.full[s], 2 * kStageBytes); // both CTAs' shares
+                    const uint32_t bar = full0 + static_cast<uint32_t>(s) * 8u;
+                    unsigned char *st = tiles + s * kStageBytes;
+                    tmaLoad2dPair(st, &mapA, ks * BK, row0, bar);
+                    tmaLoad2dPair(st + kATileBytes, &mapW, ks * BK, wrow, bar);               // columns [64c, 64c+64) of the left half
+                    tmaLoad2dPair(st + kATileBytes + kWBoxBytes, &mapW, ks * BK, wrow + BNS, bar); // and of the right half
+                }
+            }
+        } else if (warp == 1 && lane == 0 && cta == 0) {
+            // ------------------------------------------------------------ MMA issuer (even CTA)
+            // Flat loop over half-steps j = 2 * (k-step counter) + h.  The barriers of half-step j + 1
+            // are tested before the MMAs of j are issued; the result is looked at one round later.
+            const uint32_t total_steps = 2u * static_cast<uint32_t>(my_tiles) * static_cast<uint32_t>(k_steps);
+            bool rdy_full = mbarTest(&sh.full[0], 0);
+            bool rdy_empty = mbarTest(&sh.tmemEmpty[0], 1);
+            for (uint32_t j = 0; j < total_steps; ++j) {
+                const uint32_t it = j >> 1, h = j & 1u;
+                const uint32_t s = it % kStages, slot = j % kSlots;
+                if (h == 0 && !rdy_full && !mbarWait(&sh.full[s], (it / kStages) & 1, abort_flag)) goto role_done;
+                if (!rdy_empty && !mbarWait(&sh.tmemEmpty[slot], ((j / kSlots) & 1) ^ 1, abort_flag)) goto role_done;
+                tcFenceAfter();
+                {
+                    const uint32_t jn = j + 1, itn = jn >> 1;
+                    rdy_empty = mbarTest(&sh.tmemEmpty[jn % kSlots], ((jn / kSlots) & 1) ^ 1);
+                    if ((jn & 1u) == 0) rdy_full = mbarTest(&sh.full[itn % kStages], (itn / kStages) & 1);
+                }
+                const uint32_t a_addr = smemU32(tiles + s * kStageBytes);
+                const uint64_t da = smemDesc(a_addr), dw = smemDesc(a_addr + kATileBytes + h * kWBoxBytes);
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k)
+                    tcMmaPair(tmem + slot * BNS, da + static_cast<uint64_t>(k * (UMMA_K >> 4)), dw + static_cast<uint64_t>(k * (UMMA_K >> 4)),
+                              instrDescPair(), k > 0 ? 1u : 0u);
+                tcCommitPair(&sh.tmemFull[slot]);
+                if (h == 1) tcCommitPair(&sh.empty[s]);
+            }
+        }
+    role_done:;
+    } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+        // ---------------------------------------------------------------- promotion + epilogue
+        const int q = warp & 3;
+        const int part = (warp - 4) >> 2; // which 64 of a slot's 128 columns
+        const int row_in_tile = q * 32 + lane;
+        const uint32_t empty0 = mapToCta(smemU32(&sh.tmemEmpty[0]), 0);
+        const uint32_t lane_base = tmem + (static_cast<uint32_t>(q * 32) << 16) + part * 64;
+        uint32_t j = 0; // half-step counter, same numbering as the issuer's
+        Tile t;
+        const int n_blocks = p.N / 128;
+        bool rdy = false;
+        bool ok = true;
+        for (int ti = pair; ok && tileAt(sh, p.groups, n_tiles, ti, t); ti += pairs) {
+            const int local_row = t.mt * (2 * BM) + static_cast<int>(cta) * BM + row_in_tile;
+            const bool valid = local_row < sh.rowCount[t.g];
+            const long long grow = static_cast<long long>(sh.rowStart[t.g]) + local_row;
+            const float *sa_row = p.scale_a + grow * k_steps;
+            const float *sw0 = p.scale_w + (static_cast<long long>(t.g) * n_blocks + t.nt * 2) * k_steps;
+            const float *sw1 = sw0 + k_steps;
+            float acc[2 * 64];
+#pragma unroll
+            for (int i = 0; i < 2 * 64; ++i) acc[i] = 0.f;
+            // Scales are fetched kPrefetch steps ahead and kept as loaded: multiplying them right away
+            // would make the warp wait for the loads it has just issued.
+            constexpr int kPrefetch = 4;
+            float ring_a[kPrefetch], ring_w0[kPrefetch], ring_w1[kPrefetch];
+#pragma unroll
+            for (int i = 0; i < kPrefetch; ++i) {
+                ring_a[i] = (i < k_steps && valid) ? __ldg(sa_row + i) : 0.f;
+                ring_w0[i] = i < k_steps ? __ldg(sw0 + i) : 0.f;
+                ring_w1[i] = i < k_steps ? __ldg(sw1 + i) : 0.f;
+            }
+            for (int ks0 = 0; ks0 < k_steps && ok; ks0 += kPrefetch) {
+#pragma unroll
+                for (int i = 0; i < kPrefetch; ++i) {
+                    const int ks = ks0 + i;
+                    if (ks >= k_steps) break;
+                    const float s0 = ring_a[i] * ring_w0[i], s1 = ring_a[i] * ring_w1[i];
+                    const int nxt = ks + kPrefetch;
+#pragma unroll
+                    for (int h = 0; h < 2; ++h, ++j) {
+                        const uint32_t slot = j % kSlots;
+                        if (!rdy && !mbarWait(&sh.tmemFull[slot], (j / kSlots) & 1, abort_flag)) {
+                            ok = false;
+                            break;
+                        }
+                        tcFenceAfter();
+                        float v0[32], v1[32];
+                        tmemLoad32(lane_base + slot * BNS, v0);
+                        tmemLoad32(lane_base + slot * BNS + 32, v1);
+                        // While the loads are in flight, look at the next slot's barrier.
+                        rdy = mbarTest(&sh.tmemFull[(j + 1) % kSlots], ((j + 1) / kSlots) & 1);
+                        tmemLoadWait(v0);
+                        tmemLoadWait(v1);
+                        // This warp's share of the slot is in registers: hand it back to the MMA issuer.
+                        tcFenceBefore();
+                        __syncwarp();
+                        if (lane == 0) mbarArriveCluster(empty0 + slot * 8u);
+                        // The arrive has release semantics and would wait for loads issued before it:
+                        // the scale prefetch therefore goes after it, not before.
+                        if (h == 0 && nxt < k_steps) {
+                            ring_a[i] = valid ? __ldg(sa_row + nxt) : 0.f;
+                            ring_w0[i] = __ldg(sw0 + nxt);
+                            ring_w1[i] = __ldg(sw1 + nxt);
+                        }
+                        const float sc = h == 0 ? s0 : s1;
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) acc[h * 64 + e] = fmaf(v0[e], sc, acc[h * 64 + e]);
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) acc[h * 64 + 32 + e] = fmaf(v1[e], sc, acc[h * 64 + 32 + e]);
+                    }
+                    if (!ok) break;
+                }
+            }
+            if (!ok) break;
+            if (valid) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    __nv_bfloat16 *out = static_cast<__nv_bfloat16 *>(p.d) + grow * p.N + t.nt * BN + h * BNS + part * 64;
+#pragma unroll
+                    for (int e = 0; e < 64; e += 8) {
+                        uint4 o;
+                        __nv_bfloat162 *hh = reinterpret_cast<__nv_bfloat162 *>(&o);
+#pragma unroll
+                        for (int x = 0; x < 4; ++x) hh[x] = __floats2bfloat162_rn(acc[h * 64 + e + 2 * x], acc[h * 64 + e + 2 * x + 1]);
+                        *reinterpret_cast<uint4 *>(out + e) = o;
+                    }
+                }
+            }
+        }
+    }
+
+    // Neither CTA may leave (or free TMEM) while its partner can still read its shared memory,
+    // write its TMEM or arrive on its barriers.
+    tcFenceBefore();
+    __syncthreads();
+    clusterSync();
+    if (threadIdx.x == 0 && sh.abort) atomicOr(p.status, GEMM_ERR_TIMEOUT);
+    if (warp == 2) {
+        tcFenceAfter();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols));
+    }
+}
+
+} // namespace
+
+cudaError_t nixl_gemm::launchPairKernel(const CUtensorMap &mapA, const CUtensorMap &mapW, const NixlGroupedGemmParams &p, cudaStream_t stream) {
+    const size_t smem = size_t(kStages) * kStageBytes + sizeof(Shared) + 1024;
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    static bool attr_done[64] = {};
+    static int max_pairs[64] = {};
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(groupedGemmPairKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        if (e != cudaSuccess) return e;
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        // How many pairs can be resident at once: a persistent grid must not exceed it.
+        cfg.gridDim = dim3(static_cast<unsigned>(sms & ~1));
+        int clusters = 0;
+        e = cudaOccupancyMaxActiveClusters(&clusters, groupedGemmPairKernel, &cfg);
+        if (e != cudaSuccess || clusters <= 0) {
+            cudaGetLastError();
+            clusters = sms / 2;
+        }
+        max_pairs[dev] = clusters;
+        attr_done[dev] = true;
+    }
+    int pairs = (dev >= 0 && dev < 64) ? max_pairs[dev] : sms / 2;
+    if (p.grid > 0 && p.grid / 2 < pairs) pairs = p.grid / 2 > 0 ? p.grid / 2 : 1;
+    const long long max_tiles = (static_cast<long long>(p.a_rows + 2 * BM - 1) / (2 * BM) + p.groups) * (p.N / BN);
+    if (pairs > max_tiles) pairs = static_cast<int>(max_tiles);
+    cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs));
+    return cudaLaunchKernelEx(&cfg, groupedGemmPairKernel, mapA, mapW, p);
+}

@@ -1,0 +1,129 @@
+// PTX wrappers shared by the tcgen05 GEMM kernels (sm_100a): mbarrier, TMA tile loads, tcgen05
+// MMA / commit / TMEM loads, shared-memory matrix descriptors.  Every wait is bounded.
+#ifndef NIXL_B200_TCGEN05_PTX_CUH
+#define NIXL_B200_TCGEN05_PTX_CUH
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+namespace nixl_tc {
+
+constexpr uint64_t kWaitNs = 4000000000ull; // any single wait longer than 4 s aborts the kernel
+
+
+__device__ __forceinline__ uint32_t smemU32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ uint64_t nowNs() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ void mbarInit(uint64_t *b, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smemU32(b)), "r"(count));
+}
+__device__ __forceinline__ void mbarExpectTx(uint64_t *b, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smemU32(b)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbarArrive(uint64_t *b) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smemU32(b)) : "memory");
+}
+__device__ __forceinline__ bool mbarTry(uint64_t *b, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok)
+                 : "r"(smemU32(b)), "r"(parity)
+                 : "memory");
+    return ok != 0;
+}
+// Non-blocking look at a phase (never suspends the thread): used to start a poll before work that
+// does not depend on it, so the barrier's latency is hidden behind that work.
+__device__ __forceinline__ bool mbarTest(uint64_t *b, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok)
+                 : "r"(smemU32(b)), "r"(parity)
+                 : "memory");
+    return ok != 0;
+}
+// Bounded wait; false when the budget ran out or another role aborted.
+__device__ __forceinline__ bool mbarWait(uint64_t *b, uint32_t parity, volatile int *abort_flag) {
+    uint64_t t0 = 0;
+    unsigned spins = 0;
+    while (!mbarTry(b, parity)) {
+        if ((++spins & 127u) == 0) {
+            if (*abort_flag) return false;
+            const uint64_t now = nowNs();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > kWaitNs) {
+                *abort_flag = 1;
+                return false;
+            }
+        }
+    }
+    return true;
+}
+__device__ __forceinline__ void tmaLoad2d(void *smem_dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+                     smemU32(smem_dst)),
+                 "l"(map), "r"(smemU32(bar)), "r"(x), "r"(y)
+                 : "memory");
+}
+__device__ __forceinline__ void tcFenceBefore() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcFenceAfter() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcCommit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smemU32(bar)) : "memory");
+}
+__device__ __forceinline__ void tcMma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+                 " tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}" ::"r"(tmem_d),
+                 "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u)
+                 : "memory");
+}
+// 32 lanes x 32 consecutive fp32 columns -> 32 registers per thread (thread = lane = row).
+__device__ __forceinline__ void tmemLoad32(uint32_t addr, float (&v)[32]) {
+    uint32_t *r = reinterpret_cast<uint32_t *>(v);
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+                   "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+                   "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+                   "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(addr));
+}
+// Waits for outstanding TMEM loads.  The registers are listed as read-write operands so that no
+// use of them can be scheduled above the wait (the load instruction returns before its data).
+__device__ __forceinline__ void tmemLoadWait(float (&v)[32]) {
+    uint32_t *r = reinterpret_cast<uint32_t *>(v);
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]), "+r"(r[9]),
+                   "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]),
+                   "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]),
+                   "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+                 :
+                 : "memory");
+}
+
+// Shared-memory matrix descriptor for a K-major tile of 128-byte rows written by TMA with the
+// 128-byte swizzle: 8-row groups are 1024 bytes apart (stride byte offset), the leading offset
+// is unused for this layout, descriptor version 1 (sm_100), layout type 2 = SWIZZLE_128B.
+__device__ __forceinline__ uint64_t smemDesc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);       // start address, bits [0,14)
+    d |= static_cast<uint64_t>(1) << 16;                           // leading byte offset (ignored), bits [16,30)
+    d |= static_cast<uint64_t>(1024 >> 4) << 32;                   // stride byte offset, bits [32,46)
+    d |= static_cast<uint64_t>(1) << 46;                           // version, bits [46,48)
+    d |= static_cast<uint64_t>(2) << 61;                           // layout type, bits [61,64)
+    return d;
+}
+
+__device__ __forceinline__ uint64_t ldAcquireSys(const uint64_t *p) {
+    uint64_t v;
+    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+
+} // namespace nixl_tc
+
+#endif

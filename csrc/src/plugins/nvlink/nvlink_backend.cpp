@@ -14,6 +14,7 @@
 #include "backend/backend_plugin.h"
 #include "device/nixl_device_layout.h"
 #include "serdes/serdes.h"
+#include "utils/hw_info.h"
 #include "utils/log.h"
 
 namespace nixl_nvlink {
@@ -258,6 +259,11 @@ Engine::Engine(const nixlBackendInitParams *init) : nixlBackendEngine(init) {
         deviceCount_ = n;
     } else {
         cudaGetLastError();
+        // GPUs on the PCI bus that CUDA cannot open usually mean a driver / container set-up problem:
+        // say so once instead of silently moving host memory only.
+        const nixl::hwInfo &hw = nixl::hwInfo::instance();
+        if (want_cuda && hw.numNvidiaGpus > 0)
+            NIXL_WARN << "NVLINK backend: " << hw.numNvidiaGpus << " NVIDIA GPU(s) on the PCI bus but CUDA reports none; VRAM transfers are unavailable";
     }
     pinDram_ = paramBool(params, "pin_dram", true);
     auto cp = params.find("copy_path");

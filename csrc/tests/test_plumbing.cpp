@@ -10,7 +10,11 @@
 #include <thread>
 #include <unistd.h>
 
+#include <fstream>
+#include <sys/stat.h>
+
 #include "harness.h"
+#include "utils/hw_info.h"
 #include "nixl.h"
 
 namespace {
@@ -223,6 +227,35 @@ TEST_CASE(posix_file_roundtrip) {
     CHECK(src == back);
     ::close(fd);
     ::unlink(path);
+}
+
+TEST_CASE(hw_info_counts_devices_from_a_sysfs_tree) {
+    // A fake /sys/bus/pci/devices: two B200s, one NVSwitch, one ConnectX, one EFA, one unrelated NIC.
+    char tmpl[] = "/tmp/nixl_hwinfo_XXXXXX";
+    CHECK(::mkdtemp(tmpl) != nullptr);
+    const std::string root = tmpl;
+    auto add = [&](const std::string &name, const char *vendor, const char *cls, const char *device) {
+        const std::string d = root + "/" + name;
+        CHECK(::mkdir(d.c_str(), 0755) == 0);
+        std::ofstream(d + "/vendor") << vendor << "\n";
+        std::ofstream(d + "/class") << cls << "\n";
+        std::ofstream(d + "/device") << device << "\n";
+    };
+    add("0000:1b:00.0", "0x10de", "0x030200", "0x2901");
+    add("0000:43:00.0", "0x10de", "0x030200", "0x2901");
+    add("0000:05:00.0", "0x10de", "0x068000", "0x22a3");
+    add("0000:0c:00.0", "0x15b3", "0x020700", "0x1021");
+    add("0000:0d:00.0", "0x1d0f", "0x020000", "0xefa2");
+    add("0000:0e:00.0", "0x8086", "0x020000", "0x1572");
+    const nixl::hwInfo hw = nixl::hwInfo::scan(root);
+    CHECK_EQ(hw.numNvidiaGpus, 2u);
+    CHECK_EQ(hw.numNvSwitches, 1u);
+    CHECK_EQ(hw.numIbDevices, 1u);
+    CHECK_EQ(hw.numEfaDevices, 1u);
+    CHECK_EQ(hw.numAmdGpus, 0u);
+    CHECK(hw.toString().find("nvidia_gpus=2") != std::string::npos);
+    const nixl::hwInfo none = nixl::hwInfo::scan(root + "/does_not_exist");
+    CHECK_EQ(none.numNvidiaGpus, 0u);
 }
 
 TEST_MAIN()

@@ -24,7 +24,7 @@ class _Params(ctypes.Structure):
         ("grid", ctypes.c_int32), ("ranks", ctypes.c_int32), ("experts_total", ctypes.c_int32), ("expert_base", ctypes.c_int32),
         ("status", ctypes.c_void_p), ("disp_flag", ctypes.c_void_p), ("counts", ctypes.c_void_p),
         ("epoch", ctypes.c_uint64), ("timeout_ns", ctypes.c_uint64),
-        ("counts_flag", ctypes.c_void_p), ("rows_per_expert", ctypes.c_int32),
+        ("counts_flag", ctypes.c_void_p), ("rows_per_expert", ctypes.c_int32), ("tile_mode", ctypes.c_int32),
     ]
 
 
@@ -51,6 +51,7 @@ def grouped_gemm_fp8(
     grid: int = 0,
     overlapped: bool = False,
     rows_per_expert: int = 0,
+    tile_mode: int = 0,
 ) -> torch.Tensor:
     """``out[rows of g] = dequant(a[rows]) @ dequant(w[g]).T`` in bf16.
 
@@ -59,7 +60,9 @@ def grouped_gemm_fp8(
     ``fused_with``: ``(buffer, handle)`` of the EP dispatch that is filling ``a`` (optional).
     ``overlapped``: that dispatch was launched on another stream and may still be running; the
     kernel then waits for the count exchange itself (``rows_per_expert`` names the layout) and
-    ``grid`` should leave the dispatch's CTAs free (see ``Buffer.dispatch_gemm``)."""
+    ``grid`` should leave the dispatch's CTAs free (see ``Buffer.dispatch_gemm``).
+    ``tile_mode``: 0 lets the library choose, 1 forces 128 x 128 tiles on single CTAs, 2 forces
+    256 x 256 tiles on CTA pairs (``N % 256 == 0``)."""
     rows, K = a.shape
     G, N, K2 = w.shape
     if K != K2 or K % 128 or N % 128:
@@ -85,6 +88,7 @@ def grouped_gemm_fp8(
     p.a, p.scale_a, p.w, p.scale_w, p.d = a.data_ptr(), scale_a.data_ptr(), w.data_ptr(), scale_w.data_ptr(), out.data_ptr()
     p.row_start, p.row_count = row_start.data_ptr(), row_count.data_ptr()
     p.groups, p.N, p.K, p.a_rows, p.grid = G, N, K, rows, grid
+    p.tile_mode = tile_mode
     p.status = status.data_ptr()
     if fused_with is not None:
         buf, handle = fused_with

@@ -36,8 +36,27 @@ def _case(G, N, K, counts, gap=0, seed=0):
     ],
 )
 def test_matches_reference(G, N, K, counts, gap):
+    _check(G, N, K, counts, gap, tile_mode=1)
+
+
+@pytest.mark.parametrize(
+    "G,N,K,counts,gap",
+    [
+        (1, 256, 256, [256], 0),
+        (1, 256, 1024, [100], 0),
+        (2, 512, 512, [300, 57], 0),
+        (4, 256, 1024, [0, 600, 1, 129], 5),
+        (3, 512, 7168, [64, 257, 512], 0),
+    ],
+)
+def test_cta_pair_tiles_match_reference(G, N, K, counts, gap):
+    """256 x 256 tiles on CTA pairs: ragged groups, empty groups, rows that end inside either CTA's half."""
+    _check(G, N, K, counts, gap, tile_mode=2)
+
+
+def _check(G, N, K, counts, gap, tile_mode):
     a, sa, wq, sw, rs, rc = _case(G, N, K, counts, gap)
-    out = grouped_gemm_fp8(a, sa, wq, sw, rs, rc)
+    out = grouped_gemm_fp8(a, sa, wq, sw, rs, rc, tile_mode=tile_mode)
     torch.cuda.synchronize()
     assert int(out._nixl_status.item()) == 0
     want = reference_grouped_gemm(a, sa, wq, sw, rs, rc)
