@@ -44,7 +44,6 @@ constexpr int BN = 256;        // tile columns
 constexpr int BNS = 128;       // columns per half-step / TMEM slot
 constexpr int WBOX = 64;       // W rows per TMA box (per CTA and column half)
 constexpr int BK = 128;
-constexpr int UMMA_K = 32;
 constexpr int kStages = 6;
 constexpr int kThreads = 384;
 constexpr int kATileBytes = BM * BK;           // 16 KiB
@@ -93,18 +92,38 @@ __device__ __forceinline__ void tmaLoad2dPair(void *smem_dst, const CUtensorMap 
                  "l"(map), "r"(bar_cluster_addr), "r"(x), "r"(y)
                  : "memory");
 }
-__device__ __forceinline__ void tcCommitPair(uint64_t *bar) {
-    // Arrives on the barrier at this offset in both CTAs of the pair.
-    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(smemU32(bar)),
-                 "h"(static_cast<uint16_t>(3))
-                 : "memory");
+// One half-step of the issuer as a single instruction sequence: start the (non-blocking) tests of
+// the next half-step's barriers, issue the four MMAs and the commits, and only then read the test
+// results, so the barriers' latency runs behind the MMA issue instead of in front of it.
+__device__ __forceinline__ void issueHalfStep(uint32_t tmem_d, uint64_t da, uint64_t dw, uint32_t idesc, uint32_t bar_tmem_full,
+                                              uint32_t bar_stage_empty, uint32_t commit_stage, uint32_t peek_empty_bar, uint32_t peek_empty_par,
+                                              uint32_t peek_full_bar, uint32_t peek_full_par, uint32_t &rdy_empty, uint32_t &rdy_full) {
+    asm volatile(
+        "{\n"
+        " .reg .pred pe, pf, pacc, pnew, pc;\n"
+        " mbarrier.test_wait.parity.shared::cta.b64 pe, [%8], %9;\n"
+        " mbarrier.test_wait.parity.shared::cta.b64 pf, [%10], %11;\n"
+        " setp.ne.b32 pacc, %12, 0;\n"
+        " setp.eq.b32 pnew, %12, 0;\n"
+        " setp.ne.b32 pc, %7, 0;\n"
+        " tcgen05.mma.cta_group::2.kind::f8f6f4 [%2], %3, %4, %5, {%13, %13, %13, %13, %13, %13, %13, %13}, pnew;\n"
+        " add.u64 %3, %3, 2;\n add.u64 %4, %4, 2;\n"
+        " tcgen05.mma.cta_group::2.kind::f8f6f4 [%2], %3, %4, %5, {%13, %13, %13, %13, %13, %13, %13, %13}, pacc;\n"
+        " add.u64 %3, %3, 2;\n add.u64 %4, %4, 2;\n"
+        " tcgen05.mma.cta_group::2.kind::f8f6f4 [%2], %3, %4, %5, {%13, %13, %13, %13, %13, %13, %13, %13}, pacc;\n"
+        " add.u64 %3, %3, 2;\n add.u64 %4, %4, 2;\n"
+        " tcgen05.mma.cta_group::2.kind::f8f6f4 [%2], %3, %4, %5, {%13, %13, %13, %13, %13, %13, %13, %13}, pacc;\n"
+        " tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%6], %14;\n"
+        " @pc tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%15], %14;\n"
+        " selp.u32 %0, 1, 0, pe;\n"
+        " selp.u32 %1, 1, 0, pf;\n"
+        "}\n"
+        : "=r"(rdy_empty), "=r"(rdy_full), "+r"(tmem_d), "+l"(da), "+l"(dw)
+        : "r"(idesc), "r"(bar_tmem_full), "r"(commit_stage), "r"(peek_empty_bar), "r"(peek_empty_par), "r"(peek_full_bar), "r"(peek_full_par),
+          "r"(1u), "r"(0u), "h"(static_cast<uint16_t>(3)), "r"(bar_stage_empty)
+        : "memory");
 }
-__device__ __forceinline__ void tcMmaPair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-                 " tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n}" ::"r"(tmem_d),
-                 "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u)
-                 : "memory");
-}
+
 // D fp32, A and B e4m3, both K-major, M = 256 (both CTAs), N = 128.
 __device__ __forceinline__ constexpr uint32_t instrDescPair() {
     return (1u << 4) | (static_cast<uint32_t>(BNS >> 3) << 17) | (static_cast<uint32_t>((2 * BM) >> 4) << 24);
@@ -254,27 +273,40 @@ groupedGemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_con
             // Flat loop over half-steps j = 2 * (k-step counter) + h.  The barriers of half-step j + 1
             // are tested before the MMAs of j are issued; the result is looked at one round later.
             const uint32_t total_steps = 2u * static_cast<uint32_t>(my_tiles) * static_cast<uint32_t>(k_steps);
-            bool rdy_full = mbarTest(&sh.full[0], 0);
-            bool rdy_empty = mbarTest(&sh.tmemEmpty[0], 1);
+            // Ring positions are kept as counters (no divisions on this thread's critical path).
+            uint32_t s = 0, full_par = 0;   // stage of the current k-step and the parity its "full" phase has
+            uint32_t slot = 0, empty_par = 1; // TMEM slot of the current half-step and the parity of "slot is free"
+            uint32_t rdy_full = mbarTest(&sh.full[0], 0) ? 1u : 0u;
+            uint32_t rdy_empty = mbarTest(&sh.tmemEmpty[0], 1) ? 1u : 0u;
+            const uint32_t full_bar0 = smemU32(&sh.full[0]), empty_bar0 = smemU32(&sh.empty[0]);
+            const uint32_t tfull_bar0 = smemU32(&sh.tmemFull[0]), tempty_bar0 = smemU32(&sh.tmemEmpty[0]);
+            const uint64_t desc0 = smemDesc(smemU32(tiles));
             for (uint32_t j = 0; j < total_steps; ++j) {
-                const uint32_t it = j >> 1, h = j & 1u;
-                const uint32_t s = it % kStages, slot = j % kSlots;
-                if (h == 0 && !rdy_full && !mbarWait(&sh.full[s], (it / kStages) & 1, abort_flag)) goto role_done;
-                if (!rdy_empty && !mbarWait(&sh.tmemEmpty[slot], ((j / kSlots) & 1) ^ 1, abort_flag)) goto role_done;
+                const uint32_t h = j & 1u;
+                if (h == 0 && !rdy_full && !mbarWait(&sh.full[s], full_par, abort_flag)) goto role_done;
+                if (!rdy_empty && !mbarWait(&sh.tmemEmpty[slot], empty_par, abort_flag)) goto role_done;
                 tcFenceAfter();
-                {
-                    const uint32_t jn = j + 1, itn = jn >> 1;
-                    rdy_empty = mbarTest(&sh.tmemEmpty[jn % kSlots], ((jn / kSlots) & 1) ^ 1);
-                    if ((jn & 1u) == 0) rdy_full = mbarTest(&sh.full[itn % kStages], (itn / kStages) & 1);
+                // Next half-step's ring positions: its slot, and (after the second half) the next stage.
+                const uint32_t nslot = (slot + 1) & (kSlots - 1);
+                const uint32_t nempty_par = empty_par ^ (nslot == 0 ? 1u : 0u);
+                uint32_t ns = s, nfull_par = full_par;
+                if (h == 1) {
+                    ns = s + 1;
+                    if (ns == kStages) {
+                        ns = 0;
+                        nfull_par ^= 1u;
+                    }
                 }
-                const uint32_t a_addr = smemU32(tiles + s * kStageBytes);
-                const uint64_t da = smemDesc(a_addr), dw = smemDesc(a_addr + kATileBytes + h * kWBoxBytes);
-#pragma unroll
-                for (int k = 0; k < BK / UMMA_K; ++k)
-                    tcMmaPair(tmem + slot * BNS, da + static_cast<uint64_t>(k * (UMMA_K >> 4)), dw + static_cast<uint64_t>(k * (UMMA_K >> 4)),
-                              instrDescPair(), k > 0 ? 1u : 0u);
-                tcCommitPair(&sh.tmemFull[slot]);
-                if (h == 1) tcCommitPair(&sh.empty[s]);
+                const uint64_t da = desc0 + static_cast<uint64_t>((s * kStageBytes) >> 4);
+                const uint64_t dw = da + static_cast<uint64_t>((kATileBytes + h * kWBoxBytes) >> 4);
+                uint32_t peek_full = 1;
+                issueHalfStep(tmem + slot * BNS, da, dw, instrDescPair(), tfull_bar0 + slot * 8u, empty_bar0 + s * 8u, h, tempty_bar0 + nslot * 8u,
+                              nempty_par, full_bar0 + ns * 8u, nfull_par, rdy_empty, peek_full);
+                if (h == 1) rdy_full = peek_full; // after the first half the test looked at the current, already complete stage
+                slot = nslot;
+                empty_par = nempty_par;
+                s = ns;
+                full_par = nfull_par;
             }
         }
     role_done:;

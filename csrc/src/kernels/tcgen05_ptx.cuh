@@ -10,8 +10,6 @@
 
 namespace nixl_tc {
 
-constexpr uint64_t kWaitNs = 4000000000ull; // any single wait longer than 4 s aborts the kernel
-
 
 __device__ __forceinline__ uint32_t smemU32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 __device__ __forceinline__ uint64_t nowNs() {
@@ -28,11 +26,14 @@ __device__ __forceinline__ void mbarExpectTx(uint64_t *b, uint32_t bytes) {
 __device__ __forceinline__ void mbarArrive(uint64_t *b) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smemU32(b)) : "memory");
 }
+// One blocking attempt.  The suspend-time hint (nanoseconds) bounds how long the hardware may
+// park the thread before it returns "not yet": without it the limit is system-dependent, and
+// the caller's own time budget would only be looked at after many such sleeps.
 __device__ __forceinline__ bool mbarTry(uint64_t *b, uint32_t parity) {
     uint32_t ok;
-    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}"
                  : "=r"(ok)
-                 : "r"(smemU32(b)), "r"(parity)
+                 : "r"(smemU32(b)), "r"(parity), "r"(20000u)
                  : "memory");
     return ok != 0;
 }
@@ -48,17 +49,16 @@ __device__ __forceinline__ bool mbarTest(uint64_t *b, uint32_t parity) {
 }
 // Bounded wait; false when the budget ran out or another role aborted.
 __device__ __forceinline__ bool mbarWait(uint64_t *b, uint32_t parity, volatile int *abort_flag) {
-    uint64_t t0 = 0;
-    unsigned spins = 0;
+    if (mbarTry(b, parity)) return true;
+    // The budget is counted on the SM's cycle counter (cheap to read after every failed attempt;
+    // the global nanosecond timer is not): 2^33 cycles are 4.4 s at 1.97 GHz and more when the
+    // clock is lower.
+    const long long t0 = clock64();
     while (!mbarTry(b, parity)) {
-        if ((++spins & 127u) == 0) {
-            if (*abort_flag) return false;
-            const uint64_t now = nowNs();
-            if (t0 == 0) t0 = now;
-            else if (now - t0 > kWaitNs) {
-                *abort_flag = 1;
-                return false;
-            }
+        if (*abort_flag) return false;
+        if (clock64() - t0 > (1ll << 33)) {
+            *abort_flag = 1;
+            return false;
         }
     }
     return true;
