@@ -92,35 +92,42 @@ __device__ __forceinline__ void tmaLoad2dPair(void *smem_dst, const CUtensorMap 
                  "l"(map), "r"(bar_cluster_addr), "r"(x), "r"(y)
                  : "memory");
 }
-// One half-step of the issuer as a single instruction sequence: start the (non-blocking) tests of
-// the next half-step's barriers, issue the four MMAs and the commits, and only then read the test
-// results, so the barriers' latency runs behind the MMA issue instead of in front of it.
-__device__ __forceinline__ void issueHalfStep(uint32_t tmem_d, uint64_t da, uint64_t dw, uint32_t idesc, uint32_t bar_tmem_full,
-                                              uint32_t bar_stage_empty, uint32_t commit_stage, uint32_t peek_empty_bar, uint32_t peek_empty_par,
-                                              uint32_t peek_full_bar, uint32_t peek_full_par, uint32_t &rdy_empty, uint32_t &rdy_full) {
+// A whole 128-channel step of the issuer as one instruction sequence: eight MMAs (four per TMEM
+// slot), the three commits, and then a non-blocking test of the next step's barrier.  Barrier
+// instructions placed in front of the MMAs delayed them by a few hundred cycles each, so the only
+// poll of a step sits behind its MMAs, where the tensor pipe still has work queued.
+__device__ __forceinline__ void issueKStep(uint32_t tmem_d0, uint32_t tmem_d1, uint64_t da, uint64_t dw0, uint64_t dw1, uint32_t idesc,
+                                           uint32_t bar_tf0, uint32_t bar_tf1, uint32_t bar_stage_empty, uint32_t peek_bar, uint32_t peek_par,
+                                           uint32_t &ready_next) {
+    uint64_t da2 = da;
     asm volatile(
         "{\n"
-        " .reg .pred pe, pf, pacc, pnew, pc;\n"
-        " mbarrier.test_wait.parity.shared::cta.b64 pe, [%8], %9;\n"
-        " mbarrier.test_wait.parity.shared::cta.b64 pf, [%10], %11;\n"
-        " setp.ne.b32 pacc, %12, 0;\n"
-        " setp.eq.b32 pnew, %12, 0;\n"
-        " setp.ne.b32 pc, %7, 0;\n"
-        " tcgen05.mma.cta_group::2.kind::f8f6f4 [%2], %3, %4, %5, {%13, %13, %13, %13, %13, %13, %13, %13}, pnew;\n"
+        " .reg .pred pf, pacc, pnew;\n"
+        " setp.ne.b32 pacc, %13, 0;\n"
+        " setp.eq.b32 pnew, %13, 0;\n"
+        " tcgen05.mma.cta_group::2.kind::f8f6f4 [%1], %3, %4, %7, {%14, %14, %14, %14, %14, %14, %14, %14}, pnew;\n"
         " add.u64 %3, %3, 2;\n add.u64 %4, %4, 2;\n"
-        " tcgen05.mma.cta_group::2.kind::f8f6f4 [%2], %3, %4, %5, {%13, %13, %13, %13, %13, %13, %13, %13}, pacc;\n"
+        " tcgen05.mma.cta_group::2.kind::f8f6f4 [%1], %3, %4, %7, {%14, %14, %14, %14, %14, %14, %14, %14}, pacc;\n"
         " add.u64 %3, %3, 2;\n add.u64 %4, %4, 2;\n"
-        " tcgen05.mma.cta_group::2.kind::f8f6f4 [%2], %3, %4, %5, {%13, %13, %13, %13, %13, %13, %13, %13}, pacc;\n"
+        " tcgen05.mma.cta_group::2.kind::f8f6f4 [%1], %3, %4, %7, {%14, %14, %14, %14, %14, %14, %14, %14}, pacc;\n"
         " add.u64 %3, %3, 2;\n add.u64 %4, %4, 2;\n"
-        " tcgen05.mma.cta_group::2.kind::f8f6f4 [%2], %3, %4, %5, {%13, %13, %13, %13, %13, %13, %13, %13}, pacc;\n"
-        " tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%6], %14;\n"
-        " @pc tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%15], %14;\n"
-        " selp.u32 %0, 1, 0, pe;\n"
-        " selp.u32 %1, 1, 0, pf;\n"
+        " tcgen05.mma.cta_group::2.kind::f8f6f4 [%1], %3, %4, %7, {%14, %14, %14, %14, %14, %14, %14, %14}, pacc;\n"
+        " tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%8], %15;\n"
+        " tcgen05.mma.cta_group::2.kind::f8f6f4 [%2], %6, %5, %7, {%14, %14, %14, %14, %14, %14, %14, %14}, pnew;\n"
+        " add.u64 %6, %6, 2;\n add.u64 %5, %5, 2;\n"
+        " tcgen05.mma.cta_group::2.kind::f8f6f4 [%2], %6, %5, %7, {%14, %14, %14, %14, %14, %14, %14, %14}, pacc;\n"
+        " add.u64 %6, %6, 2;\n add.u64 %5, %5, 2;\n"
+        " tcgen05.mma.cta_group::2.kind::f8f6f4 [%2], %6, %5, %7, {%14, %14, %14, %14, %14, %14, %14, %14}, pacc;\n"
+        " add.u64 %6, %6, 2;\n add.u64 %5, %5, 2;\n"
+        " tcgen05.mma.cta_group::2.kind::f8f6f4 [%2], %6, %5, %7, {%14, %14, %14, %14, %14, %14, %14, %14}, pacc;\n"
+        " tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%9], %15;\n"
+        " tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%10], %15;\n"
+        " mbarrier.test_wait.parity.shared::cta.b64 pf, [%11], %12;\n"
+        " selp.u32 %0, 1, 0, pf;\n"
         "}\n"
-        : "=r"(rdy_empty), "=r"(rdy_full), "+r"(tmem_d), "+l"(da), "+l"(dw)
-        : "r"(idesc), "r"(bar_tmem_full), "r"(commit_stage), "r"(peek_empty_bar), "r"(peek_empty_par), "r"(peek_full_bar), "r"(peek_full_par),
-          "r"(1u), "r"(0u), "h"(static_cast<uint16_t>(3)), "r"(bar_stage_empty)
+        : "=r"(ready_next), "+r"(tmem_d0), "+r"(tmem_d1), "+l"(da), "+l"(dw0), "+l"(dw1), "+l"(da2)
+        : "r"(idesc), "r"(bar_tf0), "r"(bar_tf1), "r"(bar_stage_empty), "r"(peek_bar), "r"(peek_par), "r"(1u), "r"(0u),
+          "h"(static_cast<uint16_t>(3))
         : "memory");
 }
 
@@ -159,7 +166,7 @@ groupedGemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_con
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
-            mbarInit(&sh.full[s], 1);
+            mbarInit(&sh.full[s], 2); // producer (with the byte count) + slot watcher
             mbarInit(&sh.empty[s], 1);
         }
         for (int b = 0; b < kSlots; ++b) {
@@ -270,43 +277,44 @@ groupedGemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_con
             }
         } else if (warp == 1 && lane == 0 && cta == 0) {
             // ------------------------------------------------------------ MMA issuer (even CTA)
-            // Flat loop over half-steps j = 2 * (k-step counter) + h.  The barriers of half-step j + 1
-            // are tested before the MMAs of j are issued; the result is looked at one round later.
-            const uint32_t total_steps = 2u * static_cast<uint32_t>(my_tiles) * static_cast<uint32_t>(k_steps);
-            // Ring positions are kept as counters (no divisions on this thread's critical path).
-            uint32_t s = 0, full_par = 0;   // stage of the current k-step and the parity its "full" phase has
-            uint32_t slot = 0, empty_par = 1; // TMEM slot of the current half-step and the parity of "slot is free"
-            uint32_t rdy_full = mbarTest(&sh.full[0], 0) ? 1u : 0u;
-            uint32_t rdy_empty = mbarTest(&sh.tmemEmpty[0], 1) ? 1u : 0u;
-            const uint32_t full_bar0 = smemU32(&sh.full[0]), empty_bar0 = smemU32(&sh.empty[0]);
-            const uint32_t tfull_bar0 = smemU32(&sh.tmemFull[0]), tempty_bar0 = smemU32(&sh.tmemEmpty[0]);
+            // One barrier per 128-channel step: full[s] completes when both CTAs' bytes have landed
+            // (the producer's expect_tx arrival) and the step's two TMEM slots are free (the slot
+            // watcher's arrival), so this thread polls once per eight MMAs.
+            const uint32_t ksteps_total = static_cast<uint32_t>(my_tiles) * static_cast<uint32_t>(k_steps);
+            uint32_t s = 0, full_par = 0, sl = 0; // ring positions as counters: no divisions on this thread
+            uint32_t ready = 0;
+            const uint32_t full_bar0 = smemU32(&sh.full[0]), empty_bar0 = smemU32(&sh.empty[0]), tfull_bar0 = smemU32(&sh.tmemFull[0]);
             const uint64_t desc0 = smemDesc(smemU32(tiles));
-            for (uint32_t j = 0; j < total_steps; ++j) {
-                const uint32_t h = j & 1u;
-                if (h == 0 && !rdy_full && !mbarWait(&sh.full[s], full_par, abort_flag)) goto role_done;
-                if (!rdy_empty && !mbarWait(&sh.tmemEmpty[slot], empty_par, abort_flag)) goto role_done;
+            for (uint32_t it = 0; it < ksteps_total; ++it) {
+                if (!ready && !mbarWait(&sh.full[s], full_par, abort_flag)) goto role_done;
                 tcFenceAfter();
-                // Next half-step's ring positions: its slot, and (after the second half) the next stage.
-                const uint32_t nslot = (slot + 1) & (kSlots - 1);
-                const uint32_t nempty_par = empty_par ^ (nslot == 0 ? 1u : 0u);
-                uint32_t ns = s, nfull_par = full_par;
-                if (h == 1) {
-                    ns = s + 1;
-                    if (ns == kStages) {
-                        ns = 0;
-                        nfull_par ^= 1u;
-                    }
+                uint32_t ns = s + 1, nfull_par = full_par;
+                if (ns == kStages) {
+                    ns = 0;
+                    nfull_par ^= 1u;
                 }
                 const uint64_t da = desc0 + static_cast<uint64_t>((s * kStageBytes) >> 4);
-                const uint64_t dw = da + static_cast<uint64_t>((kATileBytes + h * kWBoxBytes) >> 4);
-                uint32_t peek_full = 1;
-                issueHalfStep(tmem + slot * BNS, da, dw, instrDescPair(), tfull_bar0 + slot * 8u, empty_bar0 + s * 8u, h, tempty_bar0 + nslot * 8u,
-                              nempty_par, full_bar0 + ns * 8u, nfull_par, rdy_empty, peek_full);
-                if (h == 1) rdy_full = peek_full; // after the first half the test looked at the current, already complete stage
-                slot = nslot;
-                empty_par = nempty_par;
+                const uint64_t dw0 = da + static_cast<uint64_t>(kATileBytes >> 4);
+                const uint64_t dw1 = da + static_cast<uint64_t>((kATileBytes + kWBoxBytes) >> 4);
+                issueKStep(tmem + sl * BNS, tmem + (sl + 1) * BNS, da, dw0, dw1, instrDescPair(), tfull_bar0 + sl * 8u, tfull_bar0 + (sl + 1) * 8u,
+                           empty_bar0 + s * 8u, full_bar0 + ns * 8u, nfull_par, ready);
+                sl ^= 2u;
                 s = ns;
                 full_par = nfull_par;
+            }
+        } else if (warp == 3 && lane == 0 && cta == 0) {
+            // ------------------------------------------------------------ slot watcher (even CTA)
+            // Waits until the promotion warps of both CTAs have handed back the two TMEM slots of a
+            // step and then adds its arrival to that step's full[] barrier.
+            const uint32_t ksteps_total = static_cast<uint32_t>(my_tiles) * static_cast<uint32_t>(k_steps);
+            uint32_t s = 0, sl = 0, e_par = 1;
+            for (uint32_t it = 0; it < ksteps_total; ++it) {
+                if (!mbarWait(&sh.tmemEmpty[sl], e_par, abort_flag)) goto role_done;
+                if (!mbarWait(&sh.tmemEmpty[sl + 1], e_par, abort_flag)) goto role_done;
+                mbarArrive(&sh.full[s]);
+                sl ^= 2u;
+                if (sl == 0) e_par ^= 1u;
+                if (++s == kStages) s = 0;
             }
         }
     role_done:;
