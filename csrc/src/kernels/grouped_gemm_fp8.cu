@@ -39,7 +39,6 @@ namespace {
 using namespace nixl_tc;
 
 constexpr int BM = 128, BN = 128, BK = 128; // tile; BK is also the scale granularity
-constexpr int UMMA_K = 32;                  // fp8: 32 bytes of K per instruction
 constexpr int kStages = 5;
 constexpr int kThreads = 384;              // 4 role warps + 8 promotion warps
 constexpr int kTileBytes = BM * BK;         // 16 KiB (fp8)
@@ -67,6 +66,33 @@ struct Shared {
 __device__ __forceinline__ constexpr uint32_t instrDesc() {
     return (1u << 4) | (0u << 7) | (0u << 10) | (0u << 15) | (0u << 16) | (static_cast<uint32_t>(BN >> 3) << 17) |
         (static_cast<uint32_t>(BM >> 4) << 24);
+}
+
+// One 128-channel step of the issuer as a single instruction sequence: four MMAs, the two
+// commits, then a non-blocking test of the next step's barrier.  Barrier instructions in front of
+// the MMAs delay them by a few hundred cycles each, so the step's only poll sits behind them.
+__device__ __forceinline__ void issueStep(uint32_t tmem_d, uint64_t da, uint64_t dw, uint32_t idesc, uint32_t bar_tmem_full, uint32_t bar_stage_empty,
+                                          uint32_t peek_bar, uint32_t peek_par, uint32_t &ready_next) {
+    asm volatile(
+        "{\n"
+        " .reg .pred pf, pacc, pnew;\n"
+        " setp.ne.b32 pacc, %9, 0;\n"
+        " setp.eq.b32 pnew, %9, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::f8f6f4 [%1], %2, %3, %4, {%10, %10, %10, %10}, pnew;\n"
+        " add.u64 %2, %2, 2;\n add.u64 %3, %3, 2;\n"
+        " tcgen05.mma.cta_group::1.kind::f8f6f4 [%1], %2, %3, %4, {%10, %10, %10, %10}, pacc;\n"
+        " add.u64 %2, %2, 2;\n add.u64 %3, %3, 2;\n"
+        " tcgen05.mma.cta_group::1.kind::f8f6f4 [%1], %2, %3, %4, {%10, %10, %10, %10}, pacc;\n"
+        " add.u64 %2, %2, 2;\n add.u64 %3, %3, 2;\n"
+        " tcgen05.mma.cta_group::1.kind::f8f6f4 [%1], %2, %3, %4, {%10, %10, %10, %10}, pacc;\n"
+        " tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%6];\n"
+        " tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%5];\n"
+        " mbarrier.test_wait.parity.shared::cta.b64 pf, [%7], %8;\n"
+        " selp.u32 %0, 1, 0, pf;\n"
+        "}\n"
+        : "=r"(ready_next), "+r"(tmem_d), "+l"(da), "+l"(dw)
+        : "r"(idesc), "r"(bar_tmem_full), "r"(bar_stage_empty), "r"(peek_bar), "r"(peek_par), "r"(1u), "r"(0u)
+        : "memory");
 }
 
 struct Tile {
@@ -97,7 +123,7 @@ groupedGemmKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
-            mbarInit(&sh.full[s], 1);
+            mbarInit(&sh.full[s], 2); // producer (with the byte count) + slot watcher
             mbarInit(&sh.empty[s], 1);
         }
         for (int b = 0; b < kAccBufs; ++b) {
@@ -198,28 +224,53 @@ groupedGemmKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
     producer_done:;
     } else if (warp == 1 && lane == 0) {
         // ---------------------------------------------------------------- MMA issuer
-        uint32_t it = 0;
-        Tile t;
-        for (int ti = blockIdx.x; tileAt(sh, p.groups, n_tiles, ti, t); ti += gridDim.x) {
-            for (int ks = 0; ks < k_steps; ++ks, ++it) {
-                const int s = it % kStages, buf = it % kAccBufs;
-                if (!mbarWait(&sh.tmemEmpty[buf], ((it / kAccBufs) & 1) ^ 1, abort_flag)) goto mma_done;
-                if (!mbarWait(&sh.full[s], (it / kStages) & 1, abort_flag)) goto mma_done;
-                tcFenceAfter();
-                const uint32_t a_addr = smemU32(tiles + s * kStageBytes);
-                const uint32_t w_addr = a_addr + kTileBytes;
-                const uint64_t da = smemDesc(a_addr), dw = smemDesc(w_addr);
-#pragma unroll
-                for (int k = 0; k < BK / UMMA_K; ++k) {
-                    // Advancing 32 bytes along K inside the swizzle atom = +2 in the 16-byte address field.
-                    tcMma(tmem + buf * BN, da + static_cast<uint64_t>(k * (UMMA_K >> 4)), dw + static_cast<uint64_t>(k * (UMMA_K >> 4)),
-                          instrDesc(), k > 0 ? 1u : 0u);
-                }
-                tcCommit(&sh.empty[s]);      // the stage may be refilled once these MMAs have read it
-                tcCommit(&sh.tmemFull[buf]); // and the accumulator is ready for promotion
+        // One barrier per step: full[s] completes when the stage's bytes have landed (producer) and
+        // the step's TMEM accumulator is free again (slot watcher), so this thread polls once per
+        // four MMAs, and that poll is started behind the previous step's MMAs.
+        int my_tiles = 0;
+        {
+            const int total = sh.tilePrefix[p.groups];
+            if (static_cast<int>(blockIdx.x) < total) my_tiles = (total - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
+        }
+        const uint32_t steps_total = static_cast<uint32_t>(my_tiles) * static_cast<uint32_t>(k_steps);
+        uint32_t s = 0, full_par = 0, buf = 0, ready = 0;
+        const uint32_t full_bar0 = smemU32(&sh.full[0]), empty_bar0 = smemU32(&sh.empty[0]), tfull_bar0 = smemU32(&sh.tmemFull[0]);
+        const uint64_t desc0 = smemDesc(smemU32(tiles));
+        for (uint32_t it = 0; it < steps_total; ++it) {
+            if (!ready && !mbarWait(&sh.full[s], full_par, abort_flag)) goto mma_done;
+            tcFenceAfter();
+            uint32_t ns = s + 1, nfull_par = full_par;
+            if (ns == kStages) {
+                ns = 0;
+                nfull_par ^= 1u;
             }
+            // Advancing 32 bytes along K inside the swizzle atom = +2 in the 16-byte address field (done in issueStep).
+            const uint64_t da = desc0 + static_cast<uint64_t>((s * kStageBytes) >> 4);
+            const uint64_t dw = da + static_cast<uint64_t>(kTileBytes >> 4);
+            issueStep(tmem + buf * BN, da, dw, instrDesc(), tfull_bar0 + buf * 8u, empty_bar0 + s * 8u, full_bar0 + ns * 8u, nfull_par, ready);
+            buf = (buf + 1) & (kAccBufs - 1);
+            s = ns;
+            full_par = nfull_par;
         }
     mma_done:;
+    } else if (warp == 3 && lane == 0) {
+        // ---------------------------------------------------------------- slot watcher
+        // Adds its arrival to a step's full[] barrier once the promotion warps have handed back the
+        // TMEM accumulator that step will write.
+        int my_tiles = 0;
+        {
+            const int total = sh.tilePrefix[p.groups];
+            if (static_cast<int>(blockIdx.x) < total) my_tiles = (total - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
+        }
+        const uint32_t steps_total = static_cast<uint32_t>(my_tiles) * static_cast<uint32_t>(k_steps);
+        uint32_t s = 0, buf = 0, e_par = 1;
+        for (uint32_t it = 0; it < steps_total; ++it) {
+            if (!mbarWait(&sh.tmemEmpty[buf], e_par, abort_flag)) break;
+            mbarArrive(&sh.full[s]);
+            buf = (buf + 1) & (kAccBufs - 1);
+            if (buf == 0) e_par ^= 1u;
+            if (++s == kStages) s = 0;
+        }
     } else if (warp >= 4) {
         // ---------------------------------------------------------------- promotion + epilogue
         const int q = warp & 3;            // TMEM lane quarter this warp may touch (fixed by warp id % 4)

@@ -52,12 +52,15 @@ constexpr int kStageBytes = kATileBytes + 2 * kWBoxBytes; // 32 KiB per CTA
 constexpr int kSlots = 4;
 constexpr int kTmemCols = kSlots * BNS;        // 512
 constexpr int kPromoWarps = 8;
+// A step's full[] barrier collects the producer's arrival (which carries both CTAs' byte count) and
+// one arrival from every promotion warp of the pair, sent when the warp has read the two TMEM
+// slots the step is going to overwrite (the slots of the step two before it).
+constexpr int kFullArrivals = 1 + 2 * kPromoWarps;
 
 struct Shared {
-    uint64_t full[kStages];       // used on the even CTA: both CTAs' bytes of a stage have landed
+    uint64_t full[kStages];       // used on the even CTA: a step may be issued (see kFullArrivals)
     uint64_t empty[kStages];      // per CTA: the MMAs that read the stage are done
-    uint64_t tmemFull[kSlots];    // per CTA: slot ready for promotion
-    uint64_t tmemEmpty[kSlots];   // used on the even CTA: all 16 promotion warps of the pair have read the slot
+    uint64_t tmemFull[2];         // per CTA: the two slots of an even / odd step are ready for promotion
     uint32_t tmemBase;
     int abort;
     int tilePrefix[kMaxGroups + 1];
@@ -93,41 +96,39 @@ __device__ __forceinline__ void tmaLoad2dPair(void *smem_dst, const CUtensorMap 
                  : "memory");
 }
 // A whole 128-channel step of the issuer as one instruction sequence: eight MMAs (four per TMEM
-// slot), the three commits, and then a non-blocking test of the next step's barrier.  Barrier
+// slot), the two commits, and then a non-blocking test of the next step's barrier.  Barrier
 // instructions placed in front of the MMAs delayed them by a few hundred cycles each, so the only
 // poll of a step sits behind its MMAs, where the tensor pipe still has work queued.
 __device__ __forceinline__ void issueKStep(uint32_t tmem_d0, uint32_t tmem_d1, uint64_t da, uint64_t dw0, uint64_t dw1, uint32_t idesc,
-                                           uint32_t bar_tf0, uint32_t bar_tf1, uint32_t bar_stage_empty, uint32_t peek_bar, uint32_t peek_par,
+                                           uint32_t bar_tmem_full, uint32_t bar_stage_empty, uint32_t peek_bar, uint32_t peek_par,
                                            uint32_t &ready_next) {
     uint64_t da2 = da;
     asm volatile(
         "{\n"
         " .reg .pred pf, pacc, pnew;\n"
-        " setp.ne.b32 pacc, %13, 0;\n"
-        " setp.eq.b32 pnew, %13, 0;\n"
-        " tcgen05.mma.cta_group::2.kind::f8f6f4 [%1], %3, %4, %7, {%14, %14, %14, %14, %14, %14, %14, %14}, pnew;\n"
+        " setp.ne.b32 pacc, %12, 0;\n"
+        " setp.eq.b32 pnew, %12, 0;\n"
+        " tcgen05.mma.cta_group::2.kind::f8f6f4 [%1], %3, %4, %7, {%13, %13, %13, %13, %13, %13, %13, %13}, pnew;\n"
         " add.u64 %3, %3, 2;\n add.u64 %4, %4, 2;\n"
-        " tcgen05.mma.cta_group::2.kind::f8f6f4 [%1], %3, %4, %7, {%14, %14, %14, %14, %14, %14, %14, %14}, pacc;\n"
+        " tcgen05.mma.cta_group::2.kind::f8f6f4 [%1], %3, %4, %7, {%13, %13, %13, %13, %13, %13, %13, %13}, pacc;\n"
         " add.u64 %3, %3, 2;\n add.u64 %4, %4, 2;\n"
-        " tcgen05.mma.cta_group::2.kind::f8f6f4 [%1], %3, %4, %7, {%14, %14, %14, %14, %14, %14, %14, %14}, pacc;\n"
+        " tcgen05.mma.cta_group::2.kind::f8f6f4 [%1], %3, %4, %7, {%13, %13, %13, %13, %13, %13, %13, %13}, pacc;\n"
         " add.u64 %3, %3, 2;\n add.u64 %4, %4, 2;\n"
-        " tcgen05.mma.cta_group::2.kind::f8f6f4 [%1], %3, %4, %7, {%14, %14, %14, %14, %14, %14, %14, %14}, pacc;\n"
-        " tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%8], %15;\n"
-        " tcgen05.mma.cta_group::2.kind::f8f6f4 [%2], %6, %5, %7, {%14, %14, %14, %14, %14, %14, %14, %14}, pnew;\n"
+        " tcgen05.mma.cta_group::2.kind::f8f6f4 [%1], %3, %4, %7, {%13, %13, %13, %13, %13, %13, %13, %13}, pacc;\n"
+        " tcgen05.mma.cta_group::2.kind::f8f6f4 [%2], %6, %5, %7, {%13, %13, %13, %13, %13, %13, %13, %13}, pnew;\n"
         " add.u64 %6, %6, 2;\n add.u64 %5, %5, 2;\n"
-        " tcgen05.mma.cta_group::2.kind::f8f6f4 [%2], %6, %5, %7, {%14, %14, %14, %14, %14, %14, %14, %14}, pacc;\n"
+        " tcgen05.mma.cta_group::2.kind::f8f6f4 [%2], %6, %5, %7, {%13, %13, %13, %13, %13, %13, %13, %13}, pacc;\n"
         " add.u64 %6, %6, 2;\n add.u64 %5, %5, 2;\n"
-        " tcgen05.mma.cta_group::2.kind::f8f6f4 [%2], %6, %5, %7, {%14, %14, %14, %14, %14, %14, %14, %14}, pacc;\n"
+        " tcgen05.mma.cta_group::2.kind::f8f6f4 [%2], %6, %5, %7, {%13, %13, %13, %13, %13, %13, %13, %13}, pacc;\n"
         " add.u64 %6, %6, 2;\n add.u64 %5, %5, 2;\n"
-        " tcgen05.mma.cta_group::2.kind::f8f6f4 [%2], %6, %5, %7, {%14, %14, %14, %14, %14, %14, %14, %14}, pacc;\n"
-        " tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%9], %15;\n"
-        " tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%10], %15;\n"
-        " mbarrier.test_wait.parity.shared::cta.b64 pf, [%11], %12;\n"
+        " tcgen05.mma.cta_group::2.kind::f8f6f4 [%2], %6, %5, %7, {%13, %13, %13, %13, %13, %13, %13, %13}, pacc;\n"
+        " tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%8], %14;\n"
+        " tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%9], %14;\n"
+        " mbarrier.test_wait.parity.shared::cta.b64 pf, [%10], %11;\n"
         " selp.u32 %0, 1, 0, pf;\n"
         "}\n"
         : "=r"(ready_next), "+r"(tmem_d0), "+r"(tmem_d1), "+l"(da), "+l"(dw0), "+l"(dw1), "+l"(da2)
-        : "r"(idesc), "r"(bar_tf0), "r"(bar_tf1), "r"(bar_stage_empty), "r"(peek_bar), "r"(peek_par), "r"(1u), "r"(0u),
-          "h"(static_cast<uint16_t>(3))
+        : "r"(idesc), "r"(bar_tmem_full), "r"(bar_stage_empty), "r"(peek_bar), "r"(peek_par), "r"(1u), "r"(0u), "h"(static_cast<uint16_t>(3))
         : "memory");
 }
 
@@ -166,13 +167,14 @@ groupedGemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_con
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
-            mbarInit(&sh.full[s], 2); // producer (with the byte count) + slot watcher
+            mbarInit(&sh.full[s], kFullArrivals);
             mbarInit(&sh.empty[s], 1);
         }
-        for (int b = 0; b < kSlots; ++b) {
-            mbarInit(&sh.tmemFull[b], 1);
-            mbarInit(&sh.tmemEmpty[b], 2 * kPromoWarps);
-        }
+        mbarInit(&sh.tmemFull[0], 1);
+        mbarInit(&sh.tmemFull[1], 1);
+        // The first two steps find their slots free: stand in for the promotion warps' arrivals.
+        for (int s = 0; s < 2; ++s)
+            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0], %1;" ::"r"(smemU32(&sh.full[s])), "r"(2 * kPromoWarps) : "memory");
         sh.abort = 0;
         int run = 0;
         if (p.counts_flag) {
@@ -277,9 +279,8 @@ groupedGemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_con
             }
         } else if (warp == 1 && lane == 0 && cta == 0) {
             // ------------------------------------------------------------ MMA issuer (even CTA)
-            // One barrier per 128-channel step: full[s] completes when both CTAs' bytes have landed
-            // (the producer's expect_tx arrival) and the step's two TMEM slots are free (the slot
-            // watcher's arrival), so this thread polls once per eight MMAs.
+            // One poll per eight MMAs: full[s] completes when both CTAs' bytes have landed and all
+            // promotion warps of the pair have read the step's two TMEM slots.
             const uint32_t ksteps_total = static_cast<uint32_t>(my_tiles) * static_cast<uint32_t>(k_steps);
             uint32_t s = 0, full_par = 0, sl = 0; // ring positions as counters: no divisions on this thread
             uint32_t ready = 0;
@@ -296,25 +297,11 @@ groupedGemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_con
                 const uint64_t da = desc0 + static_cast<uint64_t>((s * kStageBytes) >> 4);
                 const uint64_t dw0 = da + static_cast<uint64_t>(kATileBytes >> 4);
                 const uint64_t dw1 = da + static_cast<uint64_t>((kATileBytes + kWBoxBytes) >> 4);
-                issueKStep(tmem + sl * BNS, tmem + (sl + 1) * BNS, da, dw0, dw1, instrDescPair(), tfull_bar0 + sl * 8u, tfull_bar0 + (sl + 1) * 8u,
-                           empty_bar0 + s * 8u, full_bar0 + ns * 8u, nfull_par, ready);
+                issueKStep(tmem + sl * BNS, tmem + (sl + 1) * BNS, da, dw0, dw1, instrDescPair(), tfull_bar0 + (sl >> 1) * 8u, empty_bar0 + s * 8u,
+                           full_bar0 + ns * 8u, nfull_par, ready);
                 sl ^= 2u;
                 s = ns;
                 full_par = nfull_par;
-            }
-        } else if (warp == 3 && lane == 0 && cta == 0) {
-            // ------------------------------------------------------------ slot watcher (even CTA)
-            // Waits until the promotion warps of both CTAs have handed back the two TMEM slots of a
-            // step and then adds its arrival to that step's full[] barrier.
-            const uint32_t ksteps_total = static_cast<uint32_t>(my_tiles) * static_cast<uint32_t>(k_steps);
-            uint32_t s = 0, sl = 0, e_par = 1;
-            for (uint32_t it = 0; it < ksteps_total; ++it) {
-                if (!mbarWait(&sh.tmemEmpty[sl], e_par, abort_flag)) goto role_done;
-                if (!mbarWait(&sh.tmemEmpty[sl + 1], e_par, abort_flag)) goto role_done;
-                mbarArrive(&sh.full[s]);
-                sl ^= 2u;
-                if (sl == 0) e_par ^= 1u;
-                if (++s == kStages) s = 0;
             }
         }
     role_done:;
@@ -324,9 +311,10 @@ groupedGemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_con
         const int q = warp & 3;
         const int part = (warp - 4) >> 2; // which 64 of a slot's 128 columns
         const int row_in_tile = q * 32 + lane;
-        const uint32_t empty0 = mapToCta(smemU32(&sh.tmemEmpty[0]), 0);
+        const uint32_t full0 = mapToCta(smemU32(&sh.full[0]), 0);
         const uint32_t lane_base = tmem + (static_cast<uint32_t>(q * 32) << 16) + part * 64;
-        uint32_t j = 0; // half-step counter, same numbering as the issuer's
+        uint32_t it = 0;      // step counter, same numbering as the issuer's
+        uint32_t s2 = 2;      // stage of step it + 2, the step that reuses this step's slots
         Tile t;
         const int n_blocks = p.N / 128;
         bool rdy = false;
@@ -353,44 +341,47 @@ groupedGemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_con
             }
             for (int ks0 = 0; ks0 < k_steps && ok; ks0 += kPrefetch) {
 #pragma unroll
-                for (int i = 0; i < kPrefetch; ++i) {
+                for (int i = 0; i < kPrefetch; ++i, ++it) {
                     const int ks = ks0 + i;
                     if (ks >= k_steps) break;
                     const float s0 = ring_a[i] * ring_w0[i], s1 = ring_a[i] * ring_w1[i];
                     const int nxt = ks + kPrefetch;
-#pragma unroll
-                    for (int h = 0; h < 2; ++h, ++j) {
-                        const uint32_t slot = j % kSlots;
-                        if (!rdy && !mbarWait(&sh.tmemFull[slot], (j / kSlots) & 1, abort_flag)) {
-                            ok = false;
-                            break;
-                        }
-                        tcFenceAfter();
-                        float v0[32], v1[32];
-                        tmemLoad32(lane_base + slot * BNS, v0);
-                        tmemLoad32(lane_base + slot * BNS + 32, v1);
-                        // While the loads are in flight, look at the next slot's barrier.
-                        rdy = mbarTest(&sh.tmemFull[(j + 1) % kSlots], ((j + 1) / kSlots) & 1);
-                        tmemLoadWait(v0);
-                        tmemLoadWait(v1);
-                        // This warp's share of the slot is in registers: hand it back to the MMA issuer.
-                        tcFenceBefore();
-                        __syncwarp();
-                        if (lane == 0) mbarArriveCluster(empty0 + slot * 8u);
-                        // The arrive has release semantics and would wait for loads issued before it:
-                        // the scale prefetch therefore goes after it, not before.
-                        if (h == 0 && nxt < k_steps) {
-                            ring_a[i] = valid ? __ldg(sa_row + nxt) : 0.f;
-                            ring_w0[i] = __ldg(sw0 + nxt);
-                            ring_w1[i] = __ldg(sw1 + nxt);
-                        }
-                        const float sc = h == 0 ? s0 : s1;
-#pragma unroll
-                        for (int e = 0; e < 32; ++e) acc[h * 64 + e] = fmaf(v0[e], sc, acc[h * 64 + e]);
-#pragma unroll
-                        for (int e = 0; e < 32; ++e) acc[h * 64 + 32 + e] = fmaf(v1[e], sc, acc[h * 64 + 32 + e]);
+                    const uint32_t kp = it & 1u, sl = kp * 2u;
+                    if (!rdy && !mbarWait(&sh.tmemFull[kp], (it >> 1) & 1, abort_flag)) {
+                        ok = false;
+                        break;
                     }
-                    if (!ok) break;
+                    tcFenceAfter();
+                    float v0[32], v1[32];
+                    tmemLoad32(lane_base + sl * BNS, v0);
+                    tmemLoad32(lane_base + sl * BNS + 32, v1);
+                    tmemLoadWait(v0);
+                    tmemLoadWait(v1);
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) acc[e] = fmaf(v0[e], s0, acc[e]);
+                    tmemLoad32(lane_base + (sl + 1) * BNS, v0); // second slot's loads run behind the first slot's FMAs
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) acc[32 + e] = fmaf(v1[e], s0, acc[32 + e]);
+                    tmemLoad32(lane_base + (sl + 1) * BNS + 32, v1);
+                    // While those are in flight, look at the next step's barrier.
+                    rdy = mbarTest(&sh.tmemFull[kp ^ 1u], ((it + 1) >> 1) & 1);
+                    tmemLoadWait(v0);
+                    tmemLoadWait(v1);
+                    // Both slots of this step are in registers: tell the step that reuses them.
+                    tcFenceBefore();
+                    __syncwarp();
+                    if (lane == 0) mbarArriveCluster(full0 + s2 * 8u);
+                    if (++s2 == kStages) s2 = 0;
+                    // The scale prefetch goes behind the arrive (loads issued before it would hold it up).
+                    if (nxt < k_steps) {
+                        ring_a[i] = valid ? __ldg(sa_row + nxt) : 0.f;
+                        ring_w0[i] = __ldg(sw0 + nxt);
+                        ring_w1[i] = __ldg(sw1 + nxt);
+                    }
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) acc[64 + e] = fmaf(v0[e], s1, acc[64 + e]);
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) acc[96 + e] = fmaf(v1[e], s1, acc[96 + e]);
                 }
             }
             if (!ok) break;
