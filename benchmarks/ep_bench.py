@@ -200,7 +200,8 @@ def main():
             st = torch.zeros(1, dtype=torch.int32, device=dev)
 
             def gemm():
-                grouped_gemm_fp8(state["rx"], state["sc"], wq, sw, state["h"].expert_offsets[:El].contiguous(), state["h"].recv_count, out=d, status=st)
+                grouped_gemm_fp8(state["rx"], state["sc"], wq, sw, state["h"].expert_offsets[:El].contiguous(), state["h"].recv_count, out=d, status=st,
+                                 tile_mode=2 if compact and args.inter % 256 == 0 else 1)
 
             def fused():
                 # dispatch on a side stream with a small grid; the GEMM consumes arrivals tile by tile

@@ -8,8 +8,13 @@
 //   warp 0  TMA producer   cp.async.bulk.tensor (2-D, 128-byte swizzle) of a 128x128 A tile and a
 //                          128x128 W tile per 128-channel step into a 5-stage shared-memory ring
 //   warp 1  MMA issuer     4 x tcgen05.mma.kind::f8f6f4 (M128 N128 K32) per step into one of four
-//                          TMEM accumulators (128 lanes x 128 fp32 columns each: all 512 columns)
+//                          TMEM accumulators (128 lanes x 128 fp32 columns each: all 512 columns).
+//                          It polls one barrier per step, with a non-blocking test issued behind
+//                          the previous step's MMAs (barrier instructions in front of the MMAs
+//                          delay them by hundreds of cycles)
 //   warp 2  TMEM allocator
+//   warp 3  slot watcher   forwards "accumulator free again" into the step's full[] barrier, so
+//                          that barrier alone tells the issuer that a step may go
 //   warps 4-11 promotion + epilogue (two warps per TMEM lane quarter, 64 columns each):
 //                          tcgen05.ld the step's partial sums, multiply by
 //                          scaleA[row, step] * scaleW[g, n-block, step], accumulate in registers

@@ -6,23 +6,31 @@
 // issues M256 N128 K32 MMAs that read both CTAs' shared memory and write both CTAs' TMEM, and each
 // CTA promotes and stores its own 128 rows.
 //
-// A 128-channel step is issued as two half-steps of four MMAs, one per 128-column half of the
-// tile, each into its own 128-column TMEM slot (four slots in flight), so a slot is handed to the
-// promotion warps, read and handed back while the following half-steps execute.  To make the two
-// N = 128 instructions cover contiguous columns, CTA c keeps W rows [64c, 64c+64) of the left
-// half and of the right half of the tile (two 64-row TMA boxes).
+// A 128-channel step is eight MMAs: four into one 128-column TMEM slot for the left half of the
+// tile's columns and four into a second slot for the right half; two steps (four slots, all of
+// TMEM) are in flight.  To make the two N = 128 instruction groups cover contiguous columns, CTA c
+// keeps W rows [64c, 64c+64) of the left half and of the right half (two 64-row TMA boxes).
 //
-// The tensor pipe only stays busy while the issuing thread keeps feeding it: an MMA's issue
-// returns about when its predecessor starts, so any latency between two groups of MMAs idles the
-// pipe.  The issuer therefore polls the barriers of the next half-step (non-blocking test) before
-// it issues the current one, and the promotion warps do the same for their next slot.
+// What bounds this kernel is not the tensor pipe (eight MMAs take 512 cycles) but the hand-offs
+// around it, so they are kept to a minimum:
+//  * the issuing thread polls one barrier per step.  full[s] collects the producer's arrival (with
+//    both CTAs' byte count) and one arrival from each of the pair's sixteen promotion warps, sent
+//    when the warp has read the two slots the step will overwrite;
+//  * that poll is a non-blocking test issued behind the previous step's MMAs: barrier instructions
+//    in front of the MMAs delayed them by a few hundred cycles each;
+//  * promotion warps poll once per step too (one commit covers both slots), arrive with relaxed
+//    semantics (a cluster-scope release cost several hundred cycles per arrive) and fetch their
+//    scales behind the arrive;
+//  * ring positions are counters, not divisions, on the single-thread roles.
 //
 //   warp 0      TMA producer (both CTAs; completion bytes are counted on the even CTA's barrier)
 //   warp 1      MMA issuer (even CTA only); commits are multicast to both CTAs' barriers
 //   warp 2      TMEM allocator (512 columns, cta_group::2)
 //   warps 4-11  promotion + epilogue: lane quarter q = warp % 4, 64-column part (warp - 4) / 4 of
 //               every slot; 128 fp32 accumulators per thread, so these warps raise their register
-//               budget (setmaxnreg) with what the role warps give back
+//               budget (setmaxnreg 232) with what the role warps give back (setmaxnreg 40; the two
+//               budgets must leave the register file some slack, an exact fit never got its
+//               increase granted)
 //
 // TMA loads read this GPU's memory only and carry no cluster multicast.  Every wait is bounded.
 #include <cuda.h>
