@@ -1,0 +1,136 @@
+"""``python -m benchmarks.kvbench <command>``
+
+    kvcache                 KV sizes of a model under a parallel layout
+    plan                    nixlbench command lines for that geometry
+    profile                 run them
+    matgen                  traffic matrices + YAML of a prefill -> decode workload
+    ct-perftest             time one traffic pattern       (under torchrun, one rank per matrix row)
+    sequential-ct-perftest  run a list of patterns in order (under torchrun)
+    kv-transfer             fused paged-KV transfer benchmark (under torchrun for more than one GPU)
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+
+def _parallel(ns):
+    from nixl_b200.models import ParallelConfig
+
+    return ParallelConfig(tp=ns.tp, pp=ns.pp, cp=ns.cp)
+
+
+def _add_model_args(p):
+    p.add_argument("--model", default="llama-3-8b")
+    p.add_argument("--isl", type=int, default=4096, help="prompt length in tokens")
+    p.add_argument("--num-requests", type=int, default=1)
+    p.add_argument("--tp", type=int, default=1)
+    p.add_argument("--pp", type=int, default=1)
+    p.add_argument("--cp", type=int, default=1)
+    p.add_argument("--page-size", type=int, default=16)
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(prog="kvbench", description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    sub = ap.add_subparsers(dest="cmd", required=True)
+
+    p = sub.add_parser("kvcache")
+    _add_model_args(p)
+    p = sub.add_parser("plan")
+    _add_model_args(p)
+    for q in (p, sub.add_parser("profile")):
+        if q is not p:
+            _add_model_args(q)
+        q.add_argument("--backend", default="NVLINK")
+        q.add_argument("--mem", default="VRAM")
+        q.add_argument("--op", default="WRITE")
+        q.add_argument("--src-dev", type=int, default=0)
+        q.add_argument("--dst-dev", type=int, default=1)
+        q.add_argument("--iters", type=int, default=200)
+        q.add_argument("--extra", default="", help="appended to every nixlbench command")
+
+    p = sub.add_parser("matgen")
+    p.add_argument("--model", default="llama-3-8b")
+    p.add_argument("--num-user-requests", type=int, default=16)
+    p.add_argument("--batch-size", type=int, default=1)
+    p.add_argument("--isl-mean", type=int, default=16000)
+    p.add_argument("--isl-scale", type=int, default=10000)
+    p.add_argument("--min-isl", type=int, default=1000)
+    p.add_argument("--max-isl", type=int, default=128000)
+    p.add_argument("--prefill-tp", type=int, default=4)
+    p.add_argument("--prefill-cp", type=int, default=1)
+    p.add_argument("--decode-tp", type=int, default=4)
+    p.add_argument("--world-size", type=int, default=8)
+    p.add_argument("--seed", type=int, default=0)
+    p.add_argument("--mem-type", default="cuda")
+    p.add_argument("--xfer-op", default="WRITE")
+    p.add_argument("--results-dir", required=True)
+
+    for name in ("ct-perftest", "sequential-ct-perftest"):
+        p = sub.add_parser(name)
+        p.add_argument("config", help="YAML file (see benchmarks/kvbench/README.md)")
+        p.add_argument("--backend", default="NVLINK")
+        p.add_argument("--json-output-path")
+        p.add_argument("--no-sleep", action="store_true", help="ignore sleep_before/after_launch_sec")
+
+    sub.add_parser("kv-transfer", add_help=False)
+
+    if argv is None:
+        argv = sys.argv[1:]
+    if argv and argv[0] == "kv-transfer":
+        from . import kv_transfer
+
+        sys.argv = ["kv-transfer"] + list(argv[1:])
+        return kv_transfer.main()
+    ns = ap.parse_args(argv)
+
+    if ns.cmd == "kvcache":
+        from .plan import kvcache_report
+
+        print(json.dumps(kvcache_report(ns.model, ns.isl, ns.num_requests, _parallel(ns), ns.page_size), indent=1))
+    elif ns.cmd in ("plan", "profile"):
+        from .plan import plan_commands, profile
+
+        cmds = plan_commands(ns.model, ns.isl, ns.num_requests, _parallel(ns), ns.page_size, ns.backend, ns.mem, ns.op, ns.src_dev, ns.dst_dev,
+                             ns.iters, ns.extra)
+        if ns.cmd == "plan":
+            print("\n".join(cmds))
+        else:
+            for r in profile(cmds):
+                print("$", r["cmd"])
+                print(r["stdout"] or r["stderr"])
+    elif ns.cmd == "matgen":
+        from nixl_b200.models import ParallelConfig
+
+        from .matgen import TaskConfig, generate, write_workload
+
+        task = TaskConfig(ns.isl_mean, ns.isl_scale, ns.min_isl, ns.max_isl, ns.batch_size)
+        mats = generate(ns.model, ns.num_user_requests, task, ParallelConfig(tp=ns.prefill_tp, cp=ns.prefill_cp), ParallelConfig(tp=ns.decode_tp),
+                        ns.world_size, ns.seed)
+        print(write_workload(mats, ns.results_dir, ns.mem_type, ns.xfer_op))
+    else:
+        import yaml
+
+        from .perftest import ct_perftest, sequential_ct_perftest
+        from .traffic import pattern_from_dict
+
+        with open(ns.config) as f:
+            cfg = yaml.safe_load(f)
+        base = os.path.dirname(os.path.abspath(ns.config))
+        if ns.cmd == "ct-perftest":
+            tp = pattern_from_dict(cfg["traffic_pattern"], base)
+            ct_perftest(tp, int(cfg.get("iters", 50)), int(cfg.get("warmup_iters", 10)), ns.backend, ns.json_output_path)
+        else:
+            tps = [pattern_from_dict(d, base) for d in cfg["traffic_patterns"]]
+            sequential_ct_perftest(tps, ns.backend, ns.json_output_path, honor_sleep=not ns.no_sleep)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

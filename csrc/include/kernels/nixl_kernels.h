@@ -147,6 +147,10 @@ typedef struct NixlEpCombineParams {
     const int32_t *send_row;    /* [T][K] */
 } NixlEpCombineParams;
 
+/* Routing statistics of topk_idx [T][K]: tokens per destination rank (a token counts once per rank),
+ * (token, k) pairs per expert, and in_rank [T][R] (1 if the token has an expert on that rank). */
+int nixl_ep_layout_launch(const int64_t *topk_idx, int32_t T, int32_t K, int32_t E, int32_t R, int32_t *per_rank, int32_t *per_expert,
+                          uint8_t *in_rank, void *stream);
 int nixl_ep_dispatch_launch(const NixlEpDispatchParams *params, void *stream);
 int nixl_ep_combine_launch(const NixlEpCombineParams *params, void *stream);
 /* Barrier across ranks through the symmetric buffers (bounded): flag slot `slot` of

@@ -555,6 +555,40 @@ __global__ void __launch_bounds__(kThreads) epCombineKernel(const __grid_constan
     }
 }
 
+// ------------------------------------------------------------------ dispatch layout (counts only)
+
+// Per-rank and per-expert token counts and the token x rank membership matrix of a routing table
+// (what the reference computes in examples/device/ep/csrc/kernels/layout.cu before a
+// high-throughput dispatch).  Dispatch here does its own counting; this kernel serves callers that
+// want the numbers up front (capacity planning, load-balance statistics).
+__global__ void __launch_bounds__(256) epLayoutKernel(const int64_t *topk_idx, int T, int K, int E, int R, int *per_rank, int *per_expert,
+                                                      unsigned char *in_rank) {
+    extern __shared__ int hist[]; // [E] experts, then [R] ranks
+    int *h_expert = hist, *h_rank = hist + E;
+    for (int i = threadIdx.x; i < E + R; i += blockDim.x) hist[i] = 0;
+    __syncthreads();
+    const int El = E / R;
+    for (int t = blockIdx.x * blockDim.x + threadIdx.x; t < T; t += gridDim.x * blockDim.x) {
+        unsigned long long mask = 0;
+        for (int k = 0; k < K; ++k) {
+            const long long e = topk_idx[static_cast<long long>(t) * K + k];
+            if (e < 0 || e >= E) continue;
+            atomicAdd(h_expert + e, 1);
+            mask |= 1ull << (static_cast<int>(e) / El);
+        }
+        for (int r = 0; r < R; ++r) {
+            const bool in = (mask >> r) & 1ull;
+            in_rank[static_cast<long long>(t) * R + r] = in ? 1 : 0;
+            if (in) atomicAdd(h_rank + r, 1);
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < E; i += blockDim.x)
+        if (h_expert[i]) atomicAdd(per_expert + i, h_expert[i]);
+    for (int i = threadIdx.x; i < R; i += blockDim.x)
+        if (h_rank[i]) atomicAdd(per_rank + i, h_rank[i]);
+}
+
 // ------------------------------------------------------------------ barrier across ranks
 
 __global__ void epBarrierKernel(const void *peers, int64_t off_flags, int R, int rank, uint64_t epoch, uint64_t timeout_ns, int *status,
@@ -628,5 +662,18 @@ extern "C" int nixl_ep_barrier_launch(const void *peers, int64_t off_flags, int3
                                       int32_t *status, int32_t *mask, void *stream) {
     if (!peers || R <= 0 || R > kMaxRanks || !status || !mask) return cudaErrorInvalidValue;
     epBarrierKernel<<<1, kMaxRanks, 0, static_cast<cudaStream_t>(stream)>>>(peers, off_flags, R, rank, epoch, timeout_ns, status, mask);
+    return cudaGetLastError();
+}
+
+extern "C" int nixl_ep_layout_launch(const int64_t *topk_idx, int32_t T, int32_t K, int32_t E, int32_t R, int32_t *per_rank, int32_t *per_expert,
+                                     uint8_t *in_rank, void *stream) {
+    if (!topk_idx || !per_rank || !per_expert || !in_rank || T < 0 || K <= 0 || E <= 0 || R <= 0 || R > kMaxRanks || E % R) return cudaErrorInvalidValue;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    cudaError_t e = cudaMemsetAsync(per_rank, 0, sizeof(int32_t) * R, st);
+    if (e == cudaSuccess) e = cudaMemsetAsync(per_expert, 0, sizeof(int32_t) * E, st);
+    if (e != cudaSuccess) return e;
+    if (T == 0) return cudaSuccess;
+    const int blocks = (T + 255) / 256 < 148 ? (T + 255) / 256 : 148;
+    epLayoutKernel<<<blocks, 256, sizeof(int) * (E + R), st>>>(topk_idx, T, K, E, R, per_rank, per_expert, in_rank);
     return cudaGetLastError();
 }

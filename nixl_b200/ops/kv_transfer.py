@@ -8,7 +8,7 @@ and scatters by the receiver's block table, signalling completion in the receive
 
 The reference moves KV caches as descriptor lists (its kvbench tool); the descriptor path
 remains available through ``nixl_agent.initialize_xfer`` and is the baseline in
-``benchmarks/kvbench.py``.
+``benchmarks/kvbench/kv_transfer.py``.
 """
 from __future__ import annotations
 

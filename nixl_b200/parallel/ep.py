@@ -425,6 +425,40 @@ class Buffer:
         keep = (x, topk_idx, p)  # the hook may launch later: keep inputs alive
         return recv_x, scales, handle, hook, keep
 
+    # ------------------------------------------------------------------ routing statistics, reference-named entry points
+
+    def get_dispatch_layout(self, topk_idx: torch.Tensor, num_experts: Optional[int] = None):
+        """Routing statistics of ``topk_idx [tokens, topk]``, as the reference's
+        ``Buffer.get_dispatch_layout`` returns them: ``(num_tokens_per_rank [ranks] int32,
+        num_tokens_per_rdma_rank (None: one NVLink domain), num_tokens_per_expert [experts] int32,
+        is_token_in_rank [tokens, ranks] bool, event)``.  Dispatch does not need them (it counts by
+        itself); they are for capacity planning and load statistics."""
+        E = num_experts or self.num_experts
+        T, K = topk_idx.shape
+        with torch.cuda.device(self.device):
+            per_rank = torch.empty(self.num_ranks, dtype=torch.int32, device=self.device)
+            per_expert = torch.empty(E, dtype=torch.int32, device=self.device)
+            in_rank = torch.empty(T, self.num_ranks, dtype=torch.bool, device=self.device)
+            fn = _lib.lib().nixl_ep_layout_launch
+            fn.argtypes = [ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p,
+                           ctypes.c_void_p, ctypes.c_void_p]
+            fn.restype = ctypes.c_int
+            _lib.check(fn(topk_idx.data_ptr(), T, K, E, self.num_ranks, per_rank.data_ptr(), per_expert.data_ptr(), in_rank.data_ptr(),
+                          ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)), "nixl_ep_layout_launch")
+        return per_rank, None, per_expert, in_rank, EventOverlap(None)
+
+    def ht_dispatch(self, x: torch.Tensor, topk_idx: torch.Tensor, topk_weights: Optional[torch.Tensor] = None, use_fp8: bool = True, **_ignored):
+        """The reference's high-throughput dispatch name.  Its multi-node forwarding design needs more
+        than one NVLink domain; on one NVSwitch box this is the throughput-mode ``dispatch`` (rows
+        arrive packed per local expert, not per token).  Returns ``(recv_x | (recv_x, scales),
+        num_recv_tokens_per_expert int32 [local_experts], handle, event)``."""
+        recv_x, scales, handle = self.dispatch(x, topk_idx, use_fp8=use_fp8)
+        return ((recv_x, scales) if use_fp8 else recv_x), handle.recv_count, handle, EventOverlap(None)
+
+    def ht_combine(self, x: torch.Tensor, handle: EPHandle, topk_idx: torch.Tensor, topk_weights: torch.Tensor, **_ignored):
+        """Counterpart of ``ht_dispatch``: ``(combined_x, event)``."""
+        return self.combine(x, topk_idx, topk_weights, handle), EventOverlap(None)
+
     # ------------------------------------------------------------------ low-latency mode
 
     def low_latency_dispatch(

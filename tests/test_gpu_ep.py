@@ -188,6 +188,23 @@ def test_throughput_only_buffer_is_smaller_and_rejects_low_latency_calls():
     assert int(h.recv_count.sum()) == 128 and small.status == 0
 
 
+def test_dispatch_layout_counts_match_torch():
+    dev = torch.device("cuda", 0)
+    buf = Buffer(0, 4, 32, 1024, 300, 6, device=dev, low_latency_mode=False)  # statistics need no peers
+    g = torch.Generator(device=dev).manual_seed(3)
+    idx = torch.stack([torch.randperm(32, device=dev, generator=g)[:6] for _ in range(300)]).long()
+    idx[::7, 2] = -1
+    per_rank, _, per_expert, in_rank, _ = buf.get_dispatch_layout(idx)
+    torch.cuda.synchronize()
+    valid = idx >= 0
+    want_expert = torch.bincount(idx[valid], minlength=32)
+    ranks = torch.where(valid, idx // 8, torch.full_like(idx, -1))
+    want_in = torch.stack([(ranks == r).any(dim=1) for r in range(4)], dim=1)
+    assert torch.equal(per_expert.long(), want_expert)
+    assert torch.equal(in_rank, want_in)
+    assert torch.equal(per_rank.long(), want_in.sum(dim=0))
+
+
 def test_silent_rank_is_masked_not_waited_for():
     """Rank 1 exists but never launches: rank 0's waits run out (200 ms), rank 1 is masked and
     the status word says so; the GPU is idle again afterwards."""
