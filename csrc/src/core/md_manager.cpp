@@ -5,6 +5,7 @@
 #include <algorithm>
 
 #include "core/md_p2p.h"
+#include "core/md_etcd.h"
 #include "core/md_tcpstore.h"
 #include "utils/config.h"
 #include "utils/log.h"
@@ -71,8 +72,12 @@ nixlMetadataManager::nixlMetadataManager(nixlMetadataContext &ctx, const nixlAge
         if (b->ok()) store_ = std::move(b);
     } else if (etcd && !etcd->empty()) {
         etcdRequested_ = true;
-        NIXL_WARN << "NIXL_ETCD_ENDPOINTS is set but this build has no etcd client; central metadata calls will "
-                     "return NIXL_ERR_NOT_SUPPORTED";
+        auto b = std::make_unique<nixlEtcdMetadataBackend>(*etcd, cfg.etcdWatchTimeout);
+        if (b->ok()) {
+            nixlMetadataContext *c = &ctx_;
+            b->setInvalidateCallback([c](const std::string &agent) { c->mdInvalidateRemote(agent); });
+            store_ = std::move(b);
+        }
     }
     if (cfg.useListenThread) listener_ = std::make_unique<nixlP2PListener>(ctx, cfg.listenPort, cfg.lthrDelay);
 }

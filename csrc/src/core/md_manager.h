@@ -5,8 +5,8 @@
 //   * peer-to-peer TCP (calls that pass ipAddr/port; needs the listener thread on the
 //     receiving side), protocol in md_p2p.cpp;
 //   * a torch c10d TCPStore when NIXL_TCPSTORE_ENDPOINT=host:port is set;
-//   * etcd when NIXL_ETCD_ENDPOINTS is set - no etcd client library exists in this
-//     build, so that choice reports NIXL_ERR_NOT_SUPPORTED.
+//   * etcd when NIXL_ETCD_ENDPOINTS is set, through etcd's JSON gateway (md_etcd.cpp); when no
+//     gateway answers there, central metadata calls report NIXL_ERR_NOT_SUPPORTED.
 // Work is queued to one worker thread so sendLocalMD/fetchRemoteMD return immediately;
 // callers poll checkRemoteMD.  Without any thread the work runs inline.
 #ifndef NIXL_B200_MD_MANAGER_H

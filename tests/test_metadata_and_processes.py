@@ -125,3 +125,64 @@ def test_two_processes_over_localhost():
         if proc.is_alive():
             proc.terminate()
         proc.join(5)
+
+
+def _start_fake_etcd():
+    """The fake gateway runs in its own process: the agent's constructor probes the endpoint from
+    inside a native call, during which a server thread of this interpreter could not run."""
+    import subprocess
+    import sys
+
+    proc = subprocess.Popen([sys.executable, os.path.join(os.path.dirname(os.path.abspath(__file__)), "fake_etcd_gateway.py")],
+                            stdout=subprocess.PIPE, text=True)
+    port = int(proc.stdout.readline())
+    return proc, port
+
+
+def _etcd_keys(port):
+    import json
+    import urllib.request
+
+    return json.loads(urllib.request.urlopen(f"http://127.0.0.1:{port}/keys", timeout=5).read())
+
+
+def test_etcd_gateway_metadata_roundtrip_and_invalidation(monkeypatch):
+    proc, port = _start_fake_etcd()
+    monkeypatch.delenv("NIXL_TCPSTORE_ENDPOINT", raising=False)
+    monkeypatch.setenv("NIXL_ETCD_ENDPOINTS", f"http://127.0.0.1:1,http://127.0.0.1:{port}")  # the first endpoint is dead
+    monkeypatch.setenv("NIXL_ETCD_POLL_MS", "50")
+    from nixl_b200 import nixl_agent, nixl_agent_config
+
+    try:
+        a = nixl_agent("etcd_a", nixl_agent_config(enable_prog_thread=False, backends=["NVLINK"]))
+        b = nixl_agent("etcd_b", nixl_agent_config(enable_prog_thread=False, backends=["NVLINK"]))
+        ta, tb = torch.arange(8192, dtype=torch.uint8), torch.zeros(8192, dtype=torch.uint8)
+        a.register_memory(ta)
+        b.register_memory(tb)
+        b.fetch_remote_metadata("etcd_a")  # asked for before it exists: the fetch waits for the key
+        time.sleep(0.2)
+        a.send_local_metadata()
+        b.send_local_metadata()
+        a.fetch_remote_metadata("etcd_b")
+        deadline = time.time() + 10
+        while time.time() < deadline and not (a.check_remote_metadata("etcd_b") and b.check_remote_metadata("etcd_a")):
+            time.sleep(0.01)
+        assert a.check_remote_metadata("etcd_b") and b.check_remote_metadata("etcd_a")
+        assert "/nixl/agents/etcd_a/metadata" in _etcd_keys(port)  # documented key layout: <namespace>/<agent>/<label>
+        h = a.initialize_xfer("WRITE", ta, tb, "etcd_b")
+        assert a.transfer(h) in ("DONE", "PROC")
+        while a.check_xfer_state(h) == "PROC":
+            pass
+        assert torch.equal(ta, tb)
+        a.release_xfer_handle(h)
+        # a withdraws its metadata: its key disappears and b, which watches what it fetched, forgets a
+        a.invalidate_local_metadata()
+        deadline = time.time() + 10
+        while time.time() < deadline and ("/nixl/agents/etcd_a/metadata" in _etcd_keys(port) or b.check_remote_metadata("etcd_a")):
+            time.sleep(0.02)
+        assert "/nixl/agents/etcd_a/metadata" not in _etcd_keys(port)
+        assert not b.check_remote_metadata("etcd_a")
+        del a, b
+    finally:
+        proc.terminate()
+        proc.wait(timeout=10)
