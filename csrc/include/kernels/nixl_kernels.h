@@ -122,6 +122,8 @@ typedef struct NixlEpDispatchParams {
     int32_t *expert_offsets;  /* out [El+1] first row of each local expert (both layouts) */
     NixlEpScratch scr;
     int32_t *send_row;        /* out [T][K] (optional) row each (token, k) landed on at its receiver, -1 if not sent */
+    int32_t use_ue8m0;        /* 1 (with use_fp8): scales are powers of two, delivered as biased exponent bytes, four per
+                                 32-bit word: recv_scales is uint8 [cap][H/128] with a row pitch of H/128 bytes */
 } NixlEpDispatchParams;
 
 typedef struct NixlEpCombineParams {

@@ -293,7 +293,9 @@ PYBIND11_MODULE(_bindings, m) {
 
     // ---- agent ----
     py::class_<nixlAgent>(m, "nixlAgent")
-        .def(py::init<const std::string &, const nixlAgentConfig &>())
+        // The constructor may probe metadata stores over the network and createBackend initialises
+        // CUDA: neither should stall other Python threads.
+        .def(py::init<const std::string &, const nixlAgentConfig &>(), py::call_guard<py::gil_scoped_release>())
         .def("getAvailPlugins",
              [](nixlAgent &a) {
                  std::vector<nixl_backend_t> v;
@@ -319,7 +321,12 @@ PYBIND11_MODULE(_bindings, m) {
         .def("createBackend",
              [](nixlAgent &a, const std::string &type, const nixl_b_params_t &params) {
                  nixlBackendH *h = nullptr;
-                 throwIf(a.createBackend(type, params, h), "createBackend");
+                 nixl_status_t st;
+                 {
+                     py::gil_scoped_release nogil;
+                     st = a.createBackend(type, params, h);
+                 }
+                 throwIf(st, "createBackend");
                  return reinterpret_cast<uintptr_t>(h);
              })
         .def("registerMem",

@@ -282,7 +282,7 @@ __global__ void __launch_bounds__(kThreads) epDispatchKernel(const __grid_consta
                     if (v >= vecs) continue;
                     if (p.use_fp8) {
                         float scale;
-                        const uint2 q = quantGroup(raw[j], p.round_scale != 0, scale); // 16 lanes own one 128-channel group
+                        const uint2 q = quantGroup(raw[j], (p.round_scale | p.use_ue8m0) != 0, scale); // 16 lanes own one 128-channel group
                         reinterpret_cast<uint2 *>(rowbuf)[v] = q;
                         if ((v & 15) == 0) scalebuf[v >> 4] = scale;
                     } else {
@@ -316,7 +316,15 @@ __global__ void __launch_bounds__(kThreads) epDispatchKernel(const __grid_consta
                 char *peer = peerBase(p.peers, d);
                 uint4 *dx = reinterpret_cast<uint4 *>(peer + p.lay.off_recv_x + row * row_bytes);
                 for (int v = gtid; v < row_bytes / 16; v += nt) stPeer16(dx + v, reinterpret_cast<const uint4 *>(rowbuf)[v]);
-                if (p.use_fp8) {
+                if (p.use_fp8 && p.use_ue8m0) {
+                    // A power-of-two scale is its exponent: one biased byte per group, four groups per word.
+                    uint32_t *ds = reinterpret_cast<uint32_t *>(peer + p.lay.off_recv_scales + row * groups);
+                    for (int g = gtid; g < groups / 4; g += nt) {
+                        const float4 f = reinterpret_cast<const float4 *>(scalebuf)[g];
+                        ds[g] = ((__float_as_uint(f.x) >> 23) & 0xffu) | (((__float_as_uint(f.y) >> 23) & 0xffu) << 8) |
+                            (((__float_as_uint(f.z) >> 23) & 0xffu) << 16) | (((__float_as_uint(f.w) >> 23) & 0xffu) << 24);
+                    }
+                } else if (p.use_fp8) {
                     float4 *ds = reinterpret_cast<float4 *>(reinterpret_cast<float *>(peer + p.lay.off_recv_scales) + row * groups);
                     for (int g = gtid; g < groups / 4; g += nt) ds[g] = reinterpret_cast<const float4 *>(scalebuf)[g];
                 }

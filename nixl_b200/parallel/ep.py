@@ -55,7 +55,7 @@ class _DispatchParams(ctypes.Structure):
         ("phases", ctypes.c_int32), ("grid", ctypes.c_int32),
         ("peers", ctypes.c_void_p), ("lay", _Layout), ("epoch", ctypes.c_uint64), ("timeout_ns", ctypes.c_uint64),
         ("recv_count", ctypes.c_void_p), ("layout_range", ctypes.c_void_p), ("expert_offsets", ctypes.c_void_p), ("scr", _Scratch),
-        ("send_row", ctypes.c_void_p),
+        ("send_row", ctypes.c_void_p), ("use_ue8m0", ctypes.c_int32),
     ]
 
 
@@ -356,7 +356,7 @@ class Buffer:
         cur.wait_stream(self._side)
         return d, handle, recv_x, scales
 
-    def _dispatch(self, x, topk_idx, use_fp8, round_scale, rows_per_expert, phases_now, hook_later, grid=0):
+    def _dispatch(self, x, topk_idx, use_fp8, round_scale, rows_per_expert, phases_now, hook_later, grid=0, use_ue8m0=False):
         if not self._peers_view:
             if self.num_ranks == 1:
                 self.connect_ranks(metadata=[self.local_metadata()])
@@ -375,7 +375,7 @@ class Buffer:
         El, R = self.local_experts, self.num_ranks
         # Per-parity outputs, views and parameter block are built once and reused: the Python
         # cost of a call is a handful of attribute stores plus one foreign call.
-        key = (parity, bool(use_fp8), rows_per_expert)
+        key = (parity, bool(use_fp8), rows_per_expert, bool(use_ue8m0))
         slot = self._disp_cache.get(key)
         if slot is None:
             with torch.cuda.device(self.device):
@@ -386,6 +386,7 @@ class Buffer:
             p = _DispatchParams()
             p.K, p.H, p.E, p.R, p.rank = K, H, self.num_experts, R, self.rank
             p.use_fp8 = int(use_fp8)
+            p.use_ue8m0 = int(bool(use_ue8m0 and use_fp8))
             p.rows_per_expert = rows_per_expert
             p.cap = self.ll_rows if rows_per_expert else self.compact_rows
             p.grid = 0
@@ -399,7 +400,10 @@ class Buffer:
             raw = self._region(parity, "off_recv_x", rows * row_bytes)
             recv_x = raw.view(torch.float8_e4m3fn if use_fp8 else torch.bfloat16).view(rows, H)
             scales = None
-            if use_fp8:
+            if use_fp8 and use_ue8m0:
+                # biased exponent bytes, four per 32-bit word (row pitch H/128 bytes)
+                scales = self._region(parity, "off_recv_scales", rows * (H // 128)).view(torch.int32).view(rows, H // 512)
+            elif use_fp8:
                 scales = self._region(parity, "off_recv_scales", rows * (H // 128) * 4).view(torch.float32).view(rows, H // 128)
             src_info = self._region(parity, "off_recv_info", rows * 8).view(torch.int32).view(rows, 2)
             slot = (p, recv_count, layout_range, expert_offsets, recv_x, scales, src_info, send_row)
@@ -478,20 +482,23 @@ class Buffer:
         Returns ``(recv, recv_count, handle, event, hook)`` where ``recv`` is
         ``(packed_recv_x, packed_recv_x_scales)`` for fp8 or ``packed_recv_x`` for bf16, shaped
         ``[local_experts, ranks * max_tokens, hidden]``; only the first ``recv_count[e]`` rows of
-        expert ``e`` are valid.  The tensors alias the communication buffer: at most two
+        expert ``e`` are valid.  With ``use_ue8m0`` the scales are powers of two and arrive as biased
+        exponent bytes packed four to an int32 (``[local_experts, ranks * max_tokens, hidden // 512]``),
+        the form Blackwell's block-scaled MMAs take; ``dequant_ue8m0`` turns them back into floats.  The tensors alias the communication buffer: at most two
         dispatches' results are alive at a time."""
-        if use_ue8m0:
-            raise NotImplementedError("packed UE8M0 scales are not produced; use round_scale=True for power-of-two fp32 scales")
+        if use_ue8m0 and (not use_fp8 or self.hidden % 512):
+            raise ValueError("UE8M0 scales need fp8 dispatch and hidden % 512 == 0")
         if num_max_dispatch_tokens_per_rank not in (None, self.max_tokens) or num_experts not in (None, self.num_experts):
             raise ValueError("buffer was sized for other shapes")
         rpe = self.num_ranks * self.max_tokens
-        recv_x, scales, handle, hook, keep = self._dispatch(x, topk_idx, use_fp8, round_scale, rpe, 1 if return_recv_hook else 3, return_recv_hook)
+        recv_x, scales, handle, hook, keep = self._dispatch(x, topk_idx, use_fp8, round_scale, rpe, 1 if return_recv_hook else 3, return_recv_hook,
+                                                            use_ue8m0=use_ue8m0)
         El = self.local_experts
         packed = recv_x[: El * rpe].view(El, rpe, self.hidden)
         event = EventOverlap(self._record() if async_finish else None)
         self._keep = keep
         if use_fp8:
-            return (packed, scales[: El * rpe].view(El, rpe, self.hidden // 128)), handle.recv_count, handle, event, hook
+            return (packed, scales[: El * rpe].view(El, rpe, -1)), handle.recv_count, handle, event, hook
         return packed, handle.recv_count, handle, event, hook
 
     def low_latency_combine(
@@ -642,6 +649,12 @@ def per_token_cast_to_fp8(x: torch.Tensor, round_scale: bool = False):
         inv = 448.0 / amax
     q = (g * inv.unsqueeze(2)).to(torch.float8_e4m3fn).view(T, H)
     return q, scale
+
+
+def dequant_ue8m0(packed: torch.Tensor) -> torch.Tensor:
+    """int32 ``[..., G/4]`` of biased exponent bytes -> float32 ``[..., G]`` scales (2 ** (byte - 127))."""
+    b = packed.contiguous().view(torch.uint8).to(torch.int32)
+    return torch.ldexp(torch.ones_like(b, dtype=torch.float32), b - 127)
 
 
 def dequant_fp8(q: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:

@@ -7,7 +7,7 @@ peers waiting on each other are skipped when only one GPU is present."""
 import pytest
 import torch
 
-from nixl_b200.parallel import Buffer, dequant_fp8, per_token_cast_to_fp8
+from nixl_b200.parallel import Buffer, dequant_fp8, dequant_ue8m0, per_token_cast_to_fp8
 
 pytestmark = pytest.mark.gpu
 
@@ -186,6 +186,29 @@ def test_throughput_only_buffer_is_smaller_and_rejects_low_latency_calls():
     rx, sc, h = small.dispatch(x, idx)
     torch.cuda.synchronize()
     assert int(h.recv_count.sum()) == 128 and small.status == 0
+
+
+def test_ue8m0_scales_are_the_exponents_of_rounded_scales():
+    dev = torch.device("cuda", 0)
+    T, H, E, K = 40, 1024, 8, 2
+    buf = Buffer(0, 1, E, H, T, K, device=dev)
+    g = torch.Generator(device=dev).manual_seed(5)
+    x = (torch.randn(T, H, device=dev, generator=g) * 3).to(torch.bfloat16)
+    idx = torch.stack([torch.randperm(E, device=dev, generator=g)[:K] for _ in range(T)]).long()
+    (rx, packed), cnt, handle, _, _ = buf.low_latency_dispatch(x, idx, use_fp8=True, use_ue8m0=True)
+    torch.cuda.synchronize()
+    assert buf.status == 0 and packed.dtype == torch.int32 and packed.shape[-1] == H // 512
+    want_q, want_s = per_token_cast_to_fp8(x, round_scale=True)
+    scales = dequant_ue8m0(packed)  # [El, rows, H/128]
+    info = handle.src_info.view(E, -1, 2)
+    for le in range(E):
+        for i in range(int(cnt[le])):
+            t = int(info[le, i, 1]) // K
+            assert torch.equal(scales[le, i], want_s[t]), (le, i)
+            got = rx[le, i].view(torch.uint8).int()
+            ref = want_q[t].view(torch.uint8).int()
+            assert (got - ref).abs().max() <= 1
+    buf.destroy()
 
 
 def test_dispatch_layout_counts_match_torch():

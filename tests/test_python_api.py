@@ -133,3 +133,24 @@ def test_error_types():
         a.get_agent_metadata()  # no backend that supports remote access
     assert issubclass(nb.nixlNotFoundError, nb.nixlError)
     assert nixl_b200.__version__
+
+
+def test_python_logging_follows_nixl_log_level(monkeypatch, capsys):
+    import logging
+
+    from nixl_b200 import logging as nlog
+
+    monkeypatch.setenv("NIXL_LOG_LEVEL", "warn")
+    root = nlog.setup_logging(force=True)
+    assert root.level == logging.WARNING
+    log = nlog.get_logger("tests.sample")
+    assert log.name == "nixl.tests.sample" and not log.isEnabledFor(logging.INFO) and log.isEnabledFor(logging.ERROR)
+    monkeypatch.setenv("NIXL_LOG_LEVEL", "TRACE")
+    assert nlog.level_from_env() == logging.DEBUG
+    monkeypatch.setenv("NIXL_LOG_LEVEL", "chatty")
+    with pytest.raises(ValueError):
+        nlog.level_from_env()
+    root = nlog.setup_logging(force=True)  # falls back to INFO and says so
+    assert root.level == logging.INFO
+    monkeypatch.delenv("NIXL_LOG_LEVEL")
+    nlog.setup_logging(force=True)
