@@ -195,7 +195,10 @@ typedef struct NixlGroupedGemmParams {
      * (row_start[g] = g * rows_per_expert), 0 the compact prefix layout. */
     const uint64_t *counts_flag; /* [ranks] or NULL */
     int32_t rows_per_expert;
-    int32_t tile_mode;           /* 0: choose; 1: 128 x 128 tiles, one CTA each; 2: 256 x 256 tiles, one CTA pair each (N % 256 == 0) */
+    int32_t tile_mode;           /* 0: choose between 1 and 2; 1: 128 x 128 tiles, one CTA each; 2: 256 x 256 tiles, one CTA pair each
+                                    (N % 256 == 0); 3: as 2 with power-of-two scales applied by the tensor core: scale_a and
+                                    scale_w then point at biased exponent bytes (UE8M0), uint8 [a_rows][K/128] and
+                                    [groups][N/128][K/128], K % 512 == 0 */
 } NixlGroupedGemmParams;
 
 int nixl_grouped_gemm_fp8_launch(const NixlGroupedGemmParams *params, void *stream);

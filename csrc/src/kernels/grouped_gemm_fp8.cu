@@ -414,6 +414,13 @@ extern "C" int nixl_grouped_gemm_fp8_launch(const NixlGroupedGemmParams *params,
     // layout, where most tiles hold a handful of rows.
     int mode = p.tile_mode & 0xff;
     if (mode == 0) mode = (p.rows_per_expert == 0 && !p.counts_flag && p.N % 256 == 0 && p.a_rows >= 256LL * p.groups) ? 2 : 1;
+    if (mode == 3) {
+        if (p.N % 256 || p.K % 512 || p.counts_flag || p.disp_flag) return cudaErrorInvalidValue;
+        if ((reinterpret_cast<uintptr_t>(p.scale_a) | reinterpret_cast<uintptr_t>(p.scale_w)) & 3) return cudaErrorInvalidValue;
+        CUtensorMap mapW64;
+        if (!nixl_gemm::makeTileMap(&mapW64, p.w, static_cast<uint64_t>(p.groups) * p.N, static_cast<uint64_t>(p.K), 64)) return cudaErrorInvalidValue;
+        return nixl_gemm::launchMxPairKernel(mapA, mapW64, p, static_cast<cudaStream_t>(stream));
+    }
     if (mode == 2) {
         if (p.N % 256) return cudaErrorInvalidValue;
         CUtensorMap mapW64; // the pair kernel loads W in 64-row boxes

@@ -19,6 +19,11 @@ bool makeTileMap(CUtensorMap *map, const void *base, uint64_t rows, uint64_t k, 
 // single-CTA kernel; N must be a multiple of 256.
 cudaError_t launchPairKernel(const CUtensorMap &mapA, const CUtensorMap &mapW, const NixlGroupedGemmParams &p, cudaStream_t stream);
 
+// Same tiles with power-of-two block scales applied by the tensor core (kind::mxf8f6f4.block_scale):
+// p.scale_a / p.scale_w point at exponent bytes (uint8 [a_rows][K/128] and [groups][N/128][K/128]);
+// K must be a multiple of 512, N of 256; no dispatch overlap.
+cudaError_t launchMxPairKernel(const CUtensorMap &mapA, const CUtensorMap &mapW, const NixlGroupedGemmParams &p, cudaStream_t stream);
+
 } // namespace nixl_gemm
 
 #endif

@@ -1,0 +1,425 @@
+// Grouped fp8 expert GEMM with power-of-two (UE8M0) block scales applied by the tensor core:
+// tcgen05.mma.kind::mxf8f6f4.block_scale on CTA pairs, 256 x 256 output tiles.
+//
+//   D[rows of expert g, :] = (A * 2^(sa-127)) x (W[g] * 2^(sw-127))^T           (bf16 out)
+//   A: e4m3 [rows][K], one biased exponent byte per row per 128 channels (what EP dispatch delivers
+//      with use_ue8m0: uint8 [rows][K/128], i.e. four consecutive steps per 32-bit word)
+//   W: e4m3 [G][N][K], one exponent byte per 128 x 128 block: uint8 [G][N/128][K/128]
+//
+// With fp32 scales the partial sums of every 128-channel step have to leave TMEM to be scaled
+// (grouped_gemm_fp8_pair.cu), and that promotion, not the tensor pipe, bounds the kernel.  Here the
+// scale factors ride along with the MMA: a whole K loop accumulates in TMEM and the epilogue runs
+// once per tile.
+//
+// Scale factors reach the tensor core through TMEM.  For four steps at a time ("chunk") the
+// epilogue warps, idle during the main loop, build in shared memory the 512-byte layout the
+// hardware wants (byte (r % 32) * 16 + (r / 32) * 4 + step for row r: for A one 32-bit word per row
+// straight from the scale tensor, for W the block's word repeated for all 128 columns), the issuing
+// thread copies it to TMEM with tcgen05.cp (32x128b.warpx4) and selects the step's byte with the
+// scale-factor-id fields of the instruction descriptor.  Shared-memory chunk buffers form a ring of
+// four, TMEM scale columns are double-buffered by chunk parity.
+//
+//   warp 0      TMA producer (both CTAs; bytes counted on the even CTA's barrier)
+//   warp 1      MMA issuer (even CTA): tcgen05.cp of scale chunks, eight M256 N128 K32 MMAs per step
+//   warp 2      TMEM allocator (512 columns: 256 accumulator, 32 scale factors)
+//   warps 4-11  scale staging during the main loop, then the epilogue (TMEM -> bf16 -> global)
+//
+// TMA loads read this GPU's memory only and carry no cluster multicast.  Every wait is bounded.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "kernels/grouped_gemm_internal.h"
+#include "kernels/tcgen05_ptx.cuh"
+
+namespace {
+
+using namespace nixl_tc;
+using nixl_gemm::GEMM_ERR_TIMEOUT;
+using nixl_gemm::kMaxGroups;
+
+constexpr int BM = 128;        // rows per CTA (256 per pair)
+constexpr int BN = 256;        // tile columns
+constexpr int BNS = 128;       // columns per instruction group / accumulator half
+constexpr int WBOX = 64;       // W rows per TMA box (per CTA and column half)
+constexpr int BK = 128;
+constexpr int kStages = 6;
+constexpr int kThreads = 384;
+constexpr int kATileBytes = BM * BK;
+constexpr int kWBoxBytes = WBOX * BK;
+constexpr int kStageBytes = kATileBytes + 2 * kWBoxBytes; // 32 KiB per CTA
+constexpr int kChunkSteps = 4;                 // steps whose scale bytes share one 32-bit word
+constexpr int kSfRing = 4;                     // chunk buffers in shared memory
+constexpr int kSfAtomBytes = 512;              // 128 rows x 4 steps
+constexpr int kSfBufBytes = 3 * kSfAtomBytes;  // A, W left half, W right half
+constexpr int kTmemCols = 512;
+constexpr int kAccCols = 2 * BNS;              // accumulator: columns [0, 256)
+constexpr int kSfTmemStride = 16;              // scale columns of a chunk parity: [256 + 16 p, ...): A +0, W left +4, W right +8
+constexpr int kPromoWarps = 8;
+
+struct Shared {
+    uint64_t full[kStages];      // even CTA: both CTAs' operand bytes of a stage have landed
+    uint64_t empty[kStages];     // per CTA: the MMAs that read the stage are done
+    uint64_t sfFull[kSfRing];    // even CTA: both CTAs have staged the chunk's scale layouts (16 warp arrivals)
+    uint64_t sfEmpty[kSfRing];   // per CTA: the chunk buffer has been copied to TMEM
+    uint64_t tmemFull;           // per CTA: a tile's accumulator is complete
+    uint64_t tmemEmpty;          // even CTA: all 16 epilogue warps have read the accumulator
+    uint32_t tmemBase;
+    int abort;
+    int tilePrefix[kMaxGroups + 1];
+    int rowStart[kMaxGroups];
+    int rowCount[kMaxGroups];
+};
+
+__device__ __forceinline__ uint32_t clusterCtaRank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t mapToCta(uint32_t smem_addr, uint32_t cta) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(cta));
+    return r;
+}
+__device__ __forceinline__ void clusterSync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Relaxed on purpose: a release at cluster scope made the arriving thread wait several hundred
+// cycles, once per slot.  What the arrive has to order are this warp's TMEM reads, and those are
+// complete (tcgen05.wait::ld returned, the values are in registers) before it is issued.
+__device__ __forceinline__ void mbarArriveCluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// Tile load whose completion bytes are counted on a barrier given by its cluster address
+// (the even CTA's), as the paired MMA needs both halves before it may start.
+__device__ __forceinline__ void tmaLoad2dPair(void *smem_dst, const CUtensorMap *map, int x, int y, uint32_t bar_cluster_addr) {
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+                     smemU32(smem_dst)),
+                 "l"(map), "r"(bar_cluster_addr), "r"(x), "r"(y)
+                 : "memory");
+}
+__device__ __forceinline__ void mbarArriveClusterRelease(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tcCommitPair(uint32_t bar_addr) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar_addr),
+                 "h"(static_cast<uint16_t>(3))
+                 : "memory");
+}
+// Shared-memory descriptor of one 512-byte scale layout: 32 rows of 16 bytes, no swizzle, 8-row
+// groups 128 bytes apart.
+__device__ __forceinline__ uint64_t sfDesc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+    d |= static_cast<uint64_t>(1) << 16;
+    d |= static_cast<uint64_t>(128 >> 4) << 32;
+    d |= static_cast<uint64_t>(1) << 46;
+    return d;
+}
+// 32 x 128 bit from shared memory into four TMEM columns, replicated to all four lane quarters, in
+// both CTAs of the pair (each from its own shared memory).
+__device__ __forceinline__ void tmemCpPair(uint32_t tmem_dst, uint64_t desc) {
+    asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(tmem_dst), "l"(desc) : "memory");
+}
+// D fp32, A and B e4m3 K-major, M = 256 (both CTAs), N = 128, scale factors E8M0, scale-factor id `sf` for A and B.
+__device__ __forceinline__ uint32_t instrDescMx(uint32_t sf) {
+    return (sf << 4) | (static_cast<uint32_t>(BNS >> 3) << 17) | (1u << 23) | (static_cast<uint32_t>((2 * BM) >> 4) << 24) | (sf << 29);
+}
+
+// One 128-channel step: eight block-scaled MMAs (four per accumulator half), the commit that frees
+// the stage, then a non-blocking test of the next step's barrier (behind the MMAs on purpose).
+__device__ __forceinline__ void issueKStepMx(uint32_t tmem_d0, uint32_t tmem_d1, uint64_t da, uint64_t dw0, uint64_t dw1, uint32_t idesc, uint32_t tsfa,
+                                             uint32_t tsfb0, uint32_t tsfb1, uint32_t accumulate, uint32_t bar_stage_empty, uint32_t peek_bar,
+                                             uint32_t peek_par, uint32_t &ready_next) {
+    uint64_t da2 = da;
+    asm volatile(
+        "{\n"
+        " .reg .pred pf, pacc, pfirst;\n"
+        " setp.ne.b32 pacc, %15, 0;\n"
+        " setp.ne.b32 pfirst, %11, 0;\n"
+        " tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%1], %3, %4, %7, [%8], [%9], pfirst;\n"
+        " add.u64 %3, %3, 2;\n add.u64 %4, %4, 2;\n"
+        " tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%1], %3, %4, %7, [%8], [%9], pacc;\n"
+        " add.u64 %3, %3, 2;\n add.u64 %4, %4, 2;\n"
+        " tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%1], %3, %4, %7, [%8], [%9], pacc;\n"
+        " add.u64 %3, %3, 2;\n add.u64 %4, %4, 2;\n"
+        " tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%1], %3, %4, %7, [%8], [%9], pacc;\n"
+        " tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%2], %6, %5, %7, [%8], [%10], pfirst;\n"
+        " add.u64 %6, %6, 2;\n add.u64 %5, %5, 2;\n"
+        " tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%2], %6, %5, %7, [%8], [%10], pacc;\n"
+        " add.u64 %6, %6, 2;\n add.u64 %5, %5, 2;\n"
+        " tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%2], %6, %5, %7, [%8], [%10], pacc;\n"
+        " add.u64 %6, %6, 2;\n add.u64 %5, %5, 2;\n"
+        " tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%2], %6, %5, %7, [%8], [%10], pacc;\n"
+        " tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%12], %16;\n"
+        " mbarrier.test_wait.parity.shared::cta.b64 pf, [%13], %14;\n"
+        " selp.u32 %0, 1, 0, pf;\n"
+        "}\n"
+        : "=r"(ready_next), "+r"(tmem_d0), "+r"(tmem_d1), "+l"(da), "+l"(dw0), "+l"(dw1), "+l"(da2)
+        : "r"(idesc), "r"(tsfa), "r"(tsfb0), "r"(tsfb1), "r"(accumulate), "r"(bar_stage_empty), "r"(peek_bar), "r"(peek_par), "r"(1u),
+          "h"(static_cast<uint16_t>(3))
+        : "memory");
+}
+
+struct Tile {
+    int g, mt, nt;
+};
+
+__device__ __forceinline__ bool tileAt(const Shared &sh, int groups, int n_tiles, int t, Tile &out) {
+    if (t >= sh.tilePrefix[groups]) return false;
+    int lo = 0, hi = groups;
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (sh.tilePrefix[mid] <= t) lo = mid; else hi = mid;
+    }
+    const int local = t - sh.tilePrefix[lo];
+    out.g = lo;
+    out.mt = local / n_tiles;
+    out.nt = local - out.mt * n_tiles;
+    return true;
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+groupedGemmMxPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapW, const NixlGroupedGemmParams p) {
+    extern __shared__ __align__(1024) unsigned char dyn[];
+    unsigned char *tiles = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(dyn) + 1023) & ~uintptr_t(1023));
+    unsigned char *sf_ring = tiles + kStages * kStageBytes; // kSfRing buffers of {A, W left, W right} layouts
+    Shared &sh = *reinterpret_cast<Shared *>(sf_ring + kSfRing * kSfBufBytes);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n_tiles = p.N / BN, k_steps = p.K / BK;
+    const int chunks = k_steps / kChunkSteps; // K is a multiple of 512
+    const uint32_t cta = clusterCtaRank();
+    const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbarInit(&sh.full[s], 1);
+            mbarInit(&sh.empty[s], 1);
+        }
+        for (int b = 0; b < kSfRing; ++b) {
+            mbarInit(&sh.sfFull[b], 2 * kPromoWarps);
+            mbarInit(&sh.sfEmpty[b], 1);
+        }
+        mbarInit(&sh.tmemFull, 1);
+        mbarInit(&sh.tmemEmpty, 2 * kPromoWarps);
+        sh.abort = 0;
+        int run = 0;
+        for (int g = 0; g < p.groups; ++g) {
+            const int c = p.row_count[g];
+            sh.tilePrefix[g] = run;
+            sh.rowStart[g] = p.row_start[g];
+            sh.rowCount[g] = c;
+            run += ((c + 2 * BM - 1) / (2 * BM)) * n_tiles;
+        }
+        sh.tilePrefix[p.groups] = run;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 2) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smemU32(&sh.tmemBase)), "r"(kTmemCols));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;");
+    }
+    tcFenceBefore();
+    __syncthreads();
+    clusterSync();
+    tcFenceAfter();
+    const uint32_t tmem = sh.tmemBase;
+    volatile int *abort_flag = &sh.abort;
+    int my_tiles = 0;
+    {
+        const int total = sh.tilePrefix[p.groups];
+        if (pair < total) my_tiles = (total - pair + pairs - 1) / pairs;
+    }
+
+    if (warp == 0 && lane == 0) {
+        // ---------------------------------------------------------------- TMA producer (both CTAs)
+        const uint32_t full0 = mapToCta(smemU32(&sh.full[0]), 0);
+        uint32_t it = 0;
+        Tile t;
+        for (int ti = pair; tileAt(sh, p.groups, n_tiles, ti, t); ti += pairs) {
+            const int row0 = sh.rowStart[t.g] + t.mt * (2 * BM) + static_cast<int>(cta) * BM;
+            const int wrow = t.g * p.N + t.nt * BN + static_cast<int>(cta) * WBOX;
+            for (int ks = 0; ks < k_steps; ++ks, ++it) {
+                const int s = it % kStages;
+                if (!mbarWait(&sh.empty[s], ((it / kStages) & 1) ^ 1, abort_flag)) goto producer_done;
+                if (cta == 0) mbarExpectTx(&sh.full[s], 2 * kStageBytes);
+                const uint32_t bar = full0 + static_cast<uint32_t>(s) * 8u;
+                unsigned char *st = tiles + s * kStageBytes;
+                tmaLoad2dPair(st, &mapA, ks * BK, row0, bar);
+                tmaLoad2dPair(st + kATileBytes, &mapW, ks * BK, wrow, bar);
+                tmaLoad2dPair(st + kATileBytes + kWBoxBytes, &mapW, ks * BK, wrow + BNS, bar);
+            }
+        }
+    producer_done:;
+    } else if (warp == 1 && lane == 0 && cta == 0) {
+        // ---------------------------------------------------------------- MMA issuer (even CTA)
+        uint32_t s = 0, full_par = 0, ready = 0;
+        uint32_t cc = 0; // chunk counter over all tiles: ring buffer cc % kSfRing, TMEM scale columns by cc & 1
+        const uint32_t full_bar0 = smemU32(&sh.full[0]), empty_bar0 = smemU32(&sh.empty[0]), sfempty_bar0 = smemU32(&sh.sfEmpty[0]);
+        const uint64_t desc0 = smemDesc(smemU32(tiles));
+        const uint32_t sf_smem0 = smemU32(sf_ring);
+        for (int tile = 0; tile < my_tiles; ++tile) {
+            // The single accumulator must have been drained by the previous tile's epilogue.
+            if (!mbarWait(&sh.tmemEmpty, (static_cast<uint32_t>(tile) & 1u) ^ 1u, abort_flag)) goto issuer_done;
+            for (int ks = 0; ks < k_steps; ++ks) {
+                const uint32_t sub = static_cast<uint32_t>(ks) & (kChunkSteps - 1);
+                if (sub == 0) {
+                    const uint32_t b = cc % kSfRing;
+                    if (!mbarWait(&sh.sfFull[b], (cc / kSfRing) & 1u, abort_flag)) goto issuer_done;
+                    tcFenceAfter();
+                    const uint32_t src = sf_smem0 + b * kSfBufBytes;
+                    const uint32_t dst = tmem + kAccCols + (cc & 1u) * kSfTmemStride;
+                    tmemCpPair(dst, sfDesc(src));
+                    tmemCpPair(dst + 4, sfDesc(src + kSfAtomBytes));
+                    tmemCpPair(dst + 8, sfDesc(src + 2 * kSfAtomBytes));
+                    tcCommitPair(sfempty_bar0 + b * 8u); // the buffer may be refilled once the copies have read it
+                }
+                if (!ready && !mbarWait(&sh.full[s], full_par, abort_flag)) goto issuer_done;
+                tcFenceAfter();
+                uint32_t ns = s + 1, nfull_par = full_par;
+                if (ns == kStages) {
+                    ns = 0;
+                    nfull_par ^= 1u;
+                }
+                const uint64_t da = desc0 + static_cast<uint64_t>((s * kStageBytes) >> 4);
+                const uint64_t dw0 = da + static_cast<uint64_t>(kATileBytes >> 4);
+                const uint64_t dw1 = da + static_cast<uint64_t>((kATileBytes + kWBoxBytes) >> 4);
+                const uint32_t sfc = tmem + kAccCols + (cc & 1u) * kSfTmemStride;
+                issueKStepMx(tmem, tmem + BNS, da, dw0, dw1, instrDescMx(sub), sfc, sfc + 4, sfc + 8, ks > 0 ? 1u : 0u, empty_bar0 + s * 8u,
+                             full_bar0 + ns * 8u, nfull_par, ready);
+                if (sub == kChunkSteps - 1) ++cc;
+                s = ns;
+                full_par = nfull_par;
+            }
+            tcCommitPair(smemU32(&sh.tmemFull));
+        }
+    issuer_done:;
+    } else if (warp >= 4) {
+        // ---------------------------------------------------------------- scale staging, then the epilogue
+        const int q = warp & 3;
+        const int part = (warp - 4) >> 2; // 0: stages A's layout, 1: stages W's two layouts; epilogue: 64-column part of each half
+        const int row_in_tile = q * 32 + lane;
+        const uint32_t sffull0 = mapToCta(smemU32(&sh.sfFull[0]), 0);
+        const uint32_t tempty = mapToCta(smemU32(&sh.tmemEmpty), 0);
+        const uint32_t lane_base = tmem + (static_cast<uint32_t>(q * 32) << 16) + part * 64;
+        const uint32_t *sa32 = reinterpret_cast<const uint32_t *>(p.scale_a);
+        const uint32_t *sw32 = reinterpret_cast<const uint32_t *>(p.scale_w);
+        const int n_blocks = p.N / 128;
+        uint32_t cc = 0;
+        Tile t;
+        int tile = 0;
+        for (int ti = pair; tileAt(sh, p.groups, n_tiles, ti, t); ti += pairs, ++tile) {
+            const int local_row = t.mt * (2 * BM) + static_cast<int>(cta) * BM + row_in_tile;
+            const bool valid = local_row < sh.rowCount[t.g];
+            const long long grow = static_cast<long long>(sh.rowStart[t.g]) + local_row;
+            bool ok = true;
+            for (int c = 0; c < chunks; ++c, ++cc) {
+                const uint32_t b = cc % kSfRing;
+                if (!mbarWait(&sh.sfEmpty[b], ((cc / kSfRing) & 1u) ^ 1u, abort_flag)) {
+                    ok = false;
+                    break;
+                }
+                uint32_t *buf = reinterpret_cast<uint32_t *>(sf_ring + b * kSfBufBytes);
+                if (part == 0) {
+                    // Row r of this CTA's half: word (r % 32) * 4 + r / 32 (rows beyond the expert get exponent 127 = 1.0).
+                    const uint32_t w = valid ? __ldg(sa32 + grow * chunks + c) : 0x7f7f7f7fu;
+                    buf[lane * 4 + q] = w;
+                } else {
+                    const uint32_t wl = __ldg(sw32 + (static_cast<long long>(t.g) * n_blocks + t.nt * 2) * chunks + c);
+                    const uint32_t wr = __ldg(sw32 + (static_cast<long long>(t.g) * n_blocks + t.nt * 2 + 1) * chunks + c);
+                    buf[128 + row_in_tile] = wl;
+                    buf[256 + row_in_tile] = wr;
+                }
+                asm volatile("fence.proxy.async;" ::: "memory"); // these generic-proxy writes are read by tcgen05.cp
+                __syncwarp();
+                if (lane == 0) mbarArriveClusterRelease(sffull0 + b * 8u);
+            }
+            if (!ok) break;
+            // Epilogue: the tile's accumulator, two halves of 128 columns, this warp's 64 columns of each.
+            if (!mbarWait(&sh.tmemFull, static_cast<uint32_t>(tile) & 1u, abort_flag)) break;
+            tcFenceAfter();
+            __nv_bfloat16 *out = static_cast<__nv_bfloat16 *>(p.d) + grow * p.N + t.nt * BN + part * 64;
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                float v0[32], v1[32];
+                tmemLoad32(lane_base + h * BNS, v0);
+                tmemLoad32(lane_base + h * BNS + 32, v1);
+                tmemLoadWait(v0);
+                tmemLoadWait(v1);
+                if (h == 1) {
+                    // Everything this warp needs is in registers: the next tile may overwrite the accumulator.
+                    tcFenceBefore();
+                    __syncwarp();
+                    if (lane == 0) mbarArriveCluster(tempty);
+                }
+                if (valid) {
+#pragma unroll
+                    for (int e = 0; e < 32; e += 8) {
+                        uint4 o;
+                        __nv_bfloat162 *hh = reinterpret_cast<__nv_bfloat162 *>(&o);
+#pragma unroll
+                        for (int x = 0; x < 4; ++x) hh[x] = __floats2bfloat162_rn(v0[e + 2 * x], v0[e + 2 * x + 1]);
+                        *reinterpret_cast<uint4 *>(out + h * BNS + e) = o;
+                    }
+#pragma unroll
+                    for (int e = 0; e < 32; e += 8) {
+                        uint4 o;
+                        __nv_bfloat162 *hh = reinterpret_cast<__nv_bfloat162 *>(&o);
+#pragma unroll
+                        for (int x = 0; x < 4; ++x) hh[x] = __floats2bfloat162_rn(v1[e + 2 * x], v1[e + 2 * x + 1]);
+                        *reinterpret_cast<uint4 *>(out + h * BNS + 32 + e) = o;
+                    }
+                }
+            }
+        }
+    }
+
+    tcFenceBefore();
+    __syncthreads();
+    clusterSync();
+    if (threadIdx.x == 0 && sh.abort) atomicOr(p.status, GEMM_ERR_TIMEOUT);
+    if (warp == 2) {
+        tcFenceAfter();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols));
+    }
+}
+
+} // namespace
+
+cudaError_t nixl_gemm::launchMxPairKernel(const CUtensorMap &mapA, const CUtensorMap &mapW, const NixlGroupedGemmParams &p, cudaStream_t stream) {
+    const size_t smem = size_t(kStages) * kStageBytes + size_t(kSfRing) * kSfBufBytes + sizeof(Shared) + 1024;
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    static bool attr_done[64] = {};
+    static int max_pairs[64] = {};
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(groupedGemmMxPairKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        if (e != cudaSuccess) return e;
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        cfg.gridDim = dim3(static_cast<unsigned>(sms & ~1));
+        int clusters = 0;
+        e = cudaOccupancyMaxActiveClusters(&clusters, groupedGemmMxPairKernel, &cfg);
+        if (e != cudaSuccess || clusters <= 0) {
+            cudaGetLastError();
+            clusters = sms / 2;
+        }
+        max_pairs[dev] = clusters;
+        attr_done[dev] = true;
+    }
+    int pairs = (dev >= 0 && dev < 64) ? max_pairs[dev] : sms / 2;
+    if (p.grid > 0 && p.grid / 2 < pairs) pairs = p.grid / 2 > 0 ? p.grid / 2 : 1;
+    const long long max_tiles = (static_cast<long long>(p.a_rows + 2 * BM - 1) / (2 * BM) + p.groups) * (p.N / BN);
+    if (pairs > max_tiles) pairs = static_cast<int>(max_tiles);
+    cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs));
+    return cudaLaunchKernelEx(&cfg, groupedGemmMxPairKernel, mapA, mapW, p);
+}

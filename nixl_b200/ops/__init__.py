@@ -1,5 +1,13 @@
 """Fused GPU operations of the library (hand-written sm_100a kernels behind a C ABI)."""
-from .grouped_gemm import grouped_gemm_fp8, quantize_weights, reference_grouped_gemm  # noqa: F401
+from .grouped_gemm import (  # noqa: F401
+    from_ue8m0,
+    grouped_gemm_fp8,
+    grouped_gemm_mxfp8,
+    quantize_weights,
+    quantize_weights_ue8m0,
+    reference_grouped_gemm,
+    to_ue8m0,
+)
 from .kv_transfer import KVLayout, KVTransfer, reference_kv_transfer  # noqa: F401
 
 

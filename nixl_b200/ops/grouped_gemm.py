@@ -38,6 +38,76 @@ def quantize_weights(w: torch.Tensor):
     return q.contiguous(), scale.contiguous()
 
 
+def to_ue8m0(scale: torch.Tensor) -> torch.Tensor:
+    """Power-of-two fp32 scales -> biased exponent bytes (uint8, same shape)."""
+    bits = scale.contiguous().view(torch.int32)
+    if bool(((bits & 0x7FFFFF) != 0).any()):
+        raise ValueError("scales are not powers of two")
+    return ((bits >> 23) & 0xFF).to(torch.uint8)
+
+
+def from_ue8m0(exp: torch.Tensor) -> torch.Tensor:
+    """Biased exponent bytes -> fp32 scales."""
+    return torch.ldexp(torch.ones(exp.shape, dtype=torch.float32, device=exp.device), exp.to(torch.int32) - 127)
+
+
+def quantize_weights_ue8m0(w: torch.Tensor):
+    """bf16/fp32 ``[G, N, K]`` -> (e4m3 ``[G, N, K]``, uint8 exponents ``[G, N/128, K/128]``): 128x128 blocks whose
+    scale is the smallest power of two that keeps the block inside e4m3's range."""
+    G, N, K = w.shape
+    blocks = w.float().view(G, N // 128, 128, K // 128, 128)
+    amax = blocks.abs().amax(dim=(2, 4)).clamp(min=1e-4)
+    ex = torch.ceil(torch.log2(amax / 448.0))
+    q = (blocks * torch.exp2(-ex)[:, :, None, :, None]).to(torch.float8_e4m3fn).view(G, N, K)
+    return q.contiguous(), (ex.to(torch.int32) + 127).to(torch.uint8).contiguous()
+
+
+def grouped_gemm_mxfp8(a: torch.Tensor, scale_a: torch.Tensor, w: torch.Tensor, scale_w: torch.Tensor, row_start: torch.Tensor,
+                       row_count: torch.Tensor, out: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None, grid: int = 0) -> torch.Tensor:
+    """Grouped GEMM with power-of-two block scales applied inside the tensor core (block-scaled MMA),
+    256 x 256 tiles on CTA pairs: no per-step promotion, so it runs well above ``grouped_gemm_fp8``.
+
+    ``scale_a``: biased exponents, uint8 ``[rows, K/128]`` or the int32 ``[rows, K/512]`` packing that
+    ``Buffer.dispatch(..., use_ue8m0=True)`` delivers; ``scale_w``: uint8 ``[G, N/128, K/128]``
+    (``quantize_weights_ue8m0``).  ``K % 512 == 0`` and ``N % 256 == 0``."""
+    rows, K = a.shape
+    G, N, K2 = w.shape
+    if K != K2 or K % 512 or N % 256:
+        raise ValueError("K must be a multiple of 512, N of 256, and a and w must agree on K")
+    if a.dtype != torch.float8_e4m3fn or w.dtype != torch.float8_e4m3fn:
+        raise TypeError("a and w must be float8_e4m3fn")
+    if scale_a.dtype == torch.int32:
+        scale_a = scale_a.contiguous().view(torch.uint8)
+    if scale_a.dtype != torch.uint8 or scale_w.dtype != torch.uint8:
+        raise TypeError("scales must be UE8M0 exponent bytes")
+    if scale_a.numel() != rows * (K // 128) or tuple(scale_w.shape) != (G, N // 128, K // 128):
+        raise ValueError("scale shapes do not match")
+    if row_start.numel() == G + 1:
+        row_start = row_start[:G]
+    for t in (a, scale_a, w, scale_w, row_start, row_count):
+        if not t.is_contiguous():
+            raise ValueError("inputs must be contiguous")
+    dev = a.device
+    with torch.cuda.device(dev):
+        if out is None:
+            out = torch.empty(rows, N, dtype=torch.bfloat16, device=dev)
+        if status is None:
+            status = torch.zeros(1, dtype=torch.int32, device=dev)
+    p = _Params()
+    p.a, p.scale_a, p.w, p.scale_w, p.d = a.data_ptr(), scale_a.data_ptr(), w.data_ptr(), scale_w.data_ptr(), out.data_ptr()
+    p.row_start, p.row_count = row_start.data_ptr(), row_count.data_ptr()
+    p.groups, p.N, p.K, p.a_rows, p.grid = G, N, K, rows, grid
+    p.tile_mode = 3
+    p.status = status.data_ptr()
+    fn = _lib.lib().nixl_grouped_gemm_fp8_launch
+    fn.argtypes = [ctypes.POINTER(_Params), ctypes.c_void_p]
+    fn.restype = ctypes.c_int
+    with torch.cuda.device(dev):
+        _lib.check(fn(ctypes.byref(p), ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)), "nixl_grouped_gemm_fp8_launch (block-scaled)")
+    out._nixl_status = status
+    return out
+
+
 def grouped_gemm_fp8(
     a: torch.Tensor,
     scale_a: torch.Tensor,
