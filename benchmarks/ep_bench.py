@@ -25,7 +25,7 @@ sys.path.insert(0, ROOT)
 import torch  # noqa: E402
 import torch.distributed as dist  # noqa: E402
 
-from nixl_b200.ops import grouped_gemm_fp8, quantize_weights  # noqa: E402
+from nixl_b200.ops import grouped_gemm_fp8, grouped_gemm_mxfp8, quantize_weights, quantize_weights_ue8m0  # noqa: E402
 from nixl_b200.parallel import Buffer, per_token_cast_to_fp8  # noqa: E402
 
 
@@ -213,6 +213,24 @@ def main():
                 gemm()
 
             t_gemm = timed(gemm, args.iters, args.warmup, flush, world, dev)
+            t_mx = None
+            if compact and args.inter % 256 == 0 and H % 512 == 0:
+                # Power-of-two scales end to end: dispatch delivers exponent bytes, the tensor core applies them.
+                wq2, swb = quantize_weights_ue8m0(torch.randn(El, args.inter, H, device=dev, generator=gen) * 0.02)
+                mx = {}
+
+                def dispatch_mx():
+                    mx["rx"], mx["sc"], mx["h"] = buf.dispatch(x, idx, use_fp8=True, use_ue8m0=True)
+
+                def gemm_mx():
+                    grouped_gemm_mxfp8(mx["rx"], mx["sc"], wq2, swb, mx["h"].expert_offsets, mx["h"].recv_count, out=d, status=st)
+
+                dispatch_mx()
+                torch.cuda.synchronize()
+                t_mx = timed(gemm_mx, args.iters, args.warmup, flush, world, dev)
+                do_dispatch()  # back to the fp32-scale state the following measurements expect
+                torch.cuda.synchronize()
+                del wq2, swb
             t_unf = timed(unfused, args.iters, args.warmup, flush, world, dev)
             t_fus = timed(fused, args.iters, args.warmup, flush, world, dev)
             flops = 2.0 * recv_rows * args.inter * H
@@ -221,6 +239,8 @@ def main():
                 "dispatch_then_gemm_us": round(t_unf, 1), "fused_dispatch_gemm_us": round(t_fus, 1),
                 "gemm_status": int(st.item()) | int(buf._gemm_status.item()), "gemm_weight_GB": round(El * args.inter * H / 1e9, 3),
             })
+            if t_mx is not None:
+                rec.update({"gemm_block_scaled_us": round(t_mx, 1), "gemm_block_scaled_TFLOPs": round(flops / t_mx / 1e6, 1)})
             del wq, sw, d
 
         if not args.skip_baseline:

@@ -126,8 +126,9 @@ __device__ __forceinline__ uint32_t instrDescMx(uint32_t sf) {
     return (sf << 4) | (static_cast<uint32_t>(BNS >> 3) << 17) | (1u << 23) | (static_cast<uint32_t>((2 * BM) >> 4) << 24) | (sf << 29);
 }
 
-// One 128-channel step: eight block-scaled MMAs (four per accumulator half), the commit that frees
-// the stage, then a non-blocking test of the next step's barrier (behind the MMAs on purpose).
+// One 128-channel step: eight block-scaled MMAs (four per accumulator half) and the commit that frees
+// the stage.  The non-blocking test of the next step's barrier sits between the two groups of
+// MMAs: its latency then runs while the second group is being issued, and its result is read last.
 __device__ __forceinline__ void issueKStepMx(uint32_t tmem_d0, uint32_t tmem_d1, uint64_t da, uint64_t dw0, uint64_t dw1, uint32_t idesc, uint32_t tsfa,
                                              uint32_t tsfb0, uint32_t tsfb1, uint32_t accumulate, uint32_t bar_stage_empty, uint32_t peek_bar,
                                              uint32_t peek_par, uint32_t &ready_next) {
@@ -144,6 +145,7 @@ __device__ __forceinline__ void issueKStepMx(uint32_t tmem_d0, uint32_t tmem_d1,
         " tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%1], %3, %4, %7, [%8], [%9], pacc;\n"
         " add.u64 %3, %3, 2;\n add.u64 %4, %4, 2;\n"
         " tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%1], %3, %4, %7, [%8], [%9], pacc;\n"
+        " mbarrier.test_wait.parity.shared::cta.b64 pf, [%13], %14;\n"
         " tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%2], %6, %5, %7, [%8], [%10], pfirst;\n"
         " add.u64 %6, %6, 2;\n add.u64 %5, %5, 2;\n"
         " tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%2], %6, %5, %7, [%8], [%10], pacc;\n"
@@ -152,7 +154,6 @@ __device__ __forceinline__ void issueKStepMx(uint32_t tmem_d0, uint32_t tmem_d1,
         " add.u64 %6, %6, 2;\n add.u64 %5, %5, 2;\n"
         " tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%2], %6, %5, %7, [%8], [%10], pacc;\n"
         " tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%12], %16;\n"
-        " mbarrier.test_wait.parity.shared::cta.b64 pf, [%13], %14;\n"
         " selp.u32 %0, 1, 0, pf;\n"
         "}\n"
         : "=r"(ready_next), "+r"(tmem_d0), "+r"(tmem_d1), "+l"(da), "+l"(dw0), "+l"(dw1), "+l"(da2)

@@ -527,12 +527,16 @@ class Buffer:
 
     # ------------------------------------------------------------------ throughput mode
 
-    def dispatch(self, x: torch.Tensor, topk_idx: torch.Tensor, use_fp8: bool = True, round_scale: bool = False):
+    def dispatch(self, x: torch.Tensor, topk_idx: torch.Tensor, use_fp8: bool = True, round_scale: bool = False, use_ue8m0: bool = False):
         """Throughput-mode dispatch: compact layout.
 
         Returns ``(recv_x [rows, hidden], scales [rows, hidden//128] | None, handle)``; rows of
-        local expert ``e`` are ``handle.expert_offsets[e] : handle.expert_offsets[e] + handle.recv_count[e]``."""
-        recv_x, scales, handle, _, keep = self._dispatch(x, topk_idx, use_fp8, round_scale, 0, 3, False)
+        local expert ``e`` are ``handle.expert_offsets[e] : handle.expert_offsets[e] + handle.recv_count[e]``.
+        With ``use_ue8m0`` the scales are exponent bytes packed as int32 ``[rows, hidden//512]``, the
+        form ``grouped_gemm_mxfp8`` consumes."""
+        if use_ue8m0 and (not use_fp8 or self.hidden % 512):
+            raise ValueError("UE8M0 scales need fp8 dispatch and hidden % 512 == 0")
+        recv_x, scales, handle, _, keep = self._dispatch(x, topk_idx, use_fp8, round_scale, 0, 3, False, use_ue8m0=use_ue8m0)
         self._keep = keep
         return recv_x, scales, handle
 

@@ -211,6 +211,37 @@ def test_ue8m0_scales_are_the_exponents_of_rounded_scales():
     buf.destroy()
 
 
+def test_dispatch_ue8m0_feeds_block_scaled_gemm():
+    """Throughput dispatch with exponent-byte scales straight into the block-scaled grouped GEMM, result into the
+    exposed combine buffer, pull combine: the whole expert layer without a staging copy."""
+    from nixl_b200.ops import from_ue8m0, grouped_gemm_mxfp8, quantize_weights_ue8m0
+
+    dev = torch.device("cuda", 0)
+    T, H, E, K, N = 96, 1024, 4, 2, 1024  # N = H so the outputs can go back through combine
+    buf = Buffer(0, 1, E, H, T, K, device=dev, low_latency_mode=False)
+    g = torch.Generator(device=dev).manual_seed(9)
+    x = torch.randn(T, H, device=dev, generator=g).to(torch.bfloat16)
+    wts, idx = torch.topk(torch.softmax(torch.randn(T, E, device=dev, generator=g), -1), K, -1)
+    idx, wts = idx.long().contiguous(), wts.float().contiguous()
+    w = torch.randn(E, N, H, device=dev, generator=g) * 0.05
+    wq, swb = quantize_weights_ue8m0(w)
+    rx, packed, handle = buf.dispatch(x, idx, use_fp8=True, use_ue8m0=True)
+    y = buf.get_next_combine_buffer(handle)
+    grouped_gemm_mxfp8(rx[: buf.compact_rows], packed[: buf.compact_rows].contiguous(), wq, swb, handle.expert_offsets, handle.recv_count, out=y)
+    out = buf.combine(y, idx, wts, handle)
+    torch.cuda.synchronize()
+    assert buf.status == 0
+    q, s = per_token_cast_to_fp8(x, round_scale=True)
+    xd = dequant_fp8(q, s)
+    wd = (wq.float().view(E, N // 128, 128, H // 128, 128) * from_ue8m0(swb)[:, :, None, :, None]).view(E, N, H)
+    want = torch.zeros(T, N, device=dev)
+    for k in range(K):
+        yk = torch.einsum("th,tnh->tn", xd, wd[idx[:, k]]).to(torch.bfloat16).float()
+        want += wts[:, k : k + 1] * yk
+    torch.testing.assert_close(out.float(), want.to(torch.bfloat16).float(), rtol=3e-2, atol=3e-2)
+    buf.destroy()
+
+
 def test_dispatch_layout_counts_match_torch():
     dev = torch.device("cuda", 0)
     buf = Buffer(0, 4, 32, 1024, 300, 6, device=dev, low_latency_mode=False)  # statistics need no peers
