@@ -31,8 +31,6 @@ except Exception:  # pragma: no cover
 DEFAULT_COMM_PORT = nixlBind.DEFAULT_COMM_PORT
 
 # Opaque handle aliases (integers holding native pointers).
-nixl_xfer_handle = int
-nixl_prepped_dlist_handle = int
 nixl_backend_handle = int
 
 
@@ -93,6 +91,68 @@ _MEM = {
 _OPS = {"READ": nixlBind.NIXL_READ, "WRITE": nixlBind.NIXL_WRITE}
 
 
+class nixl_prepped_dlist_handle(int):
+    """Handle of a prepared descriptor list.  It is the native handle value (an ``int``) with
+    ownership: ``release()`` frees it, and so does garbage collection if the caller forgot
+    (src/api/python/_api.py:49 in the reference)."""
+
+    def __new__(cls, agent, value: int):
+        self = super().__new__(cls, int(value))
+        self._agent = agent
+        self._released = False
+        return self
+
+    def __repr__(self) -> str:
+        return f"nixl_prepped_dlist_handle(0x{int(self):x}, released={self._released})"
+
+    def release(self) -> None:
+        if not self._released:
+            self._agent.releasedDlistH(int(self))
+            self._released = True
+
+    def __del__(self):
+        try:
+            self.release()
+        except Exception:
+            pass
+
+
+class nixl_xfer_handle(int):
+    """Handle of a transfer request (the native handle value with ownership).  ``release()`` frees
+    it and raises if the backend cannot let go yet; when garbage collection hits that case the
+    handle is parked on the agent and released again when the agent goes away
+    (src/api/python/_api.py:89 in the reference)."""
+
+    def __new__(cls, owner, value: int):
+        self = super().__new__(cls, int(value))
+        self._owner = owner  # the nixl_agent wrapper: keeps the native agent alive and holds the leak list
+        self._released = False
+        return self
+
+    def __repr__(self) -> str:
+        return f"nixl_xfer_handle(0x{int(self):x}, released={self._released})"
+
+    def release(self) -> None:
+        if self._released:
+            return
+        st = self._owner.agent.releaseXferReq(int(self))
+        if st != nixlBind.NIXL_SUCCESS:
+            raise _error_for(st, "releaseXferReq")
+        self._released = True
+
+    def __del__(self):
+        if self._released:
+            return
+        try:
+            self.release()
+        except Exception:
+            try:
+                self._owner._leaked_xfer_handles.append(int(self))
+                self._released = True
+            except Exception:
+                pass
+
+
 def _is_tensor(x: Any) -> bool:
     return torch is not None and isinstance(x, torch.Tensor)
 
@@ -136,6 +196,7 @@ class nixl_agent:
         self.name = agent_name
         self.agent = nixlBind.nixlAgent(agent_name, cfg)
         self.notifs: dict[str, list[bytes]] = {}
+        self._leaked_xfer_handles: list[int] = []
         self.backends: dict[str, int] = {}
         self.backend_mems: dict[str, list[int]] = {}
         self.backend_options: dict[str, dict[str, str]] = {}
@@ -159,6 +220,14 @@ class nixl_agent:
 
         self.nixl_mems = dict(_MEM)
         self.nixl_ops = dict(_OPS)
+
+    def __del__(self):
+        # Transfer handles that could not be released when they were collected get one more try.
+        for h in getattr(self, "_leaked_xfer_handles", []):
+            try:
+                self.agent.releaseXferReq(h)
+            except Exception:
+                pass
 
     # ------------------------------------------------------------------ plugins / backends
 
@@ -290,11 +359,11 @@ class nixl_agent:
 
     # ------------------------------------------------------------------ transfers
 
-    def prep_xfer_dlist(self, agent_name: str, xfer_list, mem_type: Optional[str] = None, backends: Sequence[str] = ()) -> int:
+    def prep_xfer_dlist(self, agent_name: str, xfer_list, mem_type: Optional[str] = None, backends: Sequence[str] = ()) -> nixl_prepped_dlist_handle:
         """Prepare one side of a transfer. ``agent_name`` "NIXL_INIT_AGENT" (or "") = local side."""
         if agent_name == "NIXL_INIT_AGENT":
             agent_name = nixlBind.NIXL_INIT_AGENT
-        return self.agent.prepXferDlist(agent_name, self.get_xfer_descs(xfer_list, mem_type), self._handles(backends))
+        return nixl_prepped_dlist_handle(self.agent, self.agent.prepXferDlist(agent_name, self.get_xfer_descs(xfer_list, mem_type), self._handles(backends)))
 
     def estimate_xfer_cost(self, req_handle: int) -> tuple[int, int, int]:
         """(duration_us, error_margin_us, method)."""
@@ -310,17 +379,17 @@ class nixl_agent:
         notif_msg: Union[bytes, str] = b"",
         backends: Sequence[str] = (),
         skip_desc_merge: bool = False,
-    ) -> int:
-        return self.agent.makeXferReq(
+    ) -> nixl_xfer_handle:
+        return nixl_xfer_handle(self, self.agent.makeXferReq(
             _OPS[operation],
-            local_xfer_side,
+            int(local_xfer_side),
             local_indices,
-            remote_xfer_side,
+            int(remote_xfer_side),
             remote_indices,
             notif_msg if notif_msg else None,
             self._handles(backends),
             skip_desc_merge,
-        )
+        ))
 
     def initialize_xfer(
         self,
@@ -330,15 +399,15 @@ class nixl_agent:
         remote_agent: str,
         notif_msg: Union[bytes, str] = b"",
         backends: Sequence[str] = (),
-    ) -> int:
-        return self.agent.createXferReq(
+    ) -> nixl_xfer_handle:
+        return nixl_xfer_handle(self, self.agent.createXferReq(
             _OPS[operation],
             self.get_xfer_descs(local_descs),
             self.get_xfer_descs(remote_descs),
             remote_agent,
             notif_msg if notif_msg else None,
             self._handles(backends),
-        )
+        ))
 
     def transfer(self, handle: int, notif_msg: Union[bytes, str] = b"", custom_param: str = "") -> str:
         """Post the transfer. Returns "DONE", "PROC" or "ERR"."""
@@ -366,11 +435,17 @@ class nixl_agent:
         raise nixlBind.nixlNotFoundError("backend of the transfer is unknown to this wrapper")
 
     def release_xfer_handle(self, handle: int) -> None:
+        if isinstance(handle, nixl_xfer_handle):
+            handle.release()
+            return
         st = self.agent.releaseXferReq(handle)
         if st != nixlBind.NIXL_SUCCESS:
             raise _error_for(st, "releaseXferReq")
 
     def release_dlist_handle(self, handle: int) -> None:
+        if isinstance(handle, nixl_prepped_dlist_handle):
+            handle.release()
+            return
         self.agent.releasedDlistH(handle)
 
     # ------------------------------------------------------------------ device-side views

@@ -154,3 +154,42 @@ def test_python_logging_follows_nixl_log_level(monkeypatch, capsys):
     assert root.level == logging.INFO
     monkeypatch.delenv("NIXL_LOG_LEVEL")
     nlog.setup_logging(force=True)
+
+
+def test_handles_own_their_native_objects():
+    import gc
+
+    import torch
+
+    from nixl_b200 import nixl_agent, nixl_agent_config
+    from nixl_b200._api import nixl_prepped_dlist_handle, nixl_xfer_handle
+
+    a = nixl_agent("own_a", nixl_agent_config(enable_prog_thread=False, backends=["NVLINK"]))
+    b = nixl_agent("own_b", nixl_agent_config(enable_prog_thread=False, backends=["NVLINK"]))
+    src, dst = torch.arange(1024, dtype=torch.uint8), torch.zeros(1024, dtype=torch.uint8)
+    a.register_memory(src)
+    b.register_memory(dst)
+    a.add_remote_agent(b.get_agent_metadata())
+    h = a.initialize_xfer("WRITE", src, dst, "own_b")
+    assert isinstance(h, nixl_xfer_handle) and isinstance(h, int) and "released=False" in repr(h)
+    assert a.transfer(h) in ("DONE", "PROC")
+    while a.check_xfer_state(h) == "PROC":
+        pass
+    assert torch.equal(src, dst)
+    h.release()
+    h.release()  # idempotent
+    a.release_xfer_handle(h)  # also fine after release()
+    assert "released=True" in repr(h)
+    # prepared lists: wrapper in, wrapper out; dropping the last reference frees them
+    side_l = a.prep_xfer_dlist("NIXL_INIT_AGENT", src)
+    side_r = a.prep_xfer_dlist("own_b", dst)
+    assert isinstance(side_l, nixl_prepped_dlist_handle)
+    h2 = a.make_prepped_xfer("WRITE", side_l, [0], side_r, [0])
+    assert a.transfer(h2) in ("DONE", "PROC")
+    while a.check_xfer_state(h2) == "PROC":
+        pass
+    del h2
+    gc.collect()
+    a.release_dlist_handle(side_l)
+    del side_r
+    gc.collect()
