@@ -4,7 +4,7 @@
 Inputs are larger than L2 (126 MB) where DRAM figures matter, hold at most a few GB and launch
 the kernel of interest a handful of times.  One GPU only.
 
-    python benchmarks/profile_cases.py copy|kv|ep|gemm
+    python benchmarks/profile_cases.py copy|kv|ep|gemm|gemm_pair|gemm_mx
 """
 import os
 import sys
@@ -74,22 +74,52 @@ def case_ep():
     assert buf.status == 0
 
 
-def case_gemm():
-    from nixl_b200.ops import grouped_gemm_fp8, quantize_weights
+def _gemm_inputs(G=8, N=2048, K=7168, rows_per=1024, pow2=False):
     from nixl_b200.parallel import per_token_cast_to_fp8
 
-    G, N, K, rows_per = 8, 2048, 7168, 1024
     x = torch.randn(G * rows_per, K, device="cuda:0", dtype=torch.bfloat16)
-    a, sa = per_token_cast_to_fp8(x)
-    wq, sw = quantize_weights(torch.randn(G, N, K, device="cuda:0") * 0.02)
+    a, sa = per_token_cast_to_fp8(x, round_scale=pow2)
     rs = (torch.arange(G, device="cuda:0") * rows_per).int()
     rc = torch.full((G,), rows_per, device="cuda:0", dtype=torch.int32)
+    return a.contiguous(), sa.contiguous(), rs, rc
+
+
+def _case_gemm(tile_mode):
+    from nixl_b200.ops import grouped_gemm_fp8, quantize_weights
+
+    G, N, K = 8, 2048, 7168
+    a, sa, rs, rc = _gemm_inputs(G, N, K)
+    wq, sw = quantize_weights(torch.randn(G, N, K, device="cuda:0") * 0.02)
     for _ in range(3):
-        out = grouped_gemm_fp8(a.contiguous(), sa.contiguous(), wq, sw, rs, rc)
+        out = grouped_gemm_fp8(a, sa, wq, sw, rs, rc, tile_mode=tile_mode)
+    torch.cuda.synchronize()
+    assert int(out._nixl_status.item()) == 0
+
+
+def case_gemm():
+    """128 x 128 tiles on single CTAs (groupedGemmKernel)."""
+    _case_gemm(1)
+
+
+def case_gemm_pair():
+    """256 x 256 tiles on CTA pairs, fp32 block scales (groupedGemmPairKernel)."""
+    _case_gemm(2)
+
+
+def case_gemm_mx():
+    """256 x 256 tiles on CTA pairs, power-of-two scales in the tensor core (groupedGemmMxPairKernel)."""
+    from nixl_b200.ops import grouped_gemm_mxfp8, quantize_weights_ue8m0, to_ue8m0
+
+    G, N, K = 8, 2048, 7168
+    a, sa, rs, rc = _gemm_inputs(G, N, K, pow2=True)
+    wq, swb = quantize_weights_ue8m0(torch.randn(G, N, K, device="cuda:0") * 0.02)
+    sab = to_ue8m0(sa)
+    for _ in range(3):
+        out = grouped_gemm_mxfp8(a, sab, wq, swb, rs, rc)
     torch.cuda.synchronize()
     assert int(out._nixl_status.item()) == 0
 
 
 if __name__ == "__main__":
-    {"copy": case_copy, "kv": case_kv, "ep": case_ep, "gemm": case_gemm}[sys.argv[1]]()
+    {"copy": case_copy, "kv": case_kv, "ep": case_ep, "gemm": case_gemm, "gemm_pair": case_gemm_pair, "gemm_mx": case_gemm_mx}[sys.argv[1]]()
     print("ok", sys.argv[1])

@@ -143,6 +143,11 @@ class Buffer:
 
         if num_experts % num_ranks:
             raise ValueError("num_experts must be divisible by num_ranks")
+        self._init_args = dict(hidden=hidden, num_max_dispatch_tokens_per_rank=num_max_dispatch_tokens_per_rank, num_topk=num_topk,
+                               timeout_ms=timeout_ms, compact_rows=compact_rows, low_latency_mode=low_latency_mode,
+                               explicitly_destroy=explicitly_destroy, combine_pull=combine_pull)
+        self._num_sms = getattr(self, "_num_sms", 0)
+        self._store = getattr(self, "_store", None)
         self.rank, self.num_ranks, self.num_experts = rank, num_ranks, num_experts
         self.local_experts = num_experts // num_ranks
         self.hidden, self.max_tokens, self.topk = hidden, num_max_dispatch_tokens_per_rank, num_topk
@@ -218,6 +223,55 @@ class Buffer:
         half = rows * (hidden * 4 + (hidden // 128) * 4 + 8) + num_max_dispatch_tokens_per_rank * num_topk * hidden * 2
         return 2 * half + (1 << 20)
 
+    get_low_latency_buffer_size_hint = get_low_latency_rdma_size_hint
+    get_rdma_size_hint = get_low_latency_rdma_size_hint
+
+    # ------------------------------------------------------------------ reference-named utilities
+
+    def set_tcp_store_group(self, store) -> None:
+        """Use a ``torch.distributed`` store (e.g. ``TCPStore``) for the metadata exchange of ``connect_ranks``
+        instead of a collective: ranks may then join at different times (elastic set-ups)."""
+        self._store = store
+
+    def set_num_sms(self, num_sms: int) -> None:
+        """CTAs the dispatch and combine kernels use (0: one per SM), leaving the rest to concurrent compute."""
+        self._num_sms = max(0, int(num_sms))
+
+    @property
+    def num_sms(self) -> int:
+        return self._num_sms
+
+    def get_dispatch_config(self, num_ranks: Optional[int] = None) -> dict:
+        """Launch configuration in use (the reference returns tuned per-rank-count tables; here the kernels size
+        their per-token thread groups themselves and the only knob is the CTA count)."""
+        return {"num_sms": self._num_sms or torch.cuda.get_device_properties(self.device).multi_processor_count}
+
+    get_combine_config = get_dispatch_config
+
+    def get_comm_stream(self) -> torch.cuda.Stream:
+        """The stream the communication kernels run on: the caller's current stream (no hidden stream)."""
+        return torch.cuda.current_stream(self.device)
+
+    def capture(self) -> "EventOverlap":
+        """An event at the current point of the current stream."""
+        return EventOverlap(self._record())
+
+    def get_local_buffer_tensor(self, dtype: torch.dtype = torch.uint8, offset: int = 0, size: Optional[int] = None) -> torch.Tensor:
+        """A typed view of this rank's symmetric buffer (debugging, custom kernels over the same memory)."""
+        raw = self.buffer[offset : (offset + size) if size is not None else None]
+        return raw.view(dtype)
+
+    def update_memory_buffers(self, num_ranks: int, num_experts_per_rank: int, num_rdma_bytes: int = 0) -> None:
+        """Re-size for another world size (ranks joined or left for good): every rank calls this with the new
+        shape, then ``connect_ranks`` again.  Outstanding handles become invalid."""
+        if num_ranks == self.num_ranks and num_experts_per_rank == self.local_experts:
+            return
+        agent, rank, device, group, store, sms = self.agent, self.rank, self.device, self.group, self._store, self._num_sms
+        own = self._own_agent
+        self.destroy()
+        self.__init__(rank, num_ranks, num_ranks * num_experts_per_rank, device=device, agent=agent, group=group, **self._init_args)
+        self._own_agent, self._store, self._num_sms = own, store, sms
+
     # ------------------------------------------------------------------ connection management
 
     def local_metadata(self) -> dict:
@@ -236,6 +290,12 @@ class Buffer:
         over the ``torch.distributed`` group given at construction."""
         if metadata is None and self.num_ranks == 1:
             metadata = [self.local_metadata()]
+        if metadata is None and self._store is not None:
+            import pickle
+
+            self._store.set(f"nixl_ep/md/{self.rank}", pickle.dumps(self.local_metadata()))
+            want = list(remote_ranks) if remote_ranks is not None else list(range(self.num_ranks))
+            metadata = [pickle.loads(self._store.get(f"nixl_ep/md/{r}")) for r in sorted(set(want) | {self.rank})]
         if metadata is None:
             import torch.distributed as dist
 
@@ -414,7 +474,7 @@ class Buffer:
         p.round_scale = int(round_scale)
         p.peers = self._peers_view
         p.epoch = epoch
-        p.grid = grid
+        p.grid = grid or self._num_sms
         stream_ptr = ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
         fn, ref = self._dispatch_fn, ctypes.byref(p)
 
@@ -573,7 +633,7 @@ class Buffer:
         p.recv_count, p.expert_offsets = handle.recv_count.data_ptr(), handle.expert_offsets.data_ptr()
         p.topk_idx, p.topk_weights, p.out = topk_idx.data_ptr(), topk_weights.data_ptr(), out.data_ptr()
         p.T, p.K, p.H, p.E, p.R, p.rank = T, K, self.hidden, self.num_experts, self.num_ranks, self.rank
-        p.grid = 0
+        p.grid = self._num_sms
         p.peers = self._peers_view
         p.lay = self._layout(handle.parity)
         p.epoch, p.timeout_ns = handle.epoch, self.timeout_ns

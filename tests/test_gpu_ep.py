@@ -242,6 +242,30 @@ def test_dispatch_ue8m0_feeds_block_scaled_gemm():
     buf.destroy()
 
 
+def test_resize_and_utility_entry_points():
+    dev = torch.device("cuda", 0)
+    buf = Buffer(0, 1, 8, 1024, 32, 2, device=dev)
+    assert Buffer.get_low_latency_buffer_size_hint(32, 1024, 1, 8, 2) == Buffer.get_low_latency_rdma_size_hint(32, 1024, 1, 8, 2)
+    buf.set_num_sms(16)
+    assert buf.num_sms == 16 and buf.get_dispatch_config()["num_sms"] == 16
+    assert buf.get_local_buffer_tensor(torch.int32).numel() * 4 == buf.buffer.numel()
+    x = torch.randn(32, 1024, device=dev, dtype=torch.bfloat16)
+    idx = torch.randint(0, 8, (32, 2), device=dev)
+    buf.dispatch(x, idx)
+    ev = buf.capture()
+    ev.current_stream_wait()
+    torch.cuda.synchronize()
+    assert buf.status == 0
+    before = buf.buffer.numel()
+    buf.update_memory_buffers(1, 16)  # twice the local experts: a larger buffer, same agent
+    assert buf.local_experts == 16 and buf.num_experts == 16 and buf.buffer.numel() > before and buf.num_sms == 16
+    idx = torch.randint(0, 16, (32, 2), device=dev)
+    rx, sc, h = buf.dispatch(x, idx)
+    torch.cuda.synchronize()
+    assert buf.status == 0 and int(h.recv_count.sum()) == 64
+    buf.destroy()
+
+
 def test_dispatch_layout_counts_match_torch():
     dev = torch.device("cuda", 0)
     buf = Buffer(0, 4, 32, 1024, 300, 6, device=dev, low_latency_mode=False)  # statistics need no peers
