@@ -269,6 +269,7 @@ Engine::Engine(const nixlBackendInitParams *init) : nixlBackendEngine(init) {
     auto cp = params.find("copy_path");
     if (cp != params.end() && (cp->second == "bulk" || cp->second == "tma")) copyPath_ = CopyPath::BULK;
     gridOverride_ = static_cast<int>(paramLong(params, "grid_ctas", 0));
+    chunkShiftOverride_ = static_cast<int>(paramLong(params, "chunk_shift", 0));
     livenessPing_ = paramBool(params, "liveness_ping", false);
     const long dev = paramLong(params, "device_id", -1);
     if (dev >= 0) primaryDevice_ = static_cast<int>(dev);
@@ -347,6 +348,8 @@ DeviceCtx *Engine::ctx(int device) const {
     for (int i = kFlagSlots - 1; i >= 0; --i) c->freeFlags.push_back(i);
     c->arena = std::make_unique<DeviceArena>(device);
     c->gridCtas = gridOverride_ > 0 ? gridOverride_ : defaultGridCtas(device);
+    c->smCount = 148;
+    if (cudaDeviceGetAttribute(&c->smCount, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || c->smCount <= 0) c->smCount = 148;
     ctxs_[device] = std::move(c);
     return ctxs_[device].get();
 }
@@ -687,9 +690,13 @@ nixl_status_t Engine::prepXfer(const nixl_xfer_op_t &operation, const nixl_meta_
             total += d.len;
             longest = std::max<uint64_t>(longest, d.len);
         }
-        // Chunk size: aim at ~2 chunks per CTA of a full grid, between 16 KiB and 256 KiB.
-        uint32_t shift = log2Ceil(std::max<uint64_t>(1, total / (2 * static_cast<uint64_t>(c->gridCtas))));
+        // Chunk size: aim at ~2 chunks per CTA that can be resident at once (two per SM), between
+        // 16 KiB and 256 KiB.  The grid itself may be several times larger (see defaultGridCtas): a
+        // large copy then runs as many short-lived CTAs whose tail balances itself.
+        const uint64_t resident = std::min<uint64_t>(static_cast<uint64_t>(c->gridCtas), 2 * static_cast<uint64_t>(c->smCount));
+        uint32_t shift = log2Ceil(std::max<uint64_t>(1, total / (2 * std::max<uint64_t>(1, resident))));
         shift = std::min<uint32_t>(18, std::max<uint32_t>(14, shift));
+        if (chunkShiftOverride_ >= 14 && chunkShiftOverride_ <= 22) shift = static_cast<uint32_t>(chunkShiftOverride_);
         const size_t n = b.descs.size();
         std::vector<uint32_t> starts(n + 1);
         uint64_t chunks = 0;

@@ -106,6 +106,7 @@ struct DeviceCtx {
     uint64_t *flags = nullptr;         // pinned, mapped completion words
     std::vector<int> freeFlags;
     int gridCtas = 0;
+    int smCount = 148;
     std::mutex mu;
 };
 
@@ -215,6 +216,7 @@ private:
     bool pinDram_ = true;
     CopyPath copyPath_ = CopyPath::VECTOR;
     int gridOverride_ = 0;
+    int chunkShiftOverride_ = 0; // "chunk_shift" parameter: log2 of the bytes one CTA copies at a time (14..22); 0 = automatic
     size_t memcpyAsyncThreshold_ = 0;
     bool livenessPing_ = false;
 
