@@ -8,8 +8,17 @@
 // benchmarks/nixlbench.py.
 //
 //   nixlbench [--backend NVLINK] [--op WRITE|READ] [--mem VRAM|DRAM] [--src-dev 0] [--dst-dev 1]
-//             [--min 4096] [--max 1073741824] [--batch 1] [--iters 1000] [--warmup 100]
+//             [--min 4096] [--max 1073741824] [--batch 1] [--batch-max N] [--iters 1000] [--warmup 100]
 //             [--depth 1] [--copy-path vector|bulk] [--param key=value]... [--check]
+//             [--prepared] [--recreate] [--reregister] [--config file]
+//             [--file path [--num-files N] [--direct]]      storage mode (POSIX, GDS, GDS_MT backends)
+//
+// --prepared builds requests with prepXferDlist + makeXferReq (the reference's prepared_xfer),
+// --recreate creates and releases the request on every iteration (recreate_xfer), --reregister
+// registers and deregisters the source buffer on every iteration (reregister_mem), --config reads
+// "option=value" lines (config_file).  In storage mode the target side is a set of files owned by
+// the same agent: WRITE stores memory into the files, READ loads it back (filepath / num_files /
+// storage_enable_direct of the reference).
 #include <algorithm>
 #include <chrono>
 #include <cstdio>
@@ -17,6 +26,10 @@
 #include <cstring>
 #include <string>
 #include <vector>
+
+#include <fcntl.h>
+#include <fstream>
+#include <unistd.h>
 
 #include <cuda_runtime.h>
 
@@ -30,9 +43,76 @@ struct Args {
     std::string backend = "NVLINK", op = "WRITE", mem = "VRAM", copy_path = "vector";
     int src_dev = 0, dst_dev = -1, batch = 1, iters = 1000, warmup = 100, depth = 1;
     size_t min = 4096, max = size_t(1) << 30, total = size_t(8) << 30;
-    bool check = false;
+    bool check = false, prepared = false, recreate = false, reregister = false, direct = false;
+    int batch_max = 0, num_files = 1;
+    std::string file; // storage mode when set
     nixl_b_params_t extra; // --param key=value, passed to the backend
 };
+
+// One option (with its value, if it takes one).  False for an unknown option.
+bool setOption(Args &a, const std::string &k, const std::string &v) {
+    if (k == "--backend") a.backend = v;
+    else if (k == "--op") a.op = v;
+    else if (k == "--mem") a.mem = v;
+    else if (k == "--copy-path") a.copy_path = v;
+    else if (k == "--src-dev") a.src_dev = std::atoi(v.c_str());
+    else if (k == "--dst-dev") a.dst_dev = std::atoi(v.c_str());
+    else if (k == "--batch") a.batch = std::max(1, std::atoi(v.c_str()));
+    else if (k == "--batch-max") a.batch_max = std::atoi(v.c_str());
+    else if (k == "--iters") a.iters = std::atoi(v.c_str());
+    else if (k == "--warmup") a.warmup = std::atoi(v.c_str());
+    else if (k == "--depth") a.depth = std::max(1, std::atoi(v.c_str()));
+    else if (k == "--min") a.min = std::strtoull(v.c_str(), nullptr, 0);
+    else if (k == "--max") a.max = std::strtoull(v.c_str(), nullptr, 0);
+    else if (k == "--total") a.total = std::strtoull(v.c_str(), nullptr, 0);
+    else if (k == "--file") a.file = v;
+    else if (k == "--num-files") a.num_files = std::max(1, std::atoi(v.c_str()));
+    else if (k == "--param") {
+        const size_t eq = v.find('=');
+        if (eq != std::string::npos) a.extra[v.substr(0, eq)] = v.substr(eq + 1);
+    } else return false;
+    return true;
+}
+bool setFlag(Args &a, const std::string &k) {
+    if (k == "--check") a.check = true;
+    else if (k == "--prepared") a.prepared = true;
+    else if (k == "--recreate") a.recreate = true;
+    else if (k == "--reregister") a.reregister = true;
+    else if (k == "--direct") a.direct = true;
+    else return false;
+    return true;
+}
+bool loadConfig(Args &a, const std::string &path) {
+    std::ifstream f(path);
+    if (!f) return false;
+    std::string line;
+    while (std::getline(f, line)) {
+        const size_t hash = line.find('#');
+        if (hash != std::string::npos) line.erase(hash);
+        while (!line.empty() && std::isspace(static_cast<unsigned char>(line.back()))) line.pop_back();
+        size_t b = 0;
+        while (b < line.size() && std::isspace(static_cast<unsigned char>(line[b]))) ++b;
+        line.erase(0, b);
+        if (line.empty()) continue;
+        const size_t eq = line.find('=');
+        std::string k = "--" + (eq == std::string::npos ? line : line.substr(0, eq));
+        for (char &c : k)
+            if (c == '_') c = '-';
+        const std::string v = eq == std::string::npos ? "" : line.substr(eq + 1);
+        if (eq == std::string::npos || v == "true" || v == "1") {
+            if (setFlag(a, k)) continue;
+        }
+        if (v == "false" || v == "0") {
+            Args probe;
+            if (setFlag(probe, k)) continue; // a flag explicitly switched off
+        }
+        if (!setOption(a, k, v)) {
+            std::fprintf(stderr, "%s: unknown option %s\n", path.c_str(), line.c_str());
+            return false;
+        }
+    }
+    return true;
+}
 
 double pct(std::vector<double> &v, double q) {
     if (v.empty()) return 0;
@@ -45,127 +125,175 @@ int main(int argc, char **argv) {
     Args a;
     for (int i = 1; i < argc; ++i) {
         const std::string k = argv[i];
-        auto val = [&]() -> const char * { return i + 1 < argc ? argv[++i] : ""; };
-        if (k == "--backend") a.backend = val();
-        else if (k == "--op") a.op = val();
-        else if (k == "--mem") a.mem = val();
-        else if (k == "--copy-path") a.copy_path = val();
-        else if (k == "--src-dev") a.src_dev = std::atoi(val());
-        else if (k == "--dst-dev") a.dst_dev = std::atoi(val());
-        else if (k == "--batch") a.batch = std::atoi(val());
-        else if (k == "--iters") a.iters = std::atoi(val());
-        else if (k == "--warmup") a.warmup = std::atoi(val());
-        else if (k == "--depth") a.depth = std::max(1, std::atoi(val()));
-        else if (k == "--min") a.min = std::strtoull(val(), nullptr, 0);
-        else if (k == "--max") a.max = std::strtoull(val(), nullptr, 0);
-        else if (k == "--total") a.total = std::strtoull(val(), nullptr, 0);
-        else if (k == "--check") a.check = true;
-        else if (k == "--param") {
-            const std::string kv = val();
-            const size_t eq = kv.find('=');
-            if (eq != std::string::npos) a.extra[kv.substr(0, eq)] = kv.substr(eq + 1);
+        if (setFlag(a, k)) continue;
+        if (k == "--config") {
+            if (i + 1 >= argc || !loadConfig(a, argv[++i])) return 2;
+            continue;
         }
-        else {
+        if (i + 1 >= argc || !setOption(a, k, argv[i + 1])) {
             std::fprintf(stderr, "unknown option %s\n", k.c_str());
             return 2;
         }
+        ++i;
     }
     const bool vram = a.mem == "VRAM";
+    const bool storage = !a.file.empty();
     int ndev = 0;
     if (vram && (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0)) {
         std::fprintf(stderr, "no GPU\n");
         return 2;
     }
     if (a.dst_dev < 0) a.dst_dev = ndev > 1 ? 1 : 0;
-    const size_t buf_bytes = std::min(a.total, std::max<size_t>(a.max * a.batch, a.max));
+    if (a.batch_max < a.batch) a.batch_max = a.batch;
+    if (storage && a.backend == "NVLINK") a.backend = vram ? "GDS" : "POSIX";
+    const size_t buf_bytes = std::min(a.total, std::max<size_t>(a.max * a.batch_max, a.max));
     void *src = nullptr, *dst = nullptr;
-    if (vram) {
-        cudaSetDevice(a.src_dev);
-        if (cudaMalloc(&src, buf_bytes) != cudaSuccess) return 3;
-        cudaMemset(src, 0x5a, buf_bytes);
-        cudaSetDevice(a.dst_dev);
-        if (cudaMalloc(&dst, buf_bytes) != cudaSuccess) return 3;
-        cudaMemset(dst, 0, buf_bytes);
-        cudaSetDevice(a.src_dev);
-        cudaDeviceSynchronize();
-    } else {
-        src = std::malloc(buf_bytes);
-        dst = std::malloc(buf_bytes);
-        std::memset(src, 0x5a, buf_bytes);
-        std::memset(dst, 0, buf_bytes);
-    }
+    auto allocate = [&](void *&p, int dev, int fill) {
+        if (vram) {
+            cudaSetDevice(dev);
+            if (cudaMalloc(&p, buf_bytes) != cudaSuccess) return false;
+            cudaMemset(p, fill, buf_bytes);
+            cudaDeviceSynchronize();
+        } else {
+            if (posix_memalign(&p, 4096, buf_bytes) != 0) return false; // page-aligned: usable with O_DIRECT
+            std::memset(p, fill, buf_bytes);
+        }
+        return true;
+    };
+    if (!allocate(src, a.src_dev, 0x5a)) return 3;
+    if (!storage && !allocate(dst, a.dst_dev, 0)) return 3;
+    if (vram) cudaSetDevice(a.src_dev);
+
     nixlAgentConfig cfg(false);
     nixlAgent ini("initiator", cfg), tgt("target", cfg);
     nixlBackendH *bi = nullptr, *bt = nullptr;
-    nixl_b_params_t params = {{"copy_path", a.copy_path}};
+    nixl_b_params_t params;
+    if (a.backend == "NVLINK" || a.backend == "UCX") params["copy_path"] = a.copy_path;
     for (auto &kv : a.extra) params[kv.first] = kv.second;
-    if (ini.createBackend(a.backend, params, bi) != NIXL_SUCCESS || tgt.createBackend(a.backend, params, bt) != NIXL_SUCCESS) {
+    if (ini.createBackend(a.backend, params, bi) != NIXL_SUCCESS || (!storage && tgt.createBackend(a.backend, params, bt) != NIXL_SUCCESS)) {
         std::fprintf(stderr, "cannot create backend %s\n", a.backend.c_str());
         return 4;
     }
     const nixl_mem_t mt = vram ? VRAM_SEG : DRAM_SEG;
-    nixl_reg_dlist_t rs(mt), rd(mt);
+    const nixl_mem_t rmt = storage ? FILE_SEG : mt;
+    const std::string remote_name = storage ? "initiator" : "target";
+    nixl_reg_dlist_t rs(mt), rd(rmt);
     rs.addDesc(nixlBlobDesc(reinterpret_cast<uintptr_t>(src), buf_bytes, vram ? a.src_dev : 0, ""));
-    rd.addDesc(nixlBlobDesc(reinterpret_cast<uintptr_t>(dst), buf_bytes, vram ? a.dst_dev : 0, ""));
-    if (ini.registerMem(rs) != NIXL_SUCCESS || tgt.registerMem(rd) != NIXL_SUCCESS) return 5;
-    nixl_blob_t md;
-    std::string name;
-    tgt.getLocalMD(md);
-    if (ini.loadRemoteMD(md, name) != NIXL_SUCCESS) return 6;
+    std::vector<int> fds;
+    const size_t file_bytes = (buf_bytes + a.num_files - 1) / a.num_files;
+    if (storage) {
+        // The buffer is striped over num_files files of file_bytes each; devId of a FILE descriptor is its fd.
+        for (int f = 0; f < a.num_files; ++f) {
+            const std::string path = a.num_files == 1 ? a.file : a.file + "." + std::to_string(f);
+            const int fd = ::open(path.c_str(), O_RDWR | O_CREAT | (a.direct ? O_DIRECT : 0), 0644);
+            if (fd < 0 || ::ftruncate(fd, static_cast<off_t>(file_bytes)) != 0) {
+                std::fprintf(stderr, "cannot prepare %s\n", path.c_str());
+                return 5;
+            }
+            fds.push_back(fd);
+            rd.addDesc(nixlBlobDesc(0, file_bytes, static_cast<uint64_t>(fd), ""));
+        }
+        if (ini.registerMem(rs) != NIXL_SUCCESS || ini.registerMem(rd) != NIXL_SUCCESS) return 5;
+    } else {
+        rd.addDesc(nixlBlobDesc(reinterpret_cast<uintptr_t>(dst), buf_bytes, vram ? a.dst_dev : 0, ""));
+        if (ini.registerMem(rs) != NIXL_SUCCESS || tgt.registerMem(rd) != NIXL_SUCCESS) return 5;
+        nixl_blob_t md;
+        std::string name;
+        tgt.getLocalMD(md);
+        if (ini.loadRemoteMD(md, name) != NIXL_SUCCESS) return 6;
+    }
     const nixl_xfer_op_t op = a.op == "READ" ? NIXL_READ : NIXL_WRITE;
 
     std::printf("%-12s %6s %10s %10s %10s %10s %10s %10s\n", "block", "batch", "GB/s", "avg_us", "p50_us", "p99_us", "prep_us", "post_us");
-    for (size_t block = a.min; block <= a.max && block * a.batch <= buf_bytes; block *= 2) {
+    for (int batch = a.batch; batch <= a.batch_max; batch *= 2)
+    for (size_t block = a.min; block <= a.max && block * batch <= buf_bytes; block *= 2) {
         int iters = a.iters, warm = a.warmup;
-        const size_t per = block * a.batch;
+        const size_t per = block * batch;
         if (per > (size_t(64) << 20)) {
             iters = std::max<int>(10, static_cast<int>((size_t(64) << 30) / per / 16));
             warm = 3;
         }
+        if (storage) {
+            iters = std::min(iters, 200);
+            warm = std::min(warm, 5);
+        }
         std::vector<double> prep, post, xfer;
         std::vector<nixlXferReqH *> slots(a.depth, nullptr);
-        nixl_xfer_dlist_t l(mt), r(mt);
-        for (int i = 0; i < a.batch; ++i) {
-            l.addDesc(nixlBasicDesc(reinterpret_cast<uintptr_t>(src) + i * block, block, vram ? a.src_dev : 0));
-            r.addDesc(nixlBasicDesc(reinterpret_cast<uintptr_t>(dst) + i * block, block, vram ? a.dst_dev : 0));
+        nixl_xfer_dlist_t l(mt), r(rmt);
+        for (int i = 0; i < batch; ++i) {
+            const size_t off = static_cast<size_t>(i) * block;
+            l.addDesc(nixlBasicDesc(reinterpret_cast<uintptr_t>(src) + off, block, vram ? a.src_dev : 0));
+            if (storage) {
+                const size_t f = std::min<size_t>(off / file_bytes, fds.size() - 1);
+                size_t foff = off - f * file_bytes;
+                if (foff + block > file_bytes) foff = 0; // a block never straddles two files
+                r.addDesc(nixlBasicDesc(foff, block, static_cast<uint64_t>(fds[f])));
+            } else {
+                r.addDesc(nixlBasicDesc(reinterpret_cast<uintptr_t>(dst) + off, block, vram ? a.dst_dev : 0));
+            }
         }
-        for (auto &s : slots) {
+        nixlDlistH *side_l = nullptr, *side_r = nullptr;
+        std::vector<int> all_idx(batch);
+        for (int i = 0; i < batch; ++i) all_idx[i] = i;
+        if (a.prepared) {
             const auto t0 = clk::now();
-            if (ini.createXferReq(op, l, r, "target", s) != NIXL_SUCCESS) return 7;
+            if (ini.prepXferDlist(NIXL_INIT_AGENT, l, side_l) != NIXL_SUCCESS || ini.prepXferDlist(remote_name, r, side_r) != NIXL_SUCCESS) return 7;
             prep.push_back(us(t0, clk::now()));
         }
+        auto create = [&](nixlXferReqH *&h) {
+            const auto t0 = clk::now();
+            const nixl_status_t st = a.prepared ? ini.makeXferReq(op, side_l, all_idx, side_r, all_idx, h) : ini.createXferReq(op, l, r, remote_name, h);
+            prep.push_back(us(t0, clk::now()));
+            return st == NIXL_SUCCESS;
+        };
+        for (auto &s : slots)
+            if (!create(s)) return 7;
         std::vector<clk::time_point> started(a.depth);
         std::vector<bool> busy(a.depth, false);
-        clk::time_point t_begin;
+        clk::time_point t_begin = clk::now();
         int posted = 0, done = 0;
         const int total = warm + iters;
+        auto finished = [&](int s, clk::time_point now) {
+            busy[s] = false;
+            if (done >= warm) xfer.push_back(us(started[s], now));
+            ++done;
+            if (done == warm) t_begin = clk::now();
+            if (a.recreate && posted < total) {
+                ini.releaseXferReq(slots[s]);
+                slots[s] = nullptr;
+                if (!create(slots[s])) std::exit(7);
+            }
+        };
         while (done < total) {
             for (int s = 0; s < a.depth; ++s) {
                 if (busy[s]) {
                     const nixl_status_t st = ini.getXferStatus(slots[s]);
-                    if (st == NIXL_SUCCESS) {
-                        busy[s] = false;
-                        if (done >= warm) xfer.push_back(us(started[s], clk::now()));
-                        ++done;
-                        if (done == warm) t_begin = clk::now();
-                    } else if (st < 0) {
+                    if (st == NIXL_SUCCESS) finished(s, clk::now());
+                    else if (st < 0) {
                         std::fprintf(stderr, "transfer failed: %d\n", st);
                         return 8;
                     }
                 }
                 if (!busy[s] && posted < total) {
-                    if (posted == warm && warm == 0) t_begin = clk::now();
+                    if (a.reregister && a.depth == 1) {
+                        // Every iteration pays for taking the buffer out of the backend and putting it back.
+                        ini.releaseXferReq(slots[s]);
+                        slots[s] = nullptr;
+                        if (ini.deregisterMem(rs) != NIXL_SUCCESS || ini.registerMem(rs) != NIXL_SUCCESS) return 5;
+                        if (a.prepared) {
+                            ini.releasedDlistH(side_l);
+                            if (ini.prepXferDlist(NIXL_INIT_AGENT, l, side_l) != NIXL_SUCCESS) return 7;
+                        }
+                        if (!create(slots[s])) return 7;
+                    }
                     started[s] = clk::now();
                     const nixl_status_t st = ini.postXferReq(slots[s]);
                     const auto t1 = clk::now();
                     if (st < 0) return 9;
                     if (posted >= warm) post.push_back(us(started[s], t1));
                     ++posted;
-                    if (st == NIXL_SUCCESS) {
-                        if (done >= warm) xfer.push_back(us(started[s], t1));
-                        ++done;
-                        if (done == warm) t_begin = clk::now();
-                    } else busy[s] = true;
+                    if (st == NIXL_SUCCESS) finished(s, t1);
+                    else busy[s] = true;
                 }
             }
         }
@@ -176,18 +304,31 @@ int main(int argc, char **argv) {
         for (double v : post) psum += v;
         double prsum = 0;
         for (double v : prep) prsum += v;
-        std::printf("%-12zu %6d %10.2f %10.2f %10.2f %10.2f %10.2f %10.2f\n", block, a.batch, double(per) * iters / wall / 1e3,
-                    sum / std::max<size_t>(1, xfer.size()), pct(xfer, 0.5), pct(xfer, 0.99), prsum / prep.size(), psum / std::max<size_t>(1, post.size()));
+        std::printf("%-12zu %6d %10.2f %10.2f %10.2f %10.2f %10.2f %10.2f\n", block, batch, double(per) * iters / wall / 1e3,
+                    sum / std::max<size_t>(1, xfer.size()), pct(xfer, 0.5), pct(xfer, 0.99), prsum / std::max<size_t>(1, prep.size()),
+                    psum / std::max<size_t>(1, post.size()));
         std::fflush(stdout);
-        for (auto s : slots) ini.releaseXferReq(s);
+        for (auto s : slots)
+            if (s) ini.releaseXferReq(s);
+        if (side_l) ini.releasedDlistH(side_l);
+        if (side_r) ini.releasedDlistH(side_r);
         if (a.check) {
-            std::vector<unsigned char> h(std::min<size_t>(per, 1 << 20));
-            if (vram) {
+            // WRITE: the destination (memory or file) must hold the source pattern; READ from memory: the source side
+            // was overwritten with the target's zeros.
+            std::vector<unsigned char> h(std::min<size_t>(block, 1 << 20));
+            unsigned char want = 0x5a;
+            if (storage) {
+                if (op != NIXL_WRITE) continue; // a READ returns what an earlier WRITE stored: nothing fixed to compare with
+                if (::pread(fds[0], h.data(), h.size(), 0) != static_cast<ssize_t>(h.size())) return 10;
+            } else if (vram) {
                 cudaSetDevice(op == NIXL_WRITE ? a.dst_dev : a.src_dev);
                 cudaMemcpy(h.data(), op == NIXL_WRITE ? dst : src, h.size(), cudaMemcpyDeviceToHost);
                 cudaSetDevice(a.src_dev);
-            } else std::memcpy(h.data(), op == NIXL_WRITE ? dst : src, h.size());
-            const unsigned char want = op == NIXL_WRITE ? 0x5a : 0x00;
+                want = op == NIXL_WRITE ? 0x5a : 0x00;
+            } else {
+                std::memcpy(h.data(), op == NIXL_WRITE ? dst : src, h.size());
+                want = op == NIXL_WRITE ? 0x5a : 0x00;
+            }
             for (unsigned char c : h)
                 if (c != want) {
                     std::fprintf(stderr, "consistency check failed at block %zu\n", block);
@@ -195,5 +336,6 @@ int main(int argc, char **argv) {
                 }
         }
     }
+    for (int fd : fds) ::close(fd);
     return 0;
 }

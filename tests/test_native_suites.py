@@ -31,3 +31,35 @@ def test_native_nixlbench_dram_consistency():
                          env=ENV, capture_output=True, text=True, timeout=120)
     assert res.returncode == 0, res.stdout + res.stderr
     assert len(res.stdout.strip().splitlines()) >= 7
+
+
+def _nixlbench(*args):
+    exe = os.path.join(ROOT, "nixl_b200", "bin", "nixlbench")
+    return subprocess.run([exe, *args], env=ENV, capture_output=True, text=True, timeout=180)
+
+
+def test_native_nixlbench_request_modes():
+    """prepared lists, a fresh request per iteration, re-registration per iteration, batch sweep."""
+    res = _nixlbench("--mem", "DRAM", "--min", "65536", "--max", "131072", "--iters", "30", "--warmup", "3", "--prepared", "--recreate",
+                     "--batch", "2", "--batch-max", "4", "--check")
+    assert res.returncode == 0, res.stdout + res.stderr
+    rows = [ln.split() for ln in res.stdout.strip().splitlines()[1:]]
+    assert [(r[0], r[1]) for r in rows] == [("65536", "2"), ("131072", "2"), ("65536", "4"), ("131072", "4")]
+    res = _nixlbench("--mem", "DRAM", "--min", "1048576", "--max", "1048576", "--iters", "10", "--warmup", "1", "--reregister", "--check")
+    assert res.returncode == 0, res.stdout + res.stderr
+
+
+def test_native_nixlbench_storage_and_config_file(tmp_path):
+    store = str(tmp_path / "blocks.bin")
+    res = _nixlbench("--mem", "DRAM", "--file", store, "--num-files", "2", "--op", "WRITE", "--min", "262144", "--max", "524288", "--batch", "4",
+                     "--iters", "8", "--check")
+    assert res.returncode == 0, res.stdout + res.stderr
+    assert os.path.getsize(store + ".0") > 0 and os.path.getsize(store + ".1") > 0
+    res = _nixlbench("--mem", "DRAM", "--file", store, "--num-files", "2", "--op", "READ", "--min", "262144", "--max", "524288", "--batch", "4", "--iters", "8")
+    assert res.returncode == 0, res.stdout + res.stderr
+    cfg = tmp_path / "bench.cfg"
+    cfg.write_text("# options as in the command line, without the dashes\nmem=DRAM\nmin=65536\nmax=65536\niters=10\nwarmup=1\nbatch=2\ncheck=true\n")
+    res = _nixlbench("--config", str(cfg))
+    assert res.returncode == 0 and len(res.stdout.strip().splitlines()) == 2, res.stdout + res.stderr
+    cfg.write_text("no_such_option=1\n")
+    assert _nixlbench("--config", str(cfg)).returncode == 2
