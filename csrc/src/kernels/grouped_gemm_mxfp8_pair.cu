@@ -131,34 +131,36 @@ __device__ __forceinline__ uint32_t instrDescMx(uint32_t sf) {
 // MMAs: its latency then runs while the second group is being issued, and its result is read last.
 __device__ __forceinline__ void issueKStepMx(uint32_t tmem_d0, uint32_t tmem_d1, uint64_t da, uint64_t dw0, uint64_t dw1, uint32_t idesc, uint32_t tsfa,
                                              uint32_t tsfb0, uint32_t tsfb1, uint32_t accumulate, uint32_t bar_stage_empty, uint32_t peek_bar,
-                                             uint32_t peek_par, uint32_t &ready_next) {
+                                             uint32_t peek_par, uint32_t &ready_next, uint32_t peek2_bar, uint32_t peek2_par, uint32_t &ready2) {
     uint64_t da2 = da;
     asm volatile(
         "{\n"
-        " .reg .pred pf, pacc, pfirst;\n"
-        " setp.ne.b32 pacc, %15, 0;\n"
-        " setp.ne.b32 pfirst, %11, 0;\n"
-        " tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%1], %3, %4, %7, [%8], [%9], pfirst;\n"
-        " add.u64 %3, %3, 2;\n add.u64 %4, %4, 2;\n"
-        " tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%1], %3, %4, %7, [%8], [%9], pacc;\n"
-        " add.u64 %3, %3, 2;\n add.u64 %4, %4, 2;\n"
-        " tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%1], %3, %4, %7, [%8], [%9], pacc;\n"
-        " add.u64 %3, %3, 2;\n add.u64 %4, %4, 2;\n"
-        " tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%1], %3, %4, %7, [%8], [%9], pacc;\n"
-        " mbarrier.test_wait.parity.shared::cta.b64 pf, [%13], %14;\n"
-        " tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%2], %6, %5, %7, [%8], [%10], pfirst;\n"
-        " add.u64 %6, %6, 2;\n add.u64 %5, %5, 2;\n"
-        " tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%2], %6, %5, %7, [%8], [%10], pacc;\n"
-        " add.u64 %6, %6, 2;\n add.u64 %5, %5, 2;\n"
-        " tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%2], %6, %5, %7, [%8], [%10], pacc;\n"
-        " add.u64 %6, %6, 2;\n add.u64 %5, %5, 2;\n"
-        " tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%2], %6, %5, %7, [%8], [%10], pacc;\n"
-        " tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%12], %16;\n"
+        " .reg .pred pf, pf2, pacc, pfirst;\n"
+        " setp.ne.b32 pacc, %16, 0;\n"
+        " setp.ne.b32 pfirst, %12, 0;\n"
+        " tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%2], %4, %5, %8, [%9], [%10], pfirst;\n"
+        " add.u64 %4, %4, 2;\n add.u64 %5, %5, 2;\n"
+        " tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%2], %4, %5, %8, [%9], [%10], pacc;\n"
+        " add.u64 %4, %4, 2;\n add.u64 %5, %5, 2;\n"
+        " tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%2], %4, %5, %8, [%9], [%10], pacc;\n"
+        " add.u64 %4, %4, 2;\n add.u64 %5, %5, 2;\n"
+        " tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%2], %4, %5, %8, [%9], [%10], pacc;\n"
+        " mbarrier.test_wait.parity.shared::cta.b64 pf, [%14], %15;\n"
+        " tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%3], %7, %6, %8, [%9], [%11], pfirst;\n"
+        " add.u64 %7, %7, 2;\n add.u64 %6, %6, 2;\n"
+        " tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%3], %7, %6, %8, [%9], [%11], pacc;\n"
+        " mbarrier.test_wait.parity.shared::cta.b64 pf2, [%18], %19;\n"
+        " add.u64 %7, %7, 2;\n add.u64 %6, %6, 2;\n"
+        " tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%3], %7, %6, %8, [%9], [%11], pacc;\n"
+        " add.u64 %7, %7, 2;\n add.u64 %6, %6, 2;\n"
+        " tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%3], %7, %6, %8, [%9], [%11], pacc;\n"
+        " tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%13], %17;\n"
         " selp.u32 %0, 1, 0, pf;\n"
+        " selp.u32 %1, 1, 0, pf2;\n"
         "}\n"
-        : "=r"(ready_next), "+r"(tmem_d0), "+r"(tmem_d1), "+l"(da), "+l"(dw0), "+l"(dw1), "+l"(da2)
+        : "=r"(ready_next), "=r"(ready2), "+r"(tmem_d0), "+r"(tmem_d1), "+l"(da), "+l"(dw0), "+l"(dw1), "+l"(da2)
         : "r"(idesc), "r"(tsfa), "r"(tsfb0), "r"(tsfb1), "r"(accumulate), "r"(bar_stage_empty), "r"(peek_bar), "r"(peek_par), "r"(1u),
-          "h"(static_cast<uint16_t>(3))
+          "h"(static_cast<uint16_t>(3)), "r"(peek2_bar), "r"(peek2_par)
         : "memory");
 }
 
@@ -258,38 +260,42 @@ groupedGemmMxPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_c
         const uint32_t full_bar0 = smemU32(&sh.full[0]), empty_bar0 = smemU32(&sh.empty[0]), sfempty_bar0 = smemU32(&sh.sfEmpty[0]);
         const uint64_t desc0 = smemDesc(smemU32(tiles));
         const uint32_t sf_smem0 = smemU32(sf_ring);
+        const uint32_t sffull_bar0 = smemU32(&sh.sfFull[0]);
+        uint32_t sf_ready = 0;
         for (int tile = 0; tile < my_tiles; ++tile) {
             // The single accumulator must have been drained by the previous tile's epilogue.
             if (!mbarWait(&sh.tmemEmpty, (static_cast<uint32_t>(tile) & 1u) ^ 1u, abort_flag)) goto issuer_done;
-            for (int ks = 0; ks < k_steps; ++ks) {
-                const uint32_t sub = static_cast<uint32_t>(ks) & (kChunkSteps - 1);
-                if (sub == 0) {
-                    const uint32_t b = cc % kSfRing;
-                    if (!mbarWait(&sh.sfFull[b], (cc / kSfRing) & 1u, abort_flag)) goto issuer_done;
-                    tcFenceAfter();
-                    const uint32_t src = sf_smem0 + b * kSfBufBytes;
-                    const uint32_t dst = tmem + kAccCols + (cc & 1u) * kSfTmemStride;
-                    tmemCpPair(dst, sfDesc(src));
-                    tmemCpPair(dst + 4, sfDesc(src + kSfAtomBytes));
-                    tmemCpPair(dst + 8, sfDesc(src + 2 * kSfAtomBytes));
-                    tcCommitPair(sfempty_bar0 + b * 8u); // the buffer may be refilled once the copies have read it
-                }
-                if (!ready && !mbarWait(&sh.full[s], full_par, abort_flag)) goto issuer_done;
+            for (int c = 0; c < chunks; ++c, ++cc) {
+                const uint32_t b = cc % kSfRing;
+                if (!sf_ready && !mbarWait(&sh.sfFull[b], (cc / kSfRing) & 1u, abort_flag)) goto issuer_done;
                 tcFenceAfter();
-                uint32_t ns = s + 1, nfull_par = full_par;
-                if (ns == kStages) {
-                    ns = 0;
-                    nfull_par ^= 1u;
-                }
-                const uint64_t da = desc0 + static_cast<uint64_t>((s * kStageBytes) >> 4);
-                const uint64_t dw0 = da + static_cast<uint64_t>(kATileBytes >> 4);
-                const uint64_t dw1 = da + static_cast<uint64_t>((kATileBytes + kWBoxBytes) >> 4);
+                const uint32_t src = sf_smem0 + b * kSfBufBytes;
                 const uint32_t sfc = tmem + kAccCols + (cc & 1u) * kSfTmemStride;
-                issueKStepMx(tmem, tmem + BNS, da, dw0, dw1, instrDescMx(sub), sfc, sfc + 4, sfc + 8, ks > 0 ? 1u : 0u, empty_bar0 + s * 8u,
-                             full_bar0 + ns * 8u, nfull_par, ready);
-                if (sub == kChunkSteps - 1) ++cc;
-                s = ns;
-                full_par = nfull_par;
+                tmemCpPair(sfc, sfDesc(src));
+                tmemCpPair(sfc + 4, sfDesc(src + kSfAtomBytes));
+                tmemCpPair(sfc + 8, sfDesc(src + 2 * kSfAtomBytes));
+                tcCommitPair(sfempty_bar0 + b * 8u); // the buffer may be refilled once the copies have read it
+                // The next chunk's scale barrier is tested from inside the second step's MMA sequence.
+                const uint32_t nb = (cc + 1) % kSfRing, nb_par = ((cc + 1) / kSfRing) & 1u;
+#pragma unroll
+                for (uint32_t sub = 0; sub < kChunkSteps; ++sub) {
+                    if (!ready && !mbarWait(&sh.full[s], full_par, abort_flag)) goto issuer_done;
+                    tcFenceAfter();
+                    uint32_t ns = s + 1, nfull_par = full_par;
+                    if (ns == kStages) {
+                        ns = 0;
+                        nfull_par ^= 1u;
+                    }
+                    const uint64_t da = desc0 + static_cast<uint64_t>((s * kStageBytes) >> 4);
+                    const uint64_t dw0 = da + static_cast<uint64_t>(kATileBytes >> 4);
+                    const uint64_t dw1 = da + static_cast<uint64_t>((kATileBytes + kWBoxBytes) >> 4);
+                    uint32_t peek2 = 0;
+                    issueKStepMx(tmem, tmem + BNS, da, dw0, dw1, instrDescMx(sub), sfc, sfc + 4, sfc + 8, (c | static_cast<int>(sub)) ? 1u : 0u,
+                                 empty_bar0 + s * 8u, full_bar0 + ns * 8u, nfull_par, ready, sffull_bar0 + nb * 8u, nb_par, peek2);
+                    if (sub == 1) sf_ready = peek2;
+                    s = ns;
+                    full_par = nfull_par;
+                }
             }
             tcCommitPair(smemU32(&sh.tmemFull));
         }
