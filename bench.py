@@ -287,7 +287,7 @@ def main():
             "verified": ok,
             "wall_ms_per_step": round(wall * 1e3 / args.steps, 4),
             "config": {
-                "model": "nixlbench-style VRAM sweep point (BASELINE config b)",
+                "model": "nixlbench-style VRAM sweep point (VRAM to VRAM WRITE, 16 x 64 MiB per request)",
                 "block_bytes": block,
                 "batch_descs": batch,
                 "global_batch": world * batch,

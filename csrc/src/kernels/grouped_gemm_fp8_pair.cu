@@ -393,19 +393,14 @@ groupedGemmPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_con
                 }
             }
             if (!ok) break;
-            if (valid) {
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    __nv_bfloat16 *out = static_cast<__nv_bfloat16 *>(p.d) + grow * p.N + t.nt * BN + h * BNS + part * 64;
-#pragma unroll
-                    for (int e = 0; e < 64; e += 8) {
-                        uint4 o;
-                        __nv_bfloat162 *hh = reinterpret_cast<__nv_bfloat162 *>(&o);
-#pragma unroll
-                        for (int x = 0; x < 4; ++x) hh[x] = __floats2bfloat162_rn(acc[h * 64 + e + 2 * x], acc[h * 64 + e + 2 * x + 1]);
-                        *reinterpret_cast<uint4 *>(out + e) = o;
-                    }
-                }
+            {
+                // Coalesced stores: see storeRows64.  acc[h * 64 ..] are this row's 64 columns of half h.
+                const int first_row = t.mt * (2 * BM) + static_cast<int>(cta) * BM + q * 32 + (lane & ~7);
+                const long long first_grow = static_cast<long long>(sh.rowStart[t.g]) + first_row;
+                const int rows_left = sh.rowCount[t.g] - first_row;
+                __nv_bfloat16 *out = static_cast<__nv_bfloat16 *>(p.d) + first_grow * p.N + t.nt * BN + part * 64 + (lane & 7) * 8;
+                storeRows64(reinterpret_cast<const float(&)[32]>(acc[0]), reinterpret_cast<const float(&)[32]>(acc[32]), out, p.N, rows_left, lane);
+                storeRows64(reinterpret_cast<const float(&)[32]>(acc[64]), reinterpret_cast<const float(&)[32]>(acc[96]), out + BNS, p.N, rows_left, lane);
             }
         }
     }

@@ -66,6 +66,7 @@ struct Shared {
     uint64_t tmemEmpty;          // even CTA: all 16 epilogue warps have read the accumulator
     uint32_t tmemBase;
     int abort;
+    volatile uint32_t chunksIssued; // two issuing threads take turns chunk by chunk: the next chunk whose MMAs may enter the pipe
     int tilePrefix[kMaxGroups + 1];
     int rowStart[kMaxGroups];
     int rowCount[kMaxGroups];
@@ -203,9 +204,10 @@ groupedGemmMxPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_c
             mbarInit(&sh.sfFull[b], 2 * kPromoWarps);
             mbarInit(&sh.sfEmpty[b], 1);
         }
-        mbarInit(&sh.tmemFull, 1);
+        mbarInit(&sh.tmemFull, 2); // one commit from each issuing thread
         mbarInit(&sh.tmemEmpty, 2 * kPromoWarps);
         sh.abort = 0;
+        sh.chunksIssued = 0;
         int run = 0;
         for (int g = 0; g < p.groups; ++g) {
             const int c = p.row_count[g];
@@ -253,51 +255,73 @@ groupedGemmMxPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_c
             }
         }
     producer_done:;
-    } else if (warp == 1 && lane == 0 && cta == 0) {
-        // ---------------------------------------------------------------- MMA issuer (even CTA)
-        uint32_t s = 0, full_par = 0, ready = 0;
-        uint32_t cc = 0; // chunk counter over all tiles: ring buffer cc % kSfRing, TMEM scale columns by cc & 1
+    } else if ((warp == 1 || warp == 3) && lane == 0 && cta == 0) {
+        // ---------------------------------------------------------------- two MMA issuers (even CTA)
+        // The tensor pipe idles whenever its issuing thread does anything but issue (an MMA's issue
+        // returns about when its predecessor starts).  Two threads therefore alternate chunk by chunk
+        // (four steps, 32 MMAs): while one is parked in the issue of its chunk, the other waits for its
+        // next chunk's barriers and sits ready.  A turn counter keeps the chunks entering the pipe in
+        // order (the first step of a tile overwrites the accumulator, and a chunk's scale copy must
+        // precede its MMAs); even chunks use TMEM scale columns of parity 0, odd chunks parity 1.
+        const uint32_t me = warp == 1 ? 0u : 1u;
         const uint32_t full_bar0 = smemU32(&sh.full[0]), empty_bar0 = smemU32(&sh.empty[0]), sfempty_bar0 = smemU32(&sh.sfEmpty[0]);
         const uint64_t desc0 = smemDesc(smemU32(tiles));
         const uint32_t sf_smem0 = smemU32(sf_ring);
-        const uint32_t sffull_bar0 = smemU32(&sh.sfFull[0]);
-        uint32_t sf_ready = 0;
-        for (int tile = 0; tile < my_tiles; ++tile) {
-            // The single accumulator must have been drained by the previous tile's epilogue.
-            if (!mbarWait(&sh.tmemEmpty, (static_cast<uint32_t>(tile) & 1u) ^ 1u, abort_flag)) goto issuer_done;
-            for (int c = 0; c < chunks; ++c, ++cc) {
-                const uint32_t b = cc % kSfRing;
-                if (!sf_ready && !mbarWait(&sh.sfFull[b], (cc / kSfRing) & 1u, abort_flag)) goto issuer_done;
-                tcFenceAfter();
-                const uint32_t src = sf_smem0 + b * kSfBufBytes;
-                const uint32_t sfc = tmem + kAccCols + (cc & 1u) * kSfTmemStride;
-                tmemCpPair(sfc, sfDesc(src));
-                tmemCpPair(sfc + 4, sfDesc(src + kSfAtomBytes));
-                tmemCpPair(sfc + 8, sfDesc(src + 2 * kSfAtomBytes));
-                tcCommitPair(sfempty_bar0 + b * 8u); // the buffer may be refilled once the copies have read it
-                // The next chunk's scale barrier is tested from inside the second step's MMA sequence.
-                const uint32_t nb = (cc + 1) % kSfRing, nb_par = ((cc + 1) / kSfRing) & 1u;
-#pragma unroll
-                for (uint32_t sub = 0; sub < kChunkSteps; ++sub) {
-                    if (!ready && !mbarWait(&sh.full[s], full_par, abort_flag)) goto issuer_done;
-                    tcFenceAfter();
-                    uint32_t ns = s + 1, nfull_par = full_par;
-                    if (ns == kStages) {
-                        ns = 0;
-                        nfull_par ^= 1u;
+        const uint32_t total_chunks = static_cast<uint32_t>(my_tiles) * static_cast<uint32_t>(chunks);
+        for (uint32_t cc = me; cc < total_chunks; cc += 2) {
+            const uint32_t tile = cc / static_cast<uint32_t>(chunks), c = cc - tile * static_cast<uint32_t>(chunks);
+            const uint32_t it0 = cc * kChunkSteps;
+            uint32_t s = it0 % kStages, full_par = (it0 / kStages) & 1u;
+            const uint32_t b = cc % kSfRing;
+            // Everything this chunk depends on, before asking for the turn.
+            if (c == 0 && !mbarWait(&sh.tmemEmpty, (tile & 1u) ^ 1u, abort_flag)) goto issuer_done; // accumulator drained by the previous epilogue
+            if (!mbarWait(&sh.sfFull[b], (cc / kSfRing) & 1u, abort_flag)) goto issuer_done;
+            if (!mbarWait(&sh.full[s], full_par, abort_flag)) goto issuer_done;
+            {
+                const long long t0 = clock64();
+                while (sh.chunksIssued != cc) {
+                    if (*abort_flag) goto issuer_done;
+                    if (clock64() - t0 > (1ll << 33)) {
+                        *abort_flag = 1;
+                        goto issuer_done;
                     }
-                    const uint64_t da = desc0 + static_cast<uint64_t>((s * kStageBytes) >> 4);
-                    const uint64_t dw0 = da + static_cast<uint64_t>(kATileBytes >> 4);
-                    const uint64_t dw1 = da + static_cast<uint64_t>((kATileBytes + kWBoxBytes) >> 4);
-                    uint32_t peek2 = 0;
-                    issueKStepMx(tmem, tmem + BNS, da, dw0, dw1, instrDescMx(sub), sfc, sfc + 4, sfc + 8, (c | static_cast<int>(sub)) ? 1u : 0u,
-                                 empty_bar0 + s * 8u, full_bar0 + ns * 8u, nfull_par, ready, sffull_bar0 + nb * 8u, nb_par, peek2);
-                    if (sub == 1) sf_ready = peek2;
-                    s = ns;
-                    full_par = nfull_par;
                 }
             }
-            tcCommitPair(smemU32(&sh.tmemFull));
+            tcFenceAfter();
+            const uint32_t src = sf_smem0 + b * kSfBufBytes;
+            const uint32_t sfc = tmem + kAccCols + (cc & 1u) * kSfTmemStride;
+            tmemCpPair(sfc, sfDesc(src));
+            tmemCpPair(sfc + 4, sfDesc(src + kSfAtomBytes));
+            tmemCpPair(sfc + 8, sfDesc(src + 2 * kSfAtomBytes));
+            tcCommitPair(sfempty_bar0 + b * 8u); // the buffer may be refilled once the copies have read it
+            uint32_t ready = 1; // the first step's barrier was waited for above
+#pragma unroll
+            for (uint32_t sub = 0; sub < kChunkSteps; ++sub) {
+                if (!ready && !mbarWait(&sh.full[s], full_par, abort_flag)) goto issuer_done;
+                tcFenceAfter();
+                uint32_t ns = s + 1, nfull_par = full_par;
+                if (ns == kStages) {
+                    ns = 0;
+                    nfull_par ^= 1u;
+                }
+                const uint64_t da = desc0 + static_cast<uint64_t>((s * kStageBytes) >> 4);
+                const uint64_t dw0 = da + static_cast<uint64_t>(kATileBytes >> 4);
+                const uint64_t dw1 = da + static_cast<uint64_t>((kATileBytes + kWBoxBytes) >> 4);
+                uint32_t unused = 0;
+                issueKStepMx(tmem, tmem + BNS, da, dw0, dw1, instrDescMx(sub), sfc, sfc + 4, sfc + 8, (c | sub) ? 1u : 0u, empty_bar0 + s * 8u,
+                             full_bar0 + ns * 8u, nfull_par, ready, full_bar0 + ns * 8u, nfull_par, unused);
+                s = ns;
+                full_par = nfull_par;
+            }
+            // All of this chunk's MMAs are in the pipe: the other thread's chunk may follow.
+            asm volatile("" ::: "memory");
+            sh.chunksIssued = cc + 1;
+            if (c + 1 == static_cast<uint32_t>(chunks) || c + 2 == static_cast<uint32_t>(chunks)) {
+                // This thread's last chunk of the tile: its share of "accumulator complete" (both shares when
+                // the tile has a single chunk and the other thread never touches it).
+                tcCommitPair(smemU32(&sh.tmemFull));
+                if (chunks == 1) tcCommitPair(smemU32(&sh.tmemFull));
+            }
         }
     issuer_done:;
     } else if (warp >= 4) {
@@ -311,72 +335,85 @@ groupedGemmMxPairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_c
         const uint32_t *sa32 = reinterpret_cast<const uint32_t *>(p.scale_a);
         const uint32_t *sw32 = reinterpret_cast<const uint32_t *>(p.scale_w);
         const int n_blocks = p.N / 128;
-        uint32_t cc = 0;
-        Tile t;
-        int tile = 0;
-        for (int ti = pair; tileAt(sh, p.groups, n_tiles, ti, t); ti += pairs, ++tile) {
-            const int local_row = t.mt * (2 * BM) + static_cast<int>(cta) * BM + row_in_tile;
-            const bool valid = local_row < sh.rowCount[t.g];
-            const long long grow = static_cast<long long>(sh.rowStart[t.g]) + local_row;
-            bool ok = true;
-            for (int c = 0; c < chunks; ++c, ++cc) {
-                const uint32_t b = cc % kSfRing;
-                if (!mbarWait(&sh.sfEmpty[b], ((cc / kSfRing) & 1u) ^ 1u, abort_flag)) {
-                    ok = false;
-                    break;
-                }
-                uint32_t *buf = reinterpret_cast<uint32_t *>(sf_ring + b * kSfBufBytes);
-                if (part == 0) {
-                    // Row r of this CTA's half: word (r % 32) * 4 + r / 32 (rows beyond the expert get exponent 127 = 1.0).
-                    const uint32_t w = valid ? __ldg(sa32 + grow * chunks + c) : 0x7f7f7f7fu;
-                    buf[lane * 4 + q] = w;
-                } else {
-                    const uint32_t wl = __ldg(sw32 + (static_cast<long long>(t.g) * n_blocks + t.nt * 2) * chunks + c);
-                    const uint32_t wr = __ldg(sw32 + (static_cast<long long>(t.g) * n_blocks + t.nt * 2 + 1) * chunks + c);
-                    buf[128 + row_in_tile] = wl;
-                    buf[256 + row_in_tile] = wr;
-                }
-                asm volatile("fence.proxy.async;" ::: "memory"); // these generic-proxy writes are read by tcgen05.cp
-                __syncwarp();
-                if (lane == 0) mbarArriveClusterRelease(sffull0 + b * 8u);
+        // Rows and scale words of a tile, as this thread sees them.
+        struct TileView {
+            Tile t;
+            bool valid;
+            long long grow;
+        };
+        auto view = [&](int ti, TileView &v) -> bool {
+            if (!tileAt(sh, p.groups, n_tiles, ti, v.t)) return false;
+            const int local_row = v.t.mt * (2 * BM) + static_cast<int>(cta) * BM + row_in_tile;
+            v.valid = local_row < sh.rowCount[v.t.g];
+            v.grow = static_cast<long long>(sh.rowStart[v.t.g]) + local_row;
+            return true;
+        };
+        // Builds chunk c of a tile in ring buffer gcc % kSfRing once the issuer has copied that buffer's previous content out.
+        auto stage = [&](const TileView &v, int c, uint32_t gcc) -> bool {
+            const uint32_t b = gcc % kSfRing;
+            if (!mbarWait(&sh.sfEmpty[b], ((gcc / kSfRing) & 1u) ^ 1u, abort_flag)) return false;
+            uint32_t *buf = reinterpret_cast<uint32_t *>(sf_ring + b * kSfBufBytes);
+            if (part == 0) {
+                // Row r of this CTA's half: word (r % 32) * 4 + r / 32 (rows beyond the expert get exponent 127 = 1.0).
+                buf[lane * 4 + q] = v.valid ? __ldg(sa32 + v.grow * chunks + c) : 0x7f7f7f7fu;
+            } else {
+                const long long blk = (static_cast<long long>(v.t.g) * n_blocks + v.t.nt * 2) * chunks + c;
+                buf[128 + row_in_tile] = __ldg(sw32 + blk);
+                buf[256 + row_in_tile] = __ldg(sw32 + blk + chunks);
             }
+            asm volatile("fence.proxy.async;" ::: "memory"); // these generic-proxy writes are read by tcgen05.cp
+            __syncwarp();
+            if (lane == 0) mbarArriveClusterRelease(sffull0 + b * 8u);
+            return true;
+        };
+        // Staging runs ahead of the issuer by up to the ring's depth, across tile boundaries: the first
+        // chunks of the next tile are built before this tile's epilogue, so the issuer finds them
+        // waiting when the accumulator is free again.
+        const int ahead = chunks < kSfRing ? chunks : kSfRing;
+        TileView cur, nxt;
+        int ti = pair;
+        bool have = view(ti, cur);
+        uint32_t cc_base = 0;
+        bool ok = true;
+        if (have)
+            for (int c = 0; c < ahead && ok; ++c) ok = stage(cur, c, cc_base + c);
+        for (int tile = 0; have && ok; ++tile) {
+            for (int c = ahead; c < chunks && ok; ++c) ok = stage(cur, c, cc_base + c);
+            const bool have_next = view(ti + pairs, nxt);
+            if (have_next)
+                for (int c = 0; c < ahead && ok; ++c) ok = stage(nxt, c, cc_base + chunks + c);
             if (!ok) break;
+            const Tile &t = cur.t;
             // Epilogue: the tile's accumulator, two halves of 128 columns, this warp's 64 columns of each.
+            // All four TMEM loads first, then the accumulator goes back to the issuer at once; conversion
+            // and stores follow while the next tile's main loop is already running.
             if (!mbarWait(&sh.tmemFull, static_cast<uint32_t>(tile) & 1u, abort_flag)) break;
             tcFenceAfter();
-            __nv_bfloat16 *out = static_cast<__nv_bfloat16 *>(p.d) + grow * p.N + t.nt * BN + part * 64;
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                float v0[32], v1[32];
-                tmemLoad32(lane_base + h * BNS, v0);
-                tmemLoad32(lane_base + h * BNS + 32, v1);
-                tmemLoadWait(v0);
-                tmemLoadWait(v1);
-                if (h == 1) {
-                    // Everything this warp needs is in registers: the next tile may overwrite the accumulator.
-                    tcFenceBefore();
-                    __syncwarp();
-                    if (lane == 0) mbarArriveCluster(tempty);
-                }
-                if (valid) {
-#pragma unroll
-                    for (int e = 0; e < 32; e += 8) {
-                        uint4 o;
-                        __nv_bfloat162 *hh = reinterpret_cast<__nv_bfloat162 *>(&o);
-#pragma unroll
-                        for (int x = 0; x < 4; ++x) hh[x] = __floats2bfloat162_rn(v0[e + 2 * x], v0[e + 2 * x + 1]);
-                        *reinterpret_cast<uint4 *>(out + h * BNS + e) = o;
-                    }
-#pragma unroll
-                    for (int e = 0; e < 32; e += 8) {
-                        uint4 o;
-                        __nv_bfloat162 *hh = reinterpret_cast<__nv_bfloat162 *>(&o);
-#pragma unroll
-                        for (int x = 0; x < 4; ++x) hh[x] = __floats2bfloat162_rn(v1[e + 2 * x], v1[e + 2 * x + 1]);
-                        *reinterpret_cast<uint4 *>(out + h * BNS + 32 + e) = o;
-                    }
-                }
-            }
+            float v0[32], v1[32], v2[32], v3[32];
+            tmemLoad32(lane_base, v0);
+            tmemLoad32(lane_base + 32, v1);
+            tmemLoad32(lane_base + BNS, v2);
+            tmemLoad32(lane_base + BNS + 32, v3);
+            tmemLoadWait(v0);
+            tmemLoadWait(v1);
+            tmemLoadWait(v2);
+            tmemLoadWait(v3);
+            tcFenceBefore();
+            __syncwarp();
+            if (lane == 0) mbarArriveCluster(tempty);
+            // A thread holds 64 consecutive columns of its own row: eight 16-byte pieces per half.  Eight
+            // lanes exchange pieces (8 x 8 transpose by three butterfly steps) so that every store
+            // instruction writes whole 128-byte runs: lane 8g + c then holds piece c of rows 8g .. 8g + 7.
+            const int first_row = t.mt * (2 * BM) + static_cast<int>(cta) * BM + q * 32 + (lane & ~7); // tile-local row of this lane group
+            const long long first_grow = static_cast<long long>(sh.rowStart[t.g]) + first_row;
+            const int rows_left = sh.rowCount[t.g] - first_row; // rows of the group that belong to the expert
+            __nv_bfloat16 *out = static_cast<__nv_bfloat16 *>(p.d) + first_grow * p.N + t.nt * BN + part * 64 + (lane & 7) * 8;
+            storeRows64(v0, v1, out, p.N, rows_left, lane);
+            storeRows64(v2, v3, out + BNS, p.N, rows_left, lane);
+            cur = nxt;
+            have = have_next;
+            ti += pairs;
+            cc_base += static_cast<uint32_t>(chunks);
         }
     }
 

@@ -4,6 +4,7 @@
 #define NIXL_B200_TCGEN05_PTX_CUH
 
 #include <cuda.h>
+#include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
 #include <cstdint>
@@ -122,6 +123,43 @@ __device__ __forceinline__ uint64_t ldAcquireSys(const uint64_t *p) {
     uint64_t v;
     asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
     return v;
+}
+
+// Epilogue store of a 32-row x 64-column bf16 block held one row per lane (64 fp32 per thread).
+// Written row by row, every store instruction would touch 32 different 128-byte lines with 16
+// bytes each.  Instead eight lanes exchange their 16-byte pieces (an 8 x 8 transpose in three
+// butterfly steps), after which lane 8g + c holds piece c of rows 8g .. 8g + 7 and each
+// instruction writes whole 128-byte runs.  `out` points at this lane group's first row, already
+// advanced by (lane & 7) * 8 columns; rows_left counts the group's rows that may be written.
+__device__ __forceinline__ void storeRows64(const float (&lo)[32], const float (&hi)[32], __nv_bfloat16 *out, long long row_stride, int rows_left,
+                                            int lane) {
+    uint4 piece[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const float *src = i < 4 ? lo + 8 * i : hi + 8 * (i - 4);
+        __nv_bfloat162 *hh = reinterpret_cast<__nv_bfloat162 *>(&piece[i]);
+#pragma unroll
+        for (int x = 0; x < 4; ++x) hh[x] = __floats2bfloat162_rn(src[2 * x], src[2 * x + 1]);
+    }
+#pragma unroll
+    for (int m = 1; m < 8; m <<= 1) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            if (i & m) continue;
+            const int j = i | m;
+            const bool upper = (lane & m) != 0;
+            const uint4 send = upper ? piece[i] : piece[j];
+            uint4 recv;
+            recv.x = __shfl_xor_sync(0xffffffffu, send.x, m);
+            recv.y = __shfl_xor_sync(0xffffffffu, send.y, m);
+            recv.z = __shfl_xor_sync(0xffffffffu, send.z, m);
+            recv.w = __shfl_xor_sync(0xffffffffu, send.w, m);
+            if (upper) piece[i] = recv; else piece[j] = recv;
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+        if (i < rows_left) *reinterpret_cast<uint4 *>(out + static_cast<long long>(i) * row_stride) = piece[i];
 }
 
 } // namespace nixl_tc
