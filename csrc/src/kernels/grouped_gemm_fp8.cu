@@ -341,16 +341,13 @@ groupedGemmKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
                 }
             }
             if (!ok) break;
-            if (valid) {
-                __nv_bfloat16 *out = static_cast<__nv_bfloat16 *>(p.d) + grow * p.N + t.nt * BN + half * HN;
-#pragma unroll
-                for (int i = 0; i < HN; i += 8) {
-                    uint4 o;
-                    __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&o);
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(acc[i + 2 * j], acc[i + 2 * j + 1]);
-                    *reinterpret_cast<uint4 *>(out + i) = o;
-                }
+            {
+                // Coalesced stores (see storeRows64): this thread's 64 columns of its row.
+                const int first_row = t.mt * BM + q * 32 + (lane & ~7);
+                const long long first_grow = static_cast<long long>(sh.rowStart[t.g]) + first_row;
+                const int rows_left = sh.rowCount[t.g] - first_row;
+                __nv_bfloat16 *out = static_cast<__nv_bfloat16 *>(p.d) + first_grow * p.N + t.nt * BN + half * HN + (lane & 7) * 8;
+                storeRows64(reinterpret_cast<const float(&)[32]>(acc[0]), reinterpret_cast<const float(&)[32]>(acc[32]), out, p.N, rows_left, lane);
             }
         }
     }
