@@ -1,7 +1,7 @@
 // PROMETHEUS_MP telemetry exporter: one scrape endpoint for many processes of a node.
 //
 // Every exporter (one per agent, any number per process) keeps its metrics in a small file of its
-// own, mapped shared, under NIXL_TELEMETRY_PROMETHEUS_MP_DIR (default /tmp/nixl_prometheus_mp).
+// own, mapped shared, under NIXL_TELEMETRY_MULTIPROC_DIR (default /tmp/nixl_prometheus_mp).
 // Whoever holds the advisory lock on <dir>/owner.lock serves http://<addr>:<port>/metrics and
 // renders all files it finds there; the others keep trying for the lock once a second, so the
 // endpoint survives the death of its owner.  Files of processes that no longer exist are removed
@@ -83,7 +83,9 @@ void renderOne(std::ostringstream &o, const Store &s) {
 class PrometheusMpExporter final : public nixlTelemetryExporter {
 public:
     explicit PrometheusMpExporter(const nixlTelemetryExporterInitParams &p) : nixlTelemetryExporter(p) {
-        dir_ = nixl::config::getValueDefaulted<std::string>("NIXL_TELEMETRY_PROMETHEUS_MP_DIR", "/tmp/nixl_prometheus_mp");
+        // NIXL_TELEMETRY_MULTIPROC_DIR is the reference's name for the directory; the longer name is accepted too.
+        dir_ = nixl::config::getValueDefaulted<std::string>(
+            "NIXL_TELEMETRY_MULTIPROC_DIR", nixl::config::getValueDefaulted<std::string>("NIXL_TELEMETRY_PROMETHEUS_MP_DIR", "/tmp/nixl_prometheus_mp"));
         port_ = nixl::config::getValueDefaulted<int>("NIXL_TELEMETRY_PROMETHEUS_PORT", 9090);
         local_ = nixl::config::getValueDefaulted<bool>("NIXL_TELEMETRY_PROMETHEUS_LOCAL", false);
         ::mkdir(dir_.c_str(), 0777);
