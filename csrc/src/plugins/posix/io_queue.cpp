@@ -4,6 +4,8 @@
 #include <cerrno>
 #include <cstring>
 #include <linux/aio_abi.h>
+#include <linux/io_uring.h>
+#include <sys/mman.h>
 #include <sys/syscall.h>
 #include <unistd.h>
 
@@ -192,6 +194,182 @@ private:
     size_t inflight_ = 0;
 };
 
+// ---------------------------------------------------------------- io_uring (raw syscalls, no liburing)
+
+// Submission and completion rings are the kernel's shared-memory rings, mapped with mmap and
+// driven by io_uring_setup / io_uring_enter through syscall(2).  The queue is used by one thread
+// at a time (the backend serialises post and poll per request), so plain loads and stores with
+// acquire / release on the ring heads and tails are enough.
+class IoUringQueue final : public IoQueue {
+public:
+    explicit IoUringQueue(unsigned depth) {
+        unsigned entries = 1;
+        while (entries < (depth ? depth : 256) && entries < 4096) entries <<= 1;
+        io_uring_params p;
+        std::memset(&p, 0, sizeof(p));
+        fd_ = static_cast<int>(::syscall(SYS_io_uring_setup, entries, &p));
+        if (fd_ < 0) {
+            NIXL_WARN << "POSIX backend: io_uring_setup failed (" << std::strerror(errno) << ")";
+            return;
+        }
+        sqBytes_ = p.sq_off.array + p.sq_entries * sizeof(uint32_t);
+        cqBytes_ = p.cq_off.cqes + p.cq_entries * sizeof(io_uring_cqe);
+        const bool single = (p.features & IORING_FEAT_SINGLE_MMAP) != 0;
+        if (single) sqBytes_ = cqBytes_ = sqBytes_ > cqBytes_ ? sqBytes_ : cqBytes_;
+        sqRing_ = ::mmap(nullptr, sqBytes_, PROT_READ | PROT_WRITE, MAP_SHARED | MAP_POPULATE, fd_, IORING_OFF_SQ_RING);
+        cqRing_ = single ? sqRing_
+                         : ::mmap(nullptr, cqBytes_, PROT_READ | PROT_WRITE, MAP_SHARED | MAP_POPULATE, fd_, IORING_OFF_CQ_RING);
+        sqeBytes_ = p.sq_entries * sizeof(io_uring_sqe);
+        sqes_ = static_cast<io_uring_sqe *>(
+            ::mmap(nullptr, sqeBytes_, PROT_READ | PROT_WRITE, MAP_SHARED | MAP_POPULATE, fd_, IORING_OFF_SQES));
+        if (sqRing_ == MAP_FAILED || cqRing_ == MAP_FAILED || sqes_ == MAP_FAILED) {
+            NIXL_WARN << "POSIX backend: mapping the io_uring rings failed (" << std::strerror(errno) << ")";
+            if (sqRing_ == MAP_FAILED) sqRing_ = nullptr;
+            if (cqRing_ == MAP_FAILED) cqRing_ = nullptr;
+            if (sqes_ == MAP_FAILED) sqes_ = nullptr;
+            unmapAll(single);
+            ::close(fd_);
+            fd_ = -1;
+            return;
+        }
+        singleMap_ = single;
+        char *sq = static_cast<char *>(sqRing_), *cq = static_cast<char *>(cqRing_);
+        sqHead_ = reinterpret_cast<std::atomic<uint32_t> *>(sq + p.sq_off.head);
+        sqTail_ = reinterpret_cast<std::atomic<uint32_t> *>(sq + p.sq_off.tail);
+        sqMask_ = *reinterpret_cast<uint32_t *>(sq + p.sq_off.ring_mask);
+        sqArray_ = reinterpret_cast<uint32_t *>(sq + p.sq_off.array);
+        cqHead_ = reinterpret_cast<std::atomic<uint32_t> *>(cq + p.cq_off.head);
+        cqTail_ = reinterpret_cast<std::atomic<uint32_t> *>(cq + p.cq_off.tail);
+        cqMask_ = *reinterpret_cast<uint32_t *>(cq + p.cq_off.ring_mask);
+        cqes_ = reinterpret_cast<io_uring_cqe *>(cq + p.cq_off.cqes);
+        sqEntries_ = p.sq_entries;
+        cqEntries_ = p.cq_entries;
+    }
+    ~IoUringQueue() override {
+        if (fd_ < 0) return;
+        while (inflight_ > 0) reap(true);
+        unmapAll(singleMap_);
+        ::close(fd_);
+    }
+    bool ok() const { return fd_ >= 0; }
+    const char *name() const override { return "io_uring"; }
+    nixl_status_t enqueue(const IoOp &op, IoBatchState *batch) override {
+        staged_.push_back(new Slot{batch, op});
+        return NIXL_SUCCESS;
+    }
+    nixl_status_t submit() override {
+        size_t i = 0;
+        while (i < staged_.size()) {
+            // Never have more in flight than the completion ring can hold.
+            while (inflight_ >= cqEntries_) reap(true);
+            uint32_t tail = sqTail_->load(std::memory_order_relaxed);
+            const uint32_t head = sqHead_->load(std::memory_order_acquire);
+            unsigned n = 0;
+            while (i + n < staged_.size() && tail - head < sqEntries_ && inflight_ + n < cqEntries_) {
+                Slot *slot = staged_[i + n];
+                const uint32_t idx = tail & sqMask_;
+                io_uring_sqe *e = &sqes_[idx];
+                std::memset(e, 0, sizeof(*e));
+                e->opcode = slot->op.is_read ? IORING_OP_READ : IORING_OP_WRITE;
+                e->fd = slot->op.fd;
+                e->addr = reinterpret_cast<uint64_t>(slot->op.buf);
+                // One submission moves at most 1 GiB; the remainder of a larger (or short)
+                // transfer is finished synchronously when its completion is reaped.
+                e->len = static_cast<uint32_t>(slot->op.len < (1u << 30) ? slot->op.len : (1u << 30));
+                e->off = static_cast<uint64_t>(slot->op.offset);
+                e->user_data = reinterpret_cast<uint64_t>(slot);
+                sqArray_[idx] = idx;
+                ++tail;
+                ++n;
+            }
+            sqTail_->store(tail, std::memory_order_release);
+            unsigned left = n;
+            while (left) {
+                const long r = ::syscall(SYS_io_uring_enter, fd_, left, 0u, 0u, nullptr, 0);
+                if (r < 0) {
+                    if (errno == EINTR) continue;
+                    if (errno == EAGAIN || errno == EBUSY) {
+                        reap(true);
+                        continue;
+                    }
+                    const int err = errno;
+                    NIXL_ERROR << "POSIX backend: io_uring_enter failed (" << std::strerror(err) << ")";
+                    // Entries the kernel did not take stay in the ring; fail them and everything
+                    // not yet queued, and stop using this ring position.
+                    for (size_t k = i + (n - left); k < staged_.size(); ++k) {
+                        complete(staged_[k]->batch, err);
+                        delete staged_[k];
+                    }
+                    sqTail_->store(sqHead_->load(std::memory_order_acquire), std::memory_order_release);
+                    inflight_ += n - left;
+                    staged_.clear();
+                    return NIXL_ERR_BACKEND;
+                }
+                left -= static_cast<unsigned>(r);
+            }
+            inflight_ += n;
+            i += n;
+        }
+        staged_.clear();
+        return NIXL_SUCCESS;
+    }
+    void poll() override {
+        if (inflight_) reap(false);
+    }
+
+private:
+    struct Slot { IoBatchState *batch; IoOp op; };
+
+    void unmapAll(bool single) {
+        if (sqes_) ::munmap(sqes_, sqeBytes_);
+        if (cqRing_ && !single) ::munmap(cqRing_, cqBytes_);
+        if (sqRing_) ::munmap(sqRing_, sqBytes_);
+        sqes_ = nullptr;
+        sqRing_ = cqRing_ = nullptr;
+    }
+
+    // Consume what the completion ring holds; when `wait` is set and it is empty, block in the
+    // kernel for one completion first.
+    void reap(bool wait) {
+        uint32_t head = cqHead_->load(std::memory_order_relaxed);
+        if (wait && head == cqTail_->load(std::memory_order_acquire)) {
+            long r;
+            do r = ::syscall(SYS_io_uring_enter, fd_, 0u, 1u, IORING_ENTER_GETEVENTS, nullptr, 0);
+            while (r < 0 && errno == EINTR);
+        }
+        const uint32_t tail = cqTail_->load(std::memory_order_acquire);
+        for (; head != tail; ++head) {
+            const io_uring_cqe &c = cqes_[head & cqMask_];
+            auto *slot = reinterpret_cast<Slot *>(c.user_data);
+            int err = 0;
+            if (c.res < 0) err = -c.res;
+            else if (static_cast<size_t>(c.res) != slot->op.len) {
+                IoOp rest = slot->op;
+                rest.buf = static_cast<char *>(rest.buf) + c.res;
+                rest.len -= static_cast<size_t>(c.res);
+                rest.offset += c.res;
+                err = c.res == 0 ? EIO : doIo(rest);
+            }
+            complete(slot->batch, err);
+            delete slot;
+            --inflight_;
+        }
+        cqHead_->store(head, std::memory_order_release);
+    }
+
+    int fd_ = -1;
+    bool singleMap_ = false;
+    void *sqRing_ = nullptr, *cqRing_ = nullptr;
+    io_uring_sqe *sqes_ = nullptr;
+    size_t sqBytes_ = 0, cqBytes_ = 0, sqeBytes_ = 0;
+    std::atomic<uint32_t> *sqHead_ = nullptr, *sqTail_ = nullptr, *cqHead_ = nullptr, *cqTail_ = nullptr;
+    uint32_t sqMask_ = 0, cqMask_ = 0, sqEntries_ = 0, cqEntries_ = 0;
+    uint32_t *sqArray_ = nullptr;
+    io_uring_cqe *cqes_ = nullptr;
+    std::vector<Slot *> staged_;
+    size_t inflight_ = 0;
+};
+
 // ---------------------------------------------------------------- POSIX aio (glibc)
 
 class PosixAioQueue final : public IoQueue {
@@ -265,6 +443,10 @@ std::unique_ptr<IoQueue> makeQueue(QueueKind kind, unsigned pool_size, unsigned 
         auto q = std::make_unique<LinuxAioQueue>(kernel_depth);
         if (q->ok()) return q;
         NIXL_WARN << "POSIX backend: kernel AIO unavailable, using the thread pool";
+    } else if (kind == QueueKind::IO_URING) {
+        auto q = std::make_unique<IoUringQueue>(kernel_depth);
+        if (q->ok()) return q;
+        NIXL_WARN << "POSIX backend: io_uring unavailable, using the thread pool";
     } else if (kind == QueueKind::POSIX_AIO) {
         return std::make_unique<PosixAioQueue>();
     }

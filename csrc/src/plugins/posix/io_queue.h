@@ -4,8 +4,9 @@
 // implementations (linux-aio, io_uring, POSIX aio).  Here:
 //   THREADS   - a pool of workers doing pread/pwrite (default; no library needed)
 //   LINUX_AIO - kernel AIO through raw io_setup/io_submit/io_getevents system calls
+//   IO_URING  - io_uring through raw io_uring_setup/io_uring_enter system calls and mmap'd rings
 //   POSIX_AIO - glibc aio_read/aio_write
-// io_uring needs liburing, which this build does not have; asking for it selects THREADS.
+// A kernel interface that is unavailable at run time (seccomp, old kernel) selects THREADS.
 #ifndef NIXL_B200_POSIX_IO_QUEUE_H
 #define NIXL_B200_POSIX_IO_QUEUE_H
 
@@ -46,7 +47,7 @@ public:
     virtual void poll() = 0;
 };
 
-enum class QueueKind { THREADS, LINUX_AIO, POSIX_AIO };
+enum class QueueKind { THREADS, LINUX_AIO, IO_URING, POSIX_AIO };
 
 std::unique_ptr<IoQueue> makeQueue(QueueKind kind, unsigned pool_size, unsigned kernel_depth);
 

@@ -50,9 +50,10 @@ public:
         const nixl_b_params_t &p = getCustomParams();
         QueueKind kind = QueueKind::THREADS;
         if (flag(p, "use_aio")) kind = QueueKind::LINUX_AIO;
+        else if (flag(p, "use_uring")) kind = QueueKind::IO_URING;
         else if (flag(p, "use_posix_aio")) kind = QueueKind::POSIX_AIO;
-        else if (flag(p, "use_uring")) NIXL_WARN << "POSIX backend: io_uring is not built in; using the thread pool";
         queue_ = makeQueue(kind, num(p, "ios_pool_size", 8), num(p, "kernel_queue_size", 256));
+        NIXL_INFO << "POSIX backend: I/O queue " << queue_->name();
     }
 
     bool supportsRemote() const override { return false; }

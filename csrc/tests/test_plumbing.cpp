@@ -229,6 +229,62 @@ TEST_CASE(posix_file_roundtrip) {
     ::unlink(path);
 }
 
+TEST_CASE(posix_every_queue_kind_moves_more_operations_than_its_depth) {
+    // 300 descriptors through a kernel queue of 32 entries: submit has to reap while it fills.
+    constexpr size_t kOps = 300, kOpLen = 4096;
+    const char *kinds[] = {"use_aio", "use_uring", "use_posix_aio", "threads"};
+    for (const char *kind : kinds) {
+        nixlAgentConfig cfg(false);
+        const std::string me = std::string("filer_") + kind;
+        nixlAgent A(me, cfg);
+        nixl_b_params_t params = {{"kernel_queue_size", "32"}, {"ios_pool_size", "4"}};
+        if (std::string(kind) != "threads") params[kind] = "true";
+        nixlBackendH *posix = nullptr;
+        CHECK_EQ(A.createBackend("POSIX", params, posix), NIXL_SUCCESS);
+        std::vector<uint8_t> src = seeded(kOps * kOpLen, 7), back(kOps * kOpLen, 0);
+        char path[] = "/tmp/nixl_b200_queues_XXXXXX";
+        const int fd = ::mkstemp(path);
+        CHECK(fd >= 0);
+        nixl_reg_dlist_t rm(DRAM_SEG), rf(FILE_SEG);
+        rm.addDesc(nixlBlobDesc(reinterpret_cast<uintptr_t>(src.data()), src.size(), 0, ""));
+        rm.addDesc(nixlBlobDesc(reinterpret_cast<uintptr_t>(back.data()), back.size(), 0, ""));
+        rf.addDesc(nixlBlobDesc(0, 0, fd, ""));
+        CHECK_EQ(A.registerMem(rm), NIXL_SUCCESS);
+        CHECK_EQ(A.registerMem(rf), NIXL_SUCCESS);
+        nixl_xfer_dlist_t file(FILE_SEG), out(DRAM_SEG), in(DRAM_SEG);
+        for (size_t i = 0; i < kOps; ++i) {
+            // File offsets in reverse order, so that a queue which mixed up its slots would show.
+            file.addDesc(nixlBasicDesc((kOps - 1 - i) * kOpLen, kOpLen, fd));
+            out.addDesc(nixlBasicDesc(reinterpret_cast<uintptr_t>(src.data()) + i * kOpLen, kOpLen, 0));
+            in.addDesc(nixlBasicDesc(reinterpret_cast<uintptr_t>(back.data()) + i * kOpLen, kOpLen, 0));
+        }
+        nixlXferReqH *req = nullptr;
+        CHECK_EQ(A.createXferReq(NIXL_WRITE, out, file, me, req), NIXL_SUCCESS);
+        CHECK(A.postXferReq(req) >= 0);
+        CHECK_EQ(waitDone(A, req), NIXL_SUCCESS);
+        CHECK_EQ(A.releaseXferReq(req), NIXL_SUCCESS);
+        CHECK_EQ(A.createXferReq(NIXL_READ, in, file, me, req), NIXL_SUCCESS);
+        CHECK(A.postXferReq(req) >= 0);
+        CHECK_EQ(waitDone(A, req), NIXL_SUCCESS);
+        CHECK_EQ(A.releaseXferReq(req), NIXL_SUCCESS);
+        CHECK(src == back);
+        // The file holds the blocks in reverse order.
+        std::vector<uint8_t> first(kOpLen);
+        CHECK(::pread(fd, first.data(), kOpLen, 0) == static_cast<ssize_t>(kOpLen));
+        CHECK(std::equal(first.begin(), first.end(), src.begin() + (kOps - 1) * kOpLen));
+        // Reading past the end of the file fails the request instead of hanging it.
+        nixl_xfer_dlist_t beyond(FILE_SEG), one(DRAM_SEG);
+        beyond.addDesc(nixlBasicDesc(kOps * kOpLen + (1 << 20), kOpLen, fd));
+        one.addDesc(nixlBasicDesc(reinterpret_cast<uintptr_t>(back.data()), kOpLen, 0));
+        CHECK_EQ(A.createXferReq(NIXL_READ, one, beyond, me, req), NIXL_SUCCESS);
+        const nixl_status_t posted = A.postXferReq(req);
+        CHECK(posted < 0 || waitDone(A, req) < 0);
+        CHECK_EQ(A.releaseXferReq(req), NIXL_SUCCESS);
+        ::close(fd);
+        ::unlink(path);
+    }
+}
+
 TEST_CASE(hw_info_counts_devices_from_a_sysfs_tree) {
     // A fake /sys/bus/pci/devices: two B200s, one NVSwitch, one ConnectX, one EFA, one unrelated NIC.
     char tmpl[] = "/tmp/nixl_hwinfo_XXXXXX";
