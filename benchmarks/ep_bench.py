@@ -155,16 +155,18 @@ def main():
         def do_combine():
             # push: expert ranks store rows into the home rank's landing zone, which then reduces;
             # pull: home ranks load rows from the expert ranks' exposed output buffer and reduce;
-            # pull_copy: same, but the outputs first have to be copied into that buffer.
+            # pull_copy: same, but the outputs first have to be copied into that buffer;
+            # push_logfmt: push with rows in the logarithmic 10-bit format (0.66 of the bytes on the wire).
             v = variant["v"]
             if v == "default":  # what a pipeline does: the expert GEMM writes into the exposed buffer
                 v = "pull"
-            buf.combine_pull = v != "push"
+            logfmt = v == "push_logfmt"
+            buf.combine_pull = not v.startswith("push")
             src = buf.get_next_combine_buffer(state["h"]).view(-1, H) if v == "pull" else y
             if compact:
-                state["o"] = buf.combine(src, idx, w, state["h"])
+                state["o"] = buf.combine(src, idx, w, state["h"], use_logfmt=logfmt)
             else:
-                state["o"] = buf.low_latency_combine(src.view(El, -1, H), idx, w, state["h"])[0]
+                state["o"] = buf.low_latency_combine(src.view(El, -1, H), idx, w, state["h"], use_logfmt=logfmt)[0]
 
         def both():
             do_dispatch()
@@ -172,7 +174,7 @@ def main():
 
         t_disp = timed(do_dispatch, args.iters, args.warmup, flush, world, dev)
         per_variant = {}
-        for v in ("push", "pull_copy", "pull"):
+        for v in ("push", "push_logfmt", "pull_copy", "pull") if H % 512 == 0 else ("push", "pull_copy", "pull"):
             variant["v"] = v
             per_variant[f"combine_us_{v}"] = round(timed(do_combine, args.iters, args.warmup, flush, world, dev, pre=do_dispatch), 1)
             per_variant[f"dispatch_plus_combine_us_{v}"] = round(timed(both, args.iters, args.warmup, flush, world, dev), 1)

@@ -147,6 +147,10 @@ typedef struct NixlEpCombineParams {
      * and reduces them, so no row is written twice.  send_row comes from the dispatch. */
     int32_t pull;
     const int32_t *send_row;    /* [T][K] */
+    /* Push mode only: rows cross NVLink in a logarithmic 10-bit format (9-bit magnitude code on a
+     * per-128-channel grid plus sign; 0.66 of the bf16 bytes) and are decoded inside the reduction.
+     * Needs H % 512 == 0. */
+    int32_t use_logfmt;
 } NixlEpCombineParams;
 
 /* Routing statistics of topk_idx [T][K]: tokens per destination rank (a token counts once per rank),

@@ -377,6 +377,97 @@ __global__ void __launch_bounds__(kThreads) epDispatchKernel(const __grid_consta
 
 // ------------------------------------------------------------------ combine
 
+// Logarithmic 10-bit row format for combine (role of the reference's LogFMT-10 codec,
+// examples/device/ep/csrc/kernels/nixl_ep_ll.cu:459-616): per 128-channel group the magnitudes are
+// coded on a logarithmic grid of 510 steps between the group's smallest non-zero and largest
+// magnitude (at most 32 octaves), code 0 is exact zero, one further bit holds the sign.  Rounding
+// is to the nearer of the two neighbouring grid values (arithmetic midpoint), so the relative
+// error is at most (2^step - 1) / 2.  Non-finite inputs are not preserved.
+//
+// Layout of a row of H channels (H % 512 == 0) in its H * 2-byte landing slot: H / 512 blocks of
+// 160 words; in a block, lane l (16 channels l*16 .. l*16+15 of the block) owns words j*32 + l,
+// j < 5, so that a warp's five stores are each one contiguous 128 bytes; words 0..3 and the low
+// half of word 4 hold the sixteen 9-bit codes as one little-endian bit stream, the high half of
+// word 4 the sixteen sign bits.  After the blocks, at byte H * 10 / 8, one (log2 of the smallest
+// magnitude, step) pair of floats per group.
+constexpr float kLogFmtSteps = 510.f;
+constexpr float kLogFmtMaxOctaves = 32.f;
+
+__device__ __forceinline__ void stPeer4(void *p, uint32_t v) {
+    asm volatile("st.global.L1::no_allocate.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void stPeer8(void *p, const float2 &v) {
+    asm volatile("st.global.L1::no_allocate.v2.f32 [%0], {%1,%2};" ::"l"(p), "f"(v.x), "f"(v.y) : "memory");
+}
+
+// Encodes the 16 bf16 values a lane holds; the eight lanes of a 128-channel group cooperate on
+// the range.  `meta` is the group's (log2 min, step), identical in the eight lanes.
+__device__ __forceinline__ void logfmtEncode16(const uint4 &lo, const uint4 &hi, uint32_t (&w)[5], float2 &meta) {
+    const uint32_t raw[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+    float mag[16];
+    uint32_t signs = 0;
+    float amax = 0.f, amin = __int_as_float(0x7f800000);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        signs |= ((raw[i] >> 15) & 1u) << (2 * i);
+        signs |= ((raw[i] >> 31) & 1u) << (2 * i + 1);
+        mag[2 * i] = __uint_as_float((raw[i] & 0x7fffu) << 16);
+        mag[2 * i + 1] = __uint_as_float(raw[i] & 0x7fff0000u);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const float m = mag[2 * i + h];
+            amax = fmaxf(amax, m);
+            if (m > 0.f) amin = fminf(amin, m);
+        }
+    }
+#pragma unroll
+    for (int off = 4; off >= 1; off >>= 1) {
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+        amin = fminf(amin, __shfl_xor_sync(0xffffffffu, amin, off));
+    }
+    amax = fminf(amax, 3.0e38f);
+    const float log_amax = amax > 0.f ? __log2f(amax) : 0.f;
+    const float log_amin = amin <= amax ? fmaxf(__log2f(amin), log_amax - kLogFmtMaxOctaves) : log_amax;
+    const float step = (log_amax - log_amin) * (1.f / kLogFmtSteps);
+    const float step_inv = step > 0.f ? 1.f / step : 0.f;
+    // A value goes to the upper neighbour once it passes the arithmetic midpoint of the two.
+    const float bias = step > 0.f ? 1.f - __log2f(0.5f + 0.5f * exp2f(step)) * step_inv : 0.5f;
+    const float offset = bias - log_amin * step_inv;
+    meta = make_float2(log_amin, step);
+    uint64_t acc = 0;
+    int bits = 0, wi = 0;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        uint32_t code = 0;
+        if (mag[i] > 0.f) {
+            const float q = fminf(fmaxf(fmaf(__log2f(mag[i]), step_inv, offset), 0.f), kLogFmtSteps);
+            code = 1u + __float2uint_rd(q);
+        }
+        acc |= static_cast<uint64_t>(code) << bits;
+        bits += 9;
+        if (bits >= 32) {
+            w[wi++] = static_cast<uint32_t>(acc);
+            acc >>= 32;
+            bits -= 32;
+        }
+    }
+    w[4] = static_cast<uint32_t>(acc) | (signs << 16);
+}
+
+// acc[i] += weight * value_i for the 16 values of one lane's words.
+__device__ __forceinline__ void logfmtDecodeAdd16(const uint32_t (&w)[5], const float2 &meta, float weight, float (&acc)[16]) {
+    const uint32_t signs = w[4] >> 16;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const int bit = 9 * i, idx = bit >> 5, sh = bit & 31;
+        const uint32_t next = idx < 4 ? w[idx + 1] : 0u;
+        const uint32_t code = __funnelshift_r(w[idx], next, sh) & 0x1ffu;
+        float v = code ? exp2f(fmaf(static_cast<float>(code - 1u), meta.y, meta.x)) : 0.f;
+        if ((signs >> i) & 1u) v = -v;
+        acc[i] = fmaf(weight, v, acc[i]);
+    }
+}
+
 // Pull-mode combine: announce that this rank's expert outputs are complete, wait for the same
 // word from every peer, then each token's home rank loads the K rows from where dispatch put
 // them and reduces in fp32.  Every row crosses NVLink once and is never staged.
@@ -484,6 +575,28 @@ __global__ void __launch_bounds__(kThreads) epCombineKernel(const __grid_constan
             if (peer == nullptr) continue;
             const uint4 *src = reinterpret_cast<const uint4 *>(x + row * p.H);
             uint4 *dst = reinterpret_cast<uint4 *>(peer + p.lay.off_comb_x + static_cast<long long>(info.y) * p.H * 2);
+            if (p.use_logfmt) {
+                uint32_t *words = reinterpret_cast<uint32_t *>(dst);
+                float2 *meta = reinterpret_cast<float2 *>(reinterpret_cast<char *>(dst) + static_cast<long long>(p.H) * 10 / 8);
+                const int blocks = p.H / 512;
+                uint4 lo = ldNc(src + lane * 2), hi = ldNc(src + lane * 2 + 1);
+                for (int b = 0; b < blocks; ++b) {
+                    uint4 nlo = lo, nhi = hi;
+                    if (b + 1 < blocks) { // next block's loads fly while this one is encoded
+                        nlo = ldNc(src + (b + 1) * 64 + lane * 2);
+                        nhi = ldNc(src + (b + 1) * 64 + lane * 2 + 1);
+                    }
+                    uint32_t w[5];
+                    float2 m;
+                    logfmtEncode16(lo, hi, w, m);
+#pragma unroll
+                    for (int j = 0; j < 5; ++j) stPeer4(words + b * 160 + j * 32 + lane, w[j]);
+                    if ((lane & 7) == 0) stPeer8(meta + b * 4 + (lane >> 3), m);
+                    lo = nlo;
+                    hi = nhi;
+                }
+                continue;
+            }
             for (int v0 = lane; v0 < vecs; v0 += 8 * 32) { // eight loads in flight per lane
                 uint4 val[8];
 #pragma unroll
@@ -534,6 +647,45 @@ __global__ void __launch_bounds__(kThreads) epCombineKernel(const __grid_constan
                         w[k] = p.topk_weights[static_cast<long long>(t) * p.K + k];
                     else w[k] = __int_as_float(0x7fc00000); // NaN marks "skip" (a real weight may be 0)
                 }
+            }
+            if (p.use_logfmt) {
+                const long long meta_off = static_cast<long long>(p.H) * 10 / 8;
+                for (int u = gtid; u < p.H / 16; u += nt) {
+                    const int b = u >> 5, l = u & 31;
+                    float acc[16];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) acc[i] = 0.f;
+#pragma unroll
+                    for (int k0 = 0; k0 < kMaxTopk; k0 += 4) { // four rows' words in flight
+                        if (k0 >= p.K) break;
+                        uint32_t cw[4][5];
+                        float2 m[4];
+#pragma unroll
+                        for (int kk = 0; kk < 4; ++kk) {
+                            const int k = k0 + kk;
+                            if (k < p.K && w[k] == w[k]) {
+                                const char *slot = reinterpret_cast<const char *>(landing + (static_cast<long long>(t) * p.K + k) * p.H);
+                                const uint32_t *words = reinterpret_cast<const uint32_t *>(slot) + b * 160 + l;
+#pragma unroll
+                                for (int j = 0; j < 5; ++j) cw[kk][j] = words[j * 32];
+                                m[kk] = *reinterpret_cast<const float2 *>(slot + meta_off + (b * 4 + (l >> 3)) * 8);
+                            }
+                        }
+#pragma unroll
+                        for (int kk = 0; kk < 4; ++kk) {
+                            const int k = k0 + kk;
+                            if (k < p.K && w[k] == w[k]) logfmtDecodeAdd16(cw[kk], m[kk], w[k], acc);
+                        }
+                    }
+                    uint4 o[2];
+                    __nv_bfloat162 *oh = reinterpret_cast<__nv_bfloat162 *>(o);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) oh[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+                    uint4 *dst = reinterpret_cast<uint4 *>(out + static_cast<long long>(t) * p.H + b * 512 + l * 16);
+                    dst[0] = o[0];
+                    dst[1] = o[1];
+                }
+                continue;
             }
             for (int v = gtid; v < vecs; v += nt) {
                 float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -657,6 +809,7 @@ extern "C" int nixl_ep_combine_launch(const NixlEpCombineParams *params, void *s
     if (!params || !params->peers || !params->topk_idx) return cudaErrorInvalidValue;
     const NixlEpCombineParams &p = *params;
     if (p.pull && !p.send_row) return cudaErrorInvalidValue;
+    if (p.use_logfmt && (p.pull || p.H % 512)) return cudaErrorInvalidValue;
     if (p.R <= 0 || p.R > kMaxRanks || p.E <= 0 || p.E % p.R || p.K <= 0 || p.K > kMaxTopk || p.H <= 0 || p.H % 8 ||
         p.E / p.R > kMaxRanks * 8 || p.rank < 0 || p.rank >= p.R)
         return cudaErrorInvalidValue;

@@ -66,7 +66,7 @@ class _CombineParams(ctypes.Structure):
         ("T", ctypes.c_int32), ("K", ctypes.c_int32), ("H", ctypes.c_int32), ("E", ctypes.c_int32), ("R", ctypes.c_int32), ("rank", ctypes.c_int32),
         ("phases", ctypes.c_int32), ("grid", ctypes.c_int32),
         ("peers", ctypes.c_void_p), ("lay", _Layout), ("epoch", ctypes.c_uint64), ("timeout_ns", ctypes.c_uint64), ("scr", _Scratch),
-        ("pull", ctypes.c_int32), ("send_row", ctypes.c_void_p),
+        ("pull", ctypes.c_int32), ("send_row", ctypes.c_void_p), ("use_logfmt", ctypes.c_int32),
     ]
 
 
@@ -577,12 +577,17 @@ class Buffer:
         reduce ``sum_k w[t,k] * y[t,k]``.  Returns ``(combined_x [tokens, hidden], event, hook)``.
 
         ``zero_copy=True`` (on every rank) says ``x`` was written into ``get_next_combine_buffer(handle)``:
-        the home ranks then load the rows directly from there."""
-        if use_logfmt:
-            raise NotImplementedError("LogFMT compression is not implemented")
+        the home ranks then load the rows directly from there.
+
+        ``use_logfmt=True`` sends the rows in a logarithmic 10-bit format (0.66 of the bf16 bytes on
+        the wire, decoded inside the reduction; role of the reference's LogFMT-10,
+        examples/device/ep/csrc/kernels/nixl_ep_ll.cu:459-616).  It implies the push path, since the
+        encoding happens on the way out, and needs ``hidden % 512 == 0``."""
+        if use_logfmt and zero_copy:
+            raise ValueError("use_logfmt encodes rows as they are sent; it cannot be combined with zero_copy")
         flat = x.reshape(-1, self.hidden)
         out, hook = self._combine(flat, topk_idx, topk_weights, handle, 1 if return_recv_hook else 3, return_recv_hook, out,
-                                  pull=True if zero_copy else None)
+                                  pull=False if use_logfmt else (True if zero_copy else None), use_logfmt=use_logfmt)
         return out, EventOverlap(self._record() if async_finish else None), hook
 
     # ------------------------------------------------------------------ throughput mode
@@ -600,12 +605,16 @@ class Buffer:
         self._keep = keep
         return recv_x, scales, handle
 
-    def combine(self, x: torch.Tensor, topk_idx: torch.Tensor, topk_weights: torch.Tensor, handle: EPHandle, out: Optional[torch.Tensor] = None):
-        """Throughput-mode combine of ``x [rows, hidden]`` bf16 (same row order as ``dispatch`` delivered)."""
-        out, _ = self._combine(x, topk_idx, topk_weights, handle, 3, False, out)
+    def combine(self, x: torch.Tensor, topk_idx: torch.Tensor, topk_weights: torch.Tensor, handle: EPHandle, out: Optional[torch.Tensor] = None,
+                use_logfmt: bool = False):
+        """Throughput-mode combine of ``x [rows, hidden]`` bf16 (same row order as ``dispatch`` delivered).
+        ``use_logfmt`` as in :meth:`low_latency_combine`."""
+        out, _ = self._combine(x, topk_idx, topk_weights, handle, 3, False, out, pull=False if use_logfmt else None, use_logfmt=use_logfmt)
         return out
 
-    def _combine(self, x, topk_idx, topk_weights, handle, phases_now, hook_later, out, pull=None):
+    def _combine(self, x, topk_idx, topk_weights, handle, phases_now, hook_later, out, pull=None, use_logfmt=False):
+        if use_logfmt and self.hidden % 512:
+            raise ValueError("use_logfmt needs hidden % 512 == 0")
         if x.dtype != torch.bfloat16 or not x.is_contiguous():
             raise TypeError("combine input must be contiguous bf16")
         if topk_weights.dtype != torch.float32 or not topk_weights.is_contiguous():
@@ -627,6 +636,7 @@ class Buffer:
                 staged[: x.shape[0]].copy_(x)  # callers that write into get_next_combine_buffer() skip this copy
         p = self._comb_params
         p.pull = int(pull)
+        p.use_logfmt = int(use_logfmt)
         p.send_row = handle.send_row.data_ptr() if pull else None
         p.x = x.data_ptr()
         p.recv_info = handle.src_info.data_ptr()

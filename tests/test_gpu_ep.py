@@ -174,6 +174,66 @@ def test_combine_push_pull_and_zero_copy(compact, pull, zero_copy):
         b.destroy()
 
 
+@pytest.mark.parametrize("compact", [False, True])
+def test_combine_logfmt_matches_its_reference_model(compact):
+    """Rows sent in the logarithmic 10-bit format decode to what the PyTorch model of the format
+    predicts, and stay within a percent of the uncompressed result."""
+    from nixl_b200.ops.logfmt import logfmt10_roundtrip
+
+    n = min(torch.cuda.device_count(), 8)
+    tokens, hidden, experts, topk = 40, 1024, 8 * n, 4
+    bufs = _make_ranks(n, experts, hidden, tokens, topk, tag=f"eplog_{int(compact)}")
+    for it in range(2):
+        xs, idxs, ws = _inputs(bufs, tokens, hidden, experts, topk, seed=10 * it)
+        for x in xs:
+            x[1, :128] = 0          # a group of exact zeros
+            x[2, 128:256] = 0.5     # a group with a single magnitude
+            x[3, 300] = 0           # a zero inside a live group
+        results = []
+        for b, x, idx in zip(bufs, xs, idxs):
+            with torch.cuda.device(b.device):
+                if compact:
+                    rx, _, handle = b.dispatch(x, idx, use_fp8=False)
+                else:
+                    recv, _, handle, _, _ = b.low_latency_dispatch(x, idx, use_fp8=False)
+                    rx = recv.view(-1, hidden)
+                results.append((rx, handle))
+        outs = []
+        for d, b in enumerate(bufs):
+            rx, handle = results[d]
+            with torch.cuda.device(b.device):
+                y = (rx.float() * 0.37).to(torch.bfloat16)
+                if compact:
+                    outs.append(b.combine(y, idxs[d], ws[d], handle, use_logfmt=True))
+                else:
+                    outs.append(b.low_latency_combine(y.view(b.local_experts, -1, hidden), idxs[d], ws[d], handle, use_logfmt=True)[0])
+        for b in bufs:
+            torch.cuda.synchronize(b.device)
+            assert b.status == 0
+        for r, b in enumerate(bufs):
+            yk = (xs[r].float() * 0.37).to(torch.bfloat16)
+            model = torch.zeros(tokens, hidden, device=b.device)
+            exact = torch.zeros(tokens, hidden, device=b.device)
+            seen = logfmt10_roundtrip(yk)
+            for k in range(topk):
+                wk = (ws[r][:, k] * (idxs[r][:, k] >= 0).float()).unsqueeze(1)
+                model += wk * seen
+                exact += wk * yk.float()
+            got = outs[r].float()
+            # Against the model: the kernel's approximate log2 / exp2 may pick the neighbouring code on a tie.
+            assert ((got - model).norm() / model.norm()).item() < 4e-3
+            assert ((got - exact).norm() / exact.norm()).item() < 1e-2
+            torch.testing.assert_close(got, model.to(torch.bfloat16).float(), rtol=6e-2, atol=1e-3)
+            assert torch.all(got[1, :128] == 0)
+            keep = (ws[r][2] * (idxs[r][2] >= 0).float()).sum().item()
+            torch.testing.assert_close(got[2, 128:256], torch.full((128,), 0.5 * 0.37 * keep, device=b.device).to(torch.bfloat16).float(),
+                                       rtol=1e-2, atol=1e-4)
+    with pytest.raises(ValueError):
+        bufs[0].low_latency_combine(torch.zeros(1), idxs[0], ws[0], results[0][1], use_logfmt=True, zero_copy=True)
+    for b in bufs:
+        b.destroy()
+
+
 def test_throughput_only_buffer_is_smaller_and_rejects_low_latency_calls():
     dev = torch.device("cuda", 0)
     small = Buffer(0, 1, 8, 1024, 64, 2, device=dev, low_latency_mode=False)

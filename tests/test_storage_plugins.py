@@ -88,3 +88,64 @@ def test_gds_host_memory_file_roundtrip(tmp_path, name):
     a.transfer(h2)
     assert _wait(a, h2) == "DONE"
     assert torch.equal(src, dst)
+
+
+def _gusli_config(lines):
+    return "# Config file\nversion=1\n" + "\n".join(lines) + "\n"
+
+
+def test_block_backend_reads_and_writes_at_byte_offsets(tmp_path):
+    """The GUSLI-named block backend: BLK descriptors address (device id, byte offset)."""
+    store = tmp_path / "store0.bin"
+    ro = tmp_path / "readonly.bin"
+    ro.write_bytes(bytes(range(256)) * 16)
+    a = nixl_agent("blk_agent", nixl_agent_config(backends=[]))
+    a.create_backend("GUSLI", {"config_file": _gusli_config([f"11 F W N {store} sec=0x3", f"12 F R Y {ro} sec=0x3"]), "num_threads": "3"})
+    src = torch.arange(1 << 14, dtype=torch.int32)
+    dst = torch.zeros_like(src)
+    a.register_memory(src)
+    a.register_memory(dst)
+    nbytes = src.numel() * 4
+    a.register_memory([(0, 1 << 20, 11, ""), (0, 4096, 12, "")], "BLK")
+    info = a.query_memory([(0, 0, 11, ""), (0, 0, 12, ""), (0, 0, 99, "")], "GUSLI", "BLK")
+    assert info[0] is not None and info[0]["access"] == "W" and info[1]["size"] == "4096" and info[2] is None
+
+    # Two halves written to swapped positions at offset 8192 of device 11, read back straight.
+    half = nbytes // 2
+    base = src.data_ptr()
+    local = a.get_xfer_descs([(base, half, 0), (base + half, half, 0)], "DRAM")
+    swapped = a.get_xfer_descs([(8192 + half, half, 11), (8192, half, 11)], "BLK")
+    h = a.initialize_xfer("WRITE", local, swapped, "blk_agent")
+    a.transfer(h)
+    assert _wait(a, h) == "DONE"
+    raw = np.frombuffer(store.read_bytes(), dtype=np.int32)
+    assert raw.size == (8192 + nbytes) // 4
+    assert np.array_equal(raw[2048 : 2048 + half // 4], src.numpy()[half // 4 :])
+    h2 = a.initialize_xfer("READ", a.get_xfer_descs(dst), a.get_xfer_descs([(8192, nbytes, 11)], "BLK"), "blk_agent")
+    a.transfer(h2)
+    assert _wait(a, h2) == "DONE"
+    assert torch.equal(dst, torch.cat([src[half // 4 :], src[: half // 4]]))
+
+    # The read-only device serves reads and refuses writes when the request is built.
+    small = torch.zeros(256, dtype=torch.uint8)
+    a.register_memory(small)
+    h3 = a.initialize_xfer("READ", a.get_xfer_descs(small), a.get_xfer_descs([(256, 256, 12)], "BLK"), "blk_agent")
+    a.transfer(h3)
+    assert _wait(a, h3) == "DONE"
+    assert small.tolist() == list(range(256))
+    with pytest.raises(Exception):
+        a.initialize_xfer("WRITE", a.get_xfer_descs(small), a.get_xfer_descs([(0, 256, 12)], "BLK"), "blk_agent")
+    for x in (h, h2, h3):
+        a.release_xfer_handle(x)
+
+
+def test_block_backend_rejects_bad_configurations(tmp_path):
+    a = nixl_agent("blk_agent2", nixl_agent_config(backends=[]))
+    for cfg in ("", _gusli_config([]), _gusli_config(["7 N W N t127.0.0.1 sec=0x1"]), _gusli_config(["7 F W"]),
+                _gusli_config([f"7 F R N {tmp_path}/absent.bin sec=0"]), "version=2\n7 F W N /tmp/x sec=0\n"):
+        with pytest.raises(Exception):
+            a.create_backend("GUSLI", {"config_file": cfg})
+    # A device that is not in the configuration cannot be registered.
+    a.create_backend("GUSLI", {"config_file": _gusli_config([f"1 F W N {tmp_path}/d.bin sec=0"])})
+    with pytest.raises(Exception):
+        a.register_memory([(0, 4096, 2, "")], "BLK")
