@@ -378,71 +378,63 @@ __global__ void __launch_bounds__(kThreads) epDispatchKernel(const __grid_consta
 // ------------------------------------------------------------------ combine
 
 // Logarithmic 10-bit row format for combine (role of the reference's LogFMT-10 codec,
-// examples/device/ep/csrc/kernels/nixl_ep_ll.cu:459-616): per 128-channel group the magnitudes are
-// coded on a logarithmic grid of 510 steps between the group's smallest non-zero and largest
-// magnitude (at most 32 octaves), code 0 is exact zero, one further bit holds the sign.  Rounding
-// is to the nearer of the two neighbouring grid values (arithmetic midpoint), so the relative
-// error is at most (2^step - 1) / 2.  Non-finite inputs are not preserved.
+// examples/device/ep/csrc/kernels/nixl_ep_ll.cu:459-616).  The 15-bit magnitude pattern of a bf16
+// (exponent and mantissa read as one integer) is a piecewise-linear logarithm of the value, so
+// the codec works on patterns with integer and fp32 arithmetic only: per 128-channel group the
+// patterns between the smallest non-zero one (at most 32 octaves = 4096 patterns below the
+// largest) and the largest are mapped onto 510 steps; code 0 is exact zero and one further bit
+// holds the sign.  A group that spans at most 510 patterns (four octaves) is coded exactly;
+// otherwise the value is rounded to the nearest grid pattern, a relative error of at most
+// (range / 510 + 1) * 2^-8.  Non-finite inputs are clamped to the largest finite bf16.
 //
 // Layout of a row of H channels (H % 512 == 0) in its H * 2-byte landing slot: H / 512 blocks of
 // 160 words; in a block, lane l (16 channels l*16 .. l*16+15 of the block) owns words j*32 + l,
 // j < 5, so that a warp's five stores are each one contiguous 128 bytes; words 0..3 and the low
 // half of word 4 hold the sixteen 9-bit codes as one little-endian bit stream, the high half of
-// word 4 the sixteen sign bits.  After the blocks, at byte H * 10 / 8, one (log2 of the smallest
-// magnitude, step) pair of floats per group.
-constexpr float kLogFmtSteps = 510.f;
-constexpr float kLogFmtMaxOctaves = 32.f;
+// word 4 the sixteen sign bits.  After the blocks, at byte H * 10 / 8, one (smallest pattern as
+// int32, patterns per step as float) pair per group.
+constexpr unsigned kLogFmtSteps = 510;
+constexpr int kLogFmtMaxPatterns = 32 * 128;
 
 __device__ __forceinline__ void stPeer4(void *p, uint32_t v) {
     asm volatile("st.global.L1::no_allocate.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
-__device__ __forceinline__ void stPeer8(void *p, const float2 &v) {
-    asm volatile("st.global.L1::no_allocate.v2.f32 [%0], {%1,%2};" ::"l"(p), "f"(v.x), "f"(v.y) : "memory");
+__device__ __forceinline__ void stPeer8(void *p, const uint2 &v) {
+    asm volatile("st.global.L1::no_allocate.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(v.x), "r"(v.y) : "memory");
 }
 
 // Encodes the 16 bf16 values a lane holds; the eight lanes of a 128-channel group cooperate on
-// the range.  `meta` is the group's (log2 min, step), identical in the eight lanes.
-__device__ __forceinline__ void logfmtEncode16(const uint4 &lo, const uint4 &hi, uint32_t (&w)[5], float2 &meta) {
+// the range.  `meta` is the group's (smallest pattern, patterns per step), identical in the eight lanes.
+__device__ __forceinline__ void logfmtEncode16(const uint4 &lo, const uint4 &hi, uint32_t (&w)[5], uint2 &meta) {
     const uint32_t raw[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-    float mag[16];
-    uint32_t signs = 0;
-    float amax = 0.f, amin = __int_as_float(0x7f800000);
+    uint32_t pat[16];
+    uint32_t signs = 0, pmax = 0, pmin_m1 = 0xffffffffu; // zero patterns wrap to the top and drop out of the minimum
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         signs |= ((raw[i] >> 15) & 1u) << (2 * i);
-        signs |= ((raw[i] >> 31) & 1u) << (2 * i + 1);
-        mag[2 * i] = __uint_as_float((raw[i] & 0x7fffu) << 16);
-        mag[2 * i + 1] = __uint_as_float(raw[i] & 0x7fff0000u);
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            const float m = mag[2 * i + h];
-            amax = fmaxf(amax, m);
-            if (m > 0.f) amin = fminf(amin, m);
-        }
+        signs |= (raw[i] >> 31) << (2 * i + 1);
+        pat[2 * i] = min(raw[i] & 0x7fffu, 0x7f7fu);
+        pat[2 * i + 1] = min((raw[i] >> 16) & 0x7fffu, 0x7f7fu);
+        pmax = max(pmax, max(pat[2 * i], pat[2 * i + 1]));
+        pmin_m1 = min(pmin_m1, min(pat[2 * i] - 1u, pat[2 * i + 1] - 1u));
     }
 #pragma unroll
     for (int off = 4; off >= 1; off >>= 1) {
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
-        amin = fminf(amin, __shfl_xor_sync(0xffffffffu, amin, off));
+        pmax = max(pmax, __shfl_xor_sync(0xffffffffu, pmax, off));
+        pmin_m1 = min(pmin_m1, __shfl_xor_sync(0xffffffffu, pmin_m1, off));
     }
-    amax = fminf(amax, 3.0e38f);
-    const float log_amax = amax > 0.f ? __log2f(amax) : 0.f;
-    const float log_amin = amin <= amax ? fmaxf(__log2f(amin), log_amax - kLogFmtMaxOctaves) : log_amax;
-    const float step = (log_amax - log_amin) * (1.f / kLogFmtSteps);
-    const float step_inv = step > 0.f ? 1.f / step : 0.f;
-    // A value goes to the upper neighbour once it passes the arithmetic midpoint of the two.
-    const float bias = step > 0.f ? 1.f - __log2f(0.5f + 0.5f * exp2f(step)) * step_inv : 0.5f;
-    const float offset = bias - log_amin * step_inv;
-    meta = make_float2(log_amin, step);
+    int pmin = pmax ? static_cast<int>(pmin_m1 + 1u) : 0;
+    pmin = max(pmin, static_cast<int>(pmax) - kLogFmtMaxPatterns);
+    const unsigned range = pmax - static_cast<unsigned>(pmin);
+    const bool wide = range > kLogFmtSteps;
+    const float scale = wide ? static_cast<float>(kLogFmtSteps) / static_cast<float>(range) : 1.f;
+    meta = make_uint2(static_cast<uint32_t>(pmin), __float_as_uint(wide ? static_cast<float>(range) / static_cast<float>(kLogFmtSteps) : 1.f));
     uint64_t acc = 0;
     int bits = 0, wi = 0;
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
-        uint32_t code = 0;
-        if (mag[i] > 0.f) {
-            const float q = fminf(fmaxf(fmaf(__log2f(mag[i]), step_inv, offset), 0.f), kLogFmtSteps);
-            code = 1u + __float2uint_rd(q);
-        }
+        const int above = max(static_cast<int>(pat[i]) - pmin, 0);
+        const uint32_t code = pat[i] ? 1u + min(__float2uint_rn(static_cast<float>(above) * scale), kLogFmtSteps) : 0u;
         acc |= static_cast<uint64_t>(code) << bits;
         bits += 9;
         if (bits >= 32) {
@@ -455,15 +447,16 @@ __device__ __forceinline__ void logfmtEncode16(const uint4 &lo, const uint4 &hi,
 }
 
 // acc[i] += weight * value_i for the 16 values of one lane's words.
-__device__ __forceinline__ void logfmtDecodeAdd16(const uint32_t (&w)[5], const float2 &meta, float weight, float (&acc)[16]) {
-    const uint32_t signs = w[4] >> 16;
+__device__ __forceinline__ void logfmtDecodeAdd16(const uint32_t (&w)[5], const uint2 &meta, float weight, float (&acc)[16]) {
+    const float per_step = __uint_as_float(meta.y);
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
         const int bit = 9 * i, idx = bit >> 5, sh = bit & 31;
         const uint32_t next = idx < 4 ? w[idx + 1] : 0u;
         const uint32_t code = __funnelshift_r(w[idx], next, sh) & 0x1ffu;
-        float v = code ? exp2f(fmaf(static_cast<float>(code - 1u), meta.y, meta.x)) : 0.f;
-        if ((signs >> i) & 1u) v = -v;
+        const uint32_t pat = meta.x + __float2uint_rn(static_cast<float>(code - 1u) * per_step);
+        const uint32_t sign = (w[4] >> (16 + i)) << 31;
+        const float v = __uint_as_float(code ? ((pat << 16) | sign) : 0u);
         acc[i] = fmaf(weight, v, acc[i]);
     }
 }
@@ -577,7 +570,7 @@ __global__ void __launch_bounds__(kThreads) epCombineKernel(const __grid_constan
             uint4 *dst = reinterpret_cast<uint4 *>(peer + p.lay.off_comb_x + static_cast<long long>(info.y) * p.H * 2);
             if (p.use_logfmt) {
                 uint32_t *words = reinterpret_cast<uint32_t *>(dst);
-                float2 *meta = reinterpret_cast<float2 *>(reinterpret_cast<char *>(dst) + static_cast<long long>(p.H) * 10 / 8);
+                uint2 *meta = reinterpret_cast<uint2 *>(reinterpret_cast<char *>(dst) + static_cast<long long>(p.H) * 10 / 8);
                 const int blocks = p.H / 512;
                 uint4 lo = ldNc(src + lane * 2), hi = ldNc(src + lane * 2 + 1);
                 for (int b = 0; b < blocks; ++b) {
@@ -587,7 +580,7 @@ __global__ void __launch_bounds__(kThreads) epCombineKernel(const __grid_constan
                         nhi = ldNc(src + (b + 1) * 64 + lane * 2 + 1);
                     }
                     uint32_t w[5];
-                    float2 m;
+                    uint2 m;
                     logfmtEncode16(lo, hi, w, m);
 #pragma unroll
                     for (int j = 0; j < 5; ++j) stPeer4(words + b * 160 + j * 32 + lane, w[j]);
@@ -659,7 +652,7 @@ __global__ void __launch_bounds__(kThreads) epCombineKernel(const __grid_constan
                     for (int k0 = 0; k0 < kMaxTopk; k0 += 4) { // four rows' words in flight
                         if (k0 >= p.K) break;
                         uint32_t cw[4][5];
-                        float2 m[4];
+                        uint2 m[4];
 #pragma unroll
                         for (int kk = 0; kk < 4; ++kk) {
                             const int k = k0 + kk;
@@ -668,7 +661,7 @@ __global__ void __launch_bounds__(kThreads) epCombineKernel(const __grid_constan
                                 const uint32_t *words = reinterpret_cast<const uint32_t *>(slot) + b * 160 + l;
 #pragma unroll
                                 for (int j = 0; j < 5; ++j) cw[kk][j] = words[j * 32];
-                                m[kk] = *reinterpret_cast<const float2 *>(slot + meta_off + (b * 4 + (l >> 3)) * 8);
+                                m[kk] = *reinterpret_cast<const uint2 *>(slot + meta_off + (b * 4 + (l >> 3)) * 8);
                             }
                         }
 #pragma unroll

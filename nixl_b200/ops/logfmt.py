@@ -2,50 +2,56 @@
 
 The kernel side is ``logfmtEncode16`` / ``logfmtDecodeAdd16`` in ``csrc/src/kernels/ep_kernels.cu``
 (role of the reference's LogFMT-10 codec, examples/device/ep/csrc/kernels/nixl_ep_ll.cu:459-616).
-Per group of 128 channels the magnitudes are coded on a grid of 510 logarithmic steps between the
-group's smallest non-zero and largest magnitude (at most 32 octaves below the largest); code 0 is an
-exact zero and one more bit holds the sign.  This module states the same arithmetic in plain
-PyTorch: it is the oracle of the kernel's tests and lets a model check offline what the format
-does to its activations.
+The 15-bit magnitude pattern of a bf16 (exponent and mantissa read as one integer) is a
+piecewise-linear logarithm of the value.  Per group of 128 channels the patterns between the
+smallest non-zero one (at most 32 octaves = 4096 patterns below the largest) and the largest are
+mapped onto 510 steps; code 0 is an exact zero and one more bit holds the sign.  A group spanning at
+most 510 patterns (four octaves) is coded exactly.  This module states the same arithmetic in
+plain PyTorch, bit for bit: it is the oracle of the kernel's tests and lets a model check offline
+what the format does to its activations.
 """
 from __future__ import annotations
 
 import torch
 
 GROUP = 128
-STEPS = 510.0
-MAX_OCTAVES = 32.0
+STEPS = 510
+MAX_PATTERNS = 32 * 128
+_LARGEST_FINITE = 0x7F7F
 
 
 def logfmt10_codes(x: torch.Tensor):
-    """Encode ``x [..., H]`` (H % 128 == 0).  Returns ``(codes int32 [..., H] in 0..511,
-    negative bool [..., H], log_min float32 [..., H // 128], step float32 [..., H // 128])``."""
+    """Encode ``x [..., H]`` (H % 128 == 0; converted to bf16 first).  Returns ``(codes int32
+    [..., H] in 0..511, negative bool [..., H], min_pattern int32 [..., H // 128],
+    patterns_per_step float32 [..., H // 128])``."""
     if x.shape[-1] % GROUP:
         raise ValueError("the last dimension must be a multiple of 128")
-    xf = x.float()
-    g = xf.reshape(*xf.shape[:-1], -1, GROUP)
-    mag = g.abs()
-    amax = mag.amax(dim=-1).clamp(max=3.0e38)
-    amin = torch.where(mag > 0, mag, torch.full_like(mag, float("inf"))).amin(dim=-1)
-    log_amax = torch.where(amax > 0, torch.log2(amax.clamp(min=1e-45)), torch.zeros_like(amax))
-    log_amin = torch.where(amin <= amax, torch.maximum(torch.log2(amin), log_amax - MAX_OCTAVES), log_amax)
-    step = (log_amax - log_amin) / STEPS
-    pos = step > 0
-    step_inv = torch.where(pos, 1.0 / step.clamp(min=1e-38), torch.zeros_like(step))
-    # A value moves to the upper neighbour once it passes the arithmetic midpoint of the two.
-    bias = torch.where(pos, 1.0 - torch.log2(0.5 + 0.5 * torch.exp2(step)) * step_inv, torch.full_like(step, 0.5))
-    q = (torch.log2(mag.clamp(min=1e-45)) - log_amin[..., None]) * step_inv[..., None] + bias[..., None]
-    codes = torch.where(mag > 0, 1 + q.clamp(0.0, STEPS).floor().to(torch.int32), torch.zeros_like(q, dtype=torch.int32))
-    return codes.reshape(x.shape), (g < 0).reshape(x.shape), log_amin, step
+    bits = x.to(torch.bfloat16).contiguous().view(torch.int16).to(torch.int32) & 0xFFFF
+    negative = (bits >> 15).bool()
+    pat = (bits & 0x7FFF).clamp(max=_LARGEST_FINITE).reshape(*x.shape[:-1], -1, GROUP)
+    pmax = pat.amax(dim=-1)
+    pmin = torch.where(pat > 0, pat, torch.full_like(pat, 0x7FFF)).amin(dim=-1)
+    pmin = torch.where(pmax > 0, pmin, torch.zeros_like(pmin))
+    pmin = torch.maximum(pmin, pmax - MAX_PATTERNS)
+    span = pmax - pmin
+    wide = span > STEPS
+    spanf = span.clamp(min=1).float()
+    scale = torch.where(wide, torch.tensor(float(STEPS)) / spanf, torch.ones_like(spanf))
+    per_step = torch.where(wide, spanf / float(STEPS), torch.ones_like(spanf))
+    above = (pat - pmin[..., None]).clamp(min=0).float()
+    q = torch.round(above * scale[..., None]).to(torch.int32).clamp(max=STEPS)  # round half to even, as cvt.rni
+    codes = torch.where(pat > 0, 1 + q, torch.zeros_like(q))
+    return codes.reshape(x.shape), negative, pmin, per_step
 
 
-def logfmt10_decode(codes: torch.Tensor, negative: torch.Tensor, log_min: torch.Tensor, step: torch.Tensor) -> torch.Tensor:
+def logfmt10_decode(codes: torch.Tensor, negative: torch.Tensor, min_pattern: torch.Tensor, per_step: torch.Tensor) -> torch.Tensor:
     """Inverse of :func:`logfmt10_codes`, in float32."""
     c = codes.reshape(*codes.shape[:-1], -1, GROUP)
-    v = torch.exp2((c - 1).float() * step[..., None] + log_min[..., None])
-    v = torch.where(c > 0, v, torch.zeros_like(v))
-    v = torch.where(negative.reshape(c.shape), -v, v)
-    return v.reshape(codes.shape)
+    pat = min_pattern[..., None] + torch.round((c - 1).float() * per_step[..., None]).to(torch.int32)
+    pat = torch.where(c > 0, pat, torch.zeros_like(pat)).reshape(codes.shape)
+    word = (pat << 16) | (negative.to(torch.int32) << 31)
+    word = torch.where(codes > 0, word, torch.zeros_like(word))
+    return word.view(torch.float32)
 
 
 def logfmt10_roundtrip(x: torch.Tensor) -> torch.Tensor:
@@ -54,5 +60,5 @@ def logfmt10_roundtrip(x: torch.Tensor) -> torch.Tensor:
 
 
 def logfmt10_row_bytes(hidden: int) -> int:
-    """Bytes of one row on the wire: ten bits per channel plus two floats per group."""
+    """Bytes of one row on the wire: ten bits per channel plus eight bytes per group."""
     return hidden * 10 // 8 + (hidden // GROUP) * 8

@@ -220,10 +220,10 @@ def test_combine_logfmt_matches_its_reference_model(compact):
                 model += wk * seen
                 exact += wk * yk.float()
             got = outs[r].float()
-            # Against the model: the kernel's approximate log2 / exp2 may pick the neighbouring code on a tie.
-            assert ((got - model).norm() / model.norm()).item() < 4e-3
+            # The model states the kernel's arithmetic bit for bit; what is left is the order of the fp32 sums.
+            assert ((got - model).norm() / model.norm()).item() < 3e-3
             assert ((got - exact).norm() / exact.norm()).item() < 1e-2
-            torch.testing.assert_close(got, model.to(torch.bfloat16).float(), rtol=6e-2, atol=1e-3)
+            torch.testing.assert_close(got, model.to(torch.bfloat16).float(), rtol=1.6e-2, atol=1e-4)
             assert torch.all(got[1, :128] == 0)
             keep = (ws[r][2] * (idxs[r][2] >= 0).float()).sum().item()
             torch.testing.assert_close(got[2, 128:256], torch.full((128,), 0.5 * 0.37 * keep, device=b.device).to(torch.bfloat16).float(),
