@@ -5,6 +5,18 @@
 // /tmp/nixl_obj), object = file named by its key.  WRITE puts [offset, offset+len) of the
 // object, READ gets it; queryMem tells whether a key exists.  The engine keeps the reference's
 // contract so an S3 transport can replace the file calls without touching callers.
+//
+// The same engine is also built under the reference's other object-store names, with the
+// parameter that names the bucket in each of them (NIXL_OBJ_PLUGIN_NAME / NIXL_OBJ_BUCKET_PARAM):
+// AZURE_BLOB (`container_name`; src/plugins/azure_blob) and INFINIA (`dataset`;
+// src/plugins/infinia).  Their remaining parameters (account URLs, cluster and tenant names) are
+// accepted and ignored: there is no service to talk to.
+#ifndef NIXL_OBJ_PLUGIN_NAME
+#define NIXL_OBJ_PLUGIN_NAME "OBJ"
+#endif
+#ifndef NIXL_OBJ_BUCKET_PARAM
+#define NIXL_OBJ_BUCKET_PARAM "bucket"
+#endif
 #include <cerrno>
 #include <cstring>
 #include <fcntl.h>
@@ -69,7 +81,7 @@ class ObjEngine final : public nixlBackendEngine {
 public:
     explicit ObjEngine(const nixlBackendInitParams *p) : nixlBackendEngine(p) {
         std::string v;
-        if (getInitParam("bucket", v) == NIXL_SUCCESS && !v.empty()) dir_ = v;
+        if (getInitParam(NIXL_OBJ_BUCKET_PARAM, v) == NIXL_SUCCESS && !v.empty()) dir_ = v;
         else if (const char *e = std::getenv("NIXL_OBJ_BUCKET_DIR")) dir_ = e;
         else dir_ = "/tmp/nixl_obj";
         ::mkdir(dir_.c_str(), 0755);
@@ -163,7 +175,7 @@ private:
 } // namespace
 
 extern "C" NIXL_PLUGIN_EXPORT nixlBackendPlugin *nixl_plugin_init() {
-    return nixlBackendPluginCreator<ObjEngine>::create(NIXL_PLUGIN_API_VERSION, "OBJ", "1.0.0", {{"bucket", ""}, {"num_threads", "4"}},
+    return nixlBackendPluginCreator<ObjEngine>::create(NIXL_PLUGIN_API_VERSION, NIXL_OBJ_PLUGIN_NAME, "1.0.0", {{NIXL_OBJ_BUCKET_PARAM, ""}, {"num_threads", "4"}},
                                                        {DRAM_SEG, OBJ_SEG});
 }
 extern "C" NIXL_PLUGIN_EXPORT void nixl_plugin_fini() {}

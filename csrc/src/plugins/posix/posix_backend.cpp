@@ -6,6 +6,14 @@
 // where metaInfo names the file and devId is a caller-chosen unique id (:228); one I/O per
 // descriptor (:170-201); queue chosen by the use_aio / use_uring / use_posix_aio parameters
 // (:82); queryMem stats files (:348).
+//
+// Also built as libplugin_HF3FS.so (NIXL_POSIX_PLUGIN_NAME): the reference's HF3FS plugin
+// (src/plugins/hf3fs) has the same contract (local, DRAM + FILE, fd in devId) over the 3FS
+// user-space I/O rings, which this box does not have; under that name the files are served with
+// the queues of this engine.
+#ifndef NIXL_POSIX_PLUGIN_NAME
+#define NIXL_POSIX_PLUGIN_NAME "POSIX"
+#endif
 #include <atomic>
 #include <mutex>
 #include <unordered_map>
@@ -52,7 +60,8 @@ public:
         if (flag(p, "use_aio")) kind = QueueKind::LINUX_AIO;
         else if (flag(p, "use_uring")) kind = QueueKind::IO_URING;
         else if (flag(p, "use_posix_aio")) kind = QueueKind::POSIX_AIO;
-        queue_ = makeQueue(kind, num(p, "ios_pool_size", 8), num(p, "kernel_queue_size", 256));
+        // `iopool_size` is the name the reference's HF3FS plugin gives its pool (src/plugins/hf3fs).
+        queue_ = makeQueue(kind, num(p, "ios_pool_size", num(p, "iopool_size", 8)), num(p, "kernel_queue_size", 256));
         NIXL_INFO << "POSIX backend: I/O queue " << queue_->name();
     }
 
@@ -188,7 +197,7 @@ nixl_b_params_t defaults() {
 } // namespace nixl_posix
 
 extern "C" NIXL_PLUGIN_EXPORT nixlBackendPlugin *nixl_plugin_init() {
-    return nixlBackendPluginCreator<nixl_posix::Engine>::create(NIXL_PLUGIN_API_VERSION, "POSIX", "1.0.0", nixl_posix::defaults(),
+    return nixlBackendPluginCreator<nixl_posix::Engine>::create(NIXL_PLUGIN_API_VERSION, NIXL_POSIX_PLUGIN_NAME, "1.0.0", nixl_posix::defaults(),
                                                                 {DRAM_SEG, FILE_SEG});
 }
 

@@ -149,3 +149,46 @@ def test_block_backend_rejects_bad_configurations(tmp_path):
     a.create_backend("GUSLI", {"config_file": _gusli_config([f"1 F W N {tmp_path}/d.bin sec=0"])})
     with pytest.raises(Exception):
         a.register_memory([(0, 4096, 2, "")], "BLK")
+
+
+@pytest.mark.parametrize("name,param", [("AZURE_BLOB", "container_name"), ("INFINIA", "dataset")])
+def test_object_engine_under_the_other_object_store_names(tmp_path, name, param):
+    a = nixl_agent(f"obj_{name}", nixl_agent_config(backends=[]))
+    assert name in a.get_plugin_list()
+    a.create_backend(name, {param: str(tmp_path), "account_url": "https://example.invalid", "tenant": "t"})
+    src = torch.arange(4096, dtype=torch.int16)
+    dst = torch.zeros_like(src)
+    a.register_memory(src)
+    a.register_memory(dst)
+    a.register_memory([(0, 8192, 3, "blob.bin")], "OBJ")
+    remote = a.get_xfer_descs([(0, 8192, 3)], "OBJ")
+    h = a.initialize_xfer("WRITE", a.get_xfer_descs(src), remote, f"obj_{name}")
+    a.transfer(h)
+    assert _wait(a, h) == "DONE"
+    assert (tmp_path / "blob.bin").stat().st_size == 8192
+    h2 = a.initialize_xfer("READ", a.get_xfer_descs(dst), remote, f"obj_{name}")
+    a.transfer(h2)
+    assert _wait(a, h2) == "DONE"
+    assert torch.equal(src, dst)
+
+
+def test_file_engine_under_the_hf3fs_name(tmp_path):
+    a = nixl_agent("hf3fs_agent", nixl_agent_config(backends=[]))
+    a.create_backend("HF3FS", {"mem_config": "auto", "iopool_size": "2"})
+    src = torch.arange(1 << 15, dtype=torch.uint8)
+    dst = torch.zeros_like(src)
+    a.register_memory(src)
+    a.register_memory(dst)
+    fd = os.open(tmp_path / "f.bin", os.O_RDWR | os.O_CREAT, 0o644)
+    try:
+        a.register_memory([(0, 4096 + src.numel(), fd, "")], "FILE")
+        remote = a.get_xfer_descs([(4096, src.numel(), fd)], "FILE")
+        h = a.initialize_xfer("WRITE", a.get_xfer_descs(src), remote, "hf3fs_agent")
+        a.transfer(h)
+        assert _wait(a, h) == "DONE"
+        h2 = a.initialize_xfer("READ", a.get_xfer_descs(dst), remote, "hf3fs_agent")
+        a.transfer(h2)
+        assert _wait(a, h2) == "DONE"
+        assert torch.equal(src, dst) and os.fstat(fd).st_size == 4096 + src.numel()
+    finally:
+        os.close(fd)
