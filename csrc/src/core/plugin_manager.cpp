@@ -69,8 +69,10 @@ nixlPluginManager::nixlPluginManager() {
     const std::string here = selfDir();
     dirs_.push_back(here + "/plugins");
     dirs_.push_back(here);
-    aliases_["UCX"] = "NVLINK";
-    aliases_["UCX_MO"] = "NVLINK";
+    // Names of the reference's network transports resolve to the NVLink backend: inside one
+    // NVLink domain it is the engine that moves DRAM and VRAM between agents, whatever fabric
+    // the caller's configuration was written for.  A real plug-in of such a name wins.
+    for (const char *name : {"UCX", "UCX_MO", "LIBFABRIC", "MOONCAKE", "UCCL", "GPUNETIO"}) aliases_[name] = "NVLINK";
 }
 
 void nixlPluginManager::addPluginDirectory(const std::string &dir) {
