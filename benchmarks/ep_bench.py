@@ -108,6 +108,7 @@ def main():
     ap.add_argument("--topk", type=int, default=8)
     ap.add_argument("--inter", type=int, default=2048)
     ap.add_argument("--modes", default="ll,tp")
+    ap.add_argument("--num-sms", type=int, default=0, help="grid of the dispatch / combine kernels (0: one CTA per SM)")
     ap.add_argument("--skip-baseline", action="store_true")
     ap.add_argument("--skip-gemm", action="store_true")
     args = ap.parse_args()
@@ -134,6 +135,8 @@ def main():
         compact = mode != "ll"
         buf = Buffer(rank, world, E, H, T, K, device=dev, timeout_ms=20000, low_latency_mode=not compact)
         buf.connect_ranks()
+        if args.num_sms:
+            buf.set_num_sms(args.num_sms)
 
         state = {}
 

@@ -150,7 +150,28 @@ __device__ __forceinline__ uint2 quantGroup(const uint4 &raw, bool round_scale, 
     return make_uint2(w[0] | (w[1] << 16), w[2] | (w[3] << 16));
 }
 
-__global__ void __launch_bounds__(kThreads) epDispatchKernel(const __grid_constant__ NixlEpDispatchParams p) {
+// Counts the rows of up to kPending tokens as sent.  Lane k < K of a token group holds, per token,
+// the expert its k-th copy went to (-1: none).  The caller has passed a group barrier since the last
+// of those stores was issued; the fence makes them visible system-wide before any count moves.
+// Whoever completes an expert's rows raises that expert's arrival flag at its rank.
+constexpr int kPending = 4;
+__device__ __forceinline__ void countSent(const NixlEpDispatchParams &p, int El, const int (&pend)[kPending], int npend, int gtid) {
+    if (gtid >= p.K) return;
+    __threadfence_system();
+#pragma unroll
+    for (int i = 0; i < kPending; ++i) {
+        if (i >= npend || pend[i] < 0) continue;
+        const int e = pend[i];
+        const int done = atomicAdd(p.scr.sent + e, 1) + 1;
+        if (done == ldVolatile(p.scr.cnt + e)) {
+            __threadfence_system(); // acquire side of the count: other groups' rows of this expert are out
+            char *peer = peerBase(p.peers, e / El);
+            stReleaseSys(reinterpret_cast<uint64_t *>(peer + p.lay.off_disp_flag) + static_cast<long long>(e % El) * p.R + p.rank, p.epoch);
+        }
+    }
+}
+
+__global__ void __launch_bounds__(kThreads, 1) epDispatchKernel(const __grid_constant__ NixlEpDispatchParams p) {
     extern __shared__ __align__(16) unsigned char smem[];
     const int El = p.E / p.R;
     const int groups = p.H / kGroup;
@@ -268,6 +289,10 @@ __global__ void __launch_bounds__(kThreads) epDispatchKernel(const __grid_consta
         unsigned char *rowbuf = reinterpret_cast<unsigned char *>(slots + kMaxTopk);
         float *scalebuf = reinterpret_cast<float *>(rowbuf + row_bytes);
         const int bar_id = 1 + grp;
+        int pend[kPending];
+        int npend = 0; // uniform over the group
+#pragma unroll
+        for (int i = 0; i < kPending; ++i) pend[i] = -1;
         for (int t = blockIdx.x * groups_per_cta + grp; t < p.T; t += gridDim.x * groups_per_cta) {
             const uint4 *src = reinterpret_cast<const uint4 *>(x + static_cast<long long>(t) * p.H);
             // Four loads in flight per thread.  `vecs` is a multiple of 32, so the guards are warp-uniform.
@@ -334,19 +359,21 @@ __global__ void __launch_bounds__(kThreads) epDispatchKernel(const __grid_consta
                 }
             }
             groupBarrier(bar_id, nt); // all stores of this token issued (and the buffer is free for the next one)
-            if (gtid < p.K && slots[gtid] >= 0) {
-                // Count the row as sent; whoever completes an expert's rows raises its flag.
-                const int e = static_cast<int>(p.topk_idx[static_cast<long long>(t) * p.K + gtid]);
-                __threadfence_system();
-                const int done = atomicAdd(p.scr.sent + e, 1) + 1;
-                if (done == ldVolatile(p.scr.cnt + e)) {
-                    __threadfence_system(); // acquire side of the count: other groups' rows of this expert are out
-                    char *peer = peerBase(p.peers, e / El);
-                    stReleaseSys(reinterpret_cast<uint64_t *>(peer + p.lay.off_disp_flag) + static_cast<long long>(e % El) * p.R + p.rank, p.epoch);
-                }
+            // The rows still have to be counted as sent, behind a system-wide fence.  That fence waits
+            // for every store in flight to be acknowledged by the peer, so it is paid once per
+            // kPending tokens, not per token: lane k keeps the experts of its tokens until then.
+            int e_now = -1;
+            if (gtid < p.K && slots[gtid] >= 0) e_now = static_cast<int>(p.topk_idx[static_cast<long long>(t) * p.K + gtid]);
+#pragma unroll
+            for (int i = 0; i < kPending; ++i)
+                if (i == npend) pend[i] = e_now;
+            if (++npend == kPending) {
+                countSent(p, El, pend, npend, gtid);
+                npend = 0;
             }
             groupBarrier(bar_id, nt);
         }
+        if (npend > 0) countSent(p, El, pend, npend, gtid);
     }
 
     if (p.phases & 2) {
@@ -792,7 +819,16 @@ extern "C" int nixl_ep_dispatch_launch(const NixlEpDispatchParams *params, void 
             attr_done[dev] = true;
         }
     }
-    const int grid = coopGrid(reinterpret_cast<const void *>(epDispatchKernel), p.grid, smem);
+    // With many tokens per CTA the data phase is a chain of dependent steps per token (load,
+    // quantise, reserve slots, store); a second CTA per SM hides that latency.
+    int requested = p.grid;
+    if (requested <= 0) {
+        int dev = 0, sms = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (p.T >= 4 * sms) requested = 2 * sms;
+    }
+    const int grid = coopGrid(reinterpret_cast<const void *>(epDispatchKernel), requested, smem);
     void *args[] = {const_cast<NixlEpDispatchParams *>(params)};
     return cudaLaunchCooperativeKernel(reinterpret_cast<const void *>(epDispatchKernel), dim3(grid), dim3(kThreads), args, smem,
                                        static_cast<cudaStream_t>(stream));
