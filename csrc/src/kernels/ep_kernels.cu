@@ -176,14 +176,16 @@ __global__ void __launch_bounds__(kThreads, 1) epDispatchKernel(const __grid_con
     const int El = p.E / p.R;
     const int groups = p.H / kGroup;
     const int row_bytes = p.use_fp8 ? p.H : p.H * 2;
-    // shared: before[E] | ebase[E] | per token group: slots[kMaxTopk] | row bytes | scales
+    // shared: before[E] | ebase[E] | per token group: rows[kMaxTopk] | dests[kMaxTopk] | row bytes | scales
     int *before = reinterpret_cast<int *>(smem);
     int *ebase = before + p.E;
     unsigned char *group_area = reinterpret_cast<unsigned char *>(ebase + p.E);
-    const int group_bytes = (kMaxTopk * 4 + row_bytes + groups * 4 + 15) & ~15;
+    const int group_bytes = (2 * kMaxTopk * 4 + row_bytes + groups * 4 + 15) & ~15;
 
     char *self = peerBase(p.peers, p.rank);
     const int tid = threadIdx.x;
+    __shared__ char *peer_sh[kMaxRanks]; // the data phase looks a peer up per row: keep the table on chip
+    if (tid < p.R) peer_sh[tid] = peerBase(p.peers, tid);
 
     if (p.phases & 1) {
         // 1. histogram of destinations
@@ -285,8 +287,10 @@ __global__ void __launch_bounds__(kThreads, 1) epDispatchKernel(const __grid_con
         const int nt = threadsPerItem(p.T);
         const int groups_per_cta = kThreads / nt;
         const int grp = tid / nt, gtid = tid - grp * nt;
-        int *slots = reinterpret_cast<int *>(group_area + static_cast<size_t>(grp) * group_bytes);
-        unsigned char *rowbuf = reinterpret_cast<unsigned char *>(slots + kMaxTopk);
+        // Per copy of the token: the row it lands on at its receiver (-1: none) and the receiver.
+        int *rows = reinterpret_cast<int *>(group_area + static_cast<size_t>(grp) * group_bytes);
+        int *dests = rows + kMaxTopk;
+        unsigned char *rowbuf = reinterpret_cast<unsigned char *>(dests + kMaxTopk);
         float *scalebuf = reinterpret_cast<float *>(rowbuf + row_bytes);
         const int bar_id = 1 + grp;
         int pend[kPending];
@@ -295,14 +299,16 @@ __global__ void __launch_bounds__(kThreads, 1) epDispatchKernel(const __grid_con
         for (int i = 0; i < kPending; ++i) pend[i] = -1;
         for (int t = blockIdx.x * groups_per_cta + grp; t < p.T; t += gridDim.x * groups_per_cta) {
             const uint4 *src = reinterpret_cast<const uint4 *>(x + static_cast<long long>(t) * p.H);
-            // Four loads in flight per thread.  `vecs` is a multiple of 32, so the guards are warp-uniform.
-            for (int v0 = gtid; v0 < vecs; v0 += 4 * nt) {
-                uint4 raw[4];
+            // Seven loads in flight per thread (a 7168-channel row is four such rounds for a warp).
+            // `vecs` is a multiple of 32, so the guards are warp-uniform.
+            constexpr int kLoads = 7;
+            for (int v0 = gtid; v0 < vecs; v0 += kLoads * nt) {
+                uint4 raw[kLoads];
 #pragma unroll
-                for (int j = 0; j < 4; ++j)
+                for (int j = 0; j < kLoads; ++j)
                     if (v0 + j * nt < vecs) raw[j] = ldNc(src + v0 + j * nt);
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
+                for (int j = 0; j < kLoads; ++j) {
                     const int v = v0 + j * nt;
                     if (v >= vecs) continue;
                     if (p.use_fp8) {
@@ -315,30 +321,27 @@ __global__ void __launch_bounds__(kThreads, 1) epDispatchKernel(const __grid_con
                     }
                 }
             }
-            // reserve one slot per destination
+            // Lane k reserves the slot of the token's k-th copy and leaves its row and receiver in
+            // shared memory, so that the store loop below starts without a global load.
+            int e_now = -1; // expert whose sent-count this lane owes (set even when the row exceeds the capacity)
             if (gtid < p.K) {
                 const long long e = p.topk_idx[static_cast<long long>(t) * p.K + gtid];
-                int slot = -1;
-                if (e >= 0 && e < p.E && ldVolatile(p.scr.mask + static_cast<int>(e) / El) == 0) slot = atomicAdd(p.scr.fill + e, 1);
-                slots[gtid] = slot;
-                if (p.send_row != nullptr) {
-                    long long row = -1;
-                    if (slot >= 0) {
-                        row = static_cast<long long>(ebase[e]) + before[e] + slot;
-                        if (row >= p.cap) row = -1;
-                    }
-                    p.send_row[static_cast<long long>(t) * p.K + gtid] = static_cast<int>(row);
+                long long row = -1;
+                if (e >= 0 && e < p.E && ldVolatile(p.scr.mask + static_cast<int>(e) / El) == 0) {
+                    e_now = static_cast<int>(e);
+                    row = static_cast<long long>(ebase[e]) + before[e] + atomicAdd(p.scr.fill + e, 1);
+                    if (row >= p.cap) row = -1; // flagged as ST_CAPACITY above
                 }
+                rows[gtid] = static_cast<int>(row);
+                dests[gtid] = e_now >= 0 ? e_now / El : 0;
+                if (p.send_row != nullptr) p.send_row[static_cast<long long>(t) * p.K + gtid] = static_cast<int>(row);
             }
             groupBarrier(bar_id, nt);
             for (int k = 0; k < p.K; ++k) {
-                const int slot = slots[k];
-                if (slot < 0) continue;
-                const int e = static_cast<int>(p.topk_idx[static_cast<long long>(t) * p.K + k]);
-                const int d = e / El;
-                const long long row = static_cast<long long>(ebase[e]) + before[e] + slot;
-                if (row >= p.cap) continue; // flagged as ST_CAPACITY above
-                char *peer = peerBase(p.peers, d);
+                const long long row = rows[k];
+                if (row < 0) continue;
+                const int d = dests[k];
+                char *peer = peer_sh[d];
                 uint4 *dx = reinterpret_cast<uint4 *>(peer + p.lay.off_recv_x + row * row_bytes);
                 for (int v = gtid; v < row_bytes / 16; v += nt) stPeer16(dx + v, reinterpret_cast<const uint4 *>(rowbuf)[v]);
                 if (p.use_fp8 && p.use_ue8m0) {
@@ -362,8 +365,6 @@ __global__ void __launch_bounds__(kThreads, 1) epDispatchKernel(const __grid_con
             // The rows still have to be counted as sent, behind a system-wide fence.  That fence waits
             // for every store in flight to be acknowledged by the peer, so it is paid once per
             // kPending tokens, not per token: lane k keeps the experts of its tokens until then.
-            int e_now = -1;
-            if (gtid < p.K && slots[gtid] >= 0) e_now = static_cast<int>(p.topk_idx[static_cast<long long>(t) * p.K + gtid]);
 #pragma unroll
             for (int i = 0; i < kPending; ++i)
                 if (i == npend) pend[i] = e_now;
@@ -806,7 +807,7 @@ extern "C" int nixl_ep_dispatch_launch(const NixlEpDispatchParams *params, void 
         return cudaErrorInvalidValue;
     if (p.H % 512) return cudaErrorInvalidValue; // whole warps per pass; scales move as float4
     if (p.rows_per_expert > 0 && static_cast<long long>(p.rows_per_expert) < static_cast<long long>(p.R) * p.T) return cudaErrorInvalidValue;
-    const size_t group_bytes = (kMaxTopk * sizeof(int) + size_t(p.use_fp8 ? p.H : p.H * 2) + (p.H / kGroup) * sizeof(float) + 15) & ~size_t(15);
+    const size_t group_bytes = (2 * kMaxTopk * sizeof(int) + size_t(p.use_fp8 ? p.H : p.H * 2) + (p.H / kGroup) * sizeof(float) + 15) & ~size_t(15);
     const size_t smem = size_t(2) * p.E * sizeof(int) + (kThreads / 32) * group_bytes + 16;
     {
         // The shared-memory limit is a per-device function attribute.
