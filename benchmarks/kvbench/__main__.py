@@ -26,8 +26,27 @@ def _parallel(ns):
     return ParallelConfig(tp=ns.tp, pp=ns.pp, cp=ns.cp)
 
 
+def _apply_model_config(ns):
+    """Serving configuration file in the reference's layout (benchmark/kvbench/examples/block-tp8-pp2.yaml)."""
+    import yaml
+
+    with open(ns.model_config) as f:
+        cfg = yaml.safe_load(f) or {}
+    strategy, runtime, system = cfg.get("strategy") or {}, cfg.get("runtime") or {}, cfg.get("system") or {}
+    ns.tp = int(strategy.get("tp_size", ns.tp))
+    ns.pp = int(strategy.get("pp_size", ns.pp))
+    ns.cp = int(strategy.get("cp_size", ns.cp))
+    ns.kvcache_quant = str(strategy.get("kvcache_quant_mode", ns.kvcache_quant) or "")
+    ns.isl = int(runtime.get("isl", ns.isl))
+    ns.num_requests = int(runtime.get("num_requests", ns.num_requests))
+    ns.page_size = int(system.get("page_size", ns.page_size))
+
+
 def _add_model_args(p):
-    p.add_argument("--model", default="llama-3-8b")
+    p.add_argument("--model", default="llama-3-8b", help="built-in model name or architecture YAML (model_name, num_layers, num_query_heads, ...)")
+    p.add_argument("--model_config", "--model-config", dest="model_config", default="",
+                   help="YAML with strategy (tp_size, pp_size, kvcache_quant_mode), runtime (isl, num_requests) and system (page_size); overrides the flags")
+    p.add_argument("--kvcache-quant", default="", help="fp8 | bf16 | fp16 | fp32 (bytes per cached element)")
     p.add_argument("--isl", type=int, default=4096, help="prompt length in tokens")
     p.add_argument("--num-requests", type=int, default=1)
     p.add_argument("--tp", type=int, default=1)
@@ -89,16 +108,18 @@ def main(argv=None):
         sys.argv = ["kv-transfer"] + list(argv[1:])
         return kv_transfer.main()
     ns = ap.parse_args(argv)
+    if getattr(ns, "model_config", ""):
+        _apply_model_config(ns)
 
     if ns.cmd == "kvcache":
         from .plan import kvcache_report
 
-        print(json.dumps(kvcache_report(ns.model, ns.isl, ns.num_requests, _parallel(ns), ns.page_size), indent=1))
+        print(json.dumps(kvcache_report(ns.model, ns.isl, ns.num_requests, _parallel(ns), ns.page_size, ns.kvcache_quant), indent=1))
     elif ns.cmd in ("plan", "profile"):
         from .plan import plan_commands, profile
 
         cmds = plan_commands(ns.model, ns.isl, ns.num_requests, _parallel(ns), ns.page_size, ns.backend, ns.mem, ns.op, ns.src_dev, ns.dst_dev,
-                             ns.iters, ns.extra)
+                             ns.iters, ns.extra, ns.kvcache_quant)
         if ns.cmd == "plan":
             print("\n".join(cmds))
         else:

@@ -13,8 +13,8 @@ ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)
 NIXLBENCH = os.path.join(ROOT, "nixl_b200", "bin", "nixlbench")
 
 
-def kvcache_report(model_name: str, isl: int, requests: int, par: ParallelConfig, page_size: int) -> dict:
-    m = get_model(model_name)
+def kvcache_report(model_name: str, isl: int, requests: int, par: ParallelConfig, page_size: int, kvcache_quant: str = "") -> dict:
+    m = get_model(model_name, kvcache_quant)
     block = m.block_bytes(page_size, par)
     per_gpu = m.kv_bytes_per_gpu(isl, par)
     return {
@@ -33,10 +33,10 @@ def _pow2_floor(n: int) -> int:
 
 
 def plan_commands(model_name: str, isl: int, requests: int, par: ParallelConfig, page_size: int, backend: str = "NVLINK", mem: str = "VRAM",
-                  op: str = "WRITE", src_dev: int = 0, dst_dev: int = 1, iters: int = 200, extra: str = "") -> List[str]:
+                  op: str = "WRITE", src_dev: int = 0, dst_dev: int = 1, iters: int = 200, extra: str = "", kvcache_quant: str = "") -> List[str]:
     """One nixlbench line per access granularity of a KV transfer: block-sized descriptors batched
     per request (what a paged engine posts) and one contiguous layer-sized copy (the upper bound)."""
-    rep = kvcache_report(model_name, isl, requests, par, page_size)
+    rep = kvcache_report(model_name, isl, requests, par, page_size, kvcache_quant)
     block = rep["io_size"]
     blocks_per_request = -(-isl // page_size) * rep["cache_tensors_per_gpu"]
     cmds = []

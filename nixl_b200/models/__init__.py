@@ -7,10 +7,13 @@ benchmark traffic.  Parity: the model files of the reference's kvbench tool
 from .kv_models import (  # noqa: F401
     MODELS,
     DeepSeekV3,
+    GptOss,
     KVModel,
     Llama3,
     ModelConfig,
     ParallelConfig,
+    Qwen3,
     batch_descriptor_count,
     get_model,
+    model_from_yaml,
 )
