@@ -7,6 +7,7 @@
     ct-perftest             time one traffic pattern       (under torchrun, one rank per matrix row)
     sequential-ct-perftest  run a list of patterns in order (under torchrun)
     kv-transfer             fused paged-KV transfer benchmark (under torchrun for more than one GPU)
+    storage-perftest        file <-> buffer reads and writes through the POSIX (host) or GDS (CUDA) backend
 """
 from __future__ import annotations
 
@@ -100,6 +101,14 @@ def main(argv=None):
 
     sub.add_parser("kv-transfer", add_help=False)
 
+    p = sub.add_parser("storage-perftest")
+    p.add_argument("--path", required=True, help="directory for the benchmark files")
+    p.add_argument("--size", default="64M")
+    p.add_argument("--iters", type=int, default=10)
+    p.add_argument("--mem", default="cpu", help="cpu / dram or cuda / vram")
+    p.add_argument("--chunk", default="0", help="bytes per descriptor (0: one descriptor)")
+    p.add_argument("--keep-files", action="store_true")
+
     if argv is None:
         argv = sys.argv[1:]
     if argv and argv[0] == "kv-transfer":
@@ -126,6 +135,11 @@ def main(argv=None):
             for r in profile(cmds):
                 print("$", r["cmd"])
                 print(r["stdout"] or r["stderr"])
+    elif ns.cmd == "storage-perftest":
+        from .storage import storage_perftest
+        from .traffic import parse_size
+
+        print(json.dumps(storage_perftest(ns.path, parse_size(ns.size), ns.iters, ns.mem, parse_size(ns.chunk), keep_files=ns.keep_files)))
     elif ns.cmd == "matgen":
         from nixl_b200.models import ParallelConfig
 

@@ -95,3 +95,38 @@ def test_sequential_ct_perftest_two_ranks_read(tmp_path):
     rows = json.loads(out.read_text())
     assert len(rows) == 2 and rows[0]["num_senders"] == 1 and rows[0]["isolated_latency_ms"] > 0
     assert "Isolated Latency" in r.stdout
+
+
+def test_storage_backend_reads_and_writes_file_regions(tmp_path):
+    import torch
+
+    from benchmarks.kvbench.storage import FilesystemBackend, StorageOp, storage_perftest
+    from nixl_b200 import nixl_agent, nixl_agent_config
+
+    rep = storage_perftest(str(tmp_path / "bench"), 1 << 20, iters=2, mem="cpu", chunk_bytes=1 << 18)
+    assert rep["verified"] and rep["read_GBps"] > 0 and rep["chunk_bytes"] == 1 << 18
+
+    agent = nixl_agent("kvb_store_test", nixl_agent_config(backends=["POSIX"]))
+    fs = FilesystemBackend(agent, str(tmp_path / "ops"))
+    op = StorageOp(str(tmp_path / "ops" / "custom.bin"), file_size=12288, read_offset=4096, read_size=4096, write_offset=8192, write_size=2048)
+    h = fs.prepare(3, 5, op=op)
+    buf = torch.zeros(4096, dtype=torch.uint8)
+    agent.register_memory(buf)
+    rh = fs.get_read_handle(h, buf)
+    assert agent.transfer(rh) in ("DONE", "PROC")
+    while agent.check_xfer_state(rh) == "PROC":
+        pass
+    assert buf[:256].tolist() == [(5 * 31 + i) & 0xFF for i in range(256)]
+    buf[:2048] = 7
+    wh = fs.get_write_handle(h, buf)
+    agent.transfer(wh)
+    while agent.check_xfer_state(wh) == "PROC":
+        pass
+    raw = (tmp_path / "ops" / "custom.bin").read_bytes()
+    assert len(raw) == 12288 and raw[8192:10240] == bytes([7]) * 2048 and raw[:4096] == bytes(4096)
+    import pytest
+
+    with pytest.raises(ValueError):
+        StorageOp("x", 100, read_offset=90, read_size=20)
+    fs.close(remove_files=True)
+    assert not (tmp_path / "ops" / "custom.bin").exists()
