@@ -193,3 +193,35 @@ def test_handles_own_their_native_objects():
     a.release_dlist_handle(side_l)
     del side_r
     gc.collect()
+
+
+def test_raw_buffer_helpers_move_through_an_agent():
+    from nixl_b200 import _utils, nixl_agent, nixl_agent_config
+
+    n = 10000
+    a, b = _utils.malloc_passthru(n), _utils.malloc_passthru(n)
+    assert a % 4096 == 0 and b % 4096 == 0
+    try:
+        _utils.ba_buf(a, n)
+        import ctypes
+
+        ctypes.memset(b, 0, n)
+        with pytest.raises(AssertionError):
+            _utils.verify_transfer(a, b, n)
+        src = nixl_agent("raw_src", nixl_agent_config(backends=["NVLINK"]))
+        dst = nixl_agent("raw_dst", nixl_agent_config(backends=["NVLINK"]))
+        reg_a = src.register_memory([(a, n, 0, "")], "DRAM")
+        reg_b = dst.register_memory([(b, n, 0, "")], "DRAM")
+        src.add_remote_agent(dst.get_agent_metadata())
+        h = src.initialize_xfer("WRITE", src.get_xfer_descs([(a, n, 0)], "DRAM"), src.get_xfer_descs([(b, n, 0)], "DRAM"), "raw_dst")
+        state = src.transfer(h)
+        while state == "PROC":
+            state = src.check_xfer_state(h)
+        assert state == "DONE"
+        _utils.verify_transfer(a, b, n)
+        src.release_xfer_handle(h)
+        src.deregister_memory(reg_a)
+        dst.deregister_memory(reg_b)
+    finally:
+        _utils.free_passthru(a)
+        _utils.free_passthru(b)
