@@ -225,3 +225,18 @@ def test_raw_buffer_helpers_move_through_an_agent():
     finally:
         _utils.free_passthru(a)
         _utils.free_passthru(b)
+
+
+def test_reference_import_names_resolve_to_this_package():
+    import nixl
+    import nixl._bindings as bindings
+    import nixl_ep
+    from nixl._api import nixl_agent, nixl_agent_config
+    from nixl.logging import get_logger
+
+    assert nixl_agent is nixl_b200.nixl_agent and nixl_agent_config is nixl_b200.nixl_agent_config
+    assert bindings is nixl_b200._bindings and hasattr(bindings, "nixlAgent")
+    assert nixl.nixl_agent is nixl_agent and callable(get_logger)
+    assert nixl_ep.Buffer is nixl_b200.parallel.Buffer and hasattr(nixl_ep, "EventOverlap")
+    agent = nixl_agent("via_reference_names", nixl_agent_config(backends=[]))
+    assert "NVLINK" in agent.get_plugin_list()
