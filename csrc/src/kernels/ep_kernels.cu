@@ -489,6 +489,81 @@ __device__ __forceinline__ void logfmtDecodeAdd16(const uint32_t (&w)[5], const 
     }
 }
 
+// The reduction of pull-mode combine for the tokens of this thread group.  KMAX bounds top-k at
+// compile time so that the K rows' 16-byte vectors live in registers.  With kDouble the loads of
+// the next vector position are issued before the current one is reduced: a load from a peer takes
+// microseconds, and without the overlap every position would pay that latency in full.
+template <int KMAX, bool kDouble>
+__device__ __forceinline__ void pullReduce(const NixlEpCombineParams &p, int El, int vecs, int nt, int groups_per_cta, int grp, int gtid) {
+    __nv_bfloat16 *out = static_cast<__nv_bfloat16 *>(p.out);
+    for (int t = blockIdx.x * groups_per_cta + grp; t < p.T; t += gridDim.x * groups_per_cta) {
+        float w[KMAX];
+        const uint4 *src[KMAX];
+#pragma unroll
+        for (int k = 0; k < KMAX; ++k) {
+            w[k] = __int_as_float(0x7fc00000); // NaN marks "skip" (a real weight may be 0)
+            src[k] = nullptr;
+            if (k < p.K) {
+                const long long e = p.topk_idx[static_cast<long long>(t) * p.K + k];
+                const int row = p.send_row[static_cast<long long>(t) * p.K + k];
+                if (e >= 0 && e < p.E && row >= 0) {
+                    const int r = static_cast<int>(e) / El;
+                    char *peer = peerBase(p.peers, r);
+                    if (peer != nullptr && ldVolatile(p.scr.mask + r) == 0) {
+                        w[k] = p.topk_weights[static_cast<long long>(t) * p.K + k];
+                        src[k] = reinterpret_cast<const uint4 *>(peer + p.lay.off_comb_in + static_cast<long long>(row) * p.H * 2);
+                    }
+                }
+            }
+        }
+        auto load = [&](uint4(&buf)[KMAX], int v) {
+#pragma unroll
+            for (int k = 0; k < KMAX; ++k)
+                if (k < p.K && w[k] == w[k]) buf[k] = ldNc(src[k] + v);
+        };
+        auto reduceStore = [&](const uint4(&buf)[KMAX], int v) {
+            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int k = 0; k < KMAX; ++k) {
+                if (k >= p.K || w[k] != w[k]) continue;
+                const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&buf[k]);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float2 f = __bfloat1622float2(h[i]);
+                    acc[2 * i] = fmaf(w[k], f.x, acc[2 * i]);
+                    acc[2 * i + 1] = fmaf(w[k], f.y, acc[2 * i + 1]);
+                }
+            }
+            uint4 o;
+            __nv_bfloat162 *oh = reinterpret_cast<__nv_bfloat162 *>(&o);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) oh[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+            *reinterpret_cast<uint4 *>(out + static_cast<long long>(t) * p.H + v * 8) = o;
+        };
+        if constexpr (kDouble) {
+            uint4 a[KMAX], b[KMAX];
+            int v = gtid;
+            if (v < vecs) load(a, v);
+            while (v < vecs) {
+                const int v1 = v + nt;
+                if (v1 < vecs) load(b, v1);
+                reduceStore(a, v);
+                if (v1 >= vecs) break;
+                const int v2 = v1 + nt;
+                if (v2 < vecs) load(a, v2);
+                reduceStore(b, v1);
+                v = v2;
+            }
+        } else {
+            for (int v = gtid; v < vecs; v += nt) {
+                uint4 raw[KMAX];
+                load(raw, v);
+                reduceStore(raw, v);
+            }
+        }
+    }
+}
+
 // Pull-mode combine: announce that this rank's expert outputs are complete, wait for the same
 // word from every peer, then each token's home rank loads the K rows from where dispatch put
 // them and reduces in fp32.  Every row crosses NVLink once and is never staged.
@@ -513,54 +588,11 @@ __device__ __forceinline__ void epCombinePull(const NixlEpCombineParams &p) {
         }
     }
     __syncthreads();
-    __nv_bfloat16 *out = static_cast<__nv_bfloat16 *>(p.out);
     const int nt = threadsPerItem(p.T);
     const int groups_per_cta = kThreads / nt;
     const int grp = tid / nt, gtid = tid - grp * nt;
-    for (int t = blockIdx.x * groups_per_cta + grp; t < p.T; t += gridDim.x * groups_per_cta) {
-        float w[kMaxTopk];
-        const uint4 *src[kMaxTopk];
-#pragma unroll
-        for (int k = 0; k < kMaxTopk; ++k) {
-            w[k] = __int_as_float(0x7fc00000); // NaN marks "skip" (a real weight may be 0)
-            src[k] = nullptr;
-            if (k < p.K) {
-                const long long e = p.topk_idx[static_cast<long long>(t) * p.K + k];
-                const int row = p.send_row[static_cast<long long>(t) * p.K + k];
-                if (e >= 0 && e < p.E && row >= 0) {
-                    const int r = static_cast<int>(e) / El;
-                    char *peer = peerBase(p.peers, r);
-                    if (peer != nullptr && ldVolatile(p.scr.mask + r) == 0) {
-                        w[k] = p.topk_weights[static_cast<long long>(t) * p.K + k];
-                        src[k] = reinterpret_cast<const uint4 *>(peer + p.lay.off_comb_in + static_cast<long long>(row) * p.H * 2);
-                    }
-                }
-            }
-        }
-        for (int v = gtid; v < vecs; v += nt) {
-            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-            uint4 raw[kMaxTopk];
-#pragma unroll
-            for (int k = 0; k < kMaxTopk; ++k)
-                if (k < p.K && w[k] == w[k]) raw[k] = ldNc(src[k] + v);
-#pragma unroll
-            for (int k = 0; k < kMaxTopk; ++k) {
-                if (k >= p.K || w[k] != w[k]) continue;
-                const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&raw[k]);
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float2 f = __bfloat1622float2(h[i]);
-                    acc[2 * i] = fmaf(w[k], f.x, acc[2 * i]);
-                    acc[2 * i + 1] = fmaf(w[k], f.y, acc[2 * i + 1]);
-                }
-            }
-            uint4 o;
-            __nv_bfloat162 *oh = reinterpret_cast<__nv_bfloat162 *>(&o);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) oh[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
-            *reinterpret_cast<uint4 *>(out + static_cast<long long>(t) * p.H + v * 8) = o;
-        }
-    }
+    if (p.K <= 8) pullReduce<8, true>(p, El, vecs, nt, groups_per_cta, grp, gtid);
+    else pullReduce<kMaxTopk, false>(p, El, vecs, nt, groups_per_cta, grp, gtid);
 }
 
 __global__ void __launch_bounds__(kThreads) epCombineKernel(const __grid_constant__ NixlEpCombineParams p) {
