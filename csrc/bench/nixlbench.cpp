@@ -24,6 +24,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <map>
 #include <string>
 #include <vector>
 
@@ -82,6 +83,8 @@ bool setFlag(Args &a, const std::string &k) {
     else return false;
     return true;
 }
+struct Spelling;
+std::string canonicalName(const std::string &k);
 bool loadConfig(Args &a, const std::string &path) {
     std::ifstream f(path);
     if (!f) return false;
@@ -96,8 +99,7 @@ bool loadConfig(Args &a, const std::string &path) {
         if (line.empty()) continue;
         const size_t eq = line.find('=');
         std::string k = "--" + (eq == std::string::npos ? line : line.substr(0, eq));
-        for (char &c : k)
-            if (c == '_') c = '-';
+        k = canonicalName(k); // underscores, and the reference's long names
         const std::string v = eq == std::string::npos ? "" : line.substr(eq + 1);
         if (eq == std::string::npos || v == "true" || v == "1") {
             if (setFlag(a, k)) continue;
@@ -114,6 +116,49 @@ bool loadConfig(Args &a, const std::string &path) {
     return true;
 }
 
+// Accepts the spellings of the reference's nixlbench (benchmark/nixlbench/src/utils/utils.cpp:
+// gflags names with underscores, `--name=value`) next to this tool's own short ones.
+struct Spelling {
+    enum Kind { OPTION, IGNORED, POSIX_API, PARAM } kind = OPTION;
+    std::string name;  // this tool's option
+    std::string param; // backend parameter for PARAM
+};
+Spelling canonical(std::string k) {
+    for (char &c : k)
+        if (c == '_') c = '-';
+    static const std::map<std::string, std::string> same = {
+        {"--start-block-size", "--min"},     {"--max-block-size", "--max"},       {"--start-batch-size", "--batch"},
+        {"--max-batch-size", "--batch-max"}, {"--num-iter", "--iters"},           {"--warmup-iter", "--warmup"},
+        {"--op-type", "--op"},               {"--initiator-seg-type", "--mem"},   {"--check-consistency", "--check"},
+        {"--total-buffer-size", "--total"},  {"--pipeline-depth", "--depth"},     {"--recreate-xfer", "--recreate"},
+        {"--reregister-mem", "--reregister"}, {"--prepared-xfer", "--prepared"},  {"--config-file", "--config"},
+        {"--filepath", "--file"},            {"--storage-enable-direct", "--direct"},
+    };
+    static const std::map<std::string, std::string> params = {
+        {"--posix-ios-pool-size", "ios_pool_size"}, {"--posix-kernel-queue-size", "kernel_queue_size"},
+        {"--gds-mt-num-threads", "thread_count"},   {"--hf3fs-iopool-size", "iopool_size"},
+        {"--obj-bucket-name", "bucket"},            {"--azure-blob-container-name", "container_name"},
+    };
+    // One process drives both agents here: there is no runtime to rendezvous through, no second
+    // worker type and one initiator / target device each.
+    static const char *ignored[] = {"--runtime-type", "--worker-type", "--etcd-endpoints", "--scheme",       "--mode",
+                                    "--num-threads",  "--enable-pt",   "--progress-threads", "--device-list", "--target-seg-type",
+                                    "--num-initiator-dev", "--num-target-dev", "--large-blk-iter-ftr", "--benchmark-group"};
+    Spelling sp;
+    sp.name = k;
+    if (auto it = same.find(k); it != same.end()) sp.name = it->second;
+    else if (auto pit = params.find(k); pit != params.end()) {
+        sp.kind = Spelling::PARAM;
+        sp.param = pit->second;
+    } else if (k == "--posix-api-type") sp.kind = Spelling::POSIX_API;
+    else
+        for (const char *name : ignored)
+            if (k == name) sp.kind = Spelling::IGNORED;
+    return sp;
+}
+
+std::string canonicalName(const std::string &k) { return canonical(k).name; }
+
 double pct(std::vector<double> &v, double q) {
     if (v.empty()) return 0;
     std::sort(v.begin(), v.end());
@@ -124,17 +169,52 @@ double pct(std::vector<double> &v, double q) {
 int main(int argc, char **argv) {
     Args a;
     for (int i = 1; i < argc; ++i) {
-        const std::string k = argv[i];
-        if (setFlag(a, k)) continue;
-        if (k == "--config") {
-            if (i + 1 >= argc || !loadConfig(a, argv[++i])) return 2;
+        std::string k = argv[i], v;
+        bool has_value = false;
+        if (const size_t eq = k.find('='); eq != std::string::npos && k.rfind("--", 0) == 0) { // --name=value
+            v = k.substr(eq + 1);
+            k.erase(eq);
+            has_value = true;
+        }
+        const Spelling sp = canonical(k);
+        if (sp.kind == Spelling::IGNORED) {
+            std::fprintf(stderr, "note: %s has no effect in this single-process tool\n", k.c_str());
+            if (!has_value && i + 1 < argc && std::strncmp(argv[i + 1], "--", 2) != 0) ++i;
             continue;
         }
-        if (i + 1 >= argc || !setOption(a, k, argv[i + 1])) {
+        k = sp.name;
+        if (has_value && (v == "true" || v == "1") && setFlag(a, k)) continue;
+        if (has_value && (v == "false" || v == "0")) {
+            Args probe;
+            if (setFlag(probe, k)) continue;
+        }
+        if (!has_value && setFlag(a, k)) continue;
+        if (!has_value) {
+            if (i + 1 >= argc) {
+                std::fprintf(stderr, "option %s needs a value\n", k.c_str());
+                return 2;
+            }
+            v = argv[++i];
+        }
+        if (k == "--config") {
+            if (!loadConfig(a, v)) return 2;
+            continue;
+        }
+        if (sp.kind == Spelling::POSIX_API) {
+            const std::string api = v;
+            if (api == "AIO" || api == "aio") a.extra["use_aio"] = "true";
+            else if (api == "URING" || api == "uring") a.extra["use_uring"] = "true";
+            else if (api == "POSIXAIO" || api == "posixaio") a.extra["use_posix_aio"] = "true";
+            continue;
+        }
+        if (sp.kind == Spelling::PARAM) {
+            a.extra[sp.param] = v;
+            continue;
+        }
+        if (!setOption(a, k, v)) {
             std::fprintf(stderr, "unknown option %s\n", k.c_str());
             return 2;
         }
-        ++i;
     }
     const bool vram = a.mem == "VRAM";
     const bool storage = !a.file.empty();

@@ -63,3 +63,21 @@ def test_native_nixlbench_storage_and_config_file(tmp_path):
     assert res.returncode == 0 and len(res.stdout.strip().splitlines()) == 2, res.stdout + res.stderr
     cfg.write_text("no_such_option=1\n")
     assert _nixlbench("--config", str(cfg)).returncode == 2
+
+
+def test_native_nixlbench_accepts_the_reference_spellings(tmp_path):
+    """gflags-style names of the reference's nixlbench (underscores, --name=value) map onto the same options."""
+    res = _nixlbench("--backend", "NVLINK", "--initiator_seg_type=DRAM", "--op_type", "WRITE", "--start_block_size=8192",
+                     "--max_block_size=16384", "--start_batch_size", "2", "--num_iter=20", "--warmup_iter", "2", "--check_consistency",
+                     "--pipeline_depth=2", "--etcd_endpoints", "http://127.0.0.1:2379", "--scheme=pairwise", "--enable_pt")
+    assert res.returncode == 0, res.stdout + res.stderr
+    rows = [l.split() for l in res.stdout.splitlines() if l and l[0].isdigit()]
+    assert [r[0] for r in rows] == ["8192", "16384"] and all(r[1] == "2" for r in rows)
+    assert "no effect" in res.stderr and "--scheme" in res.stderr
+    store = str(tmp_path / "store.bin")
+    res = _nixlbench("--backend=POSIX", "--initiator_seg_type=DRAM", "--filepath", store, "--posix_api_type=URING", "--posix_kernel_queue_size=32",
+                     "--start_block_size=65536", "--max_block_size=65536", "--max_batch_size=8", "--start_batch_size=8", "--num_iter=5",
+                     "--warmup_iter=1", "--op_type=WRITE")
+    assert res.returncode == 0, res.stdout + res.stderr
+    assert os.path.getsize(store) >= 8 * 65536
+    assert _nixlbench("--no_such_option=1").returncode == 2
