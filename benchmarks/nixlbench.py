@@ -30,16 +30,16 @@ from nixl_b200 import nixl_agent, nixl_agent_config  # noqa: E402
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--min-block", type=int, default=4096)
-    ap.add_argument("--max-block", type=int, default=1 << 30)
+    ap.add_argument("--min-block", "--start_block_size", dest="min_block", type=int, default=4096)
+    ap.add_argument("--max-block", "--max_block_size", dest="max_block", type=int, default=1 << 30)
     ap.add_argument("--step", type=int, default=4, help="multiply the block size by this between points")
     ap.add_argument("--batches", default="1,16,256")
-    ap.add_argument("--ops", default="WRITE,READ")
+    ap.add_argument("--ops", "--op_type", dest="ops", default="WRITE,READ")
     ap.add_argument("--patterns", default="ring,alltoall,pairwise")
-    ap.add_argument("--buffer", type=int, default=4 << 30, help="bytes of source and of destination buffer per GPU")
-    ap.add_argument("--iters", type=int, default=0, help="0: chosen per point (more for small messages)")
+    ap.add_argument("--buffer", "--total_buffer_size", dest="buffer", type=int, default=4 << 30, help="bytes of source and of destination buffer per GPU")
+    ap.add_argument("--iters", "--num_iter", dest="iters", type=int, default=0, help="0: chosen per point (more for small messages)")
     ap.add_argument("--copy-path", default="vector")
-    ap.add_argument("--check-consistency", action="store_true")
+    ap.add_argument("--check-consistency", "--check_consistency", dest="check_consistency", action="store_true")
     ap.add_argument("--baselines", type=int, default=1)
     args = ap.parse_args()
 
