@@ -58,7 +58,9 @@ def case_kv():
     torch.cuda.synchronize()
 
 
-def case_ep():
+def case_ep(pull=True):
+    """Throughput dispatch and combine on one rank; the combine reads the exposed buffer (pull, what a
+    pipeline with the expert GEMM in between does) or, as `ep_push`, stores rows to the home rank first."""
     from nixl_b200.parallel import Buffer
 
     T, H, E, K = 1024, 7168, 32, 8
@@ -68,10 +70,14 @@ def case_ep():
     idx, w = idx.long().contiguous(), w.float().contiguous()
     for _ in range(3):
         rx, sc, h = buf.dispatch(x, idx)
-        y = torch.empty(rx.shape[0], H, device="cuda:0", dtype=torch.bfloat16)
+        y = buf.get_next_combine_buffer(h) if pull else torch.empty(rx.shape[0], H, device="cuda:0", dtype=torch.bfloat16)
         buf.combine(y, idx, w, h)
     torch.cuda.synchronize()
     assert buf.status == 0
+
+
+def case_ep_push():
+    case_ep(pull=False)
 
 
 def _gemm_inputs(G=8, N=2048, K=7168, rows_per=1024, pow2=False):
@@ -121,5 +127,5 @@ def case_gemm_mx():
 
 
 if __name__ == "__main__":
-    {"copy": case_copy, "kv": case_kv, "ep": case_ep, "gemm": case_gemm, "gemm_pair": case_gemm_pair, "gemm_mx": case_gemm_mx}[sys.argv[1]]()
+    {"copy": case_copy, "kv": case_kv, "ep": case_ep, "ep_push": case_ep_push, "gemm": case_gemm, "gemm_pair": case_gemm_pair, "gemm_mx": case_gemm_mx}[sys.argv[1]]()
     print("ok", sys.argv[1])
