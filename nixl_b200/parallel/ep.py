@@ -281,7 +281,21 @@ class Buffer:
             "agent": self.agent.name,
             "md": self.agent.get_agent_metadata(),
             "buffer": (self.buffer.data_ptr(), self.buffer.numel(), self.buffer.get_device()),
+            "epoch": self._epoch,
+            "barrier_epoch": self._barrier_epoch,
         }
+
+    @property
+    def epoch(self) -> int:
+        """Number of dispatches issued so far; ranks that talk to each other must agree on it."""
+        return self._epoch
+
+    def set_epoch(self, epoch: int, barrier_epoch: Optional[int] = None) -> None:
+        """Adopt the step counters of a running group (a rank that joins late or comes back after
+        having been disconnected).  ``connect_ranks`` does this itself from the peers' metadata."""
+        self._epoch = int(epoch)
+        if barrier_epoch is not None:
+            self._barrier_epoch = int(barrier_epoch)
 
     def connect_ranks(self, remote_ranks: Optional[Sequence[int]] = None, metadata: Optional[Sequence[dict]] = None) -> None:
         """Make the listed ranks reachable (all ranks by default).
@@ -312,7 +326,11 @@ class Buffer:
             if m["agent"] != self.agent.name:
                 self.agent.add_remote_agent(m["md"])
             self._connected[r] = m["agent"]
-        self._peer_desc = {r: by_rank[r]["buffer"] for r in by_rank}
+        self._peer_desc = {**getattr(self, "_peer_desc", {}), **{r: by_rank[r]["buffer"] for r in by_rank}}
+        # Flags carry the step number: a rank that missed steps (it joins late, or was away) catches up
+        # with the ranks it connects to.  Callers connect between steps, when the live ranks agree.
+        self._epoch = max([self._epoch] + [int(by_rank[r].get("epoch", 0)) for r in wanted if r in by_rank])
+        self._barrier_epoch = max([self._barrier_epoch] + [int(by_rank[r].get("barrier_epoch", 0)) for r in wanted if r in by_rank])
         self._rebuild_view()
         with torch.cuda.device(self.device):
             for r in wanted:

@@ -398,3 +398,79 @@ def test_dispatch_overlapped_with_grouped_gemm_matches_sequential():
             kb = b_rows.sum(dim=1).sort().values
             torch.testing.assert_close(ka, kb, rtol=1e-2, atol=1e-2)
     b.destroy()
+
+
+def _ll_step(bufs, live, xs, idxs, ws, hidden):
+    """One low-latency dispatch + combine on the ranks in `live`; returns their outputs."""
+    res = {}
+    for r in live:
+        b = bufs[r]
+        with torch.cuda.device(b.device):
+            recv, cnt, handle, _, _ = b.low_latency_dispatch(xs[r], idxs[r], use_fp8=False)
+            res[r] = (recv, handle)
+    outs = {}
+    for r in live:
+        b = bufs[r]
+        recv, handle = res[r]
+        with torch.cuda.device(b.device):
+            y = (recv.float() * 0.5).to(torch.bfloat16)
+            outs[r] = b.low_latency_combine(y, idxs[r], ws[r], handle)[0]
+    for r in live:
+        torch.cuda.synchronize(bufs[r].device)
+    return outs
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs (ranks wait on each other)")
+def test_rank_leaves_between_steps_and_rejoins():
+    """Scale down and up again, the scenario of the reference's elastic test: a rank is disconnected
+    between steps (on the host, nothing of it in flight), the others go on without its experts, then
+    it reconnects, catches up with the step counter and takes part again."""
+    n = min(torch.cuda.device_count(), 4)
+    tokens, hidden, topk = 24, 1024, 4
+    experts = 4 * n
+    bufs = _make_ranks(n, experts, hidden, tokens, topk, tag="epel", timeout_ms=3000)
+    xs, idxs, ws = _inputs(bufs, tokens, hidden, experts, topk, seed=77)
+    el = experts // n
+    gone = n - 1
+
+    def expect(r, masked_ranks):
+        want = torch.zeros(tokens, hidden, device=bufs[r].device)
+        yk = (xs[r].float() * 0.5).to(torch.bfloat16).float()
+        for k in range(topk):
+            e = idxs[r][:, k]
+            ok = e >= 0
+            for m in masked_ranks:
+                ok = ok & (torch.div(e.clamp(min=0), el, rounding_mode="floor") != m)
+            want += (ws[r][:, k] * ok.float()).unsqueeze(1) * yk
+        return want.to(torch.bfloat16).float()
+
+    everyone = list(range(n))
+    outs = _ll_step(bufs, everyone, xs, idxs, ws, hidden)
+    for r in everyone:
+        assert bufs[r].status == 0
+        torch.testing.assert_close(outs[r].float(), expect(r, []), rtol=2e-2, atol=2e-2)
+
+    # The last rank leaves: the others learn of it on the host before their next launch.
+    live = everyone[:-1]
+    for r in live:
+        bufs[r].disconnect_ranks([gone])
+    for _ in range(2):
+        outs = _ll_step(bufs, live, xs, idxs, ws, hidden)
+        for r in live:
+            assert bufs[r].status == 0  # nobody waited for the absent rank
+            assert int(bufs[r].query_mask_buffer()[gone]) == 1
+            torch.testing.assert_close(outs[r].float(), expect(r, [gone]), rtol=2e-2, atol=2e-2)
+
+    # It comes back: fresh metadata both ways; the returning rank adopts the others' step counter.
+    md = [b.local_metadata() for b in bufs]
+    assert bufs[gone].epoch < bufs[0].epoch
+    for r in live:
+        bufs[r].connect_ranks([gone], metadata=md)
+    bufs[gone].connect_ranks(live, metadata=md)
+    assert bufs[gone].epoch == bufs[0].epoch
+    outs = _ll_step(bufs, everyone, xs, idxs, ws, hidden)
+    for r in everyone:
+        assert bufs[r].status == 0 and int(bufs[r].query_mask_buffer().sum()) == 0
+        torch.testing.assert_close(outs[r].float(), expect(r, []), rtol=2e-2, atol=2e-2)
+    for b in bufs:
+        b.destroy()
