@@ -123,6 +123,28 @@ def wait_done(agent, handle):
             raise RuntimeError("transfer did not complete")
 
 
+def _roofline(world: int, aggregate_gbs: float) -> dict:
+    """What bounds the step and how close the run came.  One GPU copies inside its own HBM (bound: the
+    measured copy bandwidth, read + write counted, halved for one-way bytes); two or more GPUs write
+    to a neighbour over NVLink (bound: the measured 770 GB/s peer copy per direction per GPU).  The
+    per-GPU figure therefore drops from N = 1 to N = 2 by the ratio of those two bounds, not by a
+    loss of scaling."""
+    hbm = 6650.0
+    source = "fallback"
+    try:
+        with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")) as f:
+            hbm = float(json.load(f)["hbm_gbs"])
+            source = "measured"
+    except Exception:
+        pass
+    per_gpu = aggregate_gbs / world
+    if world == 1:
+        bound, what = hbm / 2, f"HBM copy, one-way bytes ({source} {hbm:.0f} GB/s read + write)"
+    else:
+        bound, what = 770.0, "NVLink peer copy per direction per GPU (measured 770 GB/s; SM-issued stores reach 711)"
+    return {"bound": what, "bound_GBps_per_gpu": round(bound, 1), "GBps_per_gpu": round(per_gpu, 1), "fraction_of_bound": round(per_gpu / bound, 3)}
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
@@ -297,6 +319,7 @@ def main():
                 "copy_path": args.copy_path,
                 "l2": "inputs larger than L2 (1 GiB source and destination per GPU); no flush needed",
                 "timing": "CUDA events on the launching stream, max over ranks",
+                "roofline": _roofline(world, gbs),
             },
             "clocks": clocks,
             "e2e": {
