@@ -29,3 +29,42 @@ def test_cpp_example_builds_and_runs(tmp_path):
     assert build.returncode == 0, build.stderr[-3000:]
     res = subprocess.run([exe], capture_output=True, text=True, timeout=120)
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
+
+
+def test_cpp_telemetry_reader_drains_a_ring_written_by_an_agent(tmp_path):
+    exe = str(tmp_path / "telemetry_reader")
+    build = subprocess.run(["g++", "-std=c++20", "-O1", "-I" + os.path.join(ROOT, "csrc", "include"),
+                            os.path.join(ROOT, "examples", "cpp", "telemetry_reader.cpp"), "-o", exe, "-pthread"], capture_output=True, text=True, timeout=300)
+    assert build.returncode == 0, build.stderr[-3000:]
+    tdir = tmp_path / "telemetry"
+    tdir.mkdir()
+    env = dict(os.environ, NIXL_TELEMETRY_ENABLE="1", NIXL_TELEMETRY_DIR=str(tdir), NIXL_TELEMETRY_RUN_INTERVAL="20", PYTHONPATH=ROOT)
+    # The ring lives as long as its agent: the writer moves 4 MiB, says so, and waits for a line on stdin.
+    code = (
+        "import sys, time, torch\n"
+        "from nixl_b200 import nixl_agent, nixl_agent_config\n"
+        "a = nixl_agent('initiator', nixl_agent_config(backends=['NVLINK']))\n"
+        "b = nixl_agent('target', nixl_agent_config(backends=['NVLINK']))\n"
+        "s, d = torch.ones(1 << 20), torch.zeros(1 << 20)\n"
+        "a.register_memory(s); b.register_memory(d)\n"
+        "a.add_remote_agent(b.get_agent_metadata())\n"
+        "h = a.initialize_xfer('WRITE', s, d, 'target')\n"
+        "st = a.transfer(h)\n"
+        "while st == 'PROC': st = a.check_xfer_state(h)\n"
+        "time.sleep(0.3)\n"
+        "print('moved', flush=True)\n"
+        "sys.stdin.readline()\n"
+    )
+    writer = subprocess.Popen([sys.executable, "-c", code], env=env, stdin=subprocess.PIPE, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+    try:
+        assert writer.stdout.readline().strip() == "moved", writer.stderr.read()[-2000:]
+        res = subprocess.run([exe, str(tdir / "initiator")], capture_output=True, text=True, timeout=60)
+        assert res.returncode == 0, res.stdout + res.stderr
+        assert "agent_tx_bytes 4194304" in res.stdout and "agent_memory_registered" in res.stdout
+        # The ring was consumed: a second pass finds nothing new.
+        again = subprocess.run([exe, str(tdir / "initiator")], capture_output=True, text=True, timeout=60)
+        assert "# 0 events" in again.stdout
+    finally:
+        writer.stdin.write("\n")
+        writer.stdin.close()
+        writer.wait(timeout=60)
