@@ -14,6 +14,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     ("partial_md_example.py", []),
     ("query_mem_example.py", []),
     ("nixl_gds_example.py", ["--mib", "2"]),
+    ("metadata_store_example.py", []),
 ])
 def test_example_runs(script, args):
     res = subprocess.run([sys.executable, os.path.join(ROOT, "examples", script), *args], capture_output=True, text=True, timeout=300)
