@@ -19,6 +19,9 @@
  *     NIXL_KV_STATIC_ERR_TOO_LARGE and a message on stderr.  Split them into several calls.
  *   - The first call on each GPU looks up the device address of the scratch area (a one-time
  *     set-up that talks to the driver).  Make that first call before any stream capture.
+ *   - Do not call it while a stream is being captured at all: every call copies the block
+ *     tables from the caller's host memory, which capture forbids for pageable memory and, for
+ *     pinned memory, would freeze the table contents of that one call into the graph.
  *   - All calls on one GPU share the one scratch area, and it keeps what the previous call
  *     left there.  The entry point clears the counter and overwrites the tables itself, in
  *     stream order, so back-to-back calls on ONE stream are safe.  Calls whose work can
@@ -31,8 +34,8 @@
  *     when pinned.
  * The entry point calls neither cudaMalloc nor cudaFree nor any allocating library routine.
  */
-#ifndef NIXL_B200_KV_XFER_STATIC_H
-#define NIXL_B200_KV_XFER_STATIC_H
+#ifndef NIXL_B200_NIXL_KV_XFER_STATIC_H
+#define NIXL_B200_NIXL_KV_XFER_STATIC_H
 
 #include "kernels/nixl_kernels.h"
 

@@ -13,6 +13,7 @@
 #include <tuple>
 
 #include "core/agent_data.h"
+#include "core/plugin_manager.h"
 #include "nixl.h"
 #include "serdes/serdes.h"
 
@@ -76,6 +77,10 @@ py::dict paramsToDict(const nixl_b_params_t &p) {
 
 PYBIND11_MODULE(_bindings, m) {
     m.doc() = "Native bindings of the B200 transfer library (NIXL-compatible API)";
+
+    // Plug-in search path of the process (the manager is a singleton shared by all agents).
+    m.def("add_plugin_directory", [](const std::string &dir) { nixlPluginManager::getInstance().addPluginDirectory(dir); });
+    m.def("get_plugin_directories", [] { return nixlPluginManager::getInstance().getPluginDirectories(); });
 
     m.attr("DRAM_SEG") = static_cast<int>(DRAM_SEG);
     m.attr("VRAM_SEG") = static_cast<int>(VRAM_SEG);

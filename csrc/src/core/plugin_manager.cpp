@@ -105,7 +105,11 @@ nixl_backend_t nixlPluginManager::resolveAlias(const nixl_backend_t &name) const
     // A real plugin of that name always wins over the alias.
     if (loaded_.count(name) || statics_.count(name) || !findFile(kBackendPrefix + name + kSuffix).empty()) return name;
     auto it = aliases_.find(name);
-    return it == aliases_.end() ? name : it->second;
+    if (it == aliases_.end()) return name;
+    if (aliasWarned_.insert(name).second)
+        NIXL_WARN << "backend name '" << name << "' has no plug-in in this build; it resolves to '" << it->second
+                  << "' (transfers inside one NVLink domain only)";
+    return it->second;
 }
 
 void nixlPluginManager::registerStaticBackend(const nixl_backend_t &name, nixlStaticPluginCreatorFunc creator) {

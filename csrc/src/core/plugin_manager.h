@@ -11,6 +11,7 @@
 #define NIXL_B200_PLUGIN_MANAGER_H
 
 #include <map>
+#include <set>
 #include <memory>
 #include <mutex>
 #include <string>
@@ -87,6 +88,7 @@ private:
     std::map<nixl_backend_t, std::shared_ptr<const nixlPluginHandle>> loaded_;
     std::map<nixl_backend_t, nixlStaticPluginCreatorFunc> statics_;
     std::map<nixl_backend_t, nixl_backend_t> aliases_;
+    mutable std::set<nixl_backend_t> aliasWarned_; // one WARN per aliased name
 };
 
 #endif

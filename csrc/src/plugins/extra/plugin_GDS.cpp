@@ -7,6 +7,9 @@
 // bounce buffer plus cudaMemcpy.  This engine is exactly that path, written out: each worker
 // streams a descriptor through two pinned staging buffers so the file I/O of chunk i+1
 // overlaps the PCIe copy of chunk i.  Host memory goes through pread/pwrite directly.
+#ifndef NIXL_GDS_PLUGIN_NAME
+#define NIXL_GDS_PLUGIN_NAME "GDS"
+#endif
 #include <cerrno>
 #include <cstring>
 #include <unistd.h>
@@ -118,6 +121,8 @@ int stagedIo(const Io &io) {
 class GdsEngine final : public nixlBackendEngine {
 public:
     explicit GdsEngine(const nixlBackendInitParams *p) : nixlBackendEngine(p) {
+        if (std::strcmp(NIXL_GDS_PLUGIN_NAME, "GDS") != 0)
+            NIXL_WARN << NIXL_GDS_PLUGIN_NAME << " backend: served by the staged-copy GDS engine of this build (same worker pool, no cuFile thread pool)";
         std::string v;
         unsigned threads = 4;
         if (getInitParam("thread_count", v) == NIXL_SUCCESS && std::atoi(v.c_str()) > 0) threads = static_cast<unsigned>(std::atoi(v.c_str()));
@@ -225,10 +230,6 @@ private:
 };
 
 } // namespace
-
-#ifndef NIXL_GDS_PLUGIN_NAME
-#define NIXL_GDS_PLUGIN_NAME "GDS"
-#endif
 
 extern "C" NIXL_PLUGIN_EXPORT nixlBackendPlugin *nixl_plugin_init() {
     return nixlBackendPluginCreator<GdsEngine>::create(

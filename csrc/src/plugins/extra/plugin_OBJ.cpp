@@ -80,6 +80,8 @@ int objectIo(const ObjIo &io) {
 class ObjEngine final : public nixlBackendEngine {
 public:
     explicit ObjEngine(const nixlBackendInitParams *p) : nixlBackendEngine(p) {
+        if (std::strcmp(NIXL_OBJ_PLUGIN_NAME, "OBJ") != 0)
+            NIXL_WARN << NIXL_OBJ_PLUGIN_NAME << " backend: this build has no client for that service; objects are files in a local directory";
         std::string v;
         if (getInitParam(NIXL_OBJ_BUCKET_PARAM, v) == NIXL_SUCCESS && !v.empty()) dir_ = v;
         else if (const char *e = std::getenv("NIXL_OBJ_BUCKET_DIR")) dir_ = e;

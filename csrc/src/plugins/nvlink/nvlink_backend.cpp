@@ -49,7 +49,8 @@ std::unordered_map<std::string, Engine *> g_registry;
 struct IpcMapping {
     void *base = nullptr;
     int refs = 0;
-    int device = -1;
+    int device = -1;     // device that was current when the handle was opened
+    int ownerLocal = -1; // local ordinal of the GPU that owns the memory
 };
 std::mutex g_ipcMu;
 std::unordered_map<std::string, IpcMapping> g_ipc;
@@ -242,6 +243,36 @@ void DeviceArena::free(void *p) {
     }
 }
 
+// ================================================================ FlagPool
+
+FlagPool::~FlagPool() {
+    for (uint64_t *p : pages_) cudaFreeHost(p);
+}
+
+uint64_t *FlagPool::acquire() {
+    std::lock_guard<std::mutex> g(mu_);
+    if (free_.empty()) {
+        void *page = nullptr;
+        if (!cudaOk(cudaHostAlloc(&page, kWordsPerPage * sizeof(uint64_t), cudaHostAllocMapped | cudaHostAllocPortable), "cudaHostAlloc(flags)"))
+            return nullptr;
+        std::memset(page, 0, kWordsPerPage * sizeof(uint64_t));
+        auto *w = static_cast<uint64_t *>(page);
+        pages_.push_back(w);
+        free_.reserve(free_.size() + kWordsPerPage);
+        for (size_t i = kWordsPerPage; i-- > 0;) free_.push_back(w + i);
+    }
+    uint64_t *w = free_.back();
+    free_.pop_back();
+    *w = 0;
+    return w;
+}
+
+void FlagPool::release(uint64_t *w) {
+    if (!w) return;
+    std::lock_guard<std::mutex> g(mu_);
+    free_.push_back(w);
+}
+
 // ================================================================ Engine: lifecycle
 
 Engine::Engine(const nixlBackendInitParams *init) : nixlBackendEngine(init) {
@@ -271,6 +302,7 @@ Engine::Engine(const nixlBackendInitParams *init) : nixlBackendEngine(init) {
     gridOverride_ = static_cast<int>(paramLong(params, "grid_ctas", 0));
     chunkShiftOverride_ = static_cast<int>(paramLong(params, "chunk_shift", 0));
     livenessPing_ = paramBool(params, "liveness_ping", false);
+    numStreams_ = static_cast<int>(std::min<long>(32, std::max<long>(1, paramLong(params, "num_streams", 4))));
     const long dev = paramLong(params, "device_id", -1);
     if (dev >= 0) primaryDevice_ = static_cast<int>(dev);
 
@@ -318,17 +350,14 @@ Engine::~Engine() {
     for (auto &c : ctxs_) {
         if (!c) continue;
         DeviceScope ds(c->device);
-        if (c->stream) {
-            cudaStreamSynchronize(c->stream);
-            cudaStreamDestroy(c->stream);
+        for (cudaStream_t st : c->streams) {
+            cudaStreamSynchronize(st);
+            cudaStreamDestroy(st);
         }
         if (c->prepStream) cudaStreamDestroy(c->prepStream);
         c->arena.reset();
-        if (c->flags) cudaFreeHost(c->flags);
     }
 }
-
-constexpr int kFlagSlots = 4096;
 
 DeviceCtx *Engine::ctx(int device) const {
     if (!cuda_ || device < 0 || device >= deviceCount_) return nullptr;
@@ -338,14 +367,14 @@ DeviceCtx *Engine::ctx(int device) const {
     DeviceScope ds(device);
     auto c = std::make_unique<DeviceCtx>();
     c->device = device;
-    if (!cudaOk(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking), "cudaStreamCreate")) return nullptr;
+    // Independent requests of one agent run side by side: each prepared request is bound to one
+    // of numStreams_ streams (the role of the reference's worker split, ucx_backend.cpp:653-754).
+    for (int i = 0; i < numStreams_; ++i) {
+        cudaStream_t st = nullptr;
+        if (!cudaOk(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking), "cudaStreamCreate")) return nullptr;
+        c->streams.push_back(st);
+    }
     if (!cudaOk(cudaStreamCreateWithFlags(&c->prepStream, cudaStreamNonBlocking), "cudaStreamCreate")) return nullptr;
-    void *flags = nullptr;
-    if (!cudaOk(cudaHostAlloc(&flags, kFlagSlots * sizeof(uint64_t), cudaHostAllocMapped | cudaHostAllocPortable), "cudaHostAlloc"))
-        return nullptr;
-    std::memset(flags, 0, kFlagSlots * sizeof(uint64_t));
-    c->flags = static_cast<uint64_t *>(flags);
-    for (int i = kFlagSlots - 1; i >= 0; --i) c->freeFlags.push_back(i);
     c->arena = std::make_unique<DeviceArena>(device);
     c->gridCtas = gridOverride_ > 0 ? gridOverride_ : defaultGridCtas(device);
     c->smCount = 148;
@@ -478,28 +507,33 @@ nixl_status_t Engine::loadRemoteConnInfo(const std::string &remote_agent, const 
         return NIXL_ERR_NOT_SUPPORTED;
     }
     std::lock_guard<std::mutex> g(peersMu_);
-    peers_[remote_agent] = p;
+    peers_[remote_agent] = std::make_shared<const PeerId>(std::move(p));
+    ++peersGen_;
     return NIXL_SUCCESS;
+}
+
+std::shared_ptr<const PeerId> Engine::findPeer(const std::string &agent, uint64_t *gen) const {
+    std::lock_guard<std::mutex> g(peersMu_);
+    if (gen) *gen = peersGen_.load(std::memory_order_relaxed);
+    auto it = peers_.find(agent);
+    return it == peers_.end() ? nullptr : it->second;
 }
 
 nixl_status_t Engine::connect(const std::string &remote_agent) {
     if (remote_agent == self_.agent) {
         std::lock_guard<std::mutex> g(peersMu_);
-        peers_[remote_agent] = self_;
+        peers_[remote_agent] = std::make_shared<const PeerId>(self_);
+        ++peersGen_;
         return NIXL_SUCCESS;
     }
-    PeerId p;
-    {
-        std::lock_guard<std::mutex> g(peersMu_);
-        auto it = peers_.find(remote_agent);
-        if (it == peers_.end()) return NIXL_ERR_NOT_FOUND;
-        p = it->second;
-    }
-    return peerAlive(p) ? NIXL_SUCCESS : NIXL_ERR_REMOTE_DISCONNECT;
+    auto p = findPeer(remote_agent);
+    if (!p) return NIXL_ERR_NOT_FOUND;
+    return peerAlive(*p, true) ? NIXL_SUCCESS : NIXL_ERR_REMOTE_DISCONNECT;
 }
 
 nixl_status_t Engine::disconnect(const std::string &remote_agent) {
     std::lock_guard<std::mutex> g(peersMu_);
+    ++peersGen_;
     return peers_.erase(remote_agent) ? NIXL_SUCCESS : NIXL_ERR_NOT_FOUND;
 }
 
@@ -509,13 +543,9 @@ nixl_status_t Engine::loadRemoteMD(const nixlBlobDesc &input, const nixl_mem_t &
     PubReg pub;
     std::memcpy(&pub, input.metaInfo.data(), sizeof(pub));
     if (pub.version != kPubVersion || pub.mem != static_cast<uint8_t>(nixl_mem)) return NIXL_ERR_MISMATCH;
-    PeerId peer;
-    {
-        std::lock_guard<std::mutex> g(peersMu_);
-        auto it = peers_.find(remote_agent);
-        if (it == peers_.end()) return NIXL_ERR_NOT_FOUND;
-        peer = it->second;
-    }
+    auto peerp = findPeer(remote_agent);
+    if (!peerp) return NIXL_ERR_NOT_FOUND;
+    const PeerId &peer = *peerp;
     auto md = std::make_unique<RemoteMD>();
     md->agent = remote_agent;
     md->mem = nixl_mem;
@@ -525,8 +555,10 @@ nixl_status_t Engine::loadRemoteMD(const nixlBlobDesc &input, const nixl_mem_t &
     md->ownerPid = peer.pid;
     md->sameProcess = peer.pid == self_.pid && peer.procTag == self_.procTag;
     if (md->sameProcess) {
-        if (nixl_mem == VRAM_SEG) md->devVisible = pub.addr;
-        else if (cuda_) {
+        if (nixl_mem == VRAM_SEG) {
+            md->devVisible = pub.addr;
+            md->ownerLocalDevice = pub.device;
+        } else if (cuda_) {
             void *dp = nullptr; // pinned by its owner? then kernels can touch it
             if (cudaHostGetDevicePointer(&dp, reinterpret_cast<void *>(pub.addr), 0) == cudaSuccess)
                 md->devVisible = reinterpret_cast<uintptr_t>(dp);
@@ -549,10 +581,16 @@ nixl_status_t Engine::loadRemoteMD(const nixlBlobDesc &input, const nixl_mem_t &
             }
             m.base = base;
             m.device = dev;
+            // Which of THIS process's ordinals owns the memory (the exporter may number its GPUs
+            // differently): kernels launched from any other local GPU need peer access to it.
+            cudaPointerAttributes attr{};
+            if (cudaPointerGetAttributes(&attr, base) == cudaSuccess && attr.type == cudaMemoryTypeDevice) m.ownerLocal = attr.device;
+            else cudaGetLastError();
         }
         ++m.refs;
         md->ipcKey = key;
         md->mapDevice = m.device;
+        md->ownerLocalDevice = m.ownerLocal;
         md->devVisible = reinterpret_cast<uintptr_t>(m.base) + pub.ipcOffset;
     }
     output = md.release();
@@ -603,28 +641,70 @@ void Engine::freeBatch(KernelBatch &b) const {
         DeviceScope ds(b.device);
         cudaEventDestroy(b.uploaded);
     }
-    if (b.flagSlot >= 0) {
-        std::lock_guard<std::mutex> g(c->mu);
-        c->freeFlags.push_back(b.flagSlot);
-    }
+    c->flags.release(b.flag);
     b.table = nullptr;
     b.counter = nullptr;
     b.uploaded = nullptr;
-    b.flagSlot = -1;
+    b.flag = nullptr;
+}
+
+// Frees a request whatever state it is in.  A launched copy kernel still reads the request's
+// descriptor table and writes its counter and completion word, on whichever stream it was
+// posted (the engine's or the caller's), so the completion word itself is what is waited on;
+// only if it does not turn within ten seconds is the whole device synchronised instead.
+void Engine::destroyReq(ReqH *req) const {
+    {
+        std::lock_guard<std::mutex> g(req->mu);
+        for (auto &b : req->kernels) {
+            if (b.inFlight && b.flag) {
+                const auto t0 = std::chrono::steady_clock::now();
+                bool done = false;
+                for (uint32_t spins = 0;; ++spins) {
+                    const uint64_t v = *reinterpret_cast<volatile uint64_t *>(b.flag);
+                    if ((v & 0x7fffffffffffffffull) == b.seq) {
+                        done = true;
+                        break;
+                    }
+                    if ((spins & 1023u) == 1023u) {
+                        if (std::chrono::steady_clock::now() - t0 > std::chrono::seconds(10)) break;
+                        std::this_thread::yield();
+                    }
+                }
+                if (!done) {
+                    DeviceScope ds(b.device);
+                    if (cudaDeviceSynchronize() != cudaSuccess) cudaGetLastError();
+                }
+                b.inFlight = false;
+            }
+            freeBatch(b);
+        }
+        for (auto &e : req->asyncEvents) {
+            DeviceScope ds(e.first);
+            if (req->asyncInFlight) cudaEventSynchronize(e.second);
+            cudaEventDestroy(e.second);
+        }
+    }
+    delete req;
 }
 
 nixl_status_t Engine::prepXfer(const nixl_xfer_op_t &operation, const nixl_meta_dlist_t &local, const nixl_meta_dlist_t &remote,
                                const std::string &remote_agent, nixlBackendReqH *&handle, const nixl_opt_b_args_t *) const {
     if (local.descCount() != remote.descCount() || local.isEmpty()) return NIXL_ERR_INVALID_PARAM;
-    auto req = std::make_unique<ReqH>();
+    ReqH *req = new ReqH();
+    // Every early return hands back what the request already holds (completion words, arena blocks, events).
+    auto fail = [&](nixl_status_t st) {
+        destroyReq(req);
+        return st;
+    };
     req->op = operation;
     req->remoteAgent = remote_agent;
+    req->peer = findPeer(remote_agent, &req->peerGen);
     std::map<int, std::vector<XferDesc>> perDevice;
 
     for (int i = 0; i < local.descCount(); ++i) {
         auto *l = dynamic_cast<LocalMD *>(local[i].metadataP);
         auto *r = dynamic_cast<RemoteMD *>(remote[i].metadataP);
-        if (!l || !r || local[i].len != remote[i].len) return NIXL_ERR_INVALID_PARAM;
+        if (!l || !r || local[i].len != remote[i].len) return fail(NIXL_ERR_INVALID_PARAM);
         const size_t len = local[i].len;
         if (len == 0) continue;
         req->totalBytes += len;
@@ -644,15 +724,18 @@ nixl_status_t Engine::prepXfer(const nixl_xfer_op_t &operation, const nixl_meta_
             }
             continue;
         }
-        if (!cuda_) return NIXL_ERR_NOT_SUPPORTED;
+        if (!cuda_) return fail(NIXL_ERR_NOT_SUPPORTED);
         if (lvis && rvis) { // the copy kernel can see both ends
             int dev;
             if (l->mem == VRAM_SEG) dev = l->device;
             else dev = r->sameProcess ? r->ownerDevice : r->mapDevice;
-            if (dev < 0) return NIXL_ERR_BACKEND;
-            if (r->mem == VRAM_SEG && r->sameProcess && !ensurePeerAccess(dev, r->ownerDevice)) {
-                NIXL_ERROR << "NVLINK backend: GPU " << dev << " cannot access GPU " << r->ownerDevice;
-                return NIXL_ERR_BACKEND;
+            if (dev < 0) return fail(NIXL_ERR_BACKEND);
+            // The launching GPU needs peer access to the GPU that owns the remote memory.  For
+            // another process's memory the IPC mapping enabled it for the device that opened the
+            // handle only; a process driving several GPUs launches from others too.
+            if (r->mem == VRAM_SEG && r->ownerLocalDevice >= 0 && !ensurePeerAccess(dev, r->ownerLocalDevice)) {
+                NIXL_ERROR << "NVLINK backend: GPU " << dev << " cannot access GPU " << r->ownerLocalDevice;
+                return fail(NIXL_ERR_NOT_SUPPORTED);
             }
             XferDesc d;
             d.src = operation == NIXL_WRITE ? lvis : rvis;
@@ -675,16 +758,18 @@ nixl_status_t Engine::prepXfer(const nixl_xfer_op_t &operation, const nixl_meta_
         }
         NIXL_ERROR << "NVLINK backend: no path between local " << nixlEnumStrings::memTypeStr(l->mem) << " and remote "
                    << nixlEnumStrings::memTypeStr(r->mem) << " of agent " << remote_agent
-                   << (r->sameProcess ? "" : " (other process; its VRAM must be cudaMalloc memory, its DRAM is reachable from DRAM only)");
-        return NIXL_ERR_NOT_SUPPORTED;
+                   << (r->sameProcess ? "" : " (other process; its VRAM must be exportable device memory, its DRAM is reachable from DRAM only)");
+        return fail(NIXL_ERR_NOT_SUPPORTED);
     }
 
     for (auto &kv : perDevice) {
         DeviceCtx *c = ctx(kv.first);
-        if (!c) return NIXL_ERR_BACKEND;
-        KernelBatch b;
+        if (!c) return fail(NIXL_ERR_BACKEND);
+        req->kernels.emplace_back();
+        KernelBatch &b = req->kernels.back(); // owned by the request from here on: fail() frees it
         b.device = kv.first;
         b.descs = std::move(kv.second);
+        b.stream = c->streams[c->nextStream.fetch_add(1, std::memory_order_relaxed) % c->streams.size()];
         uint64_t total = 0, longest = 0;
         for (auto &d : b.descs) {
             total += d.len;
@@ -703,27 +788,17 @@ nixl_status_t Engine::prepXfer(const nixl_xfer_op_t &operation, const nixl_meta_
         for (size_t i = 0; i < n; ++i) {
             starts[i] = static_cast<uint32_t>(chunks);
             chunks += (b.descs[i].len + (uint64_t(1) << shift) - 1) >> shift;
-            while (chunks > 0x7fffffffull) { // cannot happen below 2^31 * 16 KiB, but stay safe
-                return NIXL_ERR_INVALID_PARAM;
-            }
+            if (chunks > 0x7fffffffull) return fail(NIXL_ERR_INVALID_PARAM); // cannot happen below 2^31 * 16 KiB, but stay safe
         }
         starts[n] = static_cast<uint32_t>(chunks);
         b.launch.nDescs = static_cast<uint32_t>(n);
         b.launch.totalChunks = static_cast<uint32_t>(chunks);
         b.launch.chunkShift = shift;
-        {
-            std::lock_guard<std::mutex> g(c->mu);
-            if (c->freeFlags.empty()) return NIXL_ERR_BACKEND;
-            b.flagSlot = c->freeFlags.back();
-            c->freeFlags.pop_back();
-        }
-        c->flags[b.flagSlot] = 0;
-        b.launch.hostFlag = c->flags + b.flagSlot; // UVA: the pinned allocation's host address is device-visible
-        b.counter = static_cast<unsigned int *>(c->arena->alloc(256));
-        if (!b.counter) {
-            freeBatch(b);
-            return NIXL_ERR_BACKEND;
-        }
+        b.flag = c->flags.acquire();
+        if (!b.flag) return fail(NIXL_ERR_BACKEND);
+        b.launch.hostFlag = b.flag; // UVA: the pinned allocation's host address is device-visible
+        b.counter = static_cast<unsigned int *>(c->arena->alloc(sizeof(unsigned int)));
+        if (!b.counter) return fail(NIXL_ERR_BACKEND);
         b.launch.doneCounter = b.counter;
         if (n <= static_cast<size_t>(kInlineDescs)) {
             b.launch.table = nullptr;
@@ -734,10 +809,7 @@ nixl_status_t Engine::prepXfer(const nixl_xfer_op_t &operation, const nixl_meta_
             const size_t tbytes = n * sizeof(XferDesc), sbytes = (n + 1) * sizeof(uint32_t);
             const size_t toff = 0, soff = (tbytes + 15) & ~size_t(15);
             b.table = c->arena->alloc(soff + sbytes);
-            if (!b.table) {
-                freeBatch(b);
-                return NIXL_ERR_BACKEND;
-            }
+            if (!b.table) return fail(NIXL_ERR_BACKEND);
             DeviceScope ds(b.device);
             char *base = static_cast<char *>(b.table);
             // Pageable source: the runtime copies it out before returning, so the vectors may die.
@@ -745,36 +817,39 @@ nixl_status_t Engine::prepXfer(const nixl_xfer_op_t &operation, const nixl_meta_
             ok = ok && cudaOk(cudaMemcpyAsync(base + soff, starts.data(), sbytes, cudaMemcpyHostToDevice, c->prepStream), "table upload");
             ok = ok && cudaOk(cudaEventCreateWithFlags(&b.uploaded, cudaEventDisableTiming), "cudaEventCreate");
             ok = ok && cudaOk(cudaEventRecord(b.uploaded, c->prepStream), "cudaEventRecord");
-            if (!ok) {
-                freeBatch(b);
-                return NIXL_ERR_BACKEND;
-            }
+            if (!ok) return fail(NIXL_ERR_BACKEND);
             b.launch.table = reinterpret_cast<const XferDesc *>(base + toff);
             b.launch.chunkStart = reinterpret_cast<const uint32_t *>(base + soff);
         }
-        req->kernels.push_back(std::move(b));
+        // The host copy of the descriptors has served its purpose (they sit in the launch
+        // parameters or in the device table).
+        std::vector<XferDesc>().swap(b.descs);
     }
     for (auto &a : req->asyncCopies) {
         bool have = false;
         for (auto &e : req->asyncEvents) have |= e.first == a.device;
         if (have) continue;
-        if (!ctx(a.device)) return NIXL_ERR_BACKEND;
+        if (!ctx(a.device)) return fail(NIXL_ERR_BACKEND);
         DeviceScope ds(a.device);
         cudaEvent_t ev = nullptr;
-        if (!cudaOk(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming), "cudaEventCreate")) return NIXL_ERR_BACKEND;
+        if (!cudaOk(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming), "cudaEventCreate")) return fail(NIXL_ERR_BACKEND);
         req->asyncEvents.emplace_back(a.device, ev);
     }
-    handle = req.release();
+    handle = req;
     return NIXL_SUCCESS;
 }
 
-bool Engine::peerAlive(const PeerId &peer) const {
+// Liveness of a peer, host side only.  Same process: the engine registry.  Other process:
+// kill(pid, 0); callers on the post path pass force = false unless their last look is older
+// than a millisecond, so a stream of small posts does not pay a system call each.
+bool Engine::peerAlive(const PeerId &peer, bool force) const {
     if (peer.engineTag == self_.engineTag) return true;
     if (peer.pid == self_.pid && peer.procTag == self_.procTag) {
         std::lock_guard<std::mutex> g(g_regMu);
         auto it = g_registry.find(peer.agent);
         return it != g_registry.end() && it->second->engineTag() == peer.engineTag;
     }
+    if (!force) return true;
     if (::kill(static_cast<pid_t>(peer.pid), 0) != 0 && errno == ESRCH) return false;
     if (livenessPing_) {
         socklen_t alen = 0;
@@ -790,18 +865,25 @@ nixl_status_t Engine::postXfer(const nixl_xfer_op_t &operation, const nixl_meta_
                                const std::string &remote_agent, nixlBackendReqH *&handle, const nixl_opt_b_args_t *opt_args) const {
     auto *req = dynamic_cast<ReqH *>(handle);
     if (!req || req->op != operation) return NIXL_ERR_INVALID_PARAM;
-    PeerId peer;
-    {
-        std::lock_guard<std::mutex> g(peersMu_);
-        auto it = peers_.find(remote_agent);
-        if (it == peers_.end()) return NIXL_ERR_NOT_FOUND;
-        peer = it->second;
-    }
-    if (!peerAlive(peer)) return NIXL_ERR_REMOTE_DISCONNECT;
 
     std::unique_lock<std::mutex> lk(req->mu);
+    // Whatever goes wrong below, the request records it: kernels launched before the failure
+    // stay marked in flight and are waited for when the request is released.
+    auto fail = [&](nixl_status_t st) {
+        req->last = st;
+        return st;
+    };
+    if (!req->peer || req->peerGen != peersGen_.load(std::memory_order_acquire)) {
+        req->peer = findPeer(remote_agent, &req->peerGen);
+        if (!req->peer) return fail(NIXL_ERR_NOT_FOUND);
+    }
+    const int64_t now_ns = std::chrono::duration_cast<std::chrono::nanoseconds>(std::chrono::steady_clock::now().time_since_epoch()).count();
+    const bool look = livenessPing_ || now_ns - req->lastAliveNs > 1000000;
+    if (look) req->lastAliveNs = now_ns;
+    if (!peerAlive(*req->peer, look)) return fail(NIXL_ERR_REMOTE_DISCONNECT);
+
     req->notifPending = opt_args && opt_args->hasNotif;
-    req->notifMsg = req->notifPending ? opt_args->notifMsg : std::string();
+    if (req->notifPending) req->notifMsg = opt_args->notifMsg;
 
     // Optional stream-ordered posting: customParam "stream=<address of a cudaStream_t value>".
     cudaStream_t user_stream = nullptr;
@@ -829,40 +911,67 @@ nixl_status_t Engine::postXfer(const nixl_xfer_op_t &operation, const nixl_meta_
                 ? ::process_vm_writev(static_cast<pid_t>(req->cmaPid), liov, n, riov, n, 0)
                 : ::process_vm_readv(static_cast<pid_t>(req->cmaPid), liov, n, riov, n, 0);
             if (got < 0 || static_cast<size_t>(got) != want) {
-                if (errno == ESRCH) return NIXL_ERR_REMOTE_DISCONNECT;
+                if (errno == ESRCH) return fail(NIXL_ERR_REMOTE_DISCONNECT);
                 NIXL_ERROR << "NVLINK backend: cross-process DRAM copy failed: " << std::strerror(errno);
-                return NIXL_ERR_BACKEND;
+                return fail(NIXL_ERR_BACKEND);
             }
             i += n;
         }
     }
 
-    for (auto &b : req->kernels) {
-        DeviceCtx *c = ctx(b.device);
-        if (!c) return NIXL_ERR_BACKEND;
-        DeviceScope ds(b.device);
-        cudaStream_t s = has_user_stream ? user_stream : c->stream;
-        if (b.uploaded && !cudaOk(cudaStreamWaitEvent(s, b.uploaded, 0), "cudaStreamWaitEvent")) return NIXL_ERR_BACKEND;
-        b.seq = (b.seq + 1) & 0x7fffffffffffffffull;
-        if (b.seq == 0) b.seq = 1;
-        b.launch.seq = b.seq;
-        if (!cudaOk(launchBatchCopy(b.launch, c->gridCtas, copyPath_, s), "copy kernel launch")) return NIXL_ERR_BACKEND;
-        b.inFlight = true;
-    }
-
-    if (!req->asyncCopies.empty()) {
-        for (auto &a : req->asyncCopies) {
-            DeviceCtx *c = ctx(a.device);
-            DeviceScope ds(a.device);
-            cudaStream_t s = has_user_stream ? user_stream : c->stream;
-            if (!cudaOk(cudaMemcpyAsync(a.dst, a.src, a.len, cudaMemcpyDefault, s), "cudaMemcpyAsync")) return NIXL_ERR_BACKEND;
+    if (!req->kernels.empty() || !req->asyncCopies.empty()) {
+        int cur = -1;
+        if (cudaGetDevice(&cur) != cudaSuccess) cur = -1;
+        int active = cur;
+        auto use = [&](int dev) {
+            if (dev != active) {
+                cudaSetDevice(dev);
+                active = dev;
+            }
+        };
+        nixl_status_t err = NIXL_SUCCESS;
+        for (auto &b : req->kernels) {
+            DeviceCtx *c = ctx(b.device);
+            if (!c) {
+                err = NIXL_ERR_BACKEND;
+                break;
+            }
+            use(b.device);
+            cudaStream_t s = has_user_stream ? user_stream : b.stream;
+            if (b.uploaded && !cudaOk(cudaStreamWaitEvent(s, b.uploaded, 0), "cudaStreamWaitEvent")) {
+                err = NIXL_ERR_BACKEND;
+                break;
+            }
+            uint64_t seq = (b.seq + 1) & 0x7fffffffffffffffull;
+            if (seq == 0) seq = 1;
+            b.launch.seq = seq;
+            if (!cudaOk(launchBatchCopy(b.launch, c->gridCtas, copyPath_, s), "copy kernel launch")) {
+                err = NIXL_ERR_BACKEND;
+                break;
+            }
+            b.seq = seq;
+            b.inFlight = true;
         }
-        for (auto &e : req->asyncEvents) {
-            DeviceCtx *c = ctx(e.first);
-            DeviceScope ds(e.first);
-            if (!cudaOk(cudaEventRecord(e.second, has_user_stream ? user_stream : c->stream), "cudaEventRecord")) return NIXL_ERR_BACKEND;
+        if (err == NIXL_SUCCESS && !req->asyncCopies.empty()) {
+            for (auto &a : req->asyncCopies) {
+                DeviceCtx *c = ctx(a.device);
+                use(a.device);
+                cudaStream_t s = has_user_stream ? user_stream : c->streams[0];
+                if (!cudaOk(cudaMemcpyAsync(a.dst, a.src, a.len, cudaMemcpyDefault, s), "cudaMemcpyAsync")) {
+                    err = NIXL_ERR_BACKEND;
+                    break;
+                }
+            }
+            // Everything queued so far is covered by the events, also after a failed copy.
+            for (auto &e : req->asyncEvents) {
+                DeviceCtx *c = ctx(e.first);
+                use(e.first);
+                if (!cudaOk(cudaEventRecord(e.second, has_user_stream ? user_stream : c->streams[0]), "cudaEventRecord")) err = NIXL_ERR_BACKEND;
+            }
+            req->asyncInFlight = true;
         }
-        req->asyncInFlight = true;
+        if (active != cur && cur >= 0) cudaSetDevice(cur);
+        if (err != NIXL_SUCCESS) return fail(err);
     }
 
     nixl_status_t st = pollData(req);
@@ -882,16 +991,13 @@ nixl_status_t Engine::postXfer(const nixl_xfer_op_t &operation, const nixl_meta_
 nixl_status_t Engine::pollData(ReqH *req) const {
     for (auto &b : req->kernels) {
         if (!b.inFlight) continue;
-        DeviceCtx *c = ctx(b.device);
-        const uint64_t v = *reinterpret_cast<volatile uint64_t *>(c->flags + b.flagSlot);
+        const uint64_t v = *reinterpret_cast<volatile uint64_t *>(b.flag);
+        if ((v & 0x7fffffffffffffffull) != b.seq) return NIXL_IN_PROG;
+        b.inFlight = false;
         if (v >> 63) {
-            c->flags[b.flagSlot] = 0;
-            b.inFlight = false;
             NIXL_ERROR << "NVLINK backend: copy kernel reported a lost bulk copy";
             return NIXL_ERR_BACKEND;
         }
-        if (v != b.seq) return NIXL_IN_PROG;
-        b.inFlight = false;
     }
     if (req->asyncInFlight) {
         for (auto &e : req->asyncEvents) {
@@ -913,15 +1019,13 @@ nixl_status_t Engine::pollData(ReqH *req) const {
 
 nixl_status_t Engine::finishIfDone(ReqH *req) const {
     if (!req->notifPending) return NIXL_SUCCESS;
-    PeerId peer;
-    {
-        std::lock_guard<std::mutex> g(peersMu_);
-        auto it = peers_.find(req->remoteAgent);
-        if (it == peers_.end()) return NIXL_ERR_NOT_FOUND;
-        peer = it->second;
+    std::shared_ptr<const PeerId> peer = req->peer;
+    if (!peer || req->peerGen != peersGen_.load(std::memory_order_acquire)) {
+        peer = findPeer(req->remoteAgent);
+        if (!peer) return NIXL_ERR_NOT_FOUND;
     }
     req->notifPending = false;
-    return sendNotif(peer, req->notifMsg);
+    return sendNotif(*peer, req->notifMsg);
 }
 
 nixl_status_t Engine::checkXfer(nixlBackendReqH *handle) const {
@@ -942,25 +1046,7 @@ nixl_status_t Engine::releaseReqH(nixlBackendReqH *handle) const {
         std::lock_guard<std::mutex> g(progMu_);
         progWatch_.erase(std::remove(progWatch_.begin(), progWatch_.end(), req), progWatch_.end());
     }
-    {
-        std::lock_guard<std::mutex> g(req->mu);
-        // A running kernel still reads the table: wait for it (transfers are short-lived).
-        for (auto &b : req->kernels) {
-            if (b.inFlight) {
-                DeviceCtx *c = ctx(b.device);
-                DeviceScope ds(b.device);
-                cudaStreamSynchronize(c->stream);
-                b.inFlight = false;
-            }
-            freeBatch(b);
-        }
-        for (auto &e : req->asyncEvents) {
-            DeviceScope ds(e.first);
-            if (req->asyncInFlight) cudaEventSynchronize(e.second);
-            cudaEventDestroy(e.second);
-        }
-    }
-    delete req;
+    destroyReq(req);
     return NIXL_SUCCESS;
 }
 
@@ -1055,23 +1141,18 @@ nixl_status_t Engine::sendNotif(const PeerId &peer, const std::string &msg) cons
 }
 
 nixl_status_t Engine::genNotif(const std::string &remote_agent, const std::string &msg) const {
-    PeerId peer;
-    {
-        std::lock_guard<std::mutex> g(peersMu_);
-        auto it = peers_.find(remote_agent);
-        if (it == peers_.end()) return NIXL_ERR_NOT_FOUND;
-        peer = it->second;
-    }
-    return sendNotif(peer, msg);
+    auto peer = findPeer(remote_agent);
+    if (!peer) return NIXL_ERR_NOT_FOUND;
+    return sendNotif(*peer, msg);
 }
 
 nixl_status_t Engine::getNotifs(notif_list_t &notif_list) {
-    {
-        std::lock_guard<std::mutex> g(notifMu_);
-        for (auto &n : inbox_) notif_list.push_back(std::move(n));
-        inbox_.clear();
-    }
-    std::vector<char> buf(256 * 1024);
+    std::lock_guard<std::mutex> g(notifMu_);
+    for (auto &n : inbox_) notif_list.push_back(std::move(n));
+    inbox_.clear();
+    // The receive buffer lives in the engine: this is the target's polling path.
+    std::vector<char> &buf = notifBuf_;
+    if (buf.empty()) buf.resize(256 * 1024);
     for (;;) {
         const ssize_t n = ::recv(notifFd_, buf.data(), buf.size(), MSG_DONTWAIT | MSG_TRUNC);
         if (n < 0) break;
@@ -1132,7 +1213,7 @@ nixl_status_t Engine::prepMemView(const nixl_remote_meta_dlist_t &dlist, nixlMem
         if (d.remoteAgent != nixl_null_agent) {
             auto *r = dynamic_cast<RemoteMD *>(d.metadataP);
             if (!r || !r->devVisible) return NIXL_ERR_NOT_SUPPORTED;
-            if (r->mem == VRAM_SEG && r->sameProcess && !ensurePeerAccess(dev, r->ownerDevice)) return NIXL_ERR_BACKEND;
+            if (r->mem == VRAM_SEG && r->ownerLocalDevice >= 0 && !ensurePeerAccess(dev, r->ownerLocalDevice)) return NIXL_ERR_NOT_SUPPORTED;
             e.ptr = r->devVisible + (d.addr - r->addr);
             e.len = d.len;
         }
@@ -1177,7 +1258,8 @@ nixl_b_params_t nvlinkDefaults() {
         {"copy_path", "vector"},   // "vector" (SIMT 16-byte) or "bulk" (TMA 1-D through shared memory)
         {"grid_ctas", "0"},        // 0: two CTAs per SM
         {"device_id", "-1"},       // GPU that maps other processes' memory; -1: first registered / current
-        {"liveness_ping", "false"} // probe the peer's socket at every post
+        {"liveness_ping", "false"},// probe the peer's socket at every post
+        {"num_streams", "4"}       // streams per GPU that independent requests are spread over
     };
 }
 } // namespace

@@ -73,7 +73,8 @@ public:
     nixl_mem_t mem = DRAM_SEG;
     uintptr_t addr = 0;        // address in the owner's address space
     size_t len = 0;
-    int ownerDevice = -1;      // owner's CUDA ordinal (VRAM)
+    int ownerDevice = -1;      // owner's CUDA ordinal in the owner's process (VRAM)
+    int ownerLocalDevice = -1; // the same GPU's ordinal in THIS process (-1: unknown / not VRAM)
     bool sameProcess = false;
     uintptr_t devVisible = 0;  // kernel-usable address in THIS process covering [addr, addr+len); 0 if none
     int mapDevice = -1;        // local device the IPC mapping was opened on (other-process VRAM)
@@ -97,17 +98,32 @@ private:
     std::vector<Slab> slabs_;
 };
 
+// Pinned, device-mapped completion words, handed out one per prepared request.  Grows by
+// pages of kWordsPerPage words, so the number of prepared requests is bounded by host memory only.
+class FlagPool {
+public:
+    ~FlagPool();
+    uint64_t *acquire(); // zeroed word; nullptr when pinned memory cannot be had
+    void release(uint64_t *w);
+    size_t pages() const { return pages_.size(); }
+
+private:
+    static constexpr size_t kWordsPerPage = 4096;
+    std::mutex mu_;
+    std::vector<uint64_t *> pages_;
+    std::vector<uint64_t *> free_;
+};
+
 // Per-device resources of one engine.
 struct DeviceCtx {
     int device = -1;
-    cudaStream_t stream = nullptr;     // transfers
+    std::vector<cudaStream_t> streams; // transfers: a request is bound to one of them when it is prepared
+    std::atomic<uint32_t> nextStream{0};
     cudaStream_t prepStream = nullptr; // table uploads
     std::unique_ptr<DeviceArena> arena;
-    uint64_t *flags = nullptr;         // pinned, mapped completion words
-    std::vector<int> freeFlags;
+    FlagPool flags;
     int gridCtas = 0;
     int smCount = 148;
-    std::mutex mu;
 };
 
 struct KernelBatch {
@@ -116,7 +132,8 @@ struct KernelBatch {
     XferLaunch launch{};
     void *table = nullptr; // arena block holding table + chunk starts (nullptr when inline)
     unsigned int *counter = nullptr;
-    int flagSlot = -1;
+    uint64_t *flag = nullptr;      // completion word (FlagPool)
+    cudaStream_t stream = nullptr; // engine stream this batch posts on unless the caller names one
     cudaEvent_t uploaded = nullptr;
     uint64_t seq = 0;
     bool inFlight = false;
@@ -143,6 +160,10 @@ public:
     std::string notifMsg;
     std::mutex mu; // progress thread vs. user thread
     nixl_status_t last = NIXL_ERR_NOT_POSTED;
+    // Peer identity looked up at prepare time; valid while peerGen equals the engine's generation.
+    std::shared_ptr<const PeerId> peer;
+    uint64_t peerGen = 0;
+    int64_t lastAliveNs = 0; // steady-clock time of the last other-process liveness look
 };
 
 // Device-side view handle header (mirrors include/device/nixl_device.cuh).
@@ -202,7 +223,9 @@ public:
 
 private:
     DeviceCtx *ctx(int device) const;
-    bool peerAlive(const PeerId &peer) const;
+    bool peerAlive(const PeerId &peer, bool force = false) const;
+    std::shared_ptr<const PeerId> findPeer(const std::string &agent, uint64_t *gen = nullptr) const;
+    void destroyReq(ReqH *req) const; // waits for launched work, frees device resources, deletes
     nixl_status_t sendNotif(const PeerId &peer, const std::string &msg) const;
     nixl_status_t finishIfDone(ReqH *req) const; // data complete -> deliver notification
     nixl_status_t pollData(ReqH *req) const;
@@ -220,8 +243,11 @@ private:
     size_t memcpyAsyncThreshold_ = 0;
     bool livenessPing_ = false;
 
+    int numStreams_ = 4;
+
     mutable std::mutex peersMu_;
-    std::unordered_map<std::string, PeerId> peers_;
+    std::unordered_map<std::string, std::shared_ptr<const PeerId>> peers_;
+    mutable std::atomic<uint64_t> peersGen_{1}; // bumped whenever peers_ changes
 
     mutable std::mutex ctxMu_;
     mutable std::vector<std::unique_ptr<DeviceCtx>> ctxs_;
@@ -230,6 +256,7 @@ private:
     int notifFd_ = -1;
     mutable std::mutex notifMu_;
     notif_list_t inbox_; // same-process deliveries
+    std::vector<char> notifBuf_; // receive buffer of getNotifs, kept between polls
 
     // progress thread
     bool progThread_ = false;

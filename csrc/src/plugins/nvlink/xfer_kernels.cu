@@ -180,6 +180,8 @@ __global__ void __launch_bounds__(kThreads) batchCopyVector(const __grid_constan
 constexpr int kStages = 4;
 constexpr uint32_t kStageBytes = 32 * 1024;
 constexpr uint64_t kWaitBudgetNs = 2000000000ull; // a bulk load that has not landed after 2 s is treated as lost
+constexpr uint64_t kDrainBudgetNs = 100000000ull; // after a loss: 0.1 s for each younger load before the CTA leaves
+static_assert(kStages == 4, "the wait_group.read switch in batchCopyBulk enumerates kStages cases");
 
 __device__ __forceinline__ uint64_t globalTimerNs() {
     uint64_t t;
@@ -215,6 +217,20 @@ __device__ __forceinline__ void bulkStore(void *gdst, const void *smem_src, uint
 __device__ __forceinline__ void bulkCommit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 template<int N> __device__ __forceinline__ void bulkWaitRead() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
 template<int N> __device__ __forceinline__ void bulkWait() { asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory"); }
+
+// Waits for a phase of an mbarrier for at most budget_ns (looking at the clock only now and then).
+__device__ __forceinline__ bool mbarWaitBounded(uint64_t *bar, uint32_t parity, uint64_t budget_ns) {
+    uint32_t spins = 0;
+    uint64_t t0 = 0;
+    while (!mbarTryWait(bar, parity)) {
+        if ((++spins & 255u) == 0) {
+            const uint64_t now = globalTimerNs();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > budget_ns) return false;
+        }
+    }
+    return true;
+}
 
 __global__ void __launch_bounds__(128) batchCopyBulk(const __grid_constant__ XferLaunch p) {
     extern __shared__ __align__(128) unsigned char smem[];
@@ -257,15 +273,27 @@ __global__ void __launch_bounds__(128) batchCopyBulk(const __grid_constant__ Xfe
         }
         const size_t body = n & ~size_t(15);
         if (threadIdx.x == 0 && !failed) {
-            // Software pipeline: keep up to kStages loads in flight; a stage is reused once
-            // the bulk store that read it has finished reading shared memory.
+            // Software pipeline: up to kStages loads in flight.  Piece g uses slot g % kStages, and
+            // its store is bulk group number g.  Before slot g % kStages is loaded again, group
+            // g - kStages must have finished READING shared memory; `stored_total - 1 - (g - kStages)`
+            // groups were committed after it, which is the number wait_group.read may leave pending.
+            // In steady state that number is 0: the store just issued is waited for (its read of
+            // shared memory, not its arrival), while kStages - 1 younger loads stay in flight.
             const uint32_t pieces = static_cast<uint32_t>((body + kStageBytes - 1) / kStageBytes);
             uint32_t loaded = 0, stored = 0;
             while (stored < pieces) {
                 while (loaded < pieces && loaded - stored < kStages) {
                     const uint32_t g = issued + loaded;
                     const uint32_t slot = g % kStages;
-                    if (g >= kStages) bulkWaitRead<kStages - 1>(); // the store that used this slot kStages pieces ago
+                    if (g >= kStages) {
+                        const uint32_t may_pend = (issued + stored) - 1 - (g - kStages); // 0 .. kStages - 1
+                        switch (may_pend) {
+                        case 0: bulkWaitRead<0>(); break;
+                        case 1: bulkWaitRead<1>(); break;
+                        case 2: bulkWaitRead<2>(); break;
+                        default: bulkWaitRead<3>(); break;
+                        }
+                    }
                     const size_t o = size_t(loaded) * kStageBytes;
                     const uint32_t bytes = static_cast<uint32_t>(body - o < kStageBytes ? body - o : kStageBytes);
                     mbarExpectTx(&full[slot], bytes);
@@ -275,19 +303,16 @@ __global__ void __launch_bounds__(128) batchCopyBulk(const __grid_constant__ Xfe
                 const uint32_t g = issued + stored;
                 const uint32_t slot = g % kStages;
                 const uint32_t parity = (g / kStages) & 1;
-                uint32_t spins = 0;
-                uint64_t t0 = 0;
-                while (!mbarTryWait(&full[slot], parity)) {
-                    if ((++spins & 255u) == 0) { // look at the clock only now and then
-                        const uint64_t now = globalTimerNs();
-                        if (t0 == 0) t0 = now;
-                        else if (now - t0 > kWaitBudgetNs) {
-                            failed = 1;
-                            break;
-                        }
+                if (!mbarWaitBounded(&full[slot], parity, kWaitBudgetNs)) {
+                    failed = 1;
+                    // Loads already issued still target this CTA's shared memory: give each a short
+                    // second chance to land before the CTA may exit and its shared memory be reused.
+                    for (uint32_t k = stored + 1; k < loaded; ++k) {
+                        const uint32_t gk = issued + k;
+                        mbarWaitBounded(&full[gk % kStages], (gk / kStages) & 1, kDrainBudgetNs);
                     }
+                    break;
                 }
-                if (failed) break;
                 const size_t o = size_t(stored) * kStageBytes;
                 const uint32_t bytes = static_cast<uint32_t>(body - o < kStageBytes ? body - o : kStageBytes);
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

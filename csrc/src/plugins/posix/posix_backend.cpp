@@ -15,6 +15,7 @@
 #define NIXL_POSIX_PLUGIN_NAME "POSIX"
 #endif
 #include <atomic>
+#include <cstring>
 #include <mutex>
 #include <unordered_map>
 
@@ -55,6 +56,8 @@ unsigned num(const nixl_b_params_t &p, const char *k, unsigned dflt) {
 class Engine final : public nixlBackendEngine {
 public:
     explicit Engine(const nixlBackendInitParams *init) : nixlBackendEngine(init) {
+        if (std::strcmp(NIXL_POSIX_PLUGIN_NAME, "POSIX") != 0)
+            NIXL_WARN << NIXL_POSIX_PLUGIN_NAME << " backend: this build has no client for that file system; files are served by the POSIX engine's queues";
         const nixl_b_params_t &p = getCustomParams();
         QueueKind kind = QueueKind::THREADS;
         if (flag(p, "use_aio")) kind = QueueKind::LINUX_AIO;

@@ -27,4 +27,16 @@ from ._api import (  # noqa: E402,F401
     nixl_xfer_handle,
 )
 
-__version__ = "0.1.0"
+
+
+def add_plugin_directory(path: str) -> None:
+    """Put ``path`` in front of the process-wide plug-in search path (agents created later see it)."""
+    _bindings.add_plugin_directory(path)
+
+
+#: Engines that answer to the names of the reference's cloud / appliance plug-ins (AZURE_BLOB,
+#: INFINIA, HF3FS, GDS_MT) with local storage.  They are NOT clients of those services and are
+#: therefore not on the default search path; ``add_plugin_directory(STANDIN_PLUGIN_DIR)`` opts in.
+STANDIN_PLUGIN_DIR = _os.path.join(_HERE, "lib", "standin_plugins")
+
+__version__ = "0.2.0"

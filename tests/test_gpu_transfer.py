@@ -133,6 +133,118 @@ def test_notification_after_data_and_stream_order():
     a.release_xfer_handle(h)
 
 
+def test_bulk_path_deep_pipeline_is_byte_exact():
+    """One descriptor, 256 KiB chunks: every CTA runs eight 32 KiB pieces through its four
+    shared-memory stages, so each stage is refilled while the store that last used it may still
+    be reading it.  The bytes must survive, on the same GPU and (when there is one) to a peer."""
+    a, b = _pair("bulk_deep", {"copy_path": "bulk", "chunk_shift": "18"})
+    n = (24 << 20) + 4096 + 16
+    src = torch.randint(0, 255, (n,), dtype=torch.uint8, device="cuda:0")
+    targets = ["cuda:0"] + (["cuda:1"] if torch.cuda.device_count() > 1 else [])
+    a.register_memory(src)
+    for t in targets:
+        dst = torch.zeros(n, dtype=torch.uint8, device=t)
+        reg = b.register_memory(dst)
+        _connect(a, b)
+        for op in ("WRITE", "READ"):
+            if op == "READ":
+                dst.copy_(torch.randint(0, 255, (n,), dtype=torch.uint8, device=t))
+                want = dst.clone()
+            else:
+                dst.zero_()
+                want = src.clone()
+            h = a.initialize_xfer(op, src, dst, b.name)
+            for _ in range(3):
+                assert a.transfer(h) in ("DONE", "PROC")
+                assert _wait(a, h) == "DONE"
+            torch.cuda.synchronize()
+            assert torch.equal(dst.to("cuda:0"), want.to("cuda:0")) and torch.equal(src, want.to("cuda:0")), (t, op)
+            a.release_xfer_handle(h)
+            if op == "READ":
+                src.copy_(torch.randint(0, 255, (n,), dtype=torch.uint8, device="cuda:0"))
+        b.deregister_memory(reg)
+
+
+def test_release_right_after_post_on_a_busy_caller_stream():
+    """The request is posted on the caller's stream behind a long-running kernel and released at
+    once: the release must wait for the copy kernel (it reads the request's descriptor table and
+    writes its completion word), and the bytes must be intact afterwards."""
+    a, b = _pair("rel_stream")
+    n_desc, size = 64, 1 << 16  # more than 32 descriptors: the table lives in device memory
+    src = torch.randint(0, 255, (n_desc, size), dtype=torch.uint8, device="cuda:0")
+    dst = torch.zeros_like(src)
+    a.register_memory(src)
+    b.register_memory(dst)
+    _connect(a, b)
+    stream = torch.cuda.Stream()
+    for _ in range(3):
+        dst.zero_()
+        torch.cuda.synchronize()
+        h = a.initialize_xfer("WRITE", [src[i] for i in range(n_desc)], [dst[i] for i in range(n_desc)], b.name)
+        with torch.cuda.stream(stream):
+            torch.cuda._sleep(200_000_000)  # ~0.1 s of device time in front of the copy
+            assert a.transfer(h, custom_param=f"stream={stream.cuda_stream}") in ("DONE", "PROC")
+        a.release_xfer_handle(h)
+        # another request right away: it must not be handed a completion word that the first kernel still writes
+        h2 = a.initialize_xfer("WRITE", src[0], dst[0], b.name)
+        assert a.transfer(h2) in ("DONE", "PROC")
+        assert _wait(a, h2) == "DONE"
+        a.release_xfer_handle(h2)
+        torch.cuda.synchronize()
+        assert torch.equal(src, dst)
+
+
+def test_ten_thousand_prepared_requests():
+    """A serving engine keeps many prepared handles: more than one page of completion words."""
+    a, b = _pair("many")
+    src = torch.randint(0, 255, (10000, 64), dtype=torch.uint8, device="cuda:0")
+    dst = torch.zeros_like(src)
+    a.register_memory(src)
+    b.register_memory(dst)
+    _connect(a, b)
+    handles = [a.initialize_xfer("WRITE", src[i], dst[i], b.name) for i in range(10000)]
+    for h in handles[::7]:
+        a.transfer(h)
+    for h in handles[::7]:
+        assert _wait(a, h) == "DONE"
+    torch.cuda.synchronize()
+    assert torch.equal(dst[::7], src[::7]) and int(dst[1::7].max()) == 0
+    for h in handles:
+        a.release_xfer_handle(h)
+
+
+def test_independent_requests_use_several_streams():
+    """Two large requests of one agent overlap on the GPU (each prepared request is bound to one
+    of the engine's streams): posted back to back they finish in less than twice one request's time."""
+    import time
+
+    a, b = _pair("streams", {"num_streams": "4", "grid_ctas": "64"})
+    n = 1 << 28
+    src = torch.randint(0, 255, (2, n), dtype=torch.uint8, device="cuda:0")
+    dst = torch.zeros_like(src)
+    a.register_memory(src)
+    b.register_memory(dst)
+    _connect(a, b)
+    hs = [a.initialize_xfer("WRITE", src[i], dst[i], b.name) for i in range(2)]
+
+    def run(which):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for h in which:
+            a.transfer(h)
+        for h in which:
+            assert _wait(a, h) == "DONE"
+        return time.perf_counter() - t0
+
+    run(hs)
+    one = min(run(hs[:1]) for _ in range(3))
+    two = min(run(hs) for _ in range(3))
+    assert torch.equal(src, dst)
+    assert two < 1.7 * one, (one, two)
+    for h in hs:
+        a.release_xfer_handle(h)
+
+
 def test_repost_while_active_is_rejected():
     a, b = _pair("rp")
     src = torch.ones(1 << 28, dtype=torch.uint8, device="cuda:0")

@@ -5,6 +5,7 @@ import numpy as np
 import pytest
 import torch
 
+import nixl_b200
 from nixl_b200 import nixl_agent, nixl_agent_config
 
 
@@ -69,6 +70,8 @@ def test_obj_rejects_path_separators(tmp_path):
 
 @pytest.mark.parametrize("name", ["GDS", "GDS_MT"])
 def test_gds_host_memory_file_roundtrip(tmp_path, name):
+    if name == "GDS_MT":
+        nixl_b200.add_plugin_directory(nixl_b200.STANDIN_PLUGIN_DIR)
     a = nixl_agent("gds_agent_" + name, nixl_agent_config(backends=[]))
     a.create_backend(name, {"thread_count": "2"})
     path = str(tmp_path / "blocks.bin")
@@ -153,6 +156,7 @@ def test_block_backend_rejects_bad_configurations(tmp_path):
 
 @pytest.mark.parametrize("name,param", [("AZURE_BLOB", "container_name"), ("INFINIA", "dataset")])
 def test_object_engine_under_the_other_object_store_names(tmp_path, name, param):
+    nixl_b200.add_plugin_directory(nixl_b200.STANDIN_PLUGIN_DIR)
     a = nixl_agent(f"obj_{name}", nixl_agent_config(backends=[]))
     assert name in a.get_plugin_list()
     a.create_backend(name, {param: str(tmp_path), "account_url": "https://example.invalid", "tenant": "t"})
@@ -173,6 +177,7 @@ def test_object_engine_under_the_other_object_store_names(tmp_path, name, param)
 
 
 def test_file_engine_under_the_hf3fs_name(tmp_path):
+    nixl_b200.add_plugin_directory(nixl_b200.STANDIN_PLUGIN_DIR)
     a = nixl_agent("hf3fs_agent", nixl_agent_config(backends=[]))
     a.create_backend("HF3FS", {"mem_config": "auto", "iopool_size": "2"})
     src = torch.arange(1 << 15, dtype=torch.uint8)
