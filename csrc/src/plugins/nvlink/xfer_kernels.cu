@@ -345,7 +345,14 @@ __global__ void __launch_bounds__(128) batchCopyBulk(const __grid_constant__ Xfe
     }
 }
 
+__global__ void signalOnly(uint64_t *flag, uint64_t seq) { st_release_sys(flag, seq); }
+
 } // namespace
+
+cudaError_t launchSignal(uint64_t *hostFlag, uint64_t seq, cudaStream_t stream) {
+    signalOnly<<<1, 1, 0, stream>>>(hostFlag, seq);
+    return cudaGetLastError();
+}
 
 int defaultGridCtas(int device) {
     int sms = 0;

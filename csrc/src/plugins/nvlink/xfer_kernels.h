@@ -36,11 +36,17 @@ struct XferLaunch {
     uint32_t inlStart[kInlineDescs + 1];
 };
 
-// Copy engine variants: SIMT 16-byte vectors, or bulk (TMA 1-D) staged through shared memory.
-enum class CopyPath : int { VECTOR = 0, BULK = 1 };
+// Ways to move a batch: SIMT vectors, bulk (TMA 1-D) staged through shared memory, or the GPU's
+// copy engines (one cudaMemcpyAsync per descriptor followed by launchSignal: what a
+// descriptor-at-a-time transport does, kept as the baseline the kernels are measured against).
+enum class CopyPath : int { VECTOR = 0, BULK = 1, COPY_ENGINE = 2 };
 
 // Launches on `stream` of the current device.  grid_ctas == 0 picks a default.
 cudaError_t launchBatchCopy(const XferLaunch &params, int grid_ctas, CopyPath path, cudaStream_t stream);
+
+// One thread stores `seq` to the completion word with release semantics at system scope, after
+// everything queued earlier on `stream` (the copy-engine path's completion).
+cudaError_t launchSignal(uint64_t *hostFlag, uint64_t seq, cudaStream_t stream);
 
 // Largest useful grid for the current device (SM count x resident CTAs per SM).
 int defaultGridCtas(int device);
