@@ -10,7 +10,7 @@
 //   nixlbench [--backend NVLINK] [--op WRITE|READ] [--mem VRAM|DRAM] [--src-dev 0] [--dst-dev 1]
 //             [--min 4096] [--max 1073741824] [--batch 1] [--batch-max N] [--iters 1000] [--warmup 100]
 //             [--depth 1] [--copy-path vector|bulk] [--param key=value]... [--check]
-//             [--prepared] [--recreate] [--reregister] [--config file]
+//             [--prepared] [--recreate] [--reregister] [--scatter] [--config file]
 //             [--file path [--num-files N] [--direct]]      storage mode (POSIX, GDS, GDS_MT backends)
 //
 // --prepared builds requests with prepXferDlist + makeXferReq (the reference's prepared_xfer),
@@ -45,6 +45,7 @@ struct Args {
     int src_dev = 0, dst_dev = -1, batch = 1, iters = 1000, warmup = 100, depth = 1;
     size_t min = 4096, max = size_t(1) << 30, total = size_t(8) << 30;
     bool check = false, prepared = false, recreate = false, reregister = false, direct = false;
+    bool scatter = false; // target blocks of a batch in reverse order: no descriptor continues its predecessor
     int batch_max = 0, num_files = 1;
     std::string file; // storage mode when set
     nixl_b_params_t extra; // --param key=value, passed to the backend
@@ -80,6 +81,7 @@ bool setFlag(Args &a, const std::string &k) {
     else if (k == "--recreate") a.recreate = true;
     else if (k == "--reregister") a.reregister = true;
     else if (k == "--direct") a.direct = true;
+    else if (k == "--scatter") a.scatter = true;
     else return false;
     return true;
 }
@@ -309,7 +311,8 @@ int main(int argc, char **argv) {
                 if (foff + block > file_bytes) foff = 0; // a block never straddles two files
                 r.addDesc(nixlBasicDesc(foff, block, static_cast<uint64_t>(fds[f])));
             } else {
-                r.addDesc(nixlBasicDesc(reinterpret_cast<uintptr_t>(dst) + off, block, vram ? a.dst_dev : 0));
+                const size_t roff = a.scatter ? static_cast<size_t>(batch - 1 - i) * block : off;
+                r.addDesc(nixlBasicDesc(reinterpret_cast<uintptr_t>(dst) + roff, block, vram ? a.dst_dev : 0));
             }
         }
         nixlDlistH *side_l = nullptr, *side_r = nullptr;

@@ -377,6 +377,11 @@ Engine::Engine(const nixlBackendInitParams *init) : nixlBackendEngine(init) {
     chunkShiftOverride_ = static_cast<int>(paramLong(params, "chunk_shift", 0));
     livenessPing_ = paramBool(params, "liveness_ping", false);
     coalesce_ = paramBool(params, "coalesce", true);
+    proxyEnabled_ = paramBool(params, "proxy", true);
+    proxyMaxBytes_ = static_cast<size_t>(std::max<long>(0, paramLong(params, "proxy_max_bytes", static_cast<long>(proxyMaxBytes_))));
+    proxyWorkers_ = static_cast<int>(std::min<long>(kProxyMaxWorkers, std::max<long>(1, paramLong(params, "proxy_workers", proxyWorkers_))));
+    proxyIdleNs_ = static_cast<uint64_t>(std::max<long>(1, paramLong(params, "proxy_idle_us", 100))) * 1000;
+    proxyLifeNs_ = static_cast<uint64_t>(std::max<long>(10, paramLong(params, "proxy_life_us", 2000))) * 1000;
     numStreams_ = static_cast<int>(std::min<long>(32, std::max<long>(1, paramLong(params, "num_streams", 4))));
     const long dev = paramLong(params, "device_id", -1);
     if (dev >= 0) primaryDevice_ = static_cast<int>(dev);
@@ -430,6 +435,15 @@ Engine::~Engine() {
             cudaStreamDestroy(st);
         }
         if (c->prepStream) cudaStreamDestroy(c->prepStream);
+        if (c->proxy) {
+            Proxy &px = *c->proxy;
+            if (px.stream) {
+                cudaStreamSynchronize(px.stream); // the kernel leaves by itself once idle
+                cudaStreamDestroy(px.stream);
+            }
+            if (px.shared) cudaFree(px.shared);
+            if (px.pinned) cudaFreeHost(px.pinned);
+        }
         c->arena.reset();
         c->counters.reset();
     }
@@ -739,7 +753,7 @@ void Engine::destroyReq(ReqH *req) const {
                 bool done = false;
                 for (uint32_t spins = 0;; ++spins) {
                     const uint64_t v = *reinterpret_cast<volatile uint64_t *>(b.flag);
-                    if ((v & 0x7fffffffffffffffull) == b.seq) {
+                    if (b.viaProxy ? proxyDone(nullptr, b) != 0 : (v & 0x7fffffffffffffffull) == b.seq) {
                         done = true;
                         break;
                     }
@@ -881,15 +895,22 @@ nixl_status_t Engine::prepXfer(const nixl_xfer_op_t &operation, const nixl_meta_
         const uint64_t resident = std::min<uint64_t>(static_cast<uint64_t>(c->gridCtas), 2 * static_cast<uint64_t>(c->smCount));
         uint32_t shift = log2Ceil(std::max<uint64_t>(1, total / (2 * std::max<uint64_t>(1, resident))));
         shift = std::min<uint32_t>(18, std::max<uint32_t>(14, shift));
-        if (chunkShiftOverride_ >= 14 && chunkShiftOverride_ <= 22) shift = static_cast<uint32_t>(chunkShiftOverride_);
         const size_t n = b.descs.size();
+        // Small kernel-only batches may go through the doorbell proxy, whose unit of work is a warp: 4 KiB chunks.
+        b.proxyEligible = proxyEnabled_ && copyPath_ == CopyPath::VECTOR && b.ceDescs.empty() && n >= 1 && n <= kProxyMaxDescs && total <= proxyMaxBytes_;
+        if (b.proxyEligible) shift = 12;
+        if (chunkShiftOverride_ >= 12 && chunkShiftOverride_ <= 22) shift = static_cast<uint32_t>(chunkShiftOverride_);
         std::vector<uint32_t> starts(n + 1);
         uint64_t chunks = 0;
+        uint64_t per = 0; // chunks per descriptor when all descriptors have the same number, else 0
         for (size_t i = 0; i < n; ++i) {
             starts[i] = static_cast<uint32_t>(chunks);
-            chunks += (b.descs[i].len + (uint64_t(1) << shift) - 1) >> shift;
+            const uint64_t mine = (b.descs[i].len + (uint64_t(1) << shift) - 1) >> shift;
+            per = i == 0 ? mine : (per == mine ? per : 0);
+            chunks += mine;
             if (chunks > 0x7fffffffull) return fail(NIXL_ERR_INVALID_PARAM); // cannot happen below 2^31 * 16 KiB, but stay safe
         }
+        b.uniformChunks = per <= kProxyMaxPer ? static_cast<uint32_t>(per) : 0;
         starts[n] = static_cast<uint32_t>(chunks);
         b.launch.nDescs = static_cast<uint32_t>(n);
         b.launch.totalChunks = static_cast<uint32_t>(chunks);
@@ -900,12 +921,17 @@ nixl_status_t Engine::prepXfer(const nixl_xfer_op_t &operation, const nixl_meta_
         b.counter = c->counters->acquire();
         if (!b.counter) return fail(NIXL_ERR_BACKEND);
         b.launch.doneCounter = b.counter;
-        if (n <= static_cast<size_t>(kInlineDescs)) {
+        if (n == 1) b.single = b.descs[0];
+        const bool inline_ok = n <= static_cast<size_t>(kInlineDescs);
+        if (inline_ok) {
             b.launch.table = nullptr;
             b.launch.chunkStart = nullptr;
             for (size_t i = 0; i < n; ++i) b.launch.inl[i] = b.descs[i];
             for (size_t i = 0; i <= n; ++i) b.launch.inlStart[i] = starts[i];
-        } else {
+        }
+        // A device table for batches too long for the launch parameters, and for any batch of
+        // several descriptors that may go through the proxy (a proxy command has room for one).
+        if (!inline_ok || (b.proxyEligible && n > 1)) {
             const size_t tbytes = n * sizeof(XferDesc), sbytes = (n + 1) * sizeof(uint32_t);
             const size_t toff = 0, soff = (tbytes + 15) & ~size_t(15);
             b.table = c->arena->alloc(soff + sbytes);
@@ -918,8 +944,12 @@ nixl_status_t Engine::prepXfer(const nixl_xfer_op_t &operation, const nixl_meta_
             ok = ok && cudaOk(cudaEventCreateWithFlags(&b.uploaded, cudaEventDisableTiming), "cudaEventCreate");
             ok = ok && cudaOk(cudaEventRecord(b.uploaded, c->prepStream), "cudaEventRecord");
             if (!ok) return fail(NIXL_ERR_BACKEND);
-            b.launch.table = reinterpret_cast<const XferDesc *>(base + toff);
-            b.launch.chunkStart = reinterpret_cast<const uint32_t *>(base + soff);
+            b.tableDev = reinterpret_cast<const XferDesc *>(base + toff);
+            b.startsDev = reinterpret_cast<const uint32_t *>(base + soff);
+            if (!inline_ok) {
+                b.launch.table = b.tableDev;
+                b.launch.chunkStart = b.startsDev;
+            }
         }
         NIXL_DEBUG << "NVLINK backend: request to " << remote_agent << " on GPU " << b.device << ": " << n << " descriptor(s) for the copy kernel ("
                    << chunks << " chunks of " << (1u << shift) << " bytes), " << b.ceDescs.size() << " for the copy engines";
@@ -939,6 +969,116 @@ nixl_status_t Engine::prepXfer(const nixl_xfer_op_t &operation, const nixl_meta_
     }
     handle = req;
     return NIXL_SUCCESS;
+}
+
+// ---------------------------------------------------------------- doorbell proxy, host side
+
+// Starts the proxy kernel when commands are pending and none is alive.  `launched` stays true until
+// this side has SEEN the exit word; a kernel that has just left is therefore noticed by the next
+// post or poll, and the new launch queues behind it on the proxy's stream.
+void Engine::proxyEnsureRunning(DeviceCtx *c, Proxy &px) const {
+    if (px.broken) return;
+    if (px.launched) {
+        const uint64_t w = *reinterpret_cast<volatile uint64_t *>(px.exitWord);
+        if (w == 0) return;
+        px.launched = false;
+        px.nextStart = w & ~(1ull << 63);
+    }
+    if (px.nextStart >= px.posted) return; // nothing pending
+    *reinterpret_cast<volatile uint64_t *>(px.exitWord) = 0;
+    ProxyLaunch pl{};
+    pl.hostRing = px.hostRing;
+    pl.shared = px.shared;
+    pl.done = px.done;
+    pl.exitWord = px.exitWord;
+    pl.start = px.nextStart;
+    pl.gen = ++px.launches;
+    pl.idleNs = proxyIdleNs_;
+    pl.lifeNs = proxyLifeNs_;
+    DeviceScope ds(c->device);
+    if (!cudaOk(launchProxy(pl, proxyWorkers_, px.stream), "proxy kernel launch")) {
+        // Commands already written stay unserved: mark them so that their requests fail over.
+        px.broken = true;
+        return;
+    }
+    g_kernelLaunches.fetch_add(1, std::memory_order_relaxed);
+    px.launched = true;
+}
+
+bool Engine::postViaProxy(DeviceCtx *c, KernelBatch &b) const {
+    if (b.launch.nDescs > 1) {
+        if (!b.tableDev) return false;
+        if (!b.tableReady) { // the table upload of prepXfer must have landed; seen once, remembered
+            if (b.uploaded && cudaEventQuery(b.uploaded) != cudaSuccess) {
+                cudaGetLastError();
+                return false;
+            }
+            b.tableReady = true;
+        }
+    }
+    if (!c->proxy) {
+        std::lock_guard<std::mutex> g(ctxMu_);
+        if (!c->proxy) {
+            auto px = std::make_unique<Proxy>();
+            DeviceScope ds(c->device);
+            const size_t ring_bytes = kProxySlots * sizeof(ProxyCmd), done_bytes = kProxySlots * sizeof(uint64_t);
+            bool ok = cudaOk(cudaHostAlloc(&px->pinned, ring_bytes + done_bytes + 64, cudaHostAllocMapped | cudaHostAllocPortable), "cudaHostAlloc(proxy)");
+            ok = ok && cudaOk(cudaMalloc(reinterpret_cast<void **>(&px->shared), sizeof(ProxyShared)), "cudaMalloc(proxy)");
+            ok = ok && cudaOk(cudaMemset(px->shared, 0, sizeof(ProxyShared)), "cudaMemset(proxy)");
+            ok = ok && cudaOk(cudaStreamCreateWithFlags(&px->stream, cudaStreamNonBlocking), "cudaStreamCreate(proxy)");
+            if (ok) {
+                std::memset(px->pinned, 0, ring_bytes + done_bytes + 64);
+                px->hostRing = static_cast<ProxyCmd *>(px->pinned);
+                px->done = reinterpret_cast<uint64_t *>(static_cast<char *>(px->pinned) + ring_bytes);
+                px->exitWord = reinterpret_cast<uint64_t *>(static_cast<char *>(px->pinned) + ring_bytes + done_bytes);
+            } else {
+                px->broken = true;
+            }
+            c->proxy = std::move(px);
+        }
+    }
+    Proxy &px = *c->proxy;
+    std::lock_guard<std::mutex> g(px.mu);
+    if (px.broken) return false;
+    const uint64_t n = px.posted;
+    const uint32_t slot = static_cast<uint32_t>(n % kProxySlots);
+    // The slot's previous command (one ring ago) must be complete: its workers are past it.
+    if (n >= kProxySlots && *reinterpret_cast<volatile uint64_t *>(px.done + slot) < n - kProxySlots + 1) return false;
+    ProxyCmd *h = px.hostRing + slot;
+    if (b.launch.nDescs == 1) {
+        h->b = b.single.dst;
+        h->c = proxyPackC(n + 1, kProxyInline, b.launch.chunkShift, b.single.len);
+        h->a = b.single.src;
+    } else {
+        h->b = reinterpret_cast<uint64_t>(b.startsDev);
+        h->c = proxyPackC(n + 1, kProxyTable, b.launch.chunkShift, (uint64_t(b.uniformChunks) << 24) | b.launch.nDescs);
+        h->a = reinterpret_cast<uint64_t>(b.tableDev);
+    }
+    __atomic_store_n(&h->seq, n + 1, __ATOMIC_RELEASE); // the doorbell: written last
+    px.posted = n + 1;
+    b.viaProxy = true;
+    b.proxy = &px;
+    b.proxyCmd = n;
+    b.inFlight = true;
+    proxyEnsureRunning(c, px); // a failed launch marks the proxy broken; the request then reports it when polled
+    return true;
+}
+
+int Engine::proxyDone(DeviceCtx *c, KernelBatch &b) const {
+    Proxy &px = *b.proxy;
+    const uint64_t v = *reinterpret_cast<volatile uint64_t *>(px.done + (b.proxyCmd % kProxySlots));
+    if (v >= b.proxyCmd + 1) {
+        std::atomic_thread_fence(std::memory_order_acquire);
+        return 1;
+    }
+    if (px.broken.load(std::memory_order_relaxed)) return -1;
+    // Not done: if the kernel has left (idle or end of life) with this command pending, start it again.
+    if (*reinterpret_cast<volatile uint64_t *>(px.exitWord) != 0) {
+        if (!c) c = ctx(b.device);
+        std::lock_guard<std::mutex> g(px.mu);
+        proxyEnsureRunning(c, px);
+    }
+    return 0;
 }
 
 // Liveness of a peer, host side only.  Same process: the engine registry.  Other process:
@@ -1038,9 +1178,11 @@ nixl_status_t Engine::postXfer(const nixl_xfer_op_t &operation, const nixl_meta_
                 err = NIXL_ERR_BACKEND;
                 break;
             }
+            b.viaProxy = false;
+            if (b.proxyEligible && !has_user_stream && postViaProxy(c, b)) continue; // no CUDA call on this path
             use(b.device);
             cudaStream_t s = has_user_stream ? user_stream : b.stream;
-            if (b.uploaded && !cudaOk(cudaStreamWaitEvent(s, b.uploaded, 0), "cudaStreamWaitEvent")) {
+            if (b.uploaded && !b.tableReady && b.launch.table && !cudaOk(cudaStreamWaitEvent(s, b.uploaded, 0), "cudaStreamWaitEvent")) {
                 err = NIXL_ERR_BACKEND;
                 break;
             }
@@ -1107,6 +1249,16 @@ nixl_status_t Engine::postXfer(const nixl_xfer_op_t &operation, const nixl_meta_
 nixl_status_t Engine::pollData(ReqH *req) const {
     for (auto &b : req->kernels) {
         if (!b.inFlight) continue;
+        if (b.viaProxy) {
+            const int st = proxyDone(nullptr, b);
+            if (st == 0) return NIXL_IN_PROG;
+            b.inFlight = false;
+            if (st < 0) {
+                NIXL_ERROR << "NVLINK backend: the doorbell proxy kernel could not be launched";
+                return NIXL_ERR_BACKEND;
+            }
+            continue;
+        }
         const uint64_t v = *reinterpret_cast<volatile uint64_t *>(b.flag);
         if ((v & 0x7fffffffffffffffull) != b.seq) return NIXL_IN_PROG;
         b.inFlight = false;
@@ -1377,7 +1529,12 @@ nixl_b_params_t nvlinkDefaults() {
         {"grid_ctas", "0"},        // 0: two CTAs per SM
         {"device_id", "-1"},       // GPU that maps other processes' memory; -1: first registered / current
         {"liveness_ping", "false"},// probe the peer's socket at every post
-        {"num_streams", "4"}       // streams per GPU that independent requests are spread over
+        {"num_streams", "4"},      // streams per GPU that independent requests are spread over
+        {"proxy", "true"},         // small requests go through a persistent doorbell kernel instead of one launch each
+        {"proxy_max_bytes", "2097152"}, // largest request (all descriptors) the proxy takes
+        {"proxy_workers", "24"},   // worker CTAs of the proxy kernel
+        {"proxy_idle_us", "100"},  // the proxy kernel leaves after this long without a request
+        {"proxy_life_us", "2000"}  // and after this long in any case (the next request starts it again)
     };
 }
 } // namespace

@@ -133,6 +133,22 @@ private:
     std::vector<unsigned int *> free_;
 };
 
+// Host side of the doorbell proxy (xfer_kernels.h): the rings, and whether a kernel is alive.
+struct Proxy {
+    std::mutex mu;
+    void *pinned = nullptr;         // one pinned, mapped block: ring | completion words | exit word
+    ProxyCmd *hostRing = nullptr;
+    uint64_t *done = nullptr;
+    uint64_t *exitWord = nullptr;
+    ProxyShared *shared = nullptr;  // device memory
+    cudaStream_t stream = nullptr;  // proxy launches only: a new launch starts after the previous kernel has gone
+    uint64_t posted = 0;            // number of commands written so far
+    uint64_t nextStart = 0;         // first command the next launch takes
+    uint64_t launches = 0;          // launches so far (the kernel tags its ring entries with it)
+    bool launched = false;          // a kernel was launched and its exit word has not been seen yet
+    std::atomic<bool> broken{false}; // set-up or a launch failed: the proxy is not used again, its pending commands fail
+};
+
 // Per-device resources of one engine.
 struct DeviceCtx {
     int device = -1;
@@ -142,6 +158,7 @@ struct DeviceCtx {
     std::unique_ptr<DeviceArena> arena;
     std::unique_ptr<CounterPool> counters;
     FlagPool flags;
+    std::unique_ptr<Proxy> proxy;      // created with the first small request
     int gridCtas = 0;
     int smCount = 148;
 };
@@ -151,7 +168,16 @@ struct KernelBatch {
     std::vector<XferDesc> descs;   // copied by the kernel (dropped once they sit in the launch parameters / device table)
     std::vector<XferDesc> ceDescs; // large descriptors handed to the copy engines, one cudaMemcpyAsync each
     XferLaunch launch{};
-    void *table = nullptr; // arena block holding table + chunk starts (nullptr when inline)
+    void *table = nullptr; // arena block holding table + chunk starts (nullptr when only inline)
+    const XferDesc *tableDev = nullptr;   // the uploaded table and chunk starts inside `table`
+    const uint32_t *startsDev = nullptr;
+    bool proxyEligible = false; // small, kernel-only: may go through the doorbell proxy
+    bool tableReady = false;    // the upload has been seen complete
+    uint32_t uniformChunks = 0; // chunks per descriptor when every descriptor has the same number, else 0
+    bool viaProxy = false;      // the post in flight went through the proxy
+    uint64_t proxyCmd = 0;      // its command number
+    struct Proxy *proxy = nullptr; // the proxy it went through
+    XferDesc single{};          // the one descriptor of a one-descriptor batch
     unsigned int *counter = nullptr;
     uint64_t *flag = nullptr;      // completion word (FlagPool)
     cudaStream_t stream = nullptr; // engine stream this batch posts on unless the caller names one
@@ -247,6 +273,9 @@ private:
     bool peerAlive(const PeerId &peer, bool force = false) const;
     std::shared_ptr<const PeerId> findPeer(const std::string &agent, uint64_t *gen = nullptr) const;
     void destroyReq(ReqH *req) const; // waits for launched work, frees device resources, deletes
+    bool postViaProxy(DeviceCtx *c, KernelBatch &b) const; // false: take the launch path
+    void proxyEnsureRunning(DeviceCtx *c, Proxy &px) const; // px.mu held
+    int proxyDone(DeviceCtx *c, KernelBatch &b) const; // 1 complete, 0 in progress, -1 the proxy failed
     nixl_status_t sendNotif(const PeerId &peer, const std::string &msg) const;
     nixl_status_t finishIfDone(ReqH *req) const; // data complete -> deliver notification
     nixl_status_t pollData(ReqH *req) const;
@@ -271,6 +300,12 @@ private:
     bool livenessPing_ = false;
 
     int numStreams_ = 4;
+    // Doorbell proxy for small requests ("proxy", "proxy_max_bytes", "proxy_workers", "proxy_idle_us", "proxy_life_us").
+    bool proxyEnabled_ = true;
+    size_t proxyMaxBytes_ = size_t(2) << 20;
+    int proxyWorkers_ = 24;
+    uint64_t proxyIdleNs_ = 100000;
+    uint64_t proxyLifeNs_ = 2000000;
 
     mutable std::mutex peersMu_;
     std::unordered_map<std::string, std::shared_ptr<const PeerId>> peers_;

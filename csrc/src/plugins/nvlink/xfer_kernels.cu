@@ -49,11 +49,11 @@ __device__ __forceinline__ void st_stream32(void *p, const Vec32 &r) {
                  : "memory");
 }
 
-// Copies n bytes with the whole CTA.  Fastest path: source and destination share their offset
+// Copies n bytes with a group of kGroup threads (tid = index within the group).  Fastest path: source and destination share their offset
 // within 32 bytes, so after a short head both take 256-bit accesses (sm_100: one warp
 // instruction moves 1 KiB).  Otherwise 16-byte, 4-byte or byte accesses by relative alignment.
-__device__ __forceinline__ void copyRange(const char *__restrict__ s, char *__restrict__ d, size_t n) {
-    const unsigned tid = threadIdx.x;
+template<int kGroup> __device__ __forceinline__ void copyRangeBy(const char *__restrict__ s, char *__restrict__ d, size_t n, const unsigned tid) {
+    constexpr int kThreads = kGroup; // the threads that share this range: a whole CTA, or one warp
     if ((((uintptr_t)s ^ (uintptr_t)d) & 31) == 0) {
         size_t head = (32 - ((uintptr_t)s & 31)) & 31;
         if (head > n) head = n;
@@ -113,6 +113,10 @@ __device__ __forceinline__ void copyRange(const char *__restrict__ s, char *__re
     } else {
         for (size_t i = tid; i < n; i += kThreads) d[i] = s[i];
     }
+}
+
+__device__ __forceinline__ void copyRange(const char *__restrict__ s, char *__restrict__ d, size_t n) {
+    copyRangeBy<kThreads>(s, d, n, threadIdx.x);
 }
 
 // Which descriptor owns chunk c?  Upper-bound search in the prefix array.
@@ -345,9 +349,252 @@ __global__ void __launch_bounds__(128) batchCopyBulk(const __grid_constant__ Xfe
     }
 }
 
+// ------------------------------------------------------------------ doorbell proxy (contract: xfer_kernels.h)
+
+constexpr uint64_t kProxyGraceNs = 1000000000ull; // a worker that has not heard from the polling CTA for lifeNs + 1 s leaves
+
+__device__ __forceinline__ void ldVolatile16(const void *p, uint64_t &x, uint64_t &y) {
+    asm volatile("ld.volatile.global.v2.u64 {%0,%1}, [%2];" : "=l"(x), "=l"(y) : "l"(p) : "memory");
+}
+__device__ __forceinline__ void stReleaseGpu(uint64_t *p, uint64_t v) {
+    asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ uint64_t ldVolatile8(const void *p) {
+    uint64_t v;
+    asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// Sequence word of a device-ring entry: launch number in the top 16 bits, command number + 1 below.
+__device__ __forceinline__ uint64_t ringTag(uint64_t gen, uint64_t n) { return ((gen & 0xffffull) << 48) | ((n + 1) & 0xffffffffffffull); }
+
+struct ProxyWork {
+    uint64_t a, b, kind, count;
+    uint32_t shift, per, total;
+};
+
+__device__ __forceinline__ ProxyWork proxyDecode(uint64_t a, uint64_t b, uint64_t c) {
+    ProxyWork w;
+    w.a = a;
+    w.b = b;
+    w.kind = (c >> 44) & 15u;
+    w.shift = static_cast<uint32_t>((c >> 38) & 63u);
+    const uint64_t low = c & ((1ull << 38) - 1);
+    if (w.kind == kProxyInline) {
+        w.count = low;
+        w.per = 0;
+        w.total = static_cast<uint32_t>((low + (uint64_t(1) << w.shift) - 1) >> w.shift);
+    } else {
+        w.count = low & 0xffffffull;
+        w.per = static_cast<uint32_t>(low >> 24);
+        // The tables of a request may have been written while this kernel was already running: read
+        // them past L1 (ld.global.cg), never through the non-coherent path.
+        w.total = w.kind == kProxyTable ? (w.per ? w.per * static_cast<uint32_t>(w.count) : __ldcg(reinterpret_cast<const uint32_t *>(b) + w.count)) : 0;
+    }
+    return w;
+}
+
+// One warp copies chunk `ch` of the command.
+__device__ __forceinline__ void proxyCopyChunk(const ProxyWork &w, uint32_t ch, unsigned lane) {
+    const size_t chunk = size_t(1) << w.shift;
+    if (w.kind == kProxyInline) {
+        const size_t off = size_t(ch) << w.shift;
+        const size_t len = w.count - off < chunk ? w.count - off : chunk;
+        copyRangeBy<32>(reinterpret_cast<const char *>(w.a) + off, reinterpret_cast<char *>(w.b) + off, len, lane);
+        return;
+    }
+    const XferDesc *table = reinterpret_cast<const XferDesc *>(w.a);
+    const uint32_t *starts = reinterpret_cast<const uint32_t *>(w.b);
+    uint32_t i, first;
+    if (w.per) { // every descriptor has the same number of chunks: no search
+        i = ch / w.per;
+        first = i * w.per;
+    } else {
+        i = ownerOf(ch, static_cast<uint32_t>(w.count), [&](uint32_t k) { return __ldcg(starts + k); });
+        first = __ldcg(starts + i);
+    }
+    const uint64_t src = __ldcg(&table[i].src), dst = __ldcg(&table[i].dst), dlen = __ldcg(&table[i].len);
+    const size_t off = size_t(ch - first) << w.shift;
+    const size_t len = dlen - off < chunk ? dlen - off : chunk;
+    copyRangeBy<32>(reinterpret_cast<const char *>(src) + off, reinterpret_cast<char *>(dst) + off, len, lane);
+}
+
+constexpr unsigned kProxyWarps = kThreads / 32;
+constexpr unsigned kProxyChunksPerWarp = 2; // chunks one warp takes of a command before another CTA is drawn in
+
+__global__ void __launch_bounds__(kThreads) proxyKernel(const __grid_constant__ ProxyLaunch p) {
+    __shared__ ProxyCmd cmd;
+    __shared__ unsigned long long cmdNumber;
+    const unsigned workers = gridDim.x - 1;
+    const unsigned lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+
+    if (blockIdx.x == 0) {
+        // ---------------- polling CTA: host ring -> device ring; commands of at most one chunk per warp it runs itself.
+        uint64_t n = p.start, floor_head = 0;
+        const uint64_t t_start = globalTimerNs();
+        uint64_t t_last = t_start;
+        bool skip_owed = false; // a command this CTA ran itself has not been entered in the device ring yet
+        uint32_t empty_polls = 0; // polls that found nothing since the last command
+        for (;;) {
+            if (threadIdx.x == 0) {
+                // Room in the device ring: no worker may be a whole ring behind command `upto`.  Workers wait for
+                // nothing but this CTA and their own copies, so the wait ends; it is bounded all the same.
+                auto wait_room = [&](uint64_t upto) {
+                    while (upto - floor_head >= kProxySlots) {
+                        uint64_t m = ~0ull;
+                        for (unsigned w = 0; w < workers; ++w) {
+                            const uint64_t h = ldVolatile8(&p.shared->workerHead[w]);
+                            m = h < m ? h : m;
+                        }
+                        floor_head = m;
+                        if (globalTimerNs() - t_start > p.lifeNs + kProxyGraceNs) break;
+                    }
+                };
+                auto publish = [&](uint64_t a, uint64_t b, uint64_t c) {
+                    wait_room(n);
+                    ProxyCmd *d = &p.shared->ring[n % kProxySlots];
+                    d->a = a;
+                    d->b = b;
+                    d->c = c;
+                    stReleaseGpu(&d->seq, ringTag(p.gen, n));
+                };
+                if (skip_owed) { // the workers just step over a command that was run here
+                    n -= 1;
+                    publish(0, 0, proxyPackC(n + 1, kProxySkip, 0, 0));
+                    n += 1;
+                    skip_owed = false;
+                }
+                for (;;) {
+                    // Two slots per poll, all four loads in flight together: when requests stream in, one PCIe
+                    // round trip hands over two commands.
+                    const ProxyCmd *slot = p.hostRing + (n % kProxySlots), *next = p.hostRing + ((n + 1) % kProxySlots);
+                    uint64_t seq, a, b, c, seq2, a2, b2, c2;
+                    ldVolatile16(&slot->seq, seq, a);
+                    ldVolatile16(&slot->b, b, c);
+                    ldVolatile16(&next->seq, seq2, a2);
+                    ldVolatile16(&next->b, b2, c2);
+                    const uint64_t now = globalTimerNs();
+                    bool leave = now - t_start > p.lifeNs;
+                    if (seq == n + 1 && (c >> 48) == ((n + 1) & 0xffffull)) {
+                        t_last = now;
+                        const bool second = seq2 == n + 2 && (c2 >> 48) == ((n + 2) & 0xffffull);
+                        const uint64_t kind = (c >> 44) & 15u, low = c & ((1ull << 38) - 1);
+                        const uint32_t shift = static_cast<uint32_t>((c >> 38) & 63u);
+                        // Small enough for this CTA alone?  (inline: by length; table: only when the chunk count is in the command)
+                        const uint64_t chunks = kind == kProxyInline ? (low + (uint64_t(1) << shift) - 1) >> shift : (low >> 24) * (low & 0xffffffull);
+                        // ... and nothing queued around it?  A command found by the first poll after the previous one, or
+                        // with a successor already waiting, is part of a stream, and the workers overlap those; one that
+                        // arrives alone after an idle poll is run here, which saves the hop through the device ring.
+                        const bool alone = empty_polls > 0 && !second;
+                        empty_polls = 0;
+                        if (alone && chunks >= 1 && chunks <= kProxyWarps) {
+                            skip_owed = true; // entered in the device ring after the copy: off the critical path
+                            cmd.a = a;
+                            cmd.b = b;
+                            cmd.c = c;
+                            cmdNumber = n;
+                            ++n;
+                            break; // run it (all threads, below)
+                        }
+                        publish(a, b, c);
+                        ++n;
+                        if (second) {
+                            publish(a2, b2, c2);
+                            ++n;
+                        }
+                    } else {
+                        ++empty_polls;
+                        if (now - t_last > p.idleNs) leave = true;
+                    }
+                    if (leave) {
+                        publish(0, 0, proxyPackC(n + 1, kProxyExit, 0, 0));
+                        st_release_sys(p.exitWord, (1ull << 63) | n);
+                        cmd.c = proxyPackC(0, kProxyExit, 0, 0);
+                        break;
+                    }
+                }
+            }
+            __syncthreads();
+            const uint64_t a = cmd.a, b = cmd.b, c = cmd.c;
+            const uint64_t number = cmdNumber;
+            __syncthreads();
+            if (((c >> 44) & 15u) == kProxyExit) return;
+            const ProxyWork w = proxyDecode(a, b, c);
+            if (warp < w.total) proxyCopyChunk(w, warp, lane);
+            __syncthreads();
+            if (threadIdx.x == 0) st_release_sys(&p.done[number % kProxySlots], number + 1);
+        }
+    }
+
+    // ---------------- worker CTAs
+    const unsigned w = blockIdx.x - 1;
+    const uint64_t t_start = globalTimerNs();
+    if (threadIdx.x == 0) *reinterpret_cast<volatile unsigned long long *>(&p.shared->workerHead[w]) = p.start;
+    for (uint64_t n = p.start;; ++n) {
+        if (threadIdx.x == 0) {
+            ProxyCmd *slot = &p.shared->ring[n % kProxySlots];
+            const uint64_t expect = ringTag(p.gen, n);
+            uint32_t spins = 0;
+            uint64_t seq, a, b, c;
+            for (;;) {
+                // both halves in flight at once; c repeats the low bits of the command number, so a half read
+                // before the polling CTA had written it is recognised
+                ldVolatile16(&slot->seq, seq, a);
+                ldVolatile16(&slot->b, b, c);
+                if (seq == expect && (c >> 48) == ((n + 1) & 0xffffull)) break;
+                if ((++spins & 1023u) == 0 && globalTimerNs() - t_start > p.lifeNs + kProxyGraceNs) {
+                    c = proxyPackC(0, kProxyExit, 0, 0);
+                    break;
+                }
+            }
+            asm volatile("fence.acq_rel.gpu;" ::: "memory"); // the command's tables are read after the command
+            cmd.a = a;
+            cmd.b = b;
+            cmd.c = c;
+        }
+        __syncthreads();
+        const uint64_t a = cmd.a, b = cmd.b, c = cmd.c;
+        __syncthreads(); // everyone has its copy before thread 0 fetches the next command
+        const uint64_t kind = (c >> 44) & 15u;
+        if (kind == kProxyExit) return;
+        if (kind != kProxySkip) {
+            const ProxyWork work = proxyDecode(a, b, c);
+            // Every warp takes whole chunks, so that a batch of 4 KiB descriptors keeps sixteen of them in flight
+            // per CTA; a command draws in only as many CTAs as it has chunks for, and the first one rotates with the
+            // command number, so that consecutive commands run side by side on different CTAs.
+            const unsigned per_cta = kProxyWarps * kProxyChunksPerWarp;
+            const unsigned want = (work.total + per_cta - 1) / per_cta;
+            const unsigned parts = want < workers ? want : workers;
+            const unsigned r = (w + workers - static_cast<unsigned>(n % workers)) % workers;
+            if (r < parts) {
+                for (uint32_t ch = r * kProxyWarps + warp; ch < work.total; ch += parts * kProxyWarps) proxyCopyChunk(work, ch, lane);
+                __syncthreads();
+                if (threadIdx.x == 0) {
+                    bool last = true;
+                    if (parts > 1) {
+                        unsigned prev;
+                        unsigned int *ctr = &p.shared->counter[n % kProxySlots];
+                        asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(prev) : "l"(ctr) : "memory");
+                        last = prev == parts - 1;
+                        if (last) *ctr = 0;
+                    }
+                    if (last) st_release_sys(&p.done[n % kProxySlots], n + 1);
+                }
+            }
+        }
+        if (threadIdx.x == 0) *reinterpret_cast<volatile unsigned long long *>(&p.shared->workerHead[w]) = n + 1;
+    }
+}
+
 __global__ void signalOnly(uint64_t *flag, uint64_t seq) { st_release_sys(flag, seq); }
 
 } // namespace
+
+cudaError_t launchProxy(const ProxyLaunch &p, int workers, cudaStream_t stream) {
+    if (workers < 1 || workers > kProxyMaxWorkers || !p.hostRing || !p.shared || !p.done || !p.exitWord) return cudaErrorInvalidValue;
+    proxyKernel<<<workers + 1, kThreads, 0, stream>>>(p);
+    return cudaGetLastError();
+}
 
 cudaError_t launchSignal(uint64_t *hostFlag, uint64_t seq, cudaStream_t stream) {
     signalOnly<<<1, 1, 0, stream>>>(hostFlag, seq);
