@@ -959,13 +959,15 @@ def extras_ep(env, args, headline_gbs, budget_s):
 
         def do_dispatch():
             if compact:
-                state["rx"], state["sc"], state["h"] = buf.dispatch(x, idx, use_fp8=True)
+                # the weights go along: the expert ranks can then add a token's rows up before they return one row
+                state["rx"], state["sc"], state["h"] = buf.dispatch(x, idx, use_fp8=True, topk_weights=w)
             else:
                 (rx, sc), _, h, _, _ = buf.low_latency_dispatch(x, idx, use_fp8=True)
                 state["rx"], state["sc"], state["h"] = rx.view(-1, H), sc.view(-1, H // 128), h
 
         def do_combine():
-            # the expert GEMM writes into the exposed buffer, the home ranks pull their rows from it
+            # the expert GEMM writes into the exposed buffer; low-latency mode: the home ranks pull their rows from it;
+            # throughput mode: each expert rank reduces a token's rows and stores one row at the token's home rank
             src = buf.get_next_combine_buffer(state["h"])
             if compact:
                 state["o"] = buf.combine(src.view(-1, H), idx, w, state["h"])
@@ -1020,11 +1022,13 @@ def extras_ep(env, args, headline_gbs, budget_s):
             "tokens_per_gpu": T, "dispatch_us": round(t_disp, 1), "combine_us": round(t_comb, 1), "dispatch_plus_combine_us": round(t_both, 1),
             "recv_rows_rank0": recv_rows, "status": buf.status, "verified": all_agree(env, good), "max_abs_err": round(max_over_ranks(env, [max_err])[0], 4),
             "fraction_within_bf16_tolerance": round(min_over_ranks(env, [frac_tight])[0], 5),
-            "combine": "pull (home ranks load expert outputs from the exposed buffer)",
+            "combine": "rank-reduced (expert ranks add a token's rows up, one row per (token, rank) returns)" if compact else
+                       "pull (home ranks load expert outputs from the exposed buffer)",
         }
         # wire bytes per GPU and the link-time bound (rows that leave this GPU; about (W-1)/W of the copies)
         remote_rows = int(((idx // El) != rank).sum())
-        wire = remote_rows * (H + H // 128 * 4) + remote_rows * H * 2
+        remote_pairs = int(sum(int((((idx // El) == r).any(dim=1)).sum()) for r in range(W) if r != rank))  # (token, remote rank) pairs
+        wire = remote_rows * (H + H // 128 * 4) + (remote_pairs if compact else remote_rows) * H * 2
         rec["wire_bytes_per_gpu"] = wire
         if W > 1:
             rec["fraction_of_900GBps_link_bound"] = round((wire / 900e9 * 1e6) / t_both, 3)

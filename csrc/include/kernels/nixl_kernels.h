@@ -92,7 +92,19 @@ typedef struct NixlEpLayout {
     int64_t off_comb_x;      /* bf16   [M][K][H] combine landing zone */
     int64_t off_comb_flag;   /* uint64 [R]      epoch once rank r finished its combine sends (push) / its outputs are ready (pull) */
     int64_t off_comb_in;     /* bf16   [cap][H] expert outputs exposed to peers (pull-mode combine), rows as in recv_x */
+    int64_t off_grp;         /* NixlEpGroupRecord [R][M]: per source rank and token, the token's rows on this rank and their weights */
+    int64_t off_grp_tokens;  /* int32  [R]      tokens source rank r dispatched (how many of its records are valid) */
 } NixlEpLayout;
+
+/* What a token's home rank tells an expert rank about the token's copies there (written by a dispatch
+ * that was given the top-k weights): the rank-reduced combine adds those rows up, weighted, on the
+ * expert rank and returns ONE row per (token, rank) instead of one per (token, expert). */
+typedef struct NixlEpGroupRecord {
+    int32_t n;        /* copies of the token on this rank, 0..8 */
+    int32_t pad[3];
+    int32_t rows[8];  /* their rows in the receive buffer */
+    float w[8];       /* their top-k weights */
+} NixlEpGroupRecord;
 
 typedef struct NixlEpScratch { /* device memory private to the rank; zero before first use */
     int32_t *cnt;      /* [E] */
@@ -124,6 +136,8 @@ typedef struct NixlEpDispatchParams {
     int32_t *send_row;        /* out [T][K] (optional) row each (token, k) landed on at its receiver, -1 if not sent */
     int32_t use_ue8m0;        /* 1 (with use_fp8): scales are powers of two, delivered as biased exponent bytes, four per
                                  32-bit word: recv_scales is uint8 [cap][H/128] with a row pitch of H/128 bytes */
+    const float *topk_weights; /* [T][K] or NULL.  Given (K <= 8, R <= 32): group records are written for the rank-reduced combine */
+    int32_t max_tokens;       /* M: row pitch of the group records and of the rank-reduced landing zone */
 } NixlEpDispatchParams;
 
 typedef struct NixlEpCombineParams {
@@ -151,6 +165,11 @@ typedef struct NixlEpCombineParams {
      * per-128-channel grid plus sign; 0.66 of the bf16 bytes) and are decoded inside the reduction.
      * Needs H % 512 == 0. */
     int32_t use_logfmt;
+    /* Rank-reduced mode (pull == 2; the dispatch wrote group records): every expert rank adds up, per token, the
+     * rows it holds for it, weighted, and stores that one row at the token's home rank (landing row
+     * expert_rank * max_tokens + token); the home rank adds the rows of the ranks the token went to.  A token
+     * whose experts sit on fewer ranks than it has experts crosses NVLink that much less often. */
+    int32_t max_tokens;
 } NixlEpCombineParams;
 
 /* Routing statistics of topk_idx [T][K]: tokens per destination rank (a token counts once per rank),

@@ -203,6 +203,7 @@ __global__ void __launch_bounds__(kThreads, 1) epDispatchKernel(const __grid_con
             if (peer == nullptr) continue;
             int *dst = reinterpret_cast<int *>(peer + p.lay.off_counts) + static_cast<long long>(p.rank) * p.E;
             for (int e = tid; e < p.E; e += kThreads) dst[e] = ldVolatile(p.scr.cnt + e);
+            if (tid == 0) reinterpret_cast<int *>(peer + p.lay.off_grp_tokens)[p.rank] = p.topk_weights != nullptr ? p.T : 0;
             // Experts of that rank that get nothing from us are complete right away.
             uint64_t *dflag = reinterpret_cast<uint64_t *>(peer + p.lay.off_disp_flag);
             __syncthreads();
@@ -359,6 +360,32 @@ __global__ void __launch_bounds__(kThreads, 1) epDispatchKernel(const __grid_con
                 if (gtid == 0) {
                     uint2 info = make_uint2(static_cast<unsigned>(p.rank), static_cast<unsigned>(t * p.K + k));
                     *reinterpret_cast<uint2 *>(peer + p.lay.off_recv_info + row * 8) = info;
+                }
+            }
+            // Group record of this token for every rank that got copies of it (lane d serves rank d): the rows
+            // and their weights, tagged with the step number so that what an earlier step left in the slot
+            // is never taken for new.  Ranks without a copy get nothing; their slot keeps an old tag.
+            if (p.topk_weights != nullptr && gtid < p.R) {
+                const int d = gtid;
+                alignas(16) NixlEpGroupRecord rec;
+                rec.n = 0;
+                for (int k = 0; k < p.K && k < 8; ++k)
+                    if (rows[k] >= 0 && dests[k] == d) {
+                        rec.rows[rec.n] = rows[k];
+                        rec.w[rec.n] = p.topk_weights[static_cast<long long>(t) * p.K + k];
+                        ++rec.n;
+                    }
+                if (rec.n > 0) {
+                    for (int i = rec.n; i < 8; ++i) {
+                        rec.rows[i] = 0;
+                        rec.w[i] = 0.f;
+                    }
+                    rec.pad[0] = static_cast<int>(p.epoch & 0x7fffffffull);
+                    rec.pad[1] = rec.pad[2] = 0;
+                    uint4 *dst = reinterpret_cast<uint4 *>(peer_sh[d] + p.lay.off_grp) + (static_cast<long long>(p.rank) * p.max_tokens + t) * 5;
+                    const uint4 *src = reinterpret_cast<const uint4 *>(&rec);
+#pragma unroll
+                    for (int i = 0; i < 5; ++i) stPeer16(dst + i, src[i]);
                 }
             }
             groupBarrier(bar_id, nt); // all stores of this token issued (and the buffer is free for the next one)
@@ -595,6 +622,149 @@ __device__ __forceinline__ void epCombinePull(const NixlEpCombineParams &p) {
     else pullReduce<kMaxTopk, false>(p, El, vecs, nt, groups_per_cta, grp, gtid);
 }
 
+// Rank-reduced combine (NixlEpCombineParams::max_tokens).  Phase 1, expert rank: one warp per (token, home
+// rank) group record adds the token's rows up in fp32, weighted, and stores ONE bf16 row at the home rank.
+// Phase 2, home rank: add the rows of the ranks the token went to.
+__device__ __forceinline__ void epCombineRankReduce(const NixlEpCombineParams &p) {
+    const int El = p.E / p.R;
+    const int tid = threadIdx.x, lane = tid & 31;
+    char *self = peerBase(p.peers, p.rank);
+    const int vecs = p.H / 8;
+    const long long M = p.max_tokens;
+    const int tag = static_cast<int>(p.epoch & 0x7fffffffull);
+
+    if (p.phases & 1) {
+        const __nv_bfloat16 *x = static_cast<const __nv_bfloat16 *>(p.x);
+        const int *tokens_of = reinterpret_cast<const int *>(self + p.lay.off_grp_tokens);
+        const uint4 *records = reinterpret_cast<const uint4 *>(self + p.lay.off_grp);
+        int max_t = 0;
+        for (int r = 0; r < p.R; ++r) {
+            const int n = ldVolatile(tokens_of + r);
+            max_t = n > max_t ? (n < M ? n : static_cast<int>(M)) : max_t;
+        }
+        const long long items = static_cast<long long>(max_t) * p.R;
+        const long long warps = static_cast<long long>(gridDim.x) * (kThreads / 32);
+        // item = token * R + home rank: neighbouring warps store to different peers
+        for (long long i = static_cast<long long>(blockIdx.x) * (kThreads / 32) + (tid >> 5); i < items; i += warps) {
+            const int r = static_cast<int>(i % p.R);
+            const long long t = i / p.R;
+            if (t >= ldVolatile(tokens_of + r) || ldVolatile(p.scr.mask + r) != 0) continue;
+            char *peer = peerBase(p.peers, r);
+            if (peer == nullptr) continue;
+            const uint4 *rec = records + (static_cast<long long>(r) * M + t) * 5;
+            const uint4 head = rec[0];
+            const int n = static_cast<int>(head.x);
+            if (static_cast<int>(head.y) != tag || n <= 0 || n > 8) continue;
+            const uint4 r0 = rec[1], r1 = rec[2], w0 = rec[3], w1 = rec[4];
+            const int rows[8] = {int(r0.x), int(r0.y), int(r0.z), int(r0.w), int(r1.x), int(r1.y), int(r1.z), int(r1.w)};
+            const float w[8] = {__uint_as_float(w0.x), __uint_as_float(w0.y), __uint_as_float(w0.z), __uint_as_float(w0.w),
+                                __uint_as_float(w1.x), __uint_as_float(w1.y), __uint_as_float(w1.z), __uint_as_float(w1.w)};
+            const uint4 *src[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) src[k] = reinterpret_cast<const uint4 *>(x + static_cast<long long>(k < n ? rows[k] : rows[0]) * p.H);
+            uint4 *dst = reinterpret_cast<uint4 *>(peer + p.lay.off_comb_x + (static_cast<long long>(p.rank) * M + t) * p.H * 2);
+            constexpr int kU = 2; // vector positions in flight per lane (times up to eight rows)
+            for (int v0 = lane; v0 < vecs; v0 += 32 * kU) {
+                uint4 raw[kU][8];
+#pragma unroll
+                for (int u = 0; u < kU; ++u)
+#pragma unroll
+                    for (int k = 0; k < 8; ++k)
+                        if (k < n && v0 + u * 32 < vecs) raw[u][k] = ldNc(src[k] + v0 + u * 32);
+#pragma unroll
+                for (int u = 0; u < kU; ++u) {
+                    if (v0 + u * 32 >= vecs) continue;
+                    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) {
+                        if (k >= n) continue;
+                        const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&raw[u][k]);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const float2 f = __bfloat1622float2(h[j]);
+                            acc[2 * j] = fmaf(w[k], f.x, acc[2 * j]);
+                            acc[2 * j + 1] = fmaf(w[k], f.y, acc[2 * j + 1]);
+                        }
+                    }
+                    uint4 o;
+                    __nv_bfloat162 *oh = reinterpret_cast<__nv_bfloat162 *>(&o);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) oh[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+                    stPeer16(dst + v0 + u * 32, o);
+                }
+            }
+        }
+        __syncthreads();
+        if (tid == 0) __threadfence_system();
+        gridBarrier(p.scr.barrier, p.scr.status, p.timeout_ns);
+        // Everybody's rows are out: tell each home rank.
+        for (int d = blockIdx.x; d < p.R; d += gridDim.x) {
+            if (ldVolatile(p.scr.mask + d) != 0) continue;
+            char *peer = peerBase(p.peers, d);
+            if (peer != nullptr && tid == 0) {
+                __threadfence_system();
+                stReleaseSys(reinterpret_cast<uint64_t *>(peer + p.lay.off_comb_flag) + p.rank, p.epoch);
+            }
+        }
+    }
+
+    if (p.phases & 2) {
+        const uint64_t *flag = reinterpret_cast<const uint64_t *>(self + p.lay.off_comb_flag);
+        if (tid < p.R && ldVolatile(p.scr.mask + tid) == 0 && peerBase(p.peers, tid) != nullptr) {
+            if (!waitFlag(flag + tid, p.epoch, p.timeout_ns)) {
+                atomicExch(p.scr.mask + tid, 1);
+                atomicOr(p.scr.status, ST_PEER_TIMEOUT);
+            }
+        }
+        __syncthreads();
+        const __nv_bfloat16 *landing = reinterpret_cast<const __nv_bfloat16 *>(self + p.lay.off_comb_x);
+        __nv_bfloat16 *out = static_cast<__nv_bfloat16 *>(p.out);
+        const int nt = threadsPerItem(p.T);
+        const int groups_per_cta = kThreads / nt;
+        const int grp = tid / nt, gtid = tid - grp * nt;
+        for (int t = blockIdx.x * groups_per_cta + grp; t < p.T; t += gridDim.x * groups_per_cta) {
+            // ranks that hold copies of this token (and answered)
+            unsigned ranks = 0;
+            for (int k = 0; k < p.K; ++k) {
+                const long long e = p.topk_idx[static_cast<long long>(t) * p.K + k];
+                if (e >= 0 && e < p.E && ldVolatile(p.scr.mask + static_cast<int>(e) / El) == 0) ranks |= 1u << (static_cast<int>(e) / El);
+            }
+            for (int v = gtid; v < vecs; v += nt) {
+                float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                uint4 raw[8];
+                unsigned left = ranks;
+                while (left) { // eight rows' vectors in flight at a time
+                    int ds[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        ds[j] = left ? __ffs(left) - 1 : -1;
+                        left &= left - 1; // (0 stays 0)
+                    }
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        if (ds[j] >= 0) raw[j] = *reinterpret_cast<const uint4 *>(landing + (static_cast<long long>(ds[j]) * M + t) * p.H + v * 8);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        if (ds[j] < 0) continue;
+                        const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&raw[j]);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const float2 f = __bfloat1622float2(h[i]);
+                            acc[2 * i] += f.x;
+                            acc[2 * i + 1] += f.y;
+                        }
+                    }
+                }
+                uint4 o;
+                __nv_bfloat162 *oh = reinterpret_cast<__nv_bfloat162 *>(&o);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) oh[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+                *reinterpret_cast<uint4 *>(out + static_cast<long long>(t) * p.H + v * 8) = o;
+            }
+        }
+    }
+}
+
 __global__ void __launch_bounds__(kThreads) epCombineKernel(const __grid_constant__ NixlEpCombineParams p) {
     __shared__ int offs[kMaxRanks * 8 + 1]; // expert_offsets copy (El + 1 <= 513)
     __shared__ int cnts[kMaxRanks * 8];
@@ -603,6 +773,10 @@ __global__ void __launch_bounds__(kThreads) epCombineKernel(const __grid_constan
     char *self = peerBase(p.peers, p.rank);
     const int vecs = p.H / 8;
 
+    if (p.pull == 2) {
+        epCombineRankReduce(p);
+        return;
+    }
     if (p.pull) {
         epCombinePull(p);
         return;
@@ -838,6 +1012,7 @@ extern "C" int nixl_ep_dispatch_launch(const NixlEpDispatchParams *params, void 
         p.E / p.R > kMaxRanks * 8 || p.rank < 0 || p.rank >= p.R || p.T < 0)
         return cudaErrorInvalidValue;
     if (p.H % 512) return cudaErrorInvalidValue; // whole warps per pass; scales move as float4
+    if (p.topk_weights && (p.K > 8 || p.R > 32 || p.max_tokens < p.T)) return cudaErrorInvalidValue; // a group record holds eight copies
     if (p.rows_per_expert > 0 && static_cast<long long>(p.rows_per_expert) < static_cast<long long>(p.R) * p.T) return cudaErrorInvalidValue;
     const size_t group_bytes = (2 * kMaxTopk * sizeof(int) + size_t(p.use_fp8 ? p.H : p.H * 2) + (p.H / kGroup) * sizeof(float) + 15) & ~size_t(15);
     const size_t smem = size_t(2) * p.E * sizeof(int) + (kThreads / 32) * group_bytes + 16;
@@ -870,7 +1045,8 @@ extern "C" int nixl_ep_dispatch_launch(const NixlEpDispatchParams *params, void 
 extern "C" int nixl_ep_combine_launch(const NixlEpCombineParams *params, void *stream) {
     if (!params || !params->peers || !params->topk_idx) return cudaErrorInvalidValue;
     const NixlEpCombineParams &p = *params;
-    if (p.pull && !p.send_row) return cudaErrorInvalidValue;
+    if (p.pull == 1 && !p.send_row) return cudaErrorInvalidValue;
+    if (p.pull == 2 && (p.max_tokens <= 0 || p.R > 32 || p.T > p.max_tokens || !p.x)) return cudaErrorInvalidValue;
     if (p.use_logfmt && (p.pull || p.H % 512)) return cudaErrorInvalidValue;
     if (p.R <= 0 || p.R > kMaxRanks || p.E <= 0 || p.E % p.R || p.K <= 0 || p.K > kMaxTopk || p.H <= 0 || p.H % 8 ||
         p.E / p.R > kMaxRanks * 8 || p.rank < 0 || p.rank >= p.R)

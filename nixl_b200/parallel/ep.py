@@ -40,7 +40,8 @@ def _up(x: int, a: int = _ALIGN) -> int:
 
 class _Layout(ctypes.Structure):
     _fields_ = [(n, ctypes.c_int64) for n in (
-        "off_counts", "off_counts_flag", "off_disp_flag", "off_recv_x", "off_recv_scales", "off_recv_info", "off_comb_x", "off_comb_flag", "off_comb_in")]
+        "off_counts", "off_counts_flag", "off_disp_flag", "off_recv_x", "off_recv_scales", "off_recv_info", "off_comb_x", "off_comb_flag", "off_comb_in",
+        "off_grp", "off_grp_tokens")]
 
 
 class _Scratch(ctypes.Structure):
@@ -56,6 +57,7 @@ class _DispatchParams(ctypes.Structure):
         ("peers", ctypes.c_void_p), ("lay", _Layout), ("epoch", ctypes.c_uint64), ("timeout_ns", ctypes.c_uint64),
         ("recv_count", ctypes.c_void_p), ("layout_range", ctypes.c_void_p), ("expert_offsets", ctypes.c_void_p), ("scr", _Scratch),
         ("send_row", ctypes.c_void_p), ("use_ue8m0", ctypes.c_int32),
+        ("topk_weights", ctypes.c_void_p), ("max_tokens", ctypes.c_int32),
     ]
 
 
@@ -66,7 +68,7 @@ class _CombineParams(ctypes.Structure):
         ("T", ctypes.c_int32), ("K", ctypes.c_int32), ("H", ctypes.c_int32), ("E", ctypes.c_int32), ("R", ctypes.c_int32), ("rank", ctypes.c_int32),
         ("phases", ctypes.c_int32), ("grid", ctypes.c_int32),
         ("peers", ctypes.c_void_p), ("lay", _Layout), ("epoch", ctypes.c_uint64), ("timeout_ns", ctypes.c_uint64), ("scr", _Scratch),
-        ("pull", ctypes.c_int32), ("send_row", ctypes.c_void_p), ("use_logfmt", ctypes.c_int32),
+        ("pull", ctypes.c_int32), ("send_row", ctypes.c_void_p), ("use_logfmt", ctypes.c_int32), ("max_tokens", ctypes.c_int32),
     ]
 
 
@@ -85,6 +87,7 @@ class EPHandle:
     topk: int
     send_row: Optional[torch.Tensor] = None  # int32 [tokens, topk]: row each copy landed on at its receiver
     rows_per_expert: int = 0
+    has_group_records: bool = False  # the dispatch was given the weights: combine may reduce per rank before returning rows
 
 
 class EventOverlap:
@@ -175,8 +178,10 @@ class Buffer:
             ("off_recv_info", cap * 8),
             ("off_recv_scales", cap * (H // 128) * 4),
             ("off_recv_x", cap * H * 2),
-            ("off_comb_x", M * K * H * 2),
+            ("off_comb_x", M * max(K, R) * H * 2),  # [M][K] rows (push) or [R][M] rows (rank-reduced combine)
             ("off_comb_in", cap * H * 2),
+            ("off_grp", R * M * 80),
+            ("off_grp_tokens", R * 4),
         ):
             lay[name] = off
             off = _up(off + size)
@@ -434,7 +439,7 @@ class Buffer:
         cur.wait_stream(self._side)
         return d, handle, recv_x, scales
 
-    def _dispatch(self, x, topk_idx, use_fp8, round_scale, rows_per_expert, phases_now, hook_later, grid=0, use_ue8m0=False):
+    def _dispatch(self, x, topk_idx, use_fp8, round_scale, rows_per_expert, phases_now, hook_later, grid=0, use_ue8m0=False, topk_weights=None):
         if not self._peers_view:
             if self.num_ranks == 1:
                 self.connect_ranks(metadata=[self.local_metadata()])
@@ -489,6 +494,8 @@ class Buffer:
         p, recv_count, layout_range, expert_offsets, recv_x, scales, src_info, send_row = slot
 
         p.x, p.topk_idx, p.T = x.data_ptr(), topk_idx.data_ptr(), T
+        p.topk_weights = topk_weights.data_ptr() if topk_weights is not None else None
+        p.max_tokens = self.max_tokens
         p.round_scale = int(round_scale)
         p.peers = self._peers_view
         p.epoch = epoch
@@ -503,8 +510,9 @@ class Buffer:
 
         launch(phases_now)
         hook = (lambda: launch(2)) if hook_later else None
-        handle = EPHandle(parity, epoch, recv_count, expert_offsets, layout_range, src_info, self.max_tokens, H, K, send_row[:T], rows_per_expert)
-        keep = (x, topk_idx, p)  # the hook may launch later: keep inputs alive
+        handle = EPHandle(parity, epoch, recv_count, expert_offsets, layout_range, src_info, self.max_tokens, H, K, send_row[:T], rows_per_expert,
+                          has_group_records=topk_weights is not None)
+        keep = (x, topk_idx, topk_weights, p)  # the hook may launch later: keep inputs alive
         return recv_x, scales, handle, hook, keep
 
     # ------------------------------------------------------------------ routing statistics, reference-named entry points
@@ -534,7 +542,7 @@ class Buffer:
         than one NVLink domain; on one NVSwitch box this is the throughput-mode ``dispatch`` (rows
         arrive packed per local expert, not per token).  Returns ``(recv_x | (recv_x, scales),
         num_recv_tokens_per_expert int32 [local_experts], handle, event)``."""
-        recv_x, scales, handle = self.dispatch(x, topk_idx, use_fp8=use_fp8)
+        recv_x, scales, handle = self.dispatch(x, topk_idx, use_fp8=use_fp8, topk_weights=topk_weights)
         return ((recv_x, scales) if use_fp8 else recv_x), handle.recv_count, handle, EventOverlap(None)
 
     def ht_combine(self, x: torch.Tensor, handle: EPHandle, topk_idx: torch.Tensor, topk_weights: torch.Tensor, **_ignored):
@@ -610,8 +618,14 @@ class Buffer:
 
     # ------------------------------------------------------------------ throughput mode
 
-    def dispatch(self, x: torch.Tensor, topk_idx: torch.Tensor, use_fp8: bool = True, round_scale: bool = False, use_ue8m0: bool = False):
+    def dispatch(self, x: torch.Tensor, topk_idx: torch.Tensor, use_fp8: bool = True, round_scale: bool = False, use_ue8m0: bool = False,
+                 topk_weights: Optional[torch.Tensor] = None):
         """Throughput-mode dispatch: compact layout.
+
+        With ``topk_weights`` (float32 ``[tokens, topk]``, ``topk <= 8``) the expert ranks are also told which of
+        their rows belong to one token and with which weights; ``combine`` then adds those rows up on the
+        expert rank and returns one row per (token, rank) instead of one per (token, expert): with top-8
+        routing over 8 ranks about a third fewer bytes come back over NVLink.
 
         Returns ``(recv_x [rows, hidden], scales [rows, hidden//128] | None, handle)``; rows of
         local expert ``e`` are ``handle.expert_offsets[e] : handle.expert_offsets[e] + handle.recv_count[e]``.
@@ -619,7 +633,13 @@ class Buffer:
         form ``grouped_gemm_mxfp8`` consumes."""
         if use_ue8m0 and (not use_fp8 or self.hidden % 512):
             raise ValueError("UE8M0 scales need fp8 dispatch and hidden % 512 == 0")
-        recv_x, scales, handle, _, keep = self._dispatch(x, topk_idx, use_fp8, round_scale, 0, 3, False, use_ue8m0=use_ue8m0)
+        if topk_weights is not None:
+            if topk_weights.dtype != torch.float32 or not topk_weights.is_contiguous() or topk_weights.shape != topk_idx.shape:
+                raise TypeError("topk_weights must be contiguous float32 of topk_idx's shape")
+            if topk_idx.shape[1] > 8 or self.num_ranks > 32:
+                topk_weights = None  # a group record holds eight copies: fall back to the per-copy combine
+        recv_x, scales, handle, _, keep = self._dispatch(x, topk_idx, use_fp8, round_scale, 0, 3, False, use_ue8m0=use_ue8m0,
+                                                         topk_weights=topk_weights)
         self._keep = keep
         return recv_x, scales, handle
 
@@ -643,17 +663,22 @@ class Buffer:
                 out = torch.empty(T, self.hidden, dtype=torch.bfloat16, device=self.device)
         rows = self.ll_rows if handle.rows_per_expert else self.compact_rows
         staged = self._region(handle.parity, "off_comb_in", rows * self.hidden * 2).view(torch.bfloat16).view(rows, self.hidden)
+        if pull is None and handle.has_group_records and not use_logfmt and self.combine_pull is None:
+            pull = 2  # the expert ranks know which rows belong to one token: one row per (token, rank) comes back
         if pull is None:
             # Unless told otherwise: pull when the caller wrote its outputs into the exposed buffer
             # (nothing to copy), push when they live elsewhere (staging them first costs more than it saves).
             pull = self.combine_pull if self.combine_pull is not None else x.data_ptr() == staged.data_ptr()
-        if pull:
+        if pull == 2 and not handle.has_group_records:
+            raise ValueError("rank-reduced combine needs a dispatch that was given topk_weights")
+        if pull == 1 or pull is True:
             if x.shape[0] > rows:
                 raise ValueError("combine input has more rows than the buffer holds")
             if x.data_ptr() != staged.data_ptr():
                 staged[: x.shape[0]].copy_(x)  # callers that write into get_next_combine_buffer() skip this copy
         p = self._comb_params
         p.pull = int(pull)
+        p.max_tokens = self.max_tokens
         p.use_logfmt = int(use_logfmt)
         p.send_row = handle.send_row.data_ptr() if pull else None
         p.x = x.data_ptr()

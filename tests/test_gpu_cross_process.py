@@ -1,0 +1,300 @@
+"""One process per rank, as a deployment runs it: memory of the other process is reached through
+its exported handle (the NVLINK backend's IPC path), metadata travels through queues or a store.
+
+Covers transfers (small ones through the doorbell proxy, batches through the copy kernel, long runs
+through the copy engines), notifications, the GPU-initiated put, the fused KV transfer and
+expert-parallel dispatch / combine with value checks on every rank.  Ranks sit on different GPUs
+when there are several; the cases whose kernels wait for a peer need that and are skipped on one
+GPU (two kernels that wait for each other must not share a GPU)."""
+import multiprocessing as mp
+import os
+import socket
+import traceback
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _child(fn, rank, world, queues, results, barrier, extra):
+    try:
+        import sys
+
+        sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+        import torch as t
+
+        dev = rank % t.cuda.device_count()
+        t.cuda.set_device(dev)
+        fn(rank, world, dev, queues, barrier, extra)
+        t.cuda.synchronize()
+        results.put((rank, "ok", ""))
+    except Exception:  # the parent prints it
+        results.put((rank, "error", traceback.format_exc()))
+        try:
+            barrier.abort()
+        except Exception:
+            pass
+
+
+def _run_ranks(fn, world=2, extra=None, timeout=180):
+    ctx = mp.get_context("spawn")
+    queues = [ctx.Queue() for _ in range(world)]  # queues[r]: messages for rank r
+    results = ctx.Queue()
+    barrier = ctx.Barrier(world)
+    procs = [ctx.Process(target=_child, args=(fn, r, world, queues, results, barrier, extra)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = []
+    try:
+        for _ in range(world):
+            got.append(results.get(timeout=timeout))
+    finally:
+        for p in procs:
+            p.join(timeout=30)
+            if p.is_alive():
+                p.kill()
+    bad = [g for g in got if g[1] != "ok"]
+    assert not bad, "\n".join(f"rank {r}: {msg}" for r, _, msg in bad)
+
+
+def _wait(agent, handle, limit=100_000_000):
+    st = "PROC"
+    for _ in range(limit):
+        st = agent.check_xfer_state(handle)
+        if st != "PROC":
+            break
+    return st
+
+
+# ---------------------------------------------------------------------------------------------- transfers
+
+
+def _transfer_rank(rank, world, dev, queues, barrier, extra):
+    import torch
+    from nixl_b200 import nixl_agent, nixl_agent_config
+
+    agent = nixl_agent(f"xp{rank}", nixl_agent_config(enable_prog_thread=False, backends=["NVLINK"]))
+    n_big = (100 << 20) + 4096  # long enough for the copy engines when the peer is another GPU
+    sizes = {"small": 4096, "batch": 64 * 8192, "big": n_big}
+    g = torch.Generator(device=f"cuda:{dev}").manual_seed(11 + rank)
+    bufs = {k: torch.randint(0, 255, (n,), dtype=torch.uint8, device=f"cuda:{dev}", generator=g) for k, n in sizes.items()}
+    for b in bufs.values():
+        agent.register_memory(b)
+    peer = 1 - rank
+    queues[peer].put((agent.get_agent_metadata(), {k: (b.data_ptr(), b.numel(), dev) for k, b in bufs.items()}))
+    md, theirs = queues[rank].get(timeout=60)
+    agent.add_remote_agent(md)
+    barrier.wait(60)
+    if rank == 0:
+        mine_before = {k: b.clone() for k, b in bufs.items()}
+        for k, b in bufs.items():
+            addr, n, pdev = theirs[k]
+            if k == "batch":  # 64 blocks, target blocks in reverse order: nothing to merge
+                local = [(b.data_ptr() + i * 8192, 8192, dev) for i in range(64)]
+                remote = [(addr + (63 - i) * 8192, 8192, pdev) for i in range(64)]
+            else:
+                local, remote = [(b.data_ptr(), n, dev)], [(addr, n, pdev)]
+            h = agent.initialize_xfer("WRITE", agent.get_xfer_descs(local, "VRAM"), agent.get_xfer_descs(remote, "VRAM"), f"xp{peer}", f"wrote-{k}".encode())
+            assert agent.transfer(h) in ("DONE", "PROC")
+            assert _wait(agent, h) == "DONE"
+            agent.release_xfer_handle(h)
+        barrier.wait(60)  # rank 1 checks what landed, then scrambles its buffers
+        barrier.wait(60)
+        for k, b in bufs.items():  # read everything back (now different bytes)
+            addr, n, pdev = theirs[k]
+            h = agent.initialize_xfer("READ", agent.get_xfer_descs([(b.data_ptr(), n, dev)], "VRAM"), agent.get_xfer_descs([(addr, n, pdev)], "VRAM"), f"xp{peer}")
+            assert agent.transfer(h) in ("DONE", "PROC")
+            assert _wait(agent, h) == "DONE"
+            agent.release_xfer_handle(h)
+        torch.cuda.synchronize()
+        queues[peer].put({k: int(b.to(torch.int64).sum()) for k, b in bufs.items()})
+        for k in bufs:
+            assert not torch.equal(bufs[k], mine_before[k])
+    else:
+        barrier.wait(60)
+        torch.cuda.synchronize()
+        gen0 = torch.Generator(device=f"cuda:{dev}").manual_seed(11)
+        want = {k: torch.randint(0, 255, (n,), dtype=torch.uint8, device=f"cuda:{dev}", generator=gen0) for k, n in sizes.items()}
+        assert torch.equal(bufs["small"], want["small"])
+        assert torch.equal(bufs["big"], want["big"])
+        assert torch.equal(bufs["batch"].view(64, 8192).flip(0), want["batch"].view(64, 8192))
+        notifs = {}
+        for _ in range(200000):
+            for who, msgs in agent.get_new_notifs().items():
+                notifs.setdefault(who, []).extend(msgs)
+            if len(notifs.get("xp0", [])) >= 3:
+                break
+        assert sorted(notifs["xp0"]) == [b"wrote-batch", b"wrote-big", b"wrote-small"]
+        for b in bufs.values():
+            b.random_(0, 255)
+        torch.cuda.synchronize()
+        sums = {k: int(b.to(torch.int64).sum()) for k, b in bufs.items()}
+        barrier.wait(60)
+        assert queues[rank].get(timeout=120) == sums
+    barrier.wait(60)
+
+
+def test_write_read_and_notifications_between_processes():
+    _run_ranks(_transfer_rank)
+
+
+# ---------------------------------------------------------------------------------------------- device API
+
+
+def _device_put_rank(rank, world, dev, queues, barrier, extra):
+    import torch
+    from nixl_b200 import _bindings as nb
+    from nixl_b200 import nixl_agent, nixl_agent_config
+    from nixl_b200.ops import device_api
+
+    agent = nixl_agent(f"dp{rank}", nixl_agent_config(enable_prog_thread=False, backends=["NVLINK"]))
+    size, iters = (1 << 12) + 16, 5
+    g = torch.Generator(device=f"cuda:{dev}").manual_seed(5 + rank)
+    data = torch.randint(0, 255, (size * iters,), dtype=torch.uint8, device=f"cuda:{dev}", generator=g)
+    signal = torch.zeros(8, dtype=torch.int64, device=f"cuda:{dev}")
+    agent.register_memory(data)
+    agent.register_memory(signal)
+    peer = 1 - rank
+    queues[peer].put((agent.get_agent_metadata(), (data.data_ptr(), data.numel(), dev), (signal.data_ptr(), 64, dev)))
+    md, their_data, their_signal = queues[rank].get(timeout=60)
+    agent.add_remote_agent(md)
+    barrier.wait(60)
+    if rank == 0:
+        local_view = agent.prep_mem_view(agent.get_xfer_descs(data))
+        remote_view = agent.prep_mem_view(agent.get_remote_descs([(*their_data, f"dp{peer}")], "VRAM"))
+        signal_view = agent.prep_mem_view(agent.get_remote_descs([(*their_signal, f"dp{peer}")], "VRAM"))
+        status = device_api.put_test("WARP", local_view, remote_view, signal_view, size, iters, False, device=torch.device("cuda", dev))
+        assert status == [nb.NIXL_SUCCESS, nb.NIXL_ERR_INVALID_PARAM, 1, 1]
+        torch.cuda.synchronize()
+        barrier.wait(60)
+        barrier.wait(60)
+        for v in (local_view, remote_view, signal_view):
+            agent.release_mem_view(v)
+    else:
+        barrier.wait(60)
+        torch.cuda.synchronize()
+        gen0 = torch.Generator(device=f"cuda:{dev}").manual_seed(5)
+        want = torch.randint(0, 255, (size * iters,), dtype=torch.uint8, device=f"cuda:{dev}", generator=gen0)
+        assert torch.equal(data, want)
+        assert int(signal[0]) == iters
+        barrier.wait(60)
+
+
+def test_gpu_initiated_put_between_processes():
+    _run_ranks(_device_put_rank)
+
+
+# ---------------------------------------------------------------------------------------------- fused KV transfer
+
+
+def _kv_rank(rank, world, dev, queues, barrier, extra):
+    import torch
+    from nixl_b200 import nixl_agent, nixl_agent_config
+    from nixl_b200.ops import KVLayout, KVTransfer, reference_kv_transfer
+
+    agent = nixl_agent(f"kvx{rank}", nixl_agent_config(enable_prog_thread=False, backends=["NVLINK"]))
+    blocks, tensors = 48, 6
+    device = f"cuda:{dev}"
+
+    def source(t):
+        return torch.randn(blocks, 16, 2, 128, device=device, dtype=torch.bfloat16, generator=torch.Generator(device=device).manual_seed(100 + t))
+
+    perm = torch.randperm(blocks, generator=torch.Generator().manual_seed(1)).int()
+    dperm = torch.randperm(blocks, generator=torch.Generator().manual_seed(2)).int()
+    if rank == 0:
+        src = [source(t) for t in range(tensors)]
+        agent.register_memory(src)
+        md, remote = queues[rank].get(timeout=60)
+        agent.add_remote_agent(md)
+        for fp8 in (False, True):
+            x = KVTransfer(agent, src, KVLayout(16, 2, 128), "kvx1", remote[fp8], KVLayout(16, 4, 128, elem_bytes=1 if fp8 else 2),
+                           dst_head_offset=2, cast_fp8=fp8)
+            x.wait(x.post(perm.to(device), dperm.to(device)))
+            x.close()
+        barrier.wait(60)
+        barrier.wait(60)
+    else:
+        dst = [torch.zeros(blocks, 16, 4, 128, device=device, dtype=torch.bfloat16) for _ in range(tensors)]
+        dst8 = [torch.zeros(blocks, 16, 4, 128, device=device, dtype=torch.uint8) for _ in range(tensors)]
+        agent.register_memory(dst)
+        agent.register_memory(dst8)
+        queues[0].put((agent.get_agent_metadata(), {False: [(t.data_ptr(), t.numel() * 2, dev) for t in dst],
+                                                    True: [(t.data_ptr(), t.numel(), dev) for t in dst8]}))
+        barrier.wait(120)
+        torch.cuda.synchronize()
+        for t in range(tensors):
+            want = reference_kv_transfer(source(t), torch.zeros_like(dst[t]), perm.to(device), dperm.to(device), 2)
+            assert torch.equal(dst[t], want)
+            want8 = reference_kv_transfer(source(t), torch.zeros_like(dst8[t]).view(torch.float8_e4m3fn), perm.to(device), dperm.to(device), 2, cast_fp8=True)
+            assert torch.equal(dst8[t], want8.view(torch.uint8))
+        barrier.wait(60)
+
+
+def test_fused_kv_transfer_between_processes():
+    _run_ranks(_kv_rank)
+
+
+# ---------------------------------------------------------------------------------------------- expert parallelism
+
+
+def _ep_rank(rank, world, dev, queues, barrier, extra):
+    import torch
+    import torch.distributed as dist
+    from nixl_b200.parallel import Buffer, dequant_fp8, per_token_cast_to_fp8
+
+    device = torch.device("cuda", dev)
+    T, H, K, El = 96, 1024, 8, 8
+    E = El * world
+    gen = torch.Generator(device=device).manual_seed(40 + rank)
+    x = torch.randn(T, H, device=device, dtype=torch.bfloat16, generator=gen)
+    w, idx = torch.topk(torch.softmax(torch.randn(T, E, device=device, generator=gen), dim=-1), K, dim=-1)
+    idx, w = idx.to(torch.int64).contiguous(), w.float().contiguous()
+    base = dequant_fp8(*per_token_cast_to_fp8(x))
+    want = torch.zeros(T, H, device=device)
+    for k in range(K):
+        want += w[:, k].unsqueeze(1) * (base * ((1 + idx[:, k]).float() * 0.01).unsqueeze(1)).to(torch.bfloat16).float()
+    want = want.to(torch.bfloat16).float()
+    for compact in (True, False):
+        # a store of its own per buffer: the metadata keys are fixed names
+        store = dist.TCPStore("127.0.0.1", extra["ports"][int(compact)], world, is_master=rank == 0)
+        buf = Buffer(rank, world, E, H, T, K, device=device, timeout_ms=20000, low_latency_mode=not compact)
+        buf.set_tcp_store_group(store)
+        barrier.wait(60)
+        buf.connect_ranks()
+        barrier.wait(60)
+        for _ in range(3):
+            if compact:
+                rx, sc, h = buf.dispatch(x, idx, use_fp8=True, topk_weights=w)
+            else:
+                (rx, sc), _, h, _, _ = buf.low_latency_dispatch(x, idx, use_fp8=True)
+                rx, sc = rx.view(-1, H), sc.view(-1, H // 128)
+            torch.cuda.synchronize()
+            y = buf.get_next_combine_buffer(h).view(-1, H)
+            offs, cnts = h.expert_offsets.tolist(), h.recv_count.tolist()
+            for le in range(El):
+                s, c = offs[le], cnts[le]
+                if c:
+                    y[s:s + c] = (dequant_fp8(rx[s:s + c], sc[s:s + c]) * ((1 + rank * El + le) * 0.01)).to(torch.bfloat16)
+            if compact:
+                out = buf.combine(y, idx, w, h)
+            else:
+                out = buf.low_latency_combine(y.view(El, -1, H), idx, w, h)[0]
+            torch.cuda.synchronize()
+            assert buf.status == 0
+            err = (out.float() - want).abs()
+            assert bool((err <= 2e-2 + 0.13 * want.abs()).all()) and float((err <= 2e-2 + 2e-2 * want.abs()).float().mean()) > 0.98
+        barrier.wait(60)
+        buf.destroy()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="dispatch kernels of two ranks wait for each other: one GPU each")
+def test_ep_dispatch_combine_between_processes():
+    world = min(4, torch.cuda.device_count())
+    _run_ranks(_ep_rank, world=world, extra={"ports": [_free_port(), _free_port()]})

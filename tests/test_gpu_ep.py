@@ -81,13 +81,14 @@ def _check_dispatch(bufs, xs, idxs, results, use_fp8, compact):
                 assert all(int(info[start + first + j, 0]) == r for j in range(rows))
 
 
-def _run(bufs, tokens, hidden, experts, topk, use_fp8, compact, zero_copy=False):
+def _run(bufs, tokens, hidden, experts, topk, use_fp8, compact, zero_copy=False, rank_reduce=False):
     xs, idxs, ws = _inputs(bufs, tokens, hidden, experts, topk)
     results = []
-    for b, x, idx in zip(bufs, xs, idxs):  # launch every rank before waiting on any
+    for b, x, idx, w in zip(bufs, xs, idxs, ws):  # launch every rank before waiting on any
         with torch.cuda.device(b.device):
             if compact:
-                results.append(b.dispatch(x, idx, use_fp8=use_fp8))
+                results.append(b.dispatch(x, idx, use_fp8=use_fp8, topk_weights=w if rank_reduce else None))
+                assert results[-1][2].has_group_records == rank_reduce
             else:
                 recv, cnt, handle, _, _ = b.low_latency_dispatch(x, idx, use_fp8=use_fp8)
                 El, rows = b.local_experts, b.num_ranks * b.max_tokens
@@ -133,6 +134,29 @@ def _run(bufs, tokens, hidden, experts, topk, use_fp8, compact, zero_copy=False)
             yk = (base * ((1 + e.clamp(min=0)).float() * 0.01).unsqueeze(1)).to(torch.bfloat16).float()
             want += valid * ws[r][:, k].unsqueeze(1) * yk
         torch.testing.assert_close(outs[r].float(), want.to(torch.bfloat16).float(), rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("use_fp8", [True, False])
+def test_rank_reduced_combine_single_rank(use_fp8):
+    """Dispatch is given the weights, so the expert rank adds a token's rows up before one row returns."""
+    bufs = _make_ranks(1, 8, 1024, 48, 4, tag=f"ep1rr_{int(use_fp8)}")
+    for _ in range(3):  # both parity halves, and a slot reused with a new step tag
+        _run(bufs, 48, 1024, 8, 4, use_fp8, True, rank_reduce=True)
+    _run(bufs, 48, 1024, 8, 4, use_fp8, True)  # and back to the per-copy combine on the same buffer
+    for b in bufs:
+        b.destroy()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs (ranks wait on each other)")
+@pytest.mark.parametrize("ranks", [2, 4])
+def test_rank_reduced_combine_between_gpus(ranks):
+    if torch.cuda.device_count() < ranks:
+        pytest.skip(f"needs {ranks} GPUs")
+    bufs = _make_ranks(ranks, 8 * ranks, 1024, 64, 8, tag=f"eprr{ranks}")
+    for _ in range(3):
+        _run(bufs, 64, 1024, 8 * ranks, 8, True, True, rank_reduce=True)
+    for b in bufs:
+        b.destroy()
 
 
 @pytest.mark.parametrize("use_fp8", [True, False])
