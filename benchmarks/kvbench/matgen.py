@@ -16,7 +16,7 @@ from nixl_b200.models import ParallelConfig, get_model
 
 from .traffic import save_matrix
 
-# Dense bf16 throughput one B200 sustains through cuBLAS on this pool (the reference assumes 36 TFLOP/s of an H100).
+# Dense bf16 throughput one B200 sustains through cuBLAS under its power cap (the reference assumes 36 TFLOP/s of an H100).
 DEFAULT_FLOPS_PER_GPU = 1.4e15
 
 

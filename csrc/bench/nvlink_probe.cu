@@ -1,4 +1,4 @@
-// nvlink_probe: what one NVLink direction between two GPUs of this box delivers to each way of
+// nvlink_probe: what one NVLink direction between two GPUs of a machine delivers to each way of
 // moving bytes - SM-issued stores into the peer (push), SM-issued loads from the peer (pull),
 // the copy engine, and mixtures of them - one way and with the opposite direction busy.
 //

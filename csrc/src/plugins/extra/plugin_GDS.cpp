@@ -2,9 +2,9 @@
 // for its cuFile plugins (src/plugins/cuda_gds, src/plugins/gds_mt: local-only, DRAM / VRAM /
 // FILE, one I/O per descriptor, `thread_count` workers).
 //
-// GPUDirect Storage needs the nvidia-fs kernel driver and a supported file system, which this
-// pool's boxes do not have; cuFile would then run in its compatibility mode, i.e. a pinned
-// bounce buffer plus cudaMemcpy.  This engine is exactly that path, written out: each worker
+// GPUDirect Storage needs the nvidia-fs kernel driver and a supported file system; without
+// them cuFile runs in its compatibility mode, i.e. a pinned bounce buffer plus cudaMemcpy.
+// This engine is exactly that path, written out (it never calls cuFile): each worker
 // streams a descriptor through two pinned staging buffers so the file I/O of chunk i+1
 // overlaps the PCIe copy of chunk i.  Host memory goes through pread/pwrite directly.
 #ifndef NIXL_GDS_PLUGIN_NAME

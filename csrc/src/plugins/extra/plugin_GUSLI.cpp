@@ -2,8 +2,8 @@
 //
 // The reference's GUSLI plugin (src/plugins/gusli: local-only, DRAM + BLK, devId = block device
 // id, descriptor address = byte offset on the device, devices listed in a `config_file`
-// parameter) hands I/O to a user-space block server through libgusli_clnt.  That library and its
-// server are not on this box; this engine implements the library's "direct local access" mode
+// parameter) hands I/O to a user-space block server through libgusli_clnt.  This build does not
+// link that library; the engine implements the library's "direct local access" mode
 // itself: every `F` (file-backed) or `K` (kernel block device) line of the configuration is
 // opened and served with pread/pwrite from a worker pool.  `N` (networked server) lines are
 // refused at creation.  Configuration text, one device per line after the version line:

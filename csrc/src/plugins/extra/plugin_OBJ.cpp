@@ -1,6 +1,6 @@
 // OBJ backend: host memory <-> named objects.  The reference's OBJ plugin talks to S3
 // (src/plugins/obj: local-only, DRAM + OBJ, object key in the registration's metaInfo, devId a
-// caller-chosen id, asynchronous put/get).  This box has no network, so the object store here is
+// caller-chosen id, asynchronous put/get).  This build has no S3 client: the object store is
 // a directory: bucket = directory (`bucket` parameter, else $NIXL_OBJ_BUCKET_DIR, else
 // /tmp/nixl_obj), object = file named by its key.  WRITE puts [offset, offset+len) of the
 // object, READ gets it; queryMem tells whether a key exists.  The engine keeps the reference's

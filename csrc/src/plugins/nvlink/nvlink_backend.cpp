@@ -157,6 +157,12 @@ struct PubReg {
     unsigned char ipc[sizeof(cudaIpcMemHandle_t)];
     unsigned char gpuUuid[16]; // VRAM: which physical GPU holds the memory (ordinals differ between processes)
 };
+struct PubVmmChunk {
+    uint64_t base;
+    uint64_t size;
+    int32_t fd;
+    int32_t pad;
+};
 #pragma pack(pop)
 
 std::string encodePeer(const PeerId &p) {
@@ -531,7 +537,15 @@ nixl_status_t Engine::registerMem(const nixlBlobDesc &mem, const nixl_mem_t &nix
             md->ipcOffset = mem.addr - base;
         } else {
             cudaGetLastError();
-            NIXL_DEBUG << "NVLINK backend: no IPC handle for " << reinterpret_cast<void *>(mem.addr) << "; same-process use only";
+            // Not cudaMalloc memory.  Memory from the virtual memory management API (PyTorch's expandable
+            // segments, engines' own pools) is exported allocation by allocation as file descriptors.
+            if (vmmExportRange(mem.addr, mem.len, md->vmm) && fdServer_.start(self_.sockName + ".fd")) {
+                for (const auto &c : md->vmm) fdServer_.allow(c.fd);
+                NIXL_DEBUG << "NVLINK backend: " << reinterpret_cast<void *>(mem.addr) << " exported as " << md->vmm.size() << " VMM allocation(s)";
+            } else {
+                vmmCloseChunks(md->vmm);
+                NIXL_DEBUG << "NVLINK backend: no IPC handle for " << reinterpret_cast<void *>(mem.addr) << "; same-process use only";
+            }
         }
     } else if (nixl_mem == DRAM_SEG) {
         if (cuda_ && pinDram_) {
@@ -563,6 +577,8 @@ nixl_status_t Engine::deregisterMem(nixlBackendMD *meta) {
     if (md->pinnedByUs) {
         if (cudaHostUnregister(reinterpret_cast<void *>(md->addr)) != cudaSuccess) cudaGetLastError();
     }
+    for (const auto &c : md->vmm) fdServer_.revoke(c.fd);
+    vmmCloseChunks(md->vmm);
     delete md;
     return NIXL_SUCCESS;
 }
@@ -573,7 +589,7 @@ nixl_status_t Engine::getPublicData(const nixlBackendMD *meta, std::string &str)
     PubReg pub{};
     pub.version = kPubVersion;
     pub.mem = static_cast<uint8_t>(md->mem);
-    pub.hasIpc = md->hasIpc ? 1 : 0;
+    pub.hasIpc = md->hasIpc ? 1 : (md->vmm.empty() ? 0 : 2);
     pub.device = md->device;
     pub.addr = md->addr;
     pub.len = md->len;
@@ -583,6 +599,14 @@ nixl_status_t Engine::getPublicData(const nixlBackendMD *meta, std::string &str)
     if (md->mem == VRAM_SEG)
         if (const GpuUuid *u = deviceUuid(md->device)) std::memcpy(pub.gpuUuid, u->b, 16);
     str.assign(reinterpret_cast<const char *>(&pub), sizeof(pub));
+    if (pub.hasIpc == 2) { // tail: allocation count, then (base, size, descriptor number) of each
+        const uint32_t n = static_cast<uint32_t>(md->vmm.size());
+        str.append(reinterpret_cast<const char *>(&n), sizeof(n));
+        for (const auto &c : md->vmm) {
+            PubVmmChunk w{c.base, c.size, c.fd, 0};
+            str.append(reinterpret_cast<const char *>(&w), sizeof(w));
+        }
+    }
     return NIXL_SUCCESS;
 }
 
@@ -632,7 +656,7 @@ nixl_status_t Engine::disconnect(const std::string &remote_agent) {
 
 nixl_status_t Engine::loadRemoteMD(const nixlBlobDesc &input, const nixl_mem_t &nixl_mem, const std::string &remote_agent,
                                    nixlBackendMD *&output) {
-    if (input.metaInfo.size() != sizeof(PubReg)) return NIXL_ERR_MISMATCH;
+    if (input.metaInfo.size() < sizeof(PubReg)) return NIXL_ERR_MISMATCH;
     PubReg pub;
     std::memcpy(&pub, input.metaInfo.data(), sizeof(pub));
     if (pub.version != kPubVersion || pub.mem != static_cast<uint8_t>(nixl_mem)) return NIXL_ERR_MISMATCH;
@@ -657,7 +681,7 @@ nixl_status_t Engine::loadRemoteMD(const nixlBlobDesc &input, const nixl_mem_t &
                 md->devVisible = reinterpret_cast<uintptr_t>(dp);
             else cudaGetLastError();
         }
-    } else if (nixl_mem == VRAM_SEG && cuda_ && pub.hasIpc) {
+    } else if (nixl_mem == VRAM_SEG && cuda_ && pub.hasIpc == 1) {
         const std::string key(reinterpret_cast<const char *>(pub.ipc), sizeof(pub.ipc));
         std::lock_guard<std::mutex> g(g_ipcMu);
         IpcMapping &m = g_ipc[key];
@@ -684,6 +708,36 @@ nixl_status_t Engine::loadRemoteMD(const nixlBlobDesc &input, const nixl_mem_t &
         md->mapDevice = m.device;
         md->ownerLocalDevice = m.ownerLocal;
         md->devVisible = reinterpret_cast<uintptr_t>(m.base) + pub.ipcOffset;
+    } else if (nixl_mem == VRAM_SEG && cuda_ && pub.hasIpc == 2) {
+        // VMM memory of another process: fetch its allocations' descriptors and map them here.
+        const char *tail = input.metaInfo.data() + sizeof(PubReg);
+        const size_t left = input.metaInfo.size() - sizeof(PubReg);
+        uint32_t n = 0;
+        if (left < sizeof(n)) return NIXL_ERR_MISMATCH;
+        std::memcpy(&n, tail, sizeof(n));
+        if (n == 0 || left < sizeof(n) + size_t(n) * sizeof(PubVmmChunk)) return NIXL_ERR_MISMATCH;
+        std::vector<VmmChunk> chunks(n);
+        std::vector<int> numbers(n);
+        for (uint32_t i = 0; i < n; ++i) {
+            PubVmmChunk w;
+            std::memcpy(&w, tail + sizeof(n) + size_t(i) * sizeof(w), sizeof(w));
+            chunks[i] = {w.base, w.size, -1};
+            numbers[i] = w.fd;
+        }
+        int dev = primaryDevice_.load();
+        if (dev < 0 && cudaGetDevice(&dev) != cudaSuccess) dev = 0;
+        DeviceScope ds(dev);
+        cudaFree(nullptr); // make sure the device has a context before driver calls
+        const int owner_local = ordinalOfUuid(pub.gpuUuid, deviceCount_);
+        const std::vector<int> fds = vmmFetchFds(peer.sockName + ".fd", numbers);
+        if (fds.size() != n || !vmmMap(chunks, fds, deviceCount_, owner_local, md->vmmMap)) {
+            NIXL_ERROR << "NVLINK backend: cannot map the VMM memory of agent " << remote_agent
+                       << " (its allocations must be created with the POSIX file-descriptor handle type)";
+            return NIXL_ERR_BACKEND;
+        }
+        md->mapDevice = dev;
+        md->ownerLocalDevice = owner_local;
+        md->devVisible = static_cast<uintptr_t>(md->vmmMap.va) + static_cast<uintptr_t>(pub.addr - chunks.front().base);
     }
     output = md.release();
     return NIXL_SUCCESS;
@@ -709,6 +763,10 @@ nixl_status_t Engine::loadLocalMD(nixlBackendMD *input, nixlBackendMD *&output) 
 nixl_status_t Engine::unloadMD(nixlBackendMD *input) {
     auto *md = dynamic_cast<RemoteMD *>(input);
     if (!md) return NIXL_ERR_INVALID_PARAM;
+    if (md->vmmMap.va != 0) {
+        DeviceScope ds(md->mapDevice);
+        vmmUnmap(md->vmmMap);
+    }
     if (!md->ipcKey.empty()) {
         std::lock_guard<std::mutex> g(g_ipcMu);
         auto it = g_ipc.find(md->ipcKey);

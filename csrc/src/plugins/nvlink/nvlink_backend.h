@@ -34,6 +34,7 @@
 #include <cuda_runtime.h>
 
 #include "backend/backend_engine.h"
+#include "plugins/nvlink/vmm_share.h"
 #include "plugins/nvlink/xfer_kernels.h"
 
 namespace nixl_nvlink {
@@ -63,6 +64,7 @@ public:
     bool hasIpc = false;
     cudaIpcMemHandle_t ipc{};
     uint64_t ipcOffset = 0;    // addr - base of the enclosing allocation
+    std::vector<VmmChunk> vmm; // VMM memory (no IPC handle): its allocations, exported as file descriptors
 };
 
 // A peer's registration as seen from here.
@@ -81,6 +83,7 @@ public:
     int64_t ownerPid = 0;
     std::string ipcKey;        // key into the process-wide IPC mapping cache (empty: none)
     bool loopback = false;     // produced by loadLocalMD
+    VmmMapping vmmMap;         // other-process VMM memory mapped here (va == 0: none)
 };
 
 // Simple first-fit sub-allocator over device slabs (tables and counters of requests).
@@ -315,6 +318,7 @@ private:
     mutable std::vector<std::unique_ptr<DeviceCtx>> ctxs_;
     mutable std::atomic<int> primaryDevice_{-1};
 
+    VmmFdServer fdServer_; // hands exported VMM descriptors to importing processes (started with the first VMM registration)
     int notifFd_ = -1;
     mutable std::mutex notifMu_;
     notif_list_t inbox_; // same-process deliveries

@@ -9,8 +9,8 @@
 //
 // Also built as libplugin_HF3FS.so (NIXL_POSIX_PLUGIN_NAME): the reference's HF3FS plugin
 // (src/plugins/hf3fs) has the same contract (local, DRAM + FILE, fd in devId) over the 3FS
-// user-space I/O rings, which this box does not have; under that name the files are served with
-// the queues of this engine.
+// user-space I/O rings, for which this build has no client; under that name (an opt-in stand-in,
+// outside the default plug-in path) the files are served with the queues of this engine.
 #ifndef NIXL_POSIX_PLUGIN_NAME
 #define NIXL_POSIX_PLUGIN_NAME "POSIX"
 #endif

@@ -43,7 +43,20 @@ def _child(fn, rank, world, queues, results, barrier, extra):
             pass
 
 
-def _run_ranks(fn, world=2, extra=None, timeout=180):
+def _run_ranks(fn, world=2, extra=None, timeout=180, env=None):
+    saved = {k: os.environ.get(k) for k in (env or {})}
+    os.environ.update(env or {})  # the children inherit it (it has to be set before they import torch)
+    try:
+        _run_ranks_now(fn, world, extra, timeout)
+    finally:
+        for k, v in saved.items():
+            if v is None:
+                os.environ.pop(k, None)
+            else:
+                os.environ[k] = v
+
+
+def _run_ranks_now(fn, world, extra, timeout):
     ctx = mp.get_context("spawn")
     queues = [ctx.Queue() for _ in range(world)]  # queues[r]: messages for rank r
     results = ctx.Queue()
@@ -143,6 +156,60 @@ def _transfer_rank(rank, world, dev, queues, barrier, extra):
 
 def test_write_read_and_notifications_between_processes():
     _run_ranks(_transfer_rank)
+
+
+# ---------------------------------------------------------------------------------------------- VMM memory
+
+
+def _vmm_rank(rank, world, dev, queues, barrier, extra):
+    """Both processes allocate from PyTorch's expandable segments (cuMemCreate + cuMemMap memory, which CUDA IPC
+    cannot export): the registration is exported allocation by allocation and mapped by the peer."""
+    import torch
+    from nixl_b200 import nixl_agent, nixl_agent_config
+
+    assert "expandable_segments:True" in os.environ.get("PYTORCH_CUDA_ALLOC_CONF", "")
+    agent = nixl_agent(f"vm{rank}", nixl_agent_config(enable_prog_thread=False, backends=["NVLINK"]))
+    device = f"cuda:{dev}"
+    n = (44 << 20) + 8192  # spans several of the allocator's physical allocations
+    g = torch.Generator(device=device).manual_seed(21 + rank)
+    filler = torch.empty(3 << 20, dtype=torch.uint8, device=device)  # so that the buffer does not start an allocation
+    buf = torch.randint(0, 255, (n,), dtype=torch.uint8, device=device, generator=g)
+    agent.register_memory(buf)
+    peer = 1 - rank
+    queues[peer].put((agent.get_agent_metadata(), (buf.data_ptr(), n, dev)))
+    md, (addr, _, pdev) = queues[rank].get(timeout=60)
+    agent.add_remote_agent(md)
+    barrier.wait(60)
+    if rank == 0:
+        off = 5 << 20
+        h = agent.initialize_xfer("WRITE", agent.get_xfer_descs([(buf.data_ptr() + off, n - off, dev)], "VRAM"),
+                                  agent.get_xfer_descs([(addr + off, n - off, pdev)], "VRAM"), f"vm{peer}")
+        assert agent.transfer(h) in ("DONE", "PROC")
+        assert _wait(agent, h) == "DONE"
+        agent.release_xfer_handle(h)
+        barrier.wait(60)
+        h = agent.initialize_xfer("READ", agent.get_xfer_descs([(buf.data_ptr(), off, dev)], "VRAM"),
+                                  agent.get_xfer_descs([(addr, off, pdev)], "VRAM"), f"vm{peer}")
+        assert agent.transfer(h) in ("DONE", "PROC")
+        assert _wait(agent, h) == "DONE"
+        agent.release_xfer_handle(h)
+        torch.cuda.synchronize()
+        want = torch.randint(0, 255, (n,), dtype=torch.uint8, device=device, generator=torch.Generator(device=device).manual_seed(22))
+        assert torch.equal(buf[:off], want[:off])
+        barrier.wait(60)
+    else:
+        barrier.wait(60)
+        torch.cuda.synchronize()
+        off = 5 << 20
+        theirs = torch.randint(0, 255, (n,), dtype=torch.uint8, device=device, generator=torch.Generator(device=device).manual_seed(21))
+        mine = torch.randint(0, 255, (n,), dtype=torch.uint8, device=device, generator=torch.Generator(device=device).manual_seed(22))
+        assert torch.equal(buf[off:], theirs[off:]) and torch.equal(buf[:off], mine[:off])
+        barrier.wait(60)
+    del filler
+
+
+def test_vmm_memory_between_processes():
+    _run_ranks(_vmm_rank, env={"PYTORCH_CUDA_ALLOC_CONF": "expandable_segments:True", "NIXL_LOG_LEVEL": "DEBUG"})
 
 
 # ---------------------------------------------------------------------------------------------- device API
