@@ -12,6 +12,11 @@
 //             [--depth 1] [--copy-path vector|bulk] [--param key=value]... [--check]
 //             [--prepared] [--recreate] [--reregister] [--scatter] [--config file]
 //             [--file path [--num-files N] [--direct]]      storage mode (POSIX, GDS, GDS_MT backends)
+//             [--scheme pairwise|onetomany|manytoone --num-initiator-dev N --num-target-dev M]
+//
+// --scheme onetomany: one initiator GPU (--src-dev) posts the same request to M target GPUs at once; manytoone: N
+// initiator GPUs post to one target GPU (--dst-dev) at once, which is the pattern that shows what a receiver's
+// ingress sustains.  One agent per GPU, all in this process; the figure is the sum over all flows.
 //
 // --prepared builds requests with prepXferDlist + makeXferReq (the reference's prepared_xfer),
 // --recreate creates and releases the request on every iteration (recreate_xfer), --reregister
@@ -25,6 +30,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <map>
+#include <memory>
 #include <string>
 #include <vector>
 
@@ -46,6 +52,8 @@ struct Args {
     size_t min = 4096, max = size_t(1) << 30, total = size_t(8) << 30;
     bool check = false, prepared = false, recreate = false, reregister = false, direct = false;
     bool scatter = false; // target blocks of a batch in reverse order: no descriptor continues its predecessor
+    std::string scheme = "pairwise"; // pairwise | onetomany | manytoone (benchmark/nixlbench/src/utils/utils.h:122-125 of the reference)
+    int num_initiator_dev = 1, num_target_dev = 1;
     int batch_max = 0, num_files = 1;
     std::string file; // storage mode when set
     nixl_b_params_t extra; // --param key=value, passed to the backend
@@ -57,6 +65,9 @@ bool setOption(Args &a, const std::string &k, const std::string &v) {
     else if (k == "--op") a.op = v;
     else if (k == "--mem") a.mem = v;
     else if (k == "--copy-path") a.copy_path = v;
+    else if (k == "--scheme") a.scheme = v;
+    else if (k == "--num-initiator-dev") a.num_initiator_dev = std::max(1, std::atoi(v.c_str()));
+    else if (k == "--num-target-dev") a.num_target_dev = std::max(1, std::atoi(v.c_str()));
     else if (k == "--src-dev") a.src_dev = std::atoi(v.c_str());
     else if (k == "--dst-dev") a.dst_dev = std::atoi(v.c_str());
     else if (k == "--batch") a.batch = std::max(1, std::atoi(v.c_str()));
@@ -143,9 +154,9 @@ Spelling canonical(std::string k) {
     };
     // One process drives both agents here: there is no runtime to rendezvous through, no second
     // worker type and one initiator / target device each.
-    static const char *ignored[] = {"--runtime-type", "--worker-type", "--etcd-endpoints", "--scheme",       "--mode",
+    static const char *ignored[] = {"--runtime-type", "--worker-type", "--etcd-endpoints", "--mode",
                                     "--num-threads",  "--enable-pt",   "--progress-threads", "--device-list", "--target-seg-type",
-                                    "--num-initiator-dev", "--num-target-dev", "--large-blk-iter-ftr", "--benchmark-group"};
+                                    "--large-blk-iter-ftr", "--benchmark-group"};
     Spelling sp;
     sp.name = k;
     if (auto it = same.find(k); it != same.end()) sp.name = it->second;
@@ -165,6 +176,133 @@ double pct(std::vector<double> &v, double q) {
     if (v.empty()) return 0;
     std::sort(v.begin(), v.end());
     return v[std::min(v.size() - 1, static_cast<size_t>(q * v.size()))];
+}
+// One-to-many / many-to-one: a flow per (initiator GPU, target GPU) pair, all posted together every iteration.
+int runScheme(const Args &a, int ndev) {
+    const bool many_targets = a.scheme == "onetomany";
+    const int n = many_targets ? a.num_target_dev : a.num_initiator_dev;
+    if (a.mem != "VRAM" || n + 1 > ndev) {
+        std::fprintf(stderr, "--scheme %s needs VRAM and %d GPUs (found %d)\n", a.scheme.c_str(), n + 1, ndev);
+        return 2;
+    }
+    const int hub = many_targets ? a.src_dev : (a.dst_dev >= 0 ? a.dst_dev : 0); // the "one" side
+    std::vector<int> spokes;
+    for (int d = 0; d < ndev && static_cast<int>(spokes.size()) < n; ++d)
+        if (d != hub) spokes.push_back(d);
+    const size_t buf_bytes = std::min(a.total, std::max<size_t>(a.max * std::max(a.batch, a.batch_max), a.max));
+    nixlAgentConfig cfg(false);
+    nixl_b_params_t params;
+    params["copy_path"] = a.copy_path;
+    for (auto &kv : a.extra) params[kv.first] = kv.second;
+    struct Side {
+        int dev;
+        void *buf = nullptr; // hub: n regions of buf_bytes (one per spoke); spoke: one region
+        std::unique_ptr<nixlAgent> agent;
+    };
+    auto make = [&](int dev, const std::string &name, size_t bytes, int fill, Side &s) {
+        s.dev = dev;
+        cudaSetDevice(dev);
+        if (cudaMalloc(&s.buf, bytes) != cudaSuccess) return false;
+        cudaMemset(s.buf, fill, bytes);
+        cudaDeviceSynchronize();
+        s.agent = std::make_unique<nixlAgent>(name, cfg);
+        nixlBackendH *b = nullptr;
+        if (s.agent->createBackend(a.backend, params, b) != NIXL_SUCCESS) return false;
+        nixl_reg_dlist_t reg(VRAM_SEG);
+        reg.addDesc(nixlBlobDesc(reinterpret_cast<uintptr_t>(s.buf), bytes, dev, ""));
+        return s.agent->registerMem(reg) == NIXL_SUCCESS;
+    };
+    Side hub_side;
+    std::vector<Side> spoke_sides(n);
+    if (!make(hub, "hub", buf_bytes * n, many_targets ? 0x5a : 0, hub_side)) return 3;
+    for (int i = 0; i < n; ++i)
+        if (!make(spokes[i], "spoke" + std::to_string(i), buf_bytes, many_targets ? 0 : 0x5a, spoke_sides[i])) return 3;
+    // initiators learn their targets
+    auto learn = [](nixlAgent &ini, nixlAgent &tgt) {
+        nixl_blob_t md;
+        std::string name;
+        tgt.getLocalMD(md);
+        return ini.loadRemoteMD(md, name) == NIXL_SUCCESS;
+    };
+    for (int i = 0; i < n; ++i)
+        if (!(many_targets ? learn(*hub_side.agent, *spoke_sides[i].agent) : learn(*spoke_sides[i].agent, *hub_side.agent))) return 6;
+    const nixl_xfer_op_t op = a.op == "READ" ? NIXL_READ : NIXL_WRITE;
+    std::printf("# scheme %s: %s GPU %d, %d %s GPU(s)\n", a.scheme.c_str(), many_targets ? "initiator" : "target", hub, n,
+                many_targets ? "target" : "initiator");
+    std::printf("%-12s %6s %10s %12s %10s %10s\n", "block", "batch", "GB/s", "GB/s_per_flow", "p50_us", "p99_us");
+    for (int batch = a.batch; batch <= std::max(a.batch, a.batch_max); batch *= 2)
+    for (size_t block = a.min; block <= a.max && block * batch <= buf_bytes; block *= 2) {
+        const size_t per = block * batch;
+        int iters = a.iters, warm = a.warmup;
+        if (per > (size_t(64) << 20)) {
+            iters = std::max<int>(10, static_cast<int>((size_t(64) << 30) / per / 16));
+            warm = 3;
+        }
+        std::vector<nixlXferReqH *> reqs(n, nullptr);
+        for (int i = 0; i < n; ++i) {
+            nixl_xfer_dlist_t l(VRAM_SEG), r(VRAM_SEG);
+            char *hub_base = static_cast<char *>(hub_side.buf) + static_cast<size_t>(i) * buf_bytes;
+            char *spoke_base = static_cast<char *>(spoke_sides[i].buf);
+            for (int j = 0; j < batch; ++j) {
+                const size_t off = static_cast<size_t>(j) * block, roff = a.scatter ? static_cast<size_t>(batch - 1 - j) * block : off;
+                if (many_targets) {
+                    l.addDesc(nixlBasicDesc(reinterpret_cast<uintptr_t>(hub_base) + off, block, hub));
+                    r.addDesc(nixlBasicDesc(reinterpret_cast<uintptr_t>(spoke_base) + roff, block, spokes[i]));
+                } else {
+                    l.addDesc(nixlBasicDesc(reinterpret_cast<uintptr_t>(spoke_base) + off, block, spokes[i]));
+                    r.addDesc(nixlBasicDesc(reinterpret_cast<uintptr_t>(hub_base) + roff, block, hub));
+                }
+            }
+            nixlAgent &ini = many_targets ? *hub_side.agent : *spoke_sides[i].agent;
+            const std::string remote = many_targets ? "spoke" + std::to_string(i) : "hub";
+            if (ini.createXferReq(op, l, r, remote, reqs[i]) != NIXL_SUCCESS) return 7;
+        }
+        std::vector<double> step;
+        clk::time_point t_begin = clk::now();
+        for (int it = 0; it < warm + iters; ++it) {
+            if (it == warm) t_begin = clk::now();
+            const auto t0 = clk::now();
+            std::vector<bool> busy(n, false);
+            for (int i = 0; i < n; ++i) {
+                nixlAgent &ini = many_targets ? *hub_side.agent : *spoke_sides[i].agent;
+                const nixl_status_t st = ini.postXferReq(reqs[i]);
+                if (st < 0) return 9;
+                busy[i] = st != NIXL_SUCCESS;
+            }
+            for (bool any = true; any;) {
+                any = false;
+                for (int i = 0; i < n; ++i) {
+                    if (!busy[i]) continue;
+                    nixlAgent &ini = many_targets ? *hub_side.agent : *spoke_sides[i].agent;
+                    const nixl_status_t st = ini.getXferStatus(reqs[i]);
+                    if (st < 0) return 8;
+                    busy[i] = st != NIXL_SUCCESS;
+                    any |= busy[i];
+                }
+            }
+            if (it >= warm) step.push_back(us(t0, clk::now()));
+        }
+        const double wall = us(t_begin, clk::now());
+        const double gbs = double(per) * n * iters / wall / 1e3;
+        std::printf("%-12zu %6d %10.2f %12.2f %10.2f %10.2f\n", block, batch, gbs, gbs / n, pct(step, 0.5), pct(step, 0.99));
+        std::fflush(stdout);
+        for (int i = 0; i < n; ++i) (many_targets ? *hub_side.agent : *spoke_sides[i].agent).releaseXferReq(reqs[i]);
+        if (a.check && op == NIXL_WRITE) { // every landing region must hold the pattern
+            std::vector<unsigned char> h(std::min<size_t>(per, 1 << 20));
+            for (int i = 0; i < n; ++i) {
+                const void *landed = many_targets ? spoke_sides[i].buf : static_cast<char *>(hub_side.buf) + static_cast<size_t>(i) * buf_bytes;
+                cudaSetDevice(many_targets ? spokes[i] : hub);
+                cudaDeviceSynchronize();
+                cudaMemcpy(h.data(), landed, h.size(), cudaMemcpyDeviceToHost);
+                for (unsigned char c : h)
+                    if (c != 0x5a) {
+                        std::fprintf(stderr, "consistency check failed at block %zu, flow %d\n", block, i);
+                        return 10;
+                    }
+            }
+        }
+    }
+    return 0;
 }
 } // namespace
 
@@ -224,6 +362,13 @@ int main(int argc, char **argv) {
     if (vram && (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0)) {
         std::fprintf(stderr, "no GPU\n");
         return 2;
+    }
+    if (a.scheme != "pairwise") {
+        if (a.scheme != "onetomany" && a.scheme != "manytoone") {
+            std::fprintf(stderr, "unknown --scheme %s (pairwise, onetomany, manytoone)\n", a.scheme.c_str());
+            return 2;
+        }
+        return runScheme(a, ndev);
     }
     if (a.dst_dev < 0) a.dst_dev = ndev > 1 ? 1 : 0;
     if (a.batch_max < a.batch) a.batch_max = a.batch;

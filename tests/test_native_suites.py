@@ -73,7 +73,8 @@ def test_native_nixlbench_accepts_the_reference_spellings(tmp_path):
     assert res.returncode == 0, res.stdout + res.stderr
     rows = [l.split() for l in res.stdout.splitlines() if l and l[0].isdigit()]
     assert [r[0] for r in rows] == ["8192", "16384"] and all(r[1] == "2" for r in rows)
-    assert "no effect" in res.stderr and "--scheme" in res.stderr
+    assert "no effect" in res.stderr and "--enable_pt" in res.stderr
+    assert _nixlbench("--scheme", "ring").returncode == 2
     store = str(tmp_path / "store.bin")
     res = _nixlbench("--backend=POSIX", "--initiator_seg_type=DRAM", "--filepath", store, "--posix_api_type=URING", "--posix_kernel_queue_size=32",
                      "--start_block_size=65536", "--max_block_size=65536", "--max_batch_size=8", "--start_batch_size=8", "--num_iter=5",
