@@ -4,8 +4,10 @@
 32 layers x (K, V), 8 KV heads, head_dim 128, bf16, paged blocks of 16 tokens; batch of 8 requests
 x 4096-token prompts (256 blocks each) with block tables shuffled by a seeded permutation.  The
 first half of the GPUs are prefill ranks holding 2 KV heads each (TP=4 at 8 GPUs), the second
-half decode ranks holding 4 KV heads (TP=2): prefill rank p writes its heads into head slots
-(p % 2) * 2 of decode rank N/2 + p // 2.  With one GPU both caches live on it.
+half decode ranks holding 4 KV heads (TP=2), i.e. two decode replicas (GPUs 4-5 and 6-7) that take
+four requests each: prefill rank p writes its heads into head slots (p % 2) * 2 of decode rank
+N/2 + 2 * replica + p // 2, one launch per replica, starting with replica p % 2 so that the two
+senders of a decode GPU do not arrive together.  With one GPU both caches live on it.
 
 Measured per prefill rank (device clock, max over ranks): the fused kernel (block-table
 gather/scatter + TP reshard, bf16 and bf16->fp8 e4m3), against the unfused pipeline a descriptor
@@ -57,7 +59,16 @@ def main():
     n_prefill = max(1, world // 2)
     is_prefill = rank < n_prefill or world == 1
     is_decode = rank >= n_prefill or world == 1
-    decode_of = (lambda p: (n_prefill + p // 2) if world >= 4 else (world - 1))
+    # (decode rank, requests it takes) for prefill rank p: both TP=2 replicas at 8 GPUs, else one decode rank
+    replicas = 2 if world >= 8 else 1
+    per_replica = args.requests // replicas
+
+    def targets_of(p):
+        if world < 4:
+            return [(world - 1, range(args.requests))]
+        order = [(n_prefill + 2 * rep + p // 2 if world >= 8 else n_prefill + p // 2, range(rep * per_replica, (rep + 1) * per_replica))
+                 for rep in range(replicas)]
+        return order[p % len(order):] + order[:p % len(order)]
 
     agent = nixl_agent(f"kv{rank}", nixl_agent_config(enable_prog_thread=False, backends=["NVLINK"]))
     g = torch.Generator(device=dev).manual_seed(7 + rank)
@@ -82,11 +93,18 @@ def main():
         dist.all_gather_object(infos, info)
     else:
         infos = [info]
-    target = decode_of(rank) if is_prefill else None
+    my_targets = targets_of(rank) if is_prefill else []
     if world == 1:
-        target = 0
-    if is_prefill and target != rank:
-        agent.add_remote_agent(infos[target]["md"])
+        my_targets = [(0, range(args.requests))]
+    for t_rank, _ in my_targets:
+        if t_rank != rank:
+            agent.add_remote_agent(infos[t_rank]["md"])
+    target = my_targets[0][0] if my_targets else None  # the unfused baseline below sends everything to one decode rank
+    side_streams = [torch.cuda.Stream(device=dev) for _ in my_targets]
+
+    def tables_of(reqs):
+        idx = torch.cat([torch.arange(r * blocks_per_req, (r + 1) * blocks_per_req) for r in reqs]).to(dev)
+        return src_table[idx].contiguous(), dst_table[idx].contiguous()
 
     perm = torch.randperm(n_blocks, generator=torch.Generator().manual_seed(123))
     src_table = perm.int().to(dev)                     # request r uses blocks perm[r*256:(r+1)*256] of the prefill cache
@@ -116,19 +134,30 @@ def main():
         return float(t)
 
     for fp8 in (False, True):
-        xfer = None
-        if is_prefill:
-            remote = infos[target]["dst8" if fp8 else "dst"]
-            xfer = KVTransfer(agent, src, KVLayout(tokens, src_heads, head_dim), infos[target]["name"], remote,
-                              KVLayout(tokens, dst_heads, head_dim, elem_bytes=1 if fp8 else 2), dst_head_offset=head_off, cast_fp8=fp8)
+        xfers = []
+        for t_rank, reqs in my_targets:
+            remote = infos[t_rank]["dst8" if fp8 else "dst"]
+            x = KVTransfer(agent, src, KVLayout(tokens, src_heads, head_dim), infos[t_rank]["name"], remote,
+                           KVLayout(tokens, dst_heads, head_dim, elem_bytes=1 if fp8 else 2), dst_head_offset=head_off, cast_fp8=fp8)
+            xfers.append((x, *tables_of(reqs)))
+        xfer = xfers[0][0] if xfers else None
 
         def fused_all():
-            if xfer is not None:
-                xfer.post(src_table, dst_table)
+            # one launch per destination, side by side
+            cur = torch.cuda.current_stream()
+            start = torch.cuda.Event()
+            start.record(cur)
+            for (x, sb, db), s in zip(xfers, side_streams):
+                s.wait_event(start)
+                x.post(sb, db, stream=s)
+                e = torch.cuda.Event()
+                e.record(s)
+                cur.wait_event(e)
 
         def fused_one():
-            if xfer is not None:
-                xfer.post(src_table[:blocks_per_req], dst_table[:blocks_per_req])
+            if xfers:
+                x, sb, db = xfers[0]
+                x.post(sb[:blocks_per_req], db[:blocks_per_req])
 
         ms_all = time_dev(fused_all, args.iters)
         ms_one = time_dev(fused_one, args.iters)
@@ -145,8 +174,8 @@ def main():
             from nixl_b200.ops import reference_kv_transfer
             want = reference_kv_transfer(src[3], torch.zeros_like(dst[3]), src_table, dst_table, head_off)
             rec["verified"] = bool(torch.equal(want, dst[3]))
-        if xfer is not None:
-            xfer.close()
+        for x, _, _ in xfers:
+            x.close()
 
     if not args.skip_baseline:
         # Unfused: descriptor list (one per tensor x block, 8 KiB each) into staging, then reshard on the decode GPU.
