@@ -30,10 +30,10 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--iters", type=int, default=1024)
     ap.add_argument("--tile", type=int, default=256 << 10)
-    ap.add_argument("--window", type=int, default=4)
+    ap.add_argument("--window", type=int, default=8)
     ap.add_argument("--compute-passes", type=int, default=1)
     ap.add_argument("--host-iters", type=int, default=128)
-    ap.add_argument("--ctas-per-peer", type=int, default=8)
+    ap.add_argument("--ctas-per-peer", type=int, default=16)
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

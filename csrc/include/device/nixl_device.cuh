@@ -157,7 +157,9 @@ __device__ __forceinline__ nixl_status_t nixlAtomicAdd(uint64_t value, const nix
     if (p == nullptr || (reinterpret_cast<uintptr_t>(p) & 7)) return NIXL_ERR_INVALID_PARAM;
     nixl_gpu_detail::groupSync<level>(); // the group's stores happen-before the elected thread's fence
     if (nixl_gpu_detail::laneOf<level>() == 0) {
-        __threadfence_system();
+        // One release at system scope: it orders the elected thread's own stores and, through the group
+        // barrier above, the other threads' (a separate fence in front of it would wait for the peer's
+        // acknowledgements a second time).
         asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(p), "l"(value) : "memory");
     }
     if (status) status->state = 0;

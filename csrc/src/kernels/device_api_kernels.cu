@@ -83,7 +83,8 @@ __global__ void __launch_bounds__(512) putSignalKernel(NixlDevPutParams p) {
             nixlMemViewElem src{p.local_tiles, 0, tile_off};
             nixlMemViewElem dst{p.remote_tiles, static_cast<size_t>(peer),
                                 (static_cast<size_t>(p.rank) * p.window + slot) * p.tile_bytes + part * slice};
-            nixlPut<nixl_gpu_level_t::BLOCK>(src, dst, slice);
+            // deferred: the signal that follows is the flush (one wait for the peer's acknowledgements per tile, not two)
+            nixlPut<nixl_gpu_level_t::BLOCK>(src, dst, slice, 0, nixl_gpu_flags::defer);
             nixlAtomicAdd<nixl_gpu_level_t::BLOCK>(1, nixlMemViewElem{p.remote_signals, static_cast<size_t>(peer), static_cast<size_t>(p.rank) * 8});
         }
     } else {
