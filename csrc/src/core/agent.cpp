@@ -409,8 +409,10 @@ nixl_status_t nixlAgent::makeConnection(const std::string &remote_agent, const n
     if (it == data->remoteBackends.end()) return NIXL_ERR_NOT_FOUND;
     std::vector<nixlBackendEngine *> targets;
     if (extra_params && !extra_params->backends.empty()) {
-        for (auto *h : extra_params->backends)
-            if (h && it->second.count(h->getType())) targets.push_back(h->engine);
+        for (auto *h : extra_params->backends) {
+            if (!h || !data->hasBackend(h->engine)) return NIXL_ERR_NOT_FOUND; // a handle of another agent must not be driven from here
+            if (it->second.count(h->getType())) targets.push_back(h->engine);
+        }
     } else {
         for (auto &kv : it->second) targets.push_back(data->backends.at(kv.first)->engine);
     }
