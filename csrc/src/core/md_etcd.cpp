@@ -67,12 +67,12 @@ static bool waitFd(int fd, short events, int timeout_ms) {
     return ::poll(&p, 1, timeout_ms) > 0;
 }
 
-int postJson(const std::string &host, int port, const std::string &path, const std::string &body, std::string &reply, int timeout_ms) {
-    reply.clear();
+// Connected TCP socket with send / receive timeouts, or -1.
+static int connectTo(const std::string &host, int port, int timeout_ms) {
     addrinfo hints{}, *res = nullptr;
     hints.ai_family = AF_UNSPEC;
     hints.ai_socktype = SOCK_STREAM;
-    if (::getaddrinfo(host.c_str(), std::to_string(port).c_str(), &hints, &res) != 0 || !res) return 0;
+    if (::getaddrinfo(host.c_str(), std::to_string(port).c_str(), &hints, &res) != 0 || !res) return -1;
     int fd = -1;
     for (addrinfo *a = res; a; a = a->ai_next) {
         fd = ::socket(a->ai_family, a->ai_socktype | SOCK_CLOEXEC, a->ai_protocol);
@@ -85,17 +85,28 @@ int postJson(const std::string &host, int port, const std::string &path, const s
         fd = -1;
     }
     ::freeaddrinfo(res);
-    if (fd < 0) return 0;
-    std::string req = "POST " + path + " HTTP/1.1\r\nHost: " + host + ":" + std::to_string(port) +
-        "\r\nContent-Type: application/json\r\nConnection: close\r\nContent-Length: " + std::to_string(body.size()) + "\r\n\r\n" + body;
+    return fd;
+}
+
+static bool sendAll(int fd, const std::string &req) {
     size_t off = 0;
     while (off < req.size()) {
         const ssize_t n = ::send(fd, req.data() + off, req.size() - off, MSG_NOSIGNAL);
-        if (n <= 0) {
-            ::close(fd);
-            return 0;
-        }
+        if (n <= 0) return false;
         off += static_cast<size_t>(n);
+    }
+    return true;
+}
+
+int postJson(const std::string &host, int port, const std::string &path, const std::string &body, std::string &reply, int timeout_ms) {
+    reply.clear();
+    const int fd = connectTo(host, port, timeout_ms);
+    if (fd < 0) return 0;
+    std::string req = "POST " + path + " HTTP/1.1\r\nHost: " + host + ":" + std::to_string(port) +
+        "\r\nContent-Type: application/json\r\nConnection: close\r\nContent-Length: " + std::to_string(body.size()) + "\r\n\r\n" + body;
+    if (!sendAll(fd, req)) {
+        ::close(fd);
+        return 0;
     }
     std::string raw;
     char buf[8192];
@@ -126,6 +137,76 @@ int postJson(const std::string &host, int port, const std::string &path, const s
         payload.swap(joined);
     }
     reply.swap(payload);
+    return status;
+}
+
+// A streaming POST: the reply body (chunked or not) is handed to `on_data` piece by piece as it
+// arrives, until the peer closes, `keep_going` turns false or `on_data` returns false.  Returns the
+// HTTP status (0: transport failure before a status line).
+int postStream(const std::string &host, int port, const std::string &path, const std::string &body, int timeout_ms,
+               const std::function<bool()> &keep_going, const std::function<bool(const std::string &)> &on_data) {
+    const int fd = connectTo(host, port, timeout_ms);
+    if (fd < 0) return 0;
+    const std::string req = "POST " + path + " HTTP/1.1\r\nHost: " + host + ":" + std::to_string(port) +
+        "\r\nContent-Type: application/json\r\nContent-Length: " + std::to_string(body.size()) + "\r\n\r\n" + body;
+    if (!sendAll(fd, req)) {
+        ::close(fd);
+        return 0;
+    }
+    std::string raw;   // bytes not yet consumed
+    int status = 0;
+    bool chunked = false, headers_done = false;
+    size_t chunk_left = 0; // bytes of the current chunk still to come
+    char buf[8192];
+    bool open = true;
+    while (open && keep_going()) {
+        if (!waitFd(fd, POLLIN, 200)) continue;
+        const ssize_t n = ::recv(fd, buf, sizeof(buf), 0);
+        if (n <= 0) break;
+        raw.append(buf, static_cast<size_t>(n));
+        if (!headers_done) {
+            const size_t hdr_end = raw.find("\r\n\r\n");
+            if (hdr_end == std::string::npos) continue;
+            if (raw.compare(0, 5, "HTTP/") != 0) break;
+            status = std::atoi(raw.c_str() + raw.find(' ') + 1);
+            std::string headers = raw.substr(0, hdr_end);
+            std::transform(headers.begin(), headers.end(), headers.begin(), [](unsigned char c) { return std::tolower(c); });
+            chunked = headers.find("transfer-encoding: chunked") != std::string::npos;
+            raw.erase(0, hdr_end + 4);
+            headers_done = true;
+            if (status != 200) break;
+        }
+        if (!chunked) {
+            if (!raw.empty() && !on_data(raw)) open = false;
+            raw.clear();
+            continue;
+        }
+        for (;;) { // as many whole pieces as the buffer holds
+            if (chunk_left == 0) {
+                const size_t eol = raw.find("\r\n");
+                if (eol == std::string::npos) break;
+                if (eol == 0) { // the CRLF that closes the previous chunk
+                    raw.erase(0, 2);
+                    continue;
+                }
+                chunk_left = std::strtoul(raw.c_str(), nullptr, 16);
+                raw.erase(0, eol + 2);
+                if (chunk_left == 0) { // last chunk
+                    open = false;
+                    break;
+                }
+            }
+            if (raw.empty()) break;
+            const size_t take = std::min(chunk_left, raw.size());
+            if (!on_data(raw.substr(0, take))) {
+                open = false;
+                break;
+            }
+            raw.erase(0, take);
+            chunk_left -= take;
+        }
+    }
+    ::close(fd);
     return status;
 }
 
@@ -253,29 +334,79 @@ nixl_status_t nixlEtcdMetadataBackend::remove(const std::string &) {
     return ret;
 }
 
+// Called with the key of a peer's record that is gone.
+void nixlEtcdMetadataBackend::keyGone(const std::string &key) {
+    std::string agent;
+    std::function<void(const std::string &)> cb;
+    {
+        std::lock_guard<std::mutex> g(mu_);
+        auto it = watched_.find(key);
+        if (it == watched_.end()) return;
+        agent = it->second;
+        watched_.erase(it);
+        cb = onGone_;
+    }
+    NIXL_INFO << "etcd: key " << key << " is gone, invalidating the metadata of " << agent;
+    if (cb) cb(agent);
+}
+
+// One watch stream over the whole namespace (POST /v3/watch, the gateway's form of the reference's
+// DELETE watchers, nixl_etcd_metadata_backend.cpp:262-318): every DELETE event of a key this agent
+// fetched invalidates that peer at once.  Returns false when the gateway has no watch endpoint.
+bool nixlEtcdMetadataBackend::watchStream() {
+    // prefix range: [namespace + "/", namespace + "0")   ('0' is the byte after '/')
+    const std::string body = "{\"create_request\":{\"key\":\"" + nixl_http::base64Encode(namespace_ + "/") + "\",\"range_end\":\"" +
+        nixl_http::base64Encode(namespace_ + "0") + "\"}}";
+    std::string pending; // text of the stream up to the last complete line
+    bool created = false;
+    const int status = nixl_http::postStream(
+        host_, port_, "/v3/watch", body, opTimeoutMs_, [this] { return !stop_.load(); },
+        [&](const std::string &piece) {
+            pending += piece;
+            size_t nl;
+            while ((nl = pending.find('\n')) != std::string::npos) { // one JSON object per line
+                const std::string line = pending.substr(0, nl);
+                pending.erase(0, nl + 1);
+                if (line.find("\"created\"") != std::string::npos) created = true;
+                size_t at = 0;
+                while ((at = line.find("\"DELETE\"", at)) != std::string::npos) {
+                    std::string b64, key;
+                    if (jsonString(line, "key", b64, at) && nixl_http::base64Decode(b64, key)) keyGone(key);
+                    at += 8;
+                }
+            }
+            return true;
+        });
+    watchActive_ = false;
+    return status == 200 && created;
+}
+
 void nixlEtcdMetadataBackend::watchLoop() {
-    auto next = std::chrono::steady_clock::now();
+    // The stream when the gateway offers one; whenever it is not up (old gateway, connection lost),
+    // the keys fetched so far are polled instead, so a deletion is never missed for long.
+    bool stream_ok = true;
     while (!stop_) {
-        std::this_thread::sleep_for(std::chrono::milliseconds(10));
-        if (std::chrono::steady_clock::now() < next) continue;
-        next = std::chrono::steady_clock::now() + std::chrono::milliseconds(pollMs_);
+        if (stream_ok) {
+            watchActive_ = true;
+            const auto t0 = std::chrono::steady_clock::now();
+            stream_ok = watchStream();
+            if (stop_) return;
+            // what was deleted while no stream was up shows in one poll round below
+            if (!stream_ok) NIXL_INFO << "etcd: no watch stream at " << host_ << ":" << port_ << "; polling every " << pollMs_ << " ms";
+            else if (std::chrono::steady_clock::now() - t0 < std::chrono::seconds(1)) std::this_thread::sleep_for(std::chrono::milliseconds(200));
+        } else {
+            for (int waited = 0; waited < pollMs_ && !stop_; waited += 10) std::this_thread::sleep_for(std::chrono::milliseconds(10));
+        }
         std::map<std::string, std::string> snapshot;
-        std::function<void(const std::string &)> cb;
         {
             std::lock_guard<std::mutex> g(mu_);
             snapshot = watched_;
-            cb = onGone_;
         }
         for (const auto &[key, agent] : snapshot) {
             if (stop_) return;
             std::string value;
             if (get(key, value) != NIXL_ERR_NOT_FOUND) continue; // still there, or the store is unreachable: no verdict
-            {
-                std::lock_guard<std::mutex> g(mu_);
-                watched_.erase(key);
-            }
-            NIXL_INFO << "etcd: key " << key << " is gone, invalidating the metadata of " << agent;
-            if (cb) cb(agent);
+            keyGone(key);
         }
     }
 }

@@ -6,8 +6,9 @@
 // <namespace>/<agent>/<label> with namespace NIXL_ETCD_NAMESPACE (default /nixl/agents,
 // :40), fetch waits for a key that is not there yet (watch with timeout, :200; here a poll every
 // 50 ms up to the same etcdWatchTimeout), and a watcher notices when a peer deletes its keys
-// and invalidates that peer's metadata locally (:262-:330; here a poll of the keys fetched so
-// far, every NIXL_ETCD_POLL_MS, default 500).
+// and invalidates that peer's metadata locally (:262-:330; here one watch stream over the
+// namespace through POST /v3/watch, and, whenever that stream is not up, a poll of the keys
+// fetched so far every NIXL_ETCD_POLL_MS, default 500).
 #ifndef NIXL_B200_MD_ETCD_H
 #define NIXL_B200_MD_ETCD_H
 
@@ -25,6 +26,9 @@
 namespace nixl_http {
 // One request, one connection.  Returns the HTTP status (0 on transport failure) and the body.
 int postJson(const std::string &host, int port, const std::string &path, const std::string &body, std::string &reply, int timeout_ms);
+// Streaming reply: pieces of the body go to on_data as they arrive (see md_etcd.cpp).
+int postStream(const std::string &host, int port, const std::string &path, const std::string &body, int timeout_ms,
+               const std::function<bool()> &keep_going, const std::function<bool(const std::string &)> &on_data);
 std::string base64Encode(const std::string &raw);
 bool base64Decode(const std::string &text, std::string &raw);
 } // namespace nixl_http
@@ -47,6 +51,8 @@ public:
 private:
     nixl_status_t get(const std::string &key, std::string &value);
     void watchLoop();
+    bool watchStream();
+    void keyGone(const std::string &key);
 
     std::string host_, namespace_;
     int port_ = 0;
@@ -57,6 +63,7 @@ private:
     std::map<std::string, std::string> watched_;   // key -> peer agent, fetched so far
     std::function<void(const std::string &)> onGone_;
     std::atomic<bool> stop_{false};
+    std::atomic<bool> watchActive_{false}; // a watch stream is being served
     std::thread watcher_;
 };
 

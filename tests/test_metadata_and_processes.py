@@ -127,13 +127,13 @@ def test_two_processes_over_localhost():
         proc.join(5)
 
 
-def _start_fake_etcd():
+def _start_fake_etcd(*flags):
     """The fake gateway runs in its own process: the agent's constructor probes the endpoint from
     inside a native call, during which a server thread of this interpreter could not run."""
     import subprocess
     import sys
 
-    proc = subprocess.Popen([sys.executable, os.path.join(os.path.dirname(os.path.abspath(__file__)), "fake_etcd_gateway.py")],
+    proc = subprocess.Popen([sys.executable, os.path.join(os.path.dirname(os.path.abspath(__file__)), "fake_etcd_gateway.py"), *flags],
                             stdout=subprocess.PIPE, text=True)
     port = int(proc.stdout.readline())
     return proc, port
@@ -146,11 +146,14 @@ def _etcd_keys(port):
     return json.loads(urllib.request.urlopen(f"http://127.0.0.1:{port}/keys", timeout=5).read())
 
 
-def test_etcd_gateway_metadata_roundtrip_and_invalidation(monkeypatch):
-    proc, port = _start_fake_etcd()
+@pytest.mark.parametrize("watch", [True, False], ids=["watch-stream", "poll-only"])
+def test_etcd_gateway_metadata_roundtrip_and_invalidation(monkeypatch, watch):
+    """With a watch stream the DELETE event invalidates the peer at once (the poll interval is set far beyond the
+    test's patience, so only the stream can do it); a gateway without the endpoint is polled."""
+    proc, port = _start_fake_etcd(*([] if watch else ["--no-watch"]))
     monkeypatch.delenv("NIXL_TCPSTORE_ENDPOINT", raising=False)
     monkeypatch.setenv("NIXL_ETCD_ENDPOINTS", f"http://127.0.0.1:1,http://127.0.0.1:{port}")  # the first endpoint is dead
-    monkeypatch.setenv("NIXL_ETCD_POLL_MS", "50")
+    monkeypatch.setenv("NIXL_ETCD_POLL_MS", "60000" if watch else "50")
     from nixl_b200 import nixl_agent, nixl_agent_config
 
     try:
@@ -169,6 +172,11 @@ def test_etcd_gateway_metadata_roundtrip_and_invalidation(monkeypatch):
             time.sleep(0.01)
         assert a.check_remote_metadata("etcd_b") and b.check_remote_metadata("etcd_a")
         assert "/nixl/agents/etcd_a/metadata" in _etcd_keys(port)  # documented key layout: <namespace>/<agent>/<label>
+        import json
+        import urllib.request
+
+        streams = json.loads(urllib.request.urlopen(f"http://127.0.0.1:{port}/watchers", timeout=5).read())
+        assert streams == (2 if watch else 0)  # one stream per agent
         h = a.initialize_xfer("WRITE", ta, tb, "etcd_b")
         assert a.transfer(h) in ("DONE", "PROC")
         while a.check_xfer_state(h) == "PROC":
