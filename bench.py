@@ -23,6 +23,8 @@ registered source buffer and a device->host read of a digest of the buffer this 
              reshard, bf16 and bf16->fp8, ms/request, checked against the PyTorch statement
   ep         MoE dispatch + combine, DeepSeek-V3 shape, 128 and 4096 tokens per GPU, checked on
              every rank against an fp32 PyTorch statement of the routing
+  dput       GPU-initiated put with signal: a persistent kernel puts 256 KiB tiles to every peer from
+             inside its loop (device API), the consumer waits on the remote counter; µs per put
 
 Launch: ``python bench.py`` (1 GPU) or
 ``python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N``.
@@ -51,7 +53,7 @@ def parse_args():
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
     p.add_argument("--block", type=int, default=64 << 20, help="descriptor size in bytes")
     p.add_argument("--batch", type=int, default=16, help="descriptors per request")
-    p.add_argument("--extras", default="baselines,sweep,kv,ep", help="comma list of extras to run ('' or 'none': headline only)")
+    p.add_argument("--extras", default="baselines,sweep,kv,ep,dput", help="comma list of extras to run ('' or 'none': headline only)")
     p.add_argument("--extras-budget", type=float, default=120.0, help="seconds the extras may take in all; sections that do not fit are skipped")
     return p.parse_args()
 
@@ -479,7 +481,7 @@ def main():
     # ---------------------------------------------------------------- extras (outside timed regions)
     extras = {}
     wanted = [x for x in args.extras.split(",") if x and x != "none"]
-    sections = {"baselines": extras_baselines, "sweep": extras_sweep, "kv": extras_kv, "ep": extras_ep}
+    sections = {"baselines": extras_baselines, "sweep": extras_sweep, "kv": extras_kv, "ep": extras_ep, "dput": extras_dput}
     deadline = time.perf_counter() + args.extras_budget
     for name in wanted:
         fn = sections.get(name)
@@ -1037,6 +1039,93 @@ def extras_ep(env, args, headline_gbs, budget_s):
         del buf, x, logits, y
         state.clear()
         torch.cuda.empty_cache()
+    return out
+
+
+# ====================================================================== extras: GPU-initiated put with signal
+
+
+def extras_dput(env, args, headline_gbs, budget_s):
+    """A persistent kernel on every GPU puts 256 KiB tiles to every peer from inside its compute loop (1024 iterations
+    per peer, 20 producer CTAs per peer taking turns, 40 landing slots) with nixlPut<BLOCK> + nixlAtomicAdd of the device API; a consumer
+    CTA waits on the per-slot counters the peers bump and acknowledges, which gates the reuse of a landing slot.  One GPU:
+    the rank puts to itself.  Device-timed, max over ranks.  `verified`: the kernel's status word is clean, every peer's
+    counters add up to the iterations, and after the communication-only run every landing slot holds the source tile
+    of the producer CTA that wrote it last."""
+    from nixl_b200 import nixl_agent, nixl_agent_config
+    from nixl_b200.ops import device_api
+
+    torch, dist = env.torch, env.dist
+    W, rank, dev, local = env.world, env.rank, env.dev, env.local_rank
+    tile, window, cpp, iters = 256 << 10, 40, 20, 1024
+    peers = [r for r in range(W) if r != rank] or [rank]
+    P = len(peers)
+    agent = nixl_agent(f"dput{rank}", nixl_agent_config(enable_prog_thread=False, backends=["NVLINK"]))
+    tiles = torch.randn(P * cpp * tile // 4, dtype=torch.float32, device=dev)  # one source tile per producer CTA
+    landing = torch.zeros(W * window * tile, dtype=torch.uint8, device=dev)
+    signals = torch.zeros(2 * W * window, dtype=torch.int64, device=dev)  # arrival[rank][slot], then acknowledgement[rank][slot]
+    for t in (tiles, landing, signals):
+        agent.register_memory(t)
+    info = {"md": agent.get_agent_metadata(), "landing": (landing.data_ptr(), landing.numel(), local),
+            "signals": (signals.data_ptr(), signals.numel() * 8, local), "name": agent.name}
+    infos = [info]
+    if W > 1:
+        infos = [None] * W
+        dist.all_gather_object(infos, info)
+    for r, i in enumerate(infos):
+        if r != rank:
+            agent.add_remote_agent(i["md"])
+    views = [agent.prep_mem_view(agent.get_xfer_descs(tiles)), agent.prep_mem_view(agent.get_xfer_descs(signals)),
+             agent.prep_mem_view(agent.get_remote_descs([i["landing"] + (i["name"],) for i in infos], "VRAM")),
+             agent.prep_mem_view(agent.get_remote_descs([i["signals"] + (i["name"],) for i in infos], "VRAM"))]
+    peer_ids = torch.tensor(peers, dtype=torch.int32, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+
+    def run(n, passes):
+        signals.zero_()
+        barrier(env)
+        p = device_api.DevPutParams()
+        p.local_tiles, p.local_signals, p.remote_tiles, p.remote_signals = views
+        p.peer_ids = peer_ids.data_ptr()
+        p.peers, p.rank, p.iters, p.window, p.compute_passes, p.ctas_per_peer = P, rank, n, window, passes, cpp
+        p.tile_bytes, p.ack_offset, p.timeout_ns = tile, W * window * 8, 10_000_000_000
+        p.status = status.data_ptr()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        device_api.put_signal_launch(p, dev)
+        e1.record()
+        torch.cuda.synchronize()
+        return max_over_ranks(env, [e0.elapsed_time(e1) * 1e3])[0]
+
+    run(64, 1)
+    t_full = run(iters, 1)
+    def arrived_all():
+        arrived = signals[: W * window].view(W, window).sum(dim=1)
+        return all(int(arrived[r]) == iters for r in peers)
+
+    ok = int(status.item()) == 0 and arrived_all()
+    t_comm = run(iters, 0)
+    ok = ok and int(status.item()) == 0 and arrived_all()
+    all_tiles = [tiles]
+    if W > 1:
+        all_tiles = [torch.empty_like(tiles) for _ in range(W)]
+        dist.all_gather(all_tiles, tiles)
+    for r in peers:
+        pi = ([x for x in range(W) if x != r] or [r]).index(rank)
+        for slot in range(window):
+            last_it = slot + 1 + ((iters - 1 - slot) // window) * window
+            cta = pi * cpp + (last_it - 1) % cpp
+            want = all_tiles[r].view(torch.uint8)[cta * tile:(cta + 1) * tile]
+            got = landing[(r * window + slot) * tile:(r * window + slot + 1) * tile]
+            ok = ok and bool(torch.equal(want, got))
+    del all_tiles
+    out = {"n_gpus": W, "peers_per_gpu": P, "tile_bytes": tile, "iters": iters, "window": window, "ctas_per_peer": cpp,
+           "us_per_iter": round(t_full / iters, 2), "us_per_put": round(t_full / iters / P, 2), "us_per_iter_comm_only": round(t_comm / iters, 2),
+           "GBps_per_gpu": round(P * tile * iters / t_full / 1e3, 1), "GBps_per_gpu_comm_only": round(P * tile * iters / t_comm / 1e3, 1),
+           "verified": all_agree(env, ok)}
+    barrier(env)
+    for v in views:
+        agent.release_mem_view(v)
     return out
 
 

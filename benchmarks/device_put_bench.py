@@ -1,9 +1,10 @@
 #!/usr/bin/env python
 """GPU-initiated put-with-signal benchmark.
 
-A persistent kernel on every GPU puts 256 KiB bf16 tiles to every peer from inside its compute
-loop (1024 iterations) with ``nixlPut<BLOCK>`` + ``nixlAtomicAdd`` (device API); the consumer side
-waits on the remote counter.  Reported: microseconds per iteration, microseconds per put,
+A persistent kernel on every GPU puts 256 KiB tiles to every peer from inside its compute
+loop (1024 iterations per peer, ``--ctas-per-peer`` producer CTAs taking turns) with
+``nixlPut<BLOCK>`` + ``nixlAtomicAdd`` (device API); the consumer side waits on the remote
+per-slot counters and acknowledges.  Reported: microseconds per iteration, microseconds per put,
 aggregate GB/s, and the same traffic posted from the host with ``postXferReq`` as baseline.
 With one GPU the rank talks to itself.  Device-timed (CUDA events), max over ranks.
 
@@ -30,10 +31,10 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--iters", type=int, default=1024)
     ap.add_argument("--tile", type=int, default=256 << 10)
-    ap.add_argument("--window", type=int, default=8)
+    ap.add_argument("--window", type=int, default=40)
     ap.add_argument("--compute-passes", type=int, default=1)
     ap.add_argument("--host-iters", type=int, default=128)
-    ap.add_argument("--ctas-per-peer", type=int, default=16)
+    ap.add_argument("--ctas-per-peer", type=int, default=20)
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -46,9 +47,9 @@ def main():
     P = len(peers)
 
     agent = nixl_agent(f"dput{rank}", nixl_agent_config(enable_prog_thread=False, backends=["NVLINK"]))
-    tiles = torch.randn(P * args.tile // 2, dtype=torch.bfloat16, device=dev)
+    tiles = torch.randn(P * args.ctas_per_peer * args.tile // 4, dtype=torch.float32, device=dev)  # one source tile per producer CTA
     landing = torch.zeros(world * args.window * args.tile, dtype=torch.uint8, device=dev)
-    signals = torch.zeros(2 * world, dtype=torch.int64, device=dev)
+    signals = torch.zeros(2 * world * args.window, dtype=torch.int64, device=dev)  # arrival[rank][slot], then acknowledgement[rank][slot]
     for t in (tiles, landing, signals):
         agent.register_memory(t)
     info = {"md": agent.get_agent_metadata(), "landing": (landing.data_ptr(), landing.numel(), local),
@@ -78,7 +79,7 @@ def main():
         p.peer_ids = peer_ids.data_ptr()
         p.peers, p.rank, p.iters, p.window, p.compute_passes = P, rank, iters, args.window, passes
         p.ctas_per_peer = args.ctas_per_peer
-        p.tile_bytes, p.ack_offset, p.timeout_ns = args.tile, world * 8, 20_000_000_000
+        p.tile_bytes, p.ack_offset, p.timeout_ns = args.tile, world * args.window * 8, 20_000_000_000
         p.status = status.data_ptr()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
@@ -93,12 +94,27 @@ def main():
     run(64, args.compute_passes)  # warm-up
     t_full = run(args.iters, args.compute_passes)
     t_compute_only_proxy = run(args.iters, 0)  # communication only: the cost of the puts without the compute pass
-    ok = int(status.item()) == 0 and int(signals[peers[0]]) == args.iters * args.ctas_per_peer
+    arrived = signals[: world * args.window].view(world, args.window).sum(dim=1)
+    ok = int(status.item()) == 0 and all(int(arrived[r]) == args.iters for r in peers)
+    # The tiles did not change during the communication-only run: every landing slot must hold the source tile of
+    # the producer CTA that wrote it last.
+    if world > 1:
+        all_tiles = [torch.empty_like(tiles) for _ in range(world)]
+        dist.all_gather(all_tiles, tiles)
+        for r in peers:
+            pi = [x for x in range(world) if x != r].index(rank)
+            for slot in range(min(args.window, args.iters)):
+                last_it = slot + 1 + ((args.iters - 1 - slot) // args.window) * args.window
+                cta = pi * args.ctas_per_peer + (last_it - 1) % args.ctas_per_peer
+                want = all_tiles[r].view(torch.uint8)[cta * args.tile:(cta + 1) * args.tile]
+                got = landing[(r * args.window + slot) * args.tile:(r * args.window + slot + 1) * args.tile]
+                ok = ok and bool(torch.equal(want, got))
+        del all_tiles
 
     # Host-posted baseline: the same tile to every peer, posted and completed from the host.
     handles = []
     for j, r in enumerate(peers):
-        la = [(tiles.data_ptr() + j * args.tile, args.tile, local)]
+        la = [(tiles.data_ptr() + j * args.ctas_per_peer * args.tile, args.tile, local)]
         ra = [(infos[r]["landing"][0] + rank * args.window * args.tile, args.tile, infos[r]["landing"][2])]
         handles.append(agent.initialize_xfer("WRITE", agent.get_xfer_descs(la, "VRAM"), agent.get_xfer_descs(ra, "VRAM"), infos[r]["name"]))
     if world > 1:

@@ -233,23 +233,23 @@ int nixl_grouped_gemm_fp8_launch(const NixlGroupedGemmParams *params, void *stre
  * on entry 0 of `sig_view`; status_out[4] receives {last status, status of an out-of-range put,
  * get-pointer of entry 0 non-null, get-pointer of a bad index null}.
  *
- * nixl_devapi_put_signal_launch: the persistent kernel of the device-initiated benchmark.  One
- * producer CTA per peer puts a tile and signals the peer's counter every iteration from inside
- * its compute loop; one consumer CTA waits on this rank's counters and acknowledges, which is
- * the producers' flow control (at most `window` tiles in flight per peer).
- * Memory: local_signals entry 0 = this rank's word array: [0, ranks) arrival counters indexed by
- * source rank, then at ack_offset [0, ranks) acknowledgement counters; remote_signals entry r =
- * the same array of rank r; remote_tiles entry r = rank r's landing area of
- * ranks * window * tile_bytes.
+ * nixl_devapi_put_signal_launch: the persistent kernel of the device-initiated benchmark.
+ * ctas_per_peer producer CTAs per peer take turns at the iterations (CTA c: c+1, c+1+ctas_per_peer, ...): each computes
+ * its tile, puts it whole into slot (it-1) % window of the peer's landing area and bumps that slot's arrival counter
+ * at the peer; one consumer CTA waits for the slots in order and bumps the acknowledgement counters that gate the
+ * producers' reuse of a slot (window >= ctas_per_peer keeps every producer busy).
+ * Memory: local_tiles entry 0 = peers * ctas_per_peer source tiles; local_signals entry 0 = this rank's word array:
+ * arrival[source rank][slot] (ranks * window words), then at ack_offset acknowledgement[rank][slot]; remote_signals
+ * entry r = the same array of rank r; remote_tiles entry r = rank r's landing area of ranks * window * tile_bytes.
  */
 typedef struct NixlDevPutParams {
-    void *local_tiles;          /* local view, entry 0: peers * tile_bytes source tiles */
+    void *local_tiles;          /* local view, entry 0: peers * ctas_per_peer source tiles of tile_bytes */
     void *remote_tiles;         /* remote view, one entry per rank */
     void *local_signals;        /* local view, entry 0 */
     void *remote_signals;       /* remote view, one entry per rank */
     const int32_t *peer_ids;    /* device [peers] ranks this rank talks to */
     int32_t peers, rank, iters, window, compute_passes;
-    int32_t ctas_per_peer;      /* the tile is cut into this many slices, one producer CTA each */
+    int32_t ctas_per_peer;      /* producer CTAs per peer = tiles in flight per peer */
     uint64_t tile_bytes;
     uint64_t ack_offset;        /* bytes */
     uint64_t timeout_ns;

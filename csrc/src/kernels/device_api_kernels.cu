@@ -40,12 +40,16 @@ __global__ void putTestKernel(nixlMemViewH src, nixlMemViewH dst, nixlMemViewH s
 }
 
 // Persistent producer/consumer kernel of the device-initiated benchmark.
-//   producer CTAs (ctas_per_peer per peer): per iteration a stand-in compute pass over a slice of the tile,
-//                  then nixlPut<BLOCK> of the tile into the peer's slot for this rank and an
-//                  atomic add on the peer's counter for this rank;
-//   last CTA:      consumer: waits (bounded) until every peer's counter reaches the iteration.
-// Flow control: a producer may run at most `window` iterations ahead of what its peer consumed
-// (the peer publishes its consumed count back through a second counter).
+//   producer CTAs (ctas_per_peer per peer): CTA c of a peer owns iterations c+1, c+1+ctas_per_peer, ...: a stand-in
+//                  compute pass over the tile, then nixlPut<BLOCK> of the whole tile into slot (it-1) % window of
+//                  the peer's landing zone for this rank and an atomic add on that slot's arrival counter at the
+//                  peer.  A tile's stores are acknowledged by the peer before its signal leaves (about 3 us over
+//                  NVLink); with ctas_per_peer tiles in flight per peer that wait overlaps the next tiles' copies.
+//   last CTA:      consumer: thread (j, s) takes the tiles of peer j in slot s in order: waits (bounded) for the slot's
+//                  counter, then bumps the slot's acknowledgement counter at the peer.
+// Flow control: slot s is written for the k-th time only after its (k-1)-th content was acknowledged.
+// Signal words (local_signals entry 0, remote_signals entry r): arrival[peer][slot] at byte (peer * window + slot) * 8,
+// acknowledgement[peer][slot] at ack_offset + the same.
 __global__ void __launch_bounds__(512) putSignalKernel(NixlDevPutParams p) {
     __shared__ int failed;
     if (threadIdx.x == 0) failed = 0;
@@ -53,14 +57,14 @@ __global__ void __launch_bounds__(512) putSignalKernel(NixlDevPutParams p) {
     const int b = blockIdx.x;
     const int cpp = p.ctas_per_peer;
     if (b < p.peers * cpp) {
-        // Producer: slice `part` of the tile for peer `pi`.
-        const int pi = b / cpp, part = b - pi * cpp;
+        const int pi = b / cpp, lane_it = b - pi * cpp;
         const int peer = p.peer_ids[pi];
-        const size_t slice = p.tile_bytes / cpp;
-        const size_t tile_off = static_cast<size_t>(pi) * p.tile_bytes + part * slice;
+        const size_t tile_off = static_cast<size_t>(b) * p.tile_bytes; // every producer CTA has a source tile of its own
         float4 *tile = reinterpret_cast<float4 *>(static_cast<char *>(nixlGetPtr(p.local_tiles, 0)) + tile_off);
-        const size_t n4 = slice / sizeof(float4);
-        for (int it = 1; it <= p.iters; ++it) {
+        const size_t n4 = p.tile_bytes / sizeof(float4);
+        const uint64_t *ack = reinterpret_cast<const uint64_t *>(static_cast<char *>(nixlGetPtr(p.local_signals, 0)) + p.ack_offset) +
+            static_cast<size_t>(peer) * p.window;
+        for (int it = lane_it + 1; it <= p.iters; it += cpp) {
             // stand-in for the compute that produces the tile
             for (int r = 0; r < p.compute_passes; ++r)
                 for (size_t i = threadIdx.x; i < n4; i += blockDim.x) {
@@ -70,35 +74,36 @@ __global__ void __launch_bounds__(512) putSignalKernel(NixlDevPutParams p) {
                     tile[i] = v;
                 }
             __syncthreads();
-            // do not overrun the consumer: it acknowledges in ack[peer]
-            if (it > p.window) {
-                if (threadIdx.x == 0) {
-                    const uint64_t *ack = reinterpret_cast<const uint64_t *>(static_cast<char *>(nixlGetPtr(p.local_signals, 0)) + p.ack_offset) + peer;
-                    if (nixlSignalWait(ack, static_cast<uint64_t>(it - p.window), p.timeout_ns) != NIXL_SUCCESS) failed = 1;
-                }
+            const int slot = (it - 1) % p.window;
+            const uint64_t uses_before = static_cast<uint64_t>((it - 1) / p.window);
+            if (uses_before > 0) { // the slot's previous content must have been consumed
+                if (threadIdx.x == 0 && nixlSignalWait(ack + slot, uses_before, p.timeout_ns) != NIXL_SUCCESS) failed = 1;
                 __syncthreads();
                 if (failed) break;
             }
-            const size_t slot = static_cast<size_t>((it - 1) % p.window);
             nixlMemViewElem src{p.local_tiles, 0, tile_off};
-            nixlMemViewElem dst{p.remote_tiles, static_cast<size_t>(peer),
-                                (static_cast<size_t>(p.rank) * p.window + slot) * p.tile_bytes + part * slice};
+            nixlMemViewElem dst{p.remote_tiles, static_cast<size_t>(peer), (static_cast<size_t>(p.rank) * p.window + slot) * p.tile_bytes};
             // deferred: the signal that follows is the flush (one wait for the peer's acknowledgements per tile, not two)
-            nixlPut<nixl_gpu_level_t::BLOCK>(src, dst, slice, 0, nixl_gpu_flags::defer);
-            nixlAtomicAdd<nixl_gpu_level_t::BLOCK>(1, nixlMemViewElem{p.remote_signals, static_cast<size_t>(peer), static_cast<size_t>(p.rank) * 8});
+            nixlPut<nixl_gpu_level_t::BLOCK>(src, dst, p.tile_bytes, 0, nixl_gpu_flags::defer);
+            nixlAtomicAdd<nixl_gpu_level_t::BLOCK>(
+                1, nixlMemViewElem{p.remote_signals, static_cast<size_t>(peer), (static_cast<size_t>(p.rank) * p.window + slot) * 8});
         }
     } else {
-        // Consumer: thread j watches peer j's arrivals (every slice counts once) and acknowledges whole tiles.
-        if (static_cast<int>(threadIdx.x) < p.peers) {
-            const int peer = p.peer_ids[threadIdx.x];
-            const uint64_t *arrived = reinterpret_cast<const uint64_t *>(nixlGetPtr(p.local_signals, 0)) + peer;
-            for (int it = 1; it <= p.iters; ++it) {
-                if (nixlSignalWait(arrived, static_cast<uint64_t>(it) * cpp, p.timeout_ns) != NIXL_SUCCESS) {
+        // Consumer: thread (j, s) takes the tiles that peer j puts into slot s, in order.  One thread per slot: an
+        // acknowledgement is a release at system scope, which waits for the previous one to be confirmed by the peer;
+        // with a thread per slot those round trips overlap.
+        const int pi = static_cast<int>(threadIdx.x) / p.window, slot = static_cast<int>(threadIdx.x) % p.window;
+        if (pi < p.peers) {
+            const int peer = p.peer_ids[pi];
+            const uint64_t *arrived = reinterpret_cast<const uint64_t *>(nixlGetPtr(p.local_signals, 0)) + static_cast<size_t>(peer) * p.window + slot;
+            uint64_t uses = 0;
+            for (int it = slot + 1; it <= p.iters; it += p.window) {
+                if (nixlSignalWait(arrived, ++uses, p.timeout_ns) != NIXL_SUCCESS) {
                     failed = 1;
                     break;
                 }
                 nixlAtomicAdd<nixl_gpu_level_t::THREAD>(
-                    1, nixlMemViewElem{p.remote_signals, static_cast<size_t>(peer), p.ack_offset + static_cast<size_t>(p.rank) * 8});
+                    1, nixlMemViewElem{p.remote_signals, static_cast<size_t>(peer), p.ack_offset + (static_cast<size_t>(p.rank) * p.window + slot) * 8});
             }
         }
     }
@@ -122,8 +127,7 @@ extern "C" int nixl_devapi_put_test(int level, const void *src_view, const void 
 }
 
 extern "C" int nixl_devapi_put_signal_launch(const NixlDevPutParams *params, void *stream) {
-    if (!params || params->peers <= 0 || params->peers > 64 || params->window <= 0 || params->ctas_per_peer <= 0 ||
-        (params->tile_bytes % (16ull * params->ctas_per_peer)))
+    if (!params || params->peers <= 0 || params->peers > 64 || params->window <= 0 || params->ctas_per_peer <= 0 || (params->tile_bytes % 16ull))
         return cudaErrorInvalidValue;
     // All CTAs must be resident together (producers wait for acknowledgements raised by consumer
     // CTAs of the peers, and the local consumer CTA must run next to the producers).
@@ -131,7 +135,7 @@ extern "C" int nixl_devapi_put_signal_launch(const NixlDevPutParams *params, voi
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const int grid = params->peers * params->ctas_per_peer + 1;
-    if (grid > sms) return cudaErrorInvalidValue;
+    if (grid > sms || params->peers * params->window > 512) return cudaErrorInvalidValue;
     putSignalKernel<<<grid, 512, 0, static_cast<cudaStream_t>(stream)>>>(*params);
     return cudaGetLastError();
 }
