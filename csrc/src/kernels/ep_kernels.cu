@@ -622,6 +622,40 @@ __device__ __forceinline__ void epCombinePull(const NixlEpCombineParams &p) {
     else pullReduce<kMaxTopk, false>(p, El, vecs, nt, groups_per_cta, grp, gtid);
 }
 
+// One warp: dst[v] = sum over the N rows of w[k] * src[k][v], fp32 accumulation, bf16 out, U vector positions
+// (times N rows) in flight per lane.  dst may be a peer's memory.
+template <int N, int U>
+__device__ __forceinline__ void weightedRowsToPeer(const uint4 *const (&src)[8], const float (&w)[8], uint4 *dst, int vecs, int lane) {
+    for (int v0 = lane; v0 < vecs; v0 += 32 * U) {
+        uint4 raw[U][N];
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+#pragma unroll
+            for (int k = 0; k < N; ++k)
+                if (v0 + u * 32 < vecs) raw[u][k] = ldNc(src[k] + v0 + u * 32);
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            if (v0 + u * 32 >= vecs) continue;
+            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int k = 0; k < N; ++k) {
+                const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&raw[u][k]);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float2 f = __bfloat1622float2(h[j]);
+                    acc[2 * j] = fmaf(w[k], f.x, acc[2 * j]);
+                    acc[2 * j + 1] = fmaf(w[k], f.y, acc[2 * j + 1]);
+                }
+            }
+            uint4 o;
+            __nv_bfloat162 *oh = reinterpret_cast<__nv_bfloat162 *>(&o);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) oh[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+            stPeer16(dst + v0 + u * 32, o);
+        }
+    }
+}
+
 // Rank-reduced combine (NixlEpCombineParams::max_tokens).  Phase 1, expert rank: one warp per (token, home
 // rank) group record adds the token's rows up in fp32, weighted, and stores ONE bf16 row at the home rank.
 // Phase 2, home rank: add the rows of the ranks the token went to.
@@ -660,39 +694,19 @@ __device__ __forceinline__ void epCombineRankReduce(const NixlEpCombineParams &p
             const float w[8] = {__uint_as_float(w0.x), __uint_as_float(w0.y), __uint_as_float(w0.z), __uint_as_float(w0.w),
                                 __uint_as_float(w1.x), __uint_as_float(w1.y), __uint_as_float(w1.z), __uint_as_float(w1.w)};
             const uint4 *src[8];
+            float wk[8];
 #pragma unroll
-            for (int k = 0; k < 8; ++k) src[k] = reinterpret_cast<const uint4 *>(x + static_cast<long long>(k < n ? rows[k] : rows[0]) * p.H);
-            uint4 *dst = reinterpret_cast<uint4 *>(peer + p.lay.off_comb_x + (static_cast<long long>(p.rank) * M + t) * p.H * 2);
-            constexpr int kU = 2; // vector positions in flight per lane (times up to eight rows)
-            for (int v0 = lane; v0 < vecs; v0 += 32 * kU) {
-                uint4 raw[kU][8];
-#pragma unroll
-                for (int u = 0; u < kU; ++u)
-#pragma unroll
-                    for (int k = 0; k < 8; ++k)
-                        if (k < n && v0 + u * 32 < vecs) raw[u][k] = ldNc(src[k] + v0 + u * 32);
-#pragma unroll
-                for (int u = 0; u < kU; ++u) {
-                    if (v0 + u * 32 >= vecs) continue;
-                    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-                    for (int k = 0; k < 8; ++k) {
-                        if (k >= n) continue;
-                        const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&raw[u][k]);
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const float2 f = __bfloat1622float2(h[j]);
-                            acc[2 * j] = fmaf(w[k], f.x, acc[2 * j]);
-                            acc[2 * j + 1] = fmaf(w[k], f.y, acc[2 * j + 1]);
-                        }
-                    }
-                    uint4 o;
-                    __nv_bfloat162 *oh = reinterpret_cast<__nv_bfloat162 *>(&o);
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) oh[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
-                    stPeer16(dst + v0 + u * 32, o);
-                }
+            for (int k = 0; k < 8; ++k) {
+                src[k] = reinterpret_cast<const uint4 *>(x + static_cast<long long>(k < n ? rows[k] : rows[0]) * p.H);
+                wk[k] = k < n ? w[k] : 0.f; // padding rows repeat the first one with weight zero
             }
+            uint4 *dst = reinterpret_cast<uint4 *>(peer + p.lay.off_comb_x + (static_cast<long long>(p.rank) * M + t) * p.H * 2);
+            // Eight 16-byte loads in flight per lane whatever the number of rows (with top-8 over eight ranks a
+            // group has one or two rows most of the time).
+            if (n == 1) weightedRowsToPeer<1, 8>(src, wk, dst, vecs, lane);
+            else if (n == 2) weightedRowsToPeer<2, 4>(src, wk, dst, vecs, lane);
+            else if (n <= 4) weightedRowsToPeer<4, 2>(src, wk, dst, vecs, lane);
+            else weightedRowsToPeer<8, 1>(src, wk, dst, vecs, lane);
         }
         __syncthreads();
         if (tid == 0) __threadfence_system();
@@ -765,6 +779,10 @@ __device__ __forceinline__ void epCombineRankReduce(const NixlEpCombineParams &p
     }
 }
 
+// The rank-reduced mode as a kernel of its own: it needs far fewer registers than the pull mode's double-buffered
+// reduction, so two CTAs fit on an SM and twice as many loads are in flight.
+__global__ void __launch_bounds__(kThreads, 2) epCombineRankReduceKernel(const __grid_constant__ NixlEpCombineParams p) { epCombineRankReduce(p); }
+
 __global__ void __launch_bounds__(kThreads) epCombineKernel(const __grid_constant__ NixlEpCombineParams p) {
     __shared__ int offs[kMaxRanks * 8 + 1]; // expert_offsets copy (El + 1 <= 513)
     __shared__ int cnts[kMaxRanks * 8];
@@ -773,10 +791,6 @@ __global__ void __launch_bounds__(kThreads) epCombineKernel(const __grid_constan
     char *self = peerBase(p.peers, p.rank);
     const int vecs = p.H / 8;
 
-    if (p.pull == 2) {
-        epCombineRankReduce(p);
-        return;
-    }
     if (p.pull) {
         epCombinePull(p);
         return;
@@ -1051,8 +1065,16 @@ extern "C" int nixl_ep_combine_launch(const NixlEpCombineParams *params, void *s
     if (p.R <= 0 || p.R > kMaxRanks || p.E <= 0 || p.E % p.R || p.K <= 0 || p.K > kMaxTopk || p.H <= 0 || p.H % 8 ||
         p.E / p.R > kMaxRanks * 8 || p.rank < 0 || p.rank >= p.R)
         return cudaErrorInvalidValue;
-    const int grid = coopGrid(reinterpret_cast<const void *>(epCombineKernel), p.grid, 0);
     void *args[] = {const_cast<NixlEpCombineParams *>(params)};
+    if (p.pull == 2) {
+        int dev = 0, sms = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        const int grid = coopGrid(reinterpret_cast<const void *>(epCombineRankReduceKernel), p.grid > 0 ? p.grid : 2 * sms, 0);
+        return cudaLaunchCooperativeKernel(reinterpret_cast<const void *>(epCombineRankReduceKernel), dim3(grid), dim3(kThreads), args, 0,
+                                           static_cast<cudaStream_t>(stream));
+    }
+    const int grid = coopGrid(reinterpret_cast<const void *>(epCombineKernel), p.grid, 0);
     return cudaLaunchCooperativeKernel(reinterpret_cast<const void *>(epCombineKernel), dim3(grid), dim3(kThreads), args, 0,
                                        static_cast<cudaStream_t>(stream));
 }

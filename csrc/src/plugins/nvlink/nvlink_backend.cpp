@@ -173,6 +173,7 @@ std::string encodePeer(const PeerId &p) {
     sd.addBuf("ptag", &p.procTag, sizeof(p.procTag));
     sd.addBuf("etag", &p.engineTag, sizeof(p.engineTag));
     sd.addStr("sock", p.sockName);
+    if (!p.ringName.empty()) sd.addStr("ring", p.ringName);
     return sd.exportStr();
 }
 
@@ -185,6 +186,7 @@ bool decodePeer(const std::string &blob, PeerId &p) {
     if (sd.getBuf("ptag", &p.procTag, sizeof(p.procTag)) != NIXL_SUCCESS) return false;
     if (sd.getBuf("etag", &p.engineTag, sizeof(p.engineTag)) != NIXL_SUCCESS) return false;
     p.sockName = sd.getStr("sock");
+    p.ringName = sd.getBufLen("ring") > 0 ? sd.getStr("ring") : std::string();
     return !p.agent.empty() && !p.sockName.empty();
 }
 
@@ -413,6 +415,14 @@ Engine::Engine(const nixlBackendInitParams *init) : nixlBackendEngine(init) {
     int big = 8 << 20;
     setsockopt(notifFd_, SOL_SOCKET, SO_RCVBUF, &big, sizeof(big));
     setsockopt(notifFd_, SOL_SOCKET, SO_SNDBUF, &big, sizeof(big));
+
+    notifRingEnabled_ = paramBool(params, "notif_ring", true);
+    if (notifRingEnabled_ && cuda_) {
+        char ring[96];
+        std::snprintf(ring, sizeof(ring), "/nixl_b200.%lld.%016llx", static_cast<long long>(self_.pid), static_cast<unsigned long long>(self_.engineTag));
+        if (notifRing_.create(ring)) self_.ringName = ring;
+        else NIXL_DEBUG << "NVLINK backend: no shared-memory notification ring (" << std::strerror(errno) << "); notifications use datagrams";
+    }
 
     {
         std::lock_guard<std::mutex> g(g_regMu);
@@ -1237,7 +1247,18 @@ nixl_status_t Engine::postXfer(const nixl_xfer_op_t &operation, const nixl_meta_
                 break;
             }
             b.viaProxy = false;
-            if (b.proxyEligible && !has_user_stream && postViaProxy(c, b)) continue; // no CUDA call on this path
+            // A request that is one kernel batch and nothing else lets the kernel's tail release the
+            // notification itself (notif_ring.h); such a request skips the doorbell proxy, whose
+            // commands have no room for it.
+            std::shared_ptr<NotifRingWriter> ring;
+            b.notifWord = nullptr;
+            b.launch.notifWord = nullptr;
+            if (req->notifPending && req->kernels.size() == 1 && req->hostCopies.empty() && req->cmaCopies.empty() && req->asyncCopies.empty() &&
+                (ring = ringOf(*req->peer)) && ring->claim(self_.agent, req->notifMsg, &b.notifWord, &b.notifSeq)) {
+                b.launch.notifWord = ring->deviceWord(b.notifWord);
+                b.launch.notifSeq = b.notifSeq;
+            }
+            if (!b.notifWord && b.proxyEligible && !has_user_stream && postViaProxy(c, b)) continue; // no CUDA call on this path
             use(b.device);
             cudaStream_t s = has_user_stream ? user_stream : b.stream;
             if (b.uploaded && !b.tableReady && b.launch.table && !cudaOk(cudaStreamWaitEvent(s, b.uploaded, 0), "cudaStreamWaitEvent")) {
@@ -1255,14 +1276,17 @@ nixl_status_t Engine::postXfer(const nixl_xfer_op_t &operation, const nixl_meta_
                 ok = ok && cudaOk(cudaMemcpyAsync(reinterpret_cast<void *>(d.dst), reinterpret_cast<const void *>(d.src), d.len, cudaMemcpyDefault, s),
                                   "cudaMemcpyAsync");
             const cudaError_t le = b.launch.totalChunks > 0 ? launchBatchCopy(b.launch, c->gridCtas, copyPath_, s)
-                                                            : launchSignal(b.launch.hostFlag, seq, s);
+                                                            : launchSignal(b.launch.hostFlag, seq, b.launch.notifWord, b.launch.notifSeq, s);
             if (!cudaOk(le, "copy kernel launch")) {
+                if (b.notifWord) NotifRingWriter::complete(b.notifWord, b.notifSeq, false); // nothing will release the slot: void it
+                b.notifWord = nullptr;
                 err = NIXL_ERR_BACKEND; // copies queued before stay unreported: the stream is in an error state anyway
                 break;
             }
             g_kernelLaunches.fetch_add(1, std::memory_order_relaxed);
             b.seq = seq;
             b.inFlight = true;
+            if (b.notifWord) req->notifPending = false; // the kernel delivers it
             if (!ok) {
                 err = NIXL_ERR_BACKEND;
                 break;
@@ -1322,8 +1346,11 @@ nixl_status_t Engine::pollData(ReqH *req) const {
         b.inFlight = false;
         if (v >> 63) {
             NIXL_ERROR << "NVLINK backend: copy kernel reported a lost bulk copy";
+            if (b.notifWord) NotifRingWriter::complete(b.notifWord, b.notifSeq, false); // the kernel left the slot alone
+            b.notifWord = nullptr;
             return NIXL_ERR_BACKEND;
         }
+        b.notifWord = nullptr;
     }
     if (req->asyncInFlight) {
         for (auto &e : req->asyncEvents) {
@@ -1431,6 +1458,41 @@ nixl_status_t Engine::estimateXferCost(const nixl_xfer_op_t &, const nixl_meta_d
 
 // ================================================================ notifications
 
+namespace {
+void unregisterRingMapping(void *base) {
+    if (cudaHostUnregister(base) != cudaSuccess) cudaGetLastError();
+}
+} // namespace
+
+// The peer's notification ring, mapped into this process and registered with CUDA so that a
+// kernel can store into it.  nullptr: the peer has none, or it cannot be mapped here (the
+// datagram path serves then).
+std::shared_ptr<NotifRingWriter> Engine::ringOf(const PeerId &peer) const {
+    if (!notifRingEnabled_ || !cuda_ || peer.ringName.empty()) return nullptr;
+    std::lock_guard<std::mutex> g(ringMu_);
+    auto it = peerRings_.find(peer.ringName);
+    if (it != peerRings_.end()) return it->second->devBase.load(std::memory_order_acquire) ? it->second : nullptr;
+    std::shared_ptr<NotifRingWriter> w = NotifRingWriter::open(peer.ringName);
+    if (!w) {
+        NIXL_DEBUG << "NVLINK backend: cannot map the notification ring " << peer.ringName << " of " << peer.agent;
+        return nullptr;
+    }
+    peerRings_[peer.ringName] = w; // also remembers a failed registration: it is not tried again
+    if (!w->devBase.load(std::memory_order_acquire) && !w->registerFailed.load(std::memory_order_acquire)) {
+        NotifRingWriter::unregisterHook.store(&unregisterRingMapping, std::memory_order_release);
+        void *dev = nullptr;
+        if (cudaHostRegister(w->base(), w->bytes(), cudaHostRegisterMapped | cudaHostRegisterPortable) == cudaSuccess &&
+            cudaHostGetDevicePointer(&dev, w->base(), 0) == cudaSuccess && dev) {
+            w->devBase.store(static_cast<char *>(dev), std::memory_order_release);
+        } else {
+            cudaGetLastError();
+            w->registerFailed.store(true, std::memory_order_release);
+            NIXL_DEBUG << "NVLINK backend: cannot register the notification ring of " << peer.agent << " with CUDA";
+        }
+    }
+    return w->devBase.load(std::memory_order_acquire) ? w : nullptr;
+}
+
 void Engine::pushNotif(const std::string &from, const std::string &msg) {
     std::lock_guard<std::mutex> g(notifMu_);
     inbox_.emplace_back(from, msg);
@@ -1476,6 +1538,7 @@ nixl_status_t Engine::getNotifs(notif_list_t &notif_list) {
     std::lock_guard<std::mutex> g(notifMu_);
     for (auto &n : inbox_) notif_list.push_back(std::move(n));
     inbox_.clear();
+    if (notifRing_.ok()) notifRing_.poll(notif_list);
     // The receive buffer lives in the engine: this is the target's polling path.
     std::vector<char> &buf = notifBuf_;
     if (buf.empty()) buf.resize(256 * 1024);

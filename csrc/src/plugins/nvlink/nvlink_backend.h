@@ -34,6 +34,7 @@
 #include <cuda_runtime.h>
 
 #include "backend/backend_engine.h"
+#include "plugins/nvlink/notif_ring.h"
 #include "plugins/nvlink/vmm_share.h"
 #include "plugins/nvlink/xfer_kernels.h"
 
@@ -47,6 +48,7 @@ struct PeerId {
     uint64_t procTag = 0;   // random per process: tells "same pid number" from "same process"
     uint64_t engineTag = 0; // random per engine instance
     std::string sockName;   // abstract unix datagram socket receiving notifications
+    std::string ringName;   // shared-memory notification ring (empty: none)
 };
 
 class Engine;
@@ -187,6 +189,8 @@ struct KernelBatch {
     cudaEvent_t uploaded = nullptr;
     uint64_t seq = 0;
     bool inFlight = false;
+    uint64_t *notifWord = nullptr; // host address of the notification slot this post claimed (nullptr: none)
+    uint64_t notifSeq = 0;
 };
 
 struct HostCopy { void *dst; const void *src; size_t len; };
@@ -320,6 +324,11 @@ private:
 
     VmmFdServer fdServer_; // hands exported VMM descriptors to importing processes (started with the first VMM registration)
     int notifFd_ = -1;
+    bool notifRingEnabled_ = true; // "notif_ring": notifications of kernel-path requests are released by the copy kernel itself
+    NotifRingOwner notifRing_;     // the ring peers write into
+    mutable std::mutex ringMu_;
+    mutable std::unordered_map<std::string, std::shared_ptr<NotifRingWriter>> peerRings_; // by ring name
+    std::shared_ptr<NotifRingWriter> ringOf(const PeerId &peer) const; // mapped and registered with CUDA, or nullptr
     mutable std::mutex notifMu_;
     notif_list_t inbox_; // same-process deliveries
     std::vector<char> notifBuf_; // receive buffer of getNotifs, kept between polls

@@ -145,7 +145,10 @@ __device__ __forceinline__ void finishBatch(const XferLaunch &p) {
             last = prev == gridDim.x - 1;
             if (last) *p.doneCounter = 0; // ready for the next post of this request (stream order protects it)
         }
-        if (last) st_release_sys(p.hostFlag, p.seq);
+        if (last) {
+            if (p.notifWord) st_release_sys(p.notifWord, p.notifSeq); // the target learns of the data without this side's host
+            st_release_sys(p.hostFlag, p.seq);
+        }
     }
 }
 
@@ -344,6 +347,7 @@ __global__ void __launch_bounds__(128) batchCopyBulk(const __grid_constant__ Xfe
         if (last) {
             // Bit 63 set by any CTA marks the batch as failed; keep it.
             const unsigned long long cur = failed ? (1ull << 63) : (atomicAdd(reinterpret_cast<unsigned long long *>(p.hostFlag), 0ull) & (1ull << 63));
+            if (p.notifWord && !cur) st_release_sys(p.notifWord, p.notifSeq); // a failed batch notifies nobody: the host voids the slot
             st_release_sys(p.hostFlag, p.seq | cur);
         }
     }
@@ -586,7 +590,10 @@ __global__ void __launch_bounds__(kThreads) proxyKernel(const __grid_constant__ 
     }
 }
 
-__global__ void signalOnly(uint64_t *flag, uint64_t seq) { st_release_sys(flag, seq); }
+__global__ void signalOnly(uint64_t *flag, uint64_t seq, uint64_t *notifWord, uint64_t notifSeq) {
+    if (notifWord) st_release_sys(notifWord, notifSeq);
+    st_release_sys(flag, seq);
+}
 
 } // namespace
 
@@ -596,8 +603,8 @@ cudaError_t launchProxy(const ProxyLaunch &p, int workers, cudaStream_t stream) 
     return cudaGetLastError();
 }
 
-cudaError_t launchSignal(uint64_t *hostFlag, uint64_t seq, cudaStream_t stream) {
-    signalOnly<<<1, 1, 0, stream>>>(hostFlag, seq);
+cudaError_t launchSignal(uint64_t *hostFlag, uint64_t seq, uint64_t *notifWord, uint64_t notifSeq, cudaStream_t stream) {
+    signalOnly<<<1, 1, 0, stream>>>(hostFlag, seq, notifWord, notifSeq);
     return cudaGetLastError();
 }
 

@@ -32,6 +32,8 @@ struct XferLaunch {
     unsigned int *doneCounter;  // device word, zero between launches
     uint64_t *hostFlag;         // device-visible address of the pinned completion word
     uint64_t seq;               // value stored to *hostFlag when the batch is complete
+    uint64_t *notifWord;        // device-visible sequence word of a notification slot in the target's host memory, or nullptr
+    uint64_t notifSeq;          // value stored to *notifWord when the batch is complete (before the completion word)
     XferDesc inl[kInlineDescs];
     uint32_t inlStart[kInlineDescs + 1];
 };
@@ -46,7 +48,8 @@ cudaError_t launchBatchCopy(const XferLaunch &params, int grid_ctas, CopyPath pa
 
 // One thread stores `seq` to the completion word with release semantics at system scope, after
 // everything queued earlier on `stream` (the copy-engine path's completion).
-cudaError_t launchSignal(uint64_t *hostFlag, uint64_t seq, cudaStream_t stream);
+// With notifWord, `notifSeq` goes to it first.
+cudaError_t launchSignal(uint64_t *hostFlag, uint64_t seq, uint64_t *notifWord, uint64_t notifSeq, cudaStream_t stream);
 
 // ------------------------------------------------------------------ doorbell proxy
 //

@@ -158,6 +158,46 @@ def test_write_read_and_notifications_between_processes():
     _run_ranks(_transfer_rank)
 
 
+def _ring_rank(rank, world, dev, queues, barrier, extra):
+    import time
+    import torch
+    from nixl_b200 import nixl_agent, nixl_agent_config
+
+    agent = nixl_agent(f"rg{rank}", nixl_agent_config(enable_prog_thread=False, backends=["NVLINK"]))
+    buf = torch.full((1 << 28,), 5 + rank, dtype=torch.uint8, device=f"cuda:{dev}")
+    agent.register_memory(buf)
+    peer = 1 - rank
+    queues[peer].put((agent.get_agent_metadata(), (buf.data_ptr(), buf.numel(), dev)))
+    md, theirs = queues[rank].get(timeout=60)
+    agent.add_remote_agent(md)
+    torch.cuda.synchronize()
+    barrier.wait(60)
+    if rank == 0:
+        handles = []
+        for i in range(3):  # three requests in flight, none of them polled
+            h = agent.initialize_xfer("WRITE", agent.get_xfer_descs([(buf.data_ptr(), buf.numel(), dev)], "VRAM"),
+                                      agent.get_xfer_descs([theirs], "VRAM"), f"rg{peer}", f"landed-{i}".encode())
+            assert agent.transfer(h) in ("DONE", "PROC")
+            handles.append(h)
+        barrier.wait(60)  # the target has its notifications; only now does this side look at its requests
+        for h in handles:
+            assert _wait(agent, h) == "DONE"
+            agent.release_xfer_handle(h)
+    else:
+        got = []
+        end = time.monotonic() + 20
+        while time.monotonic() < end and len(got) < 3:
+            got.extend(agent.get_new_notifs().get("rg0", []))
+        assert sorted(got) == [b"landed-0", b"landed-1", b"landed-2"]
+        assert int(buf.min()) == 5 and int(buf.max()) == 5  # rank 0's bytes, complete
+        barrier.wait(60)
+    barrier.wait(60)
+
+
+def test_target_gets_notifications_while_the_initiator_never_polls():
+    _run_ranks(_ring_rank)
+
+
 # ---------------------------------------------------------------------------------------------- VMM memory
 
 

@@ -133,6 +133,44 @@ def test_notification_after_data_and_stream_order():
     a.release_xfer_handle(h)
 
 
+def _poll_notifs(agent, who, seconds):
+    import time
+    got = []
+    end = time.monotonic() + seconds
+    while time.monotonic() < end and not got:
+        got.extend(agent.get_new_notifs().get(who, []))
+    return got
+
+
+def test_notification_reaches_the_target_without_the_initiator_polling():
+    """The copy kernel's tail releases the notification in the target's ring itself: the target learns of
+    the finished WRITE although the initiator never looks at its request again.  Without the ring the
+    datagram leaves only when the initiator's host has seen the completion word."""
+    for ring in (True, False):
+        a, b = _pair(f"nr{int(ring)}", {"notif_ring": "true" if ring else "false"})
+        src = torch.full((1 << 29,), 9, dtype=torch.uint8, device="cuda:0")
+        dst = torch.zeros_like(src)
+        a.register_memory(src)
+        b.register_memory(dst)
+        _connect(a, b)
+        torch.cuda.synchronize()
+        h = a.initialize_xfer("WRITE", src, dst, b.name, b"landed")
+        assert a.transfer(h) == "PROC"  # 512 MiB: still running when the post returns
+        if ring:
+            assert _poll_notifs(b, a.name, 5.0) == [b"landed"]
+            assert int(dst[-4096:].min()) == 9 and int(dst[:4096].min()) == 9  # the data was complete before the notification
+        else:
+            assert _poll_notifs(b, a.name, 0.2) == []
+        assert _wait(a, h) == "DONE"
+        if not ring:
+            assert _poll_notifs(b, a.name, 5.0) == [b"landed"]
+        assert _poll_notifs(b, a.name, 0.05) == []  # delivered once
+        torch.cuda.synchronize()
+        assert int(dst.min()) == 9
+        a.release_xfer_handle(h)
+        del a, b
+
+
 def test_bulk_path_deep_pipeline_is_byte_exact():
     """One descriptor, 256 KiB chunks: every CTA runs eight 32 KiB pieces through its four
     shared-memory stages, so each stage is refilled while the store that last used it may still
