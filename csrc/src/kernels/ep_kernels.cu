@@ -622,24 +622,45 @@ __device__ __forceinline__ void epCombinePull(const NixlEpCombineParams &p) {
     else pullReduce<kMaxTopk, false>(p, El, vecs, nt, groups_per_cta, grp, gtid);
 }
 
-// One warp: dst[v] = sum over the N rows of w[k] * src[k][v], fp32 accumulation, bf16 out, U vector positions
-// (times N rows) in flight per lane.  dst may be a peer's memory.
-template <int N, int U>
-__device__ __forceinline__ void weightedRowsToPeer(const uint4 *const (&src)[8], const float (&w)[8], uint4 *dst, int vecs, int lane) {
-    for (int v0 = lane; v0 < vecs; v0 += 32 * U) {
-        uint4 raw[U][N];
+// Staging area of one warp of the rank-reduced combine: kRrSlots 16-byte slots per lane, filled by asynchronous
+// copies.  Loads that wait in shared memory instead of registers let a warp keep 12 KB in flight, and two CTAs fit
+// on an SM.
+constexpr int kRrSlots = 24;
+constexpr int kRrWarpBytes = kRrSlots * 32 * 16;
+constexpr int kRrCtaBytes = (kThreads / 32) * kRrWarpBytes;
+
+__device__ __forceinline__ void cpAsync16(uint32_t smem_addr, const void *g) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr), "l"(g) : "memory"); // through L2: sees what peers wrote
+}
+__device__ __forceinline__ void cpAsyncWaitAll() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
+// One warp: dst[v] = sum over the n rows (1..8) of w[k] * src[k][v] for the row's `vecs` 16-byte vectors, fp32
+// accumulation, bf16 out.  kRrSlots / n vector positions of every row are in flight per lane.  Each lane reads back
+// only the slots it filled itself, so its own wait is all the synchronisation the area needs.  dst may be a peer's memory.
+__device__ __forceinline__ void warpWeightedRows(int n, const uint4 *const (&src)[8], const float (&w)[8], uint4 *dst, int vecs, int lane,
+                                                 uint4 *stage) {
+    const int per_pass = kRrSlots / n;
+    const uint32_t sbase = static_cast<uint32_t>(__cvta_generic_to_shared(stage)) + lane * 16;
+    for (int v0 = lane; v0 < vecs; v0 += 32 * per_pass) {
+#pragma unroll 1
+        for (int u = 0; u < per_pass; ++u) {
+            const int v = v0 + u * 32;
+            if (v >= vecs) break;
 #pragma unroll
-        for (int u = 0; u < U; ++u)
-#pragma unroll
-            for (int k = 0; k < N; ++k)
-                if (v0 + u * 32 < vecs) raw[u][k] = ldNc(src[k] + v0 + u * 32);
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-            if (v0 + u * 32 >= vecs) continue;
+            for (int k = 0; k < 8; ++k)
+                if (k < n) cpAsync16(sbase + static_cast<uint32_t>((u * n + k) * 32 * 16), src[k] + v);
+        }
+        cpAsyncWaitAll();
+#pragma unroll 1
+        for (int u = 0; u < per_pass; ++u) {
+            const int v = v0 + u * 32;
+            if (v >= vecs) break;
             float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int k = 0; k < N; ++k) {
-                const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&raw[u][k]);
+            for (int k = 0; k < 8; ++k) {
+                if (k >= n) continue;
+                const uint4 raw = stage[(u * n + k) * 32 + lane];
+                const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&raw);
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const float2 f = __bfloat1622float2(h[j]);
@@ -651,7 +672,7 @@ __device__ __forceinline__ void weightedRowsToPeer(const uint4 *const (&src)[8],
             __nv_bfloat162 *oh = reinterpret_cast<__nv_bfloat162 *>(&o);
 #pragma unroll
             for (int j = 0; j < 4; ++j) oh[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
-            stPeer16(dst + v0 + u * 32, o);
+            stPeer16(dst + v, o);
         }
     }
 }
@@ -659,6 +680,7 @@ __device__ __forceinline__ void weightedRowsToPeer(const uint4 *const (&src)[8],
 // Rank-reduced combine (NixlEpCombineParams::max_tokens).  Phase 1, expert rank: one warp per (token, home
 // rank) group record adds the token's rows up in fp32, weighted, and stores ONE bf16 row at the home rank.
 // Phase 2, home rank: add the rows of the ranks the token went to.
+template <int kPhases>
 __device__ __forceinline__ void epCombineRankReduce(const NixlEpCombineParams &p) {
     const int El = p.E / p.R;
     const int tid = threadIdx.x, lane = tid & 31;
@@ -666,8 +688,10 @@ __device__ __forceinline__ void epCombineRankReduce(const NixlEpCombineParams &p
     const int vecs = p.H / 8;
     const long long M = p.max_tokens;
     const int tag = static_cast<int>(p.epoch & 0x7fffffffull);
+    extern __shared__ __align__(16) unsigned char rr_stage[];
+    uint4 *stage = reinterpret_cast<uint4 *>(rr_stage + (tid >> 5) * kRrWarpBytes);
 
-    if (p.phases & 1) {
+    if constexpr ((kPhases & 1) != 0) {
         const __nv_bfloat16 *x = static_cast<const __nv_bfloat16 *>(p.x);
         const int *tokens_of = reinterpret_cast<const int *>(self + p.lay.off_grp_tokens);
         const uint4 *records = reinterpret_cast<const uint4 *>(self + p.lay.off_grp);
@@ -701,12 +725,7 @@ __device__ __forceinline__ void epCombineRankReduce(const NixlEpCombineParams &p
                 wk[k] = k < n ? w[k] : 0.f; // padding rows repeat the first one with weight zero
             }
             uint4 *dst = reinterpret_cast<uint4 *>(peer + p.lay.off_comb_x + (static_cast<long long>(p.rank) * M + t) * p.H * 2);
-            // Eight 16-byte loads in flight per lane whatever the number of rows (with top-8 over eight ranks a
-            // group has one or two rows most of the time).
-            if (n == 1) weightedRowsToPeer<1, 8>(src, wk, dst, vecs, lane);
-            else if (n == 2) weightedRowsToPeer<2, 4>(src, wk, dst, vecs, lane);
-            else if (n <= 4) weightedRowsToPeer<4, 2>(src, wk, dst, vecs, lane);
-            else weightedRowsToPeer<8, 1>(src, wk, dst, vecs, lane);
+            warpWeightedRows(n, src, wk, dst, vecs, lane, stage);
         }
         __syncthreads();
         if (tid == 0) __threadfence_system();
@@ -722,7 +741,7 @@ __device__ __forceinline__ void epCombineRankReduce(const NixlEpCombineParams &p
         }
     }
 
-    if (p.phases & 2) {
+    if constexpr ((kPhases & 2) != 0) {
         const uint64_t *flag = reinterpret_cast<const uint64_t *>(self + p.lay.off_comb_flag);
         if (tid < p.R && ldVolatile(p.scr.mask + tid) == 0 && peerBase(p.peers, tid) != nullptr) {
             if (!waitFlag(flag + tid, p.epoch, p.timeout_ns)) {
@@ -733,55 +752,63 @@ __device__ __forceinline__ void epCombineRankReduce(const NixlEpCombineParams &p
         __syncthreads();
         const __nv_bfloat16 *landing = reinterpret_cast<const __nv_bfloat16 *>(self + p.lay.off_comb_x);
         __nv_bfloat16 *out = static_cast<__nv_bfloat16 *>(p.out);
-        const int nt = threadsPerItem(p.T);
-        const int groups_per_cta = kThreads / nt;
-        const int grp = tid / nt, gtid = tid - grp * nt;
-        for (int t = blockIdx.x * groups_per_cta + grp; t < p.T; t += gridDim.x * groups_per_cta) {
+        const int warps = gridDim.x * (kThreads / 32);
+        for (int t = blockIdx.x * (kThreads / 32) + (tid >> 5); t < p.T; t += warps) { // one warp per token
             // ranks that hold copies of this token (and answered)
             unsigned ranks = 0;
             for (int k = 0; k < p.K; ++k) {
                 const long long e = p.topk_idx[static_cast<long long>(t) * p.K + k];
                 if (e >= 0 && e < p.E && ldVolatile(p.scr.mask + static_cast<int>(e) / El) == 0) ranks |= 1u << (static_cast<int>(e) / El);
             }
-            for (int v = gtid; v < vecs; v += nt) {
-                float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-                uint4 raw[8];
+            uint4 *dst = reinterpret_cast<uint4 *>(out + static_cast<long long>(t) * p.H);
+            if (ranks == 0) {
+                for (int v = lane; v < vecs; v += 32) dst[v] = make_uint4(0u, 0u, 0u, 0u);
+                continue;
+            }
+            if (__popc(ranks) <= 8) {
+                const uint4 *src[8];
+                float one[8];
                 unsigned left = ranks;
-                while (left) { // eight rows' vectors in flight at a time
-                    int ds[8];
+                const int first = __ffs(ranks) - 1;
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        ds[j] = left ? __ffs(left) - 1 : -1;
-                        left &= left - 1; // (0 stays 0)
-                    }
+                for (int j = 0; j < 8; ++j) {
+                    const int d = left ? __ffs(left) - 1 : first;
+                    one[j] = left ? 1.f : 0.f;
+                    left &= left - 1; // (0 stays 0)
+                    src[j] = reinterpret_cast<const uint4 *>(landing + (static_cast<long long>(d) * M + t) * p.H);
+                }
+                warpWeightedRows(__popc(ranks), src, one, dst, vecs, lane, stage);
+                continue;
+            }
+            for (int v = lane; v < vecs; v += 32) { // more than eight ranks hold copies: plain loads, eight rows at a time
+                float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                unsigned left = ranks;
+                while (left) {
+                    const int d = __ffs(left) - 1;
+                    left &= left - 1;
+                    const uint4 raw = *reinterpret_cast<const uint4 *>(landing + (static_cast<long long>(d) * M + t) * p.H + v * 8);
+                    const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&raw);
 #pragma unroll
-                    for (int j = 0; j < 8; ++j)
-                        if (ds[j] >= 0) raw[j] = *reinterpret_cast<const uint4 *>(landing + (static_cast<long long>(ds[j]) * M + t) * p.H + v * 8);
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        if (ds[j] < 0) continue;
-                        const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&raw[j]);
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const float2 f = __bfloat1622float2(h[i]);
-                            acc[2 * i] += f.x;
-                            acc[2 * i + 1] += f.y;
-                        }
+                    for (int i = 0; i < 4; ++i) {
+                        const float2 f = __bfloat1622float2(h[i]);
+                        acc[2 * i] += f.x;
+                        acc[2 * i + 1] += f.y;
                     }
                 }
                 uint4 o;
                 __nv_bfloat162 *oh = reinterpret_cast<__nv_bfloat162 *>(&o);
 #pragma unroll
                 for (int i = 0; i < 4; ++i) oh[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
-                *reinterpret_cast<uint4 *>(out + static_cast<long long>(t) * p.H + v * 8) = o;
+                dst[v] = o;
             }
         }
     }
 }
 
-// The rank-reduced mode as a kernel of its own: it needs far fewer registers than the pull mode's double-buffered
-// reduction, so two CTAs fit on an SM and twice as many loads are in flight.
-__global__ void __launch_bounds__(kThreads, 2) epCombineRankReduceKernel(const __grid_constant__ NixlEpCombineParams p) { epCombineRankReduce(p); }
+// The rank-reduced mode as two kernels of its own: each phase alone needs few enough registers for two CTAs per SM,
+// which is what keeps enough loads in flight; the second launch starts when every CTA of the first has left.
+__global__ void __launch_bounds__(kThreads, 2) epCombineRankReduceSend(const __grid_constant__ NixlEpCombineParams p) { epCombineRankReduce<1>(p); }
+__global__ void __launch_bounds__(kThreads, 2) epCombineRankReduceRecv(const __grid_constant__ NixlEpCombineParams p) { epCombineRankReduce<2>(p); }
 
 __global__ void __launch_bounds__(kThreads) epCombineKernel(const __grid_constant__ NixlEpCombineParams p) {
     __shared__ int offs[kMaxRanks * 8 + 1]; // expert_offsets copy (El + 1 <= 513)
@@ -1070,9 +1097,25 @@ extern "C" int nixl_ep_combine_launch(const NixlEpCombineParams *params, void *s
         int dev = 0, sms = 0;
         cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        const int grid = coopGrid(reinterpret_cast<const void *>(epCombineRankReduceKernel), p.grid > 0 ? p.grid : 2 * sms, 0);
-        return cudaLaunchCooperativeKernel(reinterpret_cast<const void *>(epCombineRankReduceKernel), dim3(grid), dim3(kThreads), args, 0,
-                                           static_cast<cudaStream_t>(stream));
+        static bool attr_done[64] = {};
+        if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+            cudaError_t e = cudaFuncSetAttribute(epCombineRankReduceSend, cudaFuncAttributeMaxDynamicSharedMemorySize, kRrCtaBytes);
+            if (e == cudaSuccess) e = cudaFuncSetAttribute(epCombineRankReduceRecv, cudaFuncAttributeMaxDynamicSharedMemorySize, kRrCtaBytes);
+            if (e != cudaSuccess) return e;
+            attr_done[dev] = true;
+        }
+        const int want = 2 * (p.grid > 0 ? p.grid : sms); // p.grid counts SMs
+        if (p.phases & 1) { // cooperative: its CTAs meet at a grid barrier before the flags go out
+            const int grid = coopGrid(reinterpret_cast<const void *>(epCombineRankReduceSend), want, kRrCtaBytes);
+            const cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<const void *>(epCombineRankReduceSend), dim3(grid), dim3(kThreads), args,
+                                                              kRrCtaBytes, static_cast<cudaStream_t>(stream));
+            if (e != cudaSuccess) return e;
+        }
+        if (p.phases & 2) {
+            epCombineRankReduceRecv<<<want, kThreads, kRrCtaBytes, static_cast<cudaStream_t>(stream)>>>(p);
+            return cudaGetLastError();
+        }
+        return cudaSuccess;
     }
     const int grid = coopGrid(reinterpret_cast<const void *>(epCombineKernel), p.grid, 0);
     return cudaLaunchCooperativeKernel(reinterpret_cast<const void *>(epCombineKernel), dim3(grid), dim3(kThreads), args, 0,
