@@ -171,7 +171,7 @@ __device__ __forceinline__ void countSent(const NixlEpDispatchParams &p, int El,
     }
 }
 
-__global__ void __launch_bounds__(kThreads, 1) epDispatchKernel(const __grid_constant__ NixlEpDispatchParams p) {
+__global__ void __launch_bounds__(kThreads, 2) epDispatchKernel(const __grid_constant__ NixlEpDispatchParams p) {
     extern __shared__ __align__(16) unsigned char smem[];
     const int El = p.E / p.R;
     const int groups = p.H / kGroup;
