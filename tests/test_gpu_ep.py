@@ -133,7 +133,16 @@ def _run(bufs, tokens, hidden, experts, topk, use_fp8, compact, zero_copy=False,
             valid = (e >= 0).float().unsqueeze(1)
             yk = (base * ((1 + e.clamp(min=0)).float() * 0.01).unsqueeze(1)).to(torch.bfloat16).float()
             want += valid * ws[r][:, k].unsqueeze(1) * yk
-        torch.testing.assert_close(outs[r].float(), want.to(torch.bfloat16).float(), rtol=2e-2, atol=2e-2)
+        got, ref = outs[r].float(), want.to(torch.bfloat16).float()
+        if not use_fp8:
+            torch.testing.assert_close(got, ref, rtol=2e-2, atol=2e-2)
+            continue
+        # fp8: the kernel and PyTorch round x * (448 / amax) differently on exact ties, so a rare e4m3 code sits one
+        # step apart (up to 1/8 of the value, and the same x feeds every term of a token): nearly all elements to
+        # bf16 accuracy, every element to one fp8 step.
+        err = (got - ref).abs()
+        assert float((err <= 2e-2 + 2e-2 * ref.abs()).float().mean()) >= 0.999
+        assert bool((err <= 2e-2 + 0.13 * ref.abs()).all())
 
 
 @pytest.mark.parametrize("use_fp8", [True, False])
