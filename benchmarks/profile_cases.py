@@ -4,7 +4,7 @@
 Inputs are larger than L2 (126 MB) where DRAM figures matter, hold at most a few GB and launch
 the kernel of interest a handful of times.  One GPU only.
 
-    python benchmarks/profile_cases.py copy|kv|ep|gemm|gemm_pair|gemm_mx
+    python benchmarks/profile_cases.py copy|kv|ep|ep_push|ep_rr|gemm|gemm_pair|gemm_mx
 """
 import os
 import sys
@@ -58,9 +58,10 @@ def case_kv():
     torch.cuda.synchronize()
 
 
-def case_ep(pull=True):
+def case_ep(pull=True, rank_reduce=False):
     """Throughput dispatch and combine on one rank; the combine reads the exposed buffer (pull, what a
-    pipeline with the expert GEMM in between does) or, as `ep_push`, stores rows to the home rank first."""
+    pipeline with the expert GEMM in between does) or, as `ep_push`, stores rows to the home rank first; as `ep_rr`
+    dispatch is given the weights and the combine is the rank-reduced pair of kernels."""
     from nixl_b200.parallel import Buffer
 
     T, H, E, K = 1024, 7168, 32, 8
@@ -69,7 +70,7 @@ def case_ep(pull=True):
     w, idx = torch.topk(torch.softmax(torch.randn(T, E, device="cuda:0"), -1), K, -1)
     idx, w = idx.long().contiguous(), w.float().contiguous()
     for _ in range(3):
-        rx, sc, h = buf.dispatch(x, idx)
+        rx, sc, h = buf.dispatch(x, idx, topk_weights=w if rank_reduce else None)
         y = buf.get_next_combine_buffer(h) if pull else torch.empty(rx.shape[0], H, device="cuda:0", dtype=torch.bfloat16)
         buf.combine(y, idx, w, h)
     torch.cuda.synchronize()
@@ -78,6 +79,10 @@ def case_ep(pull=True):
 
 def case_ep_push():
     case_ep(pull=False)
+
+
+def case_ep_rr():
+    case_ep(rank_reduce=True)
 
 
 def _gemm_inputs(G=8, N=2048, K=7168, rows_per=1024, pow2=False):
@@ -127,5 +132,5 @@ def case_gemm_mx():
 
 
 if __name__ == "__main__":
-    {"copy": case_copy, "kv": case_kv, "ep": case_ep, "ep_push": case_ep_push, "gemm": case_gemm, "gemm_pair": case_gemm_pair, "gemm_mx": case_gemm_mx}[sys.argv[1]]()
+    {"copy": case_copy, "kv": case_kv, "ep": case_ep, "ep_push": case_ep_push, "ep_rr": case_ep_rr, "gemm": case_gemm, "gemm_pair": case_gemm_pair, "gemm_mx": case_gemm_mx}[sys.argv[1]]()
     print("ok", sys.argv[1])
