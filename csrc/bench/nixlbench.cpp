@@ -9,7 +9,7 @@
 //
 //   nixlbench [--backend NVLINK] [--op WRITE|READ] [--mem VRAM|DRAM] [--src-dev 0] [--dst-dev 1]
 //             [--min 4096] [--max 1073741824] [--batch 1] [--batch-max N] [--iters 1000] [--warmup 100]
-//             [--depth 1] [--copy-path vector|bulk] [--param key=value]... [--check]
+//             [--depth 1] [--num-threads 1] [--enable-pt] [--copy-path vector|bulk] [--param key=value]... [--check]
 //             [--prepared] [--recreate] [--reregister] [--scatter] [--config file]
 //             [--file path [--num-files N] [--direct]]      storage mode (POSIX, GDS, GDS_MT backends)
 //             [--scheme pairwise|onetomany|manytoone --num-initiator-dev N --num-target-dev M]
@@ -18,6 +18,10 @@
 // initiator GPUs post to one target GPU (--dst-dev) at once, which is the pattern that shows what a receiver's
 // ingress sustains.  One agent per GPU, all in this process; the figure is the sum over all flows.
 //
+// --num-threads T: T worker threads share the batch (thread t owns descriptors t, t + T, ...), each with its own
+// requests and pipeline (the reference's worker threads, worker/nixl/nixl_worker.cpp:125,:1834); --enable-pt gives
+// the agents a progress thread.
+//
 // --prepared builds requests with prepXferDlist + makeXferReq (the reference's prepared_xfer),
 // --recreate creates and releases the request on every iteration (recreate_xfer), --reregister
 // registers and deregisters the source buffer on every iteration (reregister_mem), --config reads
@@ -25,6 +29,7 @@
 // the same agent: WRITE stores memory into the files, READ loads it back (filepath / num_files /
 // storage_enable_direct of the reference).
 #include <algorithm>
+#include <barrier>
 #include <chrono>
 #include <cstdio>
 #include <cstdlib>
@@ -32,6 +37,7 @@
 #include <map>
 #include <memory>
 #include <string>
+#include <thread>
 #include <vector>
 
 #include <fcntl.h>
@@ -55,6 +61,8 @@ struct Args {
     std::string scheme = "pairwise"; // pairwise | onetomany | manytoone (benchmark/nixlbench/src/utils/utils.h:122-125 of the reference)
     int num_initiator_dev = 1, num_target_dev = 1;
     int batch_max = 0, num_files = 1;
+    int num_threads = 1;    // worker threads of the pairwise scheme, each with its share of the batch
+    bool enable_pt = false; // agents with a progress thread
     std::string file; // storage mode when set
     nixl_b_params_t extra; // --param key=value, passed to the backend
 };
@@ -75,6 +83,7 @@ bool setOption(Args &a, const std::string &k, const std::string &v) {
     else if (k == "--iters") a.iters = std::atoi(v.c_str());
     else if (k == "--warmup") a.warmup = std::atoi(v.c_str());
     else if (k == "--depth") a.depth = std::max(1, std::atoi(v.c_str()));
+    else if (k == "--num-threads") a.num_threads = std::max(1, std::atoi(v.c_str()));
     else if (k == "--min") a.min = std::strtoull(v.c_str(), nullptr, 0);
     else if (k == "--max") a.max = std::strtoull(v.c_str(), nullptr, 0);
     else if (k == "--total") a.total = std::strtoull(v.c_str(), nullptr, 0);
@@ -88,6 +97,7 @@ bool setOption(Args &a, const std::string &k, const std::string &v) {
 }
 bool setFlag(Args &a, const std::string &k) {
     if (k == "--check") a.check = true;
+    else if (k == "--enable-pt") a.enable_pt = true;
     else if (k == "--prepared") a.prepared = true;
     else if (k == "--recreate") a.recreate = true;
     else if (k == "--reregister") a.reregister = true;
@@ -155,7 +165,7 @@ Spelling canonical(std::string k) {
     // One process drives both agents here: there is no runtime to rendezvous through, no second
     // worker type and one initiator / target device each.
     static const char *ignored[] = {"--runtime-type", "--worker-type", "--etcd-endpoints", "--mode",
-                                    "--num-threads",  "--enable-pt",   "--progress-threads", "--device-list", "--target-seg-type",
+                                    "--progress-threads", "--device-list", "--target-seg-type",
                                     "--large-blk-iter-ftr", "--benchmark-group"};
     Spelling sp;
     sp.name = k;
@@ -391,7 +401,8 @@ int main(int argc, char **argv) {
     if (!storage && !allocate(dst, a.dst_dev, 0)) return 3;
     if (vram) cudaSetDevice(a.src_dev);
 
-    nixlAgentConfig cfg(false);
+    // "--enable-pt": the backend's progress thread completes requests; several worker threads need the agent's lock.
+    nixlAgentConfig cfg(a.enable_pt, false, 0, a.num_threads > 1 ? nixl_thread_sync_t::NIXL_THREAD_SYNC_RW : nixl_thread_sync_t::NIXL_THREAD_SYNC_NONE);
     nixlAgent ini("initiator", cfg), tgt("target", cfg);
     nixlBackendH *bi = nullptr, *bt = nullptr;
     nixl_b_params_t params;
@@ -444,10 +455,26 @@ int main(int argc, char **argv) {
             iters = std::min(iters, 200);
             warm = std::min(warm, 5);
         }
-        std::vector<double> prep, post, xfer;
+        // Worker threads ("--num-threads"): thread t owns the descriptors t, t + T, ... of the batch and runs the whole
+        // pipelined loop on them with requests of its own; the rate counts all threads' bytes over the slowest thread's time.
+        const int nthreads = std::max(1, std::min(a.num_threads, batch));
+        if (a.reregister && nthreads > 1) {
+            std::fprintf(stderr, "--reregister works with one thread\n");
+            return 2;
+        }
+        struct WorkerStats {
+            std::vector<double> prep, post, xfer;
+            double wall = 0;
+            int rc = 0;
+        };
+        std::vector<WorkerStats> stats(nthreads);
+        std::barrier start_line(nthreads);
+        auto worker = [&](int tid) -> int {
+        std::vector<double> &prep = stats[tid].prep, &post = stats[tid].post, &xfer = stats[tid].xfer;
         std::vector<nixlXferReqH *> slots(a.depth, nullptr);
         nixl_xfer_dlist_t l(mt), r(rmt);
-        for (int i = 0; i < batch; ++i) {
+        int mine = 0;
+        for (int i = tid; i < batch; i += nthreads, ++mine) {
             const size_t off = static_cast<size_t>(i) * block;
             l.addDesc(nixlBasicDesc(reinterpret_cast<uintptr_t>(src) + off, block, vram ? a.src_dev : 0));
             if (storage) {
@@ -460,9 +487,10 @@ int main(int argc, char **argv) {
                 r.addDesc(nixlBasicDesc(reinterpret_cast<uintptr_t>(dst) + roff, block, vram ? a.dst_dev : 0));
             }
         }
+        if (vram) cudaSetDevice(a.src_dev);
         nixlDlistH *side_l = nullptr, *side_r = nullptr;
-        std::vector<int> all_idx(batch);
-        for (int i = 0; i < batch; ++i) all_idx[i] = i;
+        std::vector<int> all_idx(mine);
+        for (int i = 0; i < mine; ++i) all_idx[i] = i;
         if (a.prepared) {
             const auto t0 = clk::now();
             if (ini.prepXferDlist(NIXL_INIT_AGENT, l, side_l) != NIXL_SUCCESS || ini.prepXferDlist(remote_name, r, side_r) != NIXL_SUCCESS) return 7;
@@ -478,9 +506,11 @@ int main(int argc, char **argv) {
             if (!create(s)) return 7;
         std::vector<clk::time_point> started(a.depth);
         std::vector<bool> busy(a.depth, false);
+        start_line.arrive_and_wait();
         clk::time_point t_begin = clk::now();
         int posted = 0, done = 0;
         const int total = warm + iters;
+        int failed = 0;
         auto finished = [&](int s, clk::time_point now) {
             busy[s] = false;
             if (done >= warm) xfer.push_back(us(started[s], now));
@@ -489,20 +519,20 @@ int main(int argc, char **argv) {
             if (a.recreate && posted < total) {
                 ini.releaseXferReq(slots[s]);
                 slots[s] = nullptr;
-                if (!create(slots[s])) std::exit(7);
+                if (!create(slots[s])) failed = 7;
             }
         };
-        while (done < total) {
-            for (int s = 0; s < a.depth; ++s) {
+        while (done < total && !failed) {
+            for (int s = 0; s < a.depth && !failed; ++s) {
                 if (busy[s]) {
                     const nixl_status_t st = ini.getXferStatus(slots[s]);
                     if (st == NIXL_SUCCESS) finished(s, clk::now());
                     else if (st < 0) {
                         std::fprintf(stderr, "transfer failed: %d\n", st);
-                        return 8;
+                        failed = 8;
                     }
                 }
-                if (!busy[s] && posted < total) {
+                if (!busy[s] && posted < total && !failed) {
                     if (a.reregister && a.depth == 1) {
                         // Every iteration pays for taking the buffer out of the backend and putting it back.
                         ini.releaseXferReq(slots[s]);
@@ -517,7 +547,10 @@ int main(int argc, char **argv) {
                     started[s] = clk::now();
                     const nixl_status_t st = ini.postXferReq(slots[s]);
                     const auto t1 = clk::now();
-                    if (st < 0) return 9;
+                    if (st < 0) {
+                        failed = 9;
+                        break;
+                    }
                     if (posted >= warm) post.push_back(us(started[s], t1));
                     ++posted;
                     if (st == NIXL_SUCCESS) finished(s, t1);
@@ -525,7 +558,28 @@ int main(int argc, char **argv) {
                 }
             }
         }
-        const double wall = us(t_begin, clk::now());
+        stats[tid].wall = us(t_begin, clk::now());
+        for (auto s : slots)
+            if (s) ini.releaseXferReq(s);
+        if (side_l) ini.releasedDlistH(side_l);
+        if (side_r) ini.releasedDlistH(side_r);
+        return failed;
+        };
+        {
+            std::vector<std::thread> pool;
+            for (int t = 1; t < nthreads; ++t) pool.emplace_back([&, t] { stats[t].rc = worker(t); });
+            stats[0].rc = worker(0);
+            for (auto &t : pool) t.join();
+        }
+        std::vector<double> prep, post, xfer;
+        double wall = 0;
+        for (auto &w : stats) {
+            if (w.rc) return w.rc;
+            prep.insert(prep.end(), w.prep.begin(), w.prep.end());
+            post.insert(post.end(), w.post.begin(), w.post.end());
+            xfer.insert(xfer.end(), w.xfer.begin(), w.xfer.end());
+            wall = std::max(wall, w.wall);
+        }
         double sum = 0;
         for (double v : xfer) sum += v;
         double psum = 0;
@@ -536,10 +590,6 @@ int main(int argc, char **argv) {
                     sum / std::max<size_t>(1, xfer.size()), pct(xfer, 0.5), pct(xfer, 0.99), prsum / std::max<size_t>(1, prep.size()),
                     psum / std::max<size_t>(1, post.size()));
         std::fflush(stdout);
-        for (auto s : slots)
-            if (s) ini.releaseXferReq(s);
-        if (side_l) ini.releasedDlistH(side_l);
-        if (side_r) ini.releasedDlistH(side_r);
         if (a.check) {
             // WRITE: the destination (memory or file) must hold the source pattern; READ from memory: the source side
             // was overwritten with the target's zeros.

@@ -18,7 +18,7 @@ def _run(binary, *args, timeout=300):
     return subprocess.run([path, *args], env=ENV, capture_output=True, text=True, timeout=timeout, cwd=os.path.join(ROOT, "csrc"))
 
 
-@pytest.mark.parametrize("binary", ["test_plumbing", "test_core", "test_vmm_share", "test_agent_units", "test_notif_ring"])
+@pytest.mark.parametrize("binary", ["test_plumbing", "test_core", "test_vmm_share", "test_agent_units", "test_notif_ring", "test_transfer"])
 def test_native_suite(binary):
     res = _run(binary)
     assert res.returncode == 0, res.stdout[-4000:] + res.stderr[-2000:]
@@ -69,11 +69,11 @@ def test_native_nixlbench_accepts_the_reference_spellings(tmp_path):
     """gflags-style names of the reference's nixlbench (underscores, --name=value) map onto the same options."""
     res = _nixlbench("--backend", "NVLINK", "--initiator_seg_type=DRAM", "--op_type", "WRITE", "--start_block_size=8192",
                      "--max_block_size=16384", "--start_batch_size", "2", "--num_iter=20", "--warmup_iter", "2", "--check_consistency",
-                     "--pipeline_depth=2", "--etcd_endpoints", "http://127.0.0.1:2379", "--scheme=pairwise", "--enable_pt")
+                     "--pipeline_depth=2", "--etcd_endpoints", "http://127.0.0.1:2379", "--scheme=pairwise", "--enable_pt", "--num_threads=2")
     assert res.returncode == 0, res.stdout + res.stderr
     rows = [l.split() for l in res.stdout.splitlines() if l and l[0].isdigit()]
     assert [r[0] for r in rows] == ["8192", "16384"] and all(r[1] == "2" for r in rows)
-    assert "no effect" in res.stderr and "--enable_pt" in res.stderr
+    assert "no effect" in res.stderr and "--etcd_endpoints" in res.stderr and "--enable_pt" not in res.stderr  # worker threads and the progress thread are real options
     assert _nixlbench("--scheme", "ring").returncode == 2
     store = str(tmp_path / "store.bin")
     res = _nixlbench("--backend=POSIX", "--initiator_seg_type=DRAM", "--filepath", store, "--posix_api_type=URING", "--posix_kernel_queue_size=32",
