@@ -136,6 +136,8 @@ extern "C" int nixl_devapi_put_signal_launch(const NixlDevPutParams *params, voi
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const int grid = params->peers * params->ctas_per_peer + 1;
     if (grid > sms || params->peers * params->window > 512) return cudaErrorInvalidValue;
-    putSignalKernel<<<grid, 512, 0, static_cast<cudaStream_t>(stream)>>>(*params);
-    return cudaGetLastError();
+    // Cooperative launch: the runtime refuses the launch unless every CTA can be resident at once.
+    NixlDevPutParams copy = *params;
+    void *args[] = {&copy};
+    return cudaLaunchCooperativeKernel(reinterpret_cast<const void *>(putSignalKernel), dim3(grid), dim3(512), args, 0, static_cast<cudaStream_t>(stream));
 }

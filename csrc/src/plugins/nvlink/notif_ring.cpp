@@ -2,11 +2,13 @@
 #include "plugins/nvlink/notif_ring.h"
 
 #include <cerrno>
+#include <cstdlib>
 #include <cstring>
 #include <ctime>
 #include <map>
 #include <mutex>
 
+#include <dirent.h>
 #include <fcntl.h>
 #include <signal.h>
 #include <sys/mman.h>
@@ -37,12 +39,32 @@ NotifRingOwner::~NotifRingOwner() {
     if (!name_.empty()) ::shm_unlink(name_.c_str());
 }
 
+// Rings whose owner died without unlinking them ("/<prefix>.<pid>.<tag>"): removed by whoever creates the next one.
+static void reapStaleRings(const std::string &name) {
+    const size_t dot = name.find('.');
+    if (name.size() < 2 || name[0] != '/' || dot == std::string::npos) return;
+    const std::string prefix = name.substr(1, dot); // "nixl_b200."
+    DIR *d = ::opendir("/dev/shm");
+    if (!d) return;
+    while (dirent *e = ::readdir(d)) {
+        const std::string f = e->d_name;
+        if (f.compare(0, prefix.size(), prefix) != 0) continue;
+        char *end = nullptr;
+        const long pid = std::strtol(f.c_str() + prefix.size(), &end, 10);
+        if (pid <= 0 || !end || *end != '.') continue;
+        if (::kill(static_cast<pid_t>(pid), 0) != 0 && errno == ESRCH) ::shm_unlink(("/" + f).c_str());
+    }
+    ::closedir(d);
+}
+
 bool NotifRingOwner::create(const std::string &name) {
     if (hdr_) return true;
+    reapStaleRings(name);
     const int fd = ::shm_open(name.c_str(), O_CREAT | O_EXCL | O_RDWR | O_CLOEXEC, 0600);
     if (fd < 0) return false;
     bytes_ = ringBytes();
-    if (::ftruncate(fd, static_cast<off_t>(bytes_)) != 0) {
+    // posix_fallocate: a shared-memory file system without room answers here, not with SIGBUS at the first store
+    if (::ftruncate(fd, static_cast<off_t>(bytes_)) != 0 || ::posix_fallocate(fd, 0, static_cast<off_t>(bytes_)) != 0) {
         ::close(fd);
         ::shm_unlink(name.c_str());
         return false;

@@ -129,6 +129,22 @@ TEST_CASE(another_process_writes_and_a_claimant_that_died_does_not_hold_the_ring
     CHECK(got.size() == 1);
 }
 
+TEST_CASE(rings_left_by_dead_processes_are_removed_by_the_next_owner) {
+    const pid_t child = ::fork();
+    if (child == 0) { // dies without running the owner's destructor
+        auto *leaked = new NotifRingOwner();
+        ::_exit(leaked->create("/nixl_b200_reap." + std::to_string(::getpid()) + ".leak") ? 0 : 2);
+    }
+    int status = 0;
+    CHECK(::waitpid(child, &status, 0) == child);
+    CHECK(WIFEXITED(status) && WEXITSTATUS(status) == 0);
+    const std::string stale = "/nixl_b200_reap." + std::to_string(child) + ".leak";
+    CHECK(NotifRingWriter::open(stale) != nullptr); // still there ...
+    NotifRingOwner next;
+    CHECK(next.create("/nixl_b200_reap." + std::to_string(::getpid()) + ".next"));
+    CHECK(::access(("/dev/shm" + stale).c_str(), F_OK) != 0); // ... until the next owner of the family comes
+}
+
 TEST_CASE(a_ring_that_is_gone_cannot_be_opened) {
     std::string name;
     {
