@@ -325,23 +325,42 @@ def ring_handle(env, agent, tag, block, batch, scattered=False):
     return agent.initialize_xfer("WRITE", agent.get_xfer_descs(local, "VRAM"), agent.get_xfer_descs(remote, "VRAM"), f"{tag}{peer}")
 
 
-def time_ring(env, agent, handle, steps, warm):
-    """Device time of `steps` back-to-back posts on env.stream; returns (ms, wall_s)."""
+def time_ring(env, agent, handles, steps, warm, warm_seconds=0.0):
+    """Device time of `steps` posts on env.stream; returns (ms, wall_s).  `handles`: one request, or two identical
+    ones posted alternately (a pipeline of depth two: the next launch is queued while the current one runs, so the
+    stream never waits for the host; a request is posted again only once it has completed).  Warm-up: `warm` steps,
+    and further steps until `warm_seconds` have passed."""
     torch = env.torch
+    if not isinstance(handles, (list, tuple)):
+        handles = [handles]
+    pending = [False] * len(handles)
 
-    def step():
-        if not post(env, agent, handle, env.stream_param):
-            wait_done(env, agent, handle)
+    def step(i):
+        k = i % len(handles)
+        if pending[k]:
+            wait_done(env, agent, handles[k])
+        pending[k] = not post(env, agent, handles[k], env.stream_param)
 
-    for _ in range(warm):
-        step()
+    def drain():
+        for k, h in enumerate(handles):
+            if pending[k]:
+                wait_done(env, agent, h)
+                pending[k] = False
+
+    t_warm = time.perf_counter() + warm_seconds
+    i = 0
+    while i < warm or time.perf_counter() < t_warm:
+        step(i)
+        i += 1
+    drain()
     barrier(env)
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     wall0 = time.perf_counter()
     ev0.record(env.stream)
-    for _ in range(steps):
-        step()
+    for i in range(steps):
+        step(i)
     ev1.record(env.stream)
+    drain()
     barrier(env)
     wall = time.perf_counter() - wall0
     return ev0.elapsed_time(ev1), wall
@@ -419,18 +438,17 @@ def main():
     plugin = ctypes.CDLL(os.path.join(ROOT, "nixl_b200", "lib", "plugins", "libplugin_NVLINK.so"))
     plugin.nixl_nvlink_kernel_launches.restype = ctypes.c_uint64
     handle = ring_handle(env, env.agent, "bench", block, batch)
+    handle_b = ring_handle(env, env.agent, "bench", block, batch)  # the same request once more: posted alternately (depth two)
 
     # ---------------------------------------------------------------- device-timed region
+    # Warm-up: W steps, then more of the same while the clock sampler starts up (a GPU left idle for that quarter of
+    # a second drops its clocks and the timed steps would begin on the ramp).
     warm = max(args.warmup, 3)
-    for _ in range(warm):
-        if not post(env, env.agent, handle, env.stream_param):
-            wait_done(env, env.agent, handle)
-    barrier(env)
     sampler = ClockSampler(env.local_rank)
     sampler.start()
-    time.sleep(0.25)
+    time_ring(env, env.agent, [handle, handle_b], 0, warm, warm_seconds=0.25)
     launches0 = plugin.nixl_nvlink_kernel_launches()
-    dev_ms, wall = time_ring(env, env.agent, handle, args.steps, 0)
+    dev_ms, wall = time_ring(env, env.agent, [handle, handle_b], args.steps, 0)
     launches = plugin.nixl_nvlink_kernel_launches() - launches0
     clocks = sampler.stop()
 
@@ -477,6 +495,7 @@ def main():
     gbs = env.world * step_bytes * args.steps / (dev_ms * 1e-3) / 1e9
     e2e_gbs = env.world * step_bytes * e2e_steps / e2e_s / 1e9
     env.agent.release_xfer_handle(handle)
+    env.agent.release_xfer_handle(handle_b)
 
     # ---------------------------------------------------------------- extras (outside timed regions)
     extras = {}
@@ -537,7 +556,9 @@ def main():
                           "1 GiB run), copy kernel below 96 MiB per merged descriptor, copy engines from 96 MiB between GPUs; "
                           "extras.baselines.headline_scattered_GBps is the same request with the destination blocks in reverse order (nothing to merge)",
                 "l2": "inputs larger than L2 (1 GiB source and destination per GPU); no flush needed",
-                "timing": "CUDA events on the launching stream, max over ranks",
+                "timing": "CUDA events on the launching stream, max over ranks; two identical requests are posted alternately (depth two: "
+                          "a request is posted again only after it completed) so the stream does not wait for the host between steps; "
+                          "warm-up = W steps plus further steps for 0.25 s while the clock sampler starts",
                 "roofline": roofline(env, gbs),
             },
             "clocks": clocks,
@@ -574,13 +595,15 @@ def extras_baselines(env, args, headline_gbs, budget_s):
 
     for key, tag, params, scattered in (("copy_engine_per_descriptor_GBps", "bce", {"copy_path": "ce", "coalesce": "false"}, False),
                                         ("copy_kernel_only_GBps", "bk", {"ce_threshold": "0"}, False),
-                                        ("headline_scattered_GBps", "bench", None, True)):
+                                        ("headline_scattered_GBps", "bench", None, True),
+                                        ("headline_repeat_GBps", "bench", None, False)):  # the headline once more, timed like the other arms
         agent = make_agent(env, tag, params) if params is not None else env.agent
-        h = ring_handle(env, agent, tag, block, batch, scattered)
+        h = [ring_handle(env, agent, tag, block, batch, scattered) for _ in range(2)]  # depth two, as the headline
         ms, _ = time_ring(env, agent, h, steps, 3)
         ms = max_over_ranks(env, [ms])[0]
         out[key] = round(env.world * step_bytes * steps / (ms * 1e-3) / 1e9, 2)
-        agent.release_xfer_handle(h)
+        for x in h:
+            agent.release_xfer_handle(x)
 
     if env.world > 1:
         # NCCL send/recv ring: the whole step as one message each way.

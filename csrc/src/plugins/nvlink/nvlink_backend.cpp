@@ -762,6 +762,7 @@ nixl_status_t Engine::loadLocalMD(nixlBackendMD *input, nixlBackendMD *&output) 
     md->addr = l->addr;
     md->len = l->len;
     md->ownerDevice = l->device;
+    md->ownerLocalDevice = l->device; // the agent's own memory: copies between two of its buffers on one GPU stay on the copy kernel
     md->ownerPid = self_.pid;
     md->sameProcess = true;
     md->devVisible = l->devVisible;
