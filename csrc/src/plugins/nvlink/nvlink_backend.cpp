@@ -186,7 +186,7 @@ bool decodePeer(const std::string &blob, PeerId &p) {
     if (sd.getBuf("ptag", &p.procTag, sizeof(p.procTag)) != NIXL_SUCCESS) return false;
     if (sd.getBuf("etag", &p.engineTag, sizeof(p.engineTag)) != NIXL_SUCCESS) return false;
     p.sockName = sd.getStr("sock");
-    p.ringName = sd.getBufLen("ring") > 0 ? sd.getStr("ring") : std::string();
+    p.ringName = sd.remaining() > 0 && sd.getBufLen("ring") > 0 ? sd.getStr("ring") : std::string(); // optional last field
     return !p.agent.empty() && !p.sockName.empty();
 }
 
