@@ -15,6 +15,7 @@
 #include <chrono>
 
 #include "utils/log.h"
+#include "utils/misc.h"
 
 namespace nixl_p2p {
 namespace {
@@ -22,9 +23,7 @@ constexpr char kLoad[] = "NIXLCOMM:LOAD";
 constexpr char kSend[] = "NIXLCOMM:SEND";
 constexpr char kInvl[] = "NIXLCOMM:INVL";
 
-int64_t nowMs() {
-    return std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now().time_since_epoch()).count();
-}
+using nixl_util::nowMs;
 
 bool writeAll(int fd, const char *p, size_t n) {
     while (n) {

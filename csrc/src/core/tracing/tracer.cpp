@@ -8,6 +8,7 @@
 #include "core/plugin_manager.h"
 #include "utils/config.h"
 #include "utils/log.h"
+#include "utils/misc.h"
 
 namespace nixl::trace {
 
@@ -21,10 +22,7 @@ namespace {
 thread_local std::vector<uint64_t> t_corr;
 std::atomic<uint64_t> g_nextCorr{1};
 
-uint64_t nowNs() {
-    return static_cast<uint64_t>(
-        std::chrono::duration_cast<std::chrono::nanoseconds>(std::chrono::steady_clock::now().time_since_epoch()).count());
-}
+using nixl_util::nowNs;
 
 // Writes one log line per finished span (INFO level).
 class LogBackend final : public Backend {

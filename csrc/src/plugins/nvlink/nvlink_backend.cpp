@@ -16,28 +16,19 @@
 #include "serdes/serdes.h"
 #include "utils/hw_info.h"
 #include "utils/log.h"
+#include "utils/misc.h"
 
 namespace nixl_nvlink {
 namespace {
 
 // ---------------------------------------------------------------- process-wide state
 
-uint64_t random64() {
-    static std::mutex mu;
-    static std::mt19937_64 gen{std::random_device{}() ^ (static_cast<uint64_t>(::getpid()) << 32)};
-    std::lock_guard<std::mutex> g(mu);
-    return gen();
-}
+using nixl_util::hostName;
+using nixl_util::random64;
 
 uint64_t processTag() {
     static const uint64_t tag = random64() | 1;
     return tag;
-}
-
-std::string hostName() {
-    char buf[256] = {0};
-    if (::gethostname(buf, sizeof(buf) - 1) != 0) return "localhost";
-    return buf;
 }
 
 // Engines alive in this process, by agent name: same-process peers talk directly.
@@ -1188,7 +1179,7 @@ nixl_status_t Engine::postXfer(const nixl_xfer_op_t &operation, const nixl_meta_
         req->peer = findPeer(remote_agent, &req->peerGen);
         if (!req->peer) return fail(NIXL_ERR_NOT_FOUND);
     }
-    const int64_t now_ns = std::chrono::duration_cast<std::chrono::nanoseconds>(std::chrono::steady_clock::now().time_since_epoch()).count();
+    const int64_t now_ns = static_cast<int64_t>(nixl_util::FastClock::ns()); // one stamp per post: the cycle counter
     const bool look = livenessPing_ || now_ns - req->lastAliveNs > 1000000;
     if (look) req->lastAliveNs = now_ns;
     if (!peerAlive(*req->peer, look)) return fail(NIXL_ERR_REMOTE_DISCONNECT);

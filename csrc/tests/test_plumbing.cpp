@@ -15,6 +15,7 @@
 
 #include "harness.h"
 #include "utils/hw_info.h"
+#include "utils/misc.h"
 #include "nixl.h"
 
 namespace {
@@ -312,6 +313,42 @@ TEST_CASE(hw_info_counts_devices_from_a_sysfs_tree) {
     CHECK(hw.toString().find("nvidia_gpus=2") != std::string::npos);
     const nixl::hwInfo none = nixl::hwInfo::scan(root + "/does_not_exist");
     CHECK_EQ(none.numNvidiaGpus, 0u);
+}
+
+TEST_CASE(clocks_durations_identifiers_and_strings) {
+    using namespace nixl_util;
+    // the cycle-counter clock follows the steady clock
+    const uint64_t f0 = FastClock::ns(), s0 = nowNs();
+    std::this_thread::sleep_for(std::chrono::milliseconds(20));
+    const uint64_t f1 = FastClock::ns(), s1 = nowNs();
+    CHECK(f1 > f0);
+    const double ratio = static_cast<double>(f1 - f0) / static_cast<double>(s1 - s0);
+    CHECK(ratio > 0.95 && ratio < 1.05);
+    CHECK(nowUs() >= s1 / 1000 && nowMs() >= static_cast<int64_t>(s1 / 1000000));
+
+    std::chrono::nanoseconds d{};
+    CHECK(parseDuration("1.5s", d) && d == std::chrono::milliseconds(1500));
+    CHECK(parseDuration("250ms", d) && d == std::chrono::milliseconds(250));
+    CHECK(parseDuration("40us", d) && d == std::chrono::microseconds(40));
+    CHECK(parseDuration("40", d) && d == std::chrono::microseconds(40)); // bare numbers are microseconds
+    CHECK(parseDuration("7ns", d) && d == std::chrono::nanoseconds(7));
+    CHECK(parseDuration("2min", d) && d == std::chrono::seconds(120));
+    CHECK(!parseDuration("", d) && !parseDuration("fast", d) && !parseDuration("3 parsecs", d) && !parseDuration("-1s", d));
+    CHECK(formatDuration(std::chrono::milliseconds(2500)) == "2.5s");
+    CHECK(formatDuration(std::chrono::microseconds(120000)) == "120ms");
+    CHECK(formatDuration(std::chrono::nanoseconds(35000)) == "35us");
+    CHECK(formatDuration(std::chrono::nanoseconds(800)) == "800ns");
+
+    CHECK(!hostName().empty());
+    const std::string u = uuidV4(), v = uuidV4();
+    CHECK(u != v && u.size() == 36 && u[8] == '-' && u[13] == '-' && u[18] == '-' && u[23] == '-');
+    CHECK(u[14] == '4' && (u[19] == '8' || u[19] == '9' || u[19] == 'a' || u[19] == 'b'));
+    CHECK(random64() != random64());
+
+    CHECK((split("a,b,,c", ',') == std::vector<std::string>{"a", "b", "c"}));
+    CHECK((split("a,b,,c", ',', true) == std::vector<std::string>{"a", "b", "", "c"}));
+    CHECK(split("", ',').empty());
+    CHECK(trim("  x y \t\n") == "x y" && trim(" \t ").empty());
 }
 
 TEST_MAIN()
