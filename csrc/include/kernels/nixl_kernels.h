@@ -27,6 +27,8 @@ extern "C" {
  *     optional host-visible flag.
  * A block is tokens x heads rows of head_bytes; both caches are described by byte strides,
  * which covers [block, token, head, dim] and [block, head, token, dim] layouts.
+ * Every block id is checked against the length of its view entry on both sides before a byte of
+ * the block moves (block tables are device data nobody validated): see `status`.
  * The reference moves KV caches as plain descriptor lists (benchmark/kvbench); it has no
  * counterpart of this kernel.
  */
@@ -51,6 +53,8 @@ typedef struct NixlKvXferParams {
     uint64_t host_seq;
     uint32_t *done_counter;    /* device scratch word, zero before the first launch; reset by the kernel */
     int32_t grid;              /* 0: default (two CTAs per SM) */
+    int32_t *status;           /* may be NULL; device-visible word (device or pinned host memory) that receives 1 when a block id
+                                  pointed outside its cache tensor's view entry: that block is skipped, nothing outside is touched */
 } NixlKvXferParams;
 
 int nixl_kv_xfer_launch(const NixlKvXferParams *params, void *stream);

@@ -397,7 +397,8 @@ nixlKvTransfer::nixlKvTransfer(nixlAgent &agent, const std::vector<nixlBasicDesc
         return;
     }
     if (!devAlloc(counter_, 64) || cudaHostAlloc(reinterpret_cast<void **>(&flag_), 64, cudaHostAllocMapped | cudaHostAllocPortable) != cudaSuccess) return;
-    *flag_ = 0;
+    flag_[0] = flag_[1] = 0;
+    p_.status = reinterpret_cast<int32_t *>(flag_ + 1); // second word of the pinned block: set when a block id was out of range
     p_.src_view = srcView_;
     p_.dst_view = dstView_;
     p_.n_tensors = static_cast<int32_t>(srcTensors.size());
@@ -449,5 +450,10 @@ nixl_status_t nixlKvTransfer::wait(uint64_t ticket, double timeoutSeconds) const
     const auto t0 = std::chrono::steady_clock::now();
     for (uint32_t spins = 0; !done(ticket); ++spins)
         if ((spins & 0xfff) == 0xfff && std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count() > timeoutSeconds) return NIXL_IN_PROG;
+    if (*reinterpret_cast<volatile uint64_t *>(flag_ + 1) != 0) { // the kernel skipped a block whose id pointed outside its cache tensor
+        *reinterpret_cast<volatile uint64_t *>(flag_ + 1) = 0;
+        NIXL_ERROR << "nixlKvTransfer: a block id pointed outside its cache tensor; that block was not transferred";
+        return NIXL_ERR_INVALID_PARAM;
+    }
     return NIXL_SUCCESS;
 }

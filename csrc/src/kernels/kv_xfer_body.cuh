@@ -64,6 +64,10 @@ __device__ __forceinline__ void moveBlocks(const NixlKvXferParams &p, const int3
     const int vec_per_unit = rows * vec_per_row;
     const long long units = static_cast<long long>(p.n_tensors) * p.n_pairs;
     const int dst_vec_bytes = kCast ? 8 : 16;
+    // Bytes a block spans from its base on either side (strides are non-negative), for the bounds check.
+    const long long src_extent = (p.tokens - 1LL) * p.src_token_stride + (p.heads - 1LL) * p.src_head_stride + p.head_bytes;
+    const long long dst_extent = (p.tokens - 1LL) * p.dst_token_stride + (p.dst_head_offset + p.heads - 1LL) * p.dst_head_stride +
+        (kCast ? p.head_bytes / 2 : p.head_bytes);
 
     for (long long u0 = static_cast<long long>(blockIdx.x) * kKvUnroll; u0 < units; u0 += static_cast<long long>(gridDim.x) * kKvUnroll) {
         const char *sbase[kKvUnroll];
@@ -75,9 +79,20 @@ __device__ __forceinline__ void moveBlocks(const NixlKvXferParams &p, const int3
                 // Pairs vary fastest so that consecutive units read one tensor's blocks.
                 const int t = static_cast<int>(u / p.n_pairs);
                 const int i = static_cast<int>(u - static_cast<long long>(t) * p.n_pairs);
-                sbase[k] = reinterpret_cast<const char *>(src_ent[t].ptr) + static_cast<long long>(__ldg(src_blocks + i)) * p.src_block_stride;
-                dbase[k] = reinterpret_cast<char *>(dst_ent[t].ptr) + static_cast<long long>(__ldg(dst_blocks + i)) * p.dst_block_stride +
-                    static_cast<long long>(p.dst_head_offset) * p.dst_head_stride;
+                const long long sb = __ldg(src_blocks + i), db = __ldg(dst_blocks + i);
+                const long long soff = sb * p.src_block_stride, doff = db * p.dst_block_stride;
+                // The block tables come from device memory that nobody validated: a block must lie inside its tensor's
+                // registered range on both sides, or it is skipped and reported.
+                const bool inside = sb >= 0 && db >= 0 && src_ent[t].ptr != 0 && dst_ent[t].ptr != 0 &&
+                    static_cast<unsigned long long>(soff + src_extent) <= src_ent[t].len && static_cast<unsigned long long>(doff + dst_extent) <= dst_ent[t].len;
+                if (inside) {
+                    sbase[k] = reinterpret_cast<const char *>(src_ent[t].ptr) + soff;
+                    dbase[k] = reinterpret_cast<char *>(dst_ent[t].ptr) + doff + static_cast<long long>(p.dst_head_offset) * p.dst_head_stride;
+                } else {
+                    sbase[k] = nullptr;
+                    dbase[k] = nullptr;
+                    if (threadIdx.x == 0 && p.status != nullptr) *reinterpret_cast<volatile int32_t *>(p.status) = 1;
+                }
             } else {
                 sbase[k] = nullptr;
                 dbase[k] = nullptr;

@@ -47,6 +47,7 @@ class _Params(ctypes.Structure):
         ("host_seq", ctypes.c_uint64),
         ("done_counter", ctypes.c_void_p),
         ("grid", ctypes.c_int32),
+        ("status", ctypes.c_void_p),
     ]
 
 
@@ -122,7 +123,7 @@ class KVTransfer:
             )
         # Scratch: the "last CTA" counter (zero between launches) and a pinned completion word.
         self._counter = torch.zeros(64, dtype=torch.int32, device=self.device)
-        self._flag = torch.zeros(1, dtype=torch.int64).pin_memory()
+        self._flag = torch.zeros(2, dtype=torch.int64).pin_memory()  # completion word, then the out-of-range word
         self._seq = 0
         self._p = _Params()
         sb, st, sh = src_layout.strides()
@@ -138,6 +139,7 @@ class KVTransfer:
         p.scale = scale
         p.done_counter = self._counter.data_ptr()
         p.host_flag = self._flag.data_ptr()
+        p.status = self._flag.data_ptr() + 8
         p.grid = 0
         self._launch = _lib.lib().nixl_kv_xfer_launch
         self._launch.argtypes = [ctypes.POINTER(_Params), ctypes.c_void_p]
@@ -179,8 +181,14 @@ class KVTransfer:
         return _lib.read_u64(self._flag.data_ptr()) >= ticket
 
     def wait(self, ticket: int, spins: int = 200_000_000) -> None:
+        """Blocks until the launch with that ticket has delivered.  Raises ``IndexError`` when a block id of a
+        completed launch pointed outside its cache tensor (the kernel checks every id against the registered
+        range, skips such a block and reports it; nothing outside the caches is touched)."""
         for _ in range(spins):
             if self.done(ticket):
+                if _lib.read_u64(self._flag.data_ptr() + 8):
+                    self._flag[1] = 0
+                    raise IndexError("a block id pointed outside its cache tensor; that block was not transferred")
                 return
         raise TimeoutError("KV transfer did not complete")
 

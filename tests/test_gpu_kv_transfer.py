@@ -72,6 +72,42 @@ def test_hnd_receiver_layout_and_signal():
     xfer.close()
 
 
+def test_block_ids_outside_the_cache_are_skipped_and_reported():
+    """Block tables are device data nobody validated: the kernel checks every id against the registered range of its
+    cache tensor on both sides, skips a block that does not fit and reports it; the other blocks arrive.  The caches
+    here are the first 8 blocks of 16-block allocations, so even an unchecked id would stay inside memory this test owns."""
+    src_dev = torch.device("cuda:0")
+    dst_dev = torch.device("cuda:1" if torch.cuda.device_count() > 1 else "cuda:0")
+    cfg = nixl_agent_config(enable_prog_thread=False, backends=["NVLINK"])
+    a, b = nixl_agent("kvoob_prefill", cfg), nixl_agent("kvoob_decode", cfg)
+    g = torch.Generator(device=src_dev).manual_seed(3)
+    src_all = [torch.randn(16, 16, 2, 128, device=src_dev, dtype=torch.bfloat16, generator=g) for _ in range(2)]
+    dst_all = [torch.zeros(16, 16, 4, 128, device=dst_dev, dtype=torch.bfloat16) for _ in range(2)]
+    src, dst = [t[:8] for t in src_all], [t[:8] for t in dst_all]  # what is registered and put into the views
+    a.register_memory(src)
+    b.register_memory(dst)
+    a.add_remote_agent(b.get_agent_metadata())
+    remote = [(t.data_ptr(), t.numel() * t.element_size(), t.get_device()) for t in dst]
+    xfer = KVTransfer(a, src, KVLayout(16, 2, 128), b.name, remote, KVLayout(16, 4, 128))
+    good_s = torch.tensor([0, 3, 7], device="cuda:0", dtype=torch.int32)
+    good_d = torch.tensor([7, 1, 0], device="cuda:0", dtype=torch.int32)
+    xfer.wait(xfer.post(good_s, good_d))  # in range: no report
+    for bad_s, bad_d in (([0, 8, 7], [7, 1, 0]), ([0, 3, 7], [7, 9, 0]), ([0, -1, 7], [7, 1, 0])):
+        for d in dst_all:
+            d.zero_()
+        torch.cuda.synchronize()
+        sb = torch.tensor(bad_s, device="cuda:0", dtype=torch.int32)
+        db = torch.tensor(bad_d, device="cuda:0", dtype=torch.int32)
+        with pytest.raises(IndexError):
+            xfer.wait(xfer.post(sb, db))
+        torch.cuda.synchronize()
+        for s, d_all in zip(src_all, dst_all):
+            assert torch.equal(d_all[7, :, :2].to(src_dev), s[0]) and torch.equal(d_all[0, :, :2].to(src_dev), s[7])  # the valid pairs arrived
+            assert int(d_all[1].abs().sum()) == 0 and int(d_all[8:].abs().sum()) == 0  # the bad pair moved nothing, inside or outside the cache
+    xfer.wait(xfer.post(good_s, good_d))  # the report was cleared
+    xfer.close()
+
+
 def test_rejects_bad_arguments():
     a, b, src, dst, remote = _setup("kvbad", 2, 8, 2, 4, False)
     with pytest.raises(ValueError):
