@@ -3,8 +3,10 @@
 the metric family (size sweep, KV-cache transfer, MoE dispatch/combine) and in-run baselines.
 
 Headline step: every rank posts one transfer request (BATCH descriptors of BLOCK bytes) to its
-ring neighbour (rank+1) % N through ``nixl_agent`` and polls it to completion.  With N = 1 the
-target is a second buffer on the same GPU.  The reported value is the whole-job aggregate:
+ring neighbour (rank+1) % N through ``nixl_agent`` and polls it to completion; two identical
+requests take turns (a request is posted again only once it has completed), so the next step is
+queued on the stream while the current one runs.  With N = 1 the target is a second buffer on the
+same GPU.  The reported value is the whole-job aggregate:
 N x bytes per step x steps / (max over ranks of the device time).
 
 Timing: CUDA events recorded on the stream the copies are launched on (stream-ordered posting),
@@ -16,7 +18,9 @@ registered source buffer and a device->host read of a digest of the buffer this 
 ``extras`` (outside the timed regions, every figure device-timed and the max over ranks):
   baselines  the same ring step through (a) the copy engines, one cudaMemcpyAsync per descriptor
              (what a descriptor-at-a-time transport such as UCX cuda_ipc does), (b) the copy
-             kernel only, (c) NCCL send/recv; ``vs_baseline`` divides the headline by (a)
+             kernel only, (c) the same request with its destination blocks in reverse order (nothing
+             to merge), (d) the headline once more, (e) NCCL send/recv; ``vs_baseline`` divides the
+             headline by (a)
   sweep      WRITE and READ, 4 KiB - 1 GiB, 1/16/256 descriptors per request, ring and
              all-to-all (pairwise at N = 2): GB/s per GPU and host-timed p50/p99 latency
   kv         paged KV-cache transfer, Llama-3-8B shape, prefill ranks -> decode ranks with TP
@@ -24,7 +28,8 @@ registered source buffer and a device->host read of a digest of the buffer this 
   ep         MoE dispatch + combine, DeepSeek-V3 shape, 128 and 4096 tokens per GPU, checked on
              every rank against an fp32 PyTorch statement of the routing
   dput       GPU-initiated put with signal: a persistent kernel puts 256 KiB tiles to every peer from
-             inside its loop (device API), the consumer waits on the remote counter; µs per put
+             inside its loop (device API), the consumer waits on the remote per-slot counters and
+             acknowledges; µs per put, landed tiles compared with their sources
 
 Launch: ``python bench.py`` (1 GPU) or
 ``python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N``.
