@@ -131,7 +131,7 @@ class ClockSampler:
 # ====================================================================== reference arm
 
 REFERENCE_INSTALL = (
-    "python -m pip install --no-index --no-build-isolation --find-links /opt/wheelhouse --target baseline/_ref /root/reference"
+    "python -m pip install --no-index --no-build-isolation --find-links <wheelhouse> --target baseline/_ref <reference source tree>"
 )
 
 
