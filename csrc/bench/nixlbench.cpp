@@ -12,11 +12,13 @@
 //             [--depth 1] [--num-threads 1] [--enable-pt] [--copy-path vector|bulk] [--param key=value]... [--check]
 //             [--prepared] [--recreate] [--reregister] [--scatter] [--config file]
 //             [--file path [--num-files N] [--direct]]      storage mode (POSIX, GDS, GDS_MT backends)
-//             [--scheme pairwise|onetomany|manytoone --num-initiator-dev N --num-target-dev M]
+//             [--scheme pairwise|onetomany|manytoone|tp --num-initiator-dev N --num-target-dev M]
 //
-// --scheme onetomany: one initiator GPU (--src-dev) posts the same request to M target GPUs at once; manytoone: N
-// initiator GPUs post to one target GPU (--dst-dev) at once, which is the pattern that shows what a receiver's
-// ingress sustains.  One agent per GPU, all in this process; the figure is the sum over all flows.
+// --scheme onetomany: one initiator (--src-dev) posts the same request to M targets at once; manytoone: N
+// initiators post to one target (--dst-dev) at once, which is the pattern that shows what a receiver's ingress
+// sustains; tp: N initiators x M targets, every initiator sends 1/M of each block to every target (tensor-parallel
+// resharding).  One agent per endpoint, all in this process (VRAM: one endpoint per GPU; DRAM: host buffers); the
+// figure is the sum over all flows.
 //
 // --num-threads T: T worker threads share the batch (thread t owns descriptors t, t + T, ...), each with its own
 // requests and pipeline (the reference's worker threads, worker/nixl/nixl_worker.cpp:125,:1834); --enable-pt gives
@@ -58,7 +60,7 @@ struct Args {
     size_t min = 4096, max = size_t(1) << 30, total = size_t(8) << 30;
     bool check = false, prepared = false, recreate = false, reregister = false, direct = false;
     bool scatter = false; // target blocks of a batch in reverse order: no descriptor continues its predecessor
-    std::string scheme = "pairwise"; // pairwise | onetomany | manytoone (benchmark/nixlbench/src/utils/utils.h:122-125 of the reference)
+    std::string scheme = "pairwise"; // pairwise | onetomany | manytoone | tp (benchmark/nixlbench/src/utils/utils.h:122-125 of the reference)
     int num_initiator_dev = 1, num_target_dev = 1;
     int batch_max = 0, num_files = 1;
     int num_threads = 1;    // worker threads of the pairwise scheme, each with its share of the batch
@@ -187,129 +189,168 @@ double pct(std::vector<double> &v, double q) {
     std::sort(v.begin(), v.end());
     return v[std::min(v.size() - 1, static_cast<size_t>(q * v.size()))];
 }
-// One-to-many / many-to-one: a flow per (initiator GPU, target GPU) pair, all posted together every iteration.
+// One-to-many / many-to-one / tp: a flow per (initiator, target) pair, all posted together every iteration.
+//   onetomany  one initiator (--src-dev), M targets: the same request goes to every target
+//   manytoone  N initiators, one target (--dst-dev): what a receiver's ingress sustains
+//   tp         N initiators x M targets (tensor-parallel resharding): every initiator sends 1/M of each block to
+//              every target, so a flow's descriptors are block / M bytes
+// One agent per endpoint, all in this process.  VRAM: one endpoint per GPU.  DRAM: endpoints are host buffers.
 int runScheme(const Args &a, int ndev) {
-    const bool many_targets = a.scheme == "onetomany";
-    const int n = many_targets ? a.num_target_dev : a.num_initiator_dev;
-    if (a.mem != "VRAM" || n + 1 > ndev) {
-        std::fprintf(stderr, "--scheme %s needs VRAM and %d GPUs (found %d)\n", a.scheme.c_str(), n + 1, ndev);
+    const bool vram = a.mem == "VRAM";
+    const int n_ini = a.scheme == "onetomany" ? 1 : a.num_initiator_dev;
+    const int n_tgt = a.scheme == "manytoone" ? 1 : a.num_target_dev;
+    if (vram && n_ini + n_tgt > ndev) {
+        std::fprintf(stderr, "--scheme %s needs %d GPUs (found %d)\n", a.scheme.c_str(), n_ini + n_tgt, ndev);
         return 2;
     }
-    const int hub = many_targets ? a.src_dev : (a.dst_dev >= 0 ? a.dst_dev : 0); // the "one" side
-    std::vector<int> spokes;
-    for (int d = 0; d < ndev && static_cast<int>(spokes.size()) < n; ++d)
-        if (d != hub) spokes.push_back(d);
+    // Devices: the "one" side keeps the device the options name, the others take the remaining ordinals in order.
+    std::vector<int> ini_dev, tgt_dev;
+    {
+        std::vector<bool> used(std::max(ndev, 1), false);
+        auto take = [&](int want) {
+            if (!vram) return 0;
+            if (want >= 0 && want < ndev && !used[want]) {
+                used[want] = true;
+                return want;
+            }
+            for (int d = 0; d < ndev; ++d)
+                if (!used[d]) {
+                    used[d] = true;
+                    return d;
+                }
+            return 0;
+        };
+        if (a.scheme == "manytoone") tgt_dev.push_back(take(a.dst_dev >= 0 ? a.dst_dev : 0));
+        for (int i = 0; i < n_ini; ++i) ini_dev.push_back(take(i == 0 ? a.src_dev : -1));
+        while (static_cast<int>(tgt_dev.size()) < n_tgt) tgt_dev.push_back(take(tgt_dev.empty() ? a.dst_dev : -1));
+    }
+    const int split = a.scheme == "tp" ? n_tgt : 1; // a block is cut into this many pieces, one per target
     const size_t buf_bytes = std::min(a.total, std::max<size_t>(a.max * std::max(a.batch, a.batch_max), a.max));
-    nixlAgentConfig cfg(false);
+    nixlAgentConfig cfg(a.enable_pt);
     nixl_b_params_t params;
     params["copy_path"] = a.copy_path;
     for (auto &kv : a.extra) params[kv.first] = kv.second;
+    const nixl_mem_t mt = vram ? VRAM_SEG : DRAM_SEG;
     struct Side {
-        int dev;
-        void *buf = nullptr; // hub: n regions of buf_bytes (one per spoke); spoke: one region
+        int dev = 0;
+        char *buf = nullptr; // initiator: one source region; target: one landing region per initiator
+        size_t bytes = 0;
+        std::string name;
         std::unique_ptr<nixlAgent> agent;
     };
     auto make = [&](int dev, const std::string &name, size_t bytes, int fill, Side &s) {
         s.dev = dev;
-        cudaSetDevice(dev);
-        if (cudaMalloc(&s.buf, bytes) != cudaSuccess) return false;
-        cudaMemset(s.buf, fill, bytes);
-        cudaDeviceSynchronize();
+        s.bytes = bytes;
+        s.name = name;
+        if (vram) {
+            cudaSetDevice(dev);
+            if (cudaMalloc(reinterpret_cast<void **>(&s.buf), bytes) != cudaSuccess) return false;
+            cudaMemset(s.buf, fill, bytes);
+            cudaDeviceSynchronize();
+        } else {
+            void *p = nullptr;
+            if (posix_memalign(&p, 4096, bytes) != 0) return false;
+            s.buf = static_cast<char *>(p);
+            std::memset(s.buf, fill, bytes);
+        }
         s.agent = std::make_unique<nixlAgent>(name, cfg);
         nixlBackendH *b = nullptr;
         if (s.agent->createBackend(a.backend, params, b) != NIXL_SUCCESS) return false;
-        nixl_reg_dlist_t reg(VRAM_SEG);
-        reg.addDesc(nixlBlobDesc(reinterpret_cast<uintptr_t>(s.buf), bytes, dev, ""));
+        nixl_reg_dlist_t reg(mt);
+        reg.addDesc(nixlBlobDesc(reinterpret_cast<uintptr_t>(s.buf), bytes, vram ? dev : 0, ""));
         return s.agent->registerMem(reg) == NIXL_SUCCESS;
     };
-    Side hub_side;
-    std::vector<Side> spoke_sides(n);
-    if (!make(hub, "hub", buf_bytes * n, many_targets ? 0x5a : 0, hub_side)) return 3;
-    for (int i = 0; i < n; ++i)
-        if (!make(spokes[i], "spoke" + std::to_string(i), buf_bytes, many_targets ? 0 : 0x5a, spoke_sides[i])) return 3;
-    // initiators learn their targets
-    auto learn = [](nixlAgent &ini, nixlAgent &tgt) {
-        nixl_blob_t md;
-        std::string name;
-        tgt.getLocalMD(md);
-        return ini.loadRemoteMD(md, name) == NIXL_SUCCESS;
-    };
-    for (int i = 0; i < n; ++i)
-        if (!(many_targets ? learn(*hub_side.agent, *spoke_sides[i].agent) : learn(*spoke_sides[i].agent, *hub_side.agent))) return 6;
     const nixl_xfer_op_t op = a.op == "READ" ? NIXL_READ : NIXL_WRITE;
-    std::printf("# scheme %s: %s GPU %d, %d %s GPU(s)\n", a.scheme.c_str(), many_targets ? "initiator" : "target", hub, n,
-                many_targets ? "target" : "initiator");
+    // WRITE: initiators hold the pattern, targets start at zero; READ: the other way round.
+    std::vector<Side> inis(n_ini), tgts(n_tgt);
+    for (int i = 0; i < n_ini; ++i)
+        if (!make(ini_dev[i], "ini" + std::to_string(i), buf_bytes, op == NIXL_WRITE ? 0x5a : 0, inis[i])) return 3;
+    for (int j = 0; j < n_tgt; ++j)
+        if (!make(tgt_dev[j], "tgt" + std::to_string(j), buf_bytes * n_ini, op == NIXL_WRITE ? 0 : 0x5a, tgts[j])) return 3;
+    for (auto &ini : inis)
+        for (auto &tgt : tgts) {
+            nixl_blob_t md;
+            std::string name;
+            tgt.agent->getLocalMD(md);
+            if (ini.agent->loadRemoteMD(md, name) != NIXL_SUCCESS) return 6;
+        }
+    const int flows = n_ini * n_tgt;
+    std::printf("# scheme %s: %d initiator(s) x %d target(s), %d flow(s), %s\n", a.scheme.c_str(), n_ini, n_tgt, flows, a.mem.c_str());
     std::printf("%-12s %6s %10s %12s %10s %10s\n", "block", "batch", "GB/s", "GB/s_per_flow", "p50_us", "p99_us");
     for (int batch = a.batch; batch <= std::max(a.batch, a.batch_max); batch *= 2)
     for (size_t block = a.min; block <= a.max && block * batch <= buf_bytes; block *= 2) {
-        const size_t per = block * batch;
+        const size_t piece = block / split; // bytes per descriptor of one flow
+        if (piece == 0) continue;
+        const size_t per_flow = piece * batch;
         int iters = a.iters, warm = a.warmup;
-        if (per > (size_t(64) << 20)) {
-            iters = std::max<int>(10, static_cast<int>((size_t(64) << 30) / per / 16));
+        if (per_flow * n_tgt > (size_t(64) << 20)) {
+            iters = std::max<int>(10, static_cast<int>((size_t(64) << 30) / (per_flow * n_tgt) / 16));
             warm = 3;
         }
-        std::vector<nixlXferReqH *> reqs(n, nullptr);
-        for (int i = 0; i < n; ++i) {
-            nixl_xfer_dlist_t l(VRAM_SEG), r(VRAM_SEG);
-            char *hub_base = static_cast<char *>(hub_side.buf) + static_cast<size_t>(i) * buf_bytes;
-            char *spoke_base = static_cast<char *>(spoke_sides[i].buf);
-            for (int j = 0; j < batch; ++j) {
-                const size_t off = static_cast<size_t>(j) * block, roff = a.scatter ? static_cast<size_t>(batch - 1 - j) * block : off;
-                if (many_targets) {
-                    l.addDesc(nixlBasicDesc(reinterpret_cast<uintptr_t>(hub_base) + off, block, hub));
-                    r.addDesc(nixlBasicDesc(reinterpret_cast<uintptr_t>(spoke_base) + roff, block, spokes[i]));
-                } else {
-                    l.addDesc(nixlBasicDesc(reinterpret_cast<uintptr_t>(spoke_base) + off, block, spokes[i]));
-                    r.addDesc(nixlBasicDesc(reinterpret_cast<uintptr_t>(hub_base) + roff, block, hub));
+        std::vector<nixlXferReqH *> reqs(flows, nullptr);
+        for (int i = 0; i < n_ini; ++i)
+            for (int j = 0; j < n_tgt; ++j) {
+                nixl_xfer_dlist_t l(mt), r(mt);
+                char *land = tgts[j].buf + static_cast<size_t>(i) * buf_bytes; // initiator i's region at target j
+                for (int k = 0; k < batch; ++k) {
+                    // tp: target j receives piece j of every block and packs the pieces densely
+                    const size_t loff = static_cast<size_t>(k) * block + (split > 1 ? static_cast<size_t>(j) * piece : 0);
+                    const size_t roff = (a.scatter ? static_cast<size_t>(batch - 1 - k) : static_cast<size_t>(k)) * piece;
+                    l.addDesc(nixlBasicDesc(reinterpret_cast<uintptr_t>(inis[i].buf) + loff, piece, vram ? inis[i].dev : 0));
+                    r.addDesc(nixlBasicDesc(reinterpret_cast<uintptr_t>(land) + roff, piece, vram ? tgts[j].dev : 0));
                 }
+                if (inis[i].agent->createXferReq(op, l, r, tgts[j].name, reqs[i * n_tgt + j]) != NIXL_SUCCESS) return 7;
             }
-            nixlAgent &ini = many_targets ? *hub_side.agent : *spoke_sides[i].agent;
-            const std::string remote = many_targets ? "spoke" + std::to_string(i) : "hub";
-            if (ini.createXferReq(op, l, r, remote, reqs[i]) != NIXL_SUCCESS) return 7;
-        }
         std::vector<double> step;
         clk::time_point t_begin = clk::now();
         for (int it = 0; it < warm + iters; ++it) {
             if (it == warm) t_begin = clk::now();
             const auto t0 = clk::now();
-            std::vector<bool> busy(n, false);
-            for (int i = 0; i < n; ++i) {
-                nixlAgent &ini = many_targets ? *hub_side.agent : *spoke_sides[i].agent;
-                const nixl_status_t st = ini.postXferReq(reqs[i]);
+            std::vector<bool> busy(flows, false);
+            for (int f = 0; f < flows; ++f) {
+                const nixl_status_t st = inis[f / n_tgt].agent->postXferReq(reqs[f]);
                 if (st < 0) return 9;
-                busy[i] = st != NIXL_SUCCESS;
+                busy[f] = st != NIXL_SUCCESS;
             }
             for (bool any = true; any;) {
                 any = false;
-                for (int i = 0; i < n; ++i) {
-                    if (!busy[i]) continue;
-                    nixlAgent &ini = many_targets ? *hub_side.agent : *spoke_sides[i].agent;
-                    const nixl_status_t st = ini.getXferStatus(reqs[i]);
+                for (int f = 0; f < flows; ++f) {
+                    if (!busy[f]) continue;
+                    const nixl_status_t st = inis[f / n_tgt].agent->getXferStatus(reqs[f]);
                     if (st < 0) return 8;
-                    busy[i] = st != NIXL_SUCCESS;
-                    any |= busy[i];
+                    busy[f] = st != NIXL_SUCCESS;
+                    any |= busy[f];
                 }
             }
             if (it >= warm) step.push_back(us(t0, clk::now()));
         }
         const double wall = us(t_begin, clk::now());
-        const double gbs = double(per) * n * iters / wall / 1e3;
-        std::printf("%-12zu %6d %10.2f %12.2f %10.2f %10.2f\n", block, batch, gbs, gbs / n, pct(step, 0.5), pct(step, 0.99));
+        const double gbs = double(per_flow) * flows * iters / wall / 1e3;
+        std::printf("%-12zu %6d %10.2f %12.2f %10.2f %10.2f\n", block, batch, gbs, gbs / flows, pct(step, 0.5), pct(step, 0.99));
         std::fflush(stdout);
-        for (int i = 0; i < n; ++i) (many_targets ? *hub_side.agent : *spoke_sides[i].agent).releaseXferReq(reqs[i]);
-        if (a.check && op == NIXL_WRITE) { // every landing region must hold the pattern
-            std::vector<unsigned char> h(std::min<size_t>(per, 1 << 20));
-            for (int i = 0; i < n; ++i) {
-                const void *landed = many_targets ? spoke_sides[i].buf : static_cast<char *>(hub_side.buf) + static_cast<size_t>(i) * buf_bytes;
-                cudaSetDevice(many_targets ? spokes[i] : hub);
-                cudaDeviceSynchronize();
-                cudaMemcpy(h.data(), landed, h.size(), cudaMemcpyDeviceToHost);
-                for (unsigned char c : h)
-                    if (c != 0x5a) {
-                        std::fprintf(stderr, "consistency check failed at block %zu, flow %d\n", block, i);
-                        return 10;
-                    }
-            }
+        for (int f = 0; f < flows; ++f) inis[f / n_tgt].agent->releaseXferReq(reqs[f]);
+        if (a.check) { // every landing region (WRITE) or source region (READ) must hold the pattern where flows wrote
+            std::vector<unsigned char> h(std::min<size_t>(per_flow, 1 << 20));
+            auto fetch = [&](const Side &s, const char *from) {
+                if (vram) {
+                    cudaSetDevice(s.dev);
+                    cudaDeviceSynchronize();
+                    cudaMemcpy(h.data(), from, h.size(), cudaMemcpyDeviceToHost);
+                } else {
+                    std::memcpy(h.data(), from, h.size());
+                }
+            };
+            for (int i = 0; i < n_ini; ++i)
+                for (int j = 0; j < n_tgt; ++j) {
+                    if (op == NIXL_WRITE) fetch(tgts[j], tgts[j].buf + static_cast<size_t>(i) * buf_bytes);
+                    else if (split == 1 && j == 0) fetch(inis[i], inis[i].buf);
+                    else continue;
+                    for (unsigned char c : h)
+                        if (c != 0x5a) {
+                            std::fprintf(stderr, "consistency check failed at block %zu, initiator %d, target %d\n", block, i, j);
+                            return 10;
+                        }
+                }
         }
     }
     return 0;
@@ -374,8 +415,8 @@ int main(int argc, char **argv) {
         return 2;
     }
     if (a.scheme != "pairwise") {
-        if (a.scheme != "onetomany" && a.scheme != "manytoone") {
-            std::fprintf(stderr, "unknown --scheme %s (pairwise, onetomany, manytoone)\n", a.scheme.c_str());
+        if (a.scheme != "onetomany" && a.scheme != "manytoone" && a.scheme != "tp") {
+            std::fprintf(stderr, "unknown --scheme %s (pairwise, onetomany, manytoone, tp)\n", a.scheme.c_str());
             return 2;
         }
         return runScheme(a, ndev);

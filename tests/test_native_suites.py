@@ -65,6 +65,27 @@ def test_native_nixlbench_storage_and_config_file(tmp_path):
     assert _nixlbench("--config", str(cfg)).returncode == 2
 
 
+@pytest.mark.parametrize("scheme,extra,flows", [("onetomany", ["--num-target-dev", "3"], 3), ("manytoone", ["--num-initiator-dev", "3"], 3),
+                                                ("tp", ["--num-initiator-dev", "2", "--num-target-dev", "4"], 8)])
+def test_native_nixlbench_schemes_on_host_memory(scheme, extra, flows):
+    """The communication schemes of the reference's nixlbench, here between host buffers (one agent per endpoint)."""
+    for op in ("WRITE", "READ"):
+        res = _nixlbench("--mem", "DRAM", "--scheme", scheme, *extra, "--op", op, "--min", "65536", "--max", "131072", "--batch", "4",
+                         "--iters", "30", "--warmup", "3", "--check", "--num_threads=1")
+        assert res.returncode == 0, res.stdout + res.stderr
+        assert f"{flows} flow(s)" in res.stdout
+        rows = [l.split() for l in res.stdout.splitlines() if l and l[0].isdigit()]
+        assert [r[0] for r in rows] == ["65536", "131072"] and all(float(r[2]) > 0 for r in rows)
+
+
+def test_native_nixlbench_worker_threads_share_the_batch():
+    res = _nixlbench("--mem", "DRAM", "--min", "16384", "--max", "16384", "--batch", "8", "--iters", "200", "--warmup", "10", "--num-threads", "4",
+                     "--depth", "2", "--check", "--enable-pt", "--prepared")
+    assert res.returncode == 0, res.stdout + res.stderr
+    rows = [l.split() for l in res.stdout.splitlines() if l and l[0].isdigit()]
+    assert len(rows) == 1 and rows[0][1] == "8" and float(rows[0][2]) > 0
+
+
 def test_native_nixlbench_accepts_the_reference_spellings(tmp_path):
     """gflags-style names of the reference's nixlbench (underscores, --name=value) map onto the same options."""
     res = _nixlbench("--backend", "NVLINK", "--initiator_seg_type=DRAM", "--op_type", "WRITE", "--start_block_size=8192",
