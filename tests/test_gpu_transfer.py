@@ -203,35 +203,6 @@ def test_bulk_path_deep_pipeline_is_byte_exact():
         b.deregister_memory(reg)
 
 
-def test_release_right_after_post_on_a_busy_caller_stream():
-    """The request is posted on the caller's stream behind a long-running kernel and released at
-    once: the release must wait for the copy kernel (it reads the request's descriptor table and
-    writes its completion word), and the bytes must be intact afterwards."""
-    a, b = _pair("rel_stream", {"coalesce": "false"})
-    n_desc, size = 64, 1 << 16  # more than 32 descriptors: the table lives in device memory
-    src = torch.randint(0, 255, (n_desc, size), dtype=torch.uint8, device="cuda:0")
-    dst = torch.zeros_like(src)
-    a.register_memory(src)
-    b.register_memory(dst)
-    _connect(a, b)
-    stream = torch.cuda.Stream()
-    for _ in range(3):
-        dst.zero_()
-        torch.cuda.synchronize()
-        h = a.initialize_xfer("WRITE", [src[i] for i in range(n_desc)], [dst[i] for i in range(n_desc)], b.name)
-        with torch.cuda.stream(stream):
-            torch.cuda._sleep(200_000_000)  # ~0.1 s of device time in front of the copy
-            assert a.transfer(h, custom_param=f"stream={stream.cuda_stream}") in ("DONE", "PROC")
-        a.release_xfer_handle(h)
-        # another request right away: it must not be handed a completion word that the first kernel still writes
-        h2 = a.initialize_xfer("WRITE", src[0], dst[0], b.name)
-        assert a.transfer(h2) in ("DONE", "PROC")
-        assert _wait(a, h2) == "DONE"
-        a.release_xfer_handle(h2)
-        torch.cuda.synchronize()
-        assert torch.equal(src, dst)
-
-
 def test_request_after_released_table_request_completes():
     """A request with a descriptor table is released; the next request, whose kernel runs several
     CTAs and therefore counts them, must not inherit the table's bytes as its counter."""
