@@ -1254,6 +1254,8 @@ nixl_status_t Engine::postXfer(const nixl_xfer_op_t &operation, const nixl_meta_
             use(b.device);
             cudaStream_t s = has_user_stream ? user_stream : b.stream;
             if (b.uploaded && !b.tableReady && b.launch.table && !cudaOk(cudaStreamWaitEvent(s, b.uploaded, 0), "cudaStreamWaitEvent")) {
+                if (b.notifWord) NotifRingWriter::complete(b.notifWord, b.notifSeq, false); // claimed above, never to be released by a kernel
+                b.notifWord = nullptr;
                 err = NIXL_ERR_BACKEND;
                 break;
             }
