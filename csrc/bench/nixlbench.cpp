@@ -511,6 +511,11 @@ int main(int argc, char **argv) {
         std::vector<WorkerStats> stats(nthreads);
         std::barrier start_line(nthreads);
         auto worker = [&](int tid) -> int {
+        // A worker that gives up before the common start leaves the start line, so that the others do not wait for it.
+        auto early = [&](int rc) {
+            start_line.arrive_and_drop();
+            return rc;
+        };
         std::vector<double> &prep = stats[tid].prep, &post = stats[tid].post, &xfer = stats[tid].xfer;
         std::vector<nixlXferReqH *> slots(a.depth, nullptr);
         nixl_xfer_dlist_t l(mt), r(rmt);
@@ -534,7 +539,7 @@ int main(int argc, char **argv) {
         for (int i = 0; i < mine; ++i) all_idx[i] = i;
         if (a.prepared) {
             const auto t0 = clk::now();
-            if (ini.prepXferDlist(NIXL_INIT_AGENT, l, side_l) != NIXL_SUCCESS || ini.prepXferDlist(remote_name, r, side_r) != NIXL_SUCCESS) return 7;
+            if (ini.prepXferDlist(NIXL_INIT_AGENT, l, side_l) != NIXL_SUCCESS || ini.prepXferDlist(remote_name, r, side_r) != NIXL_SUCCESS) return early(7);
             prep.push_back(us(t0, clk::now()));
         }
         auto create = [&](nixlXferReqH *&h) {
@@ -544,7 +549,7 @@ int main(int argc, char **argv) {
             return st == NIXL_SUCCESS;
         };
         for (auto &s : slots)
-            if (!create(s)) return 7;
+            if (!create(s)) return early(7);
         std::vector<clk::time_point> started(a.depth);
         std::vector<bool> busy(a.depth, false);
         start_line.arrive_and_wait();
