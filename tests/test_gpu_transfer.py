@@ -148,14 +148,19 @@ def test_notification_reaches_the_target_without_the_initiator_polling():
     datagram leaves only when the initiator's host has seen the completion word."""
     for ring in (True, False):
         a, b = _pair(f"nr{int(ring)}", {"notif_ring": "true" if ring else "false"})
-        src = torch.full((1 << 29,), 9, dtype=torch.uint8, device="cuda:0")
+        src = torch.full((1 << 28,), 9, dtype=torch.uint8, device="cuda:0")
         dst = torch.zeros_like(src)
         a.register_memory(src)
         b.register_memory(dst)
         _connect(a, b)
         torch.cuda.synchronize()
         h = a.initialize_xfer("WRITE", src, dst, b.name, b"landed")
-        assert a.transfer(h) == "PROC"  # 512 MiB: still running when the post returns
+        # Posted on a stream that is busy for a few milliseconds: the copy cannot be complete when the post returns,
+        # whatever the host does in between.
+        stream = torch.cuda.Stream()
+        with torch.cuda.stream(stream):
+            torch.cuda._sleep(20_000_000)
+            assert a.transfer(h, custom_param=f"stream={stream.cuda_stream}") == "PROC"
         if ring:
             assert _poll_notifs(b, a.name, 5.0) == [b"landed"]
             assert int(dst[-4096:].min()) == 9 and int(dst[:4096].min()) == 9  # the data was complete before the notification
