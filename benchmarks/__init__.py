@@ -1,0 +1,1 @@
+"""Benchmark drivers (`python -m benchmarks.kvbench ...`, `python benchmarks/<name>.py`)."""

@@ -240,3 +240,15 @@ def test_reference_import_names_resolve_to_this_package():
     assert nixl_ep.Buffer is nixl_b200.parallel.Buffer and hasattr(nixl_ep, "EventOverlap")
     agent = nixl_agent("via_reference_names", nixl_agent_config(backends=[]))
     assert "NVLINK" in agent.get_plugin_list()
+
+
+def test_utils_package_reads_measured_peaks(tmp_path):
+    from nixl_b200 import utils
+
+    peaks = tmp_path / "peaks.json"
+    peaks.write_text('{"hbm_gbs": 6547.2, "bf16_tflops": 1641.0}')
+    assert utils.measured_peaks(str(peaks))["hbm_gbs"] == 6547.2
+    assert utils.measured_peaks(str(tmp_path / "absent.json")) == {}
+    peaks.write_text("not json")
+    assert utils.measured_peaks(str(peaks)) == {}
+    assert utils.malloc_passthru is not None and utils.verify_transfer is not None
