@@ -393,3 +393,200 @@ def test_capi_query_mem_and_partial_metadata(tmp_path):
         ok(c.nixl_capi_destroy_backend(h))
     for h in (b, d):
         ok(c.nixl_capi_destroy_agent(h))
+
+
+class _AgentConfig(ctypes.Structure):
+    _fields_ = [("enable_prog_thread", ctypes.c_bool), ("enable_listen_thread", ctypes.c_bool), ("listen_port", ctypes.c_int),
+                ("thread_sync", ctypes.c_int), ("num_workers", ctypes.c_uint), ("pthr_delay_us", ctypes.c_uint64),
+                ("lthr_delay_us", ctypes.c_uint64), ("capture_telemetry", ctypes.c_bool)]
+
+
+class _Telemetry(ctypes.Structure):
+    _fields_ = [("start_time_us", ctypes.c_uint64), ("post_duration_us", ctypes.c_uint64), ("xfer_duration_us", ctypes.c_uint64),
+                ("total_bytes", ctypes.c_uint64), ("desc_count", ctypes.c_uint64)]
+
+
+def _free_port():
+    import socket
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def test_capi_list_editing_remote_lists_and_memory_views():
+    """The editing calls of both descriptor-list kinds, the remote list, and the memory-view calls (which need a GPU
+    backend: on a host-only agent they must answer with an error, not crash)."""
+    for kind in ("xfer", "reg"):
+        f = lambda name: getattr(c, f"nixl_capi_{kind}_dlist_{name}")  # noqa: E731
+        dl = VP()
+        ok(getattr(c, f"nixl_capi_create_{kind}_dlist")(0, ctypes.byref(dl)))
+        empty, n, mt = ctypes.c_bool(), ctypes.c_size_t(), ctypes.c_int(-1)
+        ok(f("is_empty")(dl, ctypes.byref(empty)))
+        ok(f("get_type")(dl, ctypes.byref(mt)))
+        assert empty.value and mt.value == 0
+        for i in range(5):
+            if kind == "xfer":
+                ok(f("add_desc")(dl, ctypes.c_size_t(0x1000 * (i + 1)), ctypes.c_size_t(256), ctypes.c_uint64(0)))
+            else:
+                ok(f("add_desc")(dl, ctypes.c_size_t(0x1000 * (i + 1)), ctypes.c_size_t(256), ctypes.c_uint64(0), b"m", ctypes.c_size_t(1)))
+        ok(f("desc_count")(dl, ctypes.byref(n)))
+        assert n.value == 5
+        ok(f("rem_desc")(dl, 1))
+        assert f("rem_desc")(dl, 17) != 0  # no such index
+        ok(f("desc_count")(dl, ctypes.byref(n)))
+        assert n.value == 4
+        ok(f("resize")(dl, ctypes.c_size_t(6)))  # grows with empty descriptors
+        ok(f("desc_count")(dl, ctypes.byref(n)))
+        assert n.value == 6
+        ok(f("trim")(dl))  # drops what is beyond address, length and device; the entries stay
+        ok(f("desc_count")(dl, ctypes.byref(n)))
+        assert n.value == 6
+        ok(f("resize")(dl, ctypes.c_size_t(4)))
+        ok(f("desc_count")(dl, ctypes.byref(n)))
+        assert n.value == 4
+        ok(f("print")(dl))
+        ok(f("clear")(dl))
+        ok(f("is_empty")(dl, ctypes.byref(empty)))
+        assert empty.value
+        ok(getattr(c, f"nixl_capi_destroy_{kind}_dlist")(dl))
+
+    a, ba = _agent(b"capi4_a")
+    buf = np.zeros(4096, dtype=np.uint8)
+    reg = _register(a, buf)
+    local, remote, view = VP(), VP(), VP()
+    ok(c.nixl_capi_create_xfer_dlist(0, ctypes.byref(local)))
+    ok(c.nixl_capi_xfer_dlist_add_desc(local, ctypes.c_size_t(buf.ctypes.data), ctypes.c_size_t(4096), ctypes.c_uint64(0)))
+    ok(c.nixl_capi_create_remote_dlist(0, ctypes.byref(remote)))
+    ok(c.nixl_capi_remote_dlist_add_desc(remote, ctypes.c_size_t(buf.ctypes.data), ctypes.c_size_t(4096), ctypes.c_uint64(0), b"capi4_a"))
+    assert c.nixl_capi_remote_dlist_add_desc(remote, ctypes.c_size_t(0), ctypes.c_size_t(1), ctypes.c_uint64(0), None) != 0
+    rc = c.nixl_capi_prep_mem_view_local(a, local, ctypes.byref(view), None)
+    if rc == 0:  # a GPU is present: the view exists and can be released
+        ok(c.nixl_capi_release_mem_view(a, view))
+        ok(c.nixl_capi_prep_mem_view_remote(a, remote, ctypes.byref(view), None))
+        ok(c.nixl_capi_release_mem_view(a, view))
+    else:
+        assert c.nixl_capi_prep_mem_view_remote(a, remote, ctypes.byref(view), None) != 0
+    assert c.nixl_capi_release_mem_view(a, None) != 0
+    ok(c.nixl_capi_destroy_remote_dlist(remote))
+    ok(c.nixl_capi_destroy_xfer_dlist(local))
+    ok(c.nixl_capi_deregister_mem(a, reg, None))
+    ok(c.nixl_capi_destroy_reg_dlist(reg))
+    ok(c.nixl_capi_destroy_backend(ba))
+    ok(c.nixl_capi_destroy_agent(a))
+
+
+def test_capi_configured_agents_exchange_metadata_over_the_socket_and_report_telemetry():
+    """Agents built from a configuration block (listener thread, telemetry capture): metadata pushed and fetched
+    through the peer-to-peer socket, per-request telemetry, and the invalidation of what was pushed."""
+    os.environ["NIXL_TELEMETRY_ENABLE"] = "y"
+    try:
+        port_a, port_b = _free_port(), _free_port()
+        agents = []
+        for name, port in ((b"capi5_a", port_a), (b"capi5_b", port_b)):
+            cfg = _AgentConfig(False, True, port, 2, 1, 0, 1000, True)
+            h, params, mems, bh = VP(), VP(), VP(), VP()
+            ok(c.nixl_capi_create_configured_agent(name, ctypes.byref(cfg), ctypes.byref(h)))
+            ok(c.nixl_capi_get_plugin_params(h, b"NVLINK", ctypes.byref(mems), ctypes.byref(params)))
+            ok(c.nixl_capi_create_backend(h, b"NVLINK", params, ctypes.byref(bh)))
+            ok(c.nixl_capi_destroy_params(params))
+            ok(c.nixl_capi_destroy_mem_list(mems))
+            agents.append((h, bh))
+        (a, ba), (b, bb) = agents
+        assert c.nixl_capi_create_configured_agent(b"nobody", None, ctypes.byref(VP())) != 0
+        mine = np.arange(8192, dtype=np.uint8)
+        theirs = np.zeros(8192, dtype=np.uint8)
+        reg_a, reg_b = _register(a, mine), _register(b, theirs)
+
+        to_b, to_a = VP(), VP()
+        ok(c.nixl_capi_create_opt_args(ctypes.byref(to_b)))
+        ok(c.nixl_capi_opt_args_set_ip_addr(to_b, b"127.0.0.1"))
+        ok(c.nixl_capi_opt_args_set_port(to_b, ctypes.c_uint16(port_b)))
+        ok(c.nixl_capi_create_opt_args(ctypes.byref(to_a)))
+        ok(c.nixl_capi_opt_args_set_ip_addr(to_a, b"127.0.0.1"))
+        ok(c.nixl_capi_opt_args_set_port(to_a, ctypes.c_uint16(port_a)))
+
+        def loaded(agent, name):
+            for _ in range(2000):
+                if c.nixl_capi_check_remote_md(agent, name, None) == 0:
+                    return True
+                import time
+                time.sleep(0.005)
+            return False
+
+        ok(c.nixl_capi_send_local_md(b, to_a))            # b pushes its metadata to a's listener
+        assert loaded(a, b"capi5_b")
+        ok(c.nixl_capi_fetch_remote_md(b, b"capi5_a", to_a))  # b asks a's listener for a's metadata
+        assert loaded(b, b"capi5_a")
+
+        local, remote, req = VP(), VP(), VP()
+        ok(c.nixl_capi_create_xfer_dlist(0, ctypes.byref(local)))
+        ok(c.nixl_capi_create_xfer_dlist(0, ctypes.byref(remote)))
+        for i in range(2):
+            ok(c.nixl_capi_xfer_dlist_add_desc(local, ctypes.c_size_t(mine.ctypes.data + i * 4096), ctypes.c_size_t(4096), ctypes.c_uint64(0)))
+            ok(c.nixl_capi_xfer_dlist_add_desc(remote, ctypes.c_size_t(theirs.ctypes.data + (1 - i) * 4096), ctypes.c_size_t(4096), ctypes.c_uint64(0)))
+        ok(c.nixl_capi_create_xfer_req(a, 1, local, remote, b"capi5_b", ctypes.byref(req), None))  # WRITE
+        rc = c.nixl_capi_post_xfer_req(a, req, None)
+        while rc == 1:
+            rc = c.nixl_capi_get_xfer_status(a, req)
+        assert rc == 0
+        assert (theirs[4096:] == mine[:4096]).all() and (theirs[:4096] == mine[4096:]).all()
+        t = _Telemetry()
+        ok(c.nixl_capi_get_xfer_telemetry(a, req, ctypes.byref(t)))
+        assert t.total_bytes == 8192 and t.desc_count == 2 and t.start_time_us > 0
+        assert c.nixl_capi_get_xfer_telemetry(a, req, None) != 0
+        ok(c.nixl_capi_release_xfer_req(a, req))
+        ok(c.nixl_capi_destroy_xfer_req(req))
+
+        # a later registration travels as partial metadata; then b withdraws what it pushed
+        extra = np.zeros(4096, dtype=np.uint8)
+        reg_x = _register(b, extra)
+        ok(c.nixl_capi_send_local_partial_md(b, reg_x, to_a))
+        probe = VP()
+        ok(c.nixl_capi_create_xfer_dlist(0, ctypes.byref(probe)))
+        ok(c.nixl_capi_xfer_dlist_add_desc(probe, ctypes.c_size_t(extra.ctypes.data), ctypes.c_size_t(4096), ctypes.c_uint64(0)))
+        for _ in range(2000):
+            if c.nixl_capi_check_remote_md(a, b"capi5_b", probe) == 0:
+                break
+            import time
+            time.sleep(0.005)
+        assert c.nixl_capi_check_remote_md(a, b"capi5_b", probe) == 0
+        ok(c.nixl_capi_invalidate_local_md(b, to_a))
+        for _ in range(2000):
+            if c.nixl_capi_check_remote_md(a, b"capi5_b", None) != 0:
+                break
+            import time
+            time.sleep(0.005)
+        assert c.nixl_capi_check_remote_md(a, b"capi5_b", None) != 0  # a forgot b
+
+        ok(c.nixl_capi_destroy_xfer_dlist(probe))
+        ok(c.nixl_capi_destroy_xfer_dlist(local))
+        ok(c.nixl_capi_destroy_xfer_dlist(remote))
+        ok(c.nixl_capi_destroy_opt_args(to_a))
+        ok(c.nixl_capi_destroy_opt_args(to_b))
+        for agent, reg in ((a, reg_a), (b, reg_b), (b, reg_x)):
+            ok(c.nixl_capi_deregister_mem(agent, reg, None))
+            ok(c.nixl_capi_destroy_reg_dlist(reg))
+        for h in (ba, bb):
+            ok(c.nixl_capi_destroy_backend(h))
+        for h in (a, b):
+            ok(c.nixl_capi_destroy_agent(h))
+    finally:
+        os.environ.pop("NIXL_TELEMETRY_ENABLE", None)
+
+
+def test_every_function_of_the_header_is_exported_and_exercised():
+    import re
+
+    header = open(os.path.join(os.path.dirname(LIB), "..", "..", "csrc", "include", "nixl_capi.h")).read()
+    names = sorted(set(re.findall(r"\b(nixl_capi_[a-z0-9_]+)\s*\(", header)))
+    assert len(names) >= 100
+    assert [n for n in names if not hasattr(c, n)] == []
+    me = open(__file__).read()
+    def touched(name):
+        if name in me:
+            return True
+        m = re.fullmatch(r"nixl_capi_(?:xfer|reg)_dlist_([a-z_]+)", name)  # the editing calls are looked up as f("<op>") for both kinds
+        return bool(m) and f'f("{m.group(1)}")' in me
+
+    untouched = [n for n in names if not touched(n)]
+    assert untouched == [], untouched
