@@ -252,3 +252,19 @@ def test_utils_package_reads_measured_peaks(tmp_path):
     peaks.write_text("not json")
     assert utils.measured_peaks(str(peaks)) == {}
     assert utils.malloc_passthru is not None and utils.verify_transfer is not None
+
+
+def test_agent_has_every_public_method_of_the_reference_wrapper():
+    """The method names of the reference's ``nixl_agent`` (src/api/python/_api.py), as a fixed list."""
+    from nixl_b200 import nixl_agent
+
+    expected = """add_remote_agent check_remote_metadata check_remote_xfer_done check_xfer_state create_backend deregister_memory
+    deserialize_descs estimate_xfer_cost fetch_remote_metadata get_agent_metadata get_backend_mem_types get_backend_params
+    get_new_notifs get_partial_agent_metadata get_plugin_list get_plugin_mem_types get_plugin_params get_reg_descs
+    get_remote_descs get_serialized_descs get_xfer_descs get_xfer_telemetry initialize_xfer invalidate_local_metadata
+    make_connection make_prepped_xfer prep_mem_view prep_xfer_dlist query_memory query_xfer_backend register_memory
+    release_dlist_handle release_mem_view release_xfer_handle remove_remote_agent send_local_metadata send_notif
+    send_partial_agent_metadata transfer update_notifs""".split()
+    assert len(expected) == 40
+    missing = [name for name in expected if not callable(getattr(nixl_agent, name, None))]
+    assert missing == []
