@@ -233,6 +233,12 @@ class Buffer:
 
     # ------------------------------------------------------------------ reference-named utilities
 
+    @staticmethod
+    def is_sm90_compiled() -> bool:
+        """The reference's flag for "the kernels were built with the features of sm_90 and later" (its callers use
+        it to decide whether the fp8 and bulk-copy paths exist).  This library is built for sm_100a only and has them."""
+        return True
+
     def set_tcp_store_group(self, store) -> None:
         """Use a ``torch.distributed`` store (e.g. ``TCPStore``) for the metadata exchange of ``connect_ranks``
         instead of a collective: ranks may then join at different times (elastic set-ups)."""

@@ -268,3 +268,19 @@ def test_agent_has_every_public_method_of_the_reference_wrapper():
     assert len(expected) == 40
     missing = [name for name in expected if not callable(getattr(nixl_agent, name, None))]
     assert missing == []
+
+
+def test_ep_buffer_has_every_public_method_of_the_reference_buffer():
+    """The method names of the reference's ``nixl_ep.Buffer`` (examples/device/ep/nixl_ep/buffer.py), as a fixed list."""
+    from nixl_b200.parallel import Buffer
+
+    expected = """barrier capture clean_mask_buffer combine connect_ranks destroy disconnect_ranks dispatch get_combine_config
+    get_comm_stream get_dispatch_config get_dispatch_layout get_local_buffer_tensor get_low_latency_buffer_size_hint
+    get_next_combine_buffer get_rdma_size_hint ht_combine ht_dispatch is_sm90_compiled low_latency_combine low_latency_dispatch
+    query_mask_buffer set_num_sms set_tcp_store_group update_mask_buffer update_memory_buffers""".split()
+    assert len(expected) == 26
+    assert [name for name in expected if not hasattr(Buffer, name)] == []
+    assert Buffer.is_sm90_compiled() is True
+    import nixl_ep
+
+    assert nixl_ep.Buffer is Buffer
