@@ -823,8 +823,14 @@ void Engine::destroyReq(ReqH *req) const {
                     }
                 }
                 if (!done) {
+                    NIXL_ERROR << "NVLINK backend: a released request's copy on GPU " << b.device << " did not complete within 10 s ("
+                               << (b.viaProxy ? "doorbell proxy" : "copy kernel") << "); waiting for the whole device";
                     DeviceScope ds(b.device);
-                    if (cudaDeviceSynchronize() != cudaSuccess) cudaGetLastError();
+                    const cudaError_t e = cudaDeviceSynchronize();
+                    if (e != cudaSuccess) {
+                        NIXL_ERROR << "NVLINK backend: cudaDeviceSynchronize: " << cudaGetErrorString(e);
+                        cudaGetLastError();
+                    }
                 }
                 b.inFlight = false;
             }
