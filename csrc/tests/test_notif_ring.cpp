@@ -3,6 +3,9 @@
 #include <sys/wait.h>
 #include <unistd.h>
 
+#include <algorithm>
+#include <atomic>
+#include <chrono>
 #include <cstring>
 #include <thread>
 
@@ -127,6 +130,65 @@ TEST_CASE(another_process_writes_and_a_claimant_that_died_does_not_hold_the_ring
     }
     CHECK(owner.outstanding() == 0);
     CHECK(got.size() == 1);
+}
+
+TEST_CASE(several_writers_and_one_reader_deliver_every_message_exactly_once) {
+    // The writers are threads of a child process (a second mapping of the ring in the reader's own process would
+    // hide the synchronisation from a race detector, which goes by virtual address).
+    NotifRingOwner owner;
+    CHECK(owner.create(ringName("g")));
+    const std::string name = owner.name();
+    constexpr int kWriters = 4, kEach = 3000; // 12000 messages through 1024 slots: the ring wraps many times
+    const pid_t child = ::fork();
+    if (child == 0) {
+        auto w = NotifRingWriter::open(name);
+        if (!w) ::_exit(2);
+        std::vector<std::thread> writers;
+        for (int t = 0; t < kWriters; ++t)
+            writers.emplace_back([&, t] {
+                for (int i = 0; i < kEach; ++i) {
+                    uint64_t *word = nullptr, seq = 0;
+                    const std::string msg = std::to_string(t) + ":" + std::to_string(i);
+                    while (!w->claim("writer" + std::to_string(t), msg, &word, &seq)) std::this_thread::yield(); // full: the reader is behind
+                    if (i % 7 == 3) std::this_thread::yield(); // some claims complete late, out of order
+                    NotifRingWriter::complete(word, seq, i % 11 != 5); // and some are voided
+                }
+            });
+        for (auto &t : writers) t.join();
+        ::_exit(0);
+    }
+    std::vector<std::vector<int>> seen(kWriters);
+    size_t total = 0, expected = 0;
+    for (int i = 0; i < kEach; ++i) expected += i % 11 != 5;
+    expected *= kWriters;
+    const auto end = std::chrono::steady_clock::now() + std::chrono::seconds(60);
+    while (total < expected && std::chrono::steady_clock::now() < end) {
+        NotifList got;
+        owner.poll(got);
+        for (auto &n : got) {
+            const int t = n.first.back() - '0';
+            CHECK(t >= 0 && t < kWriters && n.first == "writer" + std::to_string(t));
+            const size_t colon = n.second.find(':');
+            CHECK(colon != std::string::npos && std::stoi(n.second.substr(0, colon)) == t);
+            seen[t].push_back(std::stoi(n.second.substr(colon + 1)));
+            ++total;
+        }
+    }
+    int status = 0;
+    CHECK(::waitpid(child, &status, 0) == child);
+    CHECK(WIFEXITED(status) && WEXITSTATUS(status) == 0);
+    NotifList rest;
+    owner.poll(rest);
+    CHECK(rest.empty());
+    CHECK_EQ(total, expected);
+    CHECK_EQ(owner.outstanding(), uint64_t(0));
+    for (int t = 0; t < kWriters; ++t) {
+        std::sort(seen[t].begin(), seen[t].end());
+        CHECK(std::adjacent_find(seen[t].begin(), seen[t].end()) == seen[t].end()); // no duplicates
+        size_t at = 0;
+        for (int i = 0; i < kEach; ++i)
+            if (i % 11 != 5) CHECK(seen[t][at++] == i);
+    }
 }
 
 TEST_CASE(rings_left_by_dead_processes_are_removed_by_the_next_owner) {
