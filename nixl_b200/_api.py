@@ -136,19 +136,23 @@ class nixl_xfer_handle(int):
         if self._released:
             return
         st = self._owner.agent.releaseXferReq(int(self))
-        if st != nixlBind.NIXL_SUCCESS:
+        if st != 0:  # NIXL_SUCCESS; the literal, not the module constant: this also runs while the interpreter shuts down
             raise _error_for(st, "releaseXferReq")
         self._released = True
 
     def __del__(self):
+        # Runs at any time, also during interpreter shutdown when module globals are already gone: nothing here
+        # may fail AFTER the native release succeeded, or the handle would be parked and released a second time.
         if self._released:
             return
+        self._released = True
         try:
-            self.release()
+            refused = self._owner.agent.releaseXferReq(int(self)) != 0
         except Exception:
+            refused = True  # the call raises when the backend cannot let go yet: nothing was freed
+        if refused:
             try:
                 self._owner._leaked_xfer_handles.append(int(self))
-                self._released = True
             except Exception:
                 pass
 

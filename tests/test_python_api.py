@@ -284,3 +284,38 @@ def test_ep_buffer_has_every_public_method_of_the_reference_buffer():
     import nixl_ep
 
     assert nixl_ep.Buffer is Buffer
+
+
+def test_interpreter_exit_with_unreleased_handles_is_clean():
+    """Handles, registration descriptors and agents left alive at exit are collected in arbitrary order while module
+    globals disappear; a transfer handle must be released exactly once whatever that order is."""
+    import os
+    import subprocess
+    import sys
+    import textwrap
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = textwrap.dedent("""
+        import numpy as np, nixl_b200, os
+        from nixl._api import nixl_agent, nixl_agent_config
+        cfg = nixl_agent_config(enable_prog_thread=False, backends=["NVLINK"])
+        a, b = nixl_agent("exit_a", cfg), nixl_agent("exit_b", cfg)
+        src = np.arange(65536, dtype=np.uint8); dst = np.zeros_like(src)
+        ra = a.register_memory([(src.ctypes.data, src.nbytes, 0, "")], "DRAM")
+        rb = b.register_memory([(dst.ctypes.data, dst.nbytes, 0, "")], "DRAM")
+        a.add_remote_agent(b.get_agent_metadata())
+        hs = []
+        for i in range(3):
+            h = a.initialize_xfer("WRITE", a.get_xfer_descs([(src.ctypes.data, src.nbytes, 0)], "DRAM"),
+                                  a.get_xfer_descs([(dst.ctypes.data, dst.nbytes, 0)], "DRAM"), "exit_b", b"hi")
+            st = a.transfer(h)
+            while st == "PROC":
+                st = a.check_xfer_state(h)
+            hs.append(h)
+        side = a.prep_xfer_dlist("NIXL_INIT_AGENT", [(src.ctypes.data, 4096, 0)], "DRAM")
+        assert (src == dst).all()
+        print("ok")
+    """)
+    for _ in range(3):
+        res = subprocess.run([sys.executable, "-c", script], capture_output=True, text=True, cwd="/", env={**os.environ, "PYTHONPATH": root})
+        assert res.returncode == 0 and res.stdout.strip() == "ok", (res.returncode, res.stderr[-500:])
