@@ -157,6 +157,14 @@ class nixl_xfer_handle(int):
                 pass
 
 
+def _live(handle, what: str) -> int:
+    """The native value of a handle; a handle object that was released already is refused here, in Python (its native
+    object is gone, and passing the stale value on would be a use after free)."""
+    if getattr(handle, "_released", False):
+        raise nixlBind.nixlInvalidParamError(f"{what}: the handle was released")
+    return int(handle)
+
+
 def _is_tensor(x: Any) -> bool:
     return torch is not None and isinstance(x, torch.Tensor)
 
@@ -371,7 +379,7 @@ class nixl_agent:
 
     def estimate_xfer_cost(self, req_handle: int) -> tuple[int, int, int]:
         """(duration_us, error_margin_us, method)."""
-        return self.agent.estimateXferCost(req_handle)
+        return self.agent.estimateXferCost(_live(req_handle, "estimate_xfer_cost"))
 
     def make_prepped_xfer(
         self,
@@ -386,9 +394,9 @@ class nixl_agent:
     ) -> nixl_xfer_handle:
         return nixl_xfer_handle(self, self.agent.makeXferReq(
             _OPS[operation],
-            int(local_xfer_side),
+            _live(local_xfer_side, "make_prepped_xfer (local side)"),
             local_indices,
-            int(remote_xfer_side),
+            _live(remote_xfer_side, "make_prepped_xfer (remote side)"),
             remote_indices,
             notif_msg if notif_msg else None,
             self._handles(backends),
@@ -416,23 +424,23 @@ class nixl_agent:
     def transfer(self, handle: int, notif_msg: Union[bytes, str] = b"", custom_param: str = "") -> str:
         """Post the transfer. Returns "DONE", "PROC" or "ERR"."""
         try:
-            st = self.agent.postXferReq(handle, notif_msg if notif_msg else None, custom_param)
+            st = self.agent.postXferReq(_live(handle, "transfer"), notif_msg if notif_msg else None, custom_param)
         except nixlBind.nixlError:
             return "ERR"
         return "DONE" if st == nixlBind.NIXL_SUCCESS else "PROC"
 
     def check_xfer_state(self, handle: int) -> str:
         try:
-            st = self.agent.getXferStatus(handle)
+            st = self.agent.getXferStatus(_live(handle, "check_xfer_state"))
         except nixlBind.nixlError:
             return "ERR"
         return "DONE" if st == nixlBind.NIXL_SUCCESS else "PROC"
 
     def get_xfer_telemetry(self, handle: int):
-        return self.agent.getXferTelemetry(handle)
+        return self.agent.getXferTelemetry(_live(handle, "get_xfer_telemetry"))
 
     def query_xfer_backend(self, handle: int) -> str:
-        b = self.agent.queryXferBackend(handle)
+        b = self.agent.queryXferBackend(_live(handle, "query_xfer_backend"))
         for name, h in self.backends.items():
             if h == b:
                 return name

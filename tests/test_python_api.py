@@ -319,3 +319,28 @@ def test_interpreter_exit_with_unreleased_handles_is_clean():
     for _ in range(3):
         res = subprocess.run([sys.executable, "-c", script], capture_output=True, text=True, cwd="/", env={**os.environ, "PYTHONPATH": root})
         assert res.returncode == 0 and res.stdout.strip() == "ok", (res.returncode, res.stderr[-500:])
+
+
+def test_released_handles_are_refused_in_python(pair):
+    """A handle object remembers that it was released: using it again raises instead of handing a dangling native
+    pointer to the library."""
+    a, b = pair
+    src, dst = np.arange(8192, dtype=np.uint8), np.zeros(8192, dtype=np.uint8)
+    a.register_memory([(src.ctypes.data, src.nbytes, 0, "")], "DRAM")
+    b.register_memory([(dst.ctypes.data, dst.nbytes, 0, "")], "DRAM")
+    a.add_remote_agent(b.get_agent_metadata())
+    h = a.initialize_xfer("WRITE", a.get_xfer_descs([(src.ctypes.data, 4096, 0)], "DRAM"), a.get_xfer_descs([(dst.ctypes.data, 4096, 0)], "DRAM"), b.name)
+    assert a.transfer(h) in ("DONE", "PROC")
+    assert _wait(a, h) == "DONE"
+    a.release_xfer_handle(h)
+    a.release_xfer_handle(h)  # releasing twice is harmless
+    assert a.transfer(h) == "ERR" and a.check_xfer_state(h) == "ERR"  # refused before anything native runs
+    for call in (lambda: a.estimate_xfer_cost(h), lambda: a.query_xfer_backend(h), lambda: a.get_xfer_telemetry(h)):
+        with pytest.raises(nixl_b200._bindings.nixlInvalidParamError):
+            call()
+    side_l = a.prep_xfer_dlist("NIXL_INIT_AGENT", [(src.ctypes.data, 4096, 0)], "DRAM")
+    side_r = a.prep_xfer_dlist(b.name, [(dst.ctypes.data, 4096, 0)], "DRAM")
+    a.release_dlist_handle(side_r)
+    with pytest.raises(nixl_b200._bindings.nixlInvalidParamError):
+        a.make_prepped_xfer("WRITE", side_l, [0], side_r, [0])
+    a.release_dlist_handle(side_l)
