@@ -3,6 +3,9 @@
 Scenarios follow the reference's test/gtest/test_transfer.cpp (VRAM and DRAM, WRITE and
 READ, notifications, batches) plus what is new here: the table path for large batches,
 odd sizes and offsets, the bulk (TMA) copy path and stream-ordered posting."""
+import glob
+import os
+
 import pytest
 import torch
 
@@ -147,7 +150,12 @@ def test_notification_reaches_the_target_without_the_initiator_polling():
     the finished WRITE although the initiator never looks at its request again.  Without the ring the
     datagram leaves only when the initiator's host has seen the completion word."""
     for ring in (True, False):
+        before = set(glob.glob(f"/dev/shm/nixl_b200.{os.getpid()}.*"))
         a, b = _pair(f"nr{int(ring)}", {"notif_ring": "true" if ring else "false"})
+        rings = set(glob.glob(f"/dev/shm/nixl_b200.{os.getpid()}.*")) - before
+        if ring and len(rings) < 2:
+            pytest.skip("this box gives the engines no shared-memory ring (no room in /dev/shm?): notifications use datagrams")
+        assert ring or not rings
         src = torch.full((1 << 28,), 9, dtype=torch.uint8, device="cuda:0")
         dst = torch.zeros_like(src)
         a.register_memory(src)
