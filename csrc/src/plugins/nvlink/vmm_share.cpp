@@ -274,6 +274,7 @@ void VmmFdServer::loop() {
             msg.msg_control = control;
             msg.msg_controllen = CMSG_SPACE(sizeof(int) * rep.count);
             cmsghdr *c = CMSG_FIRSTHDR(&msg);
+            if (c == nullptr) continue; // cannot happen with the control length above; keeps the header access provably safe
             c->cmsg_level = SOL_SOCKET;
             c->cmsg_type = SCM_RIGHTS;
             c->cmsg_len = CMSG_LEN(sizeof(int) * rep.count);
