@@ -26,6 +26,11 @@ namespace {
 using nixl_util::hostName;
 using nixl_util::random64;
 
+// Words in pinned host memory that a GPU (or the doorbell proxy) writes with release semantics at system scope and
+// this side polls: read them with an acquire load, so that everything the writer did before is visible afterwards.
+inline uint64_t loadWord(const uint64_t *p) { return __atomic_load_n(p, __ATOMIC_ACQUIRE); }
+inline void storeWord(uint64_t *p, uint64_t v) { __atomic_store_n(p, v, __ATOMIC_RELEASE); }
+
 uint64_t processTag() {
     static const uint64_t tag = random64() | 1;
     return tag;
@@ -812,7 +817,7 @@ void Engine::destroyReq(ReqH *req) const {
                 const auto t0 = std::chrono::steady_clock::now();
                 bool done = false;
                 for (uint32_t spins = 0;; ++spins) {
-                    const uint64_t v = *reinterpret_cast<volatile uint64_t *>(b.flag);
+                    const uint64_t v = loadWord(b.flag);
                     if (b.viaProxy ? proxyDone(nullptr, b) != 0 : (v & 0x7fffffffffffffffull) == b.seq) {
                         done = true;
                         break;
@@ -1045,13 +1050,13 @@ nixl_status_t Engine::prepXfer(const nixl_xfer_op_t &operation, const nixl_meta_
 void Engine::proxyEnsureRunning(DeviceCtx *c, Proxy &px) const {
     if (px.broken) return;
     if (px.launched) {
-        const uint64_t w = *reinterpret_cast<volatile uint64_t *>(px.exitWord);
+        const uint64_t w = loadWord(px.exitWord);
         if (w == 0) return;
         px.launched = false;
         px.nextStart = w & ~(1ull << 63);
     }
     if (px.nextStart >= px.posted) return; // nothing pending
-    *reinterpret_cast<volatile uint64_t *>(px.exitWord) = 0;
+    storeWord(px.exitWord, 0);
     ProxyLaunch pl{};
     pl.hostRing = px.hostRing;
     pl.shared = px.shared;
@@ -1109,7 +1114,7 @@ bool Engine::postViaProxy(DeviceCtx *c, KernelBatch &b) const {
     const uint64_t n = px.posted;
     const uint32_t slot = static_cast<uint32_t>(n % kProxySlots);
     // The slot's previous command (one ring ago) must be complete: its workers are past it.
-    if (n >= kProxySlots && *reinterpret_cast<volatile uint64_t *>(px.done + slot) < n - kProxySlots + 1) return false;
+    if (n >= kProxySlots && loadWord(px.done + slot) < n - kProxySlots + 1) return false;
     ProxyCmd *h = px.hostRing + slot;
     if (b.launch.nDescs == 1) {
         h->b = b.single.dst;
@@ -1132,14 +1137,14 @@ bool Engine::postViaProxy(DeviceCtx *c, KernelBatch &b) const {
 
 int Engine::proxyDone(DeviceCtx *c, KernelBatch &b) const {
     Proxy &px = *b.proxy;
-    const uint64_t v = *reinterpret_cast<volatile uint64_t *>(px.done + (b.proxyCmd % kProxySlots));
+    const uint64_t v = loadWord(px.done + (b.proxyCmd % kProxySlots));
     if (v >= b.proxyCmd + 1) {
         std::atomic_thread_fence(std::memory_order_acquire);
         return 1;
     }
     if (px.broken.load(std::memory_order_relaxed)) return -1;
     // Not done: if the kernel has left (idle or end of life) with this command pending, start it again.
-    if (*reinterpret_cast<volatile uint64_t *>(px.exitWord) != 0) {
+    if (loadWord(px.exitWord) != 0) {
         if (!c) c = ctx(b.device);
         std::lock_guard<std::mutex> g(px.mu);
         proxyEnsureRunning(c, px);
@@ -1341,7 +1346,7 @@ nixl_status_t Engine::pollData(ReqH *req) const {
             }
             continue;
         }
-        const uint64_t v = *reinterpret_cast<volatile uint64_t *>(b.flag);
+        const uint64_t v = loadWord(b.flag);
         if ((v & 0x7fffffffffffffffull) != b.seq) return NIXL_IN_PROG;
         b.inFlight = false;
         if (v >> 63) {

@@ -1,0 +1,487 @@
+// The stand-in CUDA runtime (contract: cuda_runtime.h beside this file).
+#include "cuda_runtime.h"
+
+#include <algorithm>
+#include <atomic>
+#include <chrono>
+#include <condition_variable>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <deque>
+#include <map>
+#include <memory>
+#include <mutex>
+#include <thread>
+#include <vector>
+
+#include <unistd.h>
+
+// ---------------------------------------------------------------- streams and events
+
+struct FakeCudaStream {
+    int device = 0;
+    std::mutex mu;
+    std::condition_variable cv, idleCv;
+    std::deque<std::function<void()>> tasks;
+    bool busy = false, stop = false;
+    std::thread worker;
+
+    explicit FakeCudaStream(int dev) : device(dev) {
+        worker = std::thread([this] { run(); });
+    }
+    ~FakeCudaStream() {
+        {
+            std::lock_guard<std::mutex> g(mu);
+            stop = true;
+        }
+        cv.notify_all();
+        worker.join();
+    }
+    void push(std::function<void()> t) {
+        {
+            std::lock_guard<std::mutex> g(mu);
+            tasks.push_back(std::move(t));
+        }
+        cv.notify_one();
+    }
+    void drain() {
+        std::unique_lock<std::mutex> lk(mu);
+        idleCv.wait(lk, [this] { return tasks.empty() && !busy; });
+    }
+    void run();
+};
+
+struct FakeCudaEvent {
+    std::mutex mu;
+    std::condition_variable cv;
+    uint64_t recorded = 0;  // times cudaEventRecord was called
+    uint64_t completed = 0; // records whose marker has run
+};
+
+namespace {
+
+std::atomic<uint64_t> g_tasksRun{0};
+thread_local int t_device = 0;
+thread_local cudaError_t t_lastError = cudaSuccess;
+
+cudaError_t fail(cudaError_t e) {
+    t_lastError = e;
+    return e;
+}
+
+struct Allocation {
+    size_t size;
+    int device;
+};
+struct HostRange {
+    size_t size;
+    bool ours; // cudaHostAlloc (freed by cudaFreeHost) or cudaHostRegister
+};
+
+struct Runtime {
+    std::mutex mu;
+    int devices = 2;
+    std::map<uintptr_t, Allocation> device; // base -> allocation
+    std::map<uintptr_t, HostRange> pinned;  // base -> range
+    std::vector<std::unique_ptr<FakeCudaStream>> defaults;
+    std::vector<FakeCudaStream *> streams; // every live stream (default ones included)
+    std::map<std::pair<int, int>, bool> peer;
+
+    Runtime() {
+        if (const char *e = std::getenv("FAKE_CUDA_DEVICES")) devices = std::max(0, std::atoi(e));
+        for (int d = 0; d < devices; ++d) {
+            defaults.push_back(std::make_unique<FakeCudaStream>(d));
+            streams.push_back(defaults.back().get());
+        }
+    }
+    ~Runtime() {
+        // Streams the program never destroyed: let their workers finish what is queued.
+        for (auto &s : defaults) s->drain();
+    }
+    const Allocation *findDevice(uintptr_t p, uintptr_t *base = nullptr) {
+        auto it = device.upper_bound(p);
+        if (it == device.begin()) return nullptr;
+        --it;
+        if (p >= it->first + it->second.size) return nullptr;
+        if (base) *base = it->first;
+        return &it->second;
+    }
+    bool isPinned(uintptr_t p) {
+        auto it = pinned.upper_bound(p);
+        if (it == pinned.begin()) return false;
+        --it;
+        return p < it->first + it->second.size;
+    }
+};
+
+Runtime &rt() {
+    static Runtime *r = new Runtime(); // leaked on purpose: worker threads may outlive static destruction
+    return *r;
+}
+
+FakeCudaStream *resolve(cudaStream_t s) {
+    if (s) return s;
+    Runtime &r = rt();
+    if (t_device < 0 || t_device >= r.devices) return nullptr;
+    return r.defaults[t_device].get();
+}
+
+} // namespace
+
+void FakeCudaStream::run() {
+    std::unique_lock<std::mutex> lk(mu);
+    for (;;) {
+        cv.wait(lk, [this] { return stop || !tasks.empty(); });
+        if (tasks.empty()) {
+            if (stop) return;
+            continue;
+        }
+        std::function<void()> t = std::move(tasks.front());
+        tasks.pop_front();
+        busy = true;
+        lk.unlock();
+        t();
+        g_tasksRun.fetch_add(1, std::memory_order_relaxed);
+        lk.lock();
+        busy = false;
+        if (tasks.empty()) idleCv.notify_all();
+    }
+}
+
+namespace fake_cuda {
+void enqueue(cudaStream_t stream, std::function<void()> task) {
+    if (FakeCudaStream *s = resolve(stream)) s->push(std::move(task));
+}
+void enqueueDelay(cudaStream_t stream, unsigned microseconds) {
+    enqueue(stream, [microseconds] { std::this_thread::sleep_for(std::chrono::microseconds(microseconds)); });
+}
+int deviceCount() { return rt().devices; }
+uint64_t tasksRun() { return g_tasksRun.load(); }
+} // namespace fake_cuda
+
+extern "C" {
+
+cudaError_t cudaGetLastError(void) {
+    const cudaError_t e = t_lastError;
+    t_lastError = cudaSuccess;
+    return e;
+}
+cudaError_t cudaPeekAtLastError(void) { return t_lastError; }
+const char *cudaGetErrorString(cudaError_t e) {
+    switch (e) {
+    case cudaSuccess: return "no error";
+    case cudaErrorInvalidValue: return "invalid argument";
+    case cudaErrorMemoryAllocation: return "out of memory";
+    case cudaErrorInvalidDevice: return "invalid device ordinal";
+    case cudaErrorInvalidResourceHandle: return "invalid resource handle";
+    case cudaErrorNotReady: return "device not ready";
+    case cudaErrorPeerAccessAlreadyEnabled: return "peer access is already enabled";
+    case cudaErrorHostMemoryAlreadyRegistered: return "part or all of the requested memory range is already mapped";
+    case cudaErrorHostMemoryNotRegistered: return "pointer does not correspond to a registered memory region";
+    case cudaErrorNotSupported: return "operation not supported";
+    default: return "unknown error";
+    }
+}
+
+cudaError_t cudaGetDeviceCount(int *count) {
+    if (!count) return fail(cudaErrorInvalidValue);
+    *count = rt().devices;
+    return cudaSuccess;
+}
+cudaError_t cudaGetDevice(int *device) {
+    if (!device) return fail(cudaErrorInvalidValue);
+    *device = t_device;
+    return cudaSuccess;
+}
+cudaError_t cudaSetDevice(int device) {
+    if (device < 0 || device >= rt().devices) return fail(cudaErrorInvalidDevice);
+    t_device = device;
+    return cudaSuccess;
+}
+cudaError_t cudaDeviceGetAttribute(int *value, enum cudaDeviceAttr attr, int device) {
+    if (!value || device < 0 || device >= rt().devices) return fail(cudaErrorInvalidValue);
+    if (attr == cudaDevAttrMultiProcessorCount) {
+        *value = 148;
+        return cudaSuccess;
+    }
+    return fail(cudaErrorInvalidValue);
+}
+cudaError_t cudaGetDeviceProperties(struct cudaDeviceProp *prop, int device) {
+    if (!prop || device < 0 || device >= rt().devices) return fail(cudaErrorInvalidDevice);
+    std::memset(prop, 0, sizeof(*prop));
+    std::snprintf(prop->name, sizeof(prop->name), "stand-in GPU %d", device);
+    std::memset(prop->uuid.bytes, 0xa0 + device, sizeof(prop->uuid.bytes));
+    prop->uuid.bytes[0] = static_cast<char>(device);
+    prop->totalGlobalMem = size_t(16) << 30;
+    prop->multiProcessorCount = 148;
+    prop->major = 10;
+    prop->pciBusID = device + 1;
+    return cudaSuccess;
+}
+cudaError_t cudaDeviceSynchronize(void) {
+    std::vector<FakeCudaStream *> snap;
+    {
+        std::lock_guard<std::mutex> g(rt().mu);
+        for (FakeCudaStream *s : rt().streams)
+            if (s->device == t_device) snap.push_back(s);
+    }
+    // A stream may be destroyed by another thread while this one waits: only a program that already races does that.
+    for (FakeCudaStream *s : snap) s->drain();
+    return cudaSuccess;
+}
+cudaError_t cudaDeviceCanAccessPeer(int *can, int device, int peer) {
+    if (!can || device < 0 || peer < 0 || device >= rt().devices || peer >= rt().devices) return fail(cudaErrorInvalidDevice);
+    *can = device != peer;
+    return cudaSuccess;
+}
+cudaError_t cudaDeviceEnablePeerAccess(int peer, unsigned int) {
+    if (peer < 0 || peer >= rt().devices || peer == t_device) return fail(cudaErrorInvalidDevice);
+    std::lock_guard<std::mutex> g(rt().mu);
+    bool &on = rt().peer[{t_device, peer}];
+    if (on) return fail(cudaErrorPeerAccessAlreadyEnabled);
+    on = true;
+    return cudaSuccess;
+}
+
+cudaError_t cudaMalloc(void **ptr, size_t size) {
+    if (!ptr) return fail(cudaErrorInvalidValue);
+    void *p = nullptr;
+    if (posix_memalign(&p, 512, size ? size : 1) != 0) return fail(cudaErrorMemoryAllocation);
+    std::memset(p, 0xcd, size); // fresh device memory is not zero
+    std::lock_guard<std::mutex> g(rt().mu);
+    rt().device[reinterpret_cast<uintptr_t>(p)] = {size, t_device};
+    *ptr = p;
+    return cudaSuccess;
+}
+cudaError_t cudaFree(void *ptr) {
+    if (!ptr) return cudaSuccess;
+    {
+        std::lock_guard<std::mutex> g(rt().mu);
+        auto it = rt().device.find(reinterpret_cast<uintptr_t>(ptr));
+        if (it == rt().device.end()) return fail(cudaErrorInvalidValue);
+        rt().device.erase(it);
+    }
+    cudaDeviceSynchronize(); // as the real call: the device is idle before memory goes away
+    std::free(ptr);
+    return cudaSuccess;
+}
+cudaError_t cudaHostAlloc(void **ptr, size_t size, unsigned int) {
+    if (!ptr) return fail(cudaErrorInvalidValue);
+    void *p = nullptr;
+    if (posix_memalign(&p, 4096, size ? size : 1) != 0) return fail(cudaErrorMemoryAllocation);
+    std::lock_guard<std::mutex> g(rt().mu);
+    rt().pinned[reinterpret_cast<uintptr_t>(p)] = {size, true};
+    *ptr = p;
+    return cudaSuccess;
+}
+cudaError_t cudaFreeHost(void *ptr) {
+    if (!ptr) return cudaSuccess;
+    {
+        std::lock_guard<std::mutex> g(rt().mu);
+        auto it = rt().pinned.find(reinterpret_cast<uintptr_t>(ptr));
+        if (it == rt().pinned.end() || !it->second.ours) return fail(cudaErrorInvalidValue);
+        rt().pinned.erase(it);
+    }
+    std::free(ptr);
+    return cudaSuccess;
+}
+cudaError_t cudaHostRegister(void *ptr, size_t size, unsigned int) {
+    if (!ptr || size == 0) return fail(cudaErrorInvalidValue);
+    const uintptr_t p = reinterpret_cast<uintptr_t>(ptr);
+    std::lock_guard<std::mutex> g(rt().mu);
+    for (auto &kv : rt().pinned)
+        if (p < kv.first + kv.second.size && kv.first < p + size) return fail(cudaErrorHostMemoryAlreadyRegistered);
+    rt().pinned[p] = {size, false};
+    return cudaSuccess;
+}
+cudaError_t cudaHostUnregister(void *ptr) {
+    std::lock_guard<std::mutex> g(rt().mu);
+    auto it = rt().pinned.find(reinterpret_cast<uintptr_t>(ptr));
+    if (it == rt().pinned.end() || it->second.ours) return fail(cudaErrorHostMemoryNotRegistered);
+    rt().pinned.erase(it);
+    return cudaSuccess;
+}
+cudaError_t cudaHostGetDevicePointer(void **dev, void *host, unsigned int) {
+    if (!dev) return fail(cudaErrorInvalidValue);
+    std::lock_guard<std::mutex> g(rt().mu);
+    if (!rt().isPinned(reinterpret_cast<uintptr_t>(host))) return fail(cudaErrorInvalidValue);
+    *dev = host;
+    return cudaSuccess;
+}
+cudaError_t cudaPointerGetAttributes(struct cudaPointerAttributes *attr, const void *ptr) {
+    if (!attr) return fail(cudaErrorInvalidValue);
+    std::lock_guard<std::mutex> g(rt().mu);
+    const uintptr_t p = reinterpret_cast<uintptr_t>(ptr);
+    if (const Allocation *a = rt().findDevice(p)) {
+        *attr = {cudaMemoryTypeDevice, a->device, const_cast<void *>(ptr), nullptr};
+    } else if (rt().isPinned(p)) {
+        *attr = {cudaMemoryTypeHost, 0, const_cast<void *>(ptr), const_cast<void *>(ptr)};
+    } else {
+        *attr = {cudaMemoryTypeUnregistered, -1, nullptr, const_cast<void *>(ptr)};
+    }
+    return cudaSuccess;
+}
+
+cudaError_t cudaMemset(void *ptr, int value, size_t count) {
+    if (!ptr && count) return fail(cudaErrorInvalidValue);
+    if (FakeCudaStream *s = resolve(nullptr)) s->drain(); // the default stream's order
+    std::memset(ptr, value, count);
+    return cudaSuccess;
+}
+cudaError_t cudaMemcpy(void *dst, const void *src, size_t count, enum cudaMemcpyKind) {
+    if ((!dst || !src) && count) return fail(cudaErrorInvalidValue);
+    if (FakeCudaStream *s = resolve(nullptr)) s->drain();
+    std::memmove(dst, src, count);
+    return cudaSuccess;
+}
+cudaError_t cudaMemcpyAsync(void *dst, const void *src, size_t count, enum cudaMemcpyKind, cudaStream_t stream) {
+    if ((!dst || !src) && count) return fail(cudaErrorInvalidValue);
+    FakeCudaStream *s = resolve(stream);
+    if (!s) return fail(cudaErrorInvalidResourceHandle);
+    bool pageable_source;
+    {
+        std::lock_guard<std::mutex> g(rt().mu);
+        const uintptr_t p = reinterpret_cast<uintptr_t>(src);
+        pageable_source = !rt().findDevice(p) && !rt().isPinned(p);
+    }
+    if (pageable_source) {
+        // As the real runtime: a pageable source is taken now (the caller may free it when the call returns).
+        auto staged = std::make_shared<std::vector<char>>(static_cast<const char *>(src), static_cast<const char *>(src) + count);
+        s->push([dst, staged] { std::memcpy(dst, staged->data(), staged->size()); });
+    } else {
+        s->push([dst, src, count] { std::memmove(dst, src, count); });
+    }
+    return cudaSuccess;
+}
+
+cudaError_t cudaStreamCreateWithFlags(cudaStream_t *stream, unsigned int) {
+    if (!stream) return fail(cudaErrorInvalidValue);
+    auto *s = new FakeCudaStream(t_device);
+    std::lock_guard<std::mutex> g(rt().mu);
+    rt().streams.push_back(s);
+    *stream = s;
+    return cudaSuccess;
+}
+cudaError_t cudaStreamCreate(cudaStream_t *stream) { return cudaStreamCreateWithFlags(stream, cudaStreamDefault); }
+cudaError_t cudaStreamDestroy(cudaStream_t stream) {
+    if (!stream) return fail(cudaErrorInvalidResourceHandle);
+    stream->drain(); // the real call lets queued work finish
+    {
+        std::lock_guard<std::mutex> g(rt().mu);
+        auto &v = rt().streams;
+        v.erase(std::remove(v.begin(), v.end(), stream), v.end());
+    }
+    delete stream;
+    return cudaSuccess;
+}
+cudaError_t cudaStreamSynchronize(cudaStream_t stream) {
+    FakeCudaStream *s = resolve(stream);
+    if (!s) return fail(cudaErrorInvalidResourceHandle);
+    s->drain();
+    return cudaSuccess;
+}
+cudaError_t cudaStreamWaitEvent(cudaStream_t stream, cudaEvent_t event, unsigned int) {
+    FakeCudaStream *s = resolve(stream);
+    if (!s || !event) return fail(cudaErrorInvalidResourceHandle);
+    uint64_t want;
+    {
+        std::lock_guard<std::mutex> g(event->mu);
+        want = event->recorded; // the work captured by the latest record
+    }
+    s->push([event, want] {
+        std::unique_lock<std::mutex> lk(event->mu);
+        event->cv.wait(lk, [&] { return event->completed >= want; });
+    });
+    return cudaSuccess;
+}
+
+cudaError_t cudaEventCreateWithFlags(cudaEvent_t *event, unsigned int) {
+    if (!event) return fail(cudaErrorInvalidValue);
+    *event = new FakeCudaEvent();
+    return cudaSuccess;
+}
+cudaError_t cudaEventCreate(cudaEvent_t *event) { return cudaEventCreateWithFlags(event, cudaEventDefault); }
+cudaError_t cudaEventDestroy(cudaEvent_t event) {
+    if (!event) return fail(cudaErrorInvalidResourceHandle);
+    // The real call defers the release until the event has completed; waiting here has the same effect.
+    {
+        std::unique_lock<std::mutex> lk(event->mu);
+        event->cv.wait(lk, [&] { return event->completed >= event->recorded; });
+    }
+    delete event;
+    return cudaSuccess;
+}
+cudaError_t cudaEventRecord(cudaEvent_t event, cudaStream_t stream) {
+    FakeCudaStream *s = resolve(stream);
+    if (!s || !event) return fail(cudaErrorInvalidResourceHandle);
+    uint64_t mine;
+    {
+        std::lock_guard<std::mutex> g(event->mu);
+        mine = ++event->recorded;
+    }
+    s->push([event, mine] {
+        std::lock_guard<std::mutex> g(event->mu); // notified under the lock: cudaEventDestroy may free the event right after
+        if (event->completed < mine) event->completed = mine;
+        event->cv.notify_all();
+    });
+    return cudaSuccess;
+}
+cudaError_t cudaEventQuery(cudaEvent_t event) {
+    if (!event) return fail(cudaErrorInvalidResourceHandle);
+    std::lock_guard<std::mutex> g(event->mu);
+    if (event->completed >= event->recorded) return cudaSuccess;
+    return fail(cudaErrorNotReady); // recorded as the last error, as the real runtime does
+}
+cudaError_t cudaEventSynchronize(cudaEvent_t event) {
+    if (!event) return fail(cudaErrorInvalidResourceHandle);
+    std::unique_lock<std::mutex> lk(event->mu);
+    event->cv.wait(lk, [&] { return event->completed >= event->recorded; });
+    return cudaSuccess;
+}
+
+// Same-process handles only: the handle carries the base address and the process id.
+cudaError_t cudaIpcGetMemHandle(cudaIpcMemHandle_t *handle, void *ptr) {
+    if (!handle) return fail(cudaErrorInvalidValue);
+    std::lock_guard<std::mutex> g(rt().mu);
+    auto it = rt().device.find(reinterpret_cast<uintptr_t>(ptr));
+    if (it == rt().device.end()) return fail(cudaErrorInvalidValue); // must be the base of an allocation
+    std::memset(handle, 0, sizeof(*handle));
+    const uint64_t base = reinterpret_cast<uintptr_t>(ptr), pid = static_cast<uint64_t>(::getpid());
+    std::memcpy(handle->reserved, &base, 8);
+    std::memcpy(handle->reserved + 8, &pid, 8);
+    return cudaSuccess;
+}
+cudaError_t cudaIpcOpenMemHandle(void **ptr, cudaIpcMemHandle_t handle, unsigned int) {
+    uint64_t base = 0, pid = 0;
+    std::memcpy(&base, handle.reserved, 8);
+    std::memcpy(&pid, handle.reserved + 8, 8);
+    if (!ptr || pid != static_cast<uint64_t>(::getpid())) return fail(cudaErrorNotSupported); // another process's memory cannot be mapped here
+    *ptr = reinterpret_cast<void *>(base);
+    return cudaSuccess;
+}
+cudaError_t cudaIpcCloseMemHandle(void *) { return cudaSuccess; }
+
+static int fakeGetAddressRange(unsigned long long *base, size_t *size, unsigned long long ptr) {
+    std::lock_guard<std::mutex> g(rt().mu);
+    uintptr_t b = 0;
+    const Allocation *a = rt().findDevice(static_cast<uintptr_t>(ptr), &b);
+    if (!a) return 1;
+    if (base) *base = b;
+    if (size) *size = a->size;
+    return 0;
+}
+
+cudaError_t cudaGetDriverEntryPoint(const char *symbol, void **fn, unsigned long long, enum cudaDriverEntryPointQueryResult *result) {
+    if (!symbol || !fn) return fail(cudaErrorInvalidValue);
+    if (std::strcmp(symbol, "cuMemGetAddressRange") == 0) {
+        *fn = reinterpret_cast<void *>(&fakeGetAddressRange);
+        if (result) *result = cudaDriverEntryPointSuccess;
+        return cudaSuccess;
+    }
+    *fn = nullptr; // the virtual-memory entry points do not exist here: exports through file descriptors stay off
+    if (result) *result = cudaDriverEntryPointSymbolNotFound;
+    return cudaSuccess;
+}
+
+} // extern "C"

