@@ -6,6 +6,7 @@
 // show is anything inside the real kernels; those are covered on GPUs (tests/test_gpu_*.py).
 #include <atomic>
 #include <chrono>
+#include <cstdlib>
 #include <cstring>
 #include <random>
 #include <thread>
@@ -236,11 +237,12 @@ TEST_CASE(a_request_released_right_after_its_post_on_a_busy_stream_leaves_intact
     for (int i = 0; i < 64; ++i) rows.emplace_back(size_t(i) << 16, size_t(1) << 16);
     nixl_opt_args_t on_stream;
     on_stream.customParam = "stream=" + std::to_string(reinterpret_cast<uintptr_t>(user));
-    for (int round = 0; round < 40; ++round) {
+    const int rounds = std::getenv("FAKE_GPU_STRESS") ? 2000 : 40;
+    for (int round = 0; round < rounds; ++round) {
         std::memset(p.dst.p, 0, 64 << 16);
         p.src.p[round] ^= 0x77;
         nixlXferReqH *big = p.request(NIXL_WRITE, rows, sameOffsets(rows));
-        fake_cuda::enqueueDelay(user, 3000 + 500 * (round % 5)); // the stream is busy for a few milliseconds
+        fake_cuda::enqueueDelay(user, rounds > 40 ? 50 * (round % 7) : 3000 + 500 * (round % 5)); // the stream is busy for a while
         CHECK_EQ(p.a.postXferReq(big, &on_stream), NIXL_IN_PROG);
         CHECK_EQ(p.a.releaseXferReq(big), NIXL_SUCCESS);
         nixlXferReqH *small = p.request(NIXL_WRITE, {{0, 65536}}, {0});
@@ -347,6 +349,108 @@ TEST_CASE(threads_post_small_and_large_requests_side_by_side) {
     for (auto &t : threads) t.join();
     CHECK_EQ(failures.load(), 0);
     CHECK_EQ(seen, size_t(600));
+}
+
+TEST_CASE(host_memory_pinned_and_pageable_to_and_from_a_gpu) {
+    // The initiator's side is host memory (registered, which pins it: the copy kernel reaches it; and a second buffer
+    // registered with pinning switched off: the runtime stages it), the target's side device memory.
+    for (const char *pin : {"true", "false"}) {
+        const std::string tag = std::string("hm") + pin;
+        nixlAgent a(tag + "_a", nixlAgentConfig(false)), b(tag + "_b", nixlAgentConfig(false));
+        nixlBackendH *ha = nullptr, *hb = nullptr;
+        CHECK_EQ(a.createBackend("NVLINK", {{"pin_dram", pin}}, ha), NIXL_SUCCESS);
+        CHECK_EQ(b.createBackend("NVLINK", {}, hb), NIXL_SUCCESS);
+        std::vector<uint8_t> host(2 << 20);
+        std::mt19937 rng(4);
+        for (auto &x : host) x = static_cast<uint8_t>(rng());
+        DevBuf dev(1, host.size(), 0);
+        nixl_reg_dlist_t rh(DRAM_SEG), rd(VRAM_SEG);
+        rh.addDesc(nixlBlobDesc(reinterpret_cast<uintptr_t>(host.data()), host.size(), 0, ""));
+        rd.addDesc(nixlBlobDesc(reinterpret_cast<uintptr_t>(dev.p), dev.bytes, 1, ""));
+        CHECK_EQ(a.registerMem(rh), NIXL_SUCCESS);
+        CHECK_EQ(b.registerMem(rd), NIXL_SUCCESS);
+        nixl_blob_t md;
+        std::string name;
+        b.getLocalMD(md);
+        CHECK_EQ(a.loadRemoteMD(md, name), NIXL_SUCCESS);
+        nixl_xfer_dlist_t l(DRAM_SEG), r(VRAM_SEG);
+        for (int i = 0; i < 8; ++i) {
+            l.addDesc(nixlBasicDesc(reinterpret_cast<uintptr_t>(host.data()) + size_t(i) * 262144, 262144, 0));
+            r.addDesc(nixlBasicDesc(reinterpret_cast<uintptr_t>(dev.p) + size_t(7 - i) * 262144, 262144, 1));
+        }
+        nixlXferReqH *req = nullptr;
+        CHECK_EQ(a.createXferReq(NIXL_WRITE, l, r, tag + "_b", req), NIXL_SUCCESS);
+        CHECK(a.postXferReq(req) >= 0);
+        CHECK_EQ(waitDone(a, req), NIXL_SUCCESS);
+        for (int i = 0; i < 8; ++i) CHECK(std::memcmp(host.data() + size_t(i) * 262144, dev.p + size_t(7 - i) * 262144, 262144) == 0);
+        CHECK_EQ(a.releaseXferReq(req), NIXL_SUCCESS);
+        for (size_t i = 0; i < dev.bytes; i += 4099) dev.p[i] ^= 0x3c;
+        const std::vector<uint8_t> changed(dev.p, dev.p + dev.bytes);
+        CHECK_EQ(a.createXferReq(NIXL_READ, l, r, tag + "_b", req), NIXL_SUCCESS);
+        CHECK(a.postXferReq(req) >= 0);
+        CHECK_EQ(waitDone(a, req), NIXL_SUCCESS);
+        for (int i = 0; i < 8; ++i) CHECK(std::memcmp(host.data() + size_t(i) * 262144, changed.data() + size_t(7 - i) * 262144, 262144) == 0);
+        CHECK_EQ(a.releaseXferReq(req), NIXL_SUCCESS);
+        CHECK_EQ(a.deregisterMem(rh), NIXL_SUCCESS);
+        CHECK_EQ(b.deregisterMem(rd), NIXL_SUCCESS);
+    }
+}
+
+TEST_CASE(a_request_still_running_cannot_be_posted_again) {
+    Pair p({}, 4 << 20, 0, 0);
+    cudaSetDevice(0);
+    cudaStream_t user = nullptr;
+    CHECK_EQ(cudaStreamCreateWithFlags(&user, cudaStreamNonBlocking), cudaSuccess);
+    nixl_opt_args_t on_stream;
+    on_stream.customParam = "stream=" + std::to_string(reinterpret_cast<uintptr_t>(user));
+    nixlXferReqH *req = p.request(NIXL_WRITE, {{0, 3 << 20}}, {0});
+    fake_cuda::enqueueDelay(user, 30000);
+    CHECK_EQ(p.a.postXferReq(req, &on_stream), NIXL_IN_PROG);
+    CHECK_EQ(p.a.postXferReq(req, &on_stream), NIXL_ERR_REPOST_ACTIVE);
+    CHECK_EQ(p.a.getXferStatus(req), NIXL_IN_PROG); // the refusal did not disturb the running post
+    CHECK_EQ(waitDone(p.a, req), NIXL_SUCCESS);
+    CHECK(std::memcmp(p.src.p, p.dst.p, 3 << 20) == 0);
+    CHECK(p.a.postXferReq(req, &on_stream) >= 0); // complete: it may go again
+    CHECK_EQ(waitDone(p.a, req), NIXL_SUCCESS);
+    CHECK_EQ(p.a.releaseXferReq(req), NIXL_SUCCESS);
+    cudaStreamDestroy(user);
+}
+
+TEST_CASE(memory_views_hold_what_the_kernels_will_read) {
+    Pair p({}, 1 << 20, 0, 1);
+    nixl_xfer_dlist_t local(VRAM_SEG);
+    local.addDesc(nixlBasicDesc(reinterpret_cast<uintptr_t>(p.src.p) + 4096, 8192, 0));
+    local.addDesc(nixlBasicDesc(reinterpret_cast<uintptr_t>(p.src.p) + 65536, 100, 0));
+    nixl_remote_dlist_t remote(VRAM_SEG);
+    remote.addDesc(nixlRemoteDesc(nixlBasicDesc(reinterpret_cast<uintptr_t>(p.dst.p) + 512, 2048, 1), p.bn));
+    remote.addDesc(nixlRemoteDesc(nixlBasicDesc(0, 0, 0), nixl_null_agent)); // a hole: an absent rank
+    remote.addDesc(nixlRemoteDesc(nixlBasicDesc(reinterpret_cast<uintptr_t>(p.dst.p) + 8192, 4096, 1), p.bn));
+    cudaSetDevice(0);
+    nixlMemViewH lv = nullptr, rv = nullptr;
+    CHECK_EQ(p.a.prepMemView(local, lv), NIXL_SUCCESS);
+    CHECK_EQ(p.a.prepMemView(remote, rv), NIXL_SUCCESS);
+    struct Header { uint64_t magic; uint32_t count, kind; };
+    struct Entry { uint64_t ptr, len; };
+    const auto *lh = static_cast<const Header *>(lv);
+    const auto *le = reinterpret_cast<const Entry *>(lh + 1);
+    CHECK_EQ(lh->count, 2u);
+    CHECK_EQ(lh->kind, 1u);
+    CHECK(le[0].ptr == reinterpret_cast<uintptr_t>(p.src.p) + 4096 && le[0].len == 8192 && le[1].len == 100);
+    const auto *rh = static_cast<const Header *>(rv);
+    const auto *re = reinterpret_cast<const Entry *>(rh + 1);
+    CHECK_EQ(rh->count, 3u);
+    CHECK_EQ(rh->kind, 2u);
+    CHECK(rh->magic == lh->magic && rh->magic != 0);
+    CHECK(re[0].ptr == reinterpret_cast<uintptr_t>(p.dst.p) + 512 && re[0].len == 2048);
+    CHECK(re[1].ptr == 0); // the hole
+    CHECK(re[2].ptr == reinterpret_cast<uintptr_t>(p.dst.p) + 8192 && re[2].len == 4096);
+    // a range outside what the target registered is refused
+    nixl_remote_dlist_t bad(VRAM_SEG);
+    bad.addDesc(nixlRemoteDesc(nixlBasicDesc(reinterpret_cast<uintptr_t>(p.dst.p) + p.dst.bytes - 16, 64, 1), p.bn));
+    nixlMemViewH bv = nullptr;
+    CHECK(p.a.prepMemView(bad, bv) != NIXL_SUCCESS);
+    p.a.releaseMemView(lv);
+    p.a.releaseMemView(rv);
 }
 
 TEST_CASE(a_target_that_went_away_is_reported_and_its_metadata_dropped) {

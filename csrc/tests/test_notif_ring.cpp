@@ -1,5 +1,6 @@
 // The shared-memory notification ring of the NVLINK backend (src/plugins/nvlink/notif_ring.h), without a GPU:
 // the host plays the part of the copy kernel's tail (one store to the slot's sequence word).
+#include <sched.h>
 #include <sys/wait.h>
 #include <unistd.h>
 
@@ -133,29 +134,28 @@ TEST_CASE(another_process_writes_and_a_claimant_that_died_does_not_hold_the_ring
 }
 
 TEST_CASE(several_writers_and_one_reader_deliver_every_message_exactly_once) {
-    // The writers are threads of a child process (a second mapping of the ring in the reader's own process would
-    // hide the synchronisation from a race detector, which goes by virtual address).
+    // Every writer is a process of its own: what orders two writers that use the same slot one lap apart is the
+    // reader in between, and a race detector sees neither another process nor a second mapping of the ring in this one.
     NotifRingOwner owner;
     CHECK(owner.create(ringName("g")));
     const std::string name = owner.name();
     constexpr int kWriters = 4, kEach = 3000; // 12000 messages through 1024 slots: the ring wraps many times
-    const pid_t child = ::fork();
-    if (child == 0) {
-        auto w = NotifRingWriter::open(name);
-        if (!w) ::_exit(2);
-        std::vector<std::thread> writers;
-        for (int t = 0; t < kWriters; ++t)
-            writers.emplace_back([&, t] {
-                for (int i = 0; i < kEach; ++i) {
-                    uint64_t *word = nullptr, seq = 0;
-                    const std::string msg = std::to_string(t) + ":" + std::to_string(i);
-                    while (!w->claim("writer" + std::to_string(t), msg, &word, &seq)) std::this_thread::yield(); // full: the reader is behind
-                    if (i % 7 == 3) std::this_thread::yield(); // some claims complete late, out of order
-                    NotifRingWriter::complete(word, seq, i % 11 != 5); // and some are voided
-                }
-            });
-        for (auto &t : writers) t.join();
-        ::_exit(0);
+    std::vector<pid_t> children;
+    for (int t = 0; t < kWriters; ++t) {
+        const pid_t child = ::fork();
+        if (child == 0) {
+            auto w = NotifRingWriter::open(name);
+            if (!w) ::_exit(2);
+            for (int i = 0; i < kEach; ++i) {
+                uint64_t *word = nullptr, seq = 0;
+                const std::string msg = std::to_string(t) + ":" + std::to_string(i);
+                while (!w->claim("writer" + std::to_string(t), msg, &word, &seq)) ::sched_yield(); // full: the reader is behind
+                if (i % 7 == 3) ::sched_yield(); // some claims complete late, out of order with the other writers'
+                NotifRingWriter::complete(word, seq, i % 11 != 5); // and some are voided
+            }
+            ::_exit(0);
+        }
+        children.push_back(child);
     }
     std::vector<std::vector<int>> seen(kWriters);
     size_t total = 0, expected = 0;
@@ -174,9 +174,11 @@ TEST_CASE(several_writers_and_one_reader_deliver_every_message_exactly_once) {
             ++total;
         }
     }
-    int status = 0;
-    CHECK(::waitpid(child, &status, 0) == child);
-    CHECK(WIFEXITED(status) && WEXITSTATUS(status) == 0);
+    for (pid_t child : children) {
+        int status = 0;
+        CHECK(::waitpid(child, &status, 0) == child);
+        CHECK(WIFEXITED(status) && WEXITSTATUS(status) == 0);
+    }
     NotifList rest;
     owner.poll(rest);
     CHECK(rest.empty());
