@@ -142,6 +142,10 @@ void enqueueDelay(cudaStream_t stream, unsigned microseconds);
 // Number of devices the stand-in reports (environment FAKE_CUDA_DEVICES, default 2); tasks run so far.
 int deviceCount();
 uint64_t tasksRun();
+// Failure injection for the stand-in kernels: the next `count` launches of that kind fail with cudaErrorUnknown.
+enum class LaunchKind { Copy = 0, Signal = 1, Proxy = 2 };
+void failLaunches(LaunchKind kind, int count);
+bool takeLaunchFailure(LaunchKind kind); // used by the stand-in kernels: true = fail this launch
 } // namespace fake_cuda
 
 #endif

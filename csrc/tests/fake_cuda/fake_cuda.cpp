@@ -158,6 +158,15 @@ void enqueueDelay(cudaStream_t stream, unsigned microseconds) {
 }
 int deviceCount() { return rt().devices; }
 uint64_t tasksRun() { return g_tasksRun.load(); }
+static std::atomic<int> g_failLaunches[3];
+void failLaunches(LaunchKind kind, int count) { g_failLaunches[static_cast<int>(kind)].store(count); }
+bool takeLaunchFailure(LaunchKind kind) {
+    std::atomic<int> &c = g_failLaunches[static_cast<int>(kind)];
+    int left = c.load();
+    while (left > 0)
+        if (c.compare_exchange_weak(left, left - 1)) return true;
+    return false;
+}
 } // namespace fake_cuda
 
 extern "C" {

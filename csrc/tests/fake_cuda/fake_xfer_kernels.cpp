@@ -27,6 +27,7 @@ void copyAll(const XferDesc *descs, uint32_t n) {
 
 cudaError_t launchBatchCopy(const XferLaunch &params, int, CopyPath, cudaStream_t stream) {
     if (params.totalChunks == 0) return cudaErrorInvalidValue;
+    if (fake_cuda::takeLaunchFailure(fake_cuda::LaunchKind::Copy)) return cudaErrorUnknown;
     const XferLaunch p = params; // by value, as kernel parameters are
     fake_cuda::enqueue(stream, [p] {
         // The table is read when the kernel runs, not when it is launched: an upload that has not landed, or a table
@@ -41,6 +42,7 @@ cudaError_t launchBatchCopy(const XferLaunch &params, int, CopyPath, cudaStream_
 }
 
 cudaError_t launchSignal(uint64_t *hostFlag, uint64_t seq, uint64_t *notifWord, uint64_t notifSeq, cudaStream_t stream) {
+    if (fake_cuda::takeLaunchFailure(fake_cuda::LaunchKind::Signal)) return cudaErrorUnknown;
     fake_cuda::enqueue(stream, [=] {
         if (notifWord) storeRelease(notifWord, notifSeq);
         storeRelease(hostFlag, seq);
@@ -49,6 +51,7 @@ cudaError_t launchSignal(uint64_t *hostFlag, uint64_t seq, uint64_t *notifWord, 
 }
 
 cudaError_t launchProxy(const ProxyLaunch &launch, int, cudaStream_t stream) {
+    if (fake_cuda::takeLaunchFailure(fake_cuda::LaunchKind::Proxy)) return cudaErrorUnknown;
     const ProxyLaunch p = launch;
     fake_cuda::enqueue(stream, [p] {
         const uint64_t t_start = nowNs();

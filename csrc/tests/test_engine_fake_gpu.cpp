@@ -453,6 +453,56 @@ TEST_CASE(memory_views_hold_what_the_kernels_will_read) {
     p.a.releaseMemView(rv);
 }
 
+TEST_CASE(launch_failures_are_reported_and_leave_the_engine_usable) {
+    using fake_cuda::LaunchKind;
+    // a copy-kernel launch fails: the post says so, the request can be posted again and released
+    {
+        Pair p({{"proxy", "false"}}, 1 << 20);
+        nixl_opt_args_t args;
+        args.notif = "never";
+        nixlXferReqH *req = p.request(NIXL_WRITE, {{0, 300000}}, {0}, &args);
+        fake_cuda::failLaunches(LaunchKind::Copy, 1);
+        CHECK_EQ(p.a.postXferReq(req), NIXL_ERR_BACKEND);
+        CHECK_EQ(p.a.getXferStatus(req), NIXL_ERR_BACKEND);
+        nixl_notifs_t got;
+        p.b.getNotifs(got);
+        CHECK(got[p.an].empty()); // the slot claimed for the notification was voided, nothing was delivered
+        CHECK(p.a.postXferReq(req) >= 0); // the next launch works
+        CHECK_EQ(waitDone(p.a, req), NIXL_SUCCESS);
+        CHECK(std::memcmp(p.src.p, p.dst.p, 300000) == 0);
+        for (int i = 0; i < 2000 && got[p.an].empty(); ++i) p.b.getNotifs(got);
+        CHECK_EQ(got[p.an].size(), size_t(1)); // one notification, from the post that worked
+        CHECK_EQ(p.a.releaseXferReq(req), NIXL_SUCCESS);
+    }
+    // the one-thread kernel behind the copy engines fails
+    {
+        Pair p({{"ce_threshold", "65536"}}, 1 << 20);
+        nixlXferReqH *req = p.request(NIXL_WRITE, {{0, 1 << 19}}, {0});
+        fake_cuda::failLaunches(LaunchKind::Signal, 1);
+        CHECK_EQ(p.a.postXferReq(req), NIXL_ERR_BACKEND);
+        CHECK(p.a.postXferReq(req) >= 0);
+        CHECK_EQ(waitDone(p.a, req), NIXL_SUCCESS);
+        CHECK(std::memcmp(p.src.p, p.dst.p, 1 << 19) == 0);
+        CHECK_EQ(p.a.releaseXferReq(req), NIXL_SUCCESS);
+    }
+    // the doorbell proxy cannot be started: the request that rang it reports the failure, later small requests take
+    // the launch path
+    {
+        Pair p({}, 1 << 20);
+        nixlXferReqH *req = p.request(NIXL_WRITE, {{0, 4096}}, {0});
+        fake_cuda::failLaunches(LaunchKind::Proxy, 1);
+        const nixl_status_t first = p.a.postXferReq(req);
+        CHECK(first == NIXL_ERR_BACKEND || (first == NIXL_IN_PROG && waitDone(p.a, req) == NIXL_ERR_BACKEND));
+        for (int i = 0; i < 20; ++i) {
+            p.src.p[i] ^= 0x42;
+            CHECK(p.a.postXferReq(req) >= 0);
+            CHECK_EQ(waitDone(p.a, req), NIXL_SUCCESS);
+            CHECK(std::memcmp(p.src.p, p.dst.p, 4096) == 0);
+        }
+        CHECK_EQ(p.a.releaseXferReq(req), NIXL_SUCCESS);
+    }
+}
+
 TEST_CASE(a_target_that_went_away_is_reported_and_its_metadata_dropped) {
     auto p = std::make_unique<Pair>(nixl_b_params_t{}, 1 << 16);
     nixlXferReqH *req = p->request(NIXL_WRITE, {{0, 4096}}, {0});
