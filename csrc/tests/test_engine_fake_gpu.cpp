@@ -351,6 +351,43 @@ TEST_CASE(threads_post_small_and_large_requests_side_by_side) {
     CHECK_EQ(seen, size_t(600));
 }
 
+TEST_CASE(threads_ring_a_proxy_that_keeps_leaving) {
+    // Tiny idle time and life: the proxy leaves between and in the middle of the threads' streams of small requests, so
+    // "is it still running" is decided again and again while other threads post, poll and relaunch.
+    nixlAgentConfig cfg(false, false, 0, nixl_thread_sync_t::NIXL_THREAD_SYNC_RW);
+    Pair p({{"proxy_idle_us", "5"}, {"proxy_life_us", "60"}}, 4 << 20, 0, 1, cfg);
+    std::atomic<int> failures{0};
+    std::vector<std::thread> threads;
+    const int rounds = std::getenv("FAKE_GPU_STRESS") ? 20000 : 1500;
+    for (int t = 0; t < 4; ++t)
+        threads.emplace_back([&, t] {
+            const size_t base = size_t(t) << 20;
+            try {
+                nixlXferReqH *one = p.request(NIXL_WRITE, {{base, 2048}}, {base});
+                nixlXferReqH *three = p.request(NIXL_WRITE, {{base + 65536, 4096}, {base + 131072, 4096}, {base + 262144, 64}},
+                                                {base + 131072, base + 262144, base + 65536});
+                for (int i = 0; i < rounds; ++i) {
+                    nixlXferReqH *req = i % 4 == 3 ? three : one;
+                    p.src.p[base + (i % 2048)] = static_cast<uint8_t>(i);
+                    p.src.p[base + 65536 + (i % 4096)] = static_cast<uint8_t>(i >> 3);
+                    if (p.a.postXferReq(req) < 0 || waitDone(p.a, req) != NIXL_SUCCESS) {
+                        ++failures;
+                        continue;
+                    }
+                    if (req == one ? std::memcmp(p.src.p + base, p.dst.p + base, 2048) != 0
+                                   : std::memcmp(p.src.p + base + 65536, p.dst.p + base + 131072, 4096) != 0)
+                        ++failures;
+                    if (i % 97 == t) std::this_thread::sleep_for(std::chrono::microseconds(30));
+                }
+                if (p.a.releaseXferReq(one) != NIXL_SUCCESS || p.a.releaseXferReq(three) != NIXL_SUCCESS) ++failures;
+            } catch (const std::exception &) {
+                ++failures;
+            }
+        });
+    for (auto &t : threads) t.join();
+    CHECK_EQ(failures.load(), 0);
+}
+
 TEST_CASE(host_memory_pinned_and_pageable_to_and_from_a_gpu) {
     // The initiator's side is host memory (registered, which pins it: the copy kernel reaches it; and a second buffer
     // registered with pinning switched off: the runtime stages it), the target's side device memory.
