@@ -103,3 +103,38 @@ def test_native_nixlbench_accepts_the_reference_spellings(tmp_path):
     assert res.returncode == 0, res.stdout + res.stderr
     assert os.path.getsize(store) >= 8 * 65536
     assert _nixlbench("--no_such_option=1").returncode == 2
+
+
+# ---------------------------------------------------------------------------------------------- nixlbench on the stand-in runtime
+
+FAKE = os.path.join(ROOT, "csrc", "build", "fake_gpu")
+
+
+def _nixlbench_fake_gpu(*args, devices=2):
+    """nixlbench built against the stand-in CUDA runtime (csrc/tests/fake_cuda): its VRAM modes without a GPU."""
+    exe = os.path.join(FAKE, "nixlbench")
+    if not os.path.exists(exe):
+        subprocess.run(["make", "-C", os.path.join(ROOT, "csrc"), "-j8", "tests"], check=True, capture_output=True)
+    env = dict(ENV, NIXL_PLUGIN_DIR=os.path.join(FAKE, "plugins"), FAKE_CUDA_DEVICES=str(devices))
+    return subprocess.run([exe, *args], env=env, capture_output=True, text=True, timeout=180)
+
+
+@pytest.mark.parametrize("extra", [["--op", "WRITE"], ["--op", "READ"], ["--op", "WRITE", "--scatter", "--depth", "4"],
+                                   ["--op", "WRITE", "--prepared", "--num-threads", "2"], ["--op", "WRITE", "--param", "ce_threshold=65536"],
+                                   ["--op", "WRITE", "--param", "proxy=false", "--recreate"]])
+def test_nixlbench_vram_modes_on_the_stand_in_runtime(extra):
+    res = _nixlbench_fake_gpu("--mem", "VRAM", "--min", "4096", "--max", "1048576", "--batch", "4", "--iters", "60", "--warmup", "5", "--check", *extra)
+    assert res.returncode == 0, res.stdout + res.stderr
+    rows = [l.split() for l in res.stdout.splitlines() if l and l[0].isdigit()]
+    assert [r[0] for r in rows] == [str(4096 << i) for i in range(9)] and all(float(r[2]) > 0 for r in rows)
+
+
+@pytest.mark.parametrize("scheme,extra,flows", [("onetomany", ["--num-target-dev", "3"], 3), ("manytoone", ["--num-initiator-dev", "3", "--dst-dev", "2"], 3),
+                                                ("tp", ["--num-initiator-dev", "2", "--num-target-dev", "2"], 4)])
+def test_nixlbench_vram_schemes_on_the_stand_in_runtime(scheme, extra, flows):
+    res = _nixlbench_fake_gpu("--mem", "VRAM", "--scheme", scheme, *extra, "--min", "65536", "--max", "262144", "--batch", "4", "--iters", "30",
+                              "--warmup", "3", "--check", devices=4)
+    assert res.returncode == 0, res.stdout + res.stderr
+    assert f"{flows} flow(s), VRAM" in res.stdout
+    few = _nixlbench_fake_gpu("--mem", "VRAM", "--scheme", scheme, *extra, "--min", "65536", "--max", "65536", devices=2)
+    assert few.returncode == 2 and "needs" in few.stderr  # more endpoints than GPUs
