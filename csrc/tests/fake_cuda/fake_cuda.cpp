@@ -12,9 +12,12 @@
 #include <map>
 #include <memory>
 #include <mutex>
+#include <string>
 #include <thread>
 #include <vector>
 
+#include <fcntl.h>
+#include <sys/mman.h>
 #include <unistd.h>
 
 // ---------------------------------------------------------------- streams and events
@@ -73,6 +76,7 @@ cudaError_t fail(cudaError_t e) {
 struct Allocation {
     size_t size;
     int device;
+    std::string shm; // name of the shared-memory object behind it (device memory another process can map), or empty
 };
 struct HostRange {
     size_t size;
@@ -253,26 +257,49 @@ cudaError_t cudaDeviceEnablePeerAccess(int peer, unsigned int) {
     return cudaSuccess;
 }
 
+// "Device memory" lives in shared-memory objects, so that another process can map it through an IPC handle the way a
+// second process maps a real GPU allocation (at an address of its own).  Allocations of less than a page stay on the heap
+// (an IPC handle for them works inside the process only).
 cudaError_t cudaMalloc(void **ptr, size_t size) {
     if (!ptr) return fail(cudaErrorInvalidValue);
+    static std::atomic<uint64_t> serial{0};
     void *p = nullptr;
-    if (posix_memalign(&p, 512, size ? size : 1) != 0) return fail(cudaErrorMemoryAllocation);
+    std::string name;
+    if (size >= 4096) {
+        name = "/fakecuda." + std::to_string(::getpid()) + "." + std::to_string(serial.fetch_add(1));
+        const int fd = ::shm_open(name.c_str(), O_CREAT | O_EXCL | O_RDWR | O_CLOEXEC, 0600);
+        if (fd >= 0 && ::ftruncate(fd, static_cast<off_t>(size)) == 0) p = ::mmap(nullptr, size, PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
+        if (fd >= 0) ::close(fd);
+        if (p == nullptr || p == MAP_FAILED) {
+            if (fd >= 0) ::shm_unlink(name.c_str());
+            return fail(cudaErrorMemoryAllocation);
+        }
+    } else if (posix_memalign(&p, 512, size ? size : 1) != 0) {
+        return fail(cudaErrorMemoryAllocation);
+    }
     std::memset(p, 0xcd, size); // fresh device memory is not zero
     std::lock_guard<std::mutex> g(rt().mu);
-    rt().device[reinterpret_cast<uintptr_t>(p)] = {size, t_device};
+    rt().device[reinterpret_cast<uintptr_t>(p)] = {size, t_device, name};
     *ptr = p;
     return cudaSuccess;
 }
 cudaError_t cudaFree(void *ptr) {
     if (!ptr) return cudaSuccess;
+    Allocation a;
     {
         std::lock_guard<std::mutex> g(rt().mu);
         auto it = rt().device.find(reinterpret_cast<uintptr_t>(ptr));
         if (it == rt().device.end()) return fail(cudaErrorInvalidValue);
+        a = it->second;
         rt().device.erase(it);
     }
     cudaDeviceSynchronize(); // as the real call: the device is idle before memory goes away
-    std::free(ptr);
+    if (a.shm.empty()) {
+        std::free(ptr);
+    } else {
+        ::munmap(ptr, a.size);
+        ::shm_unlink(a.shm.c_str()); // processes that mapped it keep their mappings, as with a real handle
+    }
     return cudaSuccess;
 }
 cudaError_t cudaHostAlloc(void **ptr, size_t size, unsigned int) {
@@ -449,27 +476,62 @@ cudaError_t cudaEventSynchronize(cudaEvent_t event) {
     return cudaSuccess;
 }
 
-// Same-process handles only: the handle carries the base address and the process id.
+// The handle carries the owner's process id, the base address there, the size and the name of the shared-memory object.
+// Opened in the owner's process it gives the allocation itself; in another process a mapping of the same memory.
+namespace {
+struct IpcPayload {
+    uint64_t base, pid, size;
+    char name[40];
+};
+static_assert(sizeof(IpcPayload) <= sizeof(cudaIpcMemHandle_t), "payload fits the handle");
+std::map<uintptr_t, size_t> g_ipcMappings; // mappings of other processes' allocations (under rt().mu)
+} // namespace
+
 cudaError_t cudaIpcGetMemHandle(cudaIpcMemHandle_t *handle, void *ptr) {
     if (!handle) return fail(cudaErrorInvalidValue);
     std::lock_guard<std::mutex> g(rt().mu);
     auto it = rt().device.find(reinterpret_cast<uintptr_t>(ptr));
     if (it == rt().device.end()) return fail(cudaErrorInvalidValue); // must be the base of an allocation
+    IpcPayload pl{};
+    pl.base = reinterpret_cast<uintptr_t>(ptr);
+    pl.pid = static_cast<uint64_t>(::getpid());
+    pl.size = it->second.size;
+    std::snprintf(pl.name, sizeof(pl.name), "%s", it->second.shm.c_str());
     std::memset(handle, 0, sizeof(*handle));
-    const uint64_t base = reinterpret_cast<uintptr_t>(ptr), pid = static_cast<uint64_t>(::getpid());
-    std::memcpy(handle->reserved, &base, 8);
-    std::memcpy(handle->reserved + 8, &pid, 8);
+    std::memcpy(handle->reserved, &pl, sizeof(pl));
     return cudaSuccess;
 }
 cudaError_t cudaIpcOpenMemHandle(void **ptr, cudaIpcMemHandle_t handle, unsigned int) {
-    uint64_t base = 0, pid = 0;
-    std::memcpy(&base, handle.reserved, 8);
-    std::memcpy(&pid, handle.reserved + 8, 8);
-    if (!ptr || pid != static_cast<uint64_t>(::getpid())) return fail(cudaErrorNotSupported); // another process's memory cannot be mapped here
-    *ptr = reinterpret_cast<void *>(base);
+    if (!ptr) return fail(cudaErrorInvalidValue);
+    IpcPayload pl;
+    std::memcpy(&pl, handle.reserved, sizeof(pl));
+    pl.name[sizeof(pl.name) - 1] = 0;
+    if (pl.pid == static_cast<uint64_t>(::getpid())) { // (the real runtime refuses this; the backend never asks for it)
+        *ptr = reinterpret_cast<void *>(pl.base);
+        return cudaSuccess;
+    }
+    if (pl.name[0] == 0) return fail(cudaErrorNotSupported);
+    const int fd = ::shm_open(pl.name, O_RDWR | O_CLOEXEC, 0);
+    if (fd < 0) return fail(cudaErrorInvalidValue);
+    void *p = ::mmap(nullptr, pl.size, PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
+    ::close(fd);
+    if (p == MAP_FAILED) return fail(cudaErrorMemoryAllocation);
+    std::lock_guard<std::mutex> g(rt().mu);
+    g_ipcMappings[reinterpret_cast<uintptr_t>(p)] = pl.size;
+    // kernels of this process address it like device memory of the GPU that opened it
+    rt().device[reinterpret_cast<uintptr_t>(p)] = {pl.size, t_device, std::string()};
+    *ptr = p;
     return cudaSuccess;
 }
-cudaError_t cudaIpcCloseMemHandle(void *) { return cudaSuccess; }
+cudaError_t cudaIpcCloseMemHandle(void *ptr) {
+    std::lock_guard<std::mutex> g(rt().mu);
+    auto it = g_ipcMappings.find(reinterpret_cast<uintptr_t>(ptr));
+    if (it == g_ipcMappings.end()) return cudaSuccess; // an allocation of this process: nothing was mapped
+    ::munmap(ptr, it->second);
+    rt().device.erase(reinterpret_cast<uintptr_t>(ptr));
+    g_ipcMappings.erase(it);
+    return cudaSuccess;
+}
 
 static int fakeGetAddressRange(unsigned long long *base, size_t *size, unsigned long long ptr) {
     std::lock_guard<std::mutex> g(rt().mu);
