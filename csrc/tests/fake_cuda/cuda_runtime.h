@@ -4,8 +4,9 @@
 // stream, the copy kernels are functions that run as such tasks (fake_xfer_kernels.cpp).  What the backend's host side
 // relies on is modelled; nothing else: stream order, events and stream waits, asynchronous copies (a copy from
 // pageable host memory takes its source at once, a copy from pinned memory when it runs), pinned and registered host
-// ranges, per-device allocations with pointer attributes, peer access, same-process IPC handles, "not ready" as the
-// last error.  Driver entry points are reported as absent, so the VMM export path stays off.
+// ranges, per-device allocations with pointer attributes, peer access, IPC handles (device memory is a shared-memory
+// object that another process maps), the driver's virtual-memory calls (export of an allocation as a file descriptor,
+// import, reserve / map / unmap), "not ready" as the last error.
 //
 // Only the test build of the plug-in sees this header (it shadows the real <cuda_runtime.h> on the include path).
 #ifndef NIXL_B200_FAKE_CUDA_RUNTIME_H
@@ -142,6 +143,12 @@ void enqueueDelay(cudaStream_t stream, unsigned microseconds);
 // Number of devices the stand-in reports (environment FAKE_CUDA_DEVICES, default 2); tasks run so far.
 int deviceCount();
 uint64_t tasksRun();
+// "Virtual memory management" allocations (what cuMemCreate + cuMemMap give: PyTorch's expandable segments, engines' own
+// pools): `chunks` physical allocations of `chunk_bytes` mapped back to back into one address range of `device`.  CUDA
+// IPC refuses such memory; it is shared through the driver's export / import calls, which the stand-in offers through
+// cudaGetDriverEntryPoint.
+void *mallocVmm(size_t chunk_bytes, int chunks, int device);
+void freeVmm(void *ptr);
 // Failure injection for the stand-in kernels: the next `count` launches of that kind fail with cudaErrorUnknown.
 enum class LaunchKind { Copy = 0, Signal = 1, Proxy = 2 };
 void failLaunches(LaunchKind kind, int count);

@@ -18,6 +18,7 @@
 
 #include <fcntl.h>
 #include <sys/mman.h>
+#include <sys/stat.h>
 #include <unistd.h>
 
 // ---------------------------------------------------------------- streams and events
@@ -77,6 +78,8 @@ struct Allocation {
     size_t size;
     int device;
     std::string shm; // name of the shared-memory object behind it (device memory another process can map), or empty
+    int vmmFd = -1;  // >= 0: one physical allocation of a virtual-memory range (its memory object); CUDA IPC refuses it
+    bool mapped = false; // a mapping of an imported allocation (cuMemMap)
 };
 struct HostRange {
     size_t size;
@@ -162,6 +165,41 @@ void enqueueDelay(cudaStream_t stream, unsigned microseconds) {
 }
 int deviceCount() { return rt().devices; }
 uint64_t tasksRun() { return g_tasksRun.load(); }
+void *mallocVmm(size_t chunk_bytes, int chunks, int device) {
+    if (chunk_bytes == 0 || chunk_bytes % 4096 || chunks <= 0) return nullptr;
+    const size_t total = chunk_bytes * static_cast<size_t>(chunks);
+    char *va = static_cast<char *>(::mmap(nullptr, total, PROT_NONE, MAP_PRIVATE | MAP_ANONYMOUS | MAP_NORESERVE, -1, 0));
+    if (va == MAP_FAILED) return nullptr;
+    for (int i = 0; i < chunks; ++i) {
+        const int fd = ::memfd_create("fakecuda-vmm", MFD_CLOEXEC);
+        if (fd < 0 || ::ftruncate(fd, static_cast<off_t>(chunk_bytes)) != 0 ||
+            ::mmap(va + i * chunk_bytes, chunk_bytes, PROT_READ | PROT_WRITE, MAP_SHARED | MAP_FIXED, fd, 0) == MAP_FAILED)
+            return nullptr;
+        std::lock_guard<std::mutex> g(rt().mu);
+        Allocation a{chunk_bytes, device, std::string()};
+        a.vmmFd = fd;
+        rt().device[reinterpret_cast<uintptr_t>(va + i * chunk_bytes)] = a;
+    }
+    std::memset(va, 0xcd, total);
+    return va;
+}
+void freeVmm(void *ptr) {
+    // every chunk that starts at or behind ptr and continues the range
+    uintptr_t p = reinterpret_cast<uintptr_t>(ptr);
+    for (;;) {
+        Allocation a;
+        {
+            std::lock_guard<std::mutex> g(rt().mu);
+            auto it = rt().device.find(p);
+            if (it == rt().device.end() || it->second.vmmFd < 0) return;
+            a = it->second;
+            rt().device.erase(it);
+        }
+        ::close(a.vmmFd);
+        ::munmap(reinterpret_cast<void *>(p), a.size);
+        p += a.size;
+    }
+}
 static std::atomic<int> g_failLaunches[3];
 void failLaunches(LaunchKind kind, int count) { g_failLaunches[static_cast<int>(kind)].store(count); }
 bool takeLaunchFailure(LaunchKind kind) {
@@ -491,7 +529,7 @@ cudaError_t cudaIpcGetMemHandle(cudaIpcMemHandle_t *handle, void *ptr) {
     if (!handle) return fail(cudaErrorInvalidValue);
     std::lock_guard<std::mutex> g(rt().mu);
     auto it = rt().device.find(reinterpret_cast<uintptr_t>(ptr));
-    if (it == rt().device.end()) return fail(cudaErrorInvalidValue); // must be the base of an allocation
+    if (it == rt().device.end() || it->second.vmmFd >= 0 || it->second.mapped) return fail(cudaErrorInvalidValue); // the base of a cudaMalloc allocation only
     IpcPayload pl{};
     pl.base = reinterpret_cast<uintptr_t>(ptr);
     pl.pid = static_cast<uint64_t>(::getpid());
@@ -543,14 +581,93 @@ static int fakeGetAddressRange(unsigned long long *base, size_t *size, unsigned 
     return 0;
 }
 
+// ---- the driver's virtual-memory calls (signatures as the backend's function-pointer types) ----
+namespace {
+struct VmmHandle {
+    int fd;
+    size_t size;
+};
+int vmmRetain(unsigned long long *handle, void *addr) {
+    std::lock_guard<std::mutex> g(rt().mu);
+    uintptr_t base = 0;
+    const Allocation *a = rt().findDevice(reinterpret_cast<uintptr_t>(addr), &base);
+    if (!a || a->vmmFd < 0) return 1; // not memory of that kind
+    *handle = reinterpret_cast<uintptr_t>(new VmmHandle{::dup(a->vmmFd), a->size});
+    return 0;
+}
+int vmmExport(void *out, unsigned long long handle, int, unsigned long long) {
+    auto *h = reinterpret_cast<VmmHandle *>(static_cast<uintptr_t>(handle));
+    const int fd = ::dup(h->fd);
+    if (fd < 0) return 1;
+    *static_cast<int *>(out) = fd;
+    return 0;
+}
+int vmmImport(unsigned long long *handle, void *os_handle, int) {
+    const int fd = static_cast<int>(reinterpret_cast<uintptr_t>(os_handle));
+    struct stat st{};
+    if (::fstat(fd, &st) != 0) return 1;
+    *handle = reinterpret_cast<uintptr_t>(new VmmHandle{::dup(fd), static_cast<size_t>(st.st_size)});
+    return 0;
+}
+int vmmRelease(unsigned long long handle) {
+    auto *h = reinterpret_cast<VmmHandle *>(static_cast<uintptr_t>(handle));
+    ::close(h->fd);
+    delete h;
+    return 0;
+}
+int vmmReserve(unsigned long long *ptr, size_t size, size_t, unsigned long long, unsigned long long) {
+    void *p = ::mmap(nullptr, size, PROT_NONE, MAP_PRIVATE | MAP_ANONYMOUS | MAP_NORESERVE, -1, 0);
+    if (p == MAP_FAILED) return 2;
+    *ptr = reinterpret_cast<uintptr_t>(p);
+    return 0;
+}
+int vmmAddressFree(unsigned long long ptr, size_t size) { return ::munmap(reinterpret_cast<void *>(static_cast<uintptr_t>(ptr)), size) == 0 ? 0 : 1; }
+int vmmMapCall(unsigned long long ptr, size_t size, size_t offset, unsigned long long handle, unsigned long long) {
+    auto *h = reinterpret_cast<VmmHandle *>(static_cast<uintptr_t>(handle));
+    if (offset + size > h->size) return 1;
+    void *p = ::mmap(reinterpret_cast<void *>(static_cast<uintptr_t>(ptr)), size, PROT_READ | PROT_WRITE, MAP_SHARED | MAP_FIXED, h->fd, static_cast<off_t>(offset));
+    if (p == MAP_FAILED) return 1;
+    std::lock_guard<std::mutex> g(rt().mu);
+    Allocation a{size, t_device, std::string()};
+    a.mapped = true;
+    rt().device[static_cast<uintptr_t>(ptr)] = a;
+    return 0;
+}
+int vmmUnmapCall(unsigned long long ptr, size_t size) {
+    {
+        std::lock_guard<std::mutex> g(rt().mu);
+        rt().device.erase(static_cast<uintptr_t>(ptr));
+    }
+    void *p = ::mmap(reinterpret_cast<void *>(static_cast<uintptr_t>(ptr)), size, PROT_NONE, MAP_PRIVATE | MAP_ANONYMOUS | MAP_FIXED | MAP_NORESERVE, -1, 0);
+    return p == MAP_FAILED ? 1 : 0;
+}
+int vmmSetAccess(unsigned long long, size_t, const void *, size_t) { return 0; }
+} // namespace
+
 cudaError_t cudaGetDriverEntryPoint(const char *symbol, void **fn, unsigned long long, enum cudaDriverEntryPointQueryResult *result) {
     if (!symbol || !fn) return fail(cudaErrorInvalidValue);
-    if (std::strcmp(symbol, "cuMemGetAddressRange") == 0) {
-        *fn = reinterpret_cast<void *>(&fakeGetAddressRange);
-        if (result) *result = cudaDriverEntryPointSuccess;
-        return cudaSuccess;
-    }
-    *fn = nullptr; // the virtual-memory entry points do not exist here: exports through file descriptors stay off
+    static const struct {
+        const char *name;
+        void *fn;
+    } table[] = {
+        {"cuMemGetAddressRange", reinterpret_cast<void *>(&fakeGetAddressRange)},
+        {"cuMemRetainAllocationHandle", reinterpret_cast<void *>(&vmmRetain)},
+        {"cuMemExportToShareableHandle", reinterpret_cast<void *>(&vmmExport)},
+        {"cuMemImportFromShareableHandle", reinterpret_cast<void *>(&vmmImport)},
+        {"cuMemRelease", reinterpret_cast<void *>(&vmmRelease)},
+        {"cuMemAddressReserve", reinterpret_cast<void *>(&vmmReserve)},
+        {"cuMemAddressFree", reinterpret_cast<void *>(&vmmAddressFree)},
+        {"cuMemMap", reinterpret_cast<void *>(&vmmMapCall)},
+        {"cuMemUnmap", reinterpret_cast<void *>(&vmmUnmapCall)},
+        {"cuMemSetAccess", reinterpret_cast<void *>(&vmmSetAccess)},
+    };
+    for (const auto &e : table)
+        if (std::strcmp(symbol, e.name) == 0) {
+            *fn = e.fn;
+            if (result) *result = cudaDriverEntryPointSuccess;
+            return cudaSuccess;
+        }
+    *fn = nullptr;
     if (result) *result = cudaDriverEntryPointSymbolNotFound;
     return cudaSuccess;
 }

@@ -4,6 +4,8 @@
 // preparation (merging, tables, path choice), stream-ordered posting, completion words and their pools, the proxy's
 // ring / exit / relaunch protocol, release of requests in flight, the notification ring, threads.  What it cannot
 // show is anything inside the real kernels; those are covered on GPUs (tests/test_gpu_*.py).
+#include <fcntl.h>
+
 #include <atomic>
 #include <chrono>
 #include <cstdlib>
@@ -488,6 +490,82 @@ TEST_CASE(memory_views_hold_what_the_kernels_will_read) {
     CHECK(p.a.prepMemView(bad, bv) != NIXL_SUCCESS);
     p.a.releaseMemView(lv);
     p.a.releaseMemView(rv);
+}
+
+TEST_CASE(memory_from_the_virtual_memory_calls_is_exported_allocation_by_allocation) {
+    // Four allocations behind one address range on GPU 1; the registration covers the back half of the first, the two
+    // in the middle and the front half of the last.  CUDA IPC refuses such memory, so the backend exports each
+    // allocation as a file descriptor and serves them from its descriptor server; deregistration closes them.
+    auto open_fds = [] {
+        int n = 0;
+        for (int fd = 0; fd < 4096; ++fd) n += ::fcntl(fd, F_GETFD) != -1;
+        return n;
+    };
+    constexpr size_t chunk = 1 << 20;
+    auto *vm = static_cast<uint8_t *>(fake_cuda::mallocVmm(chunk, 4, 1));
+    CHECK(vm != nullptr);
+    cudaIpcMemHandle_t ipc;
+    CHECK(cudaIpcGetMemHandle(&ipc, vm) != cudaSuccess);
+    cudaGetLastError();
+    cudaPointerAttributes attr{};
+    CHECK_EQ(cudaPointerGetAttributes(&attr, vm + 3 * chunk + 5), cudaSuccess);
+    CHECK(attr.type == cudaMemoryTypeDevice && attr.device == 1);
+
+    const std::string an = "fg_vm_a" + std::to_string(++g_serial), bn = "fg_vm_b" + std::to_string(g_serial);
+    nixlAgent a(an, nixlAgentConfig(false)), b(bn, nixlAgentConfig(false));
+    nixlBackendH *ha = nullptr, *hb = nullptr;
+    CHECK(a.createBackend("NVLINK", {}, ha) == NIXL_SUCCESS && b.createBackend("NVLINK", {}, hb) == NIXL_SUCCESS);
+    DevBuf src(0, 3 * chunk);
+    src.randomize(99);
+    uint8_t *win = vm + chunk / 2;
+    const size_t win_len = 3 * chunk;
+    std::memset(win, 0, win_len);
+    nixl_reg_dlist_t ra(VRAM_SEG), rb(VRAM_SEG);
+    ra.addDesc(nixlBlobDesc(reinterpret_cast<uintptr_t>(src.p), src.bytes, 0, ""));
+    rb.addDesc(nixlBlobDesc(reinterpret_cast<uintptr_t>(win), win_len, 1, ""));
+    CHECK(a.registerMem(ra) == NIXL_SUCCESS);
+    CHECK(b.registerMem(rb) == NIXL_SUCCESS); // starts the descriptor server (a socket and a wake-up pipe stay open)
+    const int with_one = open_fds();
+    CHECK_EQ(b.deregisterMem(rb), NIXL_SUCCESS);
+    CHECK_EQ(open_fds(), with_one - 4); // one descriptor per allocation touched
+    for (int round = 0; round < 20; ++round) { // and none is leaked over registrations
+        CHECK(b.registerMem(rb) == NIXL_SUCCESS);
+        CHECK_EQ(open_fds(), with_one);
+        if (round < 19) CHECK_EQ(b.deregisterMem(rb), NIXL_SUCCESS);
+    }
+    // a range that runs past the last allocation has no export: it still registers (this process can use it) ...
+    // but one that is not device memory at all is refused
+    nixl_reg_dlist_t past(VRAM_SEG);
+    past.addDesc(nixlBlobDesc(reinterpret_cast<uintptr_t>(vm) + 4 * chunk, 4096, 1, ""));
+    CHECK(b.registerMem(past) != NIXL_SUCCESS);
+
+    nixl_blob_t md;
+    std::string name;
+    b.getLocalMD(md);
+    CHECK(a.loadRemoteMD(md, name) == NIXL_SUCCESS);
+    // pieces that cross the boundaries between allocations
+    nixl_xfer_dlist_t l(VRAM_SEG), r(VRAM_SEG);
+    std::vector<uint8_t> expect(win_len, 0);
+    for (int i = 0; i < 12; ++i) {
+        const size_t off = size_t(i) * 250000 + 64, len = 200000 + 16 * i;
+        l.addDesc(nixlBasicDesc(reinterpret_cast<uintptr_t>(src.p) + off, len, 0));
+        r.addDesc(nixlBasicDesc(reinterpret_cast<uintptr_t>(win) + off, len, 1));
+        std::memcpy(expect.data() + off, src.p + off, len);
+    }
+    nixlXferReqH *req = nullptr;
+    CHECK(a.createXferReq(NIXL_WRITE, l, r, bn, req) == NIXL_SUCCESS);
+    CHECK(a.postXferReq(req) >= 0);
+    CHECK_EQ(waitDone(a, req), NIXL_SUCCESS);
+    CHECK(std::memcmp(win, expect.data(), win_len) == 0);
+    CHECK_EQ(a.releaseXferReq(req), NIXL_SUCCESS);
+    CHECK_EQ(a.invalidateRemoteMD(bn), NIXL_SUCCESS);
+    CHECK_EQ(b.deregisterMem(rb), NIXL_SUCCESS);
+    CHECK_EQ(a.deregisterMem(ra), NIXL_SUCCESS);
+    for (int d = 0; d < 2; ++d) {
+        cudaSetDevice(d);
+        cudaDeviceSynchronize();
+    }
+    fake_cuda::freeVmm(vm);
 }
 
 TEST_CASE(launch_failures_are_reported_and_leave_the_engine_usable) {

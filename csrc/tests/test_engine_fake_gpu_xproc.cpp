@@ -3,7 +3,9 @@
 // the shape of CUDA IPC.  Covered: the published registration (IPC handle, offset, GPU UUID), the opened-handle cache
 // and its release, the choice between copy kernel, copy engines and doorbell proxy for another process's memory, the
 // notification ring across processes (the target learns of a WRITE that the initiator never polls), READ, and a
-// target that exits.  The process forks before anything starts a thread.
+// target that exits.  The whole run is done twice: with cudaMalloc memory (shared by IPC handle) and with memory from
+// the virtual-memory calls (five allocations behind one address range, shared as file descriptors over the target's
+// descriptor server and mapped again in the initiator).  Every process forks before anything in it starts a thread.
 #include <sys/mman.h>
 #include <sys/wait.h>
 #include <unistd.h>
@@ -56,14 +58,21 @@ int failures = 0;
     } while (0)
 
 // ------------------------------------------------------------------ target (child process)
-int target(Shared *sh) {
+int target(Shared *sh, bool vmm) {
     nixlPluginManager::getInstance().addPluginDirectory(FAKE_GPU_PLUGIN_DIR);
     nixlAgent agent("xp_target", nixlAgentConfig(false));
     nixlBackendH *h = nullptr;
     if (agent.createBackend("NVLINK", {}, h) != NIXL_SUCCESS) return 10;
     cudaSetDevice(1);
-    uint8_t *buf = nullptr;
-    if (cudaMalloc(reinterpret_cast<void **>(&buf), kBytes) != cudaSuccess) return 11;
+    uint8_t *buf = nullptr, *vm = nullptr;
+    if (vmm) {
+        // 8 MiB that start in the middle of the first of five 2 MiB allocations and end in the middle of the last
+        vm = static_cast<uint8_t *>(fake_cuda::mallocVmm(2 << 20, 5, 1));
+        if (!vm) return 11;
+        buf = vm + (1 << 20) + 4096;
+    } else if (cudaMalloc(reinterpret_cast<void **>(&buf), kBytes) != cudaSuccess) {
+        return 11;
+    }
     std::memset(buf, 0, kBytes);
     nixl_reg_dlist_t reg(VRAM_SEG);
     reg.addDesc(nixlBlobDesc(reinterpret_cast<uintptr_t>(buf), kBytes, 1, ""));
@@ -98,7 +107,8 @@ int target(Shared *sh) {
     sh->stage.store(6);
     if (!waitStage(sh, 7)) return 17;
     agent.deregisterMem(reg);
-    cudaFree(buf);
+    if (vmm) fake_cuda::freeVmm(vm);
+    else cudaFree(buf);
     return 0; // the agent goes away with the process: the initiator must notice
 }
 
@@ -206,14 +216,33 @@ void initiator(Shared *sh, pid_t child) {
 
 } // namespace
 
-int main() {
+int scenario(bool vmm) {
     auto *sh = static_cast<Shared *>(::mmap(nullptr, sizeof(Shared), PROT_READ | PROT_WRITE, MAP_SHARED | MAP_ANONYMOUS, -1, 0));
     if (sh == MAP_FAILED) return 99;
     new (&sh->stage) std::atomic<int>(0);
     const pid_t child = ::fork(); // before the stand-in runtime or an agent has started any thread
-    if (child == 0) ::_exit(target(sh));
+    if (child == 0) ::_exit(target(sh, vmm));
     initiator(sh, child);
-    std::printf("%s between_processes_on_the_stand_in_runtime\n", failures ? "[FAIL]" : "[ OK ]");
-    std::printf("1 cases, %d failed\n", failures ? 1 : 0);
-    return failures ? 1 : 0;
+    return failures;
+}
+
+int main() {
+    // One process per run, so that each run's pair forks from a process that has never started a thread.
+    const char *names[2] = {"between_processes_over_ipc_handles", "between_processes_over_exported_allocations"};
+    int failed = 0;
+    for (int vmm = 0; vmm < 2; ++vmm) {
+        std::fflush(stdout);
+        const pid_t run = ::fork();
+        if (run == 0) {
+            const int f = scenario(vmm != 0);
+            std::fflush(stdout);
+            ::_exit(f ? 1 : 0);
+        }
+        int status = 0;
+        const bool ok = ::waitpid(run, &status, 0) == run && WIFEXITED(status) && WEXITSTATUS(status) == 0;
+        std::printf("%s %s\n", ok ? "[ OK ]" : "[FAIL]", names[vmm]);
+        failed += !ok;
+    }
+    std::printf("2 cases, %d failed\n", failed);
+    return failed ? 1 : 0;
 }
