@@ -69,10 +69,12 @@ nixlPluginManager::nixlPluginManager() {
     const std::string here = selfDir();
     dirs_.push_back(here + "/plugins");
     dirs_.push_back(here);
-    // Names of the reference's network transports resolve to the NVLink backend: inside one
-    // NVLink domain it is the engine that moves DRAM and VRAM between agents, whatever fabric
-    // the caller's configuration was written for.  A real plug-in of such a name wins.
-    for (const char *name : {"UCX", "UCX_MO", "LIBFABRIC", "MOONCAKE", "UCCL", "GPUNETIO"}) aliases_[name] = "NVLINK";
+    // Names of the reference's transports without a plug-in of that name in this build.  UCX (and the GPU-initiated
+    // GPUNETIO) resolve to the NVLink backend: inside one NVLink domain it is the engine that moves DRAM and VRAM
+    // between agents, whatever fabric the caller's configuration was written for.  The transports that only exist to
+    // reach other nodes resolve to the TCP backend, the one engine here that does.  A real plug-in of such a name wins.
+    for (const char *name : {"UCX", "UCX_MO", "GPUNETIO"}) aliases_[name] = "NVLINK";
+    for (const char *name : {"LIBFABRIC", "MOONCAKE", "UCCL"}) aliases_[name] = "TCP";
 }
 
 void nixlPluginManager::addPluginDirectory(const std::string &dir) {

@@ -244,7 +244,8 @@ TEST_CASE(plugin_manager_discovery) {
     CHECK(pm.loadBackendPlugin("MOCK") == mock); // cached
     CHECK(mock->getBackendOptions().count("async_polls") == 1);
     CHECK(pm.resolveAlias("UCX") == "NVLINK" && pm.resolveAlias("POSIX") == "POSIX");
-    for (const char *fabric : {"LIBFABRIC", "MOONCAKE", "UCCL", "GPUNETIO", "UCX_MO"}) CHECK(pm.resolveAlias(fabric) == "NVLINK");
+    for (const char *fabric : {"GPUNETIO", "UCX_MO"}) CHECK(pm.resolveAlias(fabric) == "NVLINK");
+    for (const char *fabric : {"LIBFABRIC", "MOONCAKE", "UCCL"}) CHECK(pm.resolveAlias(fabric) == "TCP"); // node-to-node transports
     // static registration
     pm.registerStaticBackend("STATIC_NULL", []() -> nixlBackendPlugin * { return nullptr; });
     CHECK(pm.loadBackendPlugin("STATIC_NULL") == nullptr); // creator returned null -> refused

@@ -568,6 +568,73 @@ TEST_CASE(memory_from_the_virtual_memory_calls_is_exported_allocation_by_allocat
     fake_cuda::freeVmm(vm);
 }
 
+TEST_CASE(device_memory_crosses_the_tcp_backend_through_its_staging_buffers) {
+    // The TCP backend built against the stand-in runtime: device memory on either end is staged through a pinned buffer
+    // (4 MiB pieces), host memory is not.  9 MiB and a bit, so that the staging loop runs more than twice per message set.
+    const std::string an = "fg_tcp_a" + std::to_string(++g_serial), bn = "fg_tcp_b" + std::to_string(g_serial);
+    nixlAgent a(an, nixlAgentConfig(false)), b(bn, nixlAgentConfig(false));
+    nixlBackendH *ha = nullptr, *hb = nullptr;
+    const nixl_b_params_t params = {{"address", "127.0.0.1"}, {"rails", "2"}, {"chunk_bytes", "6291456"}};
+    CHECK(a.createBackend("TCP", params, ha) == NIXL_SUCCESS && b.createBackend("TCP", params, hb) == NIXL_SUCCESS);
+    constexpr size_t kBytes = (9 << 20) + 12345;
+    DevBuf src(0, kBytes), dst(1, kBytes, 0);
+    src.randomize(4242);
+    std::vector<uint8_t> host(kBytes, 0);
+    nixl_reg_dlist_t ra(VRAM_SEG), rb(VRAM_SEG), rh(DRAM_SEG);
+    ra.addDesc(nixlBlobDesc(reinterpret_cast<uintptr_t>(src.p), kBytes, 0, ""));
+    rb.addDesc(nixlBlobDesc(reinterpret_cast<uintptr_t>(dst.p), kBytes, 1, ""));
+    rh.addDesc(nixlBlobDesc(reinterpret_cast<uintptr_t>(host.data()), kBytes, 0, ""));
+    CHECK(a.registerMem(ra) == NIXL_SUCCESS && b.registerMem(rb) == NIXL_SUCCESS && b.registerMem(rh) == NIXL_SUCCESS);
+    // a descriptor that names the wrong GPU, and host memory passed off as device memory, are refused at registration
+    nixl_reg_dlist_t wrong(VRAM_SEG), fake(VRAM_SEG);
+    wrong.addDesc(nixlBlobDesc(reinterpret_cast<uintptr_t>(src.p), 4096, 1, ""));
+    fake.addDesc(nixlBlobDesc(reinterpret_cast<uintptr_t>(host.data()), 4096, 0, ""));
+    CHECK(a.registerMem(wrong) != NIXL_SUCCESS);
+    CHECK(a.registerMem(fake) != NIXL_SUCCESS);
+    nixl_blob_t md;
+    std::string name;
+    b.getLocalMD(md);
+    CHECK_EQ(a.loadRemoteMD(md, name), NIXL_SUCCESS);
+
+    auto run = [&](nixl_xfer_op_t op, nixl_mem_t remote_mem, uintptr_t remote, int remote_dev) {
+        nixl_xfer_dlist_t l(VRAM_SEG), r(remote_mem);
+        // three pieces, the middle one larger than a staging buffer
+        const size_t cuts[4] = {0, 1000003, (6 << 20) + 77, kBytes};
+        for (int i = 0; i < 3; ++i) {
+            l.addDesc(nixlBasicDesc(reinterpret_cast<uintptr_t>(src.p) + cuts[i], cuts[i + 1] - cuts[i], 0));
+            r.addDesc(nixlBasicDesc(remote + cuts[i], cuts[i + 1] - cuts[i], remote_dev));
+        }
+        nixl_opt_args_t args;
+        args.notif = "staged";
+        nixlXferReqH *req = nullptr;
+        CHECK_EQ(a.createXferReq(op, l, r, bn, req, &args), NIXL_SUCCESS);
+        CHECK(a.postXferReq(req) >= 0);
+        CHECK_EQ(waitDone(a, req), NIXL_SUCCESS);
+        CHECK_EQ(a.releaseXferReq(req), NIXL_SUCCESS);
+    };
+    run(NIXL_WRITE, VRAM_SEG, reinterpret_cast<uintptr_t>(dst.p), 1); // device -> device
+    CHECK(std::memcmp(src.p, dst.p, kBytes) == 0);
+    run(NIXL_WRITE, DRAM_SEG, reinterpret_cast<uintptr_t>(host.data()), 0); // device -> host
+    CHECK(std::memcmp(src.p, host.data(), kBytes) == 0);
+    for (size_t i = 0; i < kBytes; i += 997) dst.p[i] = static_cast<uint8_t>(dst.p[i] + 3);
+    std::vector<uint8_t> expect(dst.p, dst.p + kBytes);
+    run(NIXL_READ, VRAM_SEG, reinterpret_cast<uintptr_t>(dst.p), 1); // device <- device
+    CHECK(std::memcmp(src.p, expect.data(), kBytes) == 0);
+    for (size_t i = 0; i < kBytes; i += 991) host[i] = static_cast<uint8_t>(host[i] + 5);
+    run(NIXL_READ, DRAM_SEG, reinterpret_cast<uintptr_t>(host.data()), 0); // device <- host
+    CHECK(std::memcmp(src.p, host.data(), kBytes) == 0);
+    int notifs = 0;
+    const auto end = clk::now() + std::chrono::seconds(5);
+    while (notifs < 4 && clk::now() < end) {
+        nixl_notifs_t n;
+        b.getNotifs(n);
+        notifs += static_cast<int>(n[an].size());
+    }
+    CHECK_EQ(notifs, 4);
+    CHECK_EQ(a.invalidateRemoteMD(bn), NIXL_SUCCESS);
+    CHECK(a.deregisterMem(ra) == NIXL_SUCCESS && b.deregisterMem(rb) == NIXL_SUCCESS && b.deregisterMem(rh) == NIXL_SUCCESS);
+}
+
 TEST_CASE(launch_failures_are_reported_and_leave_the_engine_usable) {
     using fake_cuda::LaunchKind;
     // a copy-kernel launch fails: the post says so, the request can be posted again and released

@@ -1,0 +1,451 @@
+// The TCP backend (src/plugins/extra/plugin_TCP.cpp) through the agent: the transport for peers that NVLink does not
+// reach.  Every case runs over real sockets on the loopback interface, which is as much of "another host" as one machine
+// offers: scattered WRITE and READ, requests cut into messages and dealt over several connections, notifications that
+// follow their data, a range whose registration went away at the target, threads, two processes, a target that exits, an
+// agent that comes back under its old name, and transfers of an agent to itself.
+#include <arpa/inet.h>
+#include <netinet/in.h>
+#include <sys/mman.h>
+#include <sys/socket.h>
+#include <sys/wait.h>
+#include <unistd.h>
+
+#include <array>
+#include <atomic>
+#include <chrono>
+#include <cstring>
+#include <random>
+#include <thread>
+
+#include "harness.h"
+#include "nixl.h"
+
+namespace {
+
+using clk = std::chrono::steady_clock;
+
+nixl_status_t waitDone(nixlAgent &a, nixlXferReqH *req, int seconds = 30) {
+    nixl_status_t st;
+    const auto end = clk::now() + std::chrono::seconds(seconds);
+    while ((st = a.getXferStatus(req)) == NIXL_IN_PROG && clk::now() < end) {}
+    return st;
+}
+
+std::vector<std::string> collect(nixlAgent &agent, const std::string &from, size_t want, int seconds = 5) {
+    std::vector<std::string> got;
+    const auto end = clk::now() + std::chrono::seconds(seconds);
+    while (got.size() < want && clk::now() < end) {
+        nixl_notifs_t n;
+        agent.getNotifs(n);
+        for (auto &m : n[from]) got.push_back(m);
+    }
+    return got;
+}
+
+int g_serial = 0;
+
+struct Pair {
+    std::string an, bn;
+    std::unique_ptr<nixlAgent> a, b;
+    std::vector<uint8_t> src, dst;
+    nixl_reg_dlist_t ra{DRAM_SEG}, rb{DRAM_SEG};
+    Pair(size_t bytes, const nixl_b_params_t &params = {{"address", "127.0.0.1"}})
+        : an("tcp_a" + std::to_string(++g_serial)), bn("tcp_b" + std::to_string(g_serial)), a(new nixlAgent(an, nixlAgentConfig(false))),
+          b(new nixlAgent(bn, nixlAgentConfig(false))), src(bytes), dst(bytes, 0) {
+        nixlBackendH *ha = nullptr, *hb = nullptr;
+        if (a->createBackend("TCP", params, ha) != NIXL_SUCCESS || b->createBackend("TCP", params, hb) != NIXL_SUCCESS)
+            throw std::runtime_error("TCP backend unavailable");
+        std::mt19937 rng(1000 + g_serial);
+        for (size_t i = 0; i + 4 <= bytes; i += 4) {
+            const uint32_t v = rng();
+            std::memcpy(src.data() + i, &v, 4);
+        }
+        ra.addDesc(nixlBlobDesc(reinterpret_cast<uintptr_t>(src.data()), src.size(), 0, ""));
+        rb.addDesc(nixlBlobDesc(reinterpret_cast<uintptr_t>(dst.data()), dst.size(), 0, ""));
+        if (a->registerMem(ra) != NIXL_SUCCESS || b->registerMem(rb) != NIXL_SUCCESS) throw std::runtime_error("registration");
+        nixl_blob_t md;
+        std::string name;
+        b->getLocalMD(md);
+        if (a->loadRemoteMD(md, name) != NIXL_SUCCESS) throw std::runtime_error("metadata");
+        a->getLocalMD(md);
+        if (b->loadRemoteMD(md, name) != NIXL_SUCCESS) throw std::runtime_error("metadata");
+    }
+    nixlXferReqH *request(nixl_xfer_op_t op, const std::vector<std::array<size_t, 3>> &cuts, const nixl_opt_args_t *args = nullptr) {
+        nixl_xfer_dlist_t l(DRAM_SEG), r(DRAM_SEG);
+        for (auto &c : cuts) { // {local offset, remote offset, length}
+            l.addDesc(nixlBasicDesc(reinterpret_cast<uintptr_t>(src.data()) + c[0], c[2], 0));
+            r.addDesc(nixlBasicDesc(reinterpret_cast<uintptr_t>(dst.data()) + c[1], c[2], 0));
+        }
+        nixlXferReqH *req = nullptr;
+        if (a->createXferReq(op, l, r, bn, req, args) != NIXL_SUCCESS) throw std::runtime_error("createXferReq");
+        return req;
+    }
+};
+
+} // namespace
+
+TEST_CASE(scattered_write_then_read_between_two_agents) {
+    Pair p(4 << 20);
+    std::vector<std::array<size_t, 3>> cuts;
+    std::vector<uint8_t> expect(p.dst.size(), 0);
+    for (size_t i = 0; i < 60; ++i) {
+        const size_t lo = i * 60000 + 13, ro = (59 - i) * 60000 + 7, len = 1 + i * 997;
+        cuts.push_back({lo, ro, len});
+        std::memcpy(expect.data() + ro, p.src.data() + lo, len);
+    }
+    nixlXferReqH *w = p.request(NIXL_WRITE, cuts);
+    CHECK(p.a->postXferReq(w) >= 0);
+    CHECK_EQ(waitDone(*p.a, w), NIXL_SUCCESS);
+    CHECK(p.dst == expect);
+    // change the target's bytes and READ them back into the places they came from
+    for (auto &x : p.dst) x = static_cast<uint8_t>(x ^ 0x5a);
+    nixlXferReqH *r = p.request(NIXL_READ, cuts);
+    CHECK(p.a->postXferReq(r) >= 0);
+    CHECK_EQ(waitDone(*p.a, r), NIXL_SUCCESS);
+    for (auto &c : cuts) CHECK(std::memcmp(p.src.data() + c[0], p.dst.data() + c[1], c[2]) == 0);
+    // the same request again, as the agent allows once the last post has completed
+    CHECK(p.a->postXferReq(w) >= 0);
+    CHECK_EQ(waitDone(*p.a, w), NIXL_SUCCESS);
+    CHECK_EQ(p.a->releaseXferReq(w), NIXL_SUCCESS);
+    CHECK_EQ(p.a->releaseXferReq(r), NIXL_SUCCESS);
+    // the request ran on this backend and no other
+    nixlXferReqH *q = p.request(NIXL_WRITE, {{0, 0, 64}});
+    nixlBackendH *used = nullptr;
+    CHECK_EQ(p.a->queryXferBackend(q, used), NIXL_SUCCESS);
+    CHECK(used != nullptr);
+    CHECK_EQ(p.a->releaseXferReq(q), NIXL_SUCCESS);
+}
+
+TEST_CASE(a_large_request_is_dealt_over_the_rails_and_small_descriptors_share_messages) {
+    Pair p(40 << 20, {{"address", "127.0.0.1"}, {"rails", "3"}, {"chunk_bytes", "1048576"}});
+    // one descriptor of 33 MiB and a bit (34 messages over three connections) ...
+    const size_t big = (33 << 20) + 4321;
+    nixlXferReqH *w = p.request(NIXL_WRITE, {{5, 5, big}});
+    CHECK(p.a->postXferReq(w) >= 0);
+    CHECK_EQ(waitDone(*p.a, w), NIXL_SUCCESS);
+    CHECK(std::memcmp(p.src.data() + 5, p.dst.data() + 5, big) == 0);
+    CHECK_EQ(p.a->releaseXferReq(w), NIXL_SUCCESS);
+    // ... and five thousand of 512 bytes in reverse order (256 per message)
+    std::vector<std::array<size_t, 3>> cuts;
+    const size_t base = 34 << 20;
+    for (size_t i = 0; i < 5000; ++i) cuts.push_back({base + i * 1024, base + (4999 - i) * 1024, 512});
+    nixlXferReqH *s = p.request(NIXL_WRITE, cuts);
+    CHECK(p.a->postXferReq(s) >= 0);
+    CHECK_EQ(waitDone(*p.a, s), NIXL_SUCCESS);
+    for (auto &c : cuts) CHECK(std::memcmp(p.src.data() + c[0], p.dst.data() + c[1], 512) == 0);
+    CHECK_EQ(p.a->releaseXferReq(s), NIXL_SUCCESS);
+    // READ of the large range the other way round
+    std::memset(p.src.data() + 5, 0, big);
+    nixlXferReqH *r = p.request(NIXL_READ, {{5, 5, big}});
+    CHECK(p.a->postXferReq(r) >= 0);
+    CHECK_EQ(waitDone(*p.a, r), NIXL_SUCCESS);
+    CHECK(std::memcmp(p.src.data() + 5, p.dst.data() + 5, big) == 0);
+    CHECK_EQ(p.a->releaseXferReq(r), NIXL_SUCCESS);
+}
+
+TEST_CASE(a_notification_follows_its_data_and_plain_notifications_arrive_in_order) {
+    Pair p(8 << 20, {{"address", "127.0.0.1"}, {"rails", "4"}, {"chunk_bytes", "65536"}});
+    for (int round = 0; round < 20; ++round) {
+        std::memset(p.dst.data(), 0, p.dst.size());
+        nixl_opt_args_t args;
+        args.notif = "round " + std::to_string(round);
+        nixlXferReqH *w = p.request(NIXL_WRITE, {{0, 0, p.src.size()}}, &args);
+        CHECK(p.a->postXferReq(w) >= 0);
+        // the target only looks at its notifications; when one is there, every byte is
+        auto got = collect(*p.b, p.an, 1);
+        CHECK_EQ(got.size(), size_t(1));
+        CHECK(got[0] == args.notif);
+        CHECK(p.dst == p.src);
+        CHECK_EQ(waitDone(*p.a, w), NIXL_SUCCESS);
+        CHECK_EQ(p.a->releaseXferReq(w), NIXL_SUCCESS);
+    }
+    for (int i = 0; i < 50; ++i) CHECK_EQ(p.a->genNotif(p.bn, "n" + std::to_string(i)), NIXL_SUCCESS);
+    auto got = collect(*p.b, p.an, 50);
+    CHECK_EQ(got.size(), size_t(50));
+    for (int i = 0; i < 50; ++i) CHECK(got[i] == "n" + std::to_string(i));
+    // and the other way, on connections of the other agent's own
+    CHECK_EQ(p.b->genNotif(p.an, std::string("\0binary\xff", 8)), NIXL_SUCCESS);
+    auto back = collect(*p.a, p.bn, 1);
+    CHECK_EQ(back.size(), size_t(1));
+    CHECK(back[0] == std::string("\0binary\xff", 8));
+}
+
+TEST_CASE(a_range_whose_registration_went_away_is_refused_and_the_connection_survives) {
+    Pair p(1 << 20);
+    // a second registration at the target, published, then withdrawn behind the initiator's back
+    std::vector<uint8_t> extra(1 << 16, 0x11);
+    nixl_reg_dlist_t re(DRAM_SEG);
+    re.addDesc(nixlBlobDesc(reinterpret_cast<uintptr_t>(extra.data()), extra.size(), 0, ""));
+    CHECK_EQ(p.b->registerMem(re), NIXL_SUCCESS);
+    nixl_blob_t md;
+    std::string name;
+    p.b->getLocalMD(md);
+    CHECK_EQ(p.a->loadRemoteMD(md, name), NIXL_SUCCESS);
+    nixl_xfer_dlist_t l(DRAM_SEG), r(DRAM_SEG);
+    l.addDesc(nixlBasicDesc(reinterpret_cast<uintptr_t>(p.src.data()), 4096, 0));
+    r.addDesc(nixlBasicDesc(reinterpret_cast<uintptr_t>(extra.data()), 4096, 0));
+    nixlXferReqH *w = nullptr, *rd = nullptr;
+    CHECK_EQ(p.a->createXferReq(NIXL_WRITE, l, r, p.bn, w), NIXL_SUCCESS);
+    CHECK_EQ(p.a->createXferReq(NIXL_READ, l, r, p.bn, rd), NIXL_SUCCESS);
+    CHECK(p.a->postXferReq(w) >= 0);
+    CHECK_EQ(waitDone(*p.a, w), NIXL_SUCCESS);
+    CHECK(std::memcmp(extra.data(), p.src.data(), 4096) == 0);
+    CHECK_EQ(p.b->deregisterMem(re), NIXL_SUCCESS);
+    std::memset(extra.data(), 0x22, extra.size());
+    const std::vector<uint8_t> before = p.src;
+    CHECK(p.a->postXferReq(w) >= 0);
+    CHECK_EQ(waitDone(*p.a, w), NIXL_ERR_INVALID_PARAM); // the target's answer
+    CHECK(extra[0] == 0x22 && extra[4095] == 0x22);        // and nothing was written
+    CHECK(p.a->postXferReq(rd) >= 0);
+    CHECK_EQ(waitDone(*p.a, rd), NIXL_ERR_INVALID_PARAM);
+    CHECK(p.src == before);
+    // the connections are still good for what is registered
+    nixlXferReqH *ok = p.request(NIXL_WRITE, {{0, 0, 100000}});
+    CHECK(p.a->postXferReq(ok) >= 0);
+    CHECK_EQ(waitDone(*p.a, ok), NIXL_SUCCESS);
+    CHECK(std::memcmp(p.dst.data(), p.src.data(), 100000) == 0);
+    for (auto *q : {w, rd, ok}) CHECK_EQ(p.a->releaseXferReq(q), NIXL_SUCCESS);
+}
+
+TEST_CASE(threads_post_side_by_side_over_shared_connections) {
+    Pair p(16 << 20, {{"address", "127.0.0.1"}, {"rails", "2"}, {"chunk_bytes", "262144"}});
+    constexpr int kThreads = 6;
+    std::atomic<int> bad{0};
+    std::vector<std::thread> th;
+    for (int t = 0; t < kThreads; ++t)
+        th.emplace_back([&, t] {
+            const size_t lane = size_t(t) * (2 << 20);
+            for (int i = 0; i < 40; ++i) {
+                const size_t len = 1000 + size_t(i) * 50000 % (2 << 20);
+                nixl_opt_args_t args;
+                args.notif = "t" + std::to_string(t);
+                nixlXferReqH *w = p.request(i % 4 == 3 ? NIXL_READ : NIXL_WRITE, {{lane, lane, len}}, i % 5 == 0 ? &args : nullptr);
+                if (p.a->postXferReq(w) < 0 || waitDone(*p.a, w) != NIXL_SUCCESS) ++bad;
+                if (std::memcmp(p.src.data() + lane, p.dst.data() + lane, len) != 0) ++bad;
+                if (p.a->releaseXferReq(w) != NIXL_SUCCESS) ++bad;
+            }
+        });
+    for (auto &t : th) t.join();
+    CHECK_EQ(bad.load(), 0);
+    CHECK_EQ(collect(*p.b, p.an, kThreads * 8).size(), size_t(kThreads * 8));
+}
+
+TEST_CASE(an_agent_moves_data_and_notifies_within_itself) {
+    nixlAgent a("tcp_self", nixlAgentConfig(false));
+    nixlBackendH *h = nullptr;
+    CHECK_EQ(a.createBackend("TCP", {{"address", "127.0.0.1"}}, h), NIXL_SUCCESS);
+    std::vector<uint8_t> x(1 << 16), y(1 << 16, 0);
+    for (size_t i = 0; i < x.size(); ++i) x[i] = static_cast<uint8_t>(i * 7);
+    nixl_reg_dlist_t reg(DRAM_SEG);
+    reg.addDesc(nixlBlobDesc(reinterpret_cast<uintptr_t>(x.data()), x.size(), 0, ""));
+    reg.addDesc(nixlBlobDesc(reinterpret_cast<uintptr_t>(y.data()), y.size(), 0, ""));
+    CHECK_EQ(a.registerMem(reg), NIXL_SUCCESS);
+    nixl_xfer_dlist_t l(DRAM_SEG), r(DRAM_SEG);
+    l.addDesc(nixlBasicDesc(reinterpret_cast<uintptr_t>(x.data()), x.size(), 0));
+    r.addDesc(nixlBasicDesc(reinterpret_cast<uintptr_t>(y.data()), y.size(), 0));
+    nixl_opt_args_t args;
+    args.notif = "to myself";
+    nixlXferReqH *w = nullptr;
+    CHECK_EQ(a.createXferReq(NIXL_WRITE, l, r, "tcp_self", w, &args), NIXL_SUCCESS);
+    CHECK(a.postXferReq(w) >= 0);
+    CHECK_EQ(waitDone(a, w), NIXL_SUCCESS);
+    CHECK(x == y);
+    auto got = collect(a, "tcp_self", 1);
+    CHECK_EQ(got.size(), size_t(1));
+    CHECK(got[0] == "to myself");
+    CHECK_EQ(a.releaseXferReq(w), NIXL_SUCCESS);
+    CHECK_EQ(a.deregisterMem(reg), NIXL_SUCCESS);
+}
+
+TEST_CASE(a_target_that_is_gone_is_reported_and_one_that_comes_back_under_its_name_is_reached_again) {
+    Pair p(1 << 20);
+    nixlXferReqH *w = p.request(NIXL_WRITE, {{0, 0, 4096}});
+    CHECK(p.a->postXferReq(w) >= 0);
+    CHECK_EQ(waitDone(*p.a, w), NIXL_SUCCESS);
+    p.b->deregisterMem(p.rb);
+    p.b.reset(); // the agent and its listener are gone
+    nixl_status_t st = p.a->postXferReq(w);
+    if (st >= 0) st = waitDone(*p.a, w);
+    CHECK_EQ(st, NIXL_ERR_REMOTE_DISCONNECT);
+    // the agent has dropped what it knew of the peer
+    CHECK_EQ(p.a->checkRemoteMD(p.bn, nixl_xfer_dlist_t(DRAM_SEG)), NIXL_ERR_NOT_FOUND);
+    p.a->releaseXferReq(w);
+    // the peer starts again under its name (another port, another engine) and publishes itself
+    p.b.reset(new nixlAgent(p.bn, nixlAgentConfig(false)));
+    nixlBackendH *hb = nullptr;
+    CHECK_EQ(p.b->createBackend("TCP", {{"address", "127.0.0.1"}}, hb), NIXL_SUCCESS);
+    CHECK_EQ(p.b->registerMem(p.rb), NIXL_SUCCESS);
+    nixl_blob_t md;
+    std::string name;
+    p.b->getLocalMD(md);
+    CHECK_EQ(p.a->loadRemoteMD(md, name), NIXL_SUCCESS);
+    std::memset(p.dst.data(), 0, p.dst.size());
+    nixlXferReqH *again = p.request(NIXL_WRITE, {{100, 100, 50000}});
+    CHECK(p.a->postXferReq(again) >= 0);
+    CHECK_EQ(waitDone(*p.a, again), NIXL_SUCCESS);
+    CHECK(std::memcmp(p.src.data() + 100, p.dst.data() + 100, 50000) == 0);
+    CHECK_EQ(p.a->releaseXferReq(again), NIXL_SUCCESS);
+}
+
+TEST_CASE(a_listener_that_is_somebody_else_is_not_taken_for_the_peer) {
+    // The peer listened on a fixed port; it goes away and another agent's engine takes that port, as when the same port
+    // number answers on the wrong machine.  The introduction names the agent and engine it expects, the listener
+    // refuses it, and the post reports a peer that cannot be reached instead of writing into a stranger.
+    int probe = ::socket(AF_INET, SOCK_STREAM, 0);
+    sockaddr_in sa{};
+    sa.sin_family = AF_INET;
+    sa.sin_addr.s_addr = htonl(INADDR_LOOPBACK);
+    socklen_t len = sizeof(sa);
+    CHECK(probe >= 0 && ::bind(probe, reinterpret_cast<sockaddr *>(&sa), sizeof(sa)) == 0 &&
+          ::getsockname(probe, reinterpret_cast<sockaddr *>(&sa), &len) == 0);
+    const std::string port = std::to_string(ntohs(sa.sin_port));
+    ::close(probe);
+    const nixl_b_params_t fixed = {{"address", "127.0.0.1"}, {"port", port}};
+
+    nixlAgent ini("tcp_w_ini", nixlAgentConfig(false));
+    nixlBackendH *h = nullptr;
+    CHECK_EQ(ini.createBackend("TCP", {{"address", "127.0.0.1"}}, h), NIXL_SUCCESS);
+    std::vector<uint8_t> src(4096, 0x77), dst(4096, 0), other(4096, 0);
+    nixl_reg_dlist_t rs(DRAM_SEG), rd(DRAM_SEG), ro(DRAM_SEG);
+    rs.addDesc(nixlBlobDesc(reinterpret_cast<uintptr_t>(src.data()), src.size(), 0, ""));
+    rd.addDesc(nixlBlobDesc(reinterpret_cast<uintptr_t>(dst.data()), dst.size(), 0, ""));
+    ro.addDesc(nixlBlobDesc(reinterpret_cast<uintptr_t>(other.data()), other.size(), 0, ""));
+    CHECK_EQ(ini.registerMem(rs), NIXL_SUCCESS);
+    auto peer = std::make_unique<nixlAgent>("tcp_w_peer", nixlAgentConfig(false));
+    CHECK_EQ(peer->createBackend("TCP", fixed, h), NIXL_SUCCESS);
+    CHECK_EQ(peer->registerMem(rd), NIXL_SUCCESS);
+    nixl_blob_t md;
+    std::string name;
+    peer->getLocalMD(md);
+    CHECK_EQ(ini.loadRemoteMD(md, name), NIXL_SUCCESS);
+    nixl_xfer_dlist_t l(DRAM_SEG), r(DRAM_SEG);
+    l.addDesc(nixlBasicDesc(reinterpret_cast<uintptr_t>(src.data()), 4096, 0));
+    r.addDesc(nixlBasicDesc(reinterpret_cast<uintptr_t>(dst.data()), 4096, 0));
+    nixlXferReqH *w = nullptr;
+    CHECK_EQ(ini.createXferReq(NIXL_WRITE, l, r, "tcp_w_peer", w), NIXL_SUCCESS);
+    peer->deregisterMem(rd);
+    peer.reset();
+    nixlAgent stranger("tcp_w_stranger", nixlAgentConfig(false));
+    CHECK_EQ(stranger.createBackend("TCP", fixed, h), NIXL_SUCCESS); // the same port, somebody else
+    CHECK_EQ(stranger.registerMem(ro), NIXL_SUCCESS);
+    nixl_status_t st = ini.postXferReq(w);
+    if (st >= 0) st = waitDone(ini, w);
+    CHECK_EQ(st, NIXL_ERR_REMOTE_DISCONNECT);
+    CHECK(dst == std::vector<uint8_t>(4096, 0) && other == std::vector<uint8_t>(4096, 0));
+    ini.releaseXferReq(w);
+    CHECK_EQ(stranger.deregisterMem(ro), NIXL_SUCCESS);
+    CHECK_EQ(ini.deregisterMem(rs), NIXL_SUCCESS);
+}
+
+TEST_CASE(between_two_processes_and_a_target_that_exits) {
+    constexpr size_t kBytes = 6 << 20;
+    struct Shared {
+        std::atomic<int> stage;
+        size_t mdLen, backLen;
+        char md[1 << 15], back[1 << 15];
+        uintptr_t addr;
+        uint64_t sum;
+        int notifs;
+    };
+    auto *sh = static_cast<Shared *>(::mmap(nullptr, sizeof(Shared), PROT_READ | PROT_WRITE, MAP_SHARED | MAP_ANONYMOUS, -1, 0));
+    CHECK(sh != MAP_FAILED);
+    new (&sh->stage) std::atomic<int>(0);
+    auto waitStage = [&](int s) {
+        const auto end = clk::now() + std::chrono::seconds(30);
+        while (sh->stage.load() < s && clk::now() < end) std::this_thread::sleep_for(std::chrono::milliseconds(1));
+        return sh->stage.load() >= s;
+    };
+    const pid_t child = ::fork();
+    if (child == 0) {
+        int rc = 0;
+        {
+            nixlAgent tgt("tcp_xp_target", nixlAgentConfig(false));
+            nixlBackendH *h = nullptr;
+            std::vector<uint8_t> buf(kBytes, 0);
+            nixl_reg_dlist_t r(DRAM_SEG);
+            r.addDesc(nixlBlobDesc(reinterpret_cast<uintptr_t>(buf.data()), buf.size(), 0, ""));
+            if (tgt.createBackend("TCP", {}, h) != NIXL_SUCCESS || tgt.registerMem(r) != NIXL_SUCCESS) ::_exit(10);
+            nixl_blob_t md;
+            tgt.getLocalMD(md);
+            if (md.size() > sizeof(sh->md)) ::_exit(11);
+            std::memcpy(sh->md, md.data(), md.size());
+            sh->mdLen = md.size();
+            sh->addr = reinterpret_cast<uintptr_t>(buf.data());
+            sh->stage.store(1);
+            if (!waitStage(2)) ::_exit(12);
+            std::string name;
+            if (tgt.loadRemoteMD(nixl_blob_t(sh->back, sh->backLen), name) != NIXL_SUCCESS) rc = 13;
+            int got = 0;
+            const auto end = clk::now() + std::chrono::seconds(20);
+            while (got < 1 && clk::now() < end) {
+                nixl_notifs_t n;
+                tgt.getNotifs(n);
+                got += static_cast<int>(n["tcp_xp_initiator"].size());
+            }
+            uint64_t sum = 0;
+            for (uint8_t x : buf) sum += x;
+            sh->sum = sum;
+            sh->notifs = got;
+            for (auto &x : buf) x = static_cast<uint8_t>(x + 1);
+            if (tgt.genNotif("tcp_xp_initiator", "changed") != NIXL_SUCCESS) rc = 15;
+            sh->stage.store(4);
+            if (!waitStage(5)) rc = 14;
+            if (tgt.deregisterMem(r) != NIXL_SUCCESS) rc = 16;
+        }
+        ::_exit(rc);
+    }
+    {
+        nixlAgent ini("tcp_xp_initiator", nixlAgentConfig(false));
+        nixlBackendH *h = nullptr;
+        CHECK_EQ(ini.createBackend("TCP", {}, h), NIXL_SUCCESS); // default addresses: the host's, loopback first for a peer on it
+        std::vector<uint8_t> buf(kBytes);
+        std::mt19937 rng(5);
+        for (auto &x : buf) x = static_cast<uint8_t>(rng());
+        nixl_reg_dlist_t reg(DRAM_SEG);
+        reg.addDesc(nixlBlobDesc(reinterpret_cast<uintptr_t>(buf.data()), buf.size(), 0, ""));
+        CHECK_EQ(ini.registerMem(reg), NIXL_SUCCESS);
+        CHECK(waitStage(1));
+        std::string name;
+        CHECK_EQ(ini.loadRemoteMD(nixl_blob_t(sh->md, sh->mdLen), name), NIXL_SUCCESS);
+        nixl_blob_t md;
+        ini.getLocalMD(md);
+        CHECK(md.size() <= sizeof(sh->back));
+        std::memcpy(sh->back, md.data(), md.size());
+        sh->backLen = md.size();
+        sh->stage.store(2);
+        nixl_xfer_dlist_t l(DRAM_SEG), r(DRAM_SEG);
+        l.addDesc(nixlBasicDesc(reinterpret_cast<uintptr_t>(buf.data()), kBytes, 0));
+        r.addDesc(nixlBasicDesc(sh->addr, kBytes, 0)); // an address of the other process
+        nixl_opt_args_t args;
+        args.notif = "written";
+        nixlXferReqH *w = nullptr, *rd = nullptr;
+        CHECK_EQ(ini.createXferReq(NIXL_WRITE, l, r, "tcp_xp_target", w, &args), NIXL_SUCCESS);
+        CHECK(ini.postXferReq(w) >= 0);
+        CHECK_EQ(waitDone(ini, w), NIXL_SUCCESS);
+        CHECK(waitStage(4));
+        uint64_t sum = 0;
+        for (uint8_t x : buf) sum += x;
+        CHECK_EQ(sh->notifs, 1);
+        CHECK(sh->sum == sum);
+        CHECK_EQ(collect(ini, "tcp_xp_target", 1).size(), size_t(1));
+        std::vector<uint8_t> expect = buf;
+        for (auto &x : expect) x = static_cast<uint8_t>(x + 1);
+        CHECK_EQ(ini.createXferReq(NIXL_READ, l, r, "tcp_xp_target", rd), NIXL_SUCCESS);
+        CHECK(ini.postXferReq(rd) >= 0);
+        CHECK_EQ(waitDone(ini, rd), NIXL_SUCCESS);
+        CHECK(buf == expect);
+        sh->stage.store(5);
+        int status = 0;
+        CHECK_EQ(::waitpid(child, &status, 0), child);
+        CHECK(WIFEXITED(status) && WEXITSTATUS(status) == 0);
+        nixl_status_t st = ini.postXferReq(rd);
+        if (st >= 0) st = waitDone(ini, rd);
+        CHECK_EQ(st, NIXL_ERR_REMOTE_DISCONNECT);
+        ini.releaseXferReq(w);
+        ini.releaseXferReq(rd);
+        ini.deregisterMem(reg);
+    }
+    ::munmap(sh, sizeof(Shared));
+}
+
+TEST_MAIN()

@@ -18,7 +18,7 @@ def _run(binary, *args, timeout=300):
     return subprocess.run([path, *args], env=ENV, capture_output=True, text=True, timeout=timeout, cwd=os.path.join(ROOT, "csrc"))
 
 
-@pytest.mark.parametrize("binary", ["test_plumbing", "test_core", "test_vmm_share", "test_agent_units", "test_notif_ring", "test_transfer", "test_engine_fake_gpu", "test_engine_fake_gpu_xproc"])
+@pytest.mark.parametrize("binary", ["test_plumbing", "test_core", "test_vmm_share", "test_agent_units", "test_notif_ring", "test_transfer", "test_engine_fake_gpu", "test_engine_fake_gpu_xproc", "test_tcp_backend"])
 def test_native_suite(binary):
     res = _run(binary)
     assert res.returncode == 0, res.stdout[-4000:] + res.stderr[-2000:]
@@ -138,3 +138,13 @@ def test_nixlbench_vram_schemes_on_the_stand_in_runtime(scheme, extra, flows):
     assert f"{flows} flow(s), VRAM" in res.stdout
     few = _nixlbench_fake_gpu("--mem", "VRAM", "--scheme", scheme, *extra, "--min", "65536", "--max", "65536", devices=2)
     assert few.returncode == 2 and "needs" in few.stderr  # more endpoints than GPUs
+
+
+def test_native_nixlbench_over_the_tcp_backend():
+    """The sweep driver with the node-to-node transport: host buffers of two agents, every block checked; one worker
+    thread and three, and the backend's own parameters through --param."""
+    for extra in ([], ["--num-threads", "3", "--batch", "6"], ["--op", "READ", "--param", "rails=2", "--param", "chunk_bytes=65536"]):
+        res = _nixlbench("--backend", "TCP", "--mem", "DRAM", "--min", "4096", "--max", "1048576", "--iters", "20", "--warmup", "3", "--check", *extra)
+        assert res.returncode == 0, res.stdout + res.stderr
+        rows = [l.split() for l in res.stdout.strip().splitlines() if l and l[0].isdigit()]
+        assert len(rows) == 9 and all(float(r[2]) > 0 for r in rows), res.stdout
