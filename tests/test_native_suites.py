@@ -18,7 +18,7 @@ def _run(binary, *args, timeout=300):
     return subprocess.run([path, *args], env=ENV, capture_output=True, text=True, timeout=timeout, cwd=os.path.join(ROOT, "csrc"))
 
 
-@pytest.mark.parametrize("binary", ["test_plumbing", "test_core", "test_vmm_share", "test_agent_units", "test_notif_ring", "test_transfer", "test_engine_fake_gpu", "test_engine_fake_gpu_xproc", "test_tcp_backend"])
+@pytest.mark.parametrize("binary", ["test_plumbing", "test_core", "test_vmm_share", "test_agent_units", "test_notif_ring", "test_transfer", "test_engine_fake_gpu", "test_engine_fake_gpu_xproc", "test_tcp_backend", "test_s3_rest"])
 def test_native_suite(binary):
     res = _run(binary)
     assert res.returncode == 0, res.stdout[-4000:] + res.stderr[-2000:]
