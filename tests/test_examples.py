@@ -69,3 +69,55 @@ def test_cpp_telemetry_reader_drains_a_ring_written_by_an_agent(tmp_path):
         writer.stdin.write("\n")
         writer.stdin.close()
         writer.wait(timeout=60)
+
+
+def test_remote_storage_example_between_a_server_and_a_client(tmp_path):
+    """examples/remote_storage_example.py: a client stores its blocks on a storage server and loads them back; the server
+    moves every block over the network backend and the storage backend, one stage behind the other."""
+    import socket
+
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    script = os.path.join(ROOT, "examples", "remote_storage_example.py")
+    (tmp_path / "agents.txt").write_text(f"# storage servers\nstore0 127.0.0.1 {port}\n")
+    common = ["--buf_size", str(256 << 10), "--batch_size", "6"]
+    server = subprocess.Popen([sys.executable, script, "--role", "server", "--agent_name", "store0", "--port", str(port), "--fileprefix", str(tmp_path / "srv"),
+                               "--requests", "2", *common], stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+    try:
+        assert "serving" in server.stdout.readline()
+        client = subprocess.run([sys.executable, script, "--role", "client", "--agent_name", "kv_client", "--agents_file", str(tmp_path / "agents.txt"),
+                                 "--fileprefix", str(tmp_path / "cli"), *common], capture_output=True, text=True, timeout=240)
+        assert client.returncode == 0, client.stdout[-2000:] + client.stderr[-2000:]
+        assert "all blocks verified" in client.stdout
+        assert server.wait(timeout=60) == 0, server.stderr.read()[-2000:]
+        # what the server keeps is what the client sent: block i is filled with (17 + i) % 251
+        for i in range(6):
+            data = (tmp_path / f"srv_store0_{i}.bin").read_bytes()
+            assert len(data) == 256 << 10 and set(data) == {(17 + i) % 251}
+    finally:
+        if server.poll() is None:
+            server.kill()
+        server.wait()
+
+
+def test_cpp_etcd_example_against_the_stand_in_gateway(tmp_path):
+    """examples/cpp/etcd_metadata.cpp: full metadata, partial metadata under a label, invalidation, all through the store."""
+    exe = str(tmp_path / "etcd_metadata")
+    lib = os.path.join(ROOT, "nixl_b200", "lib")
+    build = subprocess.run(["g++", "-std=c++20", "-O1", "-I" + os.path.join(ROOT, "csrc", "include"), "-I/usr/local/cuda/include",
+                            os.path.join(ROOT, "examples", "cpp", "etcd_metadata.cpp"), "-o", exe, "-L" + lib, "-lnixl", "-Wl,-rpath," + lib, "-pthread"],
+                           capture_output=True, text=True, timeout=300)
+    assert build.returncode == 0, build.stderr[-3000:]
+    gateway = subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "fake_etcd_gateway.py")], stdout=subprocess.PIPE, text=True)
+    try:
+        port = int(gateway.stdout.readline())
+        env = dict(os.environ, NIXL_ETCD_ENDPOINTS=f"http://127.0.0.1:{port}", NIXL_PLUGIN_DIR=os.path.join(lib, "plugins"))
+        env.pop("NIXL_TCPSTORE_ENDPOINT", None)
+        res = subprocess.run([exe], env=env, capture_output=True, text=True, timeout=120)
+        assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
+        assert "label 'extra_buffers'" in res.stdout and "prefill dropped it" in res.stdout
+    finally:
+        gateway.kill()
+        gateway.wait()
