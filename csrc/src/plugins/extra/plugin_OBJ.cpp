@@ -15,9 +15,12 @@
 //
 // The same engine is also built under the reference's other object-store names, with the
 // parameter that names the bucket in each of them (NIXL_OBJ_PLUGIN_NAME / NIXL_OBJ_BUCKET_PARAM):
-// AZURE_BLOB (`container_name`; src/plugins/azure_blob) and INFINIA (`dataset`;
-// src/plugins/infinia).  Their remaining parameters (account URLs, cluster and tenant names) are
-// accepted and ignored: there is no service to talk to.
+//   * AZURE_BLOB (`container_name`; src/plugins/azure_blob): Azure Blob Storage over REST (azure_rest.h) when a
+//     `connection_string` (or $AZURE_STORAGE_CONNECTION_STRING) names the account: Shared Key or shared access
+//     signature; blobs of at least `crtMinLimit` bytes go up as blocks side by side.  With only an `account_url`
+//     (Entra ID sign-in, not built) the directory store answers, with a warning.
+//   * INFINIA (`dataset`; src/plugins/infinia): the directory store only; its cluster and tenant parameters are
+//     accepted and ignored: there is no client for that service.
 #ifndef NIXL_OBJ_PLUGIN_NAME
 #define NIXL_OBJ_PLUGIN_NAME "OBJ"
 #endif
@@ -34,6 +37,7 @@
 #include <memory>
 
 #include "backend/backend_plugin.h"
+#include "plugins/extra/azure_rest.h"
 #include "plugins/extra/s3_rest.h"
 #include "utils/file/file_utils.h"
 #include "utils/log.h"
@@ -88,13 +92,15 @@ int objectIo(const ObjIo &io) {
 class ObjEngine final : public nixlBackendEngine {
 public:
     explicit ObjEngine(const nixlBackendInitParams *p) : nixlBackendEngine(p) {
-        if (std::strcmp(NIXL_OBJ_PLUGIN_NAME, "OBJ") != 0)
-            NIXL_WARN << NIXL_OBJ_PLUGIN_NAME << " backend: this build has no client for that service; objects are files in a local directory";
         std::string v;
-        if (std::strcmp(NIXL_OBJ_PLUGIN_NAME, "OBJ") == 0 && !setupS3()) {
+        const bool is_s3 = std::strcmp(NIXL_OBJ_PLUGIN_NAME, "OBJ") == 0, is_azure = std::strcmp(NIXL_OBJ_PLUGIN_NAME, "AZURE_BLOB") == 0;
+        if ((is_s3 && !setupS3()) || (is_azure && !setupAzure())) {
             initErr = true;
             return;
         }
+        if (!s3_ && !is_s3)
+            NIXL_WARN << NIXL_OBJ_PLUGIN_NAME << " backend: " << (is_azure ? "no connection string was given" : "this build has no client for that service")
+                      << "; objects are files in a local directory";
         if (!s3_) {
             if (getInitParam(NIXL_OBJ_BUCKET_PARAM, v) == NIXL_SUCCESS && !v.empty()) dir_ = v;
             else if (const char *e = std::getenv("NIXL_OBJ_BUCKET_DIR")) dir_ = e;
@@ -261,6 +267,34 @@ private:
         return true;
     }
 
+    // Azure Blob Storage when a connection string names an account (`connection_string` or
+    // $AZURE_STORAGE_CONNECTION_STRING; `container_name` or $AZURE_STORAGE_CONTAINER_NAME).  An `account_url` alone means
+    // signing in with Entra ID, which is not built: the directory store answers then, with a warning.
+    bool setupAzure() {
+        const std::string conn = param("connection_string", "AZURE_STORAGE_CONNECTION_STRING");
+        if (conn.empty()) return true;
+        nixl_azure::Config cfg;
+        std::string err;
+        if (!nixl_azure::parseConnectionString(conn, cfg, err)) {
+            NIXL_ERROR << "AZURE_BLOB backend: connection string: " << err;
+            return false;
+        }
+        cfg.container = param(NIXL_OBJ_BUCKET_PARAM, "AZURE_STORAGE_CONTAINER_NAME");
+        if (cfg.container.empty()) {
+            NIXL_ERROR << "AZURE_BLOB backend: no container (parameter 'container_name' or AZURE_STORAGE_CONTAINER_NAME)";
+            return false;
+        }
+        cfg.caBundle = param("ca_bundle", "AZURE_CA_BUNDLE");
+        const std::string limit = param("crtMinLimit");
+        if (!limit.empty() && std::atoll(limit.c_str()) > 0) largeLimit_ = static_cast<size_t>(std::atoll(limit.c_str()));
+        s3_ = std::make_unique<nixl_azure::Client>(cfg);
+        if (!s3_->usable()) {
+            NIXL_ERROR << "AZURE_BLOB backend: https endpoint but no TLS library (libssl) could be loaded";
+            return false;
+        }
+        return true;
+    }
+
     // Progress of one object moved in pieces.
     struct Pieces {
         ObjReq *req;
@@ -286,7 +320,7 @@ private:
         ps->req = req;
         ps->io = io;
         // S3 takes no part under 5 MiB except the last one; ranges of a download have no such rule.
-        ps->piece = io.put ? std::max<size_t>(largeLimit_, 5u << 20) : largeLimit_;
+        ps->piece = io.put ? std::max(largeLimit_, s3_->minPartBytes()) : largeLimit_;
         const size_t n = (io.len + ps->piece - 1) / ps->piece;
         ps->etags.resize(n);
         ps->left.store(n);
@@ -328,7 +362,7 @@ private:
     }
 
     std::string dir_;
-    std::unique_ptr<nixl_s3::Client> s3_;
+    std::unique_ptr<nixl_s3::ObjectService> s3_; // the object service (S3 or Azure Blob); none: a directory
     size_t largeLimit_ = 0; // objects of at least this many bytes move in pieces (0: never)
     std::unique_ptr<nixlThreadPool> pool_;
 };
@@ -348,7 +382,9 @@ extern "C" NIXL_PLUGIN_EXPORT nixlBackendPlugin *nixl_plugin_init() {
                                                         {"use_virtual_addressing", "false"},
                                                         {"ca_bundle", ""},
                                                         {"crtMinLimit", ""},
-                                                        {"payload_signing", ""}},
+                                                        {"payload_signing", ""},
+                                                        {"connection_string", ""},
+                                                        {"account_url", ""}},
                                                        {DRAM_SEG, OBJ_SEG});
 }
 extern "C" NIXL_PLUGIN_EXPORT void nixl_plugin_fini() {}

@@ -392,14 +392,38 @@ struct Response {
     std::string body;                           // what was not delivered into the caller's buffer
 };
 
-struct Config {
-    std::string scheme = "https", host, bucket, region = "us-east-1", caBundle;
+struct HttpConfig {
+    std::string scheme = "https", host, caBundle;
+    std::string connectHost; // where to connect when it is not `host` (tried first; `host` is the fall-back)
     uint16_t port = 0;
-    bool virtualAddressing = false;
-    bool signPayload = true; // hash the body of a PUT into the signature (off: "UNSIGNED-PAYLOAD")
     bool verifyTls = true;
     int timeoutMs = 30000;
+};
+
+struct Config : HttpConfig {
+    std::string bucket, region = "us-east-1";
+    bool virtualAddressing = false;
+    bool signPayload = true; // hash the body of a PUT into the signature (off: "UNSIGNED-PAYLOAD")
     Credentials cred;
+};
+
+// What the OBJ engine asks of an object service.  Every call returns the HTTP status (200, 206, 404, 403, ...) or 0 when
+// the service could not be reached.  A large object goes up in parts: create -> parts (any order, side by side) ->
+// complete (or abort).
+class ObjectService {
+public:
+    virtual ~ObjectService() = default;
+    virtual bool usable() const = 0;
+    virtual int putObject(const std::string &key, const void *data, size_t len, std::string *etag = nullptr) = 0;
+    virtual int getObject(const std::string &key, uint64_t offset, void *dst, size_t len) = 0;
+    virtual int headObject(const std::string &key, uint64_t *size) = 0;
+    virtual int deleteObject(const std::string &key) = 0;
+    virtual int createMultipart(const std::string &key, std::string &upload_id) = 0;
+    virtual int uploadPart(const std::string &key, const std::string &upload_id, int number, const void *data, size_t len, std::string &etag) = 0;
+    virtual int completeMultipart(const std::string &key, const std::string &upload_id, const std::vector<std::string> &etags) = 0;
+    virtual int abortMultipart(const std::string &key, const std::string &upload_id) = 0;
+    virtual size_t minPartBytes() const = 0; // no part but the last may be smaller
+    virtual std::string lastError() const = 0;
 };
 
 // "scheme://host[:port]" -> parts.  false: not an endpoint this client understands.
@@ -424,11 +448,11 @@ inline bool parseEndpoint(const std::string &url, std::string &scheme, std::stri
     return !host.empty();
 }
 
-// ------------------------------------------------------------------ the client
+// ------------------------------------------------------------------ HTTP/1.1 requests over a pool of connections
 
-class Client {
+class Http {
 public:
-    explicit Client(Config cfg) : cfg_(std::move(cfg)) {
+    explicit Http(HttpConfig cfg) : cfg_(std::move(cfg)) {
         if (cfg_.scheme == "https") {
             const Tls &t = Tls::get();
             if (t.ok && (tlsCtx_ = t.SSL_CTX_new(t.TLS_client_method()))) {
@@ -438,114 +462,43 @@ public:
             }
         }
     }
-    ~Client() {
+    ~Http() {
         idle_.clear();
         if (tlsCtx_) Tls::get().SSL_CTX_free(tlsCtx_);
     }
-    // https was asked for and no TLS library could be loaded
+    Http(const Http &) = delete;
+    Http &operator=(const Http &) = delete;
+    // false: https was asked for and no TLS library could be loaded
     bool usable() const { return cfg_.scheme != "https" || tlsCtx_; }
-    const Config &config() const { return cfg_; }
+    const HttpConfig &config() const { return cfg_; }
+    // "host" or "host:port" as it belongs into the Host header
+    std::string hostHeader() const {
+        const bool default_port = cfg_.port == (cfg_.scheme == "https" ? 443 : 80);
+        return cfg_.host + (default_port ? "" : ":" + std::to_string(cfg_.port));
+    }
 
-    // Each returns the HTTP status (200, 206, 404, 403, ...) or 0 when the service could not be reached.
-    int putObject(const std::string &key, const void *data, size_t len, std::string *etag = nullptr) {
-        Request r = base("PUT", key);
-        Response resp = exchange(r, data, len, nullptr, 0);
-        if (etag) *etag = resp.headers["etag"];
-        return note(resp, "PutObject", key);
-    }
-    int getObject(const std::string &key, uint64_t offset, void *dst, size_t len) {
-        if (len == 0) return headObject(key, nullptr);
-        Request r = base("GET", key);
-        r.headers["range"] = "bytes=" + std::to_string(offset) + "-" + std::to_string(offset + len - 1);
-        size_t got = 0;
-        Response resp = exchange(r, nullptr, 0, dst, len, &got);
-        if ((resp.status == 200 || resp.status == 206) && got != len) { // an object that ends before the range does
-            lastError_ = "GetObject " + key + ": the object ends inside the requested range";
-            return 416;
+    // Sends `head` (request line and headers, ending in an empty line) and `body`, reads the answer.  A successful
+    // answer's body goes into `sink` (up to sink_len bytes, `*got` says how many came), anything else into
+    // Response::body.  A connection that had been idle and fails before a single byte of the answer is tried once more
+    // on a fresh one.
+    Response roundTrip(const std::string &head, const void *body, size_t body_len, bool is_head, void *sink, size_t sink_len, size_t *got = nullptr) {
+        for (int attempt = 0; attempt < 2; ++attempt) {
+            std::unique_ptr<Conn> c = acquire();
+            if (!c) return Response{};
+            const bool was_reused = c->reused;
+            bool fresh_failure = false;
+            Response resp = onConnection(*c, head, body, body_len, is_head, sink, sink_len, got, fresh_failure);
+            if (resp.status > 0) {
+                auto it = resp.headers.find("connection");
+                if (c->isOpen() && (it == resp.headers.end() || it->second != "close")) release(std::move(c));
+                return resp;
+            }
+            if (!(was_reused && fresh_failure)) return resp;
         }
-        return note(resp, "GetObject", key);
-    }
-    int headObject(const std::string &key, uint64_t *size) {
-        Request r = base("HEAD", key);
-        Response resp = exchange(r, nullptr, 0, nullptr, 0);
-        if (size && resp.status == 200) *size = std::strtoull(resp.headers["content-length"].c_str(), nullptr, 10);
-        return note(resp, "HeadObject", key);
-    }
-    int deleteObject(const std::string &key) {
-        Request r = base("DELETE", key);
-        return note(exchange(r, nullptr, 0, nullptr, 0), "DeleteObject", key);
-    }
-    // Multipart upload: create -> parts (any order, in parallel) -> complete (or abort).
-    int createMultipart(const std::string &key, std::string &upload_id) {
-        Request r = base("POST", key);
-        r.query.emplace_back("uploads", "");
-        Response resp = exchange(r, nullptr, 0, nullptr, 0);
-        upload_id = between(resp.body, "<UploadId>", "</UploadId>");
-        if (resp.status == 200 && upload_id.empty()) resp.status = 500;
-        return note(resp, "CreateMultipartUpload", key);
-    }
-    int uploadPart(const std::string &key, const std::string &upload_id, int number, const void *data, size_t len, std::string &etag) {
-        Request r = base("PUT", key);
-        r.query.emplace_back("partNumber", std::to_string(number));
-        r.query.emplace_back("uploadId", upload_id);
-        Response resp = exchange(r, data, len, nullptr, 0);
-        etag = resp.headers["etag"];
-        return note(resp, "UploadPart", key);
-    }
-    int completeMultipart(const std::string &key, const std::string &upload_id, const std::vector<std::string> &etags) {
-        std::string xml = "<CompleteMultipartUpload>";
-        for (size_t i = 0; i < etags.size(); ++i)
-            xml += "<Part><PartNumber>" + std::to_string(i + 1) + "</PartNumber><ETag>" + etags[i] + "</ETag></Part>";
-        xml += "</CompleteMultipartUpload>";
-        Request r = base("POST", key);
-        r.query.emplace_back("uploadId", upload_id);
-        Response resp = exchange(r, xml.data(), xml.size(), nullptr, 0);
-        if (resp.status == 200 && resp.body.find("<Error>") != std::string::npos) resp.status = 500; // S3 reports some failures inside a 200
-        return note(resp, "CompleteMultipartUpload", key);
-    }
-    int abortMultipart(const std::string &key, const std::string &upload_id) {
-        Request r = base("DELETE", key);
-        r.query.emplace_back("uploadId", upload_id);
-        return note(exchange(r, nullptr, 0, nullptr, 0), "AbortMultipartUpload", key);
-    }
-    std::string lastError() const {
-        std::lock_guard<std::mutex> g(mu_);
-        return lastError_;
+        return Response{};
     }
 
 private:
-    static std::string between(const std::string &s, const std::string &a, const std::string &b) {
-        const size_t i = s.find(a);
-        if (i == std::string::npos) return "";
-        const size_t j = s.find(b, i + a.size());
-        return j == std::string::npos ? "" : s.substr(i + a.size(), j - i - a.size());
-    }
-
-    Request base(const char *method, const std::string &key) const {
-        Request r;
-        r.method = method;
-        const bool default_port = cfg_.port == (cfg_.scheme == "https" ? 443 : 80);
-        std::string host = cfg_.host + (default_port ? "" : ":" + std::to_string(cfg_.port));
-        if (cfg_.virtualAddressing) {
-            host = cfg_.bucket + "." + host;
-            r.path = "/" + key;
-        } else {
-            r.path = "/" + cfg_.bucket + "/" + key;
-        }
-        r.headers["host"] = host;
-        return r;
-    }
-
-    int note(const Response &resp, const char *what, const std::string &key) {
-        if (resp.status >= 200 && resp.status < 300) return resp.status;
-        std::lock_guard<std::mutex> g(mu_);
-        if (resp.status <= 0) lastError_ = std::string(what) + " " + key + ": no answer from " + cfg_.host + ":" + std::to_string(cfg_.port);
-        else
-            lastError_ = std::string(what) + " " + key + ": HTTP " + std::to_string(resp.status) + " " + between(resp.body, "<Code>", "</Code>") + " " +
-                between(resp.body, "<Message>", "</Message>");
-        return resp.status;
-    }
-
     std::unique_ptr<Conn> acquire() {
         {
             std::lock_guard<std::mutex> g(mu_);
@@ -556,8 +509,8 @@ private:
             }
         }
         auto c = std::make_unique<Conn>();
-        const std::string host = cfg_.virtualAddressing ? cfg_.bucket + "." + cfg_.host : cfg_.host;
-        if (!c->open(host, cfg_.port, tlsCtx_, cfg_.timeoutMs) && !(cfg_.virtualAddressing && c->open(cfg_.host, cfg_.port, tlsCtx_, cfg_.timeoutMs)))
+        if (!(!cfg_.connectHost.empty() && c->open(cfg_.connectHost, cfg_.port, tlsCtx_, cfg_.timeoutMs)) &&
+            !c->open(cfg_.host, cfg_.port, tlsCtx_, cfg_.timeoutMs))
             return nullptr;
         return c;
     }
@@ -565,42 +518,6 @@ private:
         c->reused = true;
         std::lock_guard<std::mutex> g(mu_);
         if (idle_.size() < 64) idle_.push_back(std::move(c));
-    }
-
-    // Signs and sends `r` with `body`, reads the answer.  A successful answer's body goes into `sink` (up to sink_len
-    // bytes, `*got` says how many), anything else into Response::body.  A connection that had been idle and fails before
-    // a single byte of the answer is tried once more on a fresh one.
-    Response exchange(Request &r, const void *body, size_t body_len, void *sink, size_t sink_len, size_t *got = nullptr) {
-        const std::string date = amzDateNow();
-        r.headers["x-amz-date"] = date;
-        if (body_len && cfg_.signPayload) r.payloadHash = hex(sha256(body, body_len));
-        else if (body_len) r.payloadHash = "UNSIGNED-PAYLOAD";
-        else r.payloadHash = hex(sha256("", 0));
-        r.headers["x-amz-content-sha256"] = r.payloadHash;
-        if (!cfg_.cred.sessionToken.empty()) r.headers["x-amz-security-token"] = cfg_.cred.sessionToken;
-        std::string head = r.method + " " + uriEncode(r.path, true);
-        const std::string q = canonicalQuery(r);
-        if (!q.empty()) head += "?" + q;
-        head += " HTTP/1.1\r\n";
-        for (const auto &kv : r.headers) head += kv.first + ": " + kv.second + "\r\n";
-        if (!cfg_.cred.empty()) head += "authorization: " + authorizationV4(r, cfg_.cred, cfg_.region, "s3", date) + "\r\n";
-        if (body_len || r.method == "PUT" || r.method == "POST") head += "content-length: " + std::to_string(body_len) + "\r\n";
-        head += "\r\n";
-
-        for (int attempt = 0; attempt < 2; ++attempt) {
-            std::unique_ptr<Conn> c = acquire();
-            if (!c) return Response{};
-            const bool was_reused = c->reused;
-            bool fresh_failure = false;
-            Response resp = onConnection(*c, head, body, body_len, r.method == "HEAD", sink, sink_len, got, fresh_failure);
-            if (resp.status > 0) {
-                auto it = resp.headers.find("connection");
-                if (c->isOpen() && (it == resp.headers.end() || it->second != "close")) release(std::move(c));
-                return resp;
-            }
-            if (!(was_reused && fresh_failure)) return resp;
-        }
-        return Response{};
     }
 
     Response onConnection(Conn &c, const std::string &head, const void *body, size_t body_len, bool is_head, void *sink, size_t sink_len,
@@ -711,10 +628,150 @@ private:
         }
     }
 
-    Config cfg_;
+    HttpConfig cfg_;
     void *tlsCtx_ = nullptr;
-    mutable std::mutex mu_;
+    std::mutex mu_;
     std::vector<std::unique_ptr<Conn>> idle_;
+};
+
+// ------------------------------------------------------------------ the client
+
+class Client final : public ObjectService {
+public:
+    explicit Client(Config cfg) : cfg_(std::move(cfg)), http_(withConnectHost(cfg_)) {}
+    bool usable() const override { return http_.usable(); }
+    const Config &config() const { return cfg_; }
+    size_t minPartBytes() const override { return 5u << 20; }
+
+    // Each returns the HTTP status (200, 206, 404, 403, ...) or 0 when the service could not be reached.
+    int putObject(const std::string &key, const void *data, size_t len, std::string *etag = nullptr) override {
+        Request r = base("PUT", key);
+        Response resp = exchange(r, data, len, nullptr, 0);
+        if (etag) *etag = resp.headers["etag"];
+        return note(resp, "PutObject", key);
+    }
+    int getObject(const std::string &key, uint64_t offset, void *dst, size_t len) override {
+        if (len == 0) return headObject(key, nullptr);
+        Request r = base("GET", key);
+        r.headers["range"] = "bytes=" + std::to_string(offset) + "-" + std::to_string(offset + len - 1);
+        size_t got = 0;
+        Response resp = exchange(r, nullptr, 0, dst, len, &got);
+        if ((resp.status == 200 || resp.status == 206) && got != len) { // an object that ends before the range does
+            lastError_ = "GetObject " + key + ": the object ends inside the requested range";
+            return 416;
+        }
+        return note(resp, "GetObject", key);
+    }
+    int headObject(const std::string &key, uint64_t *size) override {
+        Request r = base("HEAD", key);
+        Response resp = exchange(r, nullptr, 0, nullptr, 0);
+        if (size && resp.status == 200) *size = std::strtoull(resp.headers["content-length"].c_str(), nullptr, 10);
+        return note(resp, "HeadObject", key);
+    }
+    int deleteObject(const std::string &key) override {
+        Request r = base("DELETE", key);
+        return note(exchange(r, nullptr, 0, nullptr, 0), "DeleteObject", key);
+    }
+    // Multipart upload: create -> parts (any order, in parallel) -> complete (or abort).
+    int createMultipart(const std::string &key, std::string &upload_id) override {
+        Request r = base("POST", key);
+        r.query.emplace_back("uploads", "");
+        Response resp = exchange(r, nullptr, 0, nullptr, 0);
+        upload_id = between(resp.body, "<UploadId>", "</UploadId>");
+        if (resp.status == 200 && upload_id.empty()) resp.status = 500;
+        return note(resp, "CreateMultipartUpload", key);
+    }
+    int uploadPart(const std::string &key, const std::string &upload_id, int number, const void *data, size_t len, std::string &etag) override {
+        Request r = base("PUT", key);
+        r.query.emplace_back("partNumber", std::to_string(number));
+        r.query.emplace_back("uploadId", upload_id);
+        Response resp = exchange(r, data, len, nullptr, 0);
+        etag = resp.headers["etag"];
+        return note(resp, "UploadPart", key);
+    }
+    int completeMultipart(const std::string &key, const std::string &upload_id, const std::vector<std::string> &etags) override {
+        std::string xml = "<CompleteMultipartUpload>";
+        for (size_t i = 0; i < etags.size(); ++i)
+            xml += "<Part><PartNumber>" + std::to_string(i + 1) + "</PartNumber><ETag>" + etags[i] + "</ETag></Part>";
+        xml += "</CompleteMultipartUpload>";
+        Request r = base("POST", key);
+        r.query.emplace_back("uploadId", upload_id);
+        Response resp = exchange(r, xml.data(), xml.size(), nullptr, 0);
+        if (resp.status == 200 && resp.body.find("<Error>") != std::string::npos) resp.status = 500; // S3 reports some failures inside a 200
+        return note(resp, "CompleteMultipartUpload", key);
+    }
+    int abortMultipart(const std::string &key, const std::string &upload_id) override {
+        Request r = base("DELETE", key);
+        r.query.emplace_back("uploadId", upload_id);
+        return note(exchange(r, nullptr, 0, nullptr, 0), "AbortMultipartUpload", key);
+    }
+    std::string lastError() const override {
+        std::lock_guard<std::mutex> g(mu_);
+        return lastError_;
+    }
+
+private:
+    static std::string between(const std::string &s, const std::string &a, const std::string &b) {
+        const size_t i = s.find(a);
+        if (i == std::string::npos) return "";
+        const size_t j = s.find(b, i + a.size());
+        return j == std::string::npos ? "" : s.substr(i + a.size(), j - i - a.size());
+    }
+
+    Request base(const char *method, const std::string &key) const {
+        Request r;
+        r.method = method;
+        std::string host = http_.hostHeader();
+        if (cfg_.virtualAddressing) {
+            host = cfg_.bucket + "." + host;
+            r.path = "/" + key;
+        } else {
+            r.path = "/" + cfg_.bucket + "/" + key;
+        }
+        r.headers["host"] = host;
+        return r;
+    }
+
+    int note(const Response &resp, const char *what, const std::string &key) {
+        if (resp.status >= 200 && resp.status < 300) return resp.status;
+        std::lock_guard<std::mutex> g(mu_);
+        if (resp.status <= 0) lastError_ = std::string(what) + " " + key + ": no answer from " + cfg_.host + ":" + std::to_string(cfg_.port);
+        else
+            lastError_ = std::string(what) + " " + key + ": HTTP " + std::to_string(resp.status) + " " + between(resp.body, "<Code>", "</Code>") + " " +
+                between(resp.body, "<Message>", "</Message>");
+        return resp.status;
+    }
+
+    // Signs and sends `r` with `body`; the answer as Http::roundTrip gives it.
+    Response exchange(Request &r, const void *body, size_t body_len, void *sink, size_t sink_len, size_t *got = nullptr) {
+        const std::string date = amzDateNow();
+        r.headers["x-amz-date"] = date;
+        if (body_len && cfg_.signPayload) r.payloadHash = hex(sha256(body, body_len));
+        else if (body_len) r.payloadHash = "UNSIGNED-PAYLOAD";
+        else r.payloadHash = hex(sha256("", 0));
+        r.headers["x-amz-content-sha256"] = r.payloadHash;
+        if (!cfg_.cred.sessionToken.empty()) r.headers["x-amz-security-token"] = cfg_.cred.sessionToken;
+        std::string head = r.method + " " + uriEncode(r.path, true);
+        const std::string q = canonicalQuery(r);
+        if (!q.empty()) head += "?" + q;
+        head += " HTTP/1.1\r\n";
+        for (const auto &kv : r.headers) head += kv.first + ": " + kv.second + "\r\n";
+        if (!cfg_.cred.empty()) head += "authorization: " + authorizationV4(r, cfg_.cred, cfg_.region, "s3", date) + "\r\n";
+        if (body_len || r.method == "PUT" || r.method == "POST") head += "content-length: " + std::to_string(body_len) + "\r\n";
+        head += "\r\n";
+
+        return http_.roundTrip(head, body, body_len, r.method == "HEAD", sink, sink_len, got);
+    }
+
+    static HttpConfig withConnectHost(const Config &cfg) {
+        HttpConfig h = cfg;
+        if (cfg.virtualAddressing) h.connectHost = cfg.bucket + "." + cfg.host; // where it resolves; else the endpoint itself
+        return h;
+    }
+
+    Config cfg_;
+    Http http_;
+    mutable std::mutex mu_;
     std::string lastError_;
 };
 

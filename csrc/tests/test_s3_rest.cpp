@@ -1,8 +1,10 @@
 // The S3 REST client's primitives (src/plugins/extra/s3_rest.h) against published vectors: SHA-256 (FIPS 180-4
 // examples), HMAC-SHA-256 (RFC 4231), and the Signature Version 4 of the "GET object with a range" example of the S3
 // documentation; plus the pieces that are easy to get wrong (escaping, query order, endpoint parsing).  The requests
-// themselves are exercised against a server that checks signatures in tests/test_obj_s3.py.
+// themselves are exercised against a server that checks signatures in tests/test_obj_s3.py.  The Azure Blob client's
+// pieces (azure_rest.h) follow: base64 (RFC 4648 vectors), connection strings, the text a Shared Key signs.
 #include "harness.h"
+#include "plugins/extra/azure_rest.h"
 #include "plugins/extra/s3_rest.h"
 
 using namespace nixl_s3;
@@ -76,6 +78,61 @@ TEST_CASE(escaping_and_endpoints) {
     scheme = "http";
     CHECK(!parseEndpoint("http://host:99999", scheme, host, port));
     CHECK(!parseEndpoint("", scheme, host, port));
+}
+
+TEST_CASE(base64_of_rfc_4648_and_back) {
+    const char *plain[] = {"", "f", "fo", "foo", "foob", "fooba", "foobar"};
+    const char *coded[] = {"", "Zg==", "Zm8=", "Zm9v", "Zm9vYg==", "Zm9vYmE=", "Zm9vYmFy"};
+    for (int i = 0; i < 7; ++i) {
+        CHECK(nixl_azure::base64Encode(reinterpret_cast<const uint8_t *>(plain[i]), std::strlen(plain[i])) == coded[i]);
+        std::vector<uint8_t> back;
+        CHECK(nixl_azure::base64Decode(coded[i], back));
+        CHECK(std::string(back.begin(), back.end()) == plain[i]);
+    }
+    std::vector<uint8_t> junk;
+    CHECK(!nixl_azure::base64Decode("Zm9v!", junk));
+}
+
+TEST_CASE(azure_connection_strings) {
+    nixl_azure::Config c;
+    std::string err;
+    CHECK(nixl_azure::parseConnectionString("DefaultEndpointsProtocol=https;AccountName=acct;AccountKey=Zm9vYmFy;EndpointSuffix=core.windows.net", c, err));
+    CHECK(c.scheme == "https" && c.host == "acct.blob.core.windows.net" && c.port == 443 && c.account == "acct" && c.pathPrefix.empty());
+    CHECK(std::string(c.key.begin(), c.key.end()) == "foobar");
+    nixl_azure::Config dev;
+    CHECK(nixl_azure::parseConnectionString("UseDevelopmentStorage=true", dev, err));
+    CHECK(dev.scheme == "http" && dev.host == "127.0.0.1" && dev.port == 10000 && dev.account == "devstoreaccount1" && dev.pathPrefix == "/devstoreaccount1");
+    CHECK(dev.key.size() == 64);
+    nixl_azure::Config sas;
+    CHECK(nixl_azure::parseConnectionString("BlobEndpoint=https://acct2.blob.core.windows.net/;SharedAccessSignature=?sv=2021&sig=xyz", sas, err));
+    CHECK(sas.account == "acct2" && sas.sas == "sv=2021&sig=xyz" && sas.key.empty() && sas.pathPrefix.empty());
+    nixl_azure::Config bad;
+    CHECK(!nixl_azure::parseConnectionString("AccountName=x", bad, err) && err.find("Entra") != std::string::npos);
+    CHECK(!nixl_azure::parseConnectionString("AccountKey=Zm9v", bad, err));
+    CHECK(!nixl_azure::parseConnectionString("AccountName=x;AccountKey=***", bad, err));
+}
+
+TEST_CASE(the_text_a_shared_key_signs) {
+    nixl_azure::Request r;
+    r.method = "PUT";
+    r.path = "/devstoreaccount1/kv/a%20b.bin";
+    r.query = {{"comp", "block"}, {"blockid", "YmxvY2stMDAwMDAwMDE="}};
+    r.headers["x-ms-version"] = "2021-08-06";
+    r.headers["x-ms-date"] = "Fri, 26 Jun 2015 23:39:12 GMT";
+    r.headers["content-type"] = "application/octet-stream";
+    r.contentLength = 1024;
+    CHECK(nixl_azure::stringToSign(r, "devstoreaccount1") ==
+          "PUT\n\n\n1024\n\napplication/octet-stream\n\n\n\n\n\n\n"
+          "x-ms-date:Fri, 26 Jun 2015 23:39:12 GMT\nx-ms-version:2021-08-06\n"
+          "/devstoreaccount1/devstoreaccount1/kv/a%20b.bin\nblockid:YmxvY2stMDAwMDAwMDE=\ncomp:block");
+    // an empty body leaves the length field empty (service versions from 2015-02-21 on)
+    r.contentLength = 0;
+    r.method = "GET";
+    r.query.clear();
+    CHECK(nixl_azure::stringToSign(r, "a").compare(0, 7, "GET\n\n\n\n") == 0);
+    const std::vector<uint8_t> key = {'k', 'e', 'y'};
+    const std::string auth = nixl_azure::sharedKeyAuthorization(r, "a", key);
+    CHECK(auth.compare(0, 12, "SharedKey a:") == 0 && auth.size() == 12 + 44);
 }
 
 TEST_MAIN()

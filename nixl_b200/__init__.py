@@ -34,8 +34,8 @@ def add_plugin_directory(path: str) -> None:
     _bindings.add_plugin_directory(path)
 
 
-#: Engines that answer to the names of the reference's cloud / appliance plug-ins (AZURE_BLOB,
-#: INFINIA, HF3FS, GDS_MT) with local storage.  They are NOT clients of those services and are
+#: Engines that answer to the names of the reference's appliance plug-ins (INFINIA, HF3FS, GDS_MT)
+#: with local storage.  They are NOT clients of those services and are
 #: therefore not on the default search path; ``add_plugin_directory(STANDIN_PLUGIN_DIR)`` opts in.
 STANDIN_PLUGIN_DIR = _os.path.join(_HERE, "lib", "standin_plugins")
 
