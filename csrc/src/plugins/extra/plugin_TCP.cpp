@@ -10,7 +10,10 @@
 // Shape
 //   * Every engine listens on one port ("port" parameter, default: any).  The connection info it publishes holds the
 //     host name, the port and the addresses to try (the "address" parameter or NIXL_TCP_ADDRESS; otherwise every IPv4
-//     address of the host, loopback last; a peer on the same host tries loopback first).
+//     address of the host, loopback last; a peer on the same host tries loopback first).  `device_id` names the GPU
+//     this engine serves: the interfaces nearest to it in the PCI tree (utils/topology.h) come first.  With several
+//     addresses published, and `local_addresses` (a list, or "auto") on the initiator, connection k of a peer runs from
+//     local address k to the peer's address k: the rails spread over the interfaces of both hosts.
 //   * The initiator opens `rails` connections to a peer on first use.  A request is cut into messages of at most
 //     `chunk_bytes` of payload (many small descriptors share one message, a large one is split) which are dealt over
 //     the rails; each rail has a sender thread (queue) and a receiver thread (acknowledgements, READ replies), so a post
@@ -54,6 +57,7 @@
 #include "backend/backend_plugin.h"
 #include "utils/log.h"
 #include "utils/misc.h"
+#include "utils/topology.h"
 
 #ifndef NIXL_TCP_PLUGIN_NAME
 #define NIXL_TCP_PLUGIN_NAME "TCP"
@@ -166,13 +170,22 @@ void tuneSocket(int fd, int buf_bytes) {
     }
 }
 
-int connectTo(const std::string &ip, uint16_t port, int timeout_ms) {
+// `from`: the local address to leave from (empty: the kernel's choice by route).
+int connectTo(const std::string &ip, uint16_t port, int timeout_ms, const std::string &from = "") {
     sockaddr_in a{};
     a.sin_family = AF_INET;
     a.sin_port = htons(port);
     if (::inet_pton(AF_INET, ip.c_str(), &a.sin_addr) != 1) return -1;
     const int fd = ::socket(AF_INET, SOCK_STREAM | SOCK_NONBLOCK | SOCK_CLOEXEC, 0);
     if (fd < 0) return -1;
+    if (!from.empty()) {
+        sockaddr_in l{};
+        l.sin_family = AF_INET;
+        if (::inet_pton(AF_INET, from.c_str(), &l.sin_addr) != 1 || ::bind(fd, reinterpret_cast<sockaddr *>(&l), sizeof(l)) != 0) {
+            ::close(fd);
+            return -1;
+        }
+    }
     int rc = ::connect(fd, reinterpret_cast<sockaddr *>(&a), sizeof(a));
     if (rc != 0 && errno == EINPROGRESS) {
         pollfd p{fd, POLLOUT, 0};
@@ -189,18 +202,39 @@ int connectTo(const std::string &ip, uint16_t port, int timeout_ms) {
     return fd;
 }
 
-std::vector<std::string> hostAddresses() {
-    std::vector<std::string> out, loop;
+// Orders (interface, address) pairs so that the interfaces named in `near_first` come first, in that order.
+std::vector<std::string> orderByInterface(std::vector<std::pair<std::string, std::string>> found, const std::vector<std::string> &near_first) {
+    std::vector<std::string> out;
+    for (const auto &want : near_first)
+        for (auto &f : found)
+            if (f.first == want && !f.second.empty()) {
+                out.push_back(f.second);
+                f.second.clear();
+            }
+    for (const auto &f : found)
+        if (!f.second.empty()) out.push_back(f.second);
+    return out;
+}
+
+// The host's IPv4 addresses: interfaces near GPU `gpu` first when that is known (< 0: as the kernel lists them),
+// loopback last.
+std::vector<std::string> hostAddresses(int gpu) {
+    std::vector<std::pair<std::string, std::string>> found;
+    std::vector<std::string> loop;
     ifaddrs *ifs = nullptr;
     if (::getifaddrs(&ifs) == 0) {
         for (ifaddrs *i = ifs; i; i = i->ifa_next) {
             if (!i->ifa_addr || i->ifa_addr->sa_family != AF_INET || !(i->ifa_flags & IFF_UP)) continue;
             char buf[INET_ADDRSTRLEN];
             if (!::inet_ntop(AF_INET, &reinterpret_cast<sockaddr_in *>(i->ifa_addr)->sin_addr, buf, sizeof(buf))) continue;
-            ((i->ifa_flags & IFF_LOOPBACK) ? loop : out).push_back(buf);
+            if (i->ifa_flags & IFF_LOOPBACK) loop.push_back(buf);
+            else found.emplace_back(i->ifa_name, buf);
         }
         ::freeifaddrs(ifs);
     }
+    std::vector<std::string> near;
+    if (gpu >= 0) near = nixl::pciTopology::scan().interfacesNearGpu(static_cast<size_t>(gpu));
+    std::vector<std::string> out = orderByInterface(std::move(found), near);
     if (loop.empty()) loop.push_back("127.0.0.1");
     out.insert(out.end(), loop.begin(), loop.end());
     return out;
@@ -327,6 +361,7 @@ struct Post {
     bool hasNotif = false;
     std::string notif, peer;
     const Engine *engine = nullptr;
+    uint64_t bytes = 0, startNs = 0; // for the engine's running figures of what the path delivers
     void finishOne(int st);
 };
 
@@ -568,13 +603,21 @@ public:
         cuda_ = cudaGetDeviceCount(&n) == cudaSuccess && n > 0;
         if (!cuda_) cudaGetLastError();
 
+        const int gpu = static_cast<int>(std::clamp(paramLong(cp, "device_id", -1), -1L, 1023L));
         std::string addr;
         auto it = cp.find("address");
         if (it != cp.end()) addr = it->second;
         if (addr.empty())
             if (const char *e = std::getenv("NIXL_TCP_ADDRESS")) addr = e;
-        if (!addr.empty()) addrs_.push_back(addr);
-        else addrs_ = hostAddresses();
+        if (!addr.empty()) addrs_ = nixl_util::split(addr, ',');
+        else addrs_ = hostAddresses(gpu);
+        it = cp.find("local_addresses");
+        if (it != cp.end() && it->second == "auto") {
+            for (const auto &a2 : hostAddresses(gpu))
+                if (a2.compare(0, 4, "127.") != 0) localAddrs_.push_back(a2);
+        } else if (it != cp.end() && !it->second.empty()) {
+            localAddrs_ = nixl_util::split(it->second, ',');
+        }
 
         listenFd_ = ::socket(AF_INET, SOCK_STREAM | SOCK_CLOEXEC, 0);
         sockaddr_in a{};
@@ -839,6 +882,8 @@ public:
             post->finishOne(NIXL_SUCCESS);
             return static_cast<nixl_status_t>(post->status.load());
         }
+        post->bytes = total;
+        post->startNs = nixl_util::nowNs();
         post->pending.store(static_cast<int>(msgs.size()), std::memory_order_release);
         for (auto &m : msgs) {
             const uint32_t at = peer->next.fetch_add(1, std::memory_order_relaxed);
@@ -879,6 +924,30 @@ public:
         std::vector<std::shared_ptr<ClientConn>> rails;
         if (const nixl_status_t st = railsOf(*peer, rails); st != NIXL_SUCCESS) return st;
         return sendNotif(remote_agent, msg) ? NIXL_SUCCESS : NIXL_ERR_REMOTE_DISCONNECT;
+    }
+
+    // What finished requests have shown: small ones give the round trip, large ones the rate (running averages).
+    void observe(uint64_t bytes, uint64_t ns) const {
+        auto blend = [](std::atomic<double> &avg, double sample) {
+            const double old = avg.load(std::memory_order_relaxed);
+            avg.store(old == 0 ? sample : old * 0.875 + sample * 0.125, std::memory_order_relaxed);
+        };
+        if (bytes <= (16u << 10)) blend(seenLatencyUs_, static_cast<double>(ns) / 1e3);
+        else if (bytes >= (1u << 20) && ns) blend(seenBytesPerUs_, static_cast<double>(bytes) / (static_cast<double>(ns) / 1e3));
+    }
+    // Round trip plus bytes over the rate: measured on this engine's own finished requests when there are any, else a
+    // guess for a 25 Gb/s link.  The margin is wide: a shared network does not promise anything.
+    nixl_status_t estimateXferCost(const nixl_xfer_op_t &, const nixl_meta_dlist_t &local, const nixl_meta_dlist_t &, const std::string &,
+                                   nixlBackendReqH *const &, std::chrono::microseconds &duration, std::chrono::microseconds &err_margin,
+                                   nixl_cost_t &method, const nixl_opt_args_t *) const override {
+        double bytes = 0;
+        for (const auto &d : local) bytes += static_cast<double>(d.len);
+        const double lat = seenLatencyUs_.load(std::memory_order_relaxed), rate = seenBytesPerUs_.load(std::memory_order_relaxed);
+        const double us = (lat > 0 ? lat : 100.0) + bytes / (rate > 0 ? rate : 3000.0);
+        duration = std::chrono::microseconds(static_cast<int64_t>(us + 0.5));
+        err_margin = std::chrono::microseconds(static_cast<int64_t>(us * 0.5 + 1.0));
+        method = nixl_cost_t::ANALYTICAL_BACKEND;
+        return NIXL_SUCCESS;
     }
 
     // Queues a notification on the first live connection to `agent` (never opens one: connections' own threads call this).
@@ -929,7 +998,10 @@ private:
     }
 
     // One connection to the peer's listener, introduced and accepted; nullptr if no address answers as that engine.
-    std::shared_ptr<ClientConn> dial(const Peer &peer) const {
+    // Connection number `rail` starts with the peer's address number `rail` (of those that apply) and leaves from local
+    // address number `rail` when local addresses are configured: with several interfaces on either side the
+    // connections spread over them.
+    std::shared_ptr<ClientConn> dial(const Peer &peer, size_t rail) const {
         std::vector<std::string> order;
         const bool same_host = peer.host == host_;
         auto is_loop = [](const std::string &a) { return a.compare(0, 4, "127.") == 0; };
@@ -939,8 +1011,15 @@ private:
         for (const auto &a : peer.addrs)
             if (!is_loop(a)) order.push_back(a);
         if (order.empty()) order = peer.addrs; // only a loopback address was published (tests, an explicit "address")
+        // (loopback addresses come first for a peer on this host; they take turns among themselves, the rest follows)
+        size_t group = 0;
+        while (group < order.size() && is_loop(order[group]) == is_loop(order.front())) ++group;
+        std::rotate(order.begin(), order.begin() + static_cast<long>(rail % group), order.begin() + static_cast<long>(group));
+        const std::string from = localAddrs_.empty() ? std::string() : localAddrs_[rail % localAddrs_.size()];
         for (const auto &a : order) {
-            const int fd = connectTo(a, peer.port, connectTimeoutMs_);
+            int fd = connectTo(a, peer.port, connectTimeoutMs_, from);
+            if (fd < 0 && !from.empty()) fd = connectTo(a, peer.port, connectTimeoutMs_); // no route from there: any way will do
+
             if (fd < 0) continue;
             tuneSocket(fd, bufBytes_);
             // Say who we are and whom we expect: the same port number on another machine is somebody else.
@@ -985,7 +1064,7 @@ private:
         for (auto &r : old)
             if (!r->dead()) keep.push_back(r);
         while (static_cast<int>(keep.size()) < rails_) {
-            auto c2 = dial(peer);
+            auto c2 = dial(peer, keep.size());
             if (!c2) break;
             keep.push_back(std::move(c2));
         }
@@ -1138,7 +1217,8 @@ private:
     uint64_t tag_ = 0;
     uint16_t port_ = 0;
     std::string host_;
-    std::vector<std::string> addrs_;
+    std::vector<std::string> addrs_;      // published: where the listener can be reached
+    std::vector<std::string> localAddrs_; // where outgoing connections leave from, in turn (empty: the kernel's choice)
     int listenFd_ = -1;
     std::atomic<bool> stop_{false};
     std::thread listener_;
@@ -1151,6 +1231,7 @@ private:
     std::mutex servedMu_;
     std::vector<std::unique_ptr<ServerConn>> served_;
     mutable std::atomic<uint64_t> nextId_{1};
+    mutable std::atomic<double> seenLatencyUs_{0}, seenBytesPerUs_{0};
 };
 
 void Post::finishOne(int st) {
@@ -1162,6 +1243,7 @@ void Post::finishOne(int st) {
     int e = error.load();
     // The notification goes out before the request reads as complete: whoever sees SUCCESS may tear the agent down.
     if (e == NIXL_SUCCESS && hasNotif && !engine->sendNotif(peer, notif)) e = NIXL_ERR_REMOTE_DISCONNECT;
+    if (e == NIXL_SUCCESS && startNs) engine->observe(bytes, nixl_util::nowNs() - startNs);
     status.store(e, std::memory_order_release);
 }
 
@@ -1173,6 +1255,8 @@ extern "C" NIXL_PLUGIN_EXPORT nixlBackendPlugin *nixl_plugin_init() {
                                                      {"chunk_bytes", "4194304"},
                                                      {"port", "0"},
                                                      {"address", ""},
+                                                     {"local_addresses", ""},
+                                                     {"device_id", ""},
                                                      {"socket_buffer_bytes", "4194304"},
                                                      {"connect_timeout_ms", "3000"}},
                                                     {DRAM_SEG, VRAM_SEG});

@@ -15,6 +15,7 @@
 
 #include "harness.h"
 #include "utils/hw_info.h"
+#include "utils/topology.h"
 #include "utils/misc.h"
 #include "nixl.h"
 
@@ -313,6 +314,64 @@ TEST_CASE(hw_info_counts_devices_from_a_sysfs_tree) {
     CHECK(hw.toString().find("nvidia_gpus=2") != std::string::npos);
     const nixl::hwInfo none = nixl::hwInfo::scan(root + "/does_not_exist");
     CHECK_EQ(none.numNvidiaGpus, 0u);
+}
+
+TEST_CASE(topology_orders_network_interfaces_by_their_place_in_the_pci_tree) {
+    // A node in the shape of an 8-GPU NVLink box, two of its four PCIe switches shown: each switch carries GPUs and the
+    // NICs meant for them; the two sockets are NUMA nodes 0 and 1; a management NIC hangs off the chipset.
+    //   pci0000:15 (numa 0) - 15:01.0 - 16:00.0 +- 17:00.0 - 1b:00.0  GPU 0
+    //                                           +- 17:01.0 - 1c:00.0  NIC ib0
+    //                                           +- 17:02.0 - 1d:00.0  GPU 1
+    //   pci0000:00 (numa 0) - 00:1f.0 - 02:00.0                       NIC eno1 (management)
+    //   pci0000:97 (numa 1) - 97:01.0 - 98:00.0 +- 99:00.0 - 9b:00.0  GPU 2
+    //                                           +- 99:01.0 - 9c:00.0  NIC ib1 (two ports: ib1, ib1b)
+    char tmpl[] = "/tmp/nixl_topo_XXXXXX";
+    CHECK(::mkdtemp(tmpl) != nullptr);
+    const std::string base = tmpl, bus = base + "/bus";
+    CHECK(::mkdir(bus.c_str(), 0755) == 0);
+    auto mkdirs = [](const std::string &path) {
+        for (size_t i = 1; i <= path.size(); ++i)
+            if (i == path.size() || path[i] == '/') ::mkdir(path.substr(0, i).c_str(), 0755);
+    };
+    auto add = [&](const std::string &chain, const char *vendor, const char *cls, int numa, std::vector<std::string> ifs = {}) {
+        const std::string dir = base + "/devices/" + chain;
+        mkdirs(dir);
+        std::ofstream(dir + "/vendor") << vendor << "\n";
+        std::ofstream(dir + "/class") << cls << "\n";
+        std::ofstream(dir + "/device") << "0x2901\n";
+        std::ofstream(dir + "/numa_node") << numa << "\n";
+        for (const auto &i : ifs) mkdirs(dir + "/net/" + i);
+        const std::string bdf = chain.substr(chain.rfind('/') + 1);
+        CHECK(::symlink(dir.c_str(), (bus + "/" + bdf).c_str()) == 0);
+    };
+    const std::string sw0 = "pci0000:15/0000:15:01.0/0000:16:00.0/", sw1 = "pci0000:97/0000:97:01.0/0000:98:00.0/";
+    add(sw0 + "0000:17:00.0/0000:1b:00.0", "0x10de", "0x030200", 0);
+    add(sw0 + "0000:17:01.0/0000:1c:00.0", "0x15b3", "0x020700", 0, {"ib0"});
+    add(sw0 + "0000:17:02.0/0000:1d:00.0", "0x10de", "0x030200", 0);
+    add("pci0000:00/0000:00:1f.0/0000:02:00.0", "0x8086", "0x020000", 0, {"eno1"});
+    add(sw1 + "0000:99:00.0/0000:9b:00.0", "0x10de", "0x030200", 1);
+    add(sw1 + "0000:99:01.0/0000:9c:00.0", "0x15b3", "0x020700", 1, {"ib1", "ib1b"});
+    add("pci0000:00/0000:00:14.0", "0x8086", "0x0c0330", 0); // a USB controller: neither GPU nor NIC
+
+    const nixl::pciTopology t = nixl::pciTopology::scan(bus);
+    CHECK_EQ(t.gpus().size(), size_t(3));
+    CHECK_EQ(t.nics().size(), size_t(3));
+    CHECK(t.gpus()[0].bdf == "0000:1b:00.0" && t.gpus()[2].bdf == "0000:9b:00.0" && t.gpus()[2].numaNode == 1);
+    CHECK(t.gpus()[0].chain.size() == 5 && t.gpus()[0].chain.front() == "pci0000:15" && t.gpus()[0].chain.back() == "0000:1b:00.0");
+    // under one switch: up to the switch and down again
+    const nixl::pciDevice &ib0 = *t.nicsNearGpu(0).front();
+    CHECK(ib0.bdf == "0000:1c:00.0");
+    CHECK_EQ(nixl::pciTopology::distance(t.gpus()[0], ib0), 4);
+    CHECK_EQ(nixl::pciTopology::distance(t.gpus()[1], ib0), 4);
+    // another root complex on the same socket costs 100 more, another socket 100 more again
+    CHECK((t.interfacesNearGpu(0) == std::vector<std::string>{"ib0", "eno1", "ib1", "ib1b"}));
+    CHECK((t.interfacesNearGpu(2) == std::vector<std::string>{"ib1", "ib1b", "eno1", "ib0"}));
+    CHECK(nixl::pciTopology::distance(t.gpus()[0], *t.nicsNearGpu(0)[1]) > 100 && nixl::pciTopology::distance(t.gpus()[0], *t.nicsNearGpu(0)[1]) < 200);
+    CHECK(nixl::pciTopology::distance(t.gpus()[0], *t.nicsNearGpu(0)[2]) > 200);
+    // no such GPU: bus order
+    CHECK((t.interfacesNearGpu(99) == std::vector<std::string>{"eno1", "ib0", "ib1", "ib1b"}));
+    CHECK(t.toString().find("gpu2 0000:9b:00.0 numa 1: 0000:9c:00.0(ib1,ib1b;d=4)") != std::string::npos);
+    CHECK(nixl::pciTopology::scan(base + "/absent").gpus().empty());
 }
 
 TEST_CASE(clocks_durations_identifiers_and_strings) {
