@@ -14,6 +14,11 @@
 //             [--file path [--num-files N] [--direct]]      storage mode (POSIX, GDS, GDS_MT backends)
 //             [--scheme pairwise|onetomany|manytoone|tp --num-initiator-dev N --num-target-dev M]
 //
+// --role target --listen-port P  /  --role initiator --peer-ip A --peer-port P: the pairwise sweep between two
+// processes, which may sit on two hosts (then with --backend TCP): the target registers its buffer and listens for
+// metadata on port P; the initiator fetches the target's metadata there, sends its own, learns the buffer's address
+// from a notification, runs the sweep and says when it is through.  --check reads what it wrote back over the backend.
+//
 // --scheme onetomany: one initiator (--src-dev) posts the same request to M targets at once; manytoone: N
 // initiators post to one target (--dst-dev) at once, which is the pattern that shows what a receiver's ingress
 // sustains; tp: N initiators x M targets, every initiator sends 1/M of each block to every target (tensor-parallel
@@ -42,7 +47,10 @@
 #include <thread>
 #include <vector>
 
+#include <arpa/inet.h>
 #include <fcntl.h>
+#include <netinet/in.h>
+#include <sys/socket.h>
 #include <fstream>
 #include <unistd.h>
 
@@ -67,6 +75,9 @@ struct Args {
     bool enable_pt = false; // agents with a progress thread
     std::string file; // storage mode when set
     nixl_b_params_t extra; // --param key=value, passed to the backend
+    // two processes (on one host or two): "target" owns the destination buffer and listens, "initiator" finds it there
+    std::string role, peer_ip = "127.0.0.1";
+    int peer_port = 0, listen_port = 0;
 };
 
 // One option (with its value, if it takes one).  False for an unknown option.
@@ -89,6 +100,10 @@ bool setOption(Args &a, const std::string &k, const std::string &v) {
     else if (k == "--min") a.min = std::strtoull(v.c_str(), nullptr, 0);
     else if (k == "--max") a.max = std::strtoull(v.c_str(), nullptr, 0);
     else if (k == "--total") a.total = std::strtoull(v.c_str(), nullptr, 0);
+    else if (k == "--role") a.role = v;
+    else if (k == "--peer-ip") a.peer_ip = v;
+    else if (k == "--peer-port") a.peer_port = std::atoi(v.c_str());
+    else if (k == "--listen-port") a.listen_port = std::atoi(v.c_str());
     else if (k == "--file") a.file = v;
     else if (k == "--num-files") a.num_files = std::max(1, std::atoi(v.c_str()));
     else if (k == "--param") {
@@ -357,6 +372,85 @@ int runScheme(const Args &a, int ndev) {
 }
 } // namespace
 
+
+// ---------------------------------------------------------------- two-process mode: the target side
+namespace {
+int freePort() {
+    const int fd = ::socket(AF_INET, SOCK_STREAM, 0);
+    sockaddr_in sa{};
+    sa.sin_family = AF_INET;
+    sa.sin_addr.s_addr = htonl(INADDR_LOOPBACK);
+    socklen_t len = sizeof(sa);
+    int port = 0;
+    if (fd >= 0 && ::bind(fd, reinterpret_cast<sockaddr *>(&sa), sizeof(sa)) == 0 && ::getsockname(fd, reinterpret_cast<sockaddr *>(&sa), &len) == 0)
+        port = ntohs(sa.sin_port);
+    if (fd >= 0) ::close(fd);
+    return port;
+}
+
+// Waits for a notification of `from` that starts with `prefix`; the rest of it in `rest`.
+bool waitNotif(nixlAgent &agent, const std::string &from, const std::string &prefix, std::string &rest, int seconds) {
+    const auto end = clk::now() + std::chrono::seconds(seconds);
+    while (clk::now() < end) {
+        nixl_notifs_t n;
+        agent.getNotifs(n);
+        for (const auto &m : n[from])
+            if (m.compare(0, prefix.size(), prefix) == 0) {
+                rest = m.substr(prefix.size());
+                return true;
+            }
+        std::this_thread::sleep_for(std::chrono::microseconds(200));
+    }
+    return false;
+}
+
+int runTarget(const Args &a, bool vram, size_t buf_bytes) {
+    if (a.listen_port <= 0) {
+        std::fprintf(stderr, "--role target needs --listen-port\n");
+        return 2;
+    }
+    const int dev = std::max(0, a.dst_dev);
+    void *dst = nullptr;
+    if (vram) {
+        cudaSetDevice(dev);
+        if (cudaMalloc(&dst, buf_bytes) != cudaSuccess) return 3;
+        cudaMemset(dst, 0, buf_bytes);
+        cudaDeviceSynchronize();
+    } else {
+        if (posix_memalign(&dst, 4096, buf_bytes) != 0) return 3;
+        std::memset(dst, 0, buf_bytes);
+    }
+    nixlAgentConfig cfg(a.enable_pt, true, static_cast<uint16_t>(a.listen_port));
+    nixlAgent tgt("target", cfg);
+    nixlBackendH *bt = nullptr;
+    nixl_b_params_t params;
+    for (auto &kv : a.extra) params[kv.first] = kv.second;
+    if (tgt.createBackend(a.backend, params, bt) != NIXL_SUCCESS) {
+        std::fprintf(stderr, "cannot create backend %s\n", a.backend.c_str());
+        return 4;
+    }
+    nixl_reg_dlist_t rd(vram ? VRAM_SEG : DRAM_SEG);
+    rd.addDesc(nixlBlobDesc(reinterpret_cast<uintptr_t>(dst), buf_bytes, vram ? dev : 0, ""));
+    if (tgt.registerMem(rd) != NIXL_SUCCESS) return 5;
+    std::printf("target: %zu bytes registered, listening on port %d\n", buf_bytes, a.listen_port);
+    std::fflush(stdout);
+    // the initiator's metadata arrives through the listener
+    const nixl_xfer_dlist_t none(vram ? VRAM_SEG : DRAM_SEG);
+    const auto end = clk::now() + std::chrono::seconds(600);
+    while (tgt.checkRemoteMD("initiator", none) != NIXL_SUCCESS) {
+        if (clk::now() > end) return 6;
+        std::this_thread::sleep_for(std::chrono::milliseconds(2));
+    }
+    const std::string where = "ADDR " + std::to_string(reinterpret_cast<uintptr_t>(dst)) + " " + std::to_string(buf_bytes) + " " + std::to_string(vram ? dev : 0);
+    if (tgt.genNotif("initiator", where) != NIXL_SUCCESS) return 6;
+    std::string rest;
+    if (!waitNotif(tgt, "initiator", "DONE", rest, 24 * 3600)) return 7;
+    std::printf("target: the initiator is through\n");
+    tgt.deregisterMem(rd);
+    return 0;
+}
+} // namespace
+
 int main(int argc, char **argv) {
     Args a;
     for (int i = 1; i < argc; ++i) {
@@ -425,6 +519,20 @@ int main(int argc, char **argv) {
     if (a.batch_max < a.batch) a.batch_max = a.batch;
     if (storage && a.backend == "NVLINK") a.backend = vram ? "GDS" : "POSIX";
     const size_t buf_bytes = std::min(a.total, std::max<size_t>(a.max * a.batch_max, a.max));
+    if (!a.role.empty() && a.role != "initiator" && a.role != "target") {
+        std::fprintf(stderr, "unknown --role %s (initiator, target)\n", a.role.c_str());
+        return 2;
+    }
+    const bool remote_target = a.role == "initiator";
+    if ((remote_target || a.role == "target") && storage) {
+        std::fprintf(stderr, "--role and --file do not go together\n");
+        return 2;
+    }
+    if (a.role == "target") return runTarget(a, vram, buf_bytes);
+    if (remote_target && a.peer_port <= 0) {
+        std::fprintf(stderr, "--role initiator needs --peer-port (and --peer-ip unless the target is on this host)\n");
+        return 2;
+    }
     void *src = nullptr, *dst = nullptr;
     auto allocate = [&](void *&p, int dev, int fill) {
         if (vram) {
@@ -439,17 +547,20 @@ int main(int argc, char **argv) {
         return true;
     };
     if (!allocate(src, a.src_dev, 0x5a)) return 3;
-    if (!storage && !allocate(dst, a.dst_dev, 0)) return 3;
+    if (!storage && !remote_target && !allocate(dst, a.dst_dev, 0)) return 3;
     if (vram) cudaSetDevice(a.src_dev);
 
     // "--enable-pt": the backend's progress thread completes requests; several worker threads need the agent's lock.
-    nixlAgentConfig cfg(a.enable_pt, false, 0, a.num_threads > 1 ? nixl_thread_sync_t::NIXL_THREAD_SYNC_RW : nixl_thread_sync_t::NIXL_THREAD_SYNC_NONE);
-    nixlAgent ini("initiator", cfg), tgt("target", cfg);
+    const nixl_thread_sync_t sync = a.num_threads > 1 ? nixl_thread_sync_t::NIXL_THREAD_SYNC_RW : nixl_thread_sync_t::NIXL_THREAD_SYNC_NONE;
+    nixlAgentConfig cfg(a.enable_pt, false, 0, sync);
+    // with a target in another process the initiator's metadata travels through the agents' listeners
+    nixlAgentConfig ini_cfg(a.enable_pt, remote_target, static_cast<uint16_t>(remote_target ? (a.listen_port > 0 ? a.listen_port : freePort()) : 0), sync);
+    nixlAgent ini("initiator", ini_cfg), tgt(remote_target ? "unused" : "target", cfg);
     nixlBackendH *bi = nullptr, *bt = nullptr;
     nixl_b_params_t params;
     if (a.backend == "NVLINK" || a.backend == "UCX") params["copy_path"] = a.copy_path;
     for (auto &kv : a.extra) params[kv.first] = kv.second;
-    if (ini.createBackend(a.backend, params, bi) != NIXL_SUCCESS || (!storage && tgt.createBackend(a.backend, params, bt) != NIXL_SUCCESS)) {
+    if (ini.createBackend(a.backend, params, bi) != NIXL_SUCCESS || (!storage && !remote_target && tgt.createBackend(a.backend, params, bt) != NIXL_SUCCESS)) {
         std::fprintf(stderr, "cannot create backend %s\n", a.backend.c_str());
         return 4;
     }
@@ -473,6 +584,32 @@ int main(int argc, char **argv) {
             rd.addDesc(nixlBlobDesc(0, file_bytes, static_cast<uint64_t>(fd), ""));
         }
         if (ini.registerMem(rs) != NIXL_SUCCESS || ini.registerMem(rd) != NIXL_SUCCESS) return 5;
+    } else if (remote_target) {
+        if (ini.registerMem(rs) != NIXL_SUCCESS) return 5;
+        nixl_opt_args_t where;
+        where.ipAddr = a.peer_ip;
+        where.port = a.peer_port;
+        if (ini.fetchRemoteMD("target", &where) != NIXL_SUCCESS || ini.sendLocalMD(&where) != NIXL_SUCCESS) return 6;
+        const nixl_xfer_dlist_t none(mt);
+        const auto end = clk::now() + std::chrono::seconds(60);
+        while (ini.checkRemoteMD("target", none) != NIXL_SUCCESS) {
+            if (clk::now() > end) {
+                std::fprintf(stderr, "no metadata from the target at %s:%d\n", a.peer_ip.c_str(), a.peer_port);
+                return 6;
+            }
+            std::this_thread::sleep_for(std::chrono::milliseconds(2));
+        }
+        std::string rest;
+        if (!waitNotif(ini, "target", "ADDR ", rest, 60)) return 6;
+        unsigned long long addr = 0, len = 0;
+        int their_dev = 0;
+        if (std::sscanf(rest.c_str(), "%llu %llu %d", &addr, &len, &their_dev) != 3 || len < buf_bytes) {
+            std::fprintf(stderr, "the target's buffer (%llu bytes) is smaller than this sweep needs (%zu): start both with the same sizes\n", len, buf_bytes);
+            ini.genNotif("target", "DONE");
+            return 6;
+        }
+        dst = reinterpret_cast<void *>(static_cast<uintptr_t>(addr)); // an address of the other process: never touched here
+        a.dst_dev = their_dev;
     } else {
         rd.addDesc(nixlBlobDesc(reinterpret_cast<uintptr_t>(dst), buf_bytes, vram ? a.dst_dev : 0, ""));
         if (ini.registerMem(rs) != NIXL_SUCCESS || tgt.registerMem(rd) != NIXL_SUCCESS) return 5;
@@ -644,6 +781,24 @@ int main(int argc, char **argv) {
             if (storage) {
                 if (op != NIXL_WRITE) continue; // a READ returns what an earlier WRITE stored: nothing fixed to compare with
                 if (::pread(fds[0], h.data(), h.size(), 0) != static_cast<ssize_t>(h.size())) return 10;
+            } else if (remote_target && op == NIXL_WRITE) {
+                // Read the start of what was written back into the start of the source: it holds the same pattern if
+                // the WRITE arrived, the target's zeros if it did not.
+                nixl_xfer_dlist_t l(mt), r(mt);
+                l.addDesc(nixlBasicDesc(reinterpret_cast<uintptr_t>(src), h.size(), vram ? a.src_dev : 0));
+                r.addDesc(nixlBasicDesc(reinterpret_cast<uintptr_t>(dst), h.size(), vram ? a.dst_dev : 0));
+                nixlXferReqH *back = nullptr;
+                if (ini.createXferReq(NIXL_READ, l, r, remote_name, back) != NIXL_SUCCESS) return 10;
+                nixl_status_t st = ini.postXferReq(back);
+                while (st == NIXL_IN_PROG) st = ini.getXferStatus(back);
+                ini.releaseXferReq(back);
+                if (st != NIXL_SUCCESS) return 10;
+                if (vram) cudaMemcpy(h.data(), src, h.size(), cudaMemcpyDeviceToHost);
+                else std::memcpy(h.data(), src, h.size());
+            } else if (remote_target) {
+                if (vram) cudaMemcpy(h.data(), src, h.size(), cudaMemcpyDeviceToHost);
+                else std::memcpy(h.data(), src, h.size());
+                want = 0x00;
             } else if (vram) {
                 cudaSetDevice(op == NIXL_WRITE ? a.dst_dev : a.src_dev);
                 cudaMemcpy(h.data(), op == NIXL_WRITE ? dst : src, h.size(), cudaMemcpyDeviceToHost);
@@ -661,5 +816,6 @@ int main(int argc, char **argv) {
         }
     }
     for (int fd : fds) ::close(fd);
+    if (remote_target) ini.genNotif("target", "DONE");
     return 0;
 }

@@ -148,3 +148,34 @@ def test_native_nixlbench_over_the_tcp_backend():
         assert res.returncode == 0, res.stdout + res.stderr
         rows = [l.split() for l in res.stdout.strip().splitlines() if l and l[0].isdigit()]
         assert len(rows) == 9 and all(float(r[2]) > 0 for r in rows), res.stdout
+
+
+@pytest.mark.parametrize("backend,op", [("TCP", "WRITE"), ("TCP", "READ"), ("NVLINK", "WRITE")])
+def test_native_nixlbench_between_two_processes(backend, op):
+    """--role target / --role initiator: the pairwise sweep with the target in a process of its own (on another host it
+    would be the same two commands); metadata through the agents' listeners, the buffer's address by notification."""
+    import socket
+
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    exe = os.path.join(ROOT, "nixl_b200", "bin", "nixlbench")
+    sizes = ["--mem", "DRAM", "--max", "1048576", "--batch", "2"]
+    target = subprocess.Popen([exe, "--role", "target", "--listen-port", str(port), "--backend", backend, *sizes], env=ENV,
+                              stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+    try:
+        assert "listening" in target.stdout.readline()
+        res = subprocess.run([exe, "--role", "initiator", "--peer-port", str(port), "--backend", backend, "--op", op, *sizes, "--min", "4096",
+                              "--iters", "20", "--warmup", "3", "--check"], env=ENV, capture_output=True, text=True, timeout=180)
+        if backend == "NVLINK" and res.returncode != 0 and "cross-process" in (res.stdout + res.stderr):
+            pytest.skip("cross-process memory access is not permitted here")
+        assert res.returncode == 0, res.stdout + res.stderr
+        rows = [l.split() for l in res.stdout.strip().splitlines() if l and l[0].isdigit()]
+        assert len(rows) == 9 and all(float(r[2]) > 0 for r in rows), res.stdout
+        assert target.wait(timeout=30) == 0
+        assert "through" in target.stdout.read()
+    finally:
+        if target.poll() is None:
+            target.kill()
+        target.wait()
