@@ -1124,6 +1124,9 @@ private:
                 break;
             }
             tuneSocket(fd, bufBytes_);
+            // until it has introduced itself a connection may not keep a thread waiting
+            const timeval intro{connectTimeoutMs_ / 1000, (connectTimeoutMs_ % 1000) * 1000};
+            ::setsockopt(fd, SOL_SOCKET, SO_RCVTIMEO, &intro, sizeof(intro));
             auto c = std::make_unique<ServerConn>();
             c->fd = fd;
             ServerConn *raw = c.get();
@@ -1137,6 +1140,7 @@ private:
             }
             raw->th = std::thread([this, raw] {
                 serve(raw->fd);
+                ::shutdown(raw->fd, SHUT_RDWR); // the other side sees the end now; the descriptor itself is closed when the thread is reaped
                 raw->done.store(true);
             });
             served_.push_back(std::move(c));
@@ -1153,6 +1157,7 @@ private:
             if (!recvSpin(fd, &h, sizeof(h), first ? 0 : kSpinUs) || h.magic != kMagic || h.metaLen > (64u << 20) || h.nDescs > kMaxDescsPerMsg) return;
             Hdr reply;
             reply.id = h.id;
+            if (from.empty() && (h.op != OP_HELLO || h.metaLen > 4096)) return; // a stranger gets to say who it is, briefly, and nothing else
             if (h.op == OP_HELLO || h.op == OP_NOTIF) {
                 std::string meta(h.metaLen, '\0');
                 if (!recvBuf(fd, meta.data(), meta.size())) return;
@@ -1169,6 +1174,8 @@ private:
                 reply.status = ok ? NIXL_SUCCESS : NIXL_ERR_MISMATCH;
                 if (!sendBuf(fd, &reply, sizeof(reply)) || !ok) return;
                 from = who;
+                const timeval none{0, 0}; // a known peer may stay silent for as long as it likes
+                ::setsockopt(fd, SOL_SOCKET, SO_RCVTIMEO, &none, sizeof(none));
                 continue;
             }
             if ((h.op != OP_WRITE && h.op != OP_READ) || from.empty() || h.metaLen != h.nDescs * sizeof(WireDesc)) return;

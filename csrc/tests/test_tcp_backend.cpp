@@ -406,6 +406,157 @@ TEST_CASE(connections_spread_over_the_addresses_of_both_sides) {
     CHECK(a.deregisterMem(ra) == NIXL_SUCCESS && b.deregisterMem(rb) == NIXL_SUCCESS);
 }
 
+TEST_CASE(a_listener_survives_strangers_and_garbage) {
+    // Whoever can reach the port can send bytes to it.  None of this may disturb the engine: noise, a header that
+    // promises more than ever comes, requests before an introduction, an introduction for somebody else, absurd counts,
+    // a connection dropped half way.
+    int probe = ::socket(AF_INET, SOCK_STREAM, 0);
+    sockaddr_in sa{};
+    sa.sin_family = AF_INET;
+    sa.sin_addr.s_addr = htonl(INADDR_LOOPBACK);
+    socklen_t len = sizeof(sa);
+    CHECK(probe >= 0 && ::bind(probe, reinterpret_cast<sockaddr *>(&sa), sizeof(sa)) == 0 &&
+          ::getsockname(probe, reinterpret_cast<sockaddr *>(&sa), &len) == 0);
+    const uint16_t port = ntohs(sa.sin_port);
+    ::close(probe);
+    nixlAgent a("tcp_g_a", nixlAgentConfig(false)), b("tcp_g_b", nixlAgentConfig(false));
+    nixlBackendH *h = nullptr;
+    CHECK_EQ(a.createBackend("TCP", {{"address", "127.0.0.1"}}, h), NIXL_SUCCESS);
+    CHECK_EQ(b.createBackend("TCP", {{"address", "127.0.0.1"}, {"port", std::to_string(port)}, {"connect_timeout_ms", "400"}}, h), NIXL_SUCCESS);
+    std::vector<uint8_t> src(1 << 20, 0x3c), dst(1 << 20, 0);
+    nixl_reg_dlist_t ra(DRAM_SEG), rb(DRAM_SEG);
+    ra.addDesc(nixlBlobDesc(reinterpret_cast<uintptr_t>(src.data()), src.size(), 0, ""));
+    rb.addDesc(nixlBlobDesc(reinterpret_cast<uintptr_t>(dst.data()), dst.size(), 0, ""));
+    CHECK(a.registerMem(ra) == NIXL_SUCCESS && b.registerMem(rb) == NIXL_SUCCESS);
+
+    auto dial = [&] {
+        const int fd = ::socket(AF_INET, SOCK_STREAM, 0);
+        sockaddr_in to{};
+        to.sin_family = AF_INET;
+        to.sin_addr.s_addr = htonl(INADDR_LOOPBACK);
+        to.sin_port = htons(port);
+        CHECK(fd >= 0 && ::connect(fd, reinterpret_cast<sockaddr *>(&to), sizeof(to)) == 0);
+        timeval tv{2, 0};
+        ::setsockopt(fd, SOL_SOCKET, SO_RCVTIMEO, &tv, sizeof(tv));
+        return fd;
+    };
+    // the wire header, as the backend's source gives it: magic, op, reserved, id, count, status, payload, meta, reserved
+    struct Hdr {
+        uint32_t magic = 0x4e585443u;
+        uint16_t op = 0, reserved = 0;
+        uint64_t id = 0;
+        uint32_t nDescs = 0;
+        int32_t status = 0;
+        uint64_t payloadLen = 0;
+        uint32_t metaLen = 0, reserved2 = 0;
+    };
+    static_assert(sizeof(Hdr) == 40);
+    auto closed_by_peer = [](int fd) { // the listener hangs up on what it cannot use
+        char c;
+        const ssize_t n = ::recv(fd, &c, 1, 0);
+        return n == 0 || (n < 0 && errno != EAGAIN && errno != EWOULDBLOCK);
+    };
+    std::mt19937 rng(3);
+    {   // noise
+        const int fd = dial();
+        std::vector<uint8_t> junk(4096);
+        for (auto &x : junk) x = static_cast<uint8_t>(rng());
+        CHECK(::send(fd, junk.data(), junk.size(), MSG_NOSIGNAL) > 0);
+        CHECK(closed_by_peer(fd));
+        ::close(fd);
+    }
+    {   // a WRITE before any introduction, aimed at the registered buffer
+        const int fd = dial();
+        Hdr w;
+        w.op = 2;
+        w.nDescs = 1;
+        w.metaLen = 24;
+        w.payloadLen = 64;
+        const uint64_t desc[3] = {reinterpret_cast<uintptr_t>(dst.data()), 64, 12345};
+        std::vector<uint8_t> payload(64, 0xff);
+        ::send(fd, &w, sizeof(w), MSG_NOSIGNAL);
+        ::send(fd, desc, sizeof(desc), MSG_NOSIGNAL);
+        ::send(fd, payload.data(), payload.size(), MSG_NOSIGNAL);
+        CHECK(closed_by_peer(fd));
+        ::close(fd);
+    }
+    {   // an introduction for somebody else: answered with a refusal, then closed
+        const int fd = dial();
+        std::string meta;
+        auto put = [&](const std::string &v) {
+            const uint32_t n = static_cast<uint32_t>(v.size());
+            meta.append(reinterpret_cast<const char *>(&n), 4);
+            meta.append(v);
+        };
+        put("mallory");
+        put("tcp_g_b");
+        put("1"); // not this engine's tag
+        Hdr hello;
+        hello.op = 1;
+        hello.metaLen = static_cast<uint32_t>(meta.size());
+        ::send(fd, &hello, sizeof(hello), MSG_NOSIGNAL);
+        ::send(fd, meta.data(), meta.size(), MSG_NOSIGNAL);
+        Hdr reply;
+        CHECK_EQ(::recv(fd, &reply, sizeof(reply), MSG_WAITALL), static_cast<ssize_t>(sizeof(reply)));
+        CHECK(reply.op == 4 && reply.status != 0);
+        CHECK(closed_by_peer(fd));
+        ::close(fd);
+    }
+    {   // absurd counts and lengths
+        for (int variant = 0; variant < 3; ++variant) {
+            const int fd = dial();
+            Hdr x;
+            x.op = variant == 0 ? 2 : 1;
+            x.nDescs = variant == 0 ? 0xffffffffu : 0;
+            x.metaLen = variant == 1 ? 0xffffffffu : 16;
+            x.payloadLen = ~0ull;
+            ::send(fd, &x, sizeof(x), MSG_NOSIGNAL);
+            CHECK(closed_by_peer(fd));
+            ::close(fd);
+        }
+    }
+    {   // an introduction that stops half way: the listener does not wait for the rest for ever
+        const int fd = dial();
+        Hdr x;
+        x.op = 1;
+        x.metaLen = 64;
+        ::send(fd, &x, sizeof(x), MSG_NOSIGNAL);
+        ::send(fd, "abc", 3, MSG_NOSIGNAL);
+        const auto t0 = clk::now();
+        CHECK(closed_by_peer(fd));
+        CHECK(clk::now() - t0 < std::chrono::milliseconds(1900));
+        ::close(fd);
+    }
+    {   // half a header, then gone; and a promise of a megabyte of introduction that never comes
+        const int fd = dial();
+        Hdr x;
+        ::send(fd, &x, 17, MSG_NOSIGNAL);
+        ::close(fd);
+        const int fd2 = dial();
+        x.op = 1;
+        x.metaLen = 1 << 20;
+        ::send(fd2, &x, sizeof(x), MSG_NOSIGNAL);
+        ::send(fd2, "abc", 3, MSG_NOSIGNAL);
+        ::close(fd2);
+    }
+    CHECK(dst == std::vector<uint8_t>(1 << 20, 0)); // nothing of all that reached memory
+    // and the engine serves its real peer as if nothing had happened
+    nixl_blob_t md;
+    std::string name;
+    b.getLocalMD(md);
+    CHECK_EQ(a.loadRemoteMD(md, name), NIXL_SUCCESS);
+    nixl_xfer_dlist_t l(DRAM_SEG), r(DRAM_SEG);
+    l.addDesc(nixlBasicDesc(reinterpret_cast<uintptr_t>(src.data()), src.size(), 0));
+    r.addDesc(nixlBasicDesc(reinterpret_cast<uintptr_t>(dst.data()), dst.size(), 0));
+    nixlXferReqH *w = nullptr;
+    CHECK_EQ(a.createXferReq(NIXL_WRITE, l, r, "tcp_g_b", w), NIXL_SUCCESS);
+    CHECK(a.postXferReq(w) >= 0);
+    CHECK_EQ(waitDone(a, w), NIXL_SUCCESS);
+    CHECK(src == dst);
+    CHECK_EQ(a.releaseXferReq(w), NIXL_SUCCESS);
+    CHECK(a.deregisterMem(ra) == NIXL_SUCCESS && b.deregisterMem(rb) == NIXL_SUCCESS);
+}
+
 TEST_CASE(between_two_processes_and_a_target_that_exits) {
     constexpr size_t kBytes = 6 << 20;
     struct Shared {
