@@ -1,4 +1,5 @@
-"""Fused GPU operations of the library (hand-written sm_100a kernels behind a C ABI)."""
+"""Fused GPU operations of the library (hand-written sm_100a kernels behind a C ABI), and the descriptor path for KV
+blocks that reaches peers on other hosts."""
 from .grouped_gemm import (  # noqa: F401
     from_ue8m0,
     grouped_gemm_fp8,
@@ -8,6 +9,7 @@ from .grouped_gemm import (  # noqa: F401
     reference_grouped_gemm,
     to_ue8m0,
 )
+from .kv_blocks import KVBlockTransfer, describe_blocks  # noqa: F401
 from .kv_transfer import KVLayout, KVTransfer, reference_kv_transfer  # noqa: F401
 
 

@@ -121,3 +121,30 @@ def test_cpp_etcd_example_against_the_stand_in_gateway(tmp_path):
     finally:
         gateway.kill()
         gateway.wait()
+
+
+@pytest.mark.parametrize("backends", ["NVLINK,TCP", "TCP"])
+def test_kv_blocks_between_a_prefill_and_a_decode_process(backends):
+    """examples/kv_blocks_between_hosts.py: prepared lists on both sides, block numbers per request, over the sockets
+    when only TCP is created (what two hosts would use) and over whatever the agent prefers otherwise."""
+    import socket
+
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    script = os.path.join(ROOT, "examples", "kv_blocks_between_hosts.py")
+    dec = subprocess.Popen([sys.executable, script, "--role", "decode", "--port", str(port), "--backends", backends], stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+    try:
+        assert "listening" in dec.stdout.readline()
+        pre = subprocess.run([sys.executable, script, "--role", "prefill", "--peer-port", str(port), "--backends", backends], capture_output=True, text=True, timeout=240)
+        assert pre.returncode == 0, pre.stdout[-2000:] + pre.stderr[-2000:]
+        assert "has verified the blocks" in pre.stdout
+        if backends == "TCP":
+            assert "over TCP" in pre.stdout
+        assert dec.wait(timeout=60) == 0, dec.stderr.read()[-2000:]
+        assert "20 blocks arrived" in dec.stdout.read()
+    finally:
+        if dec.poll() is None:
+            dec.kill()
+        dec.wait()

@@ -104,3 +104,50 @@ def test_two_processes_write_read_and_notify_over_sockets(backends):
         if proc.is_alive():
             proc.terminate()
         proc.join(5)
+
+
+def test_kv_block_mover_checks_what_it_is_given():
+    """`KVBlockTransfer` over two agents of one process (TCP backend, loopback): READ as well as WRITE, and the errors a
+    caller can make: a block number out of range, lists of different length, a peer whose blocks have another size."""
+    from nixl_b200 import nixl_agent, nixl_agent_config
+    from nixl_b200.ops import KVBlockTransfer, describe_blocks
+
+    a = nixl_agent("kvb_a", nixl_agent_config(backends=["TCP"]))
+    b = nixl_agent("kvb_b", nixl_agent_config(backends=["TCP"]))
+    mine = [torch.arange(16 * 512, dtype=torch.float32).reshape(16, 512) + 1000 * i for i in range(3)]
+    theirs = [torch.zeros(24, 512, dtype=torch.float32) for _ in range(3)]
+    for t in mine:
+        a.register_memory(t)
+    for t in theirs:
+        b.register_memory(t)
+    a.add_remote_agent(b.get_agent_metadata())
+    mover = KVBlockTransfer(a, mine, "kvb_b", describe_blocks(b, theirs))
+    assert mover.blocks == 16 and mover.remote_blocks == 24 and mover.bytes_moved(2) == 2 * 3 * 2048
+    mover.wait(mover.post([0, 5, 15], [23, 1, 7], "WRITE", b"three"))
+    for i in range(3):
+        assert torch.equal(theirs[i][23], mine[i][0]) and torch.equal(theirs[i][1], mine[i][5]) and torch.equal(theirs[i][7], mine[i][15])
+        assert float(theirs[i][[0, 2, 3, 22]].abs().sum()) == 0
+    deadline = time.time() + 5
+    got = {}
+    while time.time() < deadline and not got:
+        got = b.get_new_notifs()
+    assert got == {"kvb_a": [b"three"]}
+    theirs[2][9] += 7.0
+    mover.wait(mover.post([3], [9], "READ"))
+    assert torch.equal(mine[2][3], theirs[2][9]) and float(mine[0][3].abs().sum()) == 0
+    with pytest.raises(IndexError):
+        mover.post([16], [0])
+    with pytest.raises(IndexError):
+        mover.post([0], [24])
+    with pytest.raises(ValueError):
+        mover.post([0, 1], [0])
+    other = [torch.zeros(24, 256, dtype=torch.float32) for _ in range(3)]
+    for t in other:
+        b.register_memory(t)
+    with pytest.raises(ValueError):
+        KVBlockTransfer(a, mine, "kvb_b", describe_blocks(b, other))
+    with pytest.raises(ValueError):
+        KVBlockTransfer(a, mine, "kvb_b", describe_blocks(b, theirs[:2] + [theirs[0][:5]]))
+    with pytest.raises(ValueError):
+        describe_blocks(b, [theirs[0].t()])
+    mover.close()
