@@ -625,8 +625,9 @@ nixl_status_t Engine::loadRemoteConnInfo(const std::string &remote_agent, const 
     PeerId p;
     if (!decodePeer(remote_conn_info, p) || p.agent != remote_agent) return NIXL_ERR_MISMATCH;
     if (p.host != self_.host) {
-        NIXL_ERROR << "NVLINK backend: agent " << remote_agent << " runs on host " << p.host
-                   << "; this backend reaches peers of one NVLink box only";
+        // Not an error of the deployment: with the TCP backend created next to this one the agent reaches that peer there.
+        NIXL_WARN << "NVLINK backend: agent " << remote_agent << " runs on host " << p.host
+                  << "; this backend reaches peers of one NVLink box only (the TCP backend reaches other hosts)";
         return NIXL_ERR_NOT_SUPPORTED;
     }
     std::lock_guard<std::mutex> g(peersMu_);
