@@ -69,13 +69,16 @@ def test_plan_lines_follow_the_model_geometry():
     assert "llama-3-8b" in plan.model_names()
 
 
-def test_ct_perftest_two_ranks_host_memory(tmp_path):
+@pytest.mark.parametrize("backend,port", [("NVLINK", "29631"), ("TCP", "29633")])
+def test_ct_perftest_two_ranks_host_memory(tmp_path, backend, port):
+    """The traffic-matrix test between two ranks on host memory; with the TCP backend it is the run one would start over
+    several hosts (torchrun across nodes, the agents reaching each other over sockets)."""
     cfg = tmp_path / "ct.yaml"
     cfg.write_text("iters: 3\nwarmup_iters: 1\ntraffic_pattern:\n  matrix: [[0, 256K], [64K, 0]]\n  mem_type: cpu\n  shards: 4\n  xfer_op: WRITE\n")
     out = tmp_path / "report.json"
     env = dict(os.environ, PYTHONPATH=ROOT)
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
-                        "--master-port", "29631", "-m", "benchmarks.kvbench", "ct-perftest", str(cfg), "--json-output-path", str(out)],
+                        "--master-port", port, "-m", "benchmarks.kvbench", "ct-perftest", str(cfg), "--backend", backend, "--json-output-path", str(out)],
                        cwd=ROOT, env=env, capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     rep = json.loads(out.read_text())
