@@ -21,11 +21,20 @@ def test_example_runs(script, args):
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
 
 
-def test_cpp_example_builds_and_runs(tmp_path):
+def test_cpp_example_builds_with_the_pkg_config_file_and_runs(tmp_path):
+    """A C++ user's build line: flags from the pkg-config file the build writes next to the library."""
+    import shutil
+
     exe = str(tmp_path / "two_agents")
     lib = os.path.join(ROOT, "nixl_b200", "lib")
-    build = subprocess.run(["g++", "-std=c++20", "-O1", "-I" + os.path.join(ROOT, "csrc", "include"), "-I/usr/local/cuda/include",
-                            os.path.join(ROOT, "examples", "cpp", "two_agents.cpp"), "-o", exe, "-L" + lib, "-lnixl", "-Wl,-rpath," + lib, "-pthread"],
+    flags = ["-I" + os.path.join(ROOT, "csrc", "include"), "-L" + lib, "-lnixl", "-Wl,-rpath," + lib]
+    pc = os.path.join(lib, "pkgconfig", "nixl.pc")
+    if shutil.which("pkg-config") and os.path.exists(pc):
+        out = subprocess.run(["pkg-config", "--cflags", "--libs", "nixl"], env=dict(os.environ, PKG_CONFIG_PATH=os.path.dirname(pc)), capture_output=True, text=True)
+        assert out.returncode == 0, out.stderr
+        flags = out.stdout.split()
+        assert any(f.startswith("-I") for f in flags) and "-lnixl" in flags
+    build = subprocess.run(["g++", "-std=c++20", "-O1", os.path.join(ROOT, "examples", "cpp", "two_agents.cpp"), "-o", exe, *flags, "-pthread"],
                            capture_output=True, text=True, timeout=300)
     assert build.returncode == 0, build.stderr[-3000:]
     res = subprocess.run([exe], capture_output=True, text=True, timeout=120)
