@@ -5,7 +5,7 @@
 //   * an S3 service, when an endpoint is named (`endpoint_override` parameter or $AWS_ENDPOINT_OVERRIDE, e.g.
 //     "http://minio:9000" or "https://s3.us-west-2.amazonaws.com"): the REST client of s3_rest.h, with the reference's
 //     parameters (`bucket` / $AWS_DEFAULT_BUCKET, `access_key`, `secret_key`, `session_token` or the AWS_* variables,
-//     `region`, `scheme`, `use_virtual_addressing`, `ca_bundle`, `crtMinLimit`).  WRITE puts the whole object (an
+//     `region`, `scheme`, `use_virtual_addressing`, `ca_bundle`, `crtMinLimit`, `req_checksum`, `resp_checksum`).  WRITE puts the whole object (an
 //     offset other than 0 is refused, as in the reference), READ gets a byte range, queryMem asks HeadObject.  Objects of
 //     at least `crtMinLimit` bytes take the role of the reference's second client: a multipart upload whose parts, and a
 //     download whose ranges, run side by side on the engine's threads.  `payload_signing` (default: on over http, off
@@ -253,6 +253,10 @@ private:
         cfg.caBundle = param("ca_bundle", "AWS_CA_BUNDLE");
         const std::string signing = param("payload_signing");
         cfg.signPayload = signing.empty() ? cfg.scheme == "http" : signing == "true";
+        // "supported": use checksums where the service takes them; "required" (and nothing): only where the protocol
+        // demands one, which none of the calls made here does.  The names are the reference's.
+        cfg.sendChecksum = param("req_checksum") == "supported";
+        cfg.checkChecksum = param("resp_checksum") == "supported";
         const std::string limit = param("crtMinLimit");
         if (!limit.empty()) {
             const long long n = std::atoll(limit.c_str());
@@ -383,6 +387,8 @@ extern "C" NIXL_PLUGIN_EXPORT nixlBackendPlugin *nixl_plugin_init() {
                                                         {"ca_bundle", ""},
                                                         {"crtMinLimit", ""},
                                                         {"payload_signing", ""},
+                                                        {"req_checksum", ""},
+                                                        {"resp_checksum", ""},
                                                         {"connection_string", ""},
                                                         {"account_url", ""}},
                                                        {DRAM_SEG, OBJ_SEG});

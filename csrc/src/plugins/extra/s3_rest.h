@@ -141,6 +141,51 @@ inline std::string hex(const uint8_t *p, size_t n) {
 }
 inline std::string hex(const Digest &d) { return hex(d.data(), d.size()); }
 
+// CRC-32 (IEEE 802.3, the one S3 calls CRC32), eight bytes per step.
+inline uint32_t crc32(const void *data, size_t n, uint32_t crc = 0) {
+    static const auto table = [] {
+        std::array<std::array<uint32_t, 256>, 8> t{};
+        for (uint32_t i = 0; i < 256; ++i) {
+            uint32_t c = i;
+            for (int k = 0; k < 8; ++k) c = (c >> 1) ^ (0xedb88320u & (0u - (c & 1)));
+            t[0][i] = c;
+        }
+        for (uint32_t i = 0; i < 256; ++i)
+            for (int k = 1; k < 8; ++k) t[static_cast<size_t>(k)][i] = (t[static_cast<size_t>(k - 1)][i] >> 8) ^ t[0][t[static_cast<size_t>(k - 1)][i] & 0xff];
+        return t;
+    }();
+    const uint8_t *p = static_cast<const uint8_t *>(data);
+    crc = ~crc;
+    while (n >= 8) {
+        uint32_t lo, hi;
+        std::memcpy(&lo, p, 4);
+        std::memcpy(&hi, p + 4, 4);
+        lo ^= crc;
+        crc = table[7][lo & 0xff] ^ table[6][(lo >> 8) & 0xff] ^ table[5][(lo >> 16) & 0xff] ^ table[4][lo >> 24] ^ table[3][hi & 0xff] ^
+            table[2][(hi >> 8) & 0xff] ^ table[1][(hi >> 16) & 0xff] ^ table[0][hi >> 24];
+        p += 8;
+        n -= 8;
+    }
+    while (n--) crc = (crc >> 8) ^ table[0][(crc ^ *p++) & 0xff];
+    return ~crc;
+}
+
+// The checksum as S3 wants it in a header: base64 of the four bytes, most significant first.
+inline std::string crc32Header(uint32_t crc) {
+    static const char *t = "ABCDEFGHIJKLMNOPQRSTUVWXYZabcdefghijklmnopqrstuvwxyz0123456789+/";
+    const uint8_t b[4] = {static_cast<uint8_t>(crc >> 24), static_cast<uint8_t>(crc >> 16), static_cast<uint8_t>(crc >> 8), static_cast<uint8_t>(crc)};
+    const uint32_t v0 = (uint32_t(b[0]) << 16) | (uint32_t(b[1]) << 8) | b[2], v1 = uint32_t(b[3]) << 16;
+    std::string out;
+    out += t[(v0 >> 18) & 63];
+    out += t[(v0 >> 12) & 63];
+    out += t[(v0 >> 6) & 63];
+    out += t[v0 & 63];
+    out += t[(v1 >> 18) & 63];
+    out += t[(v1 >> 12) & 63];
+    out += "==";
+    return out;
+}
+
 inline Digest hmacSha256(const void *key, size_t key_len, const void *msg, size_t msg_len) {
     uint8_t k[64] = {0};
     if (key_len > 64) {
@@ -404,6 +449,8 @@ struct Config : HttpConfig {
     std::string bucket, region = "us-east-1";
     bool virtualAddressing = false;
     bool signPayload = true; // hash the body of a PUT into the signature (off: "UNSIGNED-PAYLOAD")
+    bool sendChecksum = false;  // a CRC32 of every uploaded body goes with it and the service checks it
+    bool checkChecksum = false; // ask for the stored checksum with every download and compare (whole objects only: a range has none)
     Credentials cred;
 };
 
@@ -646,6 +693,7 @@ public:
     // Each returns the HTTP status (200, 206, 404, 403, ...) or 0 when the service could not be reached.
     int putObject(const std::string &key, const void *data, size_t len, std::string *etag = nullptr) override {
         Request r = base("PUT", key);
+        if (cfg_.sendChecksum) r.headers["x-amz-checksum-crc32"] = crc32Header(crc32(data, len));
         Response resp = exchange(r, data, len, nullptr, 0);
         if (etag) *etag = resp.headers["etag"];
         return note(resp, "PutObject", key);
@@ -654,11 +702,21 @@ public:
         if (len == 0) return headObject(key, nullptr);
         Request r = base("GET", key);
         r.headers["range"] = "bytes=" + std::to_string(offset) + "-" + std::to_string(offset + len - 1);
+        if (cfg_.checkChecksum) r.headers["x-amz-checksum-mode"] = "ENABLED";
         size_t got = 0;
         Response resp = exchange(r, nullptr, 0, dst, len, &got);
         if ((resp.status == 200 || resp.status == 206) && got != len) { // an object that ends before the range does
+            std::lock_guard<std::mutex> g(mu_);
             lastError_ = "GetObject " + key + ": the object ends inside the requested range";
             return 416;
+        }
+        // The service sends the object's checksum only when the answer is the whole object.
+        auto sum = resp.headers.find("x-amz-checksum-crc32");
+        if (cfg_.checkChecksum && (resp.status == 200 || resp.status == 206) && sum != resp.headers.end() && sum->second.size() == 8 &&
+            sum->second != crc32Header(crc32(dst, len))) {
+            std::lock_guard<std::mutex> g(mu_);
+            lastError_ = "GetObject " + key + ": the bytes received do not match the object's stored CRC32";
+            return 500;
         }
         return note(resp, "GetObject", key);
     }
@@ -685,6 +743,7 @@ public:
         Request r = base("PUT", key);
         r.query.emplace_back("partNumber", std::to_string(number));
         r.query.emplace_back("uploadId", upload_id);
+        if (cfg_.sendChecksum) r.headers["x-amz-checksum-crc32"] = crc32Header(crc32(data, len));
         Response resp = exchange(r, data, len, nullptr, 0);
         etag = resp.headers["etag"];
         return note(resp, "UploadPart", key);

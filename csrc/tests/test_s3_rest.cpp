@@ -80,6 +80,20 @@ TEST_CASE(escaping_and_endpoints) {
     CHECK(!parseEndpoint("", scheme, host, port));
 }
 
+TEST_CASE(crc32_of_the_check_string_and_in_pieces) {
+    CHECK_EQ(crc32("123456789", 9), 0xcbf43926u); // the check value of CRC-32 / IEEE
+    CHECK_EQ(crc32("", 0), 0u);
+    CHECK(crc32Header(0xcbf43926u) == "y/Q5Jg==");
+    // a long buffer in pieces of awkward sizes gives what one call gives (the eight-byte steps and the tail meet)
+    std::string big(100003, 'x');
+    for (size_t i = 0; i < big.size(); ++i) big[i] = static_cast<char>(i * 131 + (i >> 7));
+    const uint32_t whole = crc32(big.data(), big.size());
+    uint32_t pieces = 0;
+    for (size_t off = 0, step = 1; off < big.size(); off += step, step = step * 3 % 97 + 1)
+        pieces = crc32(big.data() + off, std::min(step, big.size() - off), pieces);
+    CHECK_EQ(pieces, whole);
+}
+
 TEST_CASE(base64_of_rfc_4648_and_back) {
     const char *plain[] = {"", "f", "fo", "foo", "foob", "fooba", "foobar"};
     const char *coded[] = {"", "Zg==", "Zm8=", "Zm9v", "Zm9vYg==", "Zm9vYmE=", "Zm9vYmFy"};

@@ -3,13 +3,14 @@ ranged GetObject, HeadObject, DeleteObject, multipart upload), and a check of ev
 with hashlib / hmac, an implementation that shares nothing with the client's.  Runs as a process of its own:
 
     python fake_s3_server.py [--bucket NAME] [--access-key K --secret-key S] [--region R]
-                             [--close-after N] [--tls CERT KEY]
+                             [--close-after N] [--tls CERT KEY] [--corrupt-downloads]
 
 prints its port on the first line of stdout and serves until it is killed.  `--close-after N` drops every connection
 after N requests without announcing it, which is what an idle keep-alive connection looks like to a client.
 `GET /_admin/stats` answers with JSON counters; `GET /_admin/keys` with the keys of every bucket.
 """
 import argparse
+import base64
 import hashlib
 import hmac
 import json
@@ -17,6 +18,7 @@ import re
 import sys
 import threading
 import urllib.parse
+import zlib
 from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
 
 MIN_PART = 5 << 20
@@ -25,7 +27,8 @@ STATE = {
     "buckets": {},      # bucket -> {key: bytes}
     "uploads": {},      # upload id -> {"bucket", "key", "parts": {n: bytes}}
     "stats": {"put": 0, "get": 0, "head": 0, "delete": 0, "create_mpu": 0, "part": 0, "complete_mpu": 0, "abort_mpu": 0,
-              "bad_signature": 0, "unsigned_payload": 0, "connections": 0, "virtual_host": 0},
+              "bad_signature": 0, "unsigned_payload": 0, "connections": 0, "virtual_host": 0, "checksums_checked": 0, "checksums_sent": 0,
+              "bad_checksum": 0},
     "lock": threading.Lock(),
     "next_upload": 1,
 }
@@ -34,6 +37,10 @@ ARGS = None
 
 def _hmac(key, msg):
     return hmac.new(key, msg.encode(), hashlib.sha256).digest()
+
+
+def _crc(data):
+    return base64.b64encode(zlib.crc32(data).to_bytes(4, "big")).decode()
 
 
 def _bump(name):
@@ -145,6 +152,12 @@ class Handler(BaseHTTPRequestHandler):
         if not got:
             return
         objects, key, query, body = got
+        claimed = self.headers.get("x-amz-checksum-crc32")
+        if claimed is not None:
+            _bump("checksums_checked")
+            if claimed != _crc(body) or "x-amz-checksum-crc32" not in self.headers.get("Authorization", "x-amz-checksum-crc32"):
+                _bump("bad_checksum")
+                return self._error(400, "BadDigest", "The CRC32 you specified did not match the calculated checksum.")
         if "partNumber" in query:
             _bump("part")
             up = STATE["uploads"].get(query.get("uploadId"))
@@ -219,7 +232,14 @@ class Handler(BaseHTTPRequestHandler):
         if not m or int(m.group(1)) >= len(data):
             return self._error(416, "InvalidRange", "The requested range is not satisfiable")
         a, b = int(m.group(1)), min(int(m.group(2)), len(data) - 1)
-        self._reply(206, data[a:b + 1], {"Content-Range": f"bytes {a}-{b}/{len(data)}"})
+        headers = {"Content-Range": f"bytes {a}-{b}/{len(data)}"}
+        part = data[a:b + 1]
+        if self.headers.get("x-amz-checksum-mode") == "ENABLED" and a == 0 and b == len(data) - 1:  # the whole object: its checksum goes along
+            _bump("checksums_sent")
+            headers["x-amz-checksum-crc32"] = _crc(data)
+            if ARGS.corrupt_downloads and part:
+                part = bytes([part[0] ^ 0xFF]) + part[1:]
+        self._reply(206, part, headers)
 
     def do_HEAD(self):
         got = self._begin()
@@ -257,6 +277,7 @@ def main():
     ap.add_argument("--session-token", default="")
     ap.add_argument("--region", default="us-east-1")
     ap.add_argument("--close-after", type=int, default=0)
+    ap.add_argument("--corrupt-downloads", action="store_true", help="flip a byte of every download that carries a checksum")
     ap.add_argument("--tls", nargs=2, metavar=("CERT", "KEY"))
     ARGS = ap.parse_args()
     for b in ARGS.bucket or ["test-bucket"]:

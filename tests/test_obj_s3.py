@@ -191,6 +191,50 @@ def test_connections_the_server_dropped_while_idle_are_replaced():
         server.close()
 
 
+def test_checksums_go_with_uploads_and_are_compared_on_downloads(s3):
+    a = nixl_agent("s3_cs", nixl_agent_config(backends=[]))
+    a.create_backend("OBJ", s3.params(req_checksum="supported", resp_checksum="supported", crtMinLimit=str(5 << 20)))
+    small = torch.randint(0, 255, (300000,), dtype=torch.uint8)
+    big = torch.randint(0, 255, ((6 << 20) + 5,), dtype=torch.uint8)
+    a.register_memory(small)
+    a.register_memory(big)
+    assert torch.equal(_roundtrip(a, "s3_cs", "sum-small.bin", small), small)
+    assert torch.equal(_roundtrip(a, "s3_cs", "sum-big.bin", big, dev_id=2), big)
+    stats = s3.admin("stats")
+    assert stats["checksums_checked"] == 1 + 2 and stats["bad_checksum"] == 0  # one object, two parts
+    assert stats["checksums_sent"] == 1  # the small one came back whole; ranges of the large one carry none
+    assert stats["bad_signature"] == 0   # the checksum header is among the signed ones
+
+
+def test_a_download_that_does_not_match_its_checksum_fails():
+    server = _Server("--corrupt-downloads")
+    try:
+        a = nixl_agent("s3_cs2", nixl_agent_config(backends=[]))
+        a.create_backend("OBJ", server.params(req_checksum="supported", resp_checksum="supported"))
+        src = torch.arange(5000, dtype=torch.int32)
+        dst = torch.zeros_like(src)
+        a.register_memory(src)
+        a.register_memory(dst)
+        a.register_memory([(0, 20000, 1, "flipped.bin")], "OBJ")
+        remote = a.get_xfer_descs([(0, 20000, 1)], "OBJ")
+        h = a.initialize_xfer("WRITE", a.get_xfer_descs(src), remote, "s3_cs2")
+        a.transfer(h)
+        assert _wait(a, h) == "DONE"
+        h = a.initialize_xfer("READ", a.get_xfer_descs(dst), remote, "s3_cs2")
+        st = a.transfer(h)
+        assert (st if st != "PROC" else _wait(a, h)) == "ERR"
+        # without the comparison the flipped byte would have gone unnoticed
+        b = nixl_agent("s3_cs3", nixl_agent_config(backends=[]))
+        b.create_backend("OBJ", server.params())
+        b.register_memory(dst)
+        b.register_memory([(0, 20000, 1, "flipped.bin")], "OBJ")
+        h = b.initialize_xfer("READ", b.get_xfer_descs(dst), b.get_xfer_descs([(0, 20000, 1)], "OBJ"), "s3_cs3")
+        b.transfer(h)
+        assert _wait(b, h) == "DONE"
+    finally:
+        server.close()
+
+
 def test_environment_variables_name_the_service(monkeypatch, s3):
     monkeypatch.setenv("AWS_ENDPOINT_OVERRIDE", s3.endpoint)
     monkeypatch.setenv("AWS_DEFAULT_BUCKET", "kv-cache")
