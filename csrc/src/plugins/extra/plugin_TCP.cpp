@@ -24,6 +24,8 @@
 //     against the registrations (key, bounds), moves the bytes, answers.  A range outside a registration is answered with
 //     an error and its payload is discarded; the connection stays usable.
 //   * A request's notification is sent when the last acknowledgement has arrived, on the peer's first rail.
+//   * A read or a write that makes no progress for `stall_timeout_ms` (30 s) inside a message, or while answers are
+//     outstanding, counts as a broken connection; silence between messages does not.
 //   * A connection that breaks fails what was in flight on it with NIXL_ERR_REMOTE_DISCONNECT; the next post tries to
 //     connect again, and reports the same status when the peer cannot be reached.
 //
@@ -144,8 +146,9 @@ bool recvBuf(int fd, void *p, size_t n) {
 }
 
 // Reads `n` bytes, polling the socket for up to `spin_us` first: the answer to a small message is back sooner than a
-// sleeping thread is woken.
-bool recvSpin(int fd, void *p, size_t n, unsigned spin_us) {
+// sleeping thread is woken.  The socket's receive time-out ends a read that has stalled; with `idle_ok` it does not end
+// the wait for the first byte (a connection with nothing to say is not a stalled one).
+bool recvSpin(int fd, void *p, size_t n, unsigned spin_us, bool idle_ok = false) {
     if (spin_us) {
         const uint64_t end = nixl_util::nowNs() + uint64_t(spin_us) * 1000;
         do {
@@ -157,7 +160,20 @@ bool recvSpin(int fd, void *p, size_t n, unsigned spin_us) {
 #endif
         } while (nixl_util::nowNs() < end);
     }
-    return recvBuf(fd, p, n);
+    for (;;) {
+        const ssize_t k = ::recv(fd, p, n, 0);
+        if (k > 0) return recvBuf(fd, static_cast<char *>(p) + k, n - static_cast<size_t>(k));
+        if (k == 0) return false;
+        if (errno == EINTR || (idle_ok && (errno == EAGAIN || errno == EWOULDBLOCK))) continue;
+        return false;
+    }
+}
+
+// A read or write that makes no progress for this long ends the connection (0: never).
+void setStallTimeout(int fd, int ms) {
+    const timeval tv{ms / 1000, (ms % 1000) * 1000};
+    ::setsockopt(fd, SOL_SOCKET, SO_RCVTIMEO, &tv, sizeof(tv));
+    ::setsockopt(fd, SOL_SOCKET, SO_SNDTIMEO, &tv, sizeof(tv));
 }
 
 void tuneSocket(int fd, int buf_bytes) {
@@ -487,11 +503,27 @@ private:
         if (!ok) die(); // fails what is in flight, this message included
     }
 
+    // The next header.  While nothing is awaited the receive time-out only ends one round of waiting.
+    bool recvHeader(Hdr &h, bool awaiting) {
+        if (awaiting) return recvSpin(fd_, &h, sizeof(h), kSpinUs);
+        for (;;) {
+            const ssize_t k = ::recv(fd_, &h, sizeof(h), 0);
+            if (k > 0) return recvBuf(fd_, reinterpret_cast<char *>(&h) + k, sizeof(h) - static_cast<size_t>(k));
+            if (k == 0) return false;
+            if (errno == EINTR) continue;
+            if (errno != EAGAIN && errno != EWOULDBLOCK) return false;
+            if (waiting_.load(std::memory_order_relaxed) > 0) return recvSpin(fd_, &h, sizeof(h), 0); // something was sent meanwhile: from now on silence counts
+        }
+    }
+
     void receiverLoop() {
         Bounce bounce;
         for (;;) {
             Hdr h;
-            if (!recvSpin(fd_, &h, sizeof(h), waiting_.load(std::memory_order_relaxed) > 0 ? kSpinUs : 0) || h.magic != kMagic) break;
+            // With answers outstanding a silent peer is a stalled one; with none it is merely idle.  (A request that is
+            // submitted while this thread sits in an idle wait is covered by the wait's next round.)
+            const bool awaiting = waiting_.load(std::memory_order_relaxed) > 0;
+            if (!recvHeader(h, awaiting) || h.magic != kMagic) break;
             std::shared_ptr<Msg> m;
             {
                 std::lock_guard<std::mutex> g(imu_);
@@ -596,6 +628,7 @@ public:
         chunk_ = static_cast<size_t>(std::clamp(paramLong(cp, "chunk_bytes", 4L << 20), 4096L, 1L << 30));
         bufBytes_ = static_cast<int>(std::clamp(paramLong(cp, "socket_buffer_bytes", 4L << 20), 0L, 1L << 30));
         connectTimeoutMs_ = static_cast<int>(std::clamp(paramLong(cp, "connect_timeout_ms", 3000), 1L, 600000L));
+        stallTimeoutMs_ = static_cast<int>(std::clamp(paramLong(cp, "stall_timeout_ms", 30000), 0L, 3600000L));
         const long port = std::clamp(paramLong(cp, "port", 0), 0L, 65535L);
         tag_ = nixl_util::random64();
         host_ = nixl_util::hostName();
@@ -1035,8 +1068,7 @@ private:
             Hdr reply;
             if (sendBuf(fd, &h, sizeof(h)) && sendBuf(fd, meta.data(), meta.size()) && recvBuf(fd, &reply, sizeof(reply)) &&
                 reply.magic == kMagic && reply.op == OP_ACK && reply.status == NIXL_SUCCESS) {
-                timeval none{0, 0};
-                ::setsockopt(fd, SOL_SOCKET, SO_RCVTIMEO, &none, sizeof(none));
+                setStallTimeout(fd, stallTimeoutMs_);
                 return std::make_shared<ClientConn>(fd);
             }
             ::close(fd);
@@ -1154,7 +1186,7 @@ private:
         std::vector<Seg> segs;
         for (bool first = true;; first = false) {
             Hdr h;
-            if (!recvSpin(fd, &h, sizeof(h), first ? 0 : kSpinUs) || h.magic != kMagic || h.metaLen > (64u << 20) || h.nDescs > kMaxDescsPerMsg) return;
+            if (!recvSpin(fd, &h, sizeof(h), first ? 0 : kSpinUs, !from.empty()) || h.magic != kMagic || h.metaLen > (64u << 20) || h.nDescs > kMaxDescsPerMsg) return;
             Hdr reply;
             reply.id = h.id;
             if (from.empty() && (h.op != OP_HELLO || h.metaLen > 4096)) return; // a stranger gets to say who it is, briefly, and nothing else
@@ -1174,8 +1206,7 @@ private:
                 reply.status = ok ? NIXL_SUCCESS : NIXL_ERR_MISMATCH;
                 if (!sendBuf(fd, &reply, sizeof(reply)) || !ok) return;
                 from = who;
-                const timeval none{0, 0}; // a known peer may stay silent for as long as it likes
-                ::setsockopt(fd, SOL_SOCKET, SO_RCVTIMEO, &none, sizeof(none));
+                setStallTimeout(fd, stallTimeoutMs_); // a known peer may stay silent between messages for as long as it likes, not inside one
                 continue;
             }
             if ((h.op != OP_WRITE && h.op != OP_READ) || from.empty() || h.metaLen != h.nDescs * sizeof(WireDesc)) return;
@@ -1218,7 +1249,7 @@ private:
         }
     }
 
-    int rails_ = 4, bufBytes_ = 0, connectTimeoutMs_ = 3000;
+    int rails_ = 4, bufBytes_ = 0, connectTimeoutMs_ = 3000, stallTimeoutMs_ = 30000;
     size_t chunk_ = 4u << 20;
     bool cuda_ = false;
     uint64_t tag_ = 0;
@@ -1265,7 +1296,8 @@ extern "C" NIXL_PLUGIN_EXPORT nixlBackendPlugin *nixl_plugin_init() {
                                                      {"local_addresses", ""},
                                                      {"device_id", ""},
                                                      {"socket_buffer_bytes", "4194304"},
-                                                     {"connect_timeout_ms", "3000"}},
+                                                     {"connect_timeout_ms", "3000"},
+                                                     {"stall_timeout_ms", "30000"}},
                                                     {DRAM_SEG, VRAM_SEG});
 }
 extern "C" NIXL_PLUGIN_EXPORT void nixl_plugin_fini() {}

@@ -6,6 +6,7 @@
 // show is anything inside the real kernels; those are covered on GPUs (tests/test_gpu_*.py).
 #include <fcntl.h>
 
+#include <algorithm>
 #include <atomic>
 #include <chrono>
 #include <cstdlib>
@@ -633,6 +634,90 @@ TEST_CASE(device_memory_crosses_the_tcp_backend_through_its_staging_buffers) {
     CHECK_EQ(notifs, 4);
     CHECK_EQ(a.invalidateRemoteMD(bn), NIXL_SUCCESS);
     CHECK(a.deregisterMem(ra) == NIXL_SUCCESS && b.deregisterMem(rb) == NIXL_SUCCESS && b.deregisterMem(rh) == NIXL_SUCCESS);
+}
+
+TEST_CASE(random_requests_against_a_model_under_every_path_choice) {
+    // Requests drawn at random (1 to 300 pieces from one byte to 3 MiB, touching or apart, in any order on either side,
+    // WRITE and READ, some posted twice, several in flight) under engine settings that push them down different
+    // paths: everything through the copy kernel, long runs through the copy engines, small requests through the doorbell
+    // proxy, merging on and off, one stream and four.  After each wave both buffers must equal the model.
+    struct Setting {
+        const char *name;
+        nixl_b_params_t params;
+    };
+    const Setting settings[] = {
+        {"kernel only", {{"proxy", "false"}, {"ce_threshold", "0"}}},
+        {"copy engines from 256 KiB", {{"proxy", "false"}, {"ce_threshold", "262144"}}},
+        {"proxy and copy engines", {{"ce_threshold", "1048576"}, {"num_streams", "4"}}},
+        {"no merging", {{"coalesce", "false"}, {"ce_threshold", "524288"}, {"num_streams", "2"}}},
+    };
+    constexpr size_t kBytes = 24 << 20;
+    std::mt19937_64 rng(20240611);
+    for (const Setting &st : settings) {
+        Pair p(st.params, kBytes);
+        std::vector<uint8_t> model_src(p.src.p, p.src.p + kBytes), model_dst(kBytes, 0);
+        for (int wave = 0; wave < 40; ++wave) {
+            // a wave: up to three requests in flight over disjoint thirds of the buffers
+            const int in_flight = 1 + static_cast<int>(rng() % 3);
+            std::vector<nixlXferReqH *> reqs;
+            for (int r = 0; r < in_flight; ++r) {
+                const size_t lane = kBytes / 3, base = lane * static_cast<size_t>(r);
+                const nixl_xfer_op_t op = rng() % 3 == 0 ? NIXL_READ : NIXL_WRITE;
+                const int shape = static_cast<int>(rng() % 4);
+                int n = shape == 0 ? 1 : shape == 1 ? 2 + static_cast<int>(rng() % 30) : shape == 2 ? 33 + static_cast<int>(rng() % 268) : 1 + static_cast<int>(rng() % 6);
+                std::vector<size_t> len(static_cast<size_t>(n));
+                size_t total = 0;
+                for (auto &l : len) {
+                    l = shape == 3 ? 200000 + rng() % 2900000 : shape == 0 ? 1 + rng() % 5000000 : 1 + rng() % (rng() % 5 == 0 ? 150000 : 6000);
+                    total += l;
+                }
+                while (total > lane) { // shrink until the wave fits its lane
+                    total = 0;
+                    for (auto &l : len) {
+                        l = std::max<size_t>(1, l / 2);
+                        total += l;
+                    }
+                }
+                auto place = [&](bool touching) {
+                    std::vector<size_t> order(len.size()), off(len.size());
+                    for (size_t i = 0; i < order.size(); ++i) order[i] = i;
+                    if (rng() % 2) std::shuffle(order.begin(), order.end(), rng);
+                    size_t slack = lane - total, at = base;
+                    for (size_t k = 0; k < order.size(); ++k) {
+                        const size_t gap = touching || slack == 0 ? 0 : rng() % (slack / (order.size() - k) + 1);
+                        at += gap;
+                        slack -= gap;
+                        off[order[k]] = at;
+                        at += len[order[k]];
+                    }
+                    return off;
+                };
+                const std::vector<size_t> lo = place(rng() % 2), ro = place(rng() % 2);
+                std::vector<std::pair<size_t, size_t>> cuts;
+                for (size_t i = 0; i < len.size(); ++i) cuts.emplace_back(lo[i], len[i]);
+                for (size_t i = 0; i < len.size(); ++i) {
+                    if (op == NIXL_WRITE) std::memcpy(model_dst.data() + ro[i], model_src.data() + lo[i], len[i]);
+                    else std::memcpy(model_src.data() + lo[i], model_dst.data() + ro[i], len[i]);
+                }
+                nixlXferReqH *req = p.request(op, cuts, ro);
+                CHECK(p.a.postXferReq(req) >= 0);
+                reqs.push_back(req);
+            }
+            for (nixlXferReqH *req : reqs) CHECK_EQ(waitDone(p.a, req), NIXL_SUCCESS);
+            if (rng() % 2) { // the same requests once more: nothing may change
+                for (nixlXferReqH *req : reqs) CHECK(p.a.postXferReq(req) >= 0);
+                for (nixlXferReqH *req : reqs) CHECK_EQ(waitDone(p.a, req), NIXL_SUCCESS);
+            }
+            for (nixlXferReqH *req : reqs) CHECK_EQ(p.a.releaseXferReq(req), NIXL_SUCCESS);
+            if (std::memcmp(p.src.p, model_src.data(), kBytes) != 0 || std::memcmp(p.dst.p, model_dst.data(), kBytes) != 0)
+                throw harness::Failure(std::string("buffers differ from the model under '") + st.name + "', wave " + std::to_string(wave));
+            // fresh bytes for the next wave
+            for (size_t i = 0; i < kBytes; i += 4093) {
+                p.src.p[i] = model_src[i] = static_cast<uint8_t>(rng());
+                p.dst.p[i] = model_dst[i] = static_cast<uint8_t>(rng());
+            }
+        }
+    }
 }
 
 TEST_CASE(launch_failures_are_reported_and_leave_the_engine_usable) {

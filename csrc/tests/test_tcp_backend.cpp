@@ -557,6 +557,84 @@ TEST_CASE(a_listener_survives_strangers_and_garbage) {
     CHECK(a.deregisterMem(ra) == NIXL_SUCCESS && b.deregisterMem(rb) == NIXL_SUCCESS);
 }
 
+TEST_CASE(a_peer_that_falls_silent_inside_an_exchange_is_given_up) {
+    // The peer's port is taken over by a listener that accepts the introduction, takes a request and then says nothing
+    // (a host that froze).  With answers outstanding the silence is a stall: after `stall_timeout_ms` the request fails
+    // with a disconnect instead of staying in progress for ever.
+    int probe = ::socket(AF_INET, SOCK_STREAM, 0);
+    sockaddr_in sa{};
+    sa.sin_family = AF_INET;
+    sa.sin_addr.s_addr = htonl(INADDR_LOOPBACK);
+    socklen_t len = sizeof(sa);
+    CHECK(probe >= 0 && ::bind(probe, reinterpret_cast<sockaddr *>(&sa), sizeof(sa)) == 0 &&
+          ::getsockname(probe, reinterpret_cast<sockaddr *>(&sa), &len) == 0);
+    const uint16_t port = ntohs(sa.sin_port);
+    ::close(probe);
+    nixlAgent ini("tcp_st_ini", nixlAgentConfig(false));
+    nixlBackendH *h = nullptr;
+    CHECK_EQ(ini.createBackend("TCP", {{"address", "127.0.0.1"}, {"rails", "1"}, {"stall_timeout_ms", "300"}}, h), NIXL_SUCCESS);
+    std::vector<uint8_t> src(1 << 16, 1), dst(1 << 16, 0);
+    nixl_reg_dlist_t rs(DRAM_SEG), rd(DRAM_SEG);
+    rs.addDesc(nixlBlobDesc(reinterpret_cast<uintptr_t>(src.data()), src.size(), 0, ""));
+    rd.addDesc(nixlBlobDesc(reinterpret_cast<uintptr_t>(dst.data()), dst.size(), 0, ""));
+    CHECK_EQ(ini.registerMem(rs), NIXL_SUCCESS);
+    auto peer = std::make_unique<nixlAgent>("tcp_st_peer", nixlAgentConfig(false));
+    CHECK_EQ(peer->createBackend("TCP", {{"address", "127.0.0.1"}, {"port", std::to_string(port)}}, h), NIXL_SUCCESS);
+    CHECK_EQ(peer->registerMem(rd), NIXL_SUCCESS);
+    nixl_blob_t md;
+    std::string name;
+    peer->getLocalMD(md);
+    CHECK_EQ(ini.loadRemoteMD(md, name), NIXL_SUCCESS);
+    nixl_xfer_dlist_t l(DRAM_SEG), r(DRAM_SEG);
+    l.addDesc(nixlBasicDesc(reinterpret_cast<uintptr_t>(src.data()), 4096, 0));
+    r.addDesc(nixlBasicDesc(reinterpret_cast<uintptr_t>(dst.data()), 4096, 0));
+    nixlXferReqH *w = nullptr;
+    CHECK_EQ(ini.createXferReq(NIXL_WRITE, l, r, "tcp_st_peer", w), NIXL_SUCCESS);
+    peer->deregisterMem(rd);
+    peer.reset();
+
+    // the frozen host: says yes to whoever introduces itself, then reads and never answers
+    const int lfd = ::socket(AF_INET, SOCK_STREAM, 0);
+    const int one = 1;
+    ::setsockopt(lfd, SOL_SOCKET, SO_REUSEADDR, &one, sizeof(one));
+    sa.sin_port = htons(port);
+    CHECK(lfd >= 0 && ::bind(lfd, reinterpret_cast<sockaddr *>(&sa), sizeof(sa)) == 0 && ::listen(lfd, 4) == 0);
+    std::atomic<bool> stop{false};
+    std::atomic<int> got_request{0};
+    std::thread frozen([&] {
+        const int fd = ::accept(lfd, nullptr, nullptr);
+        if (fd < 0) return;
+        char hdr[40];
+        if (::recv(fd, hdr, sizeof(hdr), MSG_WAITALL) == 40) {
+            uint32_t meta_len;
+            std::memcpy(&meta_len, hdr + 32, 4);
+            std::vector<char> meta(meta_len);
+            ::recv(fd, meta.data(), meta.size(), MSG_WAITALL);
+            char reply[40] = {0};
+            std::memcpy(reply, hdr, 4);            // magic
+            const uint16_t ack = 4;
+            std::memcpy(reply + 4, &ack, 2);       // op = acknowledgement, status 0
+            ::send(fd, reply, sizeof(reply), MSG_NOSIGNAL);
+            if (::recv(fd, hdr, sizeof(hdr), MSG_WAITALL) == 40) got_request.store(1);
+        }
+        while (!stop.load()) std::this_thread::sleep_for(std::chrono::milliseconds(5));
+        ::close(fd);
+    });
+    const auto t0 = clk::now();
+    nixl_status_t st = ini.postXferReq(w);
+    CHECK_EQ(st, NIXL_IN_PROG); // the request went out
+    st = waitDone(ini, w, 10);
+    const auto took = clk::now() - t0;
+    CHECK_EQ(st, NIXL_ERR_REMOTE_DISCONNECT);
+    CHECK(took > std::chrono::milliseconds(250) && took < std::chrono::seconds(5));
+    CHECK_EQ(got_request.load(), 1);
+    stop.store(true);
+    frozen.join();
+    ::close(lfd);
+    ini.releaseXferReq(w);
+    CHECK_EQ(ini.deregisterMem(rs), NIXL_SUCCESS);
+}
+
 TEST_CASE(between_two_processes_and_a_target_that_exits) {
     constexpr size_t kBytes = 6 << 20;
     struct Shared {
