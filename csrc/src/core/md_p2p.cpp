@@ -77,8 +77,18 @@ bool recvFrame(int fd, std::string &body, int timeout_ms) {
         NIXL_ERROR << "p2p metadata: frame of " << n << " bytes exceeds the limit";
         return false;
     }
-    body.resize(n);
-    return n == 0 || readAll(fd, body.data(), n, kBodyTimeoutMs);
+    // Memory follows the bytes that have arrived, not the length a stranger announced.
+    body.clear();
+    const int64_t deadline = nowMs() + kBodyTimeoutMs;
+    for (uint64_t got = 0; got < n;) {
+        const size_t piece = static_cast<size_t>(std::min<uint64_t>(n - got, 1u << 20));
+        const int64_t left = deadline - nowMs();
+        if (left <= 0) return false;
+        body.resize(static_cast<size_t>(got) + piece);
+        if (!readAll(fd, body.data() + got, piece, static_cast<int>(left))) return false;
+        got += piece;
+    }
+    return true;
 }
 
 int dial(const std::string &ip, int port, int timeout_ms) {
@@ -139,7 +149,7 @@ nixlP2PListener::nixlP2PListener(nixlMetadataContext &ctx, uint16_t port, uint64
 nixlP2PListener::~nixlP2PListener() {
     stop();
     if (listenFd_ >= 0) ::close(listenFd_);
-    for (int fd : clients_) ::close(fd);
+    for (const Client &c : clients_) ::close(c.fd);
 }
 
 void nixlP2PListener::start() {
@@ -155,33 +165,73 @@ void nixlP2PListener::stop() {
 
 void nixlP2PListener::loop() {
     const int wait_ms = static_cast<int>(std::max<uint64_t>(1, std::min<uint64_t>(delayUs_ / 1000, 200)));
+    constexpr size_t kMaxClients = 256;
     while (!stop_) {
         std::vector<pollfd> fds;
         fds.push_back({listenFd_, POLLIN, 0});
-        for (int fd : clients_) fds.push_back({fd, POLLIN, 0});
+        for (const Client &c : clients_) fds.push_back({c.fd, POLLIN, 0});
         const int pr = ::poll(fds.data(), fds.size(), wait_ms);
-        if (pr <= 0) continue;
-        if (fds[0].revents & POLLIN) {
-            const int c = ::accept4(listenFd_, nullptr, nullptr, SOCK_NONBLOCK);
-            if (c >= 0) {
+        const size_t polled = clients_.size();
+        if (pr > 0 && (fds[0].revents & POLLIN)) {
+            const int fd = ::accept4(listenFd_, nullptr, nullptr, SOCK_NONBLOCK | SOCK_CLOEXEC);
+            if (fd >= 0 && clients_.size() >= kMaxClients) {
+                ::close(fd); // full house: better to refuse than to let strangers push the peers out
+            } else if (fd >= 0) {
                 int one = 1;
-                setsockopt(c, IPPROTO_TCP, TCP_NODELAY, &one, sizeof(one));
-                clients_.push_back(c);
+                setsockopt(fd, IPPROTO_TCP, TCP_NODELAY, &one, sizeof(one));
+                Client c;
+                c.fd = fd;
+                clients_.push_back(std::move(c));
             }
         }
-        for (size_t i = 1; i < fds.size(); ++i)
-            if (fds[i].revents & (POLLIN | POLLHUP | POLLERR)) serve(fds[i].fd);
+        const int64_t now = nowMs();
+        for (size_t i = 0; i < polled; ++i) {
+            Client &c = clients_[i];
+            bool keep = true;
+            if (pr > 0 && (fds[i + 1].revents & (POLLIN | POLLHUP | POLLERR))) keep = advance(c);
+            if (keep && c.startedMs && now - c.startedMs > kBodyTimeoutMs) keep = false; // a frame must not take for ever
+            if (!keep) {
+                ::close(c.fd);
+                c.fd = -1;
+            }
+        }
+        clients_.erase(std::remove_if(clients_.begin(), clients_.end(), [](const Client &c) { return c.fd < 0; }), clients_.end());
     }
 }
 
-// Handle one frame from a client; drops the connection on EOF or protocol error.
-void nixlP2PListener::serve(int fd) {
-    auto drop = [&] {
-        ::close(fd);
-        clients_.erase(std::remove(clients_.begin(), clients_.end(), fd), clients_.end());
-    };
-    std::string body;
-    if (!recvFrame(fd, body, 50)) return drop();
+bool nixlP2PListener::advance(Client &c) {
+    for (;;) {
+        const bool have_len = c.buf.size() >= sizeof(uint64_t);
+        if (have_len && c.buf.size() == sizeof(uint64_t)) {
+            std::memcpy(&c.frameLen, c.buf.data(), sizeof(uint64_t));
+            if (c.frameLen > kMaxFrame) {
+                NIXL_ERROR << "p2p metadata: frame of " << c.frameLen << " bytes exceeds the limit";
+                return false;
+            }
+        }
+        const uint64_t want = have_len ? sizeof(uint64_t) + c.frameLen : sizeof(uint64_t);
+        if (have_len && c.buf.size() == want) { // a whole frame
+            const std::string frame = c.buf.substr(sizeof(uint64_t));
+            c.buf.clear();
+            c.startedMs = 0;
+            if (!handle(c, frame)) return false;
+            continue;
+        }
+        char tmp[65536];
+        const size_t room = static_cast<size_t>(std::min<uint64_t>(want - c.buf.size(), sizeof(tmp)));
+        const ssize_t r = ::recv(c.fd, tmp, room, 0);
+        if (r == 0) return false;
+        if (r < 0) return errno == EINTR || errno == EAGAIN || errno == EWOULDBLOCK; // nothing more for now
+        if (c.buf.empty()) c.startedMs = nowMs();
+        c.buf.append(tmp, static_cast<size_t>(r));
+    }
+}
+
+// One frame from a client; false drops the connection (protocol error, or the answer could not be sent).
+bool nixlP2PListener::handle(Client &c, const std::string &body) {
+    const int fd = c.fd;
+    auto drop = [] { return false; };
+
     auto is = [&](const char *cmd) { return body.compare(0, std::strlen(cmd), cmd) == 0; };
     if (is(kLoad)) {
         std::string who;
@@ -200,4 +250,5 @@ void nixlP2PListener::serve(int fd) {
         NIXL_ERROR << "p2p metadata: unknown command";
         return drop();
     }
+    return true;
 }

@@ -37,8 +37,17 @@ public:
     void stop();
 
 private:
+    // One accepted connection and the frame that is arriving on it.  Frames are put together as their bytes come in, so
+    // a connection that announces much and sends little keeps nobody else waiting and holds no more memory than it sent.
+    struct Client {
+        int fd = -1;
+        std::string buf;       // the length word, then the body, as far as received
+        uint64_t frameLen = 0; // valid once buf holds the length word
+        int64_t startedMs = 0; // when the first byte of the current frame came (0: between frames)
+    };
     void loop();
-    void serve(int fd);
+    bool advance(Client &c);                           // reads what is there; false: drop the connection
+    bool handle(Client &c, const std::string &frame);  // one complete frame; false: drop the connection
 
     nixlMetadataContext &ctx_;
     int listenFd_ = -1;
@@ -46,7 +55,7 @@ private:
     uint64_t delayUs_;
     std::atomic<bool> stop_{false};
     std::thread th_;
-    std::vector<int> clients_;
+    std::vector<Client> clients_;
 };
 
 #endif

@@ -194,3 +194,48 @@ def test_etcd_gateway_metadata_roundtrip_and_invalidation(monkeypatch, watch):
     finally:
         proc.terminate()
         proc.wait(timeout=10)
+
+
+def test_the_metadata_listener_survives_strangers():
+    """Anyone who can reach the listener's port can send it bytes: noise, a frame that announces a gigabyte and sends
+    none of it, an unknown command, a connection dropped inside a frame.  The agent keeps serving its real peers, and its
+    memory does not follow announced lengths."""
+    import resource
+    import struct
+
+    from nixl_b200 import nixl_agent, nixl_agent_config
+
+    port = _free_port()
+    a = nixl_agent("md_victim", nixl_agent_config(enable_prog_thread=False, enable_listen_thread=True, listen_port=port, backends=["NVLINK"]))
+    buf = torch.zeros(4096, dtype=torch.uint8)
+    a.register_memory(buf)
+
+    def dial():
+        s = socket.create_connection(("127.0.0.1", port), timeout=5)
+        return s
+
+    before = resource.getrusage(resource.RUSAGE_SELF).ru_maxrss
+    socks = []
+    for payload in (os.urandom(512), struct.pack("<Q", 1 << 30), struct.pack("<Q", (1 << 30) + 1), struct.pack("<Q", 64) + b"NIXLCOMM:WHAT" + b"x" * 51,
+                    struct.pack("<Q", 1000) + b"NIXLCOMM:LOAD" + b"\x00" * 10, struct.pack("<Q", 13) + b"NIXLCOMM:LOAD", b"\x01\x02\x03"):
+        s = dial()
+        s.sendall(payload)
+        socks.append(s)
+    for _ in range(8):  # several that announce a gigabyte each and then just sit there
+        s = dial()
+        s.sendall(struct.pack("<Q", 1 << 30) + b"NIXLCOMM:LOAD")
+        socks.append(s)
+    time.sleep(0.5)
+    for s in socks[::2]:
+        s.close()
+    grown_kb = resource.getrusage(resource.RUSAGE_SELF).ru_maxrss - before
+    assert grown_kb < 512 << 10, grown_kb  # nothing like the announced gigabytes was set aside
+    # a real peer is served as if nothing had happened
+    b = nixl_agent("md_friend", nixl_agent_config(enable_prog_thread=False, enable_listen_thread=True, listen_port=_free_port(), backends=["NVLINK"]))
+    b.fetch_remote_metadata("md_victim", "127.0.0.1", port)
+    deadline = time.time() + 20
+    while time.time() < deadline and not b.check_remote_metadata("md_victim"):
+        time.sleep(0.01)
+    assert b.check_remote_metadata("md_victim")
+    for s in socks[1::2]:
+        s.close()
