@@ -179,3 +179,14 @@ def test_native_nixlbench_between_two_processes(backend, op):
         if target.poll() is None:
             target.kill()
         target.wait()
+
+
+@pytest.mark.parametrize("op", ["WRITE", "READ"])
+def test_nixlbench_vram_over_the_tcp_backend_on_the_stand_in_runtime(op):
+    """Device memory on both ends of the socket transport (staged through pinned buffers), driven by the sweep tool built
+    against the stand-in runtime: blocks up to 8 MiB, so the 4 MiB staging buffer is cycled, every block checked."""
+    res = _nixlbench_fake_gpu("--backend", "TCP", "--mem", "VRAM", "--op", op, "--min", "65536", "--max", str(8 << 20), "--batch", "2", "--iters", "8",
+                              "--warmup", "2", "--check", "--param", "address=127.0.0.1")
+    assert res.returncode == 0, res.stdout + res.stderr
+    rows = [l.split() for l in res.stdout.splitlines() if l and l[0].isdigit()]
+    assert [r[0] for r in rows] == [str(65536 << i) for i in range(8)] and all(float(r[2]) > 0 for r in rows)
