@@ -15,6 +15,7 @@
 #include "core/agent_data.h"
 #include "core/plugin_manager.h"
 #include "nixl.h"
+#include "utils/topology.h"
 #include "serdes/serdes.h"
 
 namespace py = pybind11;
@@ -80,6 +81,43 @@ PYBIND11_MODULE(_bindings, m) {
 
     // Plug-in search path of the process (the manager is a singleton shared by all agents).
     m.def("add_plugin_directory", [](const std::string &dir) { nixlPluginManager::getInstance().addPluginDirectory(dir); });
+    // The host's GPUs and network devices from the PCI sysfs tree, and for every GPU the interfaces nearest to it.
+    m.def(
+        "pci_topology",
+        [](const std::string &root) {
+            const nixl::pciTopology t = nixl::pciTopology::scan(root);
+            auto dev = [](const nixl::pciDevice &d) {
+                py::dict o;
+                o["bdf"] = d.bdf;
+                o["numa_node"] = d.numaNode;
+                o["chain"] = d.chain;
+                o["vendor"] = d.vendor;
+                o["device"] = d.device;
+                o["interfaces"] = d.netInterfaces;
+                return o;
+            };
+            py::dict out;
+            py::list gpus, nics, near;
+            for (const auto &g : t.gpus()) gpus.append(dev(g));
+            for (const auto &n : t.nics()) nics.append(dev(n));
+            for (size_t g = 0; g < t.gpus().size(); ++g) {
+                py::list row;
+                for (const nixl::pciDevice *n : t.nicsNearGpu(g)) {
+                    py::dict e;
+                    e["bdf"] = n->bdf;
+                    e["interfaces"] = n->netInterfaces;
+                    e["distance"] = nixl::pciTopology::distance(t.gpus()[g], *n);
+                    row.append(e);
+                }
+                near.append(row);
+            }
+            out["gpus"] = gpus;
+            out["nics"] = nics;
+            out["nics_near_gpu"] = near;
+            out["text"] = t.toString();
+            return out;
+        },
+        py::arg("root") = "");
     m.def("get_plugin_directories", [] { return nixlPluginManager::getInstance().getPluginDirectories(); });
 
     m.attr("DRAM_SEG") = static_cast<int>(DRAM_SEG);

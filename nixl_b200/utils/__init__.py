@@ -42,3 +42,13 @@ def device_timed(fn: Callable[[], None], iters: int = 10, warmup: int = 3, flush
             times.append(e0.elapsed_time(e1) * 1e3)
     times.sort()
     return times[len(times) // 2]
+
+
+def pci_topology(root: str = "") -> dict:
+    """The host's GPUs and network devices as the PCI sysfs tree shows them, and per GPU the network devices nearest to
+    it (bridges through the closest common ancestor; another root complex and another NUMA node cost 100 each).
+    ``root`` defaults to ``$NIXL_SYSFS_PCI_ROOT`` or ``/sys/bus/pci/devices``.  ``python -m nixl_b200.utils`` prints it.
+    The TCP backend uses the same order for the addresses it publishes when ``device_id`` names a GPU."""
+    from .. import _bindings
+
+    return _bindings.pci_topology(root)

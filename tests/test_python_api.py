@@ -344,3 +344,33 @@ def test_released_handles_are_refused_in_python(pair):
     with pytest.raises(nixl_b200._bindings.nixlInvalidParamError):
         a.make_prepped_xfer("WRITE", side_l, [0], side_r, [0])
     a.release_dlist_handle(side_l)
+
+
+def test_pci_topology_of_a_made_up_tree(tmp_path):
+    """`nixl_b200.utils.pci_topology`: a GPU and a NIC under one switch, a second NIC under the chipset."""
+    from nixl_b200.utils import pci_topology
+
+    bus = tmp_path / "bus"
+    bus.mkdir()
+
+    def add(chain, vendor, cls, numa, ifs=()):
+        d = tmp_path / "devices" / chain
+        d.mkdir(parents=True)
+        (d / "vendor").write_text(vendor + "\n")
+        (d / "class").write_text(cls + "\n")
+        (d / "device").write_text("0x2901\n")
+        (d / "numa_node").write_text(f"{numa}\n")
+        for i in ifs:
+            (d / "net" / i).mkdir(parents=True)
+        (bus / chain.rsplit("/", 1)[-1]).symlink_to(d)
+
+    add("pci0000:15/0000:15:01.0/0000:16:00.0/0000:17:00.0/0000:1b:00.0", "0x10de", "0x030200", 0)
+    add("pci0000:15/0000:15:01.0/0000:16:00.0/0000:17:01.0/0000:1c:00.0", "0x15b3", "0x020700", 0, ["ib0"])
+    add("pci0000:00/0000:00:1f.0/0000:02:00.0", "0x8086", "0x020000", 0, ["eno1"])
+    topo = pci_topology(str(bus))
+    assert [g["bdf"] for g in topo["gpus"]] == ["0000:1b:00.0"] and topo["gpus"][0]["chain"][0] == "pci0000:15"
+    assert [n["interfaces"] for n in topo["nics"]] == [["eno1"], ["ib0"]]
+    near = topo["nics_near_gpu"][0]
+    assert [n["interfaces"] for n in near] == [["ib0"], ["eno1"]] and near[0]["distance"] == 4 and near[1]["distance"] > 100
+    assert "gpu0 0000:1b:00.0" in topo["text"]
+    assert pci_topology(str(tmp_path / "absent")) == {"gpus": [], "nics": [], "nics_near_gpu": [], "text": ""}
