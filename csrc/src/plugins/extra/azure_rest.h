@@ -230,6 +230,12 @@ private:
         return resp.status;
     }
     nixl_s3::Response exchange(Request &r, const void *body, size_t body_len, void *sink, size_t sink_len, size_t *got = nullptr) {
+        return nixl_s3::withRetries(cfg_.maxAttempts, [&] {
+            r.headers["x-ms-date"] = httpDateNow();
+            return exchangeOnce(r, body, body_len, sink, sink_len, got);
+        });
+    }
+    nixl_s3::Response exchangeOnce(Request &r, const void *body, size_t body_len, void *sink, size_t sink_len, size_t *got) {
         r.contentLength = body_len;
         std::string target = r.path;
         char sep = '?';

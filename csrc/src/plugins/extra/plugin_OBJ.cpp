@@ -255,6 +255,7 @@ private:
         cfg.signPayload = signing.empty() ? cfg.scheme == "http" : signing == "true";
         // "supported": use checksums where the service takes them; "required" (and nothing): only where the protocol
         // demands one, which none of the calls made here does.  The names are the reference's.
+        if (const std::string tries = param("max_attempts"); !tries.empty()) cfg.maxAttempts = std::max(1, std::atoi(tries.c_str()));
         cfg.sendChecksum = param("req_checksum") == "supported";
         cfg.checkChecksum = param("resp_checksum") == "supported";
         const std::string limit = param("crtMinLimit");
@@ -289,6 +290,7 @@ private:
             return false;
         }
         cfg.caBundle = param("ca_bundle", "AZURE_CA_BUNDLE");
+        if (const std::string tries = param("max_attempts"); !tries.empty()) cfg.maxAttempts = std::max(1, std::atoi(tries.c_str()));
         const std::string limit = param("crtMinLimit");
         if (!limit.empty() && std::atoll(limit.c_str()) > 0) largeLimit_ = static_cast<size_t>(std::atoll(limit.c_str()));
         s3_ = std::make_unique<nixl_azure::Client>(cfg);
@@ -387,6 +389,7 @@ extern "C" NIXL_PLUGIN_EXPORT nixlBackendPlugin *nixl_plugin_init() {
                                                         {"ca_bundle", ""},
                                                         {"crtMinLimit", ""},
                                                         {"payload_signing", ""},
+                                                        {"max_attempts", "3"},
                                                         {"req_checksum", ""},
                                                         {"resp_checksum", ""},
                                                         {"connection_string", ""},

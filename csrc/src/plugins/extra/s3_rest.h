@@ -443,7 +443,23 @@ struct HttpConfig {
     uint16_t port = 0;
     bool verifyTls = true;
     int timeoutMs = 30000;
+    int maxAttempts = 3; // a request that got no answer, or 500 / 502 / 503 / 504, is sent again (after 100 ms, 400 ms, ...)
 };
+
+// Runs `once` until it gives an answer worth keeping or the attempts are used up.  Object stores ask for this: "slow
+// down" and internal errors are part of their contract, and the SDKs retry them by default.
+template<class Once> inline Response withRetries(int max_attempts, Once &&once) {
+    Response resp;
+    int wait_ms = 100;
+    for (int attempt = 1;; ++attempt) {
+        resp = once();
+        const bool again = resp.status <= 0 || resp.status == 500 || resp.status == 502 || resp.status == 503 || resp.status == 504;
+        if (!again || attempt >= max_attempts) return resp;
+        timespec ts{wait_ms / 1000, (wait_ms % 1000) * 1000000L};
+        ::nanosleep(&ts, nullptr);
+        wait_ms *= 4;
+    }
+}
 
 struct Config : HttpConfig {
     std::string bucket, region = "us-east-1";
@@ -801,8 +817,12 @@ private:
         return resp.status;
     }
 
-    // Signs and sends `r` with `body`; the answer as Http::roundTrip gives it.
+    // Signs and sends `r` with `body`; the answer as Http::roundTrip gives it.  Every attempt is signed afresh (the date
+    // is part of the signature).
     Response exchange(Request &r, const void *body, size_t body_len, void *sink, size_t sink_len, size_t *got = nullptr) {
+        return withRetries(cfg_.maxAttempts, [&] { return exchangeOnce(r, body, body_len, sink, sink_len, got); });
+    }
+    Response exchangeOnce(Request &r, const void *body, size_t body_len, void *sink, size_t sink_len, size_t *got) {
         const std::string date = amzDateNow();
         r.headers["x-amz-date"] = date;
         if (body_len && cfg_.signPayload) r.payloadHash = hex(sha256(body, body_len));

@@ -3,7 +3,7 @@ ranged GetObject, HeadObject, DeleteObject, multipart upload), and a check of ev
 with hashlib / hmac, an implementation that shares nothing with the client's.  Runs as a process of its own:
 
     python fake_s3_server.py [--bucket NAME] [--access-key K --secret-key S] [--region R]
-                             [--close-after N] [--tls CERT KEY] [--corrupt-downloads]
+                             [--close-after N] [--tls CERT KEY] [--corrupt-downloads] [--slow-down N]
 
 prints its port on the first line of stdout and serves until it is killed.  `--close-after N` drops every connection
 after N requests without announcing it, which is what an idle keep-alive connection looks like to a client.
@@ -28,7 +28,8 @@ STATE = {
     "uploads": {},      # upload id -> {"bucket", "key", "parts": {n: bytes}}
     "stats": {"put": 0, "get": 0, "head": 0, "delete": 0, "create_mpu": 0, "part": 0, "complete_mpu": 0, "abort_mpu": 0,
               "bad_signature": 0, "unsigned_payload": 0, "connections": 0, "virtual_host": 0, "checksums_checked": 0, "checksums_sent": 0,
-              "bad_checksum": 0},
+              "bad_checksum": 0, "slow_downs": 0},
+    "slow_down": 0,     # this many of the next requests are answered with 503 SlowDown
     "lock": threading.Lock(),
     "next_upload": 1,
 }
@@ -135,6 +136,14 @@ class Handler(BaseHTTPRequestHandler):
         length = int(self.headers.get("Content-Length") or 0)
         body = self.rfile.read(length) if length else b""
         if self.path.startswith("/_admin/"):
+            return None
+        with STATE["lock"]:
+            busy = STATE["slow_down"] > 0
+            if busy:
+                STATE["slow_down"] -= 1
+                STATE["stats"]["slow_downs"] += 1
+        if busy:
+            self._error(503, "SlowDown", "Please reduce your request rate.")
             return None
         if not self._check_signature(body):
             _bump("bad_signature")
@@ -277,9 +286,11 @@ def main():
     ap.add_argument("--session-token", default="")
     ap.add_argument("--region", default="us-east-1")
     ap.add_argument("--close-after", type=int, default=0)
+    ap.add_argument("--slow-down", type=int, default=0, help="answer the first N requests with 503 SlowDown")
     ap.add_argument("--corrupt-downloads", action="store_true", help="flip a byte of every download that carries a checksum")
     ap.add_argument("--tls", nargs=2, metavar=("CERT", "KEY"))
     ARGS = ap.parse_args()
+    STATE["slow_down"] = ARGS.slow_down
     for b in ARGS.bucket or ["test-bucket"]:
         STATE["buckets"][b] = {}
     server = ThreadingHTTPServer(("127.0.0.1", 0), Handler)

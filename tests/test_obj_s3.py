@@ -235,6 +235,36 @@ def test_a_download_that_does_not_match_its_checksum_fails():
         server.close()
 
 
+def test_a_service_that_says_slow_down_is_asked_again():
+    server = _Server("--slow-down", "2")
+    try:
+        a = nixl_agent("s3_sd", nixl_agent_config(backends=[]))
+        a.create_backend("OBJ", server.params(num_threads="1"))
+        src = torch.arange(2000, dtype=torch.int32)
+        a.register_memory(src)
+        t0 = time.time()
+        assert torch.equal(_roundtrip(a, "s3_sd", "patience.bin", src), src)  # the PUT is refused twice and goes through the third time
+        assert time.time() - t0 >= 0.45  # 100 ms and 400 ms of waiting
+        stats = server.admin("stats")
+        assert stats["slow_downs"] == 2 and stats["put"] == 1 and stats["bad_signature"] == 0
+    finally:
+        server.close()
+    # with one attempt only the refusal is the answer
+    server = _Server("--slow-down", "1")
+    try:
+        b = nixl_agent("s3_sd2", nixl_agent_config(backends=[]))
+        b.create_backend("OBJ", server.params(max_attempts="1"))
+        src = torch.arange(100, dtype=torch.int32)
+        b.register_memory(src)
+        b.register_memory([(0, 400, 1, "impatient.bin")], "OBJ")
+        h = b.initialize_xfer("WRITE", b.get_xfer_descs(src), b.get_xfer_descs([(0, 400, 1)], "OBJ"), "s3_sd2")
+        st = b.transfer(h)
+        assert (st if st != "PROC" else _wait(b, h)) == "ERR"
+        assert server.admin("keys") == {"kv-cache": {}}
+    finally:
+        server.close()
+
+
 def test_environment_variables_name_the_service(monkeypatch, s3):
     monkeypatch.setenv("AWS_ENDPOINT_OVERRIDE", s3.endpoint)
     monkeypatch.setenv("AWS_DEFAULT_BUCKET", "kv-cache")
@@ -250,7 +280,7 @@ def test_environment_variables_name_the_service(monkeypatch, s3):
 
 def test_an_endpoint_that_does_not_answer_fails_the_request_not_the_process():
     a = nixl_agent("s3_i", nixl_agent_config(backends=[]))
-    a.create_backend("OBJ", dict(KEYS, bucket="kv-cache", endpoint_override="http://127.0.0.1:1"))
+    a.create_backend("OBJ", dict(KEYS, bucket="kv-cache", endpoint_override="http://127.0.0.1:1", max_attempts="2"))
     src = torch.ones(64, dtype=torch.uint8)
     a.register_memory(src)
     a.register_memory([(0, 64, 1, "nowhere")], "OBJ")
