@@ -12,6 +12,7 @@
 //             [--depth 1] [--num-threads 1] [--enable-pt] [--copy-path vector|bulk] [--param key=value]... [--check]
 //             [--prepared] [--recreate] [--reregister] [--scatter] [--config file]
 //             [--file path [--num-files N] [--direct]]      storage mode (POSIX, GDS, GDS_MT backends)
+//             [--backend OBJ|AZURE_BLOB --param bucket=... [--obj-prefix name]]   object stores: one object per block
 //             [--scheme pairwise|onetomany|manytoone|tp --num-initiator-dev N --num-target-dev M]
 //
 // --role target --listen-port P  /  --role initiator --peer-ip A --peer-port P: the pairwise sweep between two
@@ -74,6 +75,7 @@ struct Args {
     int num_threads = 1;    // worker threads of the pairwise scheme, each with its share of the batch
     bool enable_pt = false; // agents with a progress thread
     std::string file; // storage mode when set
+    std::string obj_prefix = "nixlbench";
     nixl_b_params_t extra; // --param key=value, passed to the backend
     // two processes (on one host or two): "target" owns the destination buffer and listens, "initiator" finds it there
     std::string role, peer_ip = "127.0.0.1";
@@ -105,6 +107,7 @@ bool setOption(Args &a, const std::string &k, const std::string &v) {
     else if (k == "--peer-port") a.peer_port = std::atoi(v.c_str());
     else if (k == "--listen-port") a.listen_port = std::atoi(v.c_str());
     else if (k == "--file") a.file = v;
+    else if (k == "--obj-prefix") a.obj_prefix = v;
     else if (k == "--num-files") a.num_files = std::max(1, std::atoi(v.c_str()));
     else if (k == "--param") {
         const size_t eq = v.find('=');
@@ -178,6 +181,12 @@ Spelling canonical(std::string k) {
         {"--posix-ios-pool-size", "ios_pool_size"}, {"--posix-kernel-queue-size", "kernel_queue_size"},
         {"--gds-mt-num-threads", "thread_count"},   {"--hf3fs-iopool-size", "iopool_size"},
         {"--obj-bucket-name", "bucket"},            {"--azure-blob-container-name", "container_name"},
+        {"--obj-access-key", "access_key"},         {"--obj-secret-key", "secret_key"},
+        {"--obj-session-token", "session_token"},   {"--obj-scheme", "scheme"},
+        {"--obj-region", "region"},                 {"--obj-use-virtual-addressing", "use_virtual_addressing"},
+        {"--obj-endpoint-override", "endpoint_override"}, {"--obj-req-checksum", "req_checksum"},
+        {"--obj-ca-bundle", "ca_bundle"},           {"--obj-crt-min-limit", "crtMinLimit"},
+        {"--azure-blob-account-url", "account_url"}, {"--azure-blob-connection-string", "connection_string"},
     };
     // One process drives both agents here: there is no runtime to rendezvous through, no second
     // worker type and one initiator / target device each.
@@ -502,7 +511,10 @@ int main(int argc, char **argv) {
         }
     }
     const bool vram = a.mem == "VRAM";
-    const bool storage = !a.file.empty();
+    // Object stores (OBJ: S3 or a directory; AZURE_BLOB): every block of a batch is an object of its own, named
+    // "<prefix>-<i>" (--obj-prefix, default "nixlbench"); WRITE puts it, READ gets it.
+    const bool objects = a.backend == "OBJ" || a.backend == "AZURE_BLOB";
+    const bool storage = !a.file.empty() || objects;
     int ndev = 0;
     if (vram && (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0)) {
         std::fprintf(stderr, "no GPU\n");
@@ -565,13 +577,21 @@ int main(int argc, char **argv) {
         return 4;
     }
     const nixl_mem_t mt = vram ? VRAM_SEG : DRAM_SEG;
-    const nixl_mem_t rmt = storage ? FILE_SEG : mt;
+    const nixl_mem_t rmt = objects ? OBJ_SEG : storage ? FILE_SEG : mt;
     const std::string remote_name = storage ? "initiator" : "target";
     nixl_reg_dlist_t rs(mt), rd(rmt);
     rs.addDesc(nixlBlobDesc(reinterpret_cast<uintptr_t>(src), buf_bytes, vram ? a.src_dev : 0, ""));
     std::vector<int> fds;
     const size_t file_bytes = (buf_bytes + a.num_files - 1) / a.num_files;
-    if (storage) {
+    if (objects) {
+        if (vram) {
+            std::fprintf(stderr, "object stores take host memory: --mem DRAM\n");
+            return 2;
+        }
+        // One registration per object, long enough for the largest block; devId is the object's number.
+        for (int i = 0; i < a.batch_max; ++i) rd.addDesc(nixlBlobDesc(0, a.max, static_cast<uint64_t>(i), a.obj_prefix + "-" + std::to_string(i)));
+        if (ini.registerMem(rs) != NIXL_SUCCESS || ini.registerMem(rd) != NIXL_SUCCESS) return 5;
+    } else if (storage) {
         // The buffer is striped over num_files files of file_bytes each; devId of a FILE descriptor is its fd.
         for (int f = 0; f < a.num_files; ++f) {
             const std::string path = a.num_files == 1 ? a.file : a.file + "." + std::to_string(f);
@@ -625,6 +645,22 @@ int main(int argc, char **argv) {
     for (size_t block = a.min; block <= a.max && block * batch <= buf_bytes; block *= 2) {
         int iters = a.iters, warm = a.warmup;
         const size_t per = block * batch;
+        if (objects && op == NIXL_READ) { // what is to be read has to be there: put the batch once, untimed
+            nixl_xfer_dlist_t l(mt), r(rmt);
+            for (int i = 0; i < batch; ++i) {
+                l.addDesc(nixlBasicDesc(reinterpret_cast<uintptr_t>(src) + static_cast<size_t>(i) * block, block, 0));
+                r.addDesc(nixlBasicDesc(0, block, static_cast<uint64_t>(i)));
+            }
+            nixlXferReqH *put = nullptr;
+            if (ini.createXferReq(NIXL_WRITE, l, r, remote_name, put) != NIXL_SUCCESS) return 7;
+            nixl_status_t st = ini.postXferReq(put);
+            while (st == NIXL_IN_PROG) st = ini.getXferStatus(put);
+            ini.releaseXferReq(put);
+            if (st != NIXL_SUCCESS) {
+                std::fprintf(stderr, "cannot put the objects to read (status %d)\n", static_cast<int>(st));
+                return 7;
+            }
+        }
         if (per > (size_t(64) << 20)) {
             iters = std::max<int>(10, static_cast<int>((size_t(64) << 30) / per / 16));
             warm = 3;
@@ -660,7 +696,9 @@ int main(int argc, char **argv) {
         for (int i = tid; i < batch; i += nthreads, ++mine) {
             const size_t off = static_cast<size_t>(i) * block;
             l.addDesc(nixlBasicDesc(reinterpret_cast<uintptr_t>(src) + off, block, vram ? a.src_dev : 0));
-            if (storage) {
+            if (objects) {
+                r.addDesc(nixlBasicDesc(0, block, static_cast<uint64_t>(i)));
+            } else if (storage) {
                 const size_t f = std::min<size_t>(off / file_bytes, fds.size() - 1);
                 size_t foff = off - f * file_bytes;
                 if (foff + block > file_bytes) foff = 0; // a block never straddles two files
@@ -778,7 +816,19 @@ int main(int argc, char **argv) {
             // was overwritten with the target's zeros.
             std::vector<unsigned char> h(std::min<size_t>(block, 1 << 20));
             unsigned char want = 0x5a;
-            if (storage) {
+            if (objects) {
+                // Get the start of object 0 back into the start of the source: the pattern if the store holds what was put.
+                nixl_xfer_dlist_t l(mt), r(rmt);
+                l.addDesc(nixlBasicDesc(reinterpret_cast<uintptr_t>(src), h.size(), 0));
+                r.addDesc(nixlBasicDesc(0, h.size(), 0));
+                nixlXferReqH *back = nullptr;
+                if (ini.createXferReq(NIXL_READ, l, r, remote_name, back) != NIXL_SUCCESS) return 10;
+                nixl_status_t st = ini.postXferReq(back);
+                while (st == NIXL_IN_PROG) st = ini.getXferStatus(back);
+                ini.releaseXferReq(back);
+                if (st != NIXL_SUCCESS) return 10;
+                std::memcpy(h.data(), src, h.size());
+            } else if (storage) {
                 if (op != NIXL_WRITE) continue; // a READ returns what an earlier WRITE stored: nothing fixed to compare with
                 if (::pread(fds[0], h.data(), h.size(), 0) != static_cast<ssize_t>(h.size())) return 10;
             } else if (remote_target && op == NIXL_WRITE) {

@@ -587,7 +587,13 @@ private:
                           size_t *got, bool &before_answer) {
         Response resp;
         before_answer = true;
-        if (!c.writeAll(head.data(), head.size()) || (body_len && !c.writeAll(body, body_len))) return c.close(), resp;
+        if (body_len && body_len <= (16u << 10)) { // a small body rides in the packet of its headers
+            std::string both = head;
+            both.append(static_cast<const char *>(body), body_len);
+            if (!c.writeAll(both.data(), both.size())) return c.close(), resp;
+        } else if (!c.writeAll(head.data(), head.size()) || (body_len && !c.writeAll(body, body_len))) {
+            return c.close(), resp;
+        }
         // status line and headers
         std::string buf;
         size_t end = std::string::npos;

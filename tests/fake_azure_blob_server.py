@@ -14,6 +14,7 @@ import hashlib
 import hmac
 import json
 import re
+import socket
 import sys
 import threading
 import urllib.parse
@@ -38,6 +39,10 @@ class Handler(BaseHTTPRequestHandler):
 
     def log_message(self, *args):
         pass
+
+    def setup(self):
+        super().setup()
+        self.request.setsockopt(socket.IPPROTO_TCP, socket.TCP_NODELAY, 1)  # headers and body leave as they are written
 
     def _reply(self, status, body=b"", headers=None):
         self.send_response(status)

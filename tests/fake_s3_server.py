@@ -15,6 +15,7 @@ import hashlib
 import hmac
 import json
 import re
+import socket
 import sys
 import threading
 import urllib.parse
@@ -58,6 +59,7 @@ class Handler(BaseHTTPRequestHandler):
 
     def setup(self):
         super().setup()
+        self.request.setsockopt(socket.IPPROTO_TCP, socket.TCP_NODELAY, 1)  # headers and body leave as they are written
         _bump("connections")
 
     # ------------------------------------------------------------------ helpers

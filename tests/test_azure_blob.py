@@ -158,3 +158,14 @@ def test_the_environment_names_the_account_and_no_account_means_a_directory(monk
     c = nixl_agent("az_h", nixl_agent_config(backends=[]))
     with pytest.raises(Exception):
         c.create_backend("AZURE_BLOB", {"connection_string": "AccountName=x", "container_name": "kv-cache"})
+
+
+def test_nixlbench_against_the_blob_service(blob):
+    exe = os.path.join(os.path.dirname(HERE), "nixl_b200", "bin", "nixlbench")
+    env = dict(os.environ, NIXL_PLUGIN_DIR=os.path.join(os.path.dirname(HERE), "nixl_b200", "lib", "plugins"), NIXL_LOG_LEVEL="ERROR")
+    res = subprocess.run([exe, "--backend", "AZURE_BLOB", "--mem", "DRAM", "--azure_blob_connection_string=" + blob.connection_string(),
+                          "--azure_blob_container_name=kv-cache", "--min", "8192", "--max", "131072", "--batch", "2", "--iters", "5", "--warmup", "1", "--check"],
+                         env=env, capture_output=True, text=True, timeout=180)
+    assert res.returncode == 0, res.stdout + res.stderr
+    assert blob.admin("blobs")["kv-cache"] == {"nixlbench-0": 131072, "nixlbench-1": 131072}
+    assert blob.admin("stats")["bad_signature"] == 0

@@ -331,3 +331,20 @@ def test_the_service_over_tls(tmp_path):
         assert "untrusted" not in server.admin("keys")["kv-cache"]
     finally:
         server.close()
+
+
+def test_nixlbench_against_the_service(s3):
+    """The sweep tool with the object store as the far end: one object per block, put and got back; with the reference's
+    flag spellings for the service's parameters."""
+    exe = os.path.join(os.path.dirname(HERE), "nixl_b200", "bin", "nixlbench")
+    env = dict(os.environ, NIXL_PLUGIN_DIR=os.path.join(os.path.dirname(HERE), "nixl_b200", "lib", "plugins"), NIXL_LOG_LEVEL="ERROR")
+    common = ["--backend", "OBJ", "--mem", "DRAM", f"--obj_endpoint_override={s3.endpoint}", "--obj_bucket_name=kv-cache", f"--obj_access_key={KEYS['access_key']}",
+              f"--obj_secret_key={KEYS['secret_key']}", "--min", "4096", "--max", "262144", "--batch", "3", "--iters", "6", "--warmup", "1", "--check"]
+    for op in ("WRITE", "READ"):
+        res = subprocess.run([exe, *common, "--op", op, "--obj-prefix", "bench-" + op.lower()], env=env, capture_output=True, text=True, timeout=180)
+        assert res.returncode == 0, res.stdout + res.stderr
+        rows = [l.split() for l in res.stdout.splitlines() if l and l[0].isdigit()]
+        assert len(rows) == 7 and all(float(r[2]) > 0 for r in rows), res.stdout
+    keys = s3.admin("keys")["kv-cache"]
+    assert sorted(keys) == [f"bench-{op}-{i}" for op in ("read", "write") for i in range(3)] and set(keys.values()) == {262144}
+    assert s3.admin("stats")["bad_signature"] == 0
