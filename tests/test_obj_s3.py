@@ -344,7 +344,7 @@ def test_nixlbench_against_the_service(s3):
         res = subprocess.run([exe, *common, "--op", op, "--obj-prefix", "bench-" + op.lower()], env=env, capture_output=True, text=True, timeout=180)
         assert res.returncode == 0, res.stdout + res.stderr
         rows = [l.split() for l in res.stdout.splitlines() if l and l[0].isdigit()]
-        assert len(rows) == 7 and all(float(r[2]) > 0 for r in rows), res.stdout
+        assert len(rows) == 7 and all(float(r[3]) > 0 for r in rows), res.stdout  # (the rate of 4 KiB objects may round to 0.00 GB/s)
     keys = s3.admin("keys")["kv-cache"]
     assert sorted(keys) == [f"bench-{op}-{i}" for op in ("read", "write") for i in range(3)] and set(keys.values()) == {262144}
     assert s3.admin("stats")["bad_signature"] == 0
