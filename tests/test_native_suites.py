@@ -147,7 +147,7 @@ def test_native_nixlbench_over_the_tcp_backend():
         res = _nixlbench("--backend", "TCP", "--mem", "DRAM", "--min", "4096", "--max", "1048576", "--iters", "20", "--warmup", "3", "--check", *extra)
         assert res.returncode == 0, res.stdout + res.stderr
         rows = [l.split() for l in res.stdout.strip().splitlines() if l and l[0].isdigit()]
-        assert len(rows) == 9 and all(float(r[2]) > 0 for r in rows), res.stdout
+        assert len(rows) == 9 and all(float(r[3]) > 0 for r in rows), res.stdout
 
 
 @pytest.mark.parametrize("backend,op", [("TCP", "WRITE"), ("TCP", "READ"), ("NVLINK", "WRITE")])
@@ -172,7 +172,7 @@ def test_native_nixlbench_between_two_processes(backend, op):
             pytest.skip("cross-process memory access is not permitted here")
         assert res.returncode == 0, res.stdout + res.stderr
         rows = [l.split() for l in res.stdout.strip().splitlines() if l and l[0].isdigit()]
-        assert len(rows) == 9 and all(float(r[2]) > 0 for r in rows), res.stdout
+        assert len(rows) == 9 and all(float(r[3]) > 0 for r in rows), res.stdout
         assert target.wait(timeout=30) == 0
         assert "through" in target.stdout.read()
     finally:
