@@ -108,6 +108,9 @@ def main(argv=None):
     p.add_argument("--mem", default="cpu", help="cpu / dram or cuda / vram")
     p.add_argument("--chunk", default="0", help="bytes per descriptor (0: one descriptor)")
     p.add_argument("--keep-files", action="store_true")
+    p.add_argument("--store", default="file", choices=["file", "obj", "azure_blob"], help="file: POSIX / GDS on --path; obj / azure_blob: an object store")
+    p.add_argument("--store-param", action="append", default=[], metavar="KEY=VALUE",
+                   help="parameter of the object backend (endpoint_override, bucket, access_key, ...; connection_string, container_name)")
 
     if argv is None:
         argv = sys.argv[1:]
@@ -139,7 +142,8 @@ def main(argv=None):
         from .storage import storage_perftest
         from .traffic import parse_size
 
-        print(json.dumps(storage_perftest(ns.path, parse_size(ns.size), ns.iters, ns.mem, parse_size(ns.chunk), keep_files=ns.keep_files)))
+        print(json.dumps(storage_perftest(ns.path, parse_size(ns.size), ns.iters, ns.mem, parse_size(ns.chunk), keep_files=ns.keep_files, store=ns.store,
+                                          store_params=dict(kv.split("=", 1) for kv in ns.store_param))))
     elif ns.cmd == "matgen":
         from nixl_b200.models import ParallelConfig
 

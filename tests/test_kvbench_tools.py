@@ -133,3 +133,36 @@ def test_storage_backend_reads_and_writes_file_regions(tmp_path):
         StorageOp("x", 100, read_offset=90, read_size=20)
     fs.close(remove_files=True)
     assert not (tmp_path / "ops" / "custom.bin").exists()
+
+
+def test_storage_perftest_against_object_stores(tmp_path):
+    """kvbench's storage test with objects instead of file regions: a directory as the bucket, then an S3 service (the
+    stand-in of tests/fake_s3_server.py) through the CLI, with the region cut into several objects."""
+    from benchmarks.kvbench.storage import storage_perftest
+
+    bucket = tmp_path / "bucket"
+    bucket.mkdir()
+    rep = storage_perftest(str(bucket), 1 << 20, iters=2, store="obj", chunk_bytes=1 << 18, rank=3)
+    assert rep["verified"] and rep["store"] == "obj" and rep["read_GBps"] > 0
+    assert sorted(p.name for p in bucket.iterdir()) == [f"kvbench_tp0_rank3.{kind}.{k}" for kind in ("read", "write") for k in range(4)]
+
+    server = subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "fake_s3_server.py"), "--bucket", "kv", "--access-key", "AK", "--secret-key", "SK"],
+                              stdout=subprocess.PIPE, text=True)
+    try:
+        port = int(server.stdout.readline())
+        out = subprocess.run([sys.executable, "-m", "benchmarks.kvbench", "storage-perftest", "--path", str(tmp_path), "--size", "512K", "--iters", "2",
+                              "--store", "obj", "--store-param", f"endpoint_override=http://127.0.0.1:{port}", "--store-param", "bucket=kv",
+                              "--store-param", "access_key=AK", "--store-param", "secret_key=SK"],
+                             cwd=ROOT, env=dict(os.environ, PYTHONPATH=ROOT), capture_output=True, text=True, timeout=180)
+        assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-2000:]
+        rep = json.loads(out.stdout.strip().splitlines()[-1])
+        assert rep["verified"] is True and rep["bytes"] == 512 << 10
+        import urllib.request
+
+        keys = json.loads(urllib.request.urlopen(f"http://127.0.0.1:{port}/_admin/keys", timeout=5).read())["kv"]
+        assert keys == {"kvbench_tp0_rank0.read": 512 << 10, "kvbench_tp0_rank0.write": 512 << 10}
+        stats = json.loads(urllib.request.urlopen(f"http://127.0.0.1:{port}/_admin/stats", timeout=5).read())
+        assert stats["bad_signature"] == 0
+    finally:
+        server.kill()
+        server.wait()
