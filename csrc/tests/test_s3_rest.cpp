@@ -3,6 +3,11 @@
 // documentation; plus the pieces that are easy to get wrong (escaping, query order, endpoint parsing).  The requests
 // themselves are exercised against a server that checks signatures in tests/test_obj_s3.py.  The Azure Blob client's
 // pieces (azure_rest.h) follow: base64 (RFC 4648 vectors), connection strings, the text a Shared Key signs.
+#include <unistd.h>
+
+#include <cstdio>
+#include <thread>
+
 #include "harness.h"
 #include "plugins/extra/azure_rest.h"
 #include "plugins/extra/s3_rest.h"
@@ -147,6 +152,129 @@ TEST_CASE(the_text_a_shared_key_signs) {
     const std::vector<uint8_t> key = {'k', 'e', 'y'};
     const std::string auth = nixl_azure::sharedKeyAuthorization(r, "a", key);
     CHECK(auth.compare(0, 12, "SharedKey a:") == 0 && auth.size() == 12 + 44);
+}
+
+namespace {
+// The stand-in services of the Python suite (tests/fake_s3_server.py, tests/fake_azure_blob_server.py), started as child
+// processes; their first line of output is the port.  No interpreter or no script: the case is left out.
+struct Service {
+    FILE *pipe = nullptr;
+    int port = 0;
+    Service(const std::string &script, const std::string &flags) {
+        for (const char *dir : {"../tests/", "tests/", "../../tests/"}) {
+            const std::string path = std::string(dir) + script;
+            if (::access(path.c_str(), R_OK) != 0) continue;
+            // `exec` so that closing the pipe's process ends the server itself, not a shell in front of it
+            pipe = ::popen(("exec python3 " + path + " " + flags + " 2>/dev/null").c_str(), "r");
+            break;
+        }
+        char line[64];
+        if (pipe && std::fgets(line, sizeof(line), pipe)) port = std::atoi(line);
+    }
+    ~Service() {
+        if (!pipe) return;
+        if (port > 0) { // the server runs until it is killed: ask it to go through its admin door
+            Config c;
+            c.scheme = "http";
+            c.host = "127.0.0.1";
+            c.port = static_cast<uint16_t>(port);
+            Http h(c);
+            h.roundTrip("GET /_admin/quit HTTP/1.1\r\nhost: x\r\n\r\n", nullptr, 0, false, nullptr, 0);
+        }
+        ::pclose(pipe);
+    }
+};
+} // namespace
+
+TEST_CASE(the_s3_client_against_the_stand_in_service) {
+    Service svc("fake_s3_server.py", "--bucket kv --access-key AK --secret-key SK --close-after 5 --slow-down 1");
+    if (svc.port <= 0) {
+        std::printf("  (no stand-in service here: left out)\n");
+        return;
+    }
+    Config cfg;
+    cfg.scheme = "http";
+    cfg.host = "127.0.0.1";
+    cfg.port = static_cast<uint16_t>(svc.port);
+    cfg.bucket = "kv";
+    cfg.cred = {"AK", "SK", ""};
+    cfg.sendChecksum = cfg.checkChecksum = true;
+    Client s3(cfg);
+    CHECK(s3.usable());
+    std::vector<uint8_t> data((6u << 20) + 17), back(data.size());
+    for (size_t i = 0; i < data.size(); ++i) data[i] = static_cast<uint8_t>(i * 7 + (i >> 9));
+    uint64_t size = 0;
+    CHECK_EQ(s3.headObject("dir/one object.bin", &size), 404); // (the first request is told to slow down and asked again)
+    CHECK_EQ(s3.putObject("dir/one object.bin", data.data(), 100000), 200);
+    CHECK_EQ(s3.headObject("dir/one object.bin", &size), 200);
+    CHECK_EQ(size, uint64_t(100000));
+    CHECK_EQ(s3.getObject("dir/one object.bin", 0, back.data(), 100000), 206);
+    CHECK(std::memcmp(back.data(), data.data(), 100000) == 0);
+    CHECK_EQ(s3.getObject("dir/one object.bin", 5000, back.data(), 777), 206);
+    CHECK(std::memcmp(back.data(), data.data() + 5000, 777) == 0);
+    CHECK_EQ(s3.getObject("dir/one object.bin", 99000, back.data(), 5000), 416); // ends inside the range
+    CHECK_EQ(s3.getObject("absent", 0, back.data(), 10), 404);
+    CHECK(s3.lastError().find("NoSuchKey") != std::string::npos); // from a chunked error body
+    // multipart: two parts of 5 MiB and 1 MiB + 17, from two threads
+    std::string upload;
+    CHECK_EQ(s3.createMultipart("big", upload), 200);
+    std::vector<std::string> etags(2);
+    int st[2] = {0, 0};
+    std::thread t0([&] { st[0] = s3.uploadPart("big", upload, 1, data.data(), 5u << 20, etags[0]); });
+    std::thread t1([&] { st[1] = s3.uploadPart("big", upload, 2, data.data() + (5u << 20), data.size() - (5u << 20), etags[1]); });
+    t0.join();
+    t1.join();
+    CHECK(st[0] == 200 && st[1] == 200 && !etags[0].empty());
+    CHECK_EQ(s3.completeMultipart("big", upload, etags), 200);
+    CHECK_EQ(s3.getObject("big", 0, back.data(), back.size()), 206);
+    CHECK(back == data);
+    // a part that is too small is refused when the upload is completed, and the upload can be dropped
+    CHECK_EQ(s3.createMultipart("small-parts", upload), 200);
+    CHECK_EQ(s3.uploadPart("small-parts", upload, 1, data.data(), 1000, etags[0]), 200);
+    CHECK_EQ(s3.uploadPart("small-parts", upload, 2, data.data(), 1000, etags[1]), 200);
+    CHECK_EQ(s3.completeMultipart("small-parts", upload, etags), 400);
+    CHECK(s3.lastError().find("EntityTooSmall") != std::string::npos);
+    CHECK_EQ(s3.abortMultipart("small-parts", upload), 204);
+    CHECK_EQ(s3.deleteObject("big"), 204);
+    CHECK_EQ(s3.headObject("big", nullptr), 404);
+    // the wrong secret
+    cfg.cred.secretKey = "not it";
+    Client intruder(cfg);
+    CHECK_EQ(intruder.putObject("x", data.data(), 10), 403);
+    CHECK(intruder.lastError().find("SignatureDoesNotMatch") != std::string::npos);
+}
+
+TEST_CASE(the_azure_client_against_the_stand_in_service) {
+    const std::string key = nixl_azure::base64Encode(reinterpret_cast<const uint8_t *>("a key for the native suite"), 26);
+    Service svc("fake_azure_blob_server.py", "--account acct --container kv --key " + key);
+    if (svc.port <= 0) {
+        std::printf("  (no stand-in service here: left out)\n");
+        return;
+    }
+    nixl_azure::Config cfg;
+    std::string err;
+    CHECK(nixl_azure::parseConnectionString("AccountName=acct;AccountKey=" + key + ";BlobEndpoint=http://127.0.0.1:" + std::to_string(svc.port) + "/acct", cfg, err));
+    cfg.container = "kv";
+    nixl_azure::Client blob(cfg);
+    std::vector<uint8_t> data(300000), back(data.size());
+    for (size_t i = 0; i < data.size(); ++i) data[i] = static_cast<uint8_t>(i * 13);
+    CHECK_EQ(blob.headObject("a/b c.bin", nullptr), 404);
+    CHECK_EQ(blob.putObject("a/b c.bin", data.data(), data.size()), 201);
+    uint64_t size = 0;
+    CHECK_EQ(blob.headObject("a/b c.bin", &size), 200);
+    CHECK_EQ(size, uint64_t(data.size()));
+    CHECK_EQ(blob.getObject("a/b c.bin", 1000, back.data(), 5000), 206);
+    CHECK(std::memcmp(back.data(), data.data() + 1000, 5000) == 0);
+    std::string upload;
+    std::vector<std::string> ids(3);
+    CHECK_EQ(blob.createMultipart("blocks.bin", upload), 200);
+    for (int i = 0; i < 3; ++i) CHECK_EQ(blob.uploadPart("blocks.bin", upload, i + 1, data.data() + i * 100000, 100000, ids[static_cast<size_t>(i)]), 201);
+    CHECK_EQ(blob.completeMultipart("blocks.bin", upload, ids), 201);
+    CHECK_EQ(blob.getObject("blocks.bin", 0, back.data(), back.size()), 206);
+    CHECK(back == data);
+    CHECK_EQ(blob.deleteObject("blocks.bin"), 202);
+    CHECK_EQ(blob.getObject("blocks.bin", 0, back.data(), 10), 404);
+    CHECK(blob.lastError().find("BlobNotFound") != std::string::npos);
 }
 
 TEST_MAIN()

@@ -130,6 +130,10 @@ class Handler(BaseHTTPRequestHandler):
         self._reply(201, b"", {"ETag": '"%s"' % hashlib.md5(body).hexdigest()})
 
     def do_GET(self):
+        if self.path == "/_admin/quit":  # for a parent that can only reach this process through its port
+            self._reply(200, b"bye")
+            threading.Thread(target=self.server.shutdown, daemon=True).start()
+            return
         if self.path == "/_admin/stats":
             with STATE["lock"]:
                 return self._reply(200, json.dumps(dict(STATE["stats"], staged=len(STATE["blocks"]))).encode())

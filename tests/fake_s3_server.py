@@ -220,6 +220,10 @@ class Handler(BaseHTTPRequestHandler):
         self._error(400, "InvalidRequest", "unsupported POST")
 
     def do_GET(self):
+        if self.path == "/_admin/quit":  # for a parent that can only reach this process through its port
+            self._reply(200, b"bye")
+            threading.Thread(target=self.server.shutdown, daemon=True).start()
+            return
         if self.path == "/_admin/stats":
             with STATE["lock"]:
                 body = json.dumps(dict(STATE["stats"], open_uploads=len(STATE["uploads"]))).encode()
