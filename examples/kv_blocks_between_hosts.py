@@ -101,7 +101,7 @@ def prefill(args):
         mover.wait(h)
     n = sum(len(r) for r in requests)
     print(f"prefill: {n} blocks ({mover.bytes_moved(n)} bytes) over {backend} in {time.time() - t0:.3f} s", flush=True)
-    wait_for("the decode worker's verdict", lambda: agent.check_remote_xfer_done("decode", b"VERIFIED"), 120)
+    wait_for("the decode worker's answer", lambda: agent.check_remote_xfer_done("decode", b"VERIFIED"), 120)
     mover.close()
     print("prefill: the decode worker has verified the blocks", flush=True)
 
