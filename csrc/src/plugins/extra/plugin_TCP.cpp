@@ -84,7 +84,7 @@ constexpr uint32_t kMagic = 0x4e585443u; // "CTXN"
 constexpr uint32_t kMaxDescsPerMsg = 256;
 constexpr size_t kBounceBytes = 4u << 20;
 constexpr size_t kInlineBytes = 64u << 10;  // a WRITE up to this size is sent by the posting thread when the connection is idle
-constexpr unsigned kSpinUs = 40;            // how long a thread polls its socket for the next message before it sleeps
+constexpr unsigned kSpinUs = 100;           // how long a thread polls its socket for the next message before it sleeps
 
 enum Op : uint16_t { OP_HELLO = 1, OP_WRITE = 2, OP_READ = 3, OP_ACK = 4, OP_READ_REPLY = 5, OP_NOTIF = 6 };
 
