@@ -352,6 +352,10 @@ Engine::Engine(const nixlBackendInitParams *init) : nixlBackendEngine(init) {
     const nixl_b_params_t &params = getCustomParams();
     self_.agent = localAgent;
     self_.host = hostName();
+    // "host_id": what this engine takes for "the same NVLink box" instead of the host name.  Engines only reach peers
+    // that name the same one, so containers with their own host names on one box can be told that they share it (they
+    // must also share the IPC and pid name spaces), and a test can play two hosts on one machine.
+    if (auto it = params.find("host_id"); it != params.end() && !it->second.empty()) self_.host = it->second;
     self_.pid = ::getpid();
     self_.procTag = processTag();
     self_.engineTag = random64() | 1;
@@ -1656,6 +1660,7 @@ nixl_b_params_t nvlinkDefaults() {
         {"grid_ctas", "0"},        // 0: two CTAs per SM
         {"device_id", "-1"},       // GPU that maps other processes' memory; -1: first registered / current
         {"liveness_ping", "false"},// probe the peer's socket at every post
+        {"host_id", ""},           // name of the NVLink box (default: the host name); peers that name another one are left to other backends
         {"num_streams", "4"},      // streams per GPU that independent requests are spread over
         {"proxy", "true"},         // small requests go through a persistent doorbell kernel instead of one launch each
         {"proxy_max_bytes", "2097152"}, // largest request (all descriptors) the proxy takes

@@ -151,3 +151,41 @@ def test_kv_block_mover_checks_what_it_is_given():
     with pytest.raises(ValueError):
         describe_blocks(b, [theirs[0].t()])
     mover.close()
+
+
+def test_the_agent_takes_nvlink_inside_a_box_and_tcp_across_boxes():
+    """Three agents with both backends; the NVLINK engines of two of them are told (``host_id``) that they share a box,
+    the third that it sits in another one.  A request to the neighbour runs on NVLINK, a request to the other box on
+    TCP, without the caller naming a backend; both move their bytes."""
+    from nixl_b200 import nixl_agent, nixl_agent_config
+
+    def make(name, box):
+        a = nixl_agent(name, nixl_agent_config(backends=[]))
+        a.create_backend("NVLINK", {"host_id": box})
+        a.create_backend("TCP", {"address": "127.0.0.1"})
+        return a
+
+    here, neighbour, far = make("box_a0", "box-a"), make("box_a1", "box-a"), make("box_b0", "box-b")
+    src = torch.arange(1 << 16, dtype=torch.int32)
+    near_dst, far_dst = torch.zeros_like(src), torch.zeros_like(src)
+    here.register_memory(src)
+    neighbour.register_memory(near_dst)
+    far.register_memory(far_dst)
+    assert here.add_remote_agent(neighbour.get_agent_metadata()) == "box_a1"
+    assert here.add_remote_agent(far.get_agent_metadata()) == "box_b0"  # its NVLINK part is refused, its TCP part taken
+    for peer, dst, backend in (("box_a1", near_dst, "NVLINK"), ("box_b0", far_dst, "TCP")):
+        h = here.initialize_xfer("WRITE", src, dst, peer, b"done")
+        assert here.query_xfer_backend(h) == backend
+        state = here.transfer(h)
+        while state == "PROC":
+            state = here.check_xfer_state(h)
+        assert state == "DONE" and torch.equal(src, dst)
+        here.release_xfer_handle(h)
+    deadline = time.time() + 5
+    while time.time() < deadline and not far.check_remote_xfer_done("box_a0", b"done"):
+        time.sleep(0.001)
+    else:
+        assert time.time() < deadline
+    # naming the backend that cannot reach the peer is an error, not a silent detour
+    with pytest.raises(Exception):
+        here.initialize_xfer("WRITE", src, far_dst, "box_b0", backends=["NVLINK"])
