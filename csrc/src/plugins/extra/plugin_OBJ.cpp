@@ -17,8 +17,9 @@
 // parameter that names the bucket in each of them (NIXL_OBJ_PLUGIN_NAME / NIXL_OBJ_BUCKET_PARAM):
 //   * AZURE_BLOB (`container_name`; src/plugins/azure_blob): Azure Blob Storage over REST (azure_rest.h) when a
 //     `connection_string` (or $AZURE_STORAGE_CONNECTION_STRING) names the account: Shared Key or shared access
-//     signature; blobs of at least `crtMinLimit` bytes go up as blocks side by side.  With only an `account_url`
-//     (Entra ID sign-in, not built) the directory store answers, with a warning.
+//     signature; blobs of at least `crtMinLimit` bytes go up as blocks side by side.  An `account_url` with
+//     `account_key` (or $AZURE_STORAGE_KEY) or `sas_token` (or $AZURE_STORAGE_SAS_TOKEN) beside it does the same.  With
+//     only an `account_url` (Entra ID sign-in, not built) the directory store answers, with a warning.
 //   * INFINIA (`dataset`; src/plugins/infinia): the directory store only; its cluster and tenant parameters are
 //     accepted and ignored: there is no client for that service.
 #ifndef NIXL_OBJ_PLUGIN_NAME
@@ -276,8 +277,16 @@ private:
     // $AZURE_STORAGE_CONNECTION_STRING; `container_name` or $AZURE_STORAGE_CONTAINER_NAME).  An `account_url` alone means
     // signing in with Entra ID, which is not built: the directory store answers then, with a warning.
     bool setupAzure() {
-        const std::string conn = param("connection_string", "AZURE_STORAGE_CONNECTION_STRING");
-        if (conn.empty()) return true;
+        std::string conn = param("connection_string", "AZURE_STORAGE_CONNECTION_STRING");
+        if (conn.empty()) {
+            // An account URL with the account's key or a shared access signature beside it says the same as a
+            // connection string; an account URL alone means Entra ID.
+            const std::string url = param("account_url", "AZURE_STORAGE_ACCOUNT_URL");
+            const std::string key = param("account_key", "AZURE_STORAGE_KEY"), sas = param("sas_token", "AZURE_STORAGE_SAS_TOKEN");
+            if (url.empty() || (key.empty() && sas.empty())) return true;
+            conn = "BlobEndpoint=" + url + ";" + (key.empty() ? "SharedAccessSignature=" + sas : "AccountKey=" + key);
+            if (const std::string name = param("account_name", "AZURE_STORAGE_ACCOUNT"); !name.empty()) conn += ";AccountName=" + name;
+        }
         nixl_azure::Config cfg;
         std::string err;
         if (!nixl_azure::parseConnectionString(conn, cfg, err)) {
@@ -393,7 +402,10 @@ extern "C" NIXL_PLUGIN_EXPORT nixlBackendPlugin *nixl_plugin_init() {
                                                         {"req_checksum", ""},
                                                         {"resp_checksum", ""},
                                                         {"connection_string", ""},
-                                                        {"account_url", ""}},
+                                                        {"account_url", ""},
+                                                        {"account_key", ""},
+                                                        {"account_name", ""},
+                                                        {"sas_token", ""}},
                                                        {DRAM_SEG, OBJ_SEG});
 }
 extern "C" NIXL_PLUGIN_EXPORT void nixl_plugin_fini() {}

@@ -169,3 +169,54 @@ def test_nixlbench_against_the_blob_service(blob):
     assert res.returncode == 0, res.stdout + res.stderr
     assert blob.admin("blobs")["kv-cache"] == {"nixlbench-0": 131072, "nixlbench-1": 131072}
     assert blob.admin("stats")["bad_signature"] == 0
+
+
+def test_an_account_url_with_a_key_beside_it(monkeypatch, blob):
+    """`account_url` plus the account's key (parameter or AZURE_STORAGE_KEY) is as good as a connection string."""
+    a = nixl_agent("az_url", nixl_agent_config(backends=[]))
+    a.create_backend("AZURE_BLOB", {"account_url": f"http://127.0.0.1:{blob.port}/teststore", "account_key": KEY, "container_name": "kv-cache"})
+    src = torch.arange(777, dtype=torch.int32)
+    a.register_memory(src)
+    assert torch.equal(_roundtrip(a, "az_url", "by-url.bin", src), src)
+    monkeypatch.setenv("AZURE_STORAGE_ACCOUNT_URL", f"http://127.0.0.1:{blob.port}/teststore")
+    monkeypatch.setenv("AZURE_STORAGE_KEY", KEY)
+    b = nixl_agent("az_url2", nixl_agent_config(backends=[]))
+    b.create_backend("AZURE_BLOB", {"container_name": "kv-cache"})
+    b.register_memory(src)
+    assert torch.equal(_roundtrip(b, "az_url2", "by-env.bin", src), src)
+    assert set(blob.admin("blobs")["kv-cache"]) == {"by-url.bin", "by-env.bin"} and blob.admin("stats")["bad_signature"] == 0
+
+
+def test_any_blob_name_round_trips(blob):
+    """Names drawn by hypothesis: the escaped path is what goes on the wire and what the Shared Key signs."""
+    from hypothesis import HealthCheck, given, settings
+    from hypothesis import strategies as st
+
+    a = nixl_agent("az_names", nixl_agent_config(backends=[]))
+    a.create_backend("AZURE_BLOB", {"connection_string": blob.connection_string(), "container_name": "kv-cache"})
+    src = torch.arange(48, dtype=torch.uint8)
+    dst = torch.zeros_like(src)
+    a.register_memory(src)
+    a.register_memory(dst)
+    seen = []
+    alphabet = st.one_of(st.characters(min_codepoint=0x20, max_codepoint=0x7E), st.sampled_from(list("äßçñ漢字ключ🙂")))
+
+    @settings(max_examples=30, deadline=None, suppress_health_check=list(HealthCheck), derandomize=True)
+    @given(st.text(alphabet, min_size=1, max_size=40).filter(lambda k: k.strip("/") == k and "//" not in k and k not in (".", "..") and "\\" not in k))
+    def check(name):
+        if name in seen:
+            return
+        seen.append(name)
+        dev = len(seen)
+        src.fill_(dev % 251)
+        a.register_memory([(0, 48, dev, name)], "OBJ")
+        remote = a.get_xfer_descs([(0, 48, dev)], "OBJ")
+        for op, buf in (("WRITE", src), ("READ", dst)):
+            h = a.initialize_xfer(op, a.get_xfer_descs(buf), remote, "az_names")
+            a.transfer(h)
+            assert _wait(a, h) == "DONE", name
+            a.release_xfer_handle(h)
+        assert torch.equal(src, dst), name
+
+    check()
+    assert sorted(blob.admin("blobs")["kv-cache"]) == sorted(seen) and blob.admin("stats")["bad_signature"] == 0

@@ -348,3 +348,40 @@ def test_nixlbench_against_the_service(s3):
     keys = s3.admin("keys")["kv-cache"]
     assert sorted(keys) == [f"bench-{op}-{i}" for op in ("read", "write") for i in range(3)] and set(keys.values()) == {262144}
     assert s3.admin("stats")["bad_signature"] == 0
+
+
+def test_any_key_a_caller_may_think_of_round_trips(s3):
+    """Keys drawn by hypothesis (spaces, punctuation that URLs reserve, other scripts, slashes): the path is escaped once
+    on the wire and once more in the signature's view of it, and the service, which checks both, stores the key as given."""
+    from hypothesis import HealthCheck, given, settings
+    from hypothesis import strategies as st
+
+    a = nixl_agent("s3_keys", nixl_agent_config(backends=[]))
+    a.create_backend("OBJ", s3.params())
+    src = torch.arange(64, dtype=torch.uint8)
+    dst = torch.zeros_like(src)
+    a.register_memory(src)
+    a.register_memory(dst)
+    seen = []
+    alphabet = st.one_of(st.characters(min_codepoint=0x20, max_codepoint=0x7E), st.sampled_from(list("äßçñ漢字ключ🙂")))
+
+    @settings(max_examples=40, deadline=None, suppress_health_check=list(HealthCheck), derandomize=True)
+    @given(st.text(alphabet, min_size=1, max_size=40).filter(lambda k: k.strip("/") == k and "//" not in k and k not in (".", "..") and "\\" not in k))
+    def check(key):
+        if key in seen:
+            return
+        seen.append(key)
+        dev = len(seen)
+        src.fill_(dev % 251)
+        a.register_memory([(0, 64, dev, key)], "OBJ")
+        remote = a.get_xfer_descs([(0, 64, dev)], "OBJ")
+        for op, buf in (("WRITE", src), ("READ", dst)):
+            h = a.initialize_xfer(op, a.get_xfer_descs(buf), remote, "s3_keys")
+            a.transfer(h)
+            assert _wait(a, h) == "DONE", key
+            a.release_xfer_handle(h)
+        assert torch.equal(src, dst), key
+
+    check()
+    stored = s3.admin("keys")["kv-cache"]
+    assert sorted(stored) == sorted(seen) and s3.admin("stats")["bad_signature"] == 0
