@@ -5,6 +5,7 @@
 // ring / exit / relaunch protocol, release of requests in flight, the notification ring, threads.  What it cannot
 // show is anything inside the real kernels; those are covered on GPUs (tests/test_gpu_*.py).
 #include <fcntl.h>
+#include <unistd.h>
 
 #include <algorithm>
 #include <atomic>
@@ -718,6 +719,72 @@ TEST_CASE(random_requests_against_a_model_under_every_path_choice) {
             }
         }
     }
+}
+
+TEST_CASE(device_memory_to_files_and_back_through_the_gds_engine_against_a_model) {
+    // The GDS engine built against the stand-in runtime: pieces of device memory go to places in two files and come back,
+    // through the engine's pairs of pinned staging buffers (8 MiB each, so the 20 MiB piece cycles them) and its worker
+    // threads.  Pieces are drawn at random; a model says what the files and the buffer must hold after every request.
+    char tmpl[] = "/tmp/nixl_fake_gds_XXXXXX";
+    CHECK(::mkdtemp(tmpl) != nullptr);
+    const std::string dir = tmpl;
+    nixlAgent a("fg_gds", nixlAgentConfig(false));
+    nixlBackendH *h = nullptr;
+    CHECK_EQ(a.createBackend("GDS", {{"thread_count", "3"}}, h), NIXL_SUCCESS);
+    constexpr size_t kBytes = 48 << 20, kFile = 32 << 20;
+    DevBuf buf(1, kBytes);
+    buf.randomize(77);
+    nixl_reg_dlist_t rv(VRAM_SEG), rf(FILE_SEG);
+    rv.addDesc(nixlBlobDesc(reinterpret_cast<uintptr_t>(buf.p), kBytes, 1, ""));
+    int fds[2];
+    std::vector<std::vector<uint8_t>> model_file(2, std::vector<uint8_t>(kFile, 0));
+    for (int f = 0; f < 2; ++f) {
+        fds[f] = ::open((dir + "/f" + std::to_string(f)).c_str(), O_RDWR | O_CREAT, 0644);
+        CHECK(fds[f] >= 0 && ::ftruncate(fds[f], kFile) == 0);
+        rf.addDesc(nixlBlobDesc(0, kFile, static_cast<uint64_t>(fds[f]), ""));
+    }
+    CHECK(a.registerMem(rv) == NIXL_SUCCESS && a.registerMem(rf) == NIXL_SUCCESS);
+    std::vector<uint8_t> model_buf(buf.p, buf.p + kBytes);
+    std::mt19937_64 rng(5);
+    for (int round = 0; round < 14; ++round) {
+        const nixl_xfer_op_t op = round % 3 == 2 ? NIXL_READ : NIXL_WRITE;
+        const int n = round == 0 ? 1 : 1 + static_cast<int>(rng() % 12);
+        nixl_xfer_dlist_t l(VRAM_SEG), r(FILE_SEG);
+        size_t at_buf = rng() % 4096, at_file[2] = {rng() % 4096, rng() % 4096};
+        for (int i = 0; i < n; ++i) {
+            const int f = static_cast<int>(rng() % 2);
+            size_t len = round == 0 ? (20u << 20) + 123 : 1 + rng() % (rng() % 4 == 0 ? 3000000 : 40000);
+            len = std::min({len, kBytes - at_buf, kFile - at_file[f]});
+            if (len == 0) break;
+            l.addDesc(nixlBasicDesc(reinterpret_cast<uintptr_t>(buf.p) + at_buf, len, 1));
+            r.addDesc(nixlBasicDesc(at_file[f], len, static_cast<uint64_t>(fds[f])));
+            if (op == NIXL_WRITE) std::memcpy(model_file[static_cast<size_t>(f)].data() + at_file[f], model_buf.data() + at_buf, len);
+            else std::memcpy(model_buf.data() + at_buf, model_file[static_cast<size_t>(f)].data() + at_file[f], len);
+            at_buf += len + rng() % 5000;
+            at_file[f] += len + rng() % 5000;
+            if (at_buf >= kBytes) break;
+        }
+        if (l.descCount() == 0) continue;
+        nixlXferReqH *req = nullptr;
+        CHECK_EQ(a.createXferReq(op, l, r, "fg_gds", req), NIXL_SUCCESS);
+        CHECK(a.postXferReq(req) >= 0);
+        CHECK_EQ(waitDone(a, req, 60.0), NIXL_SUCCESS);
+        CHECK_EQ(a.releaseXferReq(req), NIXL_SUCCESS);
+        CHECK(std::memcmp(buf.p, model_buf.data(), kBytes) == 0);
+        for (int f = 0; f < 2; ++f) {
+            std::vector<uint8_t> on_disk(kFile);
+            CHECK_EQ(::pread(fds[f], on_disk.data(), kFile, 0), static_cast<ssize_t>(kFile));
+            CHECK(on_disk == model_file[static_cast<size_t>(f)]);
+        }
+        // new bytes in the buffer for the next round
+        for (size_t i = 0; i < kBytes; i += 1021) buf.p[i] = model_buf[i] = static_cast<uint8_t>(rng());
+    }
+    CHECK(a.deregisterMem(rf) == NIXL_SUCCESS && a.deregisterMem(rv) == NIXL_SUCCESS);
+    for (int f = 0; f < 2; ++f) {
+        ::close(fds[f]);
+        ::unlink((dir + "/f" + std::to_string(f)).c_str());
+    }
+    ::rmdir(dir.c_str());
 }
 
 TEST_CASE(launch_failures_are_reported_and_leave_the_engine_usable) {
