@@ -7,15 +7,18 @@
 // (or through sendLocalMD / fetchRemoteMD with a listener, a TCPStore or etcd).
 #include <cstdio>
 #include <cstring>
+#include <string>
 #include <vector>
 
 #include "nixl.h"
 
-int main() {
+int main(int argc, char **argv) {
+    // "two_agents TCP" runs the same calls over the socket backend, the one that also reaches another host.
+    const std::string backend = argc > 1 ? argv[1] : "NVLINK";
     nixlAgentConfig cfg(false);
     nixlAgent prefill("prefill", cfg), decode("decode", cfg);
     nixlBackendH *bp = nullptr, *bd = nullptr;
-    if (prefill.createBackend("NVLINK", {}, bp) != NIXL_SUCCESS || decode.createBackend("NVLINK", {}, bd) != NIXL_SUCCESS) {
+    if (prefill.createBackend(backend, {}, bp) != NIXL_SUCCESS || decode.createBackend(backend, {}, bd) != NIXL_SUCCESS) {
         std::fprintf(stderr, "backend not available (is NIXL_PLUGIN_DIR set?)\n");
         return 1;
     }
@@ -43,7 +46,9 @@ int main() {
 
     nixl_notifs_t notifs;
     while (notifs.empty()) decode.getNotifs(notifs);
-    std::printf("moved %zu bytes to %s, %s says \"%s\", data %s\n", src.size(), who.c_str(), notifs.begin()->first.c_str(),
+    nixlBackendH *used = nullptr;
+    prefill.queryXferBackend(req, used);
+    std::printf("backend %s: moved %zu bytes to %s, %s says \"%s\", data %s\n", backend.c_str(), src.size(), who.c_str(), notifs.begin()->first.c_str(),
                 notifs.begin()->second.front().c_str(), std::memcmp(src.data(), dst.data(), src.size()) == 0 ? "identical" : "DIFFERENT");
     prefill.releaseXferReq(req);
     prefill.deregisterMem(rs);

@@ -37,8 +37,11 @@ def test_cpp_example_builds_with_the_pkg_config_file_and_runs(tmp_path):
     build = subprocess.run(["g++", "-std=c++20", "-O1", os.path.join(ROOT, "examples", "cpp", "two_agents.cpp"), "-o", exe, *flags, "-pthread"],
                            capture_output=True, text=True, timeout=300)
     assert build.returncode == 0, build.stderr[-3000:]
-    res = subprocess.run([exe], capture_output=True, text=True, timeout=120)
-    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
+    env = dict(os.environ, NIXL_PLUGIN_DIR=os.path.join(lib, "plugins"))
+    for backend in ("NVLINK", "TCP"):
+        res = subprocess.run([exe, backend], env=env, capture_output=True, text=True, timeout=120)
+        assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
+        assert f"backend {backend}: moved 1048576 bytes" in res.stdout and "identical" in res.stdout
 
 
 def test_cpp_telemetry_reader_drains_a_ring_written_by_an_agent(tmp_path):
