@@ -83,7 +83,7 @@ namespace {
 constexpr uint32_t kMagic = 0x4e585443u; // "CTXN"
 constexpr uint32_t kMaxDescsPerMsg = 256;
 constexpr size_t kBounceBytes = 4u << 20;
-constexpr size_t kInlineBytes = 64u << 10;  // a WRITE up to this size is sent by the posting thread when the connection is idle
+constexpr size_t kInlineBytes = 256u << 10; // a WRITE message up to this size may be sent by the posting thread itself (the last message of a request, when its connection is idle)
 constexpr unsigned kSpinUs = 100;           // how long a thread polls its socket for the next message before it sleeps
 
 enum Op : uint16_t { OP_HELLO = 1, OP_WRITE = 2, OP_READ = 3, OP_ACK = 4, OP_READ_REPLY = 5, OP_NOTIF = 6 };
@@ -416,11 +416,11 @@ public:
     bool dead() const { return dead_.load(std::memory_order_acquire); }
     // false: the connection is gone, the message was not taken.  A small message is sent by the caller itself when the
     // connection is idle, which saves waking the sender thread; everything else queues behind what is being sent.
-    bool submit(const std::shared_ptr<Msg> &m) {
+    bool submit(const std::shared_ptr<Msg> &m, bool may_send_here = true) {
         std::unique_lock<std::mutex> g(qmu_);
         if (dead()) return false;
         const bool small = m->h.op != OP_WRITE || m->h.payloadLen <= kInlineBytes;
-        if (small && q_.empty() && !sending_) {
+        if (may_send_here && small && q_.empty() && !sending_) {
             sending_ = true;
             g.unlock();
             transmit(m);
@@ -918,10 +918,14 @@ public:
         post->bytes = total;
         post->startNs = nixl_util::nowNs();
         post->pending.store(static_cast<int>(msgs.size()), std::memory_order_release);
-        for (auto &m : msgs) {
+        // All messages but the last are handed to the connections' sender threads; the last one the posting thread may
+        // send itself, while the others are already on their way: a request of one message costs no thread wake-up at
+        // all, and a larger one keeps every connection busy at once.
+        for (size_t i = 0; i < msgs.size(); ++i) {
             const uint32_t at = peer->next.fetch_add(1, std::memory_order_relaxed);
+            const bool last = i + 1 == msgs.size();
             bool taken = false;
-            for (size_t k = 0; k < rails.size() && !taken; ++k) taken = rails[(at + k) % rails.size()]->submit(m);
+            for (size_t k = 0; k < rails.size() && !taken; ++k) taken = rails[(at + k) % rails.size()]->submit(msgs[i], last);
             if (!taken) post->finishOne(NIXL_ERR_REMOTE_DISCONNECT);
         }
         return static_cast<nixl_status_t>(post->status.load(std::memory_order_acquire));
