@@ -7,7 +7,8 @@
 Both create the NVLINK and the TCP backend; the agent uses NVLINK when the two sit in one box and TCP otherwise.  The
 decode worker publishes where its cache blocks are (`describe_blocks`, sent as a notification once it knows the prefill
 worker); the prefill worker prepares both sides once (`KVBlockTransfer`) and then names block numbers only.  Every
-request carries a notification, so the decode worker learns of finished blocks without polling anything but its agent.
+request carries a notification ("<i>/<n>:<blocks>"), so the decode worker learns of finished blocks without polling
+anything but its agent; requests finish in any order.
 Run both on one machine with --peer-ip 127.0.0.1 to try it.
 """
 import argparse
@@ -62,8 +63,9 @@ def decode(args):
     print(f"decode: {len(kv)} cache tensors of {BLOCKS} blocks registered, listening on {args.port}", flush=True)
     wait_for("the prefill worker's metadata", lambda: agent.check_remote_metadata("prefill"), 600)
     agent.send_notif("prefill", b"BLOCKS|" + describe_blocks(agent, kv))
+    # Requests finish in any order: every notification says "<i>/<n>:<blocks>", and all n have to be in.
     got = []
-    wait_for("the blocks", lambda: got.extend(agent.get_new_notifs().get("prefill", [])) or any(m.startswith(b"LAST") for m in got), 600)
+    wait_for("the blocks", lambda: got.extend(agent.get_new_notifs().get("prefill", [])) or (got and len(got) == int(got[0].split(b":")[0].split(b"/")[1])), 600)
     landed = sorted(int(x) for m in got for x in m.split(b":")[1].split(b","))
     # block b of the prefill worker went to block BLOCKS - 1 - b here
     for t_index, t in enumerate(kv):
@@ -94,7 +96,7 @@ def prefill(args):
     handles = []
     for i, blocks in enumerate(requests):
         there = [BLOCKS - 1 - b for b in blocks]
-        tag = (b"LAST:" if i == len(requests) - 1 else b"PART:") + b",".join(str(b).encode() for b in there)
+        tag = f"{i + 1}/{len(requests)}:".encode() + b",".join(str(b).encode() for b in there)
         handles.append(mover.post(blocks, there, "WRITE", tag))
     backend = agent.query_xfer_backend(handles[0])
     for h in handles:
