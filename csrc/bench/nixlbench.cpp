@@ -19,6 +19,8 @@
 // processes, which may sit on two hosts (then with --backend TCP): the target registers its buffer and listens for
 // metadata on port P; the initiator fetches the target's metadata there, sends its own, learns the buffer's address
 // from a notification, runs the sweep and says when it is through.  --check reads what it wrote back over the backend.
+// With --etcd-endpoints URL on both sides (the reference's way to rendezvous) neither needs the other's address: both
+// publish their metadata in that etcd and fetch the other's by name.
 //
 // --scheme onetomany: one initiator (--src-dev) posts the same request to M targets at once; manytoone: N
 // initiators post to one target (--dst-dev) at once, which is the pattern that shows what a receiver's ingress
@@ -78,6 +80,7 @@ struct Args {
     std::string obj_prefix = "nixlbench";
     nixl_b_params_t extra; // --param key=value, passed to the backend
     // two processes (on one host or two): "target" owns the destination buffer and listens, "initiator" finds it there
+    std::string etcd; // two processes find each other through this etcd instead of a listener's address
     std::string role, peer_ip = "127.0.0.1";
     int peer_port = 0, listen_port = 0;
 };
@@ -102,6 +105,7 @@ bool setOption(Args &a, const std::string &k, const std::string &v) {
     else if (k == "--min") a.min = std::strtoull(v.c_str(), nullptr, 0);
     else if (k == "--max") a.max = std::strtoull(v.c_str(), nullptr, 0);
     else if (k == "--total") a.total = std::strtoull(v.c_str(), nullptr, 0);
+    else if (k == "--etcd-endpoints") a.etcd = v;
     else if (k == "--role") a.role = v;
     else if (k == "--peer-ip") a.peer_ip = v;
     else if (k == "--peer-port") a.peer_port = std::atoi(v.c_str());
@@ -190,7 +194,7 @@ Spelling canonical(std::string k) {
     };
     // One process drives both agents here: there is no runtime to rendezvous through, no second
     // worker type and one initiator / target device each.
-    static const char *ignored[] = {"--runtime-type", "--worker-type", "--etcd-endpoints", "--mode",
+    static const char *ignored[] = {"--runtime-type", "--worker-type", "--mode",
                                     "--progress-threads", "--device-list", "--target-seg-type",
                                     "--large-blk-iter-ftr", "--benchmark-group"};
     Spelling sp;
@@ -414,8 +418,8 @@ bool waitNotif(nixlAgent &agent, const std::string &from, const std::string &pre
 }
 
 int runTarget(const Args &a, bool vram, size_t buf_bytes) {
-    if (a.listen_port <= 0) {
-        std::fprintf(stderr, "--role target needs --listen-port\n");
+    if (a.listen_port <= 0 && a.etcd.empty()) {
+        std::fprintf(stderr, "--role target needs --listen-port (or --etcd-endpoints)\n");
         return 2;
     }
     const int dev = std::max(0, a.dst_dev);
@@ -429,7 +433,7 @@ int runTarget(const Args &a, bool vram, size_t buf_bytes) {
         if (posix_memalign(&dst, 4096, buf_bytes) != 0) return 3;
         std::memset(dst, 0, buf_bytes);
     }
-    nixlAgentConfig cfg(a.enable_pt, true, static_cast<uint16_t>(a.listen_port));
+    nixlAgentConfig cfg(a.enable_pt, a.listen_port > 0, static_cast<uint16_t>(std::max(0, a.listen_port)));
     nixlAgent tgt("target", cfg);
     nixlBackendH *bt = nullptr;
     nixl_b_params_t params;
@@ -441,7 +445,12 @@ int runTarget(const Args &a, bool vram, size_t buf_bytes) {
     nixl_reg_dlist_t rd(vram ? VRAM_SEG : DRAM_SEG);
     rd.addDesc(nixlBlobDesc(reinterpret_cast<uintptr_t>(dst), buf_bytes, vram ? dev : 0, ""));
     if (tgt.registerMem(rd) != NIXL_SUCCESS) return 5;
-    std::printf("target: %zu bytes registered, listening on port %d\n", buf_bytes, a.listen_port);
+    if (!a.etcd.empty()) { // publish ourselves and ask for the initiator, both through the store
+        if (tgt.sendLocalMD() != NIXL_SUCCESS || tgt.fetchRemoteMD("initiator") != NIXL_SUCCESS) return 6;
+        std::printf("target: %zu bytes registered, published through %s\n", buf_bytes, a.etcd.c_str());
+    } else {
+        std::printf("target: %zu bytes registered, listening on port %d\n", buf_bytes, a.listen_port);
+    }
     std::fflush(stdout);
     // the initiator's metadata arrives through the listener
     const nixl_xfer_dlist_t none(vram ? VRAM_SEG : DRAM_SEG);
@@ -510,6 +519,7 @@ int main(int argc, char **argv) {
             return 2;
         }
     }
+    if (!a.etcd.empty()) ::setenv("NIXL_ETCD_ENDPOINTS", a.etcd.c_str(), 1); // the agents read it when they are created
     const bool vram = a.mem == "VRAM";
     // Object stores (OBJ: S3 or a directory; AZURE_BLOB): every block of a batch is an object of its own, named
     // "<prefix>-<i>" (--obj-prefix, default "nixlbench"); WRITE puts it, READ gets it.
@@ -541,8 +551,8 @@ int main(int argc, char **argv) {
         return 2;
     }
     if (a.role == "target") return runTarget(a, vram, buf_bytes);
-    if (remote_target && a.peer_port <= 0) {
-        std::fprintf(stderr, "--role initiator needs --peer-port (and --peer-ip unless the target is on this host)\n");
+    if (remote_target && a.peer_port <= 0 && a.etcd.empty()) {
+        std::fprintf(stderr, "--role initiator needs --peer-port (and --peer-ip unless the target is on this host), or --etcd-endpoints\n");
         return 2;
     }
     void *src = nullptr, *dst = nullptr;
@@ -566,7 +576,8 @@ int main(int argc, char **argv) {
     const nixl_thread_sync_t sync = a.num_threads > 1 ? nixl_thread_sync_t::NIXL_THREAD_SYNC_RW : nixl_thread_sync_t::NIXL_THREAD_SYNC_NONE;
     nixlAgentConfig cfg(a.enable_pt, false, 0, sync);
     // with a target in another process the initiator's metadata travels through the agents' listeners
-    nixlAgentConfig ini_cfg(a.enable_pt, remote_target, static_cast<uint16_t>(remote_target ? (a.listen_port > 0 ? a.listen_port : freePort()) : 0), sync);
+    const bool by_listener = remote_target && a.etcd.empty();
+    nixlAgentConfig ini_cfg(a.enable_pt, by_listener, static_cast<uint16_t>(by_listener ? (a.listen_port > 0 ? a.listen_port : freePort()) : 0), sync);
     nixlAgent ini("initiator", ini_cfg), tgt(remote_target ? "unused" : "target", cfg);
     nixlBackendH *bi = nullptr, *bt = nullptr;
     nixl_b_params_t params;
@@ -609,12 +620,13 @@ int main(int argc, char **argv) {
         nixl_opt_args_t where;
         where.ipAddr = a.peer_ip;
         where.port = a.peer_port;
-        if (ini.fetchRemoteMD("target", &where) != NIXL_SUCCESS || ini.sendLocalMD(&where) != NIXL_SUCCESS) return 6;
+        const nixl_opt_args_t *how = a.etcd.empty() ? &where : nullptr; // no address: through the central store
+        if (ini.fetchRemoteMD("target", how) != NIXL_SUCCESS || ini.sendLocalMD(how) != NIXL_SUCCESS) return 6;
         const nixl_xfer_dlist_t none(mt);
         const auto end = clk::now() + std::chrono::seconds(60);
         while (ini.checkRemoteMD("target", none) != NIXL_SUCCESS) {
             if (clk::now() > end) {
-                std::fprintf(stderr, "no metadata from the target at %s:%d\n", a.peer_ip.c_str(), a.peer_port);
+                std::fprintf(stderr, "no metadata from the target (%s)\n", a.etcd.empty() ? (a.peer_ip + ":" + std::to_string(a.peer_port)).c_str() : a.etcd.c_str());
                 return 6;
             }
             std::this_thread::sleep_for(std::chrono::milliseconds(2));

@@ -190,3 +190,30 @@ def test_nixlbench_vram_over_the_tcp_backend_on_the_stand_in_runtime(op):
     assert res.returncode == 0, res.stdout + res.stderr
     rows = [l.split() for l in res.stdout.splitlines() if l and l[0].isdigit()]
     assert [r[0] for r in rows] == [str(65536 << i) for i in range(8)] and all(float(r[2]) > 0 for r in rows)
+
+
+def test_native_nixlbench_two_processes_find_each_other_through_etcd():
+    """--etcd_endpoints on both sides, as the reference's nixlbench is started: no listener port, no peer address; both
+    publish in the store (the stand-in gateway of the metadata tests) and fetch the other by name."""
+    import sys
+
+    gateway = subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "fake_etcd_gateway.py")], stdout=subprocess.PIPE, text=True)
+    exe = os.path.join(ROOT, "nixl_b200", "bin", "nixlbench")
+    target = None
+    try:
+        port = int(gateway.stdout.readline())
+        env = {k: v for k, v in ENV.items() if k != "NIXL_TCPSTORE_ENDPOINT"}
+        common = [f"--etcd_endpoints=http://127.0.0.1:{port}", "--backend", "TCP", "--mem", "DRAM", "--max", "262144"]
+        target = subprocess.Popen([exe, "--role", "target", *common], env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+        assert "published through" in target.stdout.readline()
+        res = subprocess.run([exe, "--role", "initiator", *common, "--min", "4096", "--iters", "10", "--warmup", "2", "--check"], env=env,
+                             capture_output=True, text=True, timeout=180)
+        assert res.returncode == 0, res.stdout + res.stderr
+        assert len([l for l in res.stdout.splitlines() if l and l[0].isdigit()]) == 7
+        assert target.wait(timeout=30) == 0
+    finally:
+        for p in (target, gateway):
+            if p is not None and p.poll() is None:
+                p.kill()
+            if p is not None:
+                p.wait()
