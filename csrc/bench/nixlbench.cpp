@@ -519,6 +519,10 @@ int main(int argc, char **argv) {
             return 2;
         }
     }
+    if (!a.etcd.empty() && a.role.empty()) {
+        std::fprintf(stderr, "note: --etcd_endpoints has no effect without --role (both ends live in this process)\n");
+        a.etcd.clear();
+    }
     if (!a.etcd.empty()) ::setenv("NIXL_ETCD_ENDPOINTS", a.etcd.c_str(), 1); // the agents read it when they are created
     const bool vram = a.mem == "VRAM";
     // Object stores (OBJ: S3 or a directory; AZURE_BLOB): every block of a batch is an object of its own, named

@@ -17,6 +17,8 @@
 #include <vector>
 
 #include <fcntl.h>
+#include <signal.h>
+#include <dirent.h>
 #include <sys/mman.h>
 #include <sys/stat.h>
 #include <unistd.h>
@@ -96,6 +98,7 @@ struct Runtime {
     std::map<std::pair<int, int>, bool> peer;
 
     Runtime() {
+        reapLeftovers();
         if (const char *e = std::getenv("FAKE_CUDA_DEVICES")) devices = std::max(0, std::atoi(e));
         for (int d = 0; d < devices; ++d) {
             defaults.push_back(std::make_unique<FakeCudaStream>(d));
@@ -105,6 +108,30 @@ struct Runtime {
     ~Runtime() {
         // Streams the program never destroyed: let their workers finish what is queued.
         for (auto &s : defaults) s->drain();
+    }
+    // "Device memory" the program never freed: the objects behind it go with the process, as a GPU's memory would.
+    // (Run from atexit: the runtime object itself is never destroyed.)
+    void unlinkOwnObjects() {
+        std::vector<std::string> names;
+        {
+            std::lock_guard<std::mutex> g(mu);
+            const std::string mine = "." + std::to_string(::getpid()) + ".";
+            for (const auto &kv : device)
+                if (!kv.second.shm.empty() && kv.second.shm.find(mine) != std::string::npos) names.push_back(kv.second.shm);
+        }
+        for (const auto &n : names) ::shm_unlink(n.c_str());
+    }
+    // Objects of processes that ended without running the destructor above (a crash, _exit) would pile up in /dev/shm,
+    // and one of them would take the name of a later process that draws the same pid: remove those whose owner is gone.
+    static void reapLeftovers() {
+        DIR *d = ::opendir("/dev/shm");
+        if (!d) return;
+        while (dirent *e = ::readdir(d)) {
+            long pid = 0;
+            if (std::sscanf(e->d_name, "fakecuda.%ld.", &pid) != 1 || pid <= 0) continue;
+            if (pid == ::getpid() || (::kill(static_cast<pid_t>(pid), 0) != 0 && errno == ESRCH)) ::shm_unlink((std::string("/") + e->d_name).c_str());
+        }
+        ::closedir(d);
     }
     const Allocation *findDevice(uintptr_t p, uintptr_t *base = nullptr) {
         auto it = device.upper_bound(p);
@@ -123,7 +150,11 @@ struct Runtime {
 };
 
 Runtime &rt() {
-    static Runtime *r = new Runtime(); // leaked on purpose: worker threads may outlive static destruction
+    static Runtime *r = [] {
+        auto *x = new Runtime(); // leaked on purpose: worker threads may outlive static destruction
+        std::atexit([] { rt().unlinkOwnObjects(); });
+        return x;
+    }();
     return *r;
 }
 
@@ -305,7 +336,11 @@ cudaError_t cudaMalloc(void **ptr, size_t size) {
     std::string name;
     if (size >= 4096) {
         name = "/fakecuda." + std::to_string(::getpid()) + "." + std::to_string(serial.fetch_add(1));
-        const int fd = ::shm_open(name.c_str(), O_CREAT | O_EXCL | O_RDWR | O_CLOEXEC, 0600);
+        int fd = ::shm_open(name.c_str(), O_CREAT | O_EXCL | O_RDWR | O_CLOEXEC, 0600);
+        if (fd < 0 && errno == EEXIST) { // the name carries this process's pid: whatever has it is a dead process's leftover
+            ::shm_unlink(name.c_str());
+            fd = ::shm_open(name.c_str(), O_CREAT | O_EXCL | O_RDWR | O_CLOEXEC, 0600);
+        }
         if (fd >= 0 && ::ftruncate(fd, static_cast<off_t>(size)) == 0) p = ::mmap(nullptr, size, PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
         if (fd >= 0) ::close(fd);
         if (p == nullptr || p == MAP_FAILED) {
