@@ -10,6 +10,7 @@
 #include <thread>
 #include <unistd.h>
 
+#include <filesystem>
 #include <fstream>
 #include <sys/stat.h>
 
@@ -314,6 +315,7 @@ TEST_CASE(hw_info_counts_devices_from_a_sysfs_tree) {
     CHECK(hw.toString().find("nvidia_gpus=2") != std::string::npos);
     const nixl::hwInfo none = nixl::hwInfo::scan(root + "/does_not_exist");
     CHECK_EQ(none.numNvidiaGpus, 0u);
+    std::filesystem::remove_all(root);
 }
 
 TEST_CASE(topology_orders_network_interfaces_by_their_place_in_the_pci_tree) {
@@ -372,6 +374,7 @@ TEST_CASE(topology_orders_network_interfaces_by_their_place_in_the_pci_tree) {
     CHECK((t.interfacesNearGpu(99) == std::vector<std::string>{"eno1", "ib0", "ib1", "ib1b"}));
     CHECK(t.toString().find("gpu2 0000:9b:00.0 numa 1: 0000:9c:00.0(ib1,ib1b;d=4)") != std::string::npos);
     CHECK(nixl::pciTopology::scan(base + "/absent").gpus().empty());
+    std::filesystem::remove_all(base);
 }
 
 TEST_CASE(clocks_durations_identifiers_and_strings) {
