@@ -689,6 +689,7 @@ private:
             while ((eol = pending.find("\r\n")) == std::string::npos)
                 if (!need(pending.size() + 1)) return false;
             const size_t n = std::strtoul(pending.c_str(), nullptr, 16);
+            if (n > (64u << 20)) return false; // no answer this client reads in chunks is anywhere near that: do not trust the stream
             pending.erase(0, eol + 2);
             if (!need(n + 2)) return false;
             if (n == 0) return true; // (trailers are not used by S3)

@@ -244,6 +244,52 @@ TEST_CASE(the_s3_client_against_the_stand_in_service) {
     CHECK(intruder.lastError().find("SignatureDoesNotMatch") != std::string::npos);
 }
 
+TEST_CASE(answers_that_lie_about_their_length_do_not_take_the_client_down) {
+    // A server of this test's own: accepts one connection at a time and answers every request with what the list says.
+    // What a broken proxy or a hostile endpoint can send: a chunk size beyond all bounds, a status line that is none,
+    // headers without end, a length that is never delivered.
+    const int lfd = ::socket(AF_INET, SOCK_STREAM, 0);
+    sockaddr_in sa{};
+    sa.sin_family = AF_INET;
+    sa.sin_addr.s_addr = htonl(INADDR_LOOPBACK);
+    socklen_t len = sizeof(sa);
+    CHECK(lfd >= 0 && ::bind(lfd, reinterpret_cast<sockaddr *>(&sa), sizeof(sa)) == 0 && ::listen(lfd, 8) == 0 &&
+          ::getsockname(lfd, reinterpret_cast<sockaddr *>(&sa), &len) == 0);
+    const std::vector<std::string> answers = {
+        "HTTP/1.1 500 Oops\r\nTransfer-Encoding: chunked\r\n\r\nffffffffffffffff\r\nabc",
+        "HTTP/1.1 200 OK\r\nTransfer-Encoding: chunked\r\n\r\n7fffffff\r\nabc",
+        "this is not HTTP at all\r\n\r\n",
+        "HTTP/1.1 200 OK\r\nContent-Length: 1000000\r\n\r\nshort",
+        std::string("HTTP/1.1 200 OK\r\n") + std::string(1100000, 'x'),
+        "HTTP/1.1 206 Partial\r\nContent-Length: 99999999999999999999\r\n\r\n",
+    };
+    std::thread server([&] {
+        for (const std::string &answer : answers) {
+            const int fd = ::accept(lfd, nullptr, nullptr);
+            if (fd < 0) return;
+            char req[4096];
+            (void)!::recv(fd, req, sizeof(req), 0);
+            (void)!::send(fd, answer.data(), answer.size(), MSG_NOSIGNAL);
+            ::close(fd);
+        }
+    });
+    Config cfg;
+    cfg.scheme = "http";
+    cfg.host = "127.0.0.1";
+    cfg.port = ntohs(sa.sin_port);
+    cfg.bucket = "b";
+    cfg.maxAttempts = 1;
+    cfg.timeoutMs = 2000;
+    std::vector<uint8_t> sink(4096);
+    for (size_t i = 0; i < answers.size(); ++i) {
+        Client c(cfg); // a client of its own each time: no connection is carried over
+        const int st = c.getObject("k", 0, sink.data(), sink.size());
+        CHECK(st == 0 || st >= 400); // no answer worth the name, never success, never a crash
+    }
+    server.join();
+    ::close(lfd);
+}
+
 TEST_CASE(the_azure_client_against_the_stand_in_service) {
     const std::string key = nixl_azure::base64Encode(reinterpret_cast<const uint8_t *>("a key for the native suite"), 26);
     Service svc("fake_azure_blob_server.py", "--account acct --container kv --key " + key);
