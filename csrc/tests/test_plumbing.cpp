@@ -377,6 +377,62 @@ TEST_CASE(topology_orders_network_interfaces_by_their_place_in_the_pci_tree) {
     std::filesystem::remove_all(base);
 }
 
+TEST_CASE(topology_of_an_eight_gpu_box_gives_every_gpu_its_own_nic_first) {
+    // The shape of an HGX B200 node with eight fabric NICs (two sockets, two root complexes each, one PCIe switch per
+    // root complex with two GPUs and their two NICs behind separate downstream ports of it): every GPU's nearest NIC is
+    // the one behind the neighbouring port, then the other NIC of its switch, then the same socket, then the other.
+    char tmpl[] = "/tmp/nixl_topo8_XXXXXX";
+    CHECK(::mkdtemp(tmpl) != nullptr);
+    const std::string base = tmpl, bus = base + "/bus";
+    CHECK(::mkdir(bus.c_str(), 0755) == 0);
+    auto mkdirs = [](const std::string &path) {
+        for (size_t i = 1; i <= path.size(); ++i)
+            if (i == path.size() || path[i] == '/') ::mkdir(path.substr(0, i).c_str(), 0755);
+    };
+    auto add = [&](const std::string &chain, const char *vendor, const char *cls, int numa, const std::string &netif) {
+        const std::string dir = base + "/devices/" + chain;
+        mkdirs(dir);
+        std::ofstream(dir + "/vendor") << vendor << "\n";
+        std::ofstream(dir + "/class") << cls << "\n";
+        std::ofstream(dir + "/device") << "0x2901\n";
+        std::ofstream(dir + "/numa_node") << numa << "\n";
+        if (!netif.empty()) mkdirs(dir + "/net/" + netif);
+        CHECK(::symlink(dir.c_str(), (bus + "/" + chain.substr(chain.rfind('/') + 1)).c_str()) == 0);
+    };
+    char buf[256];
+    // root complexes 0x10, 0x30 on socket 0 and 0x90, 0xb0 on socket 1; bus numbers grow with the GPU number
+    const int roots[4] = {0x10, 0x30, 0x90, 0xb0};
+    for (int sw = 0; sw < 4; ++sw) {
+        const int r = roots[sw], numa = sw / 2;
+        for (int k = 0; k < 2; ++k) { // two GPU + NIC pairs per switch; a pair shares a second-level bridge
+            const int gpu = sw * 2 + k;
+            std::snprintf(buf, sizeof(buf), "pci0000:%02x/0000:%02x:01.0/0000:%02x:00.0/0000:%02x:0%d.0/0000:%02x:00.0/0000:%02x:00.0", r, r, r + 1, r + 2, k,
+                          r + 3 + 4 * k, r + 4 + 4 * k);
+            add(buf, "0x10de", "0x030200", numa, "");
+            std::snprintf(buf, sizeof(buf), "pci0000:%02x/0000:%02x:01.0/0000:%02x:00.0/0000:%02x:0%d.0/0000:%02x:00.0/0000:%02x:01.0", r, r, r + 1, r + 2, k,
+                          r + 3 + 4 * k, r + 4 + 4 * k);
+            add(buf, "0x1d0f", "0x020000", numa, "rdmap" + std::to_string(gpu));
+        }
+    }
+    const nixl::pciTopology t = nixl::pciTopology::scan(bus);
+    CHECK_EQ(t.gpus().size(), size_t(8));
+    CHECK_EQ(t.nics().size(), size_t(8));
+    for (size_t g = 0; g < 8; ++g) {
+        const std::vector<std::string> order = t.interfacesNearGpu(g);
+        CHECK_EQ(order.size(), size_t(8));
+        CHECK(order[0] == "rdmap" + std::to_string(g));           // its own
+        CHECK(order[1] == "rdmap" + std::to_string(g ^ 1));       // the other pair of its switch
+        const size_t socket_first = (g / 4) * 4;
+        for (size_t k = 2; k < 4; ++k) CHECK(order[k] == "rdmap" + std::to_string(socket_first + (((g % 4) / 2) ^ 1) * 2 + (k - 2))); // same socket, other root
+        for (size_t k = 4; k < 8; ++k) CHECK(order[k][5] - '0' >= 0 && (static_cast<size_t>(order[k][5] - '0') / 4) != g / 4);            // the other socket last
+        CHECK_EQ(nixl::pciTopology::distance(t.gpus()[g], *t.nicsNearGpu(g)[0]), 2);
+        CHECK(nixl::pciTopology::distance(t.gpus()[g], *t.nicsNearGpu(g)[1]) < 100);
+        CHECK(nixl::pciTopology::distance(t.gpus()[g], *t.nicsNearGpu(g)[2]) > 100 && nixl::pciTopology::distance(t.gpus()[g], *t.nicsNearGpu(g)[2]) < 200);
+        CHECK(nixl::pciTopology::distance(t.gpus()[g], *t.nicsNearGpu(g)[7]) > 200);
+    }
+    std::filesystem::remove_all(base);
+}
+
 TEST_CASE(clocks_durations_identifiers_and_strings) {
     using namespace nixl_util;
     // the cycle-counter clock follows the steady clock
