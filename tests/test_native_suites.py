@@ -217,3 +217,11 @@ def test_native_nixlbench_two_processes_find_each_other_through_etcd():
                 p.kill()
             if p is not None:
                 p.wait()
+
+
+def test_native_nixlbench_schemes_over_the_tcp_backend():
+    """Several initiators and targets at once over the sockets: six flows, each with connections of its own."""
+    res = _nixlbench("--backend", "TCP", "--mem", "DRAM", "--scheme", "tp", "--num-initiator-dev", "2", "--num-target-dev", "3", "--min", "65536",
+                     "--max", "262144", "--batch", "3", "--iters", "10", "--warmup", "2", "--check")
+    assert res.returncode == 0, res.stdout + res.stderr
+    assert "6 flow(s), DRAM" in res.stdout and len([l for l in res.stdout.splitlines() if l and l[0].isdigit()]) == 3
