@@ -29,7 +29,7 @@ def _block_rows(caches: Sequence[torch.Tensor]):
         if not t.is_contiguous():
             raise ValueError("cache tensors must be contiguous (a block is one run of bytes)")
         nbytes = t[0].numel() * t.element_size()
-        dev = t.device.index if t.is_cuda else 0
+        dev = t.get_device() if t.is_cuda else 0
         base = t.data_ptr()
         rows.extend((base + b * nbytes, nbytes, dev) for b in range(blocks))
     return rows, blocks
