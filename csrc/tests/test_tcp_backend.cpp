@@ -635,6 +635,59 @@ TEST_CASE(a_peer_that_falls_silent_inside_an_exchange_is_given_up) {
     CHECK_EQ(ini.deregisterMem(rs), NIXL_SUCCESS);
 }
 
+TEST_CASE(every_thread_configuration_of_the_agent_drives_the_backend) {
+    // The agent with and without a progress thread, unsynchronised, read-write and strict: the same scattered WRITE, READ
+    // and notification under each (the reference runs its transfer tests over this matrix).
+    struct Variant {
+        const char *name;
+        bool progress;
+        nixl_thread_sync_t sync;
+    };
+    const Variant variants[] = {{"poll", false, nixl_thread_sync_t::NIXL_THREAD_SYNC_NONE},
+                                {"poll_rw", false, nixl_thread_sync_t::NIXL_THREAD_SYNC_RW},
+                                {"progress_strict", true, nixl_thread_sync_t::NIXL_THREAD_SYNC_STRICT},
+                                {"progress_rw", true, nixl_thread_sync_t::NIXL_THREAD_SYNC_RW}};
+    for (const Variant &v : variants) {
+        const nixlAgentConfig cfg(v.progress, false, 0, v.sync);
+        nixlAgent a(std::string("tcp_v_a_") + v.name, cfg), b(std::string("tcp_v_b_") + v.name, cfg);
+        nixlBackendH *h = nullptr;
+        CHECK(a.createBackend("TCP", {{"address", "127.0.0.1"}, {"chunk_bytes", "65536"}}, h) == NIXL_SUCCESS);
+        CHECK(b.createBackend("TCP", {{"address", "127.0.0.1"}, {"chunk_bytes", "65536"}}, h) == NIXL_SUCCESS);
+        std::vector<uint8_t> src(1 << 20), dst(1 << 20, 0);
+        for (size_t i = 0; i < src.size(); ++i) src[i] = static_cast<uint8_t>(i * 11 + (i >> 8));
+        nixl_reg_dlist_t ra(DRAM_SEG), rb(DRAM_SEG);
+        ra.addDesc(nixlBlobDesc(reinterpret_cast<uintptr_t>(src.data()), src.size(), 0, ""));
+        rb.addDesc(nixlBlobDesc(reinterpret_cast<uintptr_t>(dst.data()), dst.size(), 0, ""));
+        CHECK(a.registerMem(ra) == NIXL_SUCCESS && b.registerMem(rb) == NIXL_SUCCESS);
+        nixl_blob_t md;
+        std::string name;
+        b.getLocalMD(md);
+        CHECK_EQ(a.loadRemoteMD(md, name), NIXL_SUCCESS);
+        nixl_xfer_dlist_t l(DRAM_SEG), r(DRAM_SEG);
+        for (int i = 0; i < 16; ++i) {
+            l.addDesc(nixlBasicDesc(reinterpret_cast<uintptr_t>(src.data()) + size_t(i) * 65000, 60000 + size_t(i), 0));
+            r.addDesc(nixlBasicDesc(reinterpret_cast<uintptr_t>(dst.data()) + size_t(15 - i) * 65000, 60000 + size_t(i), 0));
+        }
+        nixl_opt_args_t args;
+        args.notif = v.name;
+        nixlXferReqH *w = nullptr, *rd = nullptr;
+        CHECK_EQ(a.createXferReq(NIXL_WRITE, l, r, name, w, &args), NIXL_SUCCESS);
+        CHECK(a.postXferReq(w) >= 0);
+        CHECK_EQ(waitDone(a, w), NIXL_SUCCESS);
+        for (int i = 0; i < 16; ++i) CHECK(std::memcmp(src.data() + size_t(i) * 65000, dst.data() + size_t(15 - i) * 65000, 60000 + size_t(i)) == 0);
+        auto got = collect(b, std::string("tcp_v_a_") + v.name, 1);
+        CHECK_EQ(got.size(), size_t(1));
+        CHECK(got[0] == v.name);
+        for (auto &x : dst) x = static_cast<uint8_t>(x + 1);
+        CHECK_EQ(a.createXferReq(NIXL_READ, l, r, name, rd), NIXL_SUCCESS);
+        CHECK(a.postXferReq(rd) >= 0);
+        CHECK_EQ(waitDone(a, rd), NIXL_SUCCESS);
+        for (int i = 0; i < 16; ++i) CHECK(std::memcmp(src.data() + size_t(i) * 65000, dst.data() + size_t(15 - i) * 65000, 60000 + size_t(i)) == 0);
+        CHECK(a.releaseXferReq(w) == NIXL_SUCCESS && a.releaseXferReq(rd) == NIXL_SUCCESS);
+        CHECK(a.deregisterMem(ra) == NIXL_SUCCESS && b.deregisterMem(rb) == NIXL_SUCCESS);
+    }
+}
+
 TEST_CASE(between_two_processes_and_a_target_that_exits) {
     constexpr size_t kBytes = 6 << 20;
     struct Shared {
