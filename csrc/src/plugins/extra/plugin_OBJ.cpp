@@ -20,8 +20,9 @@
 //     signature; blobs of at least `crtMinLimit` bytes go up as blocks side by side.  An `account_url` with
 //     `account_key` (or $AZURE_STORAGE_KEY) or `sas_token` (or $AZURE_STORAGE_SAS_TOKEN) beside it does the same.  With
 //     only an `account_url` (Entra ID sign-in, not built) the directory store answers, with a warning.
-//   * INFINIA (`dataset`; src/plugins/infinia): the directory store only; its cluster and tenant parameters are
-//     accepted and ignored: there is no client for that service.
+//   * INFINIA (`dataset`; src/plugins/infinia): there is no client for that appliance's own protocol; its cluster and
+//     tenant parameters are accepted and ignored.  The directory store answers, or, when `endpoint_override` names an
+//     S3-compatible endpoint, the S3 client with `dataset` as the bucket.
 #ifndef NIXL_OBJ_PLUGIN_NAME
 #define NIXL_OBJ_PLUGIN_NAME "OBJ"
 #endif
@@ -94,13 +95,15 @@ class ObjEngine final : public nixlBackendEngine {
 public:
     explicit ObjEngine(const nixlBackendInitParams *p) : nixlBackendEngine(p) {
         std::string v;
-        const bool is_s3 = std::strcmp(NIXL_OBJ_PLUGIN_NAME, "OBJ") == 0, is_azure = std::strcmp(NIXL_OBJ_PLUGIN_NAME, "AZURE_BLOB") == 0;
+        // (INFINIA: no client for the appliance's own protocol here, but an S3-compatible endpoint, if the deployment
+        // offers one, is served like any other: `endpoint_override`, with `dataset` naming the bucket.)
+        const bool is_azure = std::strcmp(NIXL_OBJ_PLUGIN_NAME, "AZURE_BLOB") == 0, is_s3 = !is_azure;
         if ((is_s3 && !setupS3()) || (is_azure && !setupAzure())) {
             initErr = true;
             return;
         }
-        if (!s3_ && !is_s3)
-            NIXL_WARN << NIXL_OBJ_PLUGIN_NAME << " backend: " << (is_azure ? "no connection string was given" : "this build has no client for that service")
+        if (!s3_ && std::strcmp(NIXL_OBJ_PLUGIN_NAME, "OBJ") != 0)
+            NIXL_WARN << NIXL_OBJ_PLUGIN_NAME << " backend: " << (is_azure ? "no connection string was given" : "this build has no client for that service and no S3 endpoint was named")
                       << "; objects are files in a local directory";
         if (!s3_) {
             if (getInitParam(NIXL_OBJ_BUCKET_PARAM, v) == NIXL_SUCCESS && !v.empty()) dir_ = v;

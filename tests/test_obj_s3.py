@@ -385,3 +385,16 @@ def test_any_key_a_caller_may_think_of_round_trips(s3):
     check()
     stored = s3.admin("keys")["kv-cache"]
     assert sorted(stored) == sorted(seen) and s3.admin("stats")["bad_signature"] == 0
+
+
+def test_the_infinia_name_reaches_an_s3_compatible_endpoint(s3):
+    """INFINIA has no client of its own here; with an endpoint named it is the S3 client, `dataset` being the bucket."""
+    import nixl_b200
+
+    nixl_b200.add_plugin_directory(nixl_b200.STANDIN_PLUGIN_DIR)
+    a = nixl_agent("s3_inf", nixl_agent_config(backends=[]))
+    a.create_backend("INFINIA", dict(KEYS, dataset="kv-cache", endpoint_override=s3.endpoint, cluster="c", tenant="t"))
+    src = torch.arange(2048, dtype=torch.int16)
+    a.register_memory(src)
+    assert torch.equal(_roundtrip(a, "s3_inf", "from-infinia-name.bin", src), src)
+    assert "from-infinia-name.bin" in s3.admin("keys")["kv-cache"] and s3.admin("stats")["bad_signature"] == 0
