@@ -423,6 +423,11 @@ TEST_CASE(a_listener_survives_strangers_and_garbage) {
     nixlBackendH *h = nullptr;
     CHECK_EQ(a.createBackend("TCP", {{"address", "127.0.0.1"}}, h), NIXL_SUCCESS);
     CHECK_EQ(b.createBackend("TCP", {{"address", "127.0.0.1"}, {"port", std::to_string(port)}, {"connect_timeout_ms", "400"}}, h), NIXL_SUCCESS);
+    {   // the port is taken now: a second engine that insists on it does not come up
+        nixlAgent late("tcp_g_late", nixlAgentConfig(false));
+        nixlBackendH *none = nullptr;
+        CHECK(late.createBackend("TCP", {{"port", std::to_string(port)}}, none) != NIXL_SUCCESS);
+    }
     std::vector<uint8_t> src(1 << 20, 0x3c), dst(1 << 20, 0);
     nixl_reg_dlist_t ra(DRAM_SEG), rb(DRAM_SEG);
     ra.addDesc(nixlBlobDesc(reinterpret_cast<uintptr_t>(src.data()), src.size(), 0, ""));
