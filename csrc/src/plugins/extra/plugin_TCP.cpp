@@ -9,8 +9,8 @@
 //
 // Shape
 //   * Every engine listens on one port ("port" parameter, default: any).  The connection info it publishes holds the
-//     host name, the port and the addresses to try (the "address" parameter or NIXL_TCP_ADDRESS; otherwise every IPv4
-//     address of the host, loopback last; a peer on the same host tries loopback first).  `device_id` names the GPU
+//     host name, the port and the addresses to try (the "address" parameter or NIXL_TCP_ADDRESS; otherwise every IPv4 and
+//     global IPv6 address of the host, loopback last; a peer on the same host tries loopback first).  `device_id` names the GPU
 //     this engine serves: the interfaces nearest to it in the PCI tree (utils/topology.h) come first.  With several
 //     addresses published, and `local_addresses` (a list, or "auto") on the initiator, connection k of a peer runs from
 //     local address k to the peer's address k: the rails spread over the interfaces of both hosts.
@@ -186,23 +186,45 @@ void tuneSocket(int fd, int buf_bytes) {
     }
 }
 
+// A numeric IPv4 or IPv6 address (the latter with or without brackets) as a socket address.
+bool toSockaddr(std::string ip, uint16_t port, sockaddr_storage &out, socklen_t &len) {
+    if (ip.size() > 2 && ip.front() == '[' && ip.back() == ']') ip = ip.substr(1, ip.size() - 2);
+    std::memset(&out, 0, sizeof(out));
+    auto *a4 = reinterpret_cast<sockaddr_in *>(&out);
+    auto *a6 = reinterpret_cast<sockaddr_in6 *>(&out);
+    if (::inet_pton(AF_INET, ip.c_str(), &a4->sin_addr) == 1) {
+        a4->sin_family = AF_INET;
+        a4->sin_port = htons(port);
+        len = sizeof(sockaddr_in);
+        return true;
+    }
+    if (::inet_pton(AF_INET6, ip.c_str(), &a6->sin6_addr) == 1) {
+        a6->sin6_family = AF_INET6;
+        a6->sin6_port = htons(port);
+        len = sizeof(sockaddr_in6);
+        return true;
+    }
+    return false;
+}
+
+bool isLoopback(const std::string &a) { return a.compare(0, 4, "127.") == 0 || a == "::1" || a == "[::1]"; }
+
 // `from`: the local address to leave from (empty: the kernel's choice by route).
 int connectTo(const std::string &ip, uint16_t port, int timeout_ms, const std::string &from = "") {
-    sockaddr_in a{};
-    a.sin_family = AF_INET;
-    a.sin_port = htons(port);
-    if (::inet_pton(AF_INET, ip.c_str(), &a.sin_addr) != 1) return -1;
-    const int fd = ::socket(AF_INET, SOCK_STREAM | SOCK_NONBLOCK | SOCK_CLOEXEC, 0);
+    sockaddr_storage a;
+    socklen_t alen = 0;
+    if (!toSockaddr(ip, port, a, alen)) return -1;
+    const int fd = ::socket(a.ss_family, SOCK_STREAM | SOCK_NONBLOCK | SOCK_CLOEXEC, 0);
     if (fd < 0) return -1;
     if (!from.empty()) {
-        sockaddr_in l{};
-        l.sin_family = AF_INET;
-        if (::inet_pton(AF_INET, from.c_str(), &l.sin_addr) != 1 || ::bind(fd, reinterpret_cast<sockaddr *>(&l), sizeof(l)) != 0) {
+        sockaddr_storage l;
+        socklen_t llen = 0;
+        if (!toSockaddr(from, 0, l, llen) || l.ss_family != a.ss_family || ::bind(fd, reinterpret_cast<sockaddr *>(&l), llen) != 0) {
             ::close(fd);
             return -1;
         }
     }
-    int rc = ::connect(fd, reinterpret_cast<sockaddr *>(&a), sizeof(a));
+    int rc = ::connect(fd, reinterpret_cast<sockaddr *>(&a), alen);
     if (rc != 0 && errno == EINPROGRESS) {
         pollfd p{fd, POLLOUT, 0};
         int err = 0;
@@ -232,21 +254,29 @@ std::vector<std::string> orderByInterface(std::vector<std::pair<std::string, std
     return out;
 }
 
-// The host's IPv4 addresses: interfaces near GPU `gpu` first when that is known (< 0: as the kernel lists them),
+// The host's addresses (IPv4, then global IPv6): interfaces near GPU `gpu` first when that is known (< 0: as the kernel lists them),
 // loopback last.
 std::vector<std::string> hostAddresses(int gpu) {
     std::vector<std::pair<std::string, std::string>> found;
     std::vector<std::string> loop;
     ifaddrs *ifs = nullptr;
     if (::getifaddrs(&ifs) == 0) {
+        std::vector<std::pair<std::string, std::string>> found6;
         for (ifaddrs *i = ifs; i; i = i->ifa_next) {
-            if (!i->ifa_addr || i->ifa_addr->sa_family != AF_INET || !(i->ifa_flags & IFF_UP)) continue;
-            char buf[INET_ADDRSTRLEN];
-            if (!::inet_ntop(AF_INET, &reinterpret_cast<sockaddr_in *>(i->ifa_addr)->sin_addr, buf, sizeof(buf))) continue;
-            if (i->ifa_flags & IFF_LOOPBACK) loop.push_back(buf);
-            else found.emplace_back(i->ifa_name, buf);
+            if (!i->ifa_addr || !(i->ifa_flags & IFF_UP)) continue;
+            char buf[INET6_ADDRSTRLEN];
+            if (i->ifa_addr->sa_family == AF_INET) {
+                if (!::inet_ntop(AF_INET, &reinterpret_cast<sockaddr_in *>(i->ifa_addr)->sin_addr, buf, sizeof(buf))) continue;
+                if (i->ifa_flags & IFF_LOOPBACK) loop.push_back(buf);
+                else found.emplace_back(i->ifa_name, buf);
+            } else if (i->ifa_addr->sa_family == AF_INET6) {
+                const in6_addr &a6 = reinterpret_cast<sockaddr_in6 *>(i->ifa_addr)->sin6_addr;
+                if (IN6_IS_ADDR_LINKLOCAL(&a6) || (i->ifa_flags & IFF_LOOPBACK)) continue; // link-local needs a scope; loopback: the IPv4 one does
+                if (::inet_ntop(AF_INET6, &a6, buf, sizeof(buf))) found6.emplace_back(i->ifa_name, buf);
+            }
         }
         ::freeifaddrs(ifs);
+        found.insert(found.end(), found6.begin(), found6.end()); // IPv4 first: what most clusters route
     }
     std::vector<std::string> near;
     if (gpu >= 0) near = nixl::pciTopology::scan().interfacesNearGpu(static_cast<size_t>(gpu));
@@ -647,28 +677,42 @@ public:
         it = cp.find("local_addresses");
         if (it != cp.end() && it->second == "auto") {
             for (const auto &a2 : hostAddresses(gpu))
-                if (a2.compare(0, 4, "127.") != 0) localAddrs_.push_back(a2);
+                if (!isLoopback(a2)) localAddrs_.push_back(a2);
         } else if (it != cp.end() && !it->second.empty()) {
             localAddrs_ = nixl_util::split(it->second, ',');
         }
 
-        listenFd_ = ::socket(AF_INET, SOCK_STREAM | SOCK_CLOEXEC, 0);
-        sockaddr_in a{};
-        a.sin_family = AF_INET;
-        a.sin_addr.s_addr = htonl(INADDR_ANY);
-        a.sin_port = htons(static_cast<uint16_t>(port));
-        const int one = 1;
+        // One socket for both families where the host has IPv6 (an IPv6 socket that also takes IPv4), else IPv4 alone.
+        const int one = 1, zero = 0;
+        sockaddr_storage a{};
+        socklen_t len = 0;
+        listenFd_ = ::socket(AF_INET6, SOCK_STREAM | SOCK_CLOEXEC, 0);
+        if (listenFd_ >= 0 && ::setsockopt(listenFd_, IPPROTO_IPV6, IPV6_V6ONLY, &zero, sizeof(zero)) == 0) {
+            auto *a6 = reinterpret_cast<sockaddr_in6 *>(&a);
+            a6->sin6_family = AF_INET6;
+            a6->sin6_addr = in6addr_any;
+            a6->sin6_port = htons(static_cast<uint16_t>(port));
+            len = sizeof(sockaddr_in6);
+        } else {
+            if (listenFd_ >= 0) ::close(listenFd_);
+            listenFd_ = ::socket(AF_INET, SOCK_STREAM | SOCK_CLOEXEC, 0);
+            auto *a4 = reinterpret_cast<sockaddr_in *>(&a);
+            a4->sin_family = AF_INET;
+            a4->sin_addr.s_addr = htonl(INADDR_ANY);
+            a4->sin_port = htons(static_cast<uint16_t>(port));
+            len = sizeof(sockaddr_in);
+        }
         if (listenFd_ >= 0) ::setsockopt(listenFd_, SOL_SOCKET, SO_REUSEADDR, &one, sizeof(one));
-        socklen_t len = sizeof(a);
-        if (listenFd_ < 0 || ::bind(listenFd_, reinterpret_cast<sockaddr *>(&a), sizeof(a)) != 0 || ::listen(listenFd_, 128) != 0 ||
-            ::getsockname(listenFd_, reinterpret_cast<sockaddr *>(&a), &len) != 0) {
+        socklen_t got = sizeof(a);
+        if (listenFd_ < 0 || ::bind(listenFd_, reinterpret_cast<sockaddr *>(&a), len) != 0 || ::listen(listenFd_, 128) != 0 ||
+            ::getsockname(listenFd_, reinterpret_cast<sockaddr *>(&a), &got) != 0) {
             NIXL_ERROR << "TCP backend: cannot listen on port " << port << ": " << std::strerror(errno);
             if (listenFd_ >= 0) ::close(listenFd_);
             listenFd_ = -1;
             initErr = true;
             return;
         }
-        port_ = ntohs(a.sin_port);
+        port_ = ntohs(a.ss_family == AF_INET6 ? reinterpret_cast<sockaddr_in6 *>(&a)->sin6_port : reinterpret_cast<sockaddr_in *>(&a)->sin_port);
         listener_ = std::thread([this] { acceptLoop(); });
     }
 
@@ -1041,7 +1085,7 @@ private:
     std::shared_ptr<ClientConn> dial(const Peer &peer, size_t rail) const {
         std::vector<std::string> order;
         const bool same_host = peer.host == host_;
-        auto is_loop = [](const std::string &a) { return a.compare(0, 4, "127.") == 0; };
+        auto is_loop = [](const std::string &a) { return isLoopback(a); };
         if (same_host)
             for (const auto &a : peer.addrs)
                 if (is_loop(a)) order.push_back(a);

@@ -693,6 +693,44 @@ TEST_CASE(every_thread_configuration_of_the_agent_drives_the_backend) {
     }
 }
 
+TEST_CASE(peers_reach_each_other_over_ipv6_too) {
+    // The listener takes both families; a target that publishes an IPv6 address is reached there (the loopback one
+    // here), and one that publishes both is reached over either, the rails taking turns.
+    int probe = ::socket(AF_INET6, SOCK_STREAM, 0);
+    sockaddr_in6 lo{};
+    lo.sin6_family = AF_INET6;
+    lo.sin6_addr = in6addr_loopback;
+    const bool have_v6 = probe >= 0 && ::bind(probe, reinterpret_cast<sockaddr *>(&lo), sizeof(lo)) == 0;
+    if (probe >= 0) ::close(probe);
+    if (!have_v6) {
+        std::printf("  (no IPv6 on this host: left out)\n");
+        return;
+    }
+    for (const char *published : {"::1", "[::1],127.0.0.1"}) {
+        Pair p(2 << 20, {{"address", published}, {"rails", "2"}, {"chunk_bytes", "262144"}});
+        nixl_opt_args_t args;
+        args.notif = "six";
+        nixlXferReqH *w = p.request(NIXL_WRITE, {{0, 0, p.src.size()}}, &args);
+        CHECK(p.a->postXferReq(w) >= 0);
+        CHECK_EQ(waitDone(*p.a, w), NIXL_SUCCESS);
+        CHECK(p.src == p.dst);
+        CHECK_EQ(collect(*p.b, p.an, 1).size(), size_t(1));
+        CHECK_EQ(p.a->releaseXferReq(w), NIXL_SUCCESS);
+        // the connections that carried it: at least one of them between IPv6 loopback addresses
+        std::ifstream tcp6("/proc/net/tcp6");
+        std::string line;
+        int v6 = 0;
+        while (std::getline(tcp6, line)) {
+            std::istringstream is(line);
+            std::string sl, local, remote, state;
+            if ((is >> sl >> local >> remote >> state) && state == "01" && local.compare(0, 32, "00000000000000000000000001000000") == 0 &&
+                remote.compare(0, 32, "00000000000000000000000001000000") == 0)
+                ++v6;
+        }
+        if (tcp6.is_open() || v6) CHECK(v6 >= 2); // both ends of a connection show up
+    }
+}
+
 TEST_CASE(between_two_processes_and_a_target_that_exits) {
     constexpr size_t kBytes = 6 << 20;
     struct Shared {
