@@ -685,30 +685,36 @@ public:
         // One socket for both families where the host has IPv6 (an IPv6 socket that also takes IPv4), else IPv4 alone.
         const int one = 1, zero = 0;
         sockaddr_storage a{};
-        socklen_t len = 0;
-        listenFd_ = ::socket(AF_INET6, SOCK_STREAM | SOCK_CLOEXEC, 0);
-        if (listenFd_ >= 0 && ::setsockopt(listenFd_, IPPROTO_IPV6, IPV6_V6ONLY, &zero, sizeof(zero)) == 0) {
-            auto *a6 = reinterpret_cast<sockaddr_in6 *>(&a);
-            a6->sin6_family = AF_INET6;
-            a6->sin6_addr = in6addr_any;
-            a6->sin6_port = htons(static_cast<uint16_t>(port));
-            len = sizeof(sockaddr_in6);
-        } else {
-            if (listenFd_ >= 0) ::close(listenFd_);
-            listenFd_ = ::socket(AF_INET, SOCK_STREAM | SOCK_CLOEXEC, 0);
-            auto *a4 = reinterpret_cast<sockaddr_in *>(&a);
-            a4->sin_family = AF_INET;
-            a4->sin_addr.s_addr = htonl(INADDR_ANY);
-            a4->sin_port = htons(static_cast<uint16_t>(port));
-            len = sizeof(sockaddr_in);
-        }
-        if (listenFd_ >= 0) ::setsockopt(listenFd_, SOL_SOCKET, SO_REUSEADDR, &one, sizeof(one));
-        socklen_t got = sizeof(a);
-        if (listenFd_ < 0 || ::bind(listenFd_, reinterpret_cast<sockaddr *>(&a), len) != 0 || ::listen(listenFd_, 128) != 0 ||
-            ::getsockname(listenFd_, reinterpret_cast<sockaddr *>(&a), &got) != 0) {
+        auto listen_on = [&](int family) {
+            const int fd = ::socket(family, SOCK_STREAM | SOCK_CLOEXEC, 0);
+            if (fd < 0) return -1;
+            std::memset(&a, 0, sizeof(a));
+            socklen_t len;
+            if (family == AF_INET6) {
+                auto *a6 = reinterpret_cast<sockaddr_in6 *>(&a);
+                a6->sin6_family = AF_INET6;
+                a6->sin6_addr = in6addr_any;
+                a6->sin6_port = htons(static_cast<uint16_t>(port));
+                len = sizeof(sockaddr_in6);
+                if (::setsockopt(fd, IPPROTO_IPV6, IPV6_V6ONLY, &zero, sizeof(zero)) != 0) return ::close(fd), -1;
+            } else {
+                auto *a4 = reinterpret_cast<sockaddr_in *>(&a);
+                a4->sin_family = AF_INET;
+                a4->sin_addr.s_addr = htonl(INADDR_ANY);
+                a4->sin_port = htons(static_cast<uint16_t>(port));
+                len = sizeof(sockaddr_in);
+            }
+            ::setsockopt(fd, SOL_SOCKET, SO_REUSEADDR, &one, sizeof(one));
+            socklen_t got = sizeof(a);
+            if (::bind(fd, reinterpret_cast<sockaddr *>(&a), len) != 0 || ::listen(fd, 128) != 0 ||
+                ::getsockname(fd, reinterpret_cast<sockaddr *>(&a), &got) != 0)
+                return ::close(fd), -1;
+            return fd;
+        };
+        listenFd_ = listen_on(AF_INET6);
+        if (listenFd_ < 0) listenFd_ = listen_on(AF_INET);
+        if (listenFd_ < 0) {
             NIXL_ERROR << "TCP backend: cannot listen on port " << port << ": " << std::strerror(errno);
-            if (listenFd_ >= 0) ::close(listenFd_);
-            listenFd_ = -1;
             initErr = true;
             return;
         }
