@@ -355,7 +355,16 @@ TEST_CASE(a_listener_that_is_somebody_else_is_not_taken_for_the_peer) {
 TEST_CASE(connections_spread_over_the_addresses_of_both_sides) {
     // Several interfaces on both hosts, played by addresses of the loopback network: the target publishes two, the
     // initiator leaves from two others, four connections.  The kernel's table of connections shows each pair once.
-    const nixl_b_params_t target_params = {{"address", "127.0.0.2,127.0.0.3"}, {"rails", "4"}};
+    int probe = ::socket(AF_INET, SOCK_STREAM, 0);
+    sockaddr_in sa{};
+    sa.sin_family = AF_INET;
+    sa.sin_addr.s_addr = htonl(INADDR_LOOPBACK);
+    socklen_t sa_len = sizeof(sa);
+    CHECK(probe >= 0 && ::bind(probe, reinterpret_cast<sockaddr *>(&sa), sizeof(sa)) == 0 &&
+          ::getsockname(probe, reinterpret_cast<sockaddr *>(&sa), &sa_len) == 0);
+    const uint16_t port = ntohs(sa.sin_port); // the target's listener: lets the table below be read for this test's connections only
+    ::close(probe);
+    const nixl_b_params_t target_params = {{"address", "127.0.0.2,127.0.0.3"}, {"rails", "4"}, {"port", std::to_string(port)}};
     const nixl_b_params_t initiator_params = {{"address", "127.0.0.1"}, {"local_addresses", "127.0.0.4,127.0.0.5"}, {"rails", "4"}};
     nixlAgent a("tcp_spread_a", nixlAgentConfig(false)), b("tcp_spread_b", nixlAgentConfig(false));
     nixlBackendH *ha = nullptr, *hb = nullptr;
@@ -395,7 +404,9 @@ TEST_CASE(connections_spread_over_the_addresses_of_both_sides) {
         if (!(is >> sl >> local >> remote >> state) || state != "01") continue;
         for (const char *from : {"127.0.0.4", "127.0.0.5"})
             for (const char *to : {"127.0.0.2", "127.0.0.3"})
-                if (local.compare(0, 8, hex_of(from)) == 0 && remote.compare(0, 8, hex_of(to)) == 0) ++pairs[{from, to}];
+                if (local.compare(0, 8, hex_of(from)) == 0 && remote.compare(0, 8, hex_of(to)) == 0 && remote.size() >= 13 &&
+                    std::strtoul(remote.c_str() + 9, nullptr, 16) == port)
+                    ++pairs[{from, to}];
     }
     if (!pairs.empty()) { // (a container may hide the table; the transfer above has still run)
         CHECK_EQ(pairs.size(), size_t(2)); // rail k: local k % 2 -> peer k % 2

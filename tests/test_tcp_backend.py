@@ -189,3 +189,54 @@ def test_the_agent_takes_nvlink_inside_a_box_and_tcp_across_boxes():
     # naming the backend that cannot reach the peer is an error, not a silent detour
     with pytest.raises(Exception):
         here.initialize_xfer("WRITE", src, far_dst, "box_b0", backends=["NVLINK"])
+
+
+def test_connecting_ahead_of_time_and_forgetting_a_peer():
+    """`make_connection` opens the rails before the first request; `remove_remote_agent` closes them, and a peer that is
+    added again is reached again on new ones."""
+    from nixl_b200 import nixl_agent, nixl_agent_config
+
+    port = _free_port()
+    a = nixl_agent("conn_a", nixl_agent_config(backends=[]))
+    b = nixl_agent("conn_b", nixl_agent_config(backends=[]))
+    a.create_backend("TCP", {"address": "127.0.0.1", "rails": "3"})
+    b.create_backend("TCP", {"address": "127.0.0.1", "rails": "3", "port": str(port)})
+    src = torch.arange(4096, dtype=torch.int32)
+    dst = torch.zeros_like(src)
+    a.register_memory(src)
+    b.register_memory(dst)
+    meta = b.get_agent_metadata()
+    a.add_remote_agent(meta)
+
+    def established_to_peer():
+        # the kernel's table: established connections whose far end is conn_b's listener port (the initiator's halves)
+        with open("/proc/net/tcp") as f, open("/proc/net/tcp6") as f6:
+            rows = [l.split() for l in list(f)[1:] + list(f6)[1:]]
+        return sum(1 for r in rows if r[3] == "01" and r[2].endswith(":%04X" % port))
+
+    before = established_to_peer()
+    assert before == 0
+    a.make_connection("conn_b", ["TCP"])
+    assert established_to_peer() == 3  # the rails are up before any request
+    for _ in range(2):
+        h = a.initialize_xfer("WRITE", src, dst, "conn_b")
+        state = a.transfer(h)
+        while state == "PROC":
+            state = a.check_xfer_state(h)
+        assert state == "DONE" and torch.equal(src, dst)
+        a.release_xfer_handle(h)
+        dst.zero_()
+    a.remove_remote_agent("conn_b")
+    deadline = time.time() + 5
+    while time.time() < deadline and established_to_peer() > before:
+        time.sleep(0.01)
+    assert established_to_peer() <= before  # the rails are gone (the serving ends notice and close)
+    with pytest.raises(Exception):
+        a.initialize_xfer("WRITE", src, dst, "conn_b")
+    a.add_remote_agent(meta)
+    h = a.initialize_xfer("WRITE", src, dst, "conn_b")
+    state = a.transfer(h)
+    while state == "PROC":
+        state = a.check_xfer_state(h)
+    assert state == "DONE" and torch.equal(src, dst)
+    a.release_xfer_handle(h)
